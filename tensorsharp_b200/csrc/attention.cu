@@ -1,0 +1,475 @@
+// Attention over a paged bf16 KV cache: flash prefill (varlen, causal, sliding window,
+// sinks, soft-cap, GQA) and split-KV decode with a combine pass.
+//
+// Cache layout: k_cache / v_cache are [n_slots, Hkv, Dh] bf16 with slot = page * page_size +
+// offset; block_table[b, i] is the page that holds tokens [i*page_size, (i+1)*page_size) of
+// sequence b.  A query at position p attends to cache positions j with j <= p and, when
+// window > 0, j > p - window.
+//
+// Replaces in the reference: flash_attn_ext_f16 (ggml-cuda/fattn-mma-f16.cuh:1354),
+// flash_attn_ext_vec (fattn-vec.cuh:21), flash_attn_combine_results (fattn-common.cuh:721),
+// flash_attn_mask_to_KV_max (:576), soft_max_f32 with sinks (softmax.cu:47), the batched
+// cuBLAS QK^T / PV of the non-flash prefill path (ggml-cuda.cu:2084) and the host-built masks
+// of TensorSharp.GGML.Native/ggml_ops_norm_attn.cpp:1699-1884.  Scores are never materialised.
+#include "common.cuh"
+
+struct AttnArgs {
+    const bf16* q;            // [Tq, Hq, Dh]
+    const bf16* k_cache;
+    const bf16* v_cache;
+    bf16* out;                // [Tq, Hq, Dh]
+    const int* block_table;   // [B, max_pages]
+    const int* kv_lens;       // [B] tokens in the cache for this sequence (including the new ones)
+    const int* cu_q;          // [B + 1] query offsets (prefill); null for decode (one query per sequence)
+    const float* sinks;       // [Hq] or null
+    float* part_o;            // decode scratch [B, Hq, splits, Dh]
+    float* part_ml;           // decode scratch [B, Hq, splits, 2]
+    float scale;
+    float softcap;            // 0 = off
+    int window;               // 0 = full causal
+    int B, Hq, Hkv, Dh, page_size, max_pages, splits;
+};
+
+__device__ __forceinline__ long kv_slot(const AttnArgs& a, int b, int j) {
+    const int page = a.block_table[(long)b * a.max_pages + j / a.page_size];
+    return (long)page * a.page_size + j % a.page_size;
+}
+
+// ------------------------------------------------------------------------------------------
+// Decode: grid (splits, Hkv, B), 128 threads.  All G = Hq / Hkv query heads of a KV head share
+// the K / V traffic.  Lane = token for QK^T, lane = dim slice for PV.
+// ------------------------------------------------------------------------------------------
+template <int DH, int G>
+__global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
+    constexpr int DPL = DH / 32;             // output dims per lane
+    const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int len = a.kv_lens[b];
+    const int lo = (a.window > 0 && len > a.window) ? len - a.window : 0;
+    const int span = len - lo;
+    const int per = (((span + a.splits - 1) / a.splits) + 31) & ~31;
+    const int s0 = lo + split * per, s1 = min(len, s0 + per);
+
+    __shared__ __align__(16) bf16 qs[G][DH];
+    __shared__ float red_m[4][G], red_l[4][G];
+    __shared__ float red_o[4][G][DH];
+    for (int i = threadIdx.x; i < G * DH; i += 128) {
+        const int g = i / DH, d = i % DH;
+        qs[g][d] = a.q[((long)b * a.Hq + hk * G + g) * DH + d];
+    }
+    __syncthreads();
+
+    float m[G], l[G], acc[G][DPL];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m[g] = -INFINITY;
+        l[g] = 0.f;
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) acc[g][d] = 0.f;
+    }
+    for (int base = s0 + warp * 32; base < s1; base += 128) {
+        const int j = base + lane;
+        const bool valid = j < s1;
+        const long slot = valid ? kv_slot(a, b, j) : 0;
+        float s[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) s[g] = 0.f;
+        if (valid) {
+            const uint4* kp = reinterpret_cast<const uint4*>(a.k_cache + (slot * a.Hkv + hk) * DH);
+#pragma unroll 4
+            for (int c = 0; c < DH / 8; ++c) {
+                const uint4 kv = kp[c];
+                const bf162* k2 = reinterpret_cast<const bf162*>(&kv);
+                float kf[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(k2[i]);
+                    kf[2 * i] = f.x;
+                    kf[2 * i + 1] = f.y;
+                }
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const uint4 qv = *reinterpret_cast<const uint4*>(&qs[g][c * 8]);
+                    const bf162* q2 = reinterpret_cast<const bf162*>(&qv);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = __bfloat1622float2(q2[i]);
+                        s[g] += f.x * kf[2 * i] + f.y * kf[2 * i + 1];
+                    }
+                }
+            }
+        }
+        float p[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float sv = s[g] * a.scale;
+            if (a.softcap > 0.f) sv = a.softcap * tanhf(sv / a.softcap);
+            sv = valid ? sv : -INFINITY;
+            const float mx = fmaxf(m[g], warp_max(sv));
+            const float corr = (m[g] == -INFINITY) ? 0.f : __expf(m[g] - mx);
+            p[g] = valid ? __expf(sv - mx) : 0.f;
+            l[g] = l[g] * corr + warp_sum(p[g]);
+            m[g] = mx;
+#pragma unroll
+            for (int d = 0; d < DPL; ++d) acc[g][d] *= corr;
+        }
+        const int cnt = min(32, s1 - base);
+        for (int t = 0; t < cnt; ++t) {
+            const long sl = __shfl_sync(0xffffffffu, slot, t);
+            const bf16* vp = a.v_cache + (sl * a.Hkv + hk) * DH + lane * DPL;
+            float vf[DPL];
+            if (DPL == 4) {
+                const uint2 vv = *reinterpret_cast<const uint2*>(vp);
+                const bf162* v2 = reinterpret_cast<const bf162*>(&vv);
+                const float2 f0 = __bfloat1622float2(v2[0]), f1 = __bfloat1622float2(v2[1]);
+                vf[0] = f0.x; vf[1] = f0.y; vf[2 % DPL] = f1.x; vf[3 % DPL] = f1.y;
+            } else if (DPL == 8) {
+                const uint4 vv = *reinterpret_cast<const uint4*>(vp);
+                const bf162* v2 = reinterpret_cast<const bf162*>(&vv);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(v2[i]);
+                    vf[(2 * i) % DPL] = f.x;
+                    vf[(2 * i + 1) % DPL] = f.y;
+                }
+            } else {
+#pragma unroll
+                for (int d = 0; d < DPL; ++d) vf[d] = bf2f(vp[d]);
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float pg = __shfl_sync(0xffffffffu, p[g], t);
+#pragma unroll
+                for (int d = 0; d < DPL; ++d) acc[g][d] += pg * vf[d];
+            }
+        }
+    }
+    // merge the four warps
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        if (lane == 0) { red_m[warp][g] = m[g]; red_l[warp][g] = l[g]; }
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) red_o[warp][g][lane * DPL + d] = acc[g][d];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < G * DH; i += 128) {
+        const int g = i / DH, d = i % DH;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red_m[w][g]);
+        float ll = 0.f, o = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float c = (red_m[w][g] == -INFINITY) ? 0.f : __expf(red_m[w][g] - mm);
+            ll += red_l[w][g] * c;
+            o += red_o[w][g][d] * c;
+        }
+        const long pi = ((long)b * a.Hq + hk * G + g) * a.splits + split;
+        a.part_o[pi * DH + d] = o;
+        if (d == 0) { a.part_ml[pi * 2] = mm; a.part_ml[pi * 2 + 1] = ll; }
+    }
+}
+
+// grid (Hq, B), DH threads (rounded up to 32): merge split partials, apply the sink, normalise.
+__global__ void attn_combine_kernel(AttnArgs a) {
+    const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    const long base = ((long)b * a.Hq + h) * a.splits;
+    float mm = a.sinks ? a.sinks[h] : -INFINITY;
+    for (int s = 0; s < a.splits; ++s) mm = fmaxf(mm, a.part_ml[(base + s) * 2]);
+    float ll = a.sinks ? __expf(a.sinks[h] - mm) : 0.f, o = 0.f;
+    for (int s = 0; s < a.splits; ++s) {
+        const float ms = a.part_ml[(base + s) * 2];
+        const float c = (ms == -INFINITY) ? 0.f : __expf(ms - mm);
+        ll += a.part_ml[(base + s) * 2 + 1] * c;
+        if (d < a.Dh) o += a.part_o[(base + s) * a.Dh + d] * c;
+    }
+    if (d < a.Dh) a.out[((long)b * a.Hq + h) * a.Dh + d] = f2bf(ll > 0.f ? o / ll : 0.f);
+}
+
+template <int DH>
+static int launch_decode_g(const AttnArgs& a, cudaStream_t s) {
+    dim3 grid(a.splits, a.Hkv, a.B);
+    const int G = a.Hq / a.Hkv;
+    switch (G) {
+    case 1: attn_decode_kernel<DH, 1><<<grid, 128, 0, s>>>(a); break;
+    case 2: attn_decode_kernel<DH, 2><<<grid, 128, 0, s>>>(a); break;
+    case 4: attn_decode_kernel<DH, 4><<<grid, 128, 0, s>>>(a); break;
+    case 8: attn_decode_kernel<DH, 8><<<grid, 128, 0, s>>>(a); break;
+    default:
+        tsb_set_error("attn_decode: unsupported GQA group size %d (supported 1, 2, 4, 8)", G);
+        return TSB_ERR_UNSUPPORTED;
+    }
+    return TSB_OK;
+}
+
+// Query heads per KV head above 8 are handled by the caller splitting the head group.
+extern "C" int tsb_attn_decode(const AttnArgs* args, void* stream) {
+    AttnArgs a = *args;
+    TSB_CHECK_ARG(a.Hkv > 0 && a.Hq % a.Hkv == 0, "attn_decode: Hq=%d not a multiple of Hkv=%d", a.Hq, a.Hkv);
+    TSB_CHECK_ARG(a.splits >= 1 && a.part_o && a.part_ml, "attn_decode: scratch for %d splits missing", a.splits);
+    if (a.B == 0) return TSB_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    int rc;
+    switch (a.Dh) {
+    case 64: rc = launch_decode_g<64>(a, s); break;
+    case 128: rc = launch_decode_g<128>(a, s); break;
+    case 256: rc = launch_decode_g<256>(a, s); break;
+    default:
+        tsb_set_error("attn_decode: unsupported head dim %d (supported 64, 128, 256)", a.Dh);
+        return TSB_ERR_UNSUPPORTED;
+    }
+    if (rc != TSB_OK) return rc;
+    TSB_CHECK_LAUNCH();
+    attn_combine_kernel<<<dim3(a.Hq, a.B), (a.Dh + 31) & ~31, 0, s>>>(a);
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// Prefill: flash attention on mma.sync m16n8k16 bf16, 64 queries x one head per CTA, 64-token
+// KV tiles streamed with cp.async double buffering from the paged cache.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t* r, const void* p) {
+    const uint32_t sa = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(sa));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t* r, const void* p) {
+    const uint32_t sa = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(sa));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    bf162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Tile row r, 16-byte chunk c of a [rows][DH] bf16 tile with an XOR swizzle over 8 rows.
+template <int DH>
+__device__ __forceinline__ bf16* tile_ptr(bf16* base, int r, int c) {
+    return base + r * DH + ((c ^ (r & 7)) << 3);
+}
+
+template <int DH>
+__global__ void __launch_bounds__(128) attn_prefill_kernel(AttnArgs a) {
+    constexpr int BM = 64, BN = 64, CH = DH / 8;   // CH = 16-byte chunks per row
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
+    bf16* sK = sQ + BM * DH;         // 2 stages
+    bf16* sV = sK + 2 * BN * DH;     // 2 stages
+
+    const int b = blockIdx.z, h = blockIdx.y, hk = h / (a.Hq / a.Hkv);
+    const int q0 = a.cu_q[b], qlen = a.cu_q[b + 1] - q0;
+    const int m0 = blockIdx.x * BM;
+    if (m0 >= qlen) return;
+    const int kvlen = a.kv_lens[b];
+    const int pos0 = kvlen - qlen;                 // cache position of the sequence's first query
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rows = min(BM, qlen - m0);
+
+    // KV range needed by this query tile
+    const int p_last = pos0 + m0 + rows - 1;
+    int j_lo = 0;
+    if (a.window > 0) j_lo = max(0, pos0 + m0 - a.window + 1);
+    const int j_hi = p_last + 1;                   // exclusive
+    const int t_lo = j_lo / BN, t_hi = (j_hi + BN - 1) / BN;
+
+    // Q tile -> shared (rows beyond the sequence are zero)
+    for (int i = threadIdx.x; i < BM * CH; i += 128) {
+        const int r = i / CH, c = i % CH;
+        bf16* dst = tile_ptr<DH>(sQ, r, c);
+        if (r < rows) cp_async16(dst, a.q + ((long)(q0 + m0 + r) * a.Hq + h) * DH + c * 8);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+    auto load_kv = [&](int t, int stage) {
+        bf16* dk = sK + stage * BN * DH;
+        bf16* dv = sV + stage * BN * DH;
+        for (int i = threadIdx.x; i < BN * CH; i += 128) {
+            const int r = i / CH, c = i % CH;
+            const int j = t * BN + r;
+            bf16* pk = tile_ptr<DH>(dk, r, c);
+            bf16* pv = tile_ptr<DH>(dv, r, c);
+            if (j < kvlen) {
+                const long off = (kv_slot(a, b, j) * a.Hkv + hk) * DH + c * 8;
+                cp_async16(pk, a.k_cache + off);
+                cp_async16(pv, a.v_cache + off);
+            } else {
+                *reinterpret_cast<uint4*>(pk) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(pv) = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    load_kv(t_lo, 0);
+    cp_async_commit();
+
+    float o[DH / 8][4];
+#pragma unroll
+    for (int i = 0; i < DH / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+    const int r_lo = warp * 16 + (lane >> 2);      // this thread's two query rows: r_lo, r_lo + 8
+    const int qpos_a = pos0 + m0 + r_lo, qpos_b = qpos_a + 8;
+
+    for (int t = t_lo; t < t_hi; ++t) {
+        const int stage = (t - t_lo) & 1;
+        if (t + 1 < t_hi) load_kv(t + 1, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const bf16* tK = sK + stage * BN * DH;
+        const bf16* tV = sV + stage * BN * DH;
+
+        // S = Q K^T  (16 x 64 per warp)
+        float s[BN / 8][4];
+#pragma unroll
+        for (int i = 0; i < BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < DH / 16; ++kk) {
+            uint32_t qa[4];
+            ldsm_x4(qa, tile_ptr<DH>(sQ, warp * 16 + (lane & 15), kk * 2 + (lane >> 4)));
+#pragma unroll
+            for (int nt = 0; nt < BN / 16; ++nt) {
+                uint32_t kb[4];
+                const int tok = nt * 16 + ((lane >> 4) << 3) + (lane & 7);
+                ldsm_x4(kb, tile_ptr<DH>(const_cast<bf16*>(tK), tok, kk * 2 + ((lane >> 3) & 1)));
+                mma_bf16(s[2 * nt], qa, kb[0], kb[1]);
+                mma_bf16(s[2 * nt + 1], qa, kb[2], kb[3]);
+            }
+        }
+        // scale, soft-cap, mask, online softmax
+        float mx[2] = {mrow[0], mrow[1]};
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = t * BN + nt * 8 + (lane & 3) * 2 + (e & 1);
+                const int qp = (e < 2) ? qpos_a : qpos_b;
+                float v = s[nt][e] * a.scale;
+                if (a.softcap > 0.f) v = a.softcap * tanhf(v / a.softcap);
+                const bool ok = j <= qp && j < kvlen && (a.window <= 0 || j > qp - a.window);
+                v = ok ? v : -INFINITY;
+                s[nt][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        }
+        float corr[2], rsum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            corr[r] = (mrow[r] == -INFINITY) ? 0.f : __expf(mrow[r] - mx[r]);
+            mrow[r] = mx[r];
+        }
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float mref = mx[e >> 1];
+                const float p = (mref == -INFINITY) ? 0.f : __expf(s[nt][e] - mref);
+                s[nt][e] = p;
+                rsum[e >> 1] += p;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) lrow[r] = lrow[r] * corr[r] + rsum[r];
+#pragma unroll
+        for (int i = 0; i < DH / 8; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0];
+            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+        // O += P V
+#pragma unroll
+        for (int kt = 0; kt < BN / 16; ++kt) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16(s[2 * kt][0], s[2 * kt][1]);
+            pa[1] = pack_bf16(s[2 * kt][2], s[2 * kt][3]);
+            pa[2] = pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]);
+            pa[3] = pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3]);
+#pragma unroll
+            for (int dt = 0; dt < DH / 16; ++dt) {
+                uint32_t vb[4];
+                const int tok = kt * 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
+                ldsm_x4_t(vb, tile_ptr<DH>(const_cast<bf16*>(tV), tok, dt * 2 + (lane >> 4)));
+                mma_bf16(o[2 * dt], pa, vb[0], vb[1]);
+                mma_bf16(o[2 * dt + 1], pa, vb[2], vb[3]);
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    // row sums across the four lanes that share a row
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        lrow[r] += __shfl_xor_sync(0xffffffffu, lrow[r], 1);
+        lrow[r] += __shfl_xor_sync(0xffffffffu, lrow[r], 2);
+    }
+    float inv[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float mm = mrow[r], ll = lrow[r], oc = 1.f;
+        if (a.sinks) {
+            const float sk = a.sinks[h];
+            const float mn = fmaxf(mm, sk);
+            oc = (mm == -INFINITY) ? 0.f : __expf(mm - mn);
+            ll = ll * oc + __expf(sk - mn);
+        }
+        inv[r] = ll > 0.f ? oc / ll : 0.f;
+    }
+    const int ra = warp * 16 + (lane >> 2), rb = ra + 8;
+#pragma unroll
+    for (int i = 0; i < DH / 8; ++i) {
+        const int d = i * 8 + (lane & 3) * 2;
+        if (ra < rows)
+            *reinterpret_cast<uint32_t*>(a.out + ((long)(q0 + m0 + ra) * a.Hq + h) * DH + d) =
+                pack_bf16(o[i][0] * inv[0], o[i][1] * inv[0]);
+        if (rb < rows)
+            *reinterpret_cast<uint32_t*>(a.out + ((long)(q0 + m0 + rb) * a.Hq + h) * DH + d) =
+                pack_bf16(o[i][2] * inv[1], o[i][3] * inv[1]);
+    }
+}
+
+template <int DH>
+static int launch_prefill(const AttnArgs& a, int max_q, cudaStream_t s) {
+    const size_t smem = (size_t)(64 + 4 * 64) * DH * sizeof(bf16);
+    static bool configured = false;
+    if (!configured) {
+        TSB_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            (int)smem));
+        configured = true;
+    }
+    dim3 grid((max_q + 63) / 64, a.Hq, a.B);
+    attn_prefill_kernel<DH><<<grid, 128, smem, s>>>(a);
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}
+
+extern "C" int tsb_attn_prefill(const AttnArgs* args, int max_q_len, void* stream) {
+    const AttnArgs& a = *args;
+    TSB_CHECK_ARG(a.Hkv > 0 && a.Hq % a.Hkv == 0, "attn_prefill: Hq=%d not a multiple of Hkv=%d", a.Hq, a.Hkv);
+    TSB_CHECK_ARG(a.cu_q != nullptr, "attn_prefill: cu_q is required");
+    if (a.B == 0 || max_q_len == 0) return TSB_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (a.Dh) {
+    case 64: return launch_prefill<64>(a, max_q_len, s);
+    case 128: return launch_prefill<128>(a, max_q_len, s);
+    case 256: return launch_prefill<256>(a, max_q_len, s);
+    default:
+        tsb_set_error("attn_prefill: unsupported head dim %d (supported 64, 128, 256)", a.Dh);
+        return TSB_ERR_UNSUPPORTED;
+    }
+}

@@ -1,0 +1,385 @@
+// Fused normalisation, rotary embedding + KV-cache write, gated activations, embedding
+// gather, row dequantisation and arg-max.
+//
+// Replaces in the reference: rms_norm_f32 (+mul, +add) (ggml-cuda/norm.cu:108, :358-435),
+// l2_norm_f32 (:287), rope_neox / rope_norm with YaRN and freq factors (rope.cu:44, :111),
+// the rope + view + set_rows fusion (ggml-cuda.cu:3359-3790 item 2), k_set_rows
+// (set-rows.cu:113), unary_gated_op_kernel / swiglu_oai_kernel (unary.cu:255, :352),
+// k_get_rows* (getrows.cu:6-225), dequantize_block_* (convert.cu), argmax_f32 (argmax.cu:8),
+// softcap_f32 (softcap.cu:3), quantize_q8_1 fused into the producer.
+#include "quant_blocks.cuh"
+
+// ------------------------------------------------------------------------------------------
+// RMSNorm family.  One block per row.
+//   v      = x (+ delta)                       (delta optional; when given, v is also stored
+//                                               back to x, which is the residual stream)
+//   n      = v * rsqrt(mean(v^2) + eps) * w    (w optional)
+//   y_bf16 = n            y_f32 = (add ? add : 0) + n         yq/yds = q8(n)
+// ------------------------------------------------------------------------------------------
+template <typename TX>
+__global__ void __launch_bounds__(256) rmsnorm_kernel(TX* x, const bf16* delta, const float* w, float eps,
+                                                      int D, bf16* y_bf16, float* y_f32, const float* add,
+                                                      int8_t* yq, float2* yds, int l2_mode) {
+    __shared__ float red[32];
+    const long row = blockIdx.x;
+    TX* xr = x + row * D;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        float v = (float)xr[i];
+        if (delta) {
+            v += bf2f(delta[row * D + i]);
+            xr[i] = (TX)v;
+        }
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    // l2_mode: x / max(||x||, eps) (ggml l2_norm); otherwise RMS.
+    const float rs = l2_mode ? 1.f / fmaxf(sqrtf(ss), eps) : rsqrtf(ss / (float)D + eps);
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int dpad = (D + 31) & ~31;
+    for (int i = threadIdx.x; i < dpad; i += blockDim.x) {
+        float n = 0.f;
+        if (i < D) {
+            n = (float)xr[i] * rs;
+            if (w) n *= w[i];
+            if (y_bf16) y_bf16[row * D + i] = f2bf(n);
+            if (y_f32) y_f32[row * D + i] = (add ? add[row * D + i] : 0.f) + n;
+        }
+        if (yq) {
+            // whole warps iterate together because blockDim.x and dpad are multiples of 32
+            const float amax = warp_max(fabsf(n));
+            const float sum = warp_sum(n);
+            const float d = amax / 127.f;
+            if (i < D) yq[row * D + i] = (int8_t)__float2int_rn(amax > 0.f ? n / d : 0.f);
+            if (lane == 0 && i < D) yds[row * (D / 32) + i / 32] = make_float2(d, sum);
+        }
+    }
+}
+
+extern "C" int tsb_rmsnorm(void* x, int x_f32, const void* delta, const float* w, float eps, long rows, int D,
+                           void* y_bf16, float* y_f32, const float* add, void* yq, void* yds, int l2_mode,
+                           void* stream) {
+    TSB_CHECK_ARG(D > 0 && rows >= 0, "rmsnorm: bad shape rows=%ld D=%d", rows, D);
+    TSB_CHECK_ARG(!yq || D % 32 == 0, "rmsnorm: q8 output needs D %% 32 == 0, got %d", D);
+    if (rows == 0) return TSB_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (x_f32)
+        rmsnorm_kernel<float><<<(unsigned)rows, 256, 0, s>>>((float*)x, (const bf16*)delta, w, eps, D, (bf16*)y_bf16,
+                                                             y_f32, add, (int8_t*)yq, (float2*)yds, l2_mode);
+    else
+        rmsnorm_kernel<bf16><<<(unsigned)rows, 256, 0, s>>>((bf16*)x, (const bf16*)delta, w, eps, D, (bf16*)y_bf16,
+                                                            y_f32, add, (int8_t*)yq, (float2*)yds, l2_mode);
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// Per-head norm + RoPE + KV-cache write.  One warp per (token, head); heads are laid out
+// q[0..Hq), k[0..Hkv), v[0..Hkv).  Head dim <= 512.
+// ------------------------------------------------------------------------------------------
+struct RopeParams {
+    float theta_base;      // rope.freq_base
+    float freq_scale;      // 1 / rope.scaling.factor
+    float ext_factor;      // YaRN mix (0 = plain)
+    float attn_factor;     // magnitude scale
+    float corr_lo, corr_hi;  // YaRN ramp bounds (already computed on the host)
+    int rot_dim;           // number of rotated dims (<= head dim); 0 disables RoPE
+    int mode;              // 0 = NeoX (pairs i, i + rot/2), 1 = adjacent pairs (2i, 2i+1)
+};
+
+struct QkvArgs {
+    const void* q; const void* k; const void* v;   // inputs (same dtype), may alias one buffer
+    long q_tok, q_head, k_tok, k_head, v_tok, v_head;  // element strides
+    int in_f32;
+    const float* qn; const float* kn;   // per-head RMSNorm weights [Dh] or null
+    int v_norm;                         // 1: unweighted RMSNorm on V
+    float eps;
+    const int* pos;                     // [T]
+    const long* slot;                   // [T] flat slot in the KV cache (page * page_size + offset), <0 = skip
+    const float* freq_factors;          // [rot_dim/2] or null
+    bf16* q_out;                        // [T, Hq, Dh]
+    bf16* k_cache; bf16* v_cache;       // [slots, Hkv, Dh]
+    float q_scale;                      // multiplied into q after RoPE (1 = none)
+    int T, Hq, Hkv, Dh;
+    RopeParams rp;
+};
+
+__device__ __forceinline__ void rope_cs(const RopeParams& rp, const float* ff, int pair, float pos, float& c, float& s) {
+    float theta = pos * powf(rp.theta_base, -2.f * (float)pair / (float)rp.rot_dim);
+    if (ff) theta /= ff[pair];
+    float th = rp.freq_scale * theta;
+    float ms = rp.attn_factor;
+    if (rp.ext_factor != 0.f) {
+        const float y = ((float)pair - rp.corr_lo) / fmaxf(0.001f, rp.corr_hi - rp.corr_lo);
+        const float ramp = (1.f - fminf(1.f, fmaxf(0.f, y))) * rp.ext_factor;
+        th = th * (1.f - ramp) + theta * ramp;
+        ms *= 1.f + 0.1f * logf(1.f / rp.freq_scale);
+    }
+    sincosf(th, &s, &c);
+    c *= ms;
+    s *= ms;
+}
+
+__global__ void __launch_bounds__(128) qkv_rope_kernel(QkvArgs a) {
+    const int lane = threadIdx.x & 31;
+    const long wid = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int H = a.Hq + 2 * a.Hkv;
+    if (wid >= (long)a.T * H) return;
+    const int t = (int)(wid / H), h = (int)(wid % H);
+    const int Dh = a.Dh;
+    const void* src;
+    long off;
+    int kind;  // 0 q, 1 k, 2 v
+    if (h < a.Hq) { kind = 0; src = a.q; off = t * a.q_tok + h * a.q_head; }
+    else if (h < a.Hq + a.Hkv) { kind = 1; src = a.k; off = t * a.k_tok + (h - a.Hq) * a.k_head; }
+    else { kind = 2; src = a.v; off = t * a.v_tok + (h - a.Hq - a.Hkv) * a.v_head; }
+    const long slot = a.slot ? a.slot[t] : -1;
+    if (kind != 0 && slot < 0) return;
+    // each lane holds up to 16 values: element e = lane + 32 * j
+    float v[16];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const int e = lane + 32 * j;
+        float x = 0.f;
+        if (e < Dh) x = a.in_f32 ? reinterpret_cast<const float*>(src)[off + e]
+                                  : bf2f(reinterpret_cast<const bf16*>(src)[off + e]);
+        v[j] = x;
+        ss += x * x;
+    }
+    const float* nw = kind == 0 ? a.qn : (kind == 1 ? a.kn : nullptr);
+    if (nw || (kind == 2 && a.v_norm)) {
+        ss = warp_sum(ss);
+        const float rs = rsqrtf(ss / (float)Dh + a.eps);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int e = lane + 32 * j;
+            if (e < Dh) v[j] *= rs * (nw ? nw[e] : 1.f);
+        }
+    }
+    bf16* dst;
+    if (kind == 0) dst = a.q_out + ((long)t * a.Hq + h) * Dh;
+    else if (kind == 1) dst = a.k_cache + (slot * a.Hkv + (h - a.Hq)) * Dh;
+    else dst = a.v_cache + (slot * a.Hkv + (h - a.Hq - a.Hkv)) * Dh;
+    const int rot = a.rp.rot_dim;
+    if (kind == 2 || rot == 0) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int e = lane + 32 * j;
+            if (e < Dh) dst[e] = f2bf(kind == 0 ? v[j] * a.q_scale : v[j]);
+        }
+        return;
+    }
+    const float pos = (float)a.pos[t];
+    const float qs = kind == 0 ? a.q_scale : 1.f;
+    if (a.rp.mode == 0) {
+        // NeoX: element e pairs with e + rot/2.  The partner lives in another register or lane;
+        // stage through shared memory (one row of 512 floats per warp).
+        __shared__ float stage[4][512];
+        float* st = stage[threadIdx.x >> 5];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int e = lane + 32 * j;
+            if (e < Dh) st[e] = v[j];
+        }
+        __syncwarp();
+        const int half = rot >> 1;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int e = lane + 32 * j;
+            if (e >= Dh) continue;
+            float o = v[j];
+            if (e < rot) {
+                const int pair = e < half ? e : e - half;
+                float c, s;
+                rope_cs(a.rp, a.freq_factors, pair, pos, c, s);
+                const float x0 = st[pair], x1 = st[pair + half];
+                o = e < half ? x0 * c - x1 * s : x0 * s + x1 * c;
+            }
+            dst[e] = f2bf(o * qs);
+        }
+    } else {
+        // adjacent pairs (2i, 2i+1): the partner is in the neighbouring lane
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int e = lane + 32 * j;
+            const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
+            if (e >= Dh) continue;
+            float o = v[j];
+            if (e < rot) {
+                float c, s;
+                rope_cs(a.rp, a.freq_factors, e >> 1, pos, c, s);
+                o = (e & 1) ? other * s + v[j] * c : v[j] * c - other * s;
+            }
+            dst[e] = f2bf(o * qs);
+        }
+    }
+}
+
+extern "C" int tsb_qkv_rope(const QkvArgs* args, void* stream) {
+    const QkvArgs& a = *args;
+    TSB_CHECK_ARG(a.Dh > 0 && a.Dh <= 512, "qkv_rope: head dim %d out of range (1..512)", a.Dh);
+    TSB_CHECK_ARG(a.rp.rot_dim <= a.Dh && a.rp.rot_dim % 2 == 0, "qkv_rope: bad rot_dim %d", a.rp.rot_dim);
+    const long warps = (long)a.T * (a.Hq + 2 * a.Hkv);
+    if (warps == 0) return TSB_OK;
+    qkv_rope_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, (cudaStream_t)stream>>>(a);
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// Gated activation: out[t, f] = act(gate[t, f] (+bg[f])) * (up[t, f] (+bu[f])), optional q8 output.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float glu_apply(int act, float g, float u) {
+    switch (act) {
+    case 1: return g / (1.f + __expf(-g)) * u;
+    case 2: {
+        const float c = 0.7978845608028654f;
+        return 0.5f * g * (1.f + tanhf(c * (g + 0.044715f * g * g * g))) * u;
+    }
+    case 3: return 0.5f * g * (1.f + erff(g * 0.7071067811865476f)) * u;
+    case 4: {
+        const float x = fminf(g, 7.f), y = fminf(fmaxf(u, -7.f), 7.f);
+        return x / (1.f + __expf(-1.702f * x)) * (y + 1.f);
+    }
+    case 5: { const float r = fmaxf(g, 0.f); return r * r; }             // ReLU^2 (no gate)
+    case 6: return g / (1.f + __expf(-g));                                // SiLU (no gate)
+    case 7: return u / (1.f + __expf(-g));                                // sigmoid(g) * u
+    default: return g * u;
+    }
+}
+
+template <typename T>
+__global__ void glu_kernel(const T* gate, const T* up, long g_stride, long u_stride, int F, int act, bf16* out,
+                           int8_t* yq, float2* yds, long rows) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int fpad = (F + 31) & ~31;
+    const long total = rows * fpad;
+    if (idx >= total) return;
+    const long t = idx / fpad;
+    const int f = (int)(idx % fpad);
+    float r = 0.f;
+    if (f < F) {
+        const float g = (float)gate[t * g_stride + f];
+        const float u = up ? (float)up[t * u_stride + f] : 0.f;
+        r = glu_apply(act, g, u);
+        if (out) out[t * F + f] = f2bf(r);
+    }
+    if (yq) {
+        const float amax = warp_max(fabsf(r));
+        const float sum = warp_sum(r);
+        const float d = amax / 127.f;
+        if (f < F) yq[t * F + f] = (int8_t)__float2int_rn(amax > 0.f ? r / d : 0.f);
+        if ((threadIdx.x & 31) == 0 && f < F) yds[t * (F / 32) + f / 32] = make_float2(d, sum);
+    }
+}
+
+extern "C" int tsb_glu(const void* gate, const void* up, int in_f32, long g_stride, long u_stride, long rows, int F,
+                       int act, void* out, void* yq, void* yds, void* stream) {
+    TSB_CHECK_ARG(!yq || F % 32 == 0, "glu: q8 output needs F %% 32 == 0, got %d", F);
+    if (rows == 0 || F == 0) return TSB_OK;
+    const long total = rows * ((F + 31) & ~31);
+    dim3 grid((unsigned)((total + 255) / 256));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (in_f32)
+        glu_kernel<float><<<grid, 256, 0, s>>>((const float*)gate, (const float*)up, g_stride, u_stride, F, act,
+                                               (bf16*)out, (int8_t*)yq, (float2*)yds, rows);
+    else
+        glu_kernel<bf16><<<grid, 256, 0, s>>>((const bf16*)gate, (const bf16*)up, g_stride, u_stride, F, act,
+                                              (bf16*)out, (int8_t*)yq, (float2*)yds, rows);
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// Row gather with dequantisation (embedding lookup when ids != null, whole-matrix decode to
+// bf16 when ids == null).  One thread per 8 output values.
+// ------------------------------------------------------------------------------------------
+template <typename TO>
+__global__ void gather_rows_kernel(QW w, const int* ids, long n_rows, float scale, TO* out) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int k8n = w.K >> 3;
+    if (idx >= n_rows * k8n) return;
+    const long r = idx / k8n;
+    const int k8 = (int)(idx % k8n);
+    long src = ids ? (long)ids[r] : r;
+    if (src < 0 || src >= w.N) src = 0;
+    float v[8];
+    dequant8(w, src, k8, v);
+    TO* o = out + r * w.K + 8 * k8;
+    if (sizeof(TO) == 2) {
+        bf16 b[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) b[i] = f2bf(v[i] * scale);
+        *reinterpret_cast<uint4*>(o) = *reinterpret_cast<const uint4*>(b);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = (TO)(v[i] * scale);
+    }
+}
+
+extern "C" int tsb_gather_rows(const void* p0, const void* p1, const void* p2, const void* p3, int type, int N, int K,
+                               const int* ids, long n_rows, float scale, void* out, int out_f32, void* stream) {
+    TSB_CHECK_ARG(K % 8 == 0, "gather_rows: K=%d must be a multiple of 8", K);
+    if (n_rows == 0) return TSB_OK;
+    QW w{(const uint8_t*)p0, (const uint8_t*)p1, (const uint8_t*)p2, (const uint8_t*)p3, type, N, K};
+    const long total = n_rows * (K / 8);
+    dim3 grid((unsigned)((total + 255) / 256));
+    if (out_f32)
+        gather_rows_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>(w, ids, n_rows, scale, (float*)out);
+    else
+        gather_rows_kernel<bf16><<<grid, 256, 0, (cudaStream_t)stream>>>(w, ids, n_rows, scale, (bf16*)out);
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// Row arg-max over float logits with optional soft-cap (cap * tanh(x / cap)).  One block per row.
+// Ties resolve to the lowest index, like the host sampler.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* logits, long stride, int V, int* out_idx,
+                                                      float* out_val) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const float* row = logits + blockIdx.x * stride;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    if (lane == 0) { sv[w] = best; si[w] = bi; }
+    __syncthreads();
+    if (w == 0) {
+        const int nw = blockDim.x >> 5;
+        best = lane < nw ? sv[lane] : -INFINITY;
+        bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (lane == 0) {
+            out_idx[blockIdx.x] = bi;
+            if (out_val) out_val[blockIdx.x] = best;
+        }
+    }
+}
+
+extern "C" int tsb_argmax(const float* logits, long stride, long rows, int V, int* out_idx, float* out_val,
+                          void* stream) {
+    if (rows == 0) return TSB_OK;
+    TSB_CHECK_ARG(V > 0, "argmax: empty vocabulary");
+    argmax_kernel<<<(unsigned)rows, 1024, 0, (cudaStream_t)stream>>>(logits, stride, V, out_idx, out_val);
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}

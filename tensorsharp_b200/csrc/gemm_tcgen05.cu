@@ -1,0 +1,223 @@
+// bf16 GEMM on the 5th-generation tensor cores:  Y[t, n] = sum_k X[t, k] * W[n, k]
+//   (+ bias[n]) (+ residual[t, n]),  f32 accumulation in tensor memory.
+//
+// The problem is run "weights as the M operand": each CTA owns 128 rows of W (output
+// features) and BN tokens, so that a small token count still fills the 128-lane MMA and the
+// same kernel serves batched decode (BN = 32) and prefill (BN = 256).
+//
+//   warp 0    : TMA producer - W and X tiles (64-element K slabs, 128-byte swizzle) into a
+//               STAGES-deep shared-memory ring, completion on mbarriers
+//   warp 1    : allocates tensor memory, one thread issues tcgen05.mma (128 x BN x 16) and
+//               commits each stage back to the producer
+//   warps 2-5 : epilogue - tcgen05.ld the accumulator (lane = feature, column = token),
+//               add bias / residual, store coalesced along the feature dimension
+//
+// Replaces in the reference: mul_mat_q + stream-k fixup + quantize_mmq_q8_1
+// (ggml-cuda/mmq.cuh:3301, :3542, quantize.cu:51), mul_mat_f (mmf.cuh:25) and the cuBLAS
+// fallback (ggml-cuda.cu:1361-1497): quantised weights are decoded once into an L2-resident
+// bf16 scratch by tsb_gather_rows and consumed here.
+#include <cudaTypedefs.h>
+#include <mutex>
+#include "tcgen05.cuh"
+
+struct GemmEpi {
+    void* out;              // [T, ldo]
+    const float* bias;      // [N] or null
+    const void* residual;   // same dtype / layout as out, or null
+    long ldo;
+    int T, N;               // valid tokens, valid features
+    int out_f32;
+};
+
+template <int BN, int STAGES>
+struct GemmSmem {
+    static constexpr int A_BYTES = 128 * 64 * 2;
+    static constexpr int B_BYTES = BN * 64 * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
+    static constexpr int TOTAL = BAR_OFF + (2 * STAGES + 1) * 8 + 16 + 1024;  // + alignment slack
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW,
+                                                        const __grid_constant__ CUtensorMap tmX, GemmEpi ep, int K,
+                                                        int* status) {
+    using L = GemmSmem<BN, STAGES>;
+    constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_bar = empty_bar + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * 128;       // first feature (row of W)
+    const int n0 = blockIdx.y * BN;        // first token
+    const int kblocks = (K + 63) / 64;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            tc::mbar_init(&full_bar[s], 1);
+            tc::mbar_init(&empty_bar[s], 1);
+        }
+        tc::mbar_init(acc_bar, 1);
+        tc::fence_barrier_init();
+    }
+    if (warp == 1) tc::tmem_alloc<TMEM_COLS>(tmem_slot);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tc::tma_prefetch_desc(&tmW);
+            tc::tma_prefetch_desc(&tmX);
+            for (int kb = 0; kb < kblocks; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                if (!tc::mbar_wait(&empty_bar[s], ph ^ 1)) { atomicExch(status, 1); break; }
+                unsigned char* a = smem + s * L::STAGE_BYTES;
+                tc::mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+                tc::tma_load_2d(a, &tmW, &full_bar[s], kb * 64, m0);
+                tc::tma_load_2d(a + L::A_BYTES, &tmX, &full_bar[s], kb * 64, n0);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = tc::make_idesc_bf16(128, BN);
+            bool ok = true;
+            for (int kb = 0; kb < kblocks && ok; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                if (!tc::mbar_wait(&full_bar[s], ph)) { atomicExch(status, 2); ok = false; break; }
+                tc::fence_after_sync();
+                const uint32_t a = tc::smem_u32(smem + s * L::STAGE_BYTES);
+                const uint64_t da = tc::make_desc_sw128(a), db = tc::make_desc_sw128(a + L::A_BYTES);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)   // 4 x (K = 16) per 64-element slab: +32 bytes = +2 descriptor units
+                    tc::mma_f16_ss(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                tc::mma_commit(&empty_bar[s]);
+            }
+            if (ok) tc::mma_commit(acc_bar);
+        }
+        __syncwarp();
+    } else {
+        const int q = warp & 3;                       // TMEM lane quadrant this warp may read
+        const int n = m0 + q * 32 + lane;             // feature owned by this thread
+        if (tc::mbar_wait(acc_bar, 0)) {
+            tc::fence_after_sync();
+            const float bias = (ep.bias && n < ep.N) ? ep.bias[n] : 0.f;
+#pragma unroll 1
+            for (int c = 0; c < BN / 16; ++c) {
+                uint32_t r[16];
+                tc::tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + c * 16, r);
+                tc::tmem_ld_wait();
+                if (n < ep.N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = n0 + c * 16 + j;
+                        if (t < ep.T) {
+                            float v = __uint_as_float(r[j]) + bias;
+                            const long o = (long)t * ep.ldo + n;
+                            if (ep.out_f32) {
+                                if (ep.residual) v += reinterpret_cast<const float*>(ep.residual)[o];
+                                reinterpret_cast<float*>(ep.out)[o] = v;
+                            } else {
+                                if (ep.residual) v += bf2f(reinterpret_cast<const bf16*>(ep.residual)[o]);
+                                reinterpret_cast<bf16*>(ep.out)[o] = f2bf(v);
+                            }
+                        }
+                    }
+                }
+            }
+        } else {
+            atomicExch(status, 3);
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc::fence_after_sync();
+        tc::tmem_dealloc<TMEM_COLS>(tmem_base);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+static PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+static std::once_flag g_encode_once;
+
+static void resolve_encode() {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+        g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+}
+
+int tsb_make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_elems,
+                          uint32_t box_rows, uint32_t box_cols) {
+    std::call_once(g_encode_once, resolve_encode);
+    if (!g_encode) {
+        tsb_set_error("cuTensorMapEncodeTiled is not available from the driver");
+        return TSB_ERR_CUDA;
+    }
+    TSB_CHECK_ARG((reinterpret_cast<uintptr_t>(base) & 15) == 0, "tensor map base %p is not 16-byte aligned", base);
+    TSB_CHECK_ARG((row_stride_elems * 2) % 16 == 0, "tensor map row stride %llu elements is not a multiple of 16 bytes",
+                  (unsigned long long)row_stride_elems);
+    cuuint64_t gdim[2] = {cols, rows};
+    cuuint64_t gstride[1] = {row_stride_elems * 2};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        tsb_set_error("cuTensorMapEncodeTiled failed with CUresult %d (rows=%llu cols=%llu box=%ux%u)", (int)r,
+                      (unsigned long long)rows, (unsigned long long)cols, box_rows, box_cols);
+        return TSB_ERR_CUDA;
+    }
+    return TSB_OK;
+}
+
+template <int BN, int STAGES>
+static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmEpi& ep, int K, int* status,
+                       cudaStream_t s) {
+    using L = GemmSmem<BN, STAGES>;
+    static bool configured = false;
+    if (!configured) {
+        TSB_CHECK_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            L::TOTAL));
+        configured = true;
+    }
+    dim3 grid((ep.N + 127) / 128, (ep.T + BN - 1) / BN);
+    gemm_bf16_kernel<BN, STAGES><<<grid, 192, L::TOTAL, s>>>(tw, tx, ep, K, status);
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}
+
+// W: [N, K] bf16 row-major (ldw elements per row); X: [T, K] bf16 (ldx); out: [T, ldo].
+// `status` is a device int the kernel sets non-zero if one of its bounded waits gave up.
+extern "C" int tsb_gemm_bf16(const void* W, long ldw, const void* X, long ldx, void* out, long ldo, int out_f32,
+                             const float* bias, const void* residual, int T, int N, int K, int* status, void* stream) {
+    TSB_CHECK_ARG(T >= 0 && N > 0 && K > 0, "gemm_bf16: bad shape T=%d N=%d K=%d", T, N, K);
+    TSB_CHECK_ARG(K % 8 == 0 && ldw % 8 == 0 && ldx % 8 == 0, "gemm_bf16: K, ldw, ldx must be multiples of 8");
+    TSB_CHECK_ARG(status != nullptr, "gemm_bf16: status word is required");
+    if (T == 0) return TSB_OK;
+    const int bn = T <= 32 ? 32 : (T <= 64 ? 64 : (T <= 128 ? 128 : 256));
+    CUtensorMap tw, tx;
+    int rc = tsb_make_tmap_2d_bf16(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 128, 64);
+    if (rc) return rc;
+    rc = tsb_make_tmap_2d_bf16(&tx, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, (uint32_t)bn, 64);
+    if (rc) return rc;
+    GemmEpi ep{out, bias, residual, ldo, T, N, out_f32};
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (bn) {
+    case 32: return launch_gemm<32, 8>(tw, tx, ep, K, status, s);
+    case 64: return launch_gemm<64, 8>(tw, tx, ep, K, status, s);
+    case 128: return launch_gemm<128, 6>(tw, tx, ep, K, status, s);
+    default: return launch_gemm<256, 4>(tw, tx, ep, K, status, s);
+    }
+}

@@ -1,0 +1,448 @@
+// Weight-streaming GEMV / small-batch GEMM over GGUF-quantised weights (decode path).
+//
+//   out[m, n] = sum_k W[n, k] * x[m, k]  (+ bias[n]) (+ residual[m, n])      m < M <= 8 per pass
+//
+// One warp owns one output row (or a gate/up row pair when a GLU epilogue is requested) and
+// streams that row's blocks with 16-byte loads; activations are pre-quantised to int8 in
+// groups of 32 with a float scale and the group's float sum (same arithmetic contract as
+// ggml's q8_1 activations), so the inner product is dp4a.  Weights are read exactly once
+// per call; activations come from L1.  The optional `ids` argument turns the launch into a
+// mixture-of-experts GEMV: problem p uses expert ids[p], activation row p / x_div and
+// output row p.
+//
+// Replaces in the reference: mul_mat_vec_q + quantize_q8_1 (ggml-cuda/mmvq.cu:143,
+// quantize.cu:5), mul_mat_vec_f (mmvf.cu:8), the bias / GLU fusion of
+// ggml-cuda.cu:3359-3790 item (5), and the per-expert unrolled graphs of
+// TensorSharp.GGML.Native/ggml_ops_fused.cpp:1766 for the single-token case.
+#include "quant_blocks.cuh"
+
+enum { ACT_NONE = 0, ACT_SWIGLU = 1, ACT_GEGLU_TANH = 2, ACT_GEGLU_ERF = 3, ACT_SWIGLU_OAI = 4,
+       ACT_RELU2 = 5 };
+
+__device__ __forceinline__ float act_glu(int act, float g, float u) {
+    switch (act) {
+    case ACT_SWIGLU: return g / (1.f + __expf(-g)) * u;
+    case ACT_GEGLU_TANH: {
+        const float c = 0.7978845608028654f;
+        float t = tanhf(c * (g + 0.044715f * g * g * g));
+        return 0.5f * g * (1.f + t) * u;
+    }
+    case ACT_GEGLU_ERF: return 0.5f * g * (1.f + erff(g * 0.7071067811865476f)) * u;
+    case ACT_SWIGLU_OAI: {
+        float x = fminf(g, 7.f), y = fminf(fmaxf(u, -7.f), 7.f);
+        return x / (1.f + __expf(-1.702f * x)) * (y + 1.f);
+    }
+    default: return g * u;
+    }
+}
+
+struct GemvArgs {
+    QW w;
+    const int8_t* xq;      // [Mx, K] int8
+    const float2* xds;     // [Mx, K/32] (scale, sum of x)
+    const bf16* xb;        // [Mx, K] bf16 (used by float-weight types)
+    void* out;             // [P or M, N_out]
+    const float* bias;     // [E, N] or null
+    const void* residual;  // same shape/dtype as out, or null
+    const int* ids;        // [P] expert per problem, or null
+    const float* row_scale;  // [P] multiply the result (before residual) or null
+    int M;                 // activation rows handled per problem (1 when ids != null)
+    int x_div;             // activation row of problem p is p / x_div
+    int out_f32;           // 1: float output, 0: bf16
+    int act;               // GLU activation; rows [0,N/2) are gate, [N/2,N) are up
+    int n_out;             // N, or N/2 with GLU
+};
+
+template <int M>
+__device__ __forceinline__ void dot_q4k(const QW& w, long row, int lane, const int8_t* xq,
+                                        const float2* xds, float* acc, int mv) {
+    const int K = w.K, nb = K >> 8, units = nb << 3, kb = K >> 5;
+    for (int u = lane; u < units; u += 32) {
+        const int b = u >> 3, uu = u & 7, c = uu >> 1, h = uu & 1;
+        const uint8_t* blk = w.p0 + (row * nb + b) * 144;
+        const uint4 hdr = ld_stream_u4(blk);
+        const uint4 qv = ld_stream_u4(blk + 16 + 32 * c + 16 * h);
+        const float d = h2f_bits(hdr.x & 0xffff), dmin = h2f_bits(hdr.x >> 16);
+        int sc0, sc1, mn0, mn1;
+        if (c < 2) {
+            const int s0 = 16 * c;
+            sc0 = (hdr.y >> s0) & 63; sc1 = (hdr.y >> (s0 + 8)) & 63;
+            mn0 = (hdr.z >> s0) & 63; mn1 = (hdr.z >> (s0 + 8)) & 63;
+        } else {
+            const int s0 = 16 * (c - 2);
+            sc0 = ((hdr.w >> s0) & 0xF) | (((hdr.y >> (s0 + 6)) & 3) << 4);
+            sc1 = ((hdr.w >> (s0 + 8)) & 0xF) | (((hdr.y >> (s0 + 14)) & 3) << 4);
+            mn0 = ((hdr.w >> (s0 + 4)) & 0xF) | (((hdr.z >> (s0 + 6)) & 3) << 4);
+            mn1 = ((hdr.w >> (s0 + 12)) & 0xF) | (((hdr.z >> (s0 + 14)) & 3) << 4);
+        }
+        const float ds0 = d * sc0, ds1 = d * sc1, dm0 = dmin * mn0, dm1 = dmin * mn1;
+        const uint32_t q[4] = {qv.x, qv.y, qv.z, qv.w};
+        const int xoff = b * 256 + 64 * c + 16 * h;
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const int mr = m < mv ? m : 0;
+            const int4 xa = *reinterpret_cast<const int4*>(xq + (long)mr * K + xoff);
+            const int4 xb = *reinterpret_cast<const int4*>(xq + (long)mr * K + xoff + 32);
+            const int xai[4] = {xa.x, xa.y, xa.z, xa.w}, xbi[4] = {xb.x, xb.y, xb.z, xb.w};
+            int s0 = 0, s1 = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                s0 = __dp4a((int)(q[i] & 0x0F0F0F0Fu), xai[i], s0);
+                s1 = __dp4a((int)((q[i] >> 4) & 0x0F0F0F0Fu), xbi[i], s1);
+            }
+            const float2 e0 = xds[(long)mr * kb + b * 8 + 2 * c], e1 = xds[(long)mr * kb + b * 8 + 2 * c + 1];
+            float v = ds0 * e0.x * (float)s0 + ds1 * e1.x * (float)s1;
+            if (h == 0) v -= dm0 * e0.y + dm1 * e1.y;
+            acc[m] += v;
+        }
+    }
+}
+
+template <int M>
+__device__ __forceinline__ void dot_q5k(const QW& w, long row, int lane, const int8_t* xq,
+                                        const float2* xds, float* acc, int mv) {
+    const int K = w.K, nb = K >> 8, units = nb << 3, kb = K >> 5;
+    for (int u = lane; u < units; u += 32) {
+        const int b = u >> 3, uu = u & 7, c = uu >> 1, h = uu & 1;
+        const uint8_t* blk = w.p0 + (row * nb + b) * 176;
+        const uint4 hdr = ld_stream_u4(blk);
+        const uint4 hv = ld_stream_u4(blk + 16 + 16 * h);
+        const uint4 qv = ld_stream_u4(blk + 48 + 32 * c + 16 * h);
+        const float d = h2f_bits(hdr.x & 0xffff), dmin = h2f_bits(hdr.x >> 16);
+        int sc0, sc1, mn0, mn1;
+        if (c < 2) {
+            const int s0 = 16 * c;
+            sc0 = (hdr.y >> s0) & 63; sc1 = (hdr.y >> (s0 + 8)) & 63;
+            mn0 = (hdr.z >> s0) & 63; mn1 = (hdr.z >> (s0 + 8)) & 63;
+        } else {
+            const int s0 = 16 * (c - 2);
+            sc0 = ((hdr.w >> s0) & 0xF) | (((hdr.y >> (s0 + 6)) & 3) << 4);
+            sc1 = ((hdr.w >> (s0 + 8)) & 0xF) | (((hdr.y >> (s0 + 14)) & 3) << 4);
+            mn0 = ((hdr.w >> (s0 + 4)) & 0xF) | (((hdr.z >> (s0 + 6)) & 3) << 4);
+            mn1 = ((hdr.w >> (s0 + 12)) & 0xF) | (((hdr.z >> (s0 + 14)) & 3) << 4);
+        }
+        const float ds0 = d * sc0, ds1 = d * sc1, dm0 = dmin * mn0, dm1 = dmin * mn1;
+        const uint32_t q[4] = {qv.x, qv.y, qv.z, qv.w};
+        const uint32_t hq[4] = {hv.x, hv.y, hv.z, hv.w};
+        uint32_t lo[4], hi[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            lo[i] = (q[i] & 0x0F0F0F0Fu) | (((hq[i] >> (2 * c)) & 0x01010101u) << 4);
+            hi[i] = ((q[i] >> 4) & 0x0F0F0F0Fu) | (((hq[i] >> (2 * c + 1)) & 0x01010101u) << 4);
+        }
+        const int xoff = b * 256 + 64 * c + 16 * h;
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const int mr = m < mv ? m : 0;
+            const int4 xa = *reinterpret_cast<const int4*>(xq + (long)mr * K + xoff);
+            const int4 xb = *reinterpret_cast<const int4*>(xq + (long)mr * K + xoff + 32);
+            const int xai[4] = {xa.x, xa.y, xa.z, xa.w}, xbi[4] = {xb.x, xb.y, xb.z, xb.w};
+            int s0 = 0, s1 = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                s0 = __dp4a((int)lo[i], xai[i], s0);
+                s1 = __dp4a((int)hi[i], xbi[i], s1);
+            }
+            const float2 e0 = xds[(long)mr * kb + b * 8 + 2 * c], e1 = xds[(long)mr * kb + b * 8 + 2 * c + 1];
+            float v = ds0 * e0.x * (float)s0 + ds1 * e1.x * (float)s1;
+            if (h == 0) v -= dm0 * e0.y + dm1 * e1.y;
+            acc[m] += v;
+        }
+    }
+}
+
+// Q6_K planes.  Unit = (block b, half n, l-range 16*h): 64 values in four quarters of 16.
+template <int M>
+__device__ __forceinline__ void dot_q6k(const QW& w, long row, int lane, const int8_t* xq,
+                                        const float2* xds, float* acc, int mv) {
+    const int K = w.K, nb = K >> 8, units = nb << 2, kb = K >> 5;
+    for (int u = lane; u < units; u += 32) {
+        const int b = u >> 2, n = (u >> 1) & 1, h = u & 1;
+        const long blk = row * nb + b;
+        const uint4 la = ld_stream_u4(w.p0 + blk * 128 + 64 * n + 16 * h);
+        const uint4 lb = ld_stream_u4(w.p0 + blk * 128 + 64 * n + 32 + 16 * h);
+        const uint4 hv = ld_stream_u4(w.p1 + blk * 64 + 32 * n + 16 * h);
+        const float d = __half2float(reinterpret_cast<const __half*>(w.p3)[blk]);
+        const int8_t* scp = reinterpret_cast<const int8_t*>(w.p2) + blk * 16 + 8 * n + h;
+        const float s0 = d * scp[0], s1 = d * scp[2], s2 = d * scp[4], s3 = d * scp[6];
+        const uint32_t a[4] = {la.x, la.y, la.z, la.w}, bb[4] = {lb.x, lb.y, lb.z, lb.w};
+        const uint32_t hh[4] = {hv.x, hv.y, hv.z, hv.w};
+        int q0[4], q1[4], q2[4], q3[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            q0[i] = __vsub4((a[i] & 0x0F0F0F0Fu) | ((hh[i] & 0x03030303u) << 4), 0x20202020u);
+            q1[i] = __vsub4((bb[i] & 0x0F0F0F0Fu) | (((hh[i] >> 2) & 0x03030303u) << 4), 0x20202020u);
+            q2[i] = __vsub4(((a[i] >> 4) & 0x0F0F0F0Fu) | (((hh[i] >> 4) & 0x03030303u) << 4), 0x20202020u);
+            q3[i] = __vsub4(((bb[i] >> 4) & 0x0F0F0F0Fu) | (((hh[i] >> 6) & 0x03030303u) << 4), 0x20202020u);
+        }
+        const int xoff = b * 256 + 128 * n + 16 * h;
+        const int g0 = b * 8 + 4 * n;
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const int mr = m < mv ? m : 0;
+            const int8_t* xp = xq + (long)mr * K + xoff;
+            const int4 x0 = *reinterpret_cast<const int4*>(xp);
+            const int4 x1 = *reinterpret_cast<const int4*>(xp + 32);
+            const int4 x2 = *reinterpret_cast<const int4*>(xp + 64);
+            const int4 x3 = *reinterpret_cast<const int4*>(xp + 96);
+            const int a0[4] = {x0.x, x0.y, x0.z, x0.w}, a1[4] = {x1.x, x1.y, x1.z, x1.w};
+            const int a2[4] = {x2.x, x2.y, x2.z, x2.w}, a3[4] = {x3.x, x3.y, x3.z, x3.w};
+            int t0 = 0, t1 = 0, t2 = 0, t3 = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                t0 = __dp4a(q0[i], a0[i], t0);
+                t1 = __dp4a(q1[i], a1[i], t1);
+                t2 = __dp4a(q2[i], a2[i], t2);
+                t3 = __dp4a(q3[i], a3[i], t3);
+            }
+            const float2* e = xds + (long)mr * kb + g0;
+            acc[m] += s0 * e[0].x * (float)t0 + s1 * e[1].x * (float)t1 + s2 * e[2].x * (float)t2 +
+                      s3 * e[3].x * (float)t3;
+        }
+    }
+}
+
+// Q8_0 planes.  Unit = one 32-value block (two 16-byte loads).
+template <int M>
+__device__ __forceinline__ void dot_q8_0(const QW& w, long row, int lane, const int8_t* xq,
+                                         const float2* xds, float* acc, int mv) {
+    const int K = w.K, kb = K >> 5;
+    const int8_t* wr = reinterpret_cast<const int8_t*>(w.p0) + row * K;
+    const __half* dr = reinterpret_cast<const __half*>(w.p1) + row * kb;
+    for (int u = lane; u < kb; u += 32) {
+        const uint4 qa = ld_stream_u4(wr + u * 32), qb = ld_stream_u4(wr + u * 32 + 16);
+        const float d = __half2float(dr[u]);
+        const int q[8] = {(int)qa.x, (int)qa.y, (int)qa.z, (int)qa.w, (int)qb.x, (int)qb.y, (int)qb.z, (int)qb.w};
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const int mr = m < mv ? m : 0;
+            const int4 x0 = *reinterpret_cast<const int4*>(xq + (long)mr * K + u * 32);
+            const int4 x1 = *reinterpret_cast<const int4*>(xq + (long)mr * K + u * 32 + 16);
+            const int xi[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+            int s = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s = __dp4a(q[i], xi[i], s);
+            acc[m] += d * xds[(long)mr * kb + u].x * (float)s;
+        }
+    }
+}
+
+// Four 4-bit MXFP4 codes (one per byte, low nibble) -> four int8 values (2 x e2m1 value).
+__device__ __forceinline__ int mxfp4_lut4(uint32_t idx) {
+    const uint32_t m = idx & 0x07070707u;
+    const uint32_t t = m | (m >> 4);
+    const uint32_t sel = (t & 0xFFu) | ((t >> 8) & 0xFF00u);
+    const uint32_t mag = __byte_perm(0x03020100u, 0x0C080604u, sel);
+    const uint32_t neg = ((idx >> 3) & 0x01010101u) * 0xFFu;
+    return (int)__vsub4(mag ^ neg, neg);
+}
+
+// MXFP4 / Q4_0 planes.  Unit = one 32-value block (one 16-byte load).
+template <int M, bool MX>
+__device__ __forceinline__ void dot_q4_32(const QW& w, long row, int lane, const int8_t* xq,
+                                          const float2* xds, float* acc, int mv) {
+    const int K = w.K, kb = K >> 5;
+    const uint8_t* wr = w.p0 + row * (K >> 1);
+    for (int u = lane; u < kb; u += 32) {
+        const uint4 qv = ld_stream_u4(wr + u * 16);
+        float d;
+        if (MX) d = e8m0_half_scale(w.p1[row * kb + u]);
+        else d = __half2float(reinterpret_cast<const __half*>(w.p1)[row * kb + u]);
+        const uint32_t q[4] = {qv.x, qv.y, qv.z, qv.w};
+        int lo[4], hi[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (MX) {
+                lo[i] = mxfp4_lut4(q[i] & 0x0F0F0F0Fu);
+                hi[i] = mxfp4_lut4((q[i] >> 4) & 0x0F0F0F0Fu);
+            } else {
+                lo[i] = (int)__vsub4(q[i] & 0x0F0F0F0Fu, 0x08080808u);
+                hi[i] = (int)__vsub4((q[i] >> 4) & 0x0F0F0F0Fu, 0x08080808u);
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const int mr = m < mv ? m : 0;
+            const int4 x0 = *reinterpret_cast<const int4*>(xq + (long)mr * K + u * 32);
+            const int4 x1 = *reinterpret_cast<const int4*>(xq + (long)mr * K + u * 32 + 16);
+            const int xl[4] = {x0.x, x0.y, x0.z, x0.w}, xh[4] = {x1.x, x1.y, x1.z, x1.w};
+            int s = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                s = __dp4a(lo[i], xl[i], s);
+                s = __dp4a(hi[i], xh[i], s);
+            }
+            acc[m] += d * xds[(long)mr * kb + u].x * (float)s;
+        }
+    }
+}
+
+// Float-weight types (BF16 / F16 / F32) against bf16 activations.
+template <int M>
+__device__ __forceinline__ void dot_float(const QW& w, long row, int lane, const bf16* xb, float* acc, int mv) {
+    const int K = w.K, units = K >> 3;
+    for (int u = lane; u < units; u += 32) {
+        float wv[8];
+        dequant8(w, row, u, wv);
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const int mr = m < mv ? m : 0;
+            const uint4 xv = *reinterpret_cast<const uint4*>(xb + (long)mr * K + 8 * u);
+            const bf16* xe = reinterpret_cast<const bf16*>(&xv);
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s += wv[i] * bf2f(xe[i]);
+            acc[m] += s;
+        }
+    }
+}
+
+template <int M>
+__device__ __forceinline__ void dot_row(const QW& w, long row, int lane, const int8_t* xq,
+                                        const float2* xds, const bf16* xb, float* acc, int mv) {
+    switch (w.type) {
+    case TSB_Q4_K: dot_q4k<M>(w, row, lane, xq, xds, acc, mv); break;
+    case TSB_Q5_K: dot_q5k<M>(w, row, lane, xq, xds, acc, mv); break;
+    case TSB_Q6_K: dot_q6k<M>(w, row, lane, xq, xds, acc, mv); break;
+    case TSB_Q8_0: dot_q8_0<M>(w, row, lane, xq, xds, acc, mv); break;
+    case TSB_MXFP4: dot_q4_32<M, true>(w, row, lane, xq, xds, acc, mv); break;
+    case TSB_Q4_0: dot_q4_32<M, false>(w, row, lane, xq, xds, acc, mv); break;
+    default: dot_float<M>(w, row, lane, xb, acc, mv); break;
+    }
+}
+
+template <int M, bool GLU>
+__global__ void __launch_bounds__(128) gemv_kernel(GemvArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int n_out = a.n_out;
+    if (r >= n_out) return;
+    const int p = blockIdx.y;                       // problem (MoE slot) or M-chunk
+    int expert = 0, xrow, orow;
+    if (a.ids) {
+        expert = a.ids[p];
+        if (expert < 0) return;
+        xrow = p / a.x_div;
+        orow = p;
+    } else {
+        xrow = p * M;
+        orow = p * M;
+    }
+    const int K = a.w.K, kb = K >> 5;
+    const int8_t* xq = a.xq ? a.xq + (long)xrow * K : nullptr;
+    const float2* xds = a.xds ? a.xds + (long)xrow * kb : nullptr;
+    const bf16* xb = a.xb ? a.xb + (long)xrow * K : nullptr;
+    const long wrow = (long)expert * a.w.N + r;
+    float acc[M], acc2[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) { acc[m] = 0.f; acc2[m] = 0.f; }
+    const int mv = a.ids ? 1 : min(M, a.M - orow);
+    dot_row<M>(a.w, wrow, lane, xq, xds, xb, acc, mv);
+    if (GLU) dot_row<M>(a.w, wrow + n_out, lane, xq, xds, xb, acc2, mv);
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+        acc[m] = warp_sum(acc[m]);
+        if (GLU) acc2[m] = warp_sum(acc2[m]);
+    }
+    if (lane == 0) {
+        const int mrows = mv;
+        for (int m = 0; m < M; ++m) {
+            if (m >= mrows) break;
+            float v = acc[m];
+            if (a.bias) v += a.bias[(long)expert * a.w.N + r];
+            if (GLU) {
+                float u = acc2[m];
+                if (a.bias) u += a.bias[(long)expert * a.w.N + r + n_out];
+                v = act_glu(a.act, v, u);
+            } else if (a.act == ACT_RELU2) {
+                v = fmaxf(v, 0.f);
+                v = v * v;
+            }
+            if (a.row_scale) v *= a.row_scale[orow + m];
+            const long o = (long)(orow + m) * n_out + r;
+            if (a.out_f32) {
+                if (a.residual) v += reinterpret_cast<const float*>(a.residual)[o];
+                reinterpret_cast<float*>(a.out)[o] = v;
+            } else {
+                if (a.residual) v += bf2f(reinterpret_cast<const bf16*>(a.residual)[o]);
+                reinterpret_cast<bf16*>(a.out)[o] = f2bf(v);
+            }
+        }
+    }
+}
+
+// x [M, K] (bf16 or f32) -> int8 groups of 32 with (scale, float sum).  One warp per group.
+template <typename T>
+__global__ void quantize_q8_kernel(const T* x, int8_t* xq, float2* xds, long n_groups) {
+    const long g = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (g >= n_groups) return;
+    const int lane = threadIdx.x & 31;
+    const float v = (float)x[g * 32 + lane];
+    const float amax = warp_max(fabsf(v));
+    const float sum = warp_sum(v);
+    const float d = amax / 127.f;
+    const float q = (amax > 0.f) ? v / d : 0.f;
+    xq[g * 32 + lane] = (int8_t)__float2int_rn(q);
+    if (lane == 0) xds[g] = make_float2(d, sum);
+}
+
+static bool type_uses_q8(int t) {
+    return t == TSB_Q4_K || t == TSB_Q5_K || t == TSB_Q6_K || t == TSB_Q8_0 || t == TSB_MXFP4 || t == TSB_Q4_0;
+}
+
+extern "C" int tsb_quantize_q8(const void* x, int x_is_f32, void* xq, void* xds, long rows, int K, void* stream) {
+    TSB_CHECK_ARG(K % 32 == 0, "quantize_q8: K=%d is not a multiple of 32", K);
+    const long groups = rows * (K / 32);
+    if (groups == 0) return TSB_OK;
+    const int wpb = 8;
+    dim3 grid((unsigned)((groups + wpb - 1) / wpb)), block(32 * wpb);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (x_is_f32)
+        quantize_q8_kernel<float><<<grid, block, 0, s>>>((const float*)x, (int8_t*)xq, (float2*)xds, groups);
+    else
+        quantize_q8_kernel<bf16><<<grid, block, 0, s>>>((const bf16*)x, (int8_t*)xq, (float2*)xds, groups);
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}
+
+template <bool GLU>
+static int launch_gemv(const GemvArgs& a, int problems, cudaStream_t s) {
+    const int rows = a.n_out;
+    dim3 block(128);
+    if (a.ids) {
+        dim3 grid((rows + 3) / 4, problems);
+        gemv_kernel<1, GLU><<<grid, block, 0, s>>>(a);
+    } else {
+        const int M = a.M;
+        if (M <= 1) { dim3 grid((rows + 3) / 4, 1); gemv_kernel<1, GLU><<<grid, block, 0, s>>>(a); }
+        else if (M <= 2) { dim3 grid((rows + 3) / 4, 1); gemv_kernel<2, GLU><<<grid, block, 0, s>>>(a); }
+        else if (M <= 4) { dim3 grid((rows + 3) / 4, 1); gemv_kernel<4, GLU><<<grid, block, 0, s>>>(a); }
+        else { dim3 grid((rows + 3) / 4, (M + 7) / 8); gemv_kernel<8, GLU><<<grid, block, 0, s>>>(a); }
+    }
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}
+
+// out = act(W x + bias) * row_scale + residual.  See GemvArgs for the meaning of each field.
+extern "C" int tsb_gemv(const void* p0, const void* p1, const void* p2, const void* p3, int type, int N, int K,
+                        const void* xq, const void* xds, const void* xb, void* out, const float* bias,
+                        const void* residual, const int* ids, const float* row_scale, int M, int problems,
+                        int x_div, int out_f32, int act, void* stream) {
+    TSB_CHECK_ARG(N > 0 && K > 0 && M >= 0, "gemv: bad shape N=%d K=%d M=%d", N, K, M);
+    const bool q8 = type_uses_q8(type);
+    TSB_CHECK_ARG(!q8 || (xq && xds), "gemv: quantised weight type %d needs int8 activations", type);
+    TSB_CHECK_ARG(q8 || xb, "gemv: float weight type %d needs bf16 activations", type);
+    const bool kq = type == TSB_Q4_K || type == TSB_Q5_K || type == TSB_Q6_K;
+    TSB_CHECK_ARG(K % (kq ? 256 : 32) == 0, "gemv: K=%d not a whole number of blocks for type %d", K, type);
+    const bool glu = act >= ACT_SWIGLU && act <= ACT_SWIGLU_OAI;
+    TSB_CHECK_ARG(!glu || N % 2 == 0, "gemv: GLU needs an even row count, got %d", N);
+    if (M == 0 || (ids && problems == 0)) return TSB_OK;
+    GemvArgs a;
+    a.w = QW{(const uint8_t*)p0, (const uint8_t*)p1, (const uint8_t*)p2, (const uint8_t*)p3, type, N, K};
+    a.xq = (const int8_t*)xq; a.xds = (const float2*)xds; a.xb = (const bf16*)xb;
+    a.out = out; a.bias = bias; a.residual = residual; a.ids = ids; a.row_scale = row_scale;
+    a.M = M; a.x_div = x_div > 0 ? x_div : 1; a.out_f32 = out_f32; a.act = act;
+    a.n_out = glu ? N / 2 : N;
+    return glu ? launch_gemv<true>(a, problems, (cudaStream_t)stream)
+               : launch_gemv<false>(a, problems, (cudaStream_t)stream);
+}
