@@ -383,3 +383,30 @@ extern "C" int tsb_argmax(const float* logits, long stride, long rows, int V, in
     TSB_CHECK_LAUNCH();
     return TSB_OK;
 }
+
+// ------------------------------------------------------------------------------------------
+// Decode bookkeeping on the device, so that a captured decode graph can run step after step
+// without the host: feed the sampled ids back as the next inputs, advance positions and
+// cache lengths, and look up the KV slot of the new position in the block table.
+// ------------------------------------------------------------------------------------------
+__global__ void decode_advance_kernel(const int* sampled, int* tokens, int* positions, int* kv_lens, long* slots,
+                                      const int* block_table, int max_pages, int page_size, int B) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= B) return;
+    tokens[b] = sampled[b];
+    const int p = positions[b] + 1;
+    positions[b] = p;
+    kv_lens[b] = p + 1;
+    int page = p / page_size;
+    if (page >= max_pages) page = max_pages - 1;   // out of reserved pages: stay inside the table
+    slots[b] = (long)block_table[(long)b * max_pages + page] * page_size + p % page_size;
+}
+
+extern "C" int tsb_decode_advance(const int* sampled, int* tokens, int* positions, int* kv_lens, long* slots,
+                                  const int* block_table, int max_pages, int page_size, int B, void* stream) {
+    if (B == 0) return TSB_OK;
+    decode_advance_kernel<<<(B + 127) / 128, 128, 0, (cudaStream_t)stream>>>(sampled, tokens, positions, kv_lens, slots,
+                                                                            block_table, max_pages, page_size, B);
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}

@@ -1,0 +1,215 @@
+"""Model base class: GGUF loading, configuration, weights, KV pool and the public
+single-sequence API (``forward`` / ``reset_kv_cache`` / ``truncate_kv_cache``).
+
+Parity: TensorSharp.Models/ModelBase.cs:285-300 (ParseBaseConfig), :302-408 (context
+length: env MAX_CONTEXT, then metadata, fallback 4096), :499-511 (which tensors stay
+quantised), :532-658 (LoadWeights), :660-706 (one-time device upload), :1991-2007
+(factory by ``general.architecture``); TensorSharp.Runtime/Contracts.cs
+(IModelArchitecture: Forward, ResetKVCache, SupportsKVCacheTruncation, TruncateKVCache).
+Unlike the reference, ``forward_batch`` runs any number of sequences in one packed batch.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..gguf.constants import GGMLType
+from ..gguf.reader import GGUFFile
+from ..ops import functional as F
+from ..ops.functional import Batch
+from ..quant import codecs
+from ..quant.qweight import QuantWeight
+from ..runtime.paged_kv import PagedKV, SeqState
+
+
+@dataclass
+class ModelConfig:
+    """Fields read from ``{arch}.*`` GGUF metadata (ModelPrimitives.cs ModelConfig)."""
+    arch: str = ""
+    n_layers: int = 0
+    hidden: int = 0
+    n_heads: int = 0
+    n_kv_heads: int = 0
+    head_dim: int = 0
+    ffn: int = 0
+    vocab: int = 0
+    eps: float = 1e-6
+    rope_base: float = 10000.0
+    rope_scale: float = 1.0
+    context_length: int = 4096
+    chat_template: Optional[str] = None
+    extra: Dict[str, object] = field(default_factory=dict)
+
+
+_REGISTRY: Dict[str, Callable] = {}
+
+
+def register_architecture(*names: str):
+    def deco(cls):
+        for n in names:
+            _REGISTRY[n] = cls
+        return cls
+    return deco
+
+
+def supported_architectures() -> List[str]:
+    return sorted(_REGISTRY)
+
+
+class ModelBase:
+    supports_kv_truncation = True
+
+    def __init__(self, path: str, device="cuda", *, max_context: Optional[int] = None, max_seqs: int = 1,
+                 page_size: int = 64, kv_dtype: Optional[torch.dtype] = None, tp_rank: int = 0, tp_size: int = 1,
+                 ep_rank: int = 0, ep_size: int = 1, comm=None):
+        self.path = path
+        self.device = torch.device(device)
+        self.gguf = GGUFFile(path)
+        self.tp_rank, self.tp_size, self.ep_rank, self.ep_size, self.comm = tp_rank, tp_size, ep_rank, ep_size, comm
+        g = self.gguf
+        self.arch = g.get_str("general.architecture", "")
+        self.cfg = self.parse_base_config()
+        self.parse_config()
+        ctx_env = os.environ.get("MAX_CONTEXT")
+        self.max_context = int(max_context or (int(ctx_env) if ctx_env else 0) or self.cfg.context_length or 4096)
+        self.page_size = page_size
+        self.max_seqs = max_seqs
+        self.kv_dtype = kv_dtype or (torch.bfloat16 if self.device.type == "cuda" else torch.float32)
+        self.weights: Dict[str, object] = {}
+        self.load_weights()
+        self.kv = self.make_kv_pool()
+        self._default_seq: Optional[SeqState] = None
+        self.timing: Dict[str, float] = {}
+
+    # ------------------------------------------------------------------ configuration
+    def parse_base_config(self) -> ModelConfig:
+        g, a = self.gguf, self.arch
+        c = ModelConfig(arch=a)
+        c.n_layers = g.get_int(f"{a}.block_count")
+        c.hidden = g.get_int(f"{a}.embedding_length")
+        c.n_heads = g.get_int(f"{a}.attention.head_count")
+        c.n_kv_heads = g.get_int(f"{a}.attention.head_count_kv", c.n_heads)
+        c.eps = g.get_float(f"{a}.attention.layer_norm_rms_epsilon", 1e-6)
+        c.rope_base = g.get_float(f"{a}.rope.freq_base", 10000.0)
+        c.rope_scale = g.get_float(f"{a}.rope.scaling.factor", 1.0) or 1.0
+        c.chat_template = g.get_str("tokenizer.chat_template")
+        kl = g.get_int(f"{a}.attention.key_length", 0)
+        vl = g.get_int(f"{a}.attention.value_length", 0)
+        c.head_dim = kl or vl or (c.hidden // max(1, c.n_heads))
+        c.ffn = g.get_int(f"{a}.feed_forward_length", 0)
+        c.context_length = g.get_int(f"{a}.context_length", 4096)
+        if "token_embd.weight" in g.tensors:
+            c.vocab = g.tensors["token_embd.weight"].shape[0]
+        else:
+            toks = g.get_array("tokenizer.ggml.tokens")
+            c.vocab = len(toks) if toks else 0
+        return c
+
+    def parse_config(self) -> None:
+        """Architecture-specific metadata; subclasses override."""
+
+    # ------------------------------------------------------------------ weights
+    def has(self, name: str) -> bool:
+        return name in self.gguf.tensors
+
+    def qw(self, name: str, optional: bool = False) -> Optional[QuantWeight]:
+        """A matrix kept in its GGUF block form (2-D weights and 3-D expert stacks)."""
+        if name not in self.gguf.tensors:
+            if optional:
+                return None
+            raise KeyError(f"{self.path}: tensor {name!r} not found")
+        ti = self.gguf.tensors[name]
+        raw = self.gguf.tensor_bytes_view(name)
+        return QuantWeight.from_raw(raw, ti.ggml_type, ti.shape, self.device, name)
+
+    def f32(self, name: str, optional: bool = False) -> Optional[torch.Tensor]:
+        """A small tensor (norm weight, bias, scalar table) decoded to float32 on the device."""
+        if name not in self.gguf.tensors:
+            if optional:
+                return None
+            raise KeyError(f"{self.path}: tensor {name!r} not found")
+        ti = self.gguf.tensors[name]
+        raw = torch.from_numpy(np.array(self.gguf.tensor_bytes_view(name)))
+        return codecs.dequantize(raw, ti.ggml_type, ti.shape).to(self.device).contiguous()
+
+    def load_weights(self) -> None:
+        raise NotImplementedError
+
+    # ------------------------------------------------------------------ KV pool
+    def kv_layer_shapes(self) -> List[Optional[Tuple[int, int]]]:
+        c = self.cfg
+        return [(c.n_kv_heads // self.tp_size, c.head_dim)] * c.n_layers
+
+    def kv_donors(self) -> Dict[int, int]:
+        return {}
+
+    def make_kv_pool(self) -> PagedKV:
+        pages_per_seq = (self.max_context + self.page_size - 1) // self.page_size
+        return PagedKV(self.kv_layer_shapes(), pages_per_seq * self.max_seqs, self.page_size, self.device,
+                       self.kv_dtype, self.kv_donors(), max_seqs=max(self.max_seqs, 1))
+
+    # ------------------------------------------------------------------ execution
+    def forward_batch(self, batch: Batch, want_logits: bool = True) -> Optional[torch.Tensor]:
+        """Run the packed batch; returns float32 logits ``[B, vocab]`` for the last token of
+        every sequence (or ``None`` when ``want_logits`` is false: prefill chunks)."""
+        raise NotImplementedError
+
+    def reset_recurrent_state(self, slot: int) -> None:
+        """Zero per-sequence recurrent state (models with linear-attention / SSM layers)."""
+
+    # ------------------------------------------------------------------ single-sequence API
+    def _seq(self) -> SeqState:
+        if self._default_seq is None:
+            self._default_seq = self.kv.new_seq()
+            self.reset_recurrent_state(self._default_seq.slot)
+        return self._default_seq
+
+    @property
+    def cache_length(self) -> int:
+        return self._default_seq.length if self._default_seq is not None else 0
+
+    def forward(self, tokens: Sequence[int], want_logits: bool = True) -> Optional[torch.Tensor]:
+        """Append ``tokens`` to the default sequence and return the next-token logits
+        (float32 ``[vocab]`` on the compute device).  IModelArchitecture.Forward."""
+        batch = self.kv.build_batch([self._seq()], [list(tokens)])
+        out = self.forward_batch(batch, want_logits)
+        return out[0] if out is not None else None
+
+    def forward_refill(self, tokens: Sequence[int], chunk: int = 2048) -> torch.Tensor:
+        """Chunked prefill: all chunks but the last skip the logits (Qwen3Model.cs:238
+        ForwardRefill; chunk size policy TensorSharp.Server/ModelService.cs:791-801)."""
+        tokens = list(tokens)
+        out = None
+        for i in range(0, len(tokens), chunk):
+            last = i + chunk >= len(tokens)
+            out = self.forward(tokens[i:i + chunk], want_logits=last)
+        return out
+
+    def reset_kv_cache(self) -> None:
+        if self._default_seq is not None:
+            self.kv.truncate(self._default_seq, 0)
+            self.reset_recurrent_state(self._default_seq.slot)
+
+    def truncate_kv_cache(self, n_tokens: int) -> None:
+        if not self.supports_kv_truncation:
+            raise RuntimeError(f"{type(self).__name__} cannot truncate its cache (recurrent state)")
+        if self._default_seq is not None:
+            self.kv.truncate(self._default_seq, n_tokens)
+
+    def close(self) -> None:
+        self.gguf.close()
+
+    # ------------------------------------------------------------------ factory
+    @staticmethod
+    def create(path: str, device="cuda", **kw) -> "ModelBase":
+        """Open ``path`` and instantiate the graph for its ``general.architecture``."""
+        from . import _load_all  # noqa: F401  (registers every architecture)
+        with GGUFFile(path) as g:
+            arch = g.get_str("general.architecture", "")
+        if arch not in _REGISTRY:
+            raise ValueError(f"unsupported architecture {arch!r}; supported: {supported_architectures()}")
+        return _REGISTRY[arch](path, device, **kw)

@@ -1,0 +1,97 @@
+"""Qwen3 dense decoder: GQA attention with per-head QK RMSNorm, NeoX RoPE, SwiGLU FFN.
+
+Parity: TensorSharp.Models/Models/Qwen3/Qwen3Model.cs:32-55 (construction, fused QKV and
+gate/up), :175-236 (Forward: embedding, blocks, output_norm, last-row logits, tied
+embeddings), :317-421 (attention: QK-norm, RoPE mode NeoX, cache write, causal softmax).
+Tensor names: blk.{l}.{attn_norm, attn_q, attn_k, attn_v, attn_q_norm, attn_k_norm,
+attn_output, ffn_norm, ffn_gate, ffn_up, ffn_down}.weight, output_norm.weight,
+output.weight (optional), token_embd.weight.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..ops import functional as F
+from ..ops.functional import Batch, RopeSpec
+from ..quant.qweight import QuantWeight
+from .base import ModelBase, register_architecture
+
+
+@register_architecture("qwen3", "qwen2", "llama")
+class Qwen3Model(ModelBase):
+    def load_weights(self) -> None:
+        c = self.cfg
+        self.tok_emb = self.qw("token_embd.weight")
+        self.out_norm = self.f32("output_norm.weight")
+        self.lm_head = self.qw("output.weight", optional=True) or self.tok_emb
+        self.layers = []
+        for l in range(c.n_layers):
+            p = f"blk.{l}."
+            q, k, v = self.qw(p + "attn_q.weight"), self.qw(p + "attn_k.weight"), self.qw(p + "attn_v.weight")
+            L = {
+                "attn_norm": self.f32(p + "attn_norm.weight"),
+                "q_norm": self.f32(p + "attn_q_norm.weight", optional=True),
+                "k_norm": self.f32(p + "attn_k_norm.weight", optional=True),
+                "wo": self.qw(p + "attn_output.weight"),
+                "ffn_norm": self.f32(p + "ffn_norm.weight"),
+                "down": self.qw(p + "ffn_down.weight"),
+            }
+            # fused QKV needs one ggml type for the three matrices (Qwen3Model.cs:67-78)
+            if q.ggml_type == k.ggml_type == v.ggml_type:
+                L["wqkv"] = QuantWeight.concat_rows([q, k, v], p + "attn_qkv")
+            else:
+                L["wq"], L["wk"], L["wv"] = q, k, v
+            g, u = self.qw(p + "ffn_gate.weight"), self.qw(p + "ffn_up.weight")
+            if g.ggml_type == u.ggml_type:
+                L["gate_up"] = QuantWeight.concat_rows([g, u], p + "ffn_gate_up")
+            else:
+                L["gate"], L["up"] = g, u
+            for b in ("attn_q.bias", "attn_k.bias", "attn_v.bias"):
+                if self.has(p + b):
+                    L.setdefault("qkv_bias", [])
+                    L["qkv_bias"].append(self.f32(p + b))
+            if "qkv_bias" in L:
+                L["qkv_bias"] = torch.cat(L["qkv_bias"])
+            self.layers.append(L)
+        self.rope = RopeSpec(rot_dim=self.gguf.get_int(f"{self.arch}.rope.dimension_count", c.head_dim) or c.head_dim,
+                             theta_base=c.rope_base, mode=0 if self.arch != "llama" else 1,
+                             freq_scale=1.0 / c.rope_scale)
+
+    def forward_batch(self, batch: Batch, want_logits: bool = True) -> Optional[torch.Tensor]:
+        c = self.cfg
+        Hq, Hkv, Dh = c.n_heads, c.n_kv_heads, c.head_dim
+        T = batch.T
+        small = T <= F.GEMV_MAX_M
+        mid = torch.float32 if small else torch.bfloat16
+        h = F.embed(self.tok_emb, batch.tokens)
+        for l, L in enumerate(self.layers):
+            a = F.norm(h, L["attn_norm"], c.eps, want_q8=small)
+            if "wqkv" in L:
+                qkv = F.linear(a, L["wqkv"], bias=L.get("qkv_bias"), out_dtype=mid)
+                q = qkv[:, :Hq * Dh].view(T, Hq, Dh)
+                k = qkv[:, Hq * Dh:(Hq + Hkv) * Dh].view(T, Hkv, Dh)
+                v = qkv[:, (Hq + Hkv) * Dh:].view(T, Hkv, Dh)
+            else:
+                q = F.linear(a, L["wq"], out_dtype=mid).view(T, Hq, Dh)
+                k = F.linear(a, L["wk"], out_dtype=mid).view(T, Hkv, Dh)
+                v = F.linear(a, L["wv"], out_dtype=mid).view(T, Hkv, Dh)
+            qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=self.kv.k[l],
+                                  v_cache=self.kv.v[l], rope=self.rope, qn=L["q_norm"], kn=L["k_norm"], eps=c.eps)
+            o = F.attention(qr, self.kv.k[l], self.kv.v[l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh)
+            h = F.linear(F.as_act(o), L["wo"], residual=h)
+            a = F.norm(h, L["ffn_norm"], c.eps, want_q8=small)
+            if "gate_up" in L:
+                gu = F.linear(a, L["gate_up"], act="swiglu", out_dtype=torch.bfloat16)
+            else:
+                gu = F.glu("swiglu", F.linear(a, L["gate"], out_dtype=mid), F.linear(a, L["up"], out_dtype=mid))
+            h = F.linear(F.as_act(gu), L["down"], residual=h)
+        if not want_logits:
+            return None
+        last = h[batch.last_idx].contiguous()
+        a = F.norm(last, self.out_norm, c.eps, want_q8=True)
+        return self.lm_head_logits(a)
+
+    def lm_head_logits(self, a) -> torch.Tensor:
+        return F.linear(a, self.lm_head, out_dtype=torch.float32)

@@ -1,0 +1,283 @@
+"""ctypes bindings for the sm_100a kernels in ``libtsb200.so``.
+
+Each function takes torch CUDA tensors, passes their raw pointers and the current
+stream, and raises on a non-zero status.  There is no fallback here: if the library
+is missing the call fails loudly.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional
+
+import torch
+
+from ..gguf.constants import GGMLType
+from ..quant.qweight import QuantWeight
+from . import native
+
+ACT = {None: 0, "none": 0, "swiglu": 1, "geglu": 2, "geglu_tanh": 2, "geglu_erf": 3, "swiglu_oai": 4,
+       "relu2": 5, "silu": 6, "sigmoid_mul": 7}
+
+_vp = C.c_void_p
+
+
+def _p(t: Optional[torch.Tensor]):
+    return _vp(t.data_ptr()) if t is not None else _vp(0)
+
+
+def _stream():
+    return _vp(torch.cuda.current_stream().cuda_stream)
+
+
+def _planes(w: QuantWeight):
+    ps = [_vp(p.data_ptr()) for p in w.planes]
+    while len(ps) < 4:
+        ps.append(_vp(0))
+    return ps
+
+
+class RopeParams(C.Structure):
+    _fields_ = [("theta_base", C.c_float), ("freq_scale", C.c_float), ("ext_factor", C.c_float),
+                ("attn_factor", C.c_float), ("corr_lo", C.c_float), ("corr_hi", C.c_float),
+                ("rot_dim", C.c_int), ("mode", C.c_int)]
+
+
+class QkvArgs(C.Structure):
+    _fields_ = [("q", _vp), ("k", _vp), ("v", _vp),
+                ("q_tok", C.c_long), ("q_head", C.c_long), ("k_tok", C.c_long), ("k_head", C.c_long),
+                ("v_tok", C.c_long), ("v_head", C.c_long),
+                ("in_f32", C.c_int), ("qn", _vp), ("kn", _vp), ("v_norm", C.c_int), ("eps", C.c_float),
+                ("pos", _vp), ("slot", _vp), ("freq_factors", _vp), ("q_out", _vp), ("k_cache", _vp),
+                ("v_cache", _vp), ("q_scale", C.c_float),
+                ("T", C.c_int), ("Hq", C.c_int), ("Hkv", C.c_int), ("Dh", C.c_int), ("rp", RopeParams)]
+
+
+class AttnArgs(C.Structure):
+    _fields_ = [("q", _vp), ("k_cache", _vp), ("v_cache", _vp), ("out", _vp), ("block_table", _vp),
+                ("kv_lens", _vp), ("cu_q", _vp), ("sinks", _vp), ("part_o", _vp), ("part_ml", _vp),
+                ("scale", C.c_float), ("softcap", C.c_float), ("window", C.c_int),
+                ("B", C.c_int), ("Hq", C.c_int), ("Hkv", C.c_int), ("Dh", C.c_int), ("page_size", C.c_int),
+                ("max_pages", C.c_int), ("splits", C.c_int)]
+
+
+_configured = False
+LAUNCHES = 0          # kernels launched through this module (eager mode; graph replays add theirs)
+
+
+def _count(n: int = 1) -> None:
+    global LAUNCHES
+    LAUNCHES += n
+
+
+def _lib():
+    global _configured
+    lib = native.lib()
+    if not _configured:
+        for name in ("tsb_quantize_q8", "tsb_gemv", "tsb_rmsnorm", "tsb_qkv_rope", "tsb_glu", "tsb_gather_rows",
+                     "tsb_argmax", "tsb_decode_advance", "tsb_attn_decode", "tsb_attn_prefill", "tsb_gemm_bf16"):
+            getattr(lib, name).restype = C.c_int
+        _configured = True
+    return lib
+
+
+# --------------------------------------------------------------------------------------------
+def quantize_q8(x: torch.Tensor):
+    """x [rows, K] (bf16 or f32) -> (int8 [rows, K], float32 [rows, K/32, 2])."""
+    assert x.is_cuda and x.is_contiguous()
+    rows, K = x.shape
+    xq = torch.empty((rows, K), dtype=torch.int8, device=x.device)
+    xds = torch.empty((rows, K // 32, 2), dtype=torch.float32, device=x.device)
+    native.check(_lib().tsb_quantize_q8(_p(x), C.c_int(x.dtype == torch.float32), _p(xq), _p(xds), C.c_long(rows),
+                                        C.c_int(K), _stream()), "quantize_q8")
+    _count(1)
+    return xq, xds
+
+
+def gemv(w: QuantWeight, *, xq=None, xds=None, xb=None, M: int, out_dtype=torch.float32, bias=None, residual=None,
+         act=None, ids=None, row_scale=None, x_div: int = 1, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Small-batch matvec over quantised weights.  With ``ids`` ([P] int32) each problem p
+    uses expert ids[p], activation row p // x_div and output row p."""
+    a = ACT[act]
+    glu = 1 <= a <= 4
+    n_out = w.N // 2 if glu else w.N
+    problems = int(ids.numel()) if ids is not None else 1
+    rows = problems if ids is not None else M
+    dev = w.device
+    if out is None:
+        out = torch.empty((rows, n_out), dtype=out_dtype, device=dev)
+    ps = _planes(w)
+    native.check(_lib().tsb_gemv(ps[0], ps[1], ps[2], ps[3], C.c_int(int(w.ggml_type)), C.c_int(w.N), C.c_int(w.K),
+                                 _p(xq), _p(xds), _p(xb), _p(out), _p(bias), _p(residual), _p(ids), _p(row_scale),
+                                 C.c_int(M), C.c_int(problems), C.c_int(x_div),
+                                 C.c_int(out.dtype == torch.float32), C.c_int(a), _stream()), "gemv")
+    _count(1)
+    return out
+
+
+def rmsnorm(x: torch.Tensor, w: Optional[torch.Tensor], eps: float, *, delta=None, want_bf16=True, want_q8=False,
+            want_f32=False, add=None, l2=False):
+    """Fused (x += delta) -> RMSNorm -> {bf16, f32 (+add), q8}.  Returns (y_bf16, y_f32, yq, yds)."""
+    assert x.is_cuda and x.is_contiguous()
+    D = x.shape[-1]
+    rows = x.numel() // D
+    dev = x.device
+    yb = torch.empty(x.shape, dtype=torch.bfloat16, device=dev) if want_bf16 else None
+    yf = torch.empty(x.shape, dtype=torch.float32, device=dev) if (want_f32 or add is not None) else None
+    yq = yds = None
+    if want_q8:
+        yq = torch.empty((rows, D), dtype=torch.int8, device=dev)
+        yds = torch.empty((rows, D // 32, 2), dtype=torch.float32, device=dev)
+    native.check(_lib().tsb_rmsnorm(_p(x), C.c_int(x.dtype == torch.float32), _p(delta), _p(w), C.c_float(eps),
+                                    C.c_long(rows), C.c_int(D), _p(yb), _p(yf), _p(add), _p(yq), _p(yds),
+                                    C.c_int(1 if l2 else 0), _stream()), "rmsnorm")
+    _count(1)
+    return yb, yf, yq, yds
+
+
+def yarn_corr_dims(n_dims: int, n_ctx_orig: int, freq_base: float, beta_fast: float, beta_slow: float):
+    """ggml's rope_yarn_corr_dims: the pair-index range over which YaRN blends."""
+    def corr(n_rot):
+        return n_dims * math.log(n_ctx_orig / (n_rot * 2 * math.pi)) / (2 * math.log(freq_base))
+    lo = max(0.0, math.floor(corr(beta_fast)))
+    hi = min(n_dims - 1.0, math.ceil(corr(beta_slow)))
+    return lo, hi
+
+
+def qkv_rope(*, q, k, v, q_strides, k_strides, v_strides, Hq, Hkv, Dh, pos, slot, q_out, k_cache, v_cache,
+             qn=None, kn=None, v_norm=False, eps=1e-6, rope: RopeParams, freq_factors=None, q_scale=1.0):
+    T = int(pos.numel())
+    a = QkvArgs()
+    a.q, a.k, a.v = _p(q), _p(k), _p(v)
+    a.q_tok, a.q_head = q_strides
+    a.k_tok, a.k_head = k_strides
+    a.v_tok, a.v_head = v_strides
+    a.in_f32 = int(q.dtype == torch.float32)
+    a.qn, a.kn = _p(qn), _p(kn)
+    a.v_norm = int(v_norm)
+    a.eps = eps
+    a.pos, a.slot, a.freq_factors = _p(pos), _p(slot), _p(freq_factors)
+    a.q_out, a.k_cache, a.v_cache = _p(q_out), _p(k_cache), _p(v_cache)
+    a.q_scale = q_scale
+    a.T, a.Hq, a.Hkv, a.Dh = T, Hq, Hkv, Dh
+    a.rp = rope
+    native.check(_lib().tsb_qkv_rope(C.byref(a), _stream()), "qkv_rope")
+    _count(1)
+
+
+def glu(gate: torch.Tensor, up: Optional[torch.Tensor], act: str, F: int, g_stride: int, u_stride: int, rows: int,
+        want_bf16=True, want_q8=False):
+    dev = gate.device
+    out = torch.empty((rows, F), dtype=torch.bfloat16, device=dev) if want_bf16 else None
+    yq = yds = None
+    if want_q8:
+        yq = torch.empty((rows, F), dtype=torch.int8, device=dev)
+        yds = torch.empty((rows, F // 32, 2), dtype=torch.float32, device=dev)
+    native.check(_lib().tsb_glu(_p(gate), _p(up), C.c_int(gate.dtype == torch.float32), C.c_long(g_stride),
+                                C.c_long(u_stride), C.c_long(rows), C.c_int(F), C.c_int(ACT[act]), _p(out), _p(yq),
+                                _p(yds), _stream()), "glu")
+    _count(1)
+    return out, yq, yds
+
+
+def gather_rows(w: QuantWeight, ids: Optional[torch.Tensor], scale: float = 1.0, out_dtype=torch.bfloat16,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Embedding lookup (ids given) or whole-matrix decode to ``out_dtype`` (ids None)."""
+    n = int(ids.numel()) if ids is not None else w.rows
+    if out is None:
+        out = torch.empty((n, w.K), dtype=out_dtype, device=w.device)
+    ps = _planes(w)
+    native.check(_lib().tsb_gather_rows(ps[0], ps[1], ps[2], ps[3], C.c_int(int(w.ggml_type)), C.c_int(w.rows),
+                                        C.c_int(w.K), _p(ids), C.c_long(n), C.c_float(scale), _p(out),
+                                        C.c_int(out.dtype == torch.float32), _stream()), "gather_rows")
+    _count(1)
+    return out
+
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    assert logits.dtype == torch.float32 and logits.stride(-1) == 1
+    rows, V = logits.shape
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    native.check(_lib().tsb_argmax(_p(logits), C.c_long(logits.stride(0)), C.c_long(rows), C.c_int(V), _p(out), _vp(0),
+                                   _stream()), "argmax")
+    _count(1)
+    return out
+
+
+def decode_advance(sampled, batch) -> None:
+    """In-place, on the device: next tokens = sampled, positions / kv_lens += 1, new KV slots."""
+    B = batch.tokens.shape[0]
+    native.check(_lib().tsb_decode_advance(_p(sampled), _p(batch.tokens), _p(batch.positions), _p(batch.kv_lens),
+                                           _p(batch.slots), _p(batch.block_table), C.c_int(batch.block_table.shape[1]),
+                                           C.c_int(batch.page_size), C.c_int(B), _stream()), "decode_advance")
+    _count(1)
+
+
+def _attn_args(q, k_cache, v_cache, out, block_table, kv_lens, cu_q, sinks, scale, softcap, window, Hq, Hkv, Dh,
+               page_size, B):
+    a = AttnArgs()
+    a.q, a.k_cache, a.v_cache, a.out = _p(q), _p(k_cache), _p(v_cache), _p(out)
+    a.block_table, a.kv_lens, a.cu_q, a.sinks = _p(block_table), _p(kv_lens), _p(cu_q), _p(sinks)
+    a.scale, a.softcap, a.window = scale, softcap or 0.0, int(window or 0)
+    a.B, a.Hq, a.Hkv, a.Dh, a.page_size = B, Hq, Hkv, Dh, page_size
+    a.max_pages = block_table.shape[1]
+    a.splits = 1
+    return a
+
+
+def attn_decode(q, k_cache, v_cache, block_table, kv_lens, *, scale, Hq, Hkv, Dh, page_size, splits, sinks=None,
+                softcap=0.0, window=0, out=None):
+    """q [B, Hq, Dh] bf16; one query per sequence against the paged cache."""
+    B = q.shape[0]
+    if out is None:
+        out = torch.empty_like(q)
+    a = _attn_args(q, k_cache, v_cache, out, block_table, kv_lens, None, sinks, scale, softcap, window, Hq, Hkv, Dh,
+                   page_size, B)
+    a.splits = splits
+    part_o = torch.empty((B, Hq, splits, Dh), dtype=torch.float32, device=q.device)
+    part_ml = torch.empty((B, Hq, splits, 2), dtype=torch.float32, device=q.device)
+    a.part_o, a.part_ml = _p(part_o), _p(part_ml)
+    native.check(_lib().tsb_attn_decode(C.byref(a), _stream()), "attn_decode")
+    _count(2)
+    return out
+
+
+def attn_prefill(q, k_cache, v_cache, block_table, kv_lens, cu_q, max_q_len, *, scale, Hq, Hkv, Dh, page_size,
+                 sinks=None, softcap=0.0, window=0, out=None):
+    """q [T, Hq, Dh] bf16 packed over sequences (cu_q [B+1])."""
+    B = kv_lens.shape[0]
+    if out is None:
+        out = torch.empty_like(q)
+    a = _attn_args(q, k_cache, v_cache, out, block_table, kv_lens, cu_q, sinks, scale, softcap, window, Hq, Hkv, Dh,
+                   page_size, B)
+    native.check(_lib().tsb_attn_prefill(C.byref(a), C.c_int(max_q_len), _stream()), "attn_prefill")
+    _count(1)
+    return out
+
+
+_status_words = {}
+
+
+def gemm_status(device) -> torch.Tensor:
+    key = torch.device(device).index or 0
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status_words[key]
+
+
+def gemm_bf16(W: torch.Tensor, X: torch.Tensor, *, out_dtype=torch.bfloat16, bias=None, residual=None,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[T, N] = X[T, K] @ W[N, K]^T on tcgen05 tensor cores (bf16 in, f32 accumulate)."""
+    assert W.dtype == torch.bfloat16 and X.dtype == torch.bfloat16
+    assert W.stride(1) == 1 and X.stride(1) == 1
+    N, K = W.shape
+    T = X.shape[0]
+    if out is None:
+        out = torch.empty((T, N), dtype=out_dtype, device=X.device)
+    native.check(_lib().tsb_gemm_bf16(_p(W), C.c_long(W.stride(0)), _p(X), C.c_long(X.stride(0)), _p(out),
+                                      C.c_long(out.stride(0)), C.c_int(out.dtype == torch.float32), _p(bias),
+                                      _p(residual), C.c_int(T), C.c_int(N), C.c_int(K), _p(gemm_status(X.device)),
+                                      _stream()), "gemm_bf16")
+    _count(1)
+    return out

@@ -1,0 +1,125 @@
+"""Plain PyTorch fp32 restatements of every fused op.
+
+These are the numerical oracle for the CUDA kernels and the execution path of the CPU
+backend (tiny-model tests, golden parity).  They mirror the reference's semantics:
+RMSNorm (TensorApplyCPU.cs:2206), RoPE NeoX / adjacent-pair with YaRN
+(TensorApplyCPU.cs:1658-1806), softmax attention with sinks
+(Models/GptOss/GptOssModel.cs:591-623), sliding-window masks (:575), gated activations
+(GptOssModel.cs:901-934 for the clamp variant).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+
+def rmsnorm(x: torch.Tensor, w: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    x = x.float()
+    y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+    return y * w.float() if w is not None else y
+
+
+def l2norm(x: torch.Tensor, eps: float) -> torch.Tensor:
+    x = x.float()
+    return x / x.norm(dim=-1, keepdim=True).clamp_min(eps)
+
+
+def layernorm(x, w, b, eps):
+    return torch.nn.functional.layer_norm(x.float(), (x.shape[-1],), w, b, eps)
+
+
+def rope_cos_sin(pos: torch.Tensor, rot_dim: int, theta_base: float, freq_scale: float = 1.0,
+                 ext_factor: float = 0.0, attn_factor: float = 1.0, corr_lo: float = 0.0, corr_hi: float = 0.0,
+                 freq_factors: Optional[torch.Tensor] = None):
+    """cos / sin tables [T, rot_dim/2] following ggml's rope_yarn."""
+    pair = torch.arange(rot_dim // 2, dtype=torch.float32, device=pos.device)
+    theta = pos.float().unsqueeze(1) * torch.pow(torch.tensor(theta_base, dtype=torch.float32, device=pos.device),
+                                                 -2.0 * pair / rot_dim)
+    if freq_factors is not None:
+        theta = theta / freq_factors.float()
+    th = freq_scale * theta
+    ms = attn_factor
+    if ext_factor != 0.0:
+        y = (pair - corr_lo) / max(0.001, corr_hi - corr_lo)
+        ramp = (1.0 - y.clamp(0, 1)) * ext_factor
+        th = th * (1 - ramp) + theta * ramp
+        ms = ms * (1.0 + 0.1 * math.log(1.0 / freq_scale))
+    return torch.cos(th) * ms, torch.sin(th) * ms
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, rot_dim: int, mode: int) -> torch.Tensor:
+    """x [T, H, Dh]; mode 0 = NeoX (i, i + rot/2), 1 = adjacent pairs (2i, 2i+1)."""
+    x = x.float()
+    if rot_dim == 0:
+        return x
+    xr, xp = x[..., :rot_dim], x[..., rot_dim:]
+    c, s = cos.unsqueeze(1), sin.unsqueeze(1)
+    if mode == 0:
+        h = rot_dim // 2
+        x0, x1 = xr[..., :h], xr[..., h:]
+        out = torch.cat([x0 * c - x1 * s, x0 * s + x1 * c], -1)
+    else:
+        x0, x1 = xr[..., 0::2], xr[..., 1::2]
+        out = torch.stack([x0 * c - x1 * s, x0 * s + x1 * c], -1).flatten(-2)
+    return torch.cat([out, xp], -1)
+
+
+def glu(act: str, g: torch.Tensor, u: Optional[torch.Tensor]) -> torch.Tensor:
+    g = g.float()
+    u = u.float() if u is not None else None
+    if act == "swiglu":
+        return torch.nn.functional.silu(g) * u
+    if act in ("geglu", "geglu_tanh"):
+        return torch.nn.functional.gelu(g, approximate="tanh") * u
+    if act == "geglu_erf":
+        return torch.nn.functional.gelu(g) * u
+    if act == "swiglu_oai":
+        x = g.clamp(max=7.0)
+        y = u.clamp(-7.0, 7.0)
+        return x * torch.sigmoid(1.702 * x) * (y + 1.0)
+    if act == "relu2":
+        return torch.relu(g) ** 2
+    if act == "silu":
+        return torch.nn.functional.silu(g)
+    if act == "sigmoid_mul":
+        return torch.sigmoid(g) * u
+    return g * u
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_pos: torch.Tensor, *, scale: float,
+              window: int = 0, sinks: Optional[torch.Tensor] = None, softcap: float = 0.0) -> torch.Tensor:
+    """Naive attention for one sequence.  q [Tq, Hq, Dh]; k, v [Tk, Hkv, Dh] hold cache
+    positions 0..Tk-1; q_pos [Tq] are the queries' positions.  Returns [Tq, Hq, Dh] f32."""
+    Tq, Hq, Dh = q.shape
+    Tk, Hkv, _ = k.shape
+    g = Hq // Hkv
+    qf = q.float().permute(1, 0, 2)                                  # [Hq, Tq, Dh]
+    kf = k.float().permute(1, 0, 2).repeat_interleave(g, 0)          # [Hq, Tk, Dh]
+    vf = v.float().permute(1, 0, 2).repeat_interleave(g, 0)
+    s = torch.matmul(qf, kf.transpose(1, 2)) * scale                  # [Hq, Tq, Tk]
+    if softcap and softcap > 0:
+        s = softcap * torch.tanh(s / softcap)
+    j = torch.arange(Tk, device=q.device).view(1, 1, Tk)
+    p = q_pos.view(1, Tq, 1)
+    ok = j <= p
+    if window and window > 0:
+        ok = ok & (j > p - window)
+    s = s.masked_fill(~ok, float("-inf"))
+    if sinks is not None:
+        s = torch.cat([s, sinks.float().view(Hq, 1, 1).expand(Hq, Tq, 1)], -1)
+        pr = torch.softmax(s, -1)[..., :Tk]
+    else:
+        pr = torch.softmax(s, -1)
+    pr = torch.nan_to_num(pr, nan=0.0)
+    return torch.matmul(pr, vf).permute(1, 0, 2).contiguous()
+
+
+def quantize_q8_dequant(x: torch.Tensor) -> torch.Tensor:
+    """What the GEMV kernels see: x rounded to int8 in groups of 32 (scale amax/127)."""
+    xf = x.float()
+    g = xf.reshape(-1, 32)
+    d = g.abs().amax(1, keepdim=True) / 127.0
+    q = torch.where(d > 0, torch.round(g / d), torch.zeros_like(g))
+    return (q * d).reshape(xf.shape)

@@ -1,0 +1,264 @@
+"""Numerics of every sm_100a kernel against the fp32 PyTorch restatement of the same op."""
+import math
+
+import pytest
+import torch
+
+from tensorsharp_b200.gguf.constants import GGMLType
+from tensorsharp_b200.ops import reference as ref
+from tensorsharp_b200.quant import codecs
+from tensorsharp_b200.quant.qweight import QuantWeight
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+QTYPES = [GGMLType.Q4_K, GGMLType.Q5_K, GGMLType.Q6_K, GGMLType.Q8_0, GGMLType.Q4_0, GGMLType.MXFP4]
+FTYPES = [GGMLType.BF16, GGMLType.F16, GGMLType.F32]
+
+
+def K():
+    from tensorsharp_b200.ops import kernels
+    return kernels
+
+
+def rel_err(a, b):
+    a, b = a.float(), b.float()
+    return float((a - b).norm() / b.norm().clamp_min(1e-12))
+
+
+@pytest.mark.parametrize("t", QTYPES + FTYPES)
+def test_gather_rows_matches_codec(t):
+    torch.manual_seed(0)
+    w = torch.randn(70, 512, device=DEV) * 0.05
+    qw = QuantWeight.from_float(w, t)
+    want = qw.dequantize()
+    got = K().gather_rows(qw, None, 1.0, torch.float32)
+    assert torch.allclose(got, want, atol=1e-6, rtol=1e-6)
+    ids = torch.tensor([3, 69, 0, 3], dtype=torch.int32, device=DEV)
+    got = K().gather_rows(qw, ids, 2.0, torch.bfloat16)
+    assert torch.allclose(got.float(), (want[ids.long()] * 2.0).bfloat16().float(), atol=1e-6)
+
+
+@pytest.mark.parametrize("t", QTYPES)
+@pytest.mark.parametrize("M", [1, 3, 8, 13])
+def test_gemv_quant(t, M):
+    torch.manual_seed(1)
+    N, Kd = 203, 768
+    w = torch.randn(N, Kd, device=DEV) * 0.05
+    x = torch.randn(M, Kd, device=DEV)
+    qw = QuantWeight.from_float(w, t)
+    xq, xds = K().quantize_q8(x.bfloat16())
+    xref = ref.quantize_q8_dequant(x.bfloat16().float())
+    want = xref @ qw.dequantize().t()
+    got = K().gemv(qw, xq=xq, xds=xds, M=M)
+    assert rel_err(got, want) < 2e-3, rel_err(got, want)
+    # bias + residual, bf16 output
+    bias = torch.randn(N, device=DEV)
+    res = torch.randn(M, N, device=DEV)
+    got = K().gemv(qw, xq=xq, xds=xds, M=M, bias=bias, residual=res)
+    assert rel_err(got, want + bias + res) < 2e-3
+
+
+@pytest.mark.parametrize("t", FTYPES)
+def test_gemv_float(t):
+    torch.manual_seed(2)
+    N, Kd, M = 130, 256, 5
+    w = torch.randn(N, Kd, device=DEV) * 0.05
+    x = torch.randn(M, Kd, device=DEV).bfloat16()
+    qw = QuantWeight.from_float(w, t)
+    want = x.float() @ qw.dequantize().t()
+    got = K().gemv(qw, xb=x, M=M)
+    assert rel_err(got, want) < 1e-3
+
+
+@pytest.mark.parametrize("act", ["swiglu", "geglu", "geglu_erf", "swiglu_oai"])
+def test_gemv_glu(act):
+    torch.manual_seed(3)
+    F, Kd, M = 96, 512, 2
+    w = torch.randn(2 * F, Kd, device=DEV) * 0.1
+    x = torch.randn(M, Kd, device=DEV)
+    qw = QuantWeight.from_float(w, GGMLType.Q4_K)
+    xq, xds = K().quantize_q8(x.bfloat16())
+    y = ref.quantize_q8_dequant(x.bfloat16().float()) @ qw.dequantize().t()
+    want = ref.glu(act, y[:, :F], y[:, F:])
+    got = K().gemv(qw, xq=xq, xds=xds, M=M, act=act)
+    assert got.shape == (M, F)
+    assert rel_err(got, want) < 3e-3
+
+
+def test_gemv_moe_ids():
+    torch.manual_seed(4)
+    E, N, Kd, T, topk = 6, 64, 256, 3, 2
+    w = torch.randn(E, N, Kd, device=DEV) * 0.1
+    qw = QuantWeight.from_float(w, GGMLType.MXFP4)
+    x = torch.randn(T, Kd, device=DEV)
+    ids = torch.tensor([0, 5, 2, 2, 4, 1], dtype=torch.int32, device=DEV)
+    scale = torch.rand(T * topk, device=DEV)
+    xq, xds = K().quantize_q8(x.bfloat16())
+    xr = ref.quantize_q8_dequant(x.bfloat16().float())
+    wd = qw.dequantize().view(E, N, Kd)
+    want = torch.stack([wd[int(ids[p])] @ xr[p // topk] * scale[p] for p in range(T * topk)])
+    got = K().gemv(qw, xq=xq, xds=xds, M=1, ids=ids, x_div=topk, row_scale=scale)
+    assert rel_err(got, want) < 2e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm(dtype):
+    torch.manual_seed(5)
+    rows, D = 7, 2560
+    x = torch.randn(rows, D, device=DEV).to(dtype)
+    w = torch.rand(D, device=DEV) + 0.5
+    want = ref.rmsnorm(x, w, 1e-6)
+    yb, yf, yq, yds = K().rmsnorm(x.clone(), w, 1e-6, want_q8=True, want_f32=True)
+    assert rel_err(yf, want) < 1e-5
+    assert rel_err(yb, want) < 5e-3
+    deq = (yq.float().view(rows, D // 32, 32) * yds[..., 0:1]).view(rows, D)
+    assert rel_err(deq, want) < 1e-2
+    assert torch.allclose(yds[..., 1], want.view(rows, D // 32, 32).sum(-1), atol=1e-3)
+    # delta add writes the stream back
+    delta = torch.randn(rows, D, device=DEV).bfloat16()
+    xs = x.clone()
+    yb, *_ = K().rmsnorm(xs, w, 1e-6, delta=delta)
+    assert rel_err(xs, x.float() + delta.float()) < 5e-3
+    assert rel_err(yb, ref.rmsnorm(x.float() + delta.float(), w, 1e-6)) < 6e-3
+    # sandwich add and L2
+    h = torch.randn(rows, D, device=DEV)
+    _, yf, _, _ = K().rmsnorm(x.clone(), w, 1e-6, want_bf16=False, add=h)
+    assert rel_err(yf, h + want) < 1e-5
+    _, yf, _, _ = K().rmsnorm(x.clone(), None, 1e-6, want_bf16=False, want_f32=True, l2=True)
+    assert rel_err(yf, ref.l2norm(x, 1e-6)) < 1e-5
+
+
+@pytest.mark.parametrize("mode,rot,Dh,yarn", [(0, 128, 128, False), (0, 64, 128, True), (1, 64, 64, False),
+                                              (0, 256, 256, False), (1, 32, 96, True)])
+def test_qkv_rope_cache(mode, rot, Dh, yarn):
+    from tensorsharp_b200.ops import functional as F
+    torch.manual_seed(6)
+    T, Hq, Hkv = 9, 4, 2
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * Dh, device=DEV)
+    pos = torch.tensor([0, 1, 2, 3, 100, 4000, 31999, 7, 8], dtype=torch.int32, device=DEV)
+    slots = torch.arange(T, dtype=torch.int64, device=DEV) + 5
+    qn, kn = torch.rand(Dh, device=DEV) + 0.5, torch.rand(Dh, device=DEV) + 0.5
+    spec = F.RopeSpec(rot_dim=rot, theta_base=150000.0, mode=mode)
+    if yarn:
+        lo, hi = K().yarn_corr_dims(rot, 4096, 150000.0, 32.0, 1.0)
+        spec = F.RopeSpec(rot_dim=rot, theta_base=150000.0, mode=mode, freq_scale=1 / 32.0, ext_factor=1.0,
+                          attn_factor=1.0, corr_lo=lo, corr_hi=hi)
+    outs = {}
+    for dev in ("cuda", "cpu"):
+        x = qkv.to(dev)
+        q = x[:, :Hq * Dh].view(T, Hq, Dh)
+        k = x[:, Hq * Dh:(Hq + Hkv) * Dh].view(T, Hkv, Dh)
+        v = x[:, (Hq + Hkv) * Dh:].view(T, Hkv, Dh)
+        kc = torch.zeros(32, Hkv, Dh, dtype=torch.bfloat16 if dev == "cuda" else torch.float32, device=dev)
+        vc = torch.zeros_like(kc)
+        batch = F.Batch(tokens=pos.to(dev), positions=pos.to(dev), slots=slots.to(dev), cu_q=None, kv_lens=None,
+                        block_table=None, last_idx=None, seq_slots=None, max_q_len=T, max_kv_len=T, is_decode=False,
+                        page_size=16)
+        qo = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=kc, v_cache=vc, rope=spec,
+                              qn=qn.to(dev), kn=kn.to(dev), v_norm=True, q_scale=0.5)
+        outs[dev] = (qo.float().cpu(), kc.float().cpu(), vc.float().cpu())
+    for a, b in zip(outs["cuda"], outs["cpu"]):
+        assert rel_err(a, b) < 6e-3, rel_err(a, b)
+
+
+def _paged(T_total, Hkv, Dh, page_size, lens):
+    """Random cache with a shuffled page table for sequences of the given lengths."""
+    n_pages = sum((l + page_size - 1) // page_size for l in lens) + 3
+    kc = torch.randn(n_pages * page_size, Hkv, Dh, device=DEV).bfloat16()
+    vc = torch.randn(n_pages * page_size, Hkv, Dh, device=DEV).bfloat16()
+    perm = torch.randperm(n_pages).tolist()
+    width = max((l + page_size - 1) // page_size for l in lens)
+    table = torch.zeros(len(lens), width, dtype=torch.int32)
+    for b, l in enumerate(lens):
+        for i in range((l + page_size - 1) // page_size):
+            table[b, i] = perm.pop()
+    return kc, vc, table.to(DEV)
+
+
+def _gather(kc, table, b, L, ps):
+    pages = table[b, :(L + ps - 1) // ps].long()
+    idx = (pages.unsqueeze(1) * ps + torch.arange(ps, device=kc.device)).reshape(-1)[:L]
+    return kc[idx]
+
+
+@pytest.mark.parametrize("Hq,Hkv,Dh", [(8, 2, 128), (4, 4, 64), (16, 2, 256), (2, 1, 64)])
+@pytest.mark.parametrize("window,sinks,softcap", [(0, False, 0.0), (100, True, 0.0), (0, False, 30.0)])
+def test_attn_decode(Hq, Hkv, Dh, window, sinks, softcap):
+    torch.manual_seed(7)
+    ps, lens = 16, [1, 37, 300, 1025]
+    B = len(lens)
+    kc, vc, table = _paged(sum(lens), Hkv, Dh, ps, lens)
+    q = torch.randn(B, Hq, Dh, device=DEV).bfloat16()
+    sk = torch.randn(Hq, device=DEV) if sinks else None
+    kv_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    for splits in (1, 5):
+        got = K().attn_decode(q, kc, vc, table, kv_lens, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh, page_size=ps,
+                              splits=splits, sinks=sk, softcap=softcap, window=window)
+        for b, L in enumerate(lens):
+            want = ref.attention(q[b:b + 1], _gather(kc, table, b, L, ps), _gather(vc, table, b, L, ps),
+                                 torch.tensor([L - 1], device=DEV), scale=Dh ** -0.5, window=window, sinks=sk,
+                                 softcap=softcap)
+            assert rel_err(got[b], want[0]) < 1e-2, (b, splits, rel_err(got[b], want[0]))
+
+
+@pytest.mark.parametrize("Hq,Hkv,Dh", [(4, 2, 128), (2, 2, 64), (4, 1, 256)])
+@pytest.mark.parametrize("window,sinks,softcap", [(0, False, 0.0), (70, True, 0.0), (0, False, 50.0)])
+def test_attn_prefill(Hq, Hkv, Dh, window, sinks, softcap):
+    torch.manual_seed(8)
+    ps = 16
+    qlens, lens = [5, 64, 150, 1], [5, 200, 150, 90]     # (new queries, total cache length)
+    B = len(lens)
+    kc, vc, table = _paged(sum(lens), Hkv, Dh, ps, lens)
+    T = sum(qlens)
+    q = torch.randn(T, Hq, Dh, device=DEV).bfloat16()
+    sk = torch.randn(Hq, device=DEV) if sinks else None
+    cu = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32, device=DEV)
+    kv_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    got = K().attn_prefill(q, kc, vc, table, kv_lens, cu, max(qlens), scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh,
+                           page_size=ps, sinks=sk, softcap=softcap, window=window)
+    o = 0
+    for b, (ql, L) in enumerate(zip(qlens, lens)):
+        qpos = torch.arange(L - ql, L, device=DEV)
+        want = ref.attention(q[o:o + ql], _gather(kc, table, b, L, ps), _gather(vc, table, b, L, ps), qpos,
+                             scale=Dh ** -0.5, window=window, sinks=sk, softcap=softcap)
+        assert rel_err(got[o:o + ql], want) < 1.5e-2, (b, rel_err(got[o:o + ql], want))
+        o += ql
+
+
+@pytest.mark.parametrize("T,N,Kd", [(5, 128, 64), (33, 200, 320), (100, 384, 2560), (300, 1000, 512), (2048, 256, 1024)])
+def test_gemm_bf16_tcgen05(T, N, Kd):
+    torch.manual_seed(9)
+    W = (torch.randn(N, Kd, device=DEV) * 0.05).bfloat16()
+    X = torch.randn(T, Kd, device=DEV).bfloat16()
+    want = X.float() @ W.float().t()
+    got = K().gemm_bf16(W, X, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert int(K().gemm_status(DEV).item()) == 0
+    assert rel_err(got, want) < 1e-3, rel_err(got, want)
+    bias = torch.randn(N, device=DEV)
+    res = torch.randn(T, N, device=DEV).bfloat16()
+    got = K().gemm_bf16(W, X, out_dtype=torch.bfloat16, bias=bias, residual=res)
+    assert rel_err(got, want + bias + res.float()) < 6e-3
+
+
+@pytest.mark.parametrize("act", ["swiglu", "geglu", "swiglu_oai", "relu2", "sigmoid_mul"])
+def test_glu(act):
+    torch.manual_seed(10)
+    T, F = 6, 160
+    y = torch.randn(T, 2 * F, device=DEV)
+    g, u = y[:, :F], y[:, F:]
+    want = ref.glu(act, g, u if act != "relu2" else None)
+    out, yq, yds = K().glu(g, None if act == "relu2" else u, act, F, 2 * F, 2 * F, T, want_q8=True)
+    assert rel_err(out, want) < 5e-3
+    deq = (yq.float().view(T, F // 32, 32) * yds[..., 0:1]).view(T, F)
+    assert rel_err(deq, want) < 1.2e-2
+
+
+def test_argmax():
+    torch.manual_seed(11)
+    x = torch.randn(5, 151936, device=DEV)
+    x[2, 77] = 100.0
+    x[3, 5] = x[3, 9000] = 50.0
+    got = K().argmax(x)
+    assert got.tolist() == x.argmax(-1).tolist()
+    assert got[3].item() == 5
