@@ -38,6 +38,8 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--prefill", type=int, default=2048)
     ap.add_argument("--model", default="qwen3-4b", choices=["qwen3-4b", "qwen3-tiny"])
+    ap.add_argument("--prefill-repeats", type=int, default=3, help="timed prefill repetitions (median reported)")
+    ap.add_argument("--no-graph", action="store_true", help="run decode steps eagerly (for kernel-level profiling)")
     ap.add_argument("--cache-dir", default=os.environ.get("TSB_BENCH_CACHE", os.path.join(tempfile.gettempdir(), "tsb_bench")))
     return ap.parse_args()
 
@@ -169,21 +171,23 @@ def run_ours(args) -> dict:
     for s in seqs:
         model.kv.free_seq(s)
     ttfts = []
-    for _ in range(3):
+    for _ in range(args.prefill_repeats):
         seqs, first, ms = prefill_once()
         ttfts.append(ms)
-        if _ < 2:
+        if _ < args.prefill_repeats - 1:
             for s in seqs:
                 model.kv.free_seq(s)
     ttfts.sort()
     prefill_ms = ttfts[len(ttfts) // 2]
 
     # ---- decode: K timed steps of the whole batch -------------------------------------------
-    dg = DecodeGraph(model, seqs, 2 * (K + W) + 8)
+    dg = DecodeGraph(model, seqs, 2 * (K + W) + 8, use_graph=not args.no_graph)
     dg.set_tokens(first.tolist())
     dg.capture()
+    n0 = kernels.LAUNCHES
     for _ in range(W):
         dg.step()
+    launches_eager = (kernels.LAUNCHES - n0) // max(1, W)
     clocks = ClockSampler(local)
     if rank == 0:
         clocks.start()
@@ -229,7 +233,7 @@ def run_ours(args) -> dict:
         "prefill_tok_s": B * P / (prefill_ms / 1e3), "ttft_ms_p50": prefill_ms,
         "e2e": {"value": B * K / (max(e2e_ms, e2e_wall_ms) / 1e3), "unit": "tok/s", "h2d_bytes_per_step": 4 * B,
                 "d2h_bytes_per_step": 4 * B, "ms_per_step_device": e2e_ms / K, "ms_per_step_wall": e2e_wall_ms / K},
-        "gpu_launches": dg.launches_per_step * K,
+        "gpu_launches": (dg.launches_per_step or launches_eager) * K,
         "kernel_status": status,
         "clocks": clock_info,
     }
