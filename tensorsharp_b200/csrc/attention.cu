@@ -12,6 +12,7 @@
 // cuBLAS QK^T / PV of the non-flash prefill path (ggml-cuda.cu:2084) and the host-built masks
 // of TensorSharp.GGML.Native/ggml_ops_norm_attn.cpp:1699-1884.  Scores are never materialised.
 #include "common.cuh"
+#include "tsb_noalloc.h"
 
 struct AttnArgs {
     const bf16* q;            // [Tq, Hq, Dh]
@@ -223,6 +224,43 @@ extern "C" int tsb_attn_decode(const AttnArgs* args, void* stream) {
     attn_combine_kernel<<<dim3(a.Hq, a.B), (a.Dh + 31) & ~31, 0, s>>>(a);
     TSB_CHECK_LAUNCH();
     return TSB_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free variant (see tsb_noalloc.h): the split-KV partials live in a file-scope
+// device array instead of caller scratch.  In host code the array's name is only a handle
+// for the runtime, not a device address, so its address is fetched once per device with
+// cudaGetSymbolAddress and that pointer is what the kernels receive.
+// ------------------------------------------------------------------------------------------
+static __device__ __align__(256) float g_attn_noalloc_scratch[TSB_ATTN_NOALLOC_MAX_FLOATS];
+
+static float* g_attn_noalloc_ptr[64] = {nullptr};
+
+extern "C" long tsb_attn_decode_noalloc_capacity(void) { return (long)TSB_ATTN_NOALLOC_MAX_FLOATS; }
+
+extern "C" int tsb_attn_decode_noalloc(const AttnArgs* args, void* stream) {
+    TSB_CHECK_ARG(args != nullptr, "attn_decode_noalloc: null arguments");
+    AttnArgs a = *args;
+    TSB_CHECK_ARG(a.B >= 0 && a.Hq > 0 && a.Dh > 0 && a.splits >= 1, "attn_decode_noalloc: bad sizes B=%d Hq=%d Dh=%d splits=%d",
+                  a.B, a.Hq, a.Dh, a.splits);
+    const long slots = (long)a.B * a.Hq * a.splits;
+    const long need = slots * (a.Dh + 2);
+    TSB_CHECK_ARG(need <= (long)TSB_ATTN_NOALLOC_MAX_FLOATS,
+                  "attn_decode_noalloc: B*Hq*splits*(Dh+2) = %ld floats exceeds the built-in scratch of %ld floats; "
+                  "use fewer splits or a smaller batch", need, (long)TSB_ATTN_NOALLOC_MAX_FLOATS);
+    int dev = -1;
+    TSB_CHECK_CUDA(cudaGetDevice(&dev));
+    TSB_CHECK_ARG(dev >= 0 && dev < 64, "attn_decode_noalloc: device ordinal %d out of range", dev);
+    if (g_attn_noalloc_ptr[dev] == nullptr) {
+        // one-time set-up for this device (current device == dev): resolve the device address
+        float* p = nullptr;
+        TSB_CHECK_CUDA(cudaGetSymbolAddress((void**)&p, g_attn_noalloc_scratch));
+        g_attn_noalloc_ptr[dev] = p;
+    }
+    float* base = g_attn_noalloc_ptr[dev];
+    a.part_o = base;                       // [B, Hq, splits, Dh]
+    a.part_ml = base + slots * a.Dh;       // [B, Hq, splits, 2]
+    return tsb_attn_decode(&a, stream);
 }
 
 // ------------------------------------------------------------------------------------------
