@@ -30,6 +30,8 @@ def file_type(name: str, layer: int, n_layers: int, scheme: str) -> GGMLType:
     scheme = scheme.upper()
     if scheme in ("F16", "BF16", "F32", "Q8_0", "Q4_0", "Q4_K", "Q5_K", "Q6_K", "MXFP4"):
         return GGMLType[scheme]
+    if scheme == "Q4_K_UNIFORM":     # one type per matrix class (what the reference's fused decode needs)
+        return GGMLType.Q6_K if name in ("output.weight", "token_embd.weight") else GGMLType.Q4_K
     if scheme == "Q4_K_M":
         if name in ("output.weight", "token_embd.weight"):
             return GGMLType.Q6_K
