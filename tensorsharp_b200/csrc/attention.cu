@@ -43,6 +43,8 @@ __device__ __forceinline__ long kv_slot(const AttnArgs& a, int b, int j) {
 template <int DH, int G>
 __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
     constexpr int DPL = DH / 32;             // output dims per lane
+    pdl_wait();
+    pdl_trigger();
     const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int len = a.kv_lens[b];
@@ -114,34 +116,46 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
 #pragma unroll
             for (int d = 0; d < DPL; ++d) acc[g][d] *= corr;
         }
+        // P V: eight value rows are fetched before any of them is used, so the loads overlap
         const int cnt = min(32, s1 - base);
-        for (int t = 0; t < cnt; ++t) {
-            const long sl = __shfl_sync(0xffffffffu, slot, t);
-            const bf16* vp = a.v_cache + (sl * a.Hkv + hk) * DH + lane * DPL;
-            float vf[DPL];
-            if (DPL == 4) {
-                const uint2 vv = *reinterpret_cast<const uint2*>(vp);
-                const bf162* v2 = reinterpret_cast<const bf162*>(&vv);
-                const float2 f0 = __bfloat1622float2(v2[0]), f1 = __bfloat1622float2(v2[1]);
-                vf[0] = f0.x; vf[1] = f0.y; vf[2 % DPL] = f1.x; vf[3 % DPL] = f1.y;
-            } else if (DPL == 8) {
-                const uint4 vv = *reinterpret_cast<const uint4*>(vp);
-                const bf162* v2 = reinterpret_cast<const bf162*>(&vv);
+        for (int t0 = 0; t0 < cnt; t0 += 8) {
+            float vf[8][DPL];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 f = __bfloat1622float2(v2[i]);
-                    vf[(2 * i) % DPL] = f.x;
-                    vf[(2 * i + 1) % DPL] = f.y;
+            for (int u = 0; u < 8; ++u) {
+                const long sl = __shfl_sync(0xffffffffu, slot, (t0 + u) & 31);
+                const bf16* vp = a.v_cache + (sl * a.Hkv + hk) * DH + lane * DPL;
+                if (t0 + u < cnt) {
+                    if (DPL == 4) {
+                        const uint2 vv = *reinterpret_cast<const uint2*>(vp);
+                        const bf162* v2 = reinterpret_cast<const bf162*>(&vv);
+                        const float2 f0 = __bfloat1622float2(v2[0]), f1 = __bfloat1622float2(v2[1]);
+                        vf[u][0] = f0.x; vf[u][1 % DPL] = f0.y; vf[u][2 % DPL] = f1.x; vf[u][3 % DPL] = f1.y;
+                    } else if (DPL == 8) {
+                        const uint4 vv = *reinterpret_cast<const uint4*>(vp);
+                        const bf162* v2 = reinterpret_cast<const bf162*>(&vv);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float2 f = __bfloat1622float2(v2[i]);
+                            vf[u][(2 * i) % DPL] = f.x;
+                            vf[u][(2 * i + 1) % DPL] = f.y;
+                        }
+                    } else {
+#pragma unroll
+                        for (int d = 0; d < DPL; ++d) vf[u][d] = bf2f(vp[d]);
+                    }
+                } else {
+#pragma unroll
+                    for (int d = 0; d < DPL; ++d) vf[u][d] = 0.f;
                 }
-            } else {
-#pragma unroll
-                for (int d = 0; d < DPL; ++d) vf[d] = bf2f(vp[d]);
             }
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float pg = __shfl_sync(0xffffffffu, p[g], t);
+            for (int u = 0; u < 8; ++u) {
 #pragma unroll
-                for (int d = 0; d < DPL; ++d) acc[g][d] += pg * vf[d];
+                for (int g = 0; g < G; ++g) {
+                    const float pg = __shfl_sync(0xffffffffu, p[g], (t0 + u) & 31);
+#pragma unroll
+                    for (int d = 0; d < DPL; ++d) acc[g][d] += pg * vf[u][d];
+                }
             }
         }
     }
@@ -173,6 +187,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
 
 // grid (Hq, B), DH threads (rounded up to 32): merge split partials, apply the sink, normalise.
 __global__ void attn_combine_kernel(AttnArgs a) {
+    pdl_wait();
+    pdl_trigger();
     const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
     const long base = ((long)b * a.Hq + h) * a.splits;
     float mm = a.sinks ? a.sinks[h] : -INFINITY;
@@ -192,10 +208,10 @@ static int launch_decode_g(const AttnArgs& a, cudaStream_t s) {
     dim3 grid(a.splits, a.Hkv, a.B);
     const int G = a.Hq / a.Hkv;
     switch (G) {
-    case 1: attn_decode_kernel<DH, 1><<<grid, 128, 0, s>>>(a); break;
-    case 2: attn_decode_kernel<DH, 2><<<grid, 128, 0, s>>>(a); break;
-    case 4: attn_decode_kernel<DH, 4><<<grid, 128, 0, s>>>(a); break;
-    case 8: attn_decode_kernel<DH, 8><<<grid, 128, 0, s>>>(a); break;
+    case 1: if (tsb_launch(attn_decode_kernel<DH, 1>, grid, dim3(128), 0, s, a) != cudaSuccess) return TSB_ERR_CUDA; break;
+    case 2: if (tsb_launch(attn_decode_kernel<DH, 2>, grid, dim3(128), 0, s, a) != cudaSuccess) return TSB_ERR_CUDA; break;
+    case 4: if (tsb_launch(attn_decode_kernel<DH, 4>, grid, dim3(128), 0, s, a) != cudaSuccess) return TSB_ERR_CUDA; break;
+    case 8: if (tsb_launch(attn_decode_kernel<DH, 8>, grid, dim3(128), 0, s, a) != cudaSuccess) return TSB_ERR_CUDA; break;
     default:
         tsb_set_error("attn_decode: unsupported GQA group size %d (supported 1, 2, 4, 8)", G);
         return TSB_ERR_UNSUPPORTED;
@@ -221,7 +237,7 @@ extern "C" int tsb_attn_decode(const AttnArgs* args, void* stream) {
     }
     if (rc != TSB_OK) return rc;
     TSB_CHECK_LAUNCH();
-    attn_combine_kernel<<<dim3(a.Hq, a.B), (a.Dh + 31) & ~31, 0, s>>>(a);
+    TSB_CHECK_CUDA(tsb_launch(attn_combine_kernel, dim3(a.Hq, a.B), dim3((a.Dh + 31) & ~31), 0, s, a));
     TSB_CHECK_LAUNCH();
     return TSB_OK;
 }
@@ -304,6 +320,8 @@ __device__ __forceinline__ bf16* tile_ptr(bf16* base, int r, int c) {
 template <int DH>
 __global__ void __launch_bounds__(128) attn_prefill_kernel(AttnArgs a) {
     constexpr int BM = 64, BN = 64, CH = DH / 8;   // CH = 16-byte chunks per row
+    pdl_wait();
+    pdl_trigger();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
     bf16* sK = sQ + BM * DH;         // 2 stages
@@ -491,7 +509,7 @@ static int launch_prefill(const AttnArgs& a, int max_q, cudaStream_t s) {
         configured = true;
     }
     dim3 grid((max_q + 63) / 64, a.Hq, a.B);
-    attn_prefill_kernel<DH><<<grid, 128, smem, s>>>(a);
+    TSB_CHECK_CUDA(tsb_launch(attn_prefill_kernel<DH>, grid, dim3(128), smem, s, a));
     TSB_CHECK_LAUNCH();
     return TSB_OK;
 }

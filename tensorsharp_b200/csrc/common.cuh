@@ -55,7 +55,37 @@ enum TsbGgmlType {
 };
 
 #ifdef __CUDACC__
+#include <utility>
 typedef __nv_bfloat16 bf16;
+
+// Programmatic dependent launch: every kernel of this library is launched with the
+// programmatic-serialisation attribute, calls pdl_wait() before its first global access (it
+// returns once every earlier kernel in the stream has completed and flushed) and
+// pdl_trigger() right after, which lets the next kernel's blocks be scheduled and run up to
+// their own pdl_wait() while this one is still executing.  This hides the launch latency
+// between the several hundred small kernels of a decode step.  Both are no-ops for a kernel
+// launched without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool tsb_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t tsb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                     Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tsb_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 typedef __nv_bfloat162 bf162;
 
 __device__ __forceinline__ float warp_sum(float v) {

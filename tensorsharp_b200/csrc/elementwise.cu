@@ -21,6 +21,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(TX* x, const bf16* delta, 
                                                       int D, bf16* y_bf16, float* y_f32, const float* add,
                                                       int8_t* yq, float2* yds, int l2_mode) {
     __shared__ float red[32];
+    pdl_wait();
+    pdl_trigger();
     const long row = blockIdx.x;
     TX* xr = x + row * D;
     float ss = 0.f;
@@ -57,6 +59,120 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(TX* x, const bf16* delta, 
     }
 }
 
+// Vectorised variant (D % 4 == 0): each thread keeps up to VMAX float4 chunks of the row in
+// registers, so every global load is issued before the first reduction and the row is read
+// exactly once.  A q8 group of 32 values is 8 neighbouring lanes.
+template <typename TX, int VMAX>
+__global__ void __launch_bounds__(1024) rmsnorm_vec_kernel(TX* x, const bf16* delta, const float* w, float eps, int D,
+                                                           bf16* y_bf16, float* y_f32, const float* add, int8_t* yq,
+                                                           float2* yds, int l2_mode) {
+    __shared__ float red[32];
+    const long row = blockIdx.x;
+    const int nvec = D >> 2, tid = threadIdx.x, nt = blockDim.x;
+    float4 wv[VMAX];
+#pragma unroll
+    for (int j = 0; j < VMAX; ++j) {          // weights do not depend on the previous kernel
+        const int i = tid + j * nt;
+        wv[j] = (w && i < nvec) ? reinterpret_cast<const float4*>(w)[i] : make_float4(1.f, 1.f, 1.f, 1.f);
+    }
+    pdl_wait();
+    pdl_trigger();
+    float4 v[VMAX];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < VMAX; ++j) {
+        const int i = tid + j * nt;
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < nvec) {
+            if (sizeof(TX) == 4) {
+                t = reinterpret_cast<const float4*>(x + row * D)[i];
+            } else {
+                const uint2 r = reinterpret_cast<const uint2*>(x + row * D)[i];
+                const float2 a = __bfloat1622float2(*reinterpret_cast<const bf162*>(&r.x));
+                const float2 b = __bfloat1622float2(*reinterpret_cast<const bf162*>(&r.y));
+                t = make_float4(a.x, a.y, b.x, b.y);
+            }
+            if (delta) {
+                const uint2 r = reinterpret_cast<const uint2*>(delta + row * D)[i];
+                const float2 a = __bfloat1622float2(*reinterpret_cast<const bf162*>(&r.x));
+                const float2 b = __bfloat1622float2(*reinterpret_cast<const bf162*>(&r.y));
+                t.x += a.x; t.y += a.y; t.z += b.x; t.w += b.y;
+                if (sizeof(TX) == 4) {
+                    reinterpret_cast<float4*>(x + row * D)[i] = t;
+                } else {
+                    uint2 o;
+                    *reinterpret_cast<bf162*>(&o.x) = __floats2bfloat162_rn(t.x, t.y);
+                    *reinterpret_cast<bf162*>(&o.y) = __floats2bfloat162_rn(t.z, t.w);
+                    reinterpret_cast<uint2*>(x + row * D)[i] = o;
+                }
+            }
+        }
+        v[j] = t;
+        ss += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;
+    }
+    ss = block_sum(ss, red);
+    const float rs = l2_mode ? 1.f / fmaxf(sqrtf(ss), eps) : rsqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int j = 0; j < VMAX; ++j) {
+        const int i = tid + j * nt;
+        const bool ok = i < nvec;
+        float4 n = make_float4(v[j].x * rs * wv[j].x, v[j].y * rs * wv[j].y, v[j].z * rs * wv[j].z, v[j].w * rs * wv[j].w);
+        if (ok) {
+            if (y_bf16) {
+                uint2 o;
+                *reinterpret_cast<bf162*>(&o.x) = __floats2bfloat162_rn(n.x, n.y);
+                *reinterpret_cast<bf162*>(&o.y) = __floats2bfloat162_rn(n.z, n.w);
+                reinterpret_cast<uint2*>(y_bf16 + row * D)[i] = o;
+            }
+            if (y_f32) {
+                float4 o = n;
+                if (add) {
+                    const float4 ad = reinterpret_cast<const float4*>(add + row * D)[i];
+                    o.x += ad.x; o.y += ad.y; o.z += ad.z; o.w += ad.w;
+                }
+                reinterpret_cast<float4*>(y_f32 + row * D)[i] = o;
+            }
+        }
+        if (yq) {
+            float amax = fmaxf(fmaxf(fabsf(n.x), fabsf(n.y)), fmaxf(fabsf(n.z), fabsf(n.w)));
+            float sum = n.x + n.y + n.z + n.w;
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) {
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            }
+            if (ok) {
+                const float inv = amax > 0.f ? 127.f / amax : 0.f;
+                char4 q;
+                q.x = (signed char)__float2int_rn(n.x * inv);
+                q.y = (signed char)__float2int_rn(n.y * inv);
+                q.z = (signed char)__float2int_rn(n.z * inv);
+                q.w = (signed char)__float2int_rn(n.w * inv);
+                reinterpret_cast<char4*>(yq + row * D)[i] = q;
+                if ((i & 7) == 0) yds[row * (D / 32) + (i >> 3)] = make_float2(amax / 127.f, sum);
+            }
+        }
+    }
+}
+
+template <typename TX>
+static cudaError_t launch_rmsnorm(TX* x, const bf16* delta, const float* w, float eps, long rows, int D, bf16* yb,
+                                  float* yf, const float* add, int8_t* yq, float2* yds, int l2, cudaStream_t s) {
+    if (D % 4 == 0 && D <= 16384) {
+        const int nvec = D / 4;
+        if (nvec <= 1024) {
+            const int nt = (nvec + 31) & ~31;
+            return tsb_launch(rmsnorm_vec_kernel<TX, 1>, dim3((unsigned)rows), dim3(nt), 0, s, x, delta, w, eps, D, yb,
+                              yf, add, yq, yds, l2);
+        }
+        const int nt = (((nvec + 3) / 4) + 31) & ~31;
+        return tsb_launch(rmsnorm_vec_kernel<TX, 4>, dim3((unsigned)rows), dim3(nt), 0, s, x, delta, w, eps, D, yb, yf,
+                          add, yq, yds, l2);
+    }
+    return tsb_launch(rmsnorm_kernel<TX>, dim3((unsigned)rows), dim3(256), 0, s, x, delta, w, eps, D, yb, yf, add, yq,
+                      yds, l2);
+}
+
 extern "C" int tsb_rmsnorm(void* x, int x_f32, const void* delta, const float* w, float eps, long rows, int D,
                            void* y_bf16, float* y_f32, const float* add, void* yq, void* yds, int l2_mode,
                            void* stream) {
@@ -65,12 +181,11 @@ extern "C" int tsb_rmsnorm(void* x, int x_f32, const void* delta, const float* w
     if (rows == 0) return TSB_OK;
     cudaStream_t s = (cudaStream_t)stream;
     if (x_f32)
-        rmsnorm_kernel<float><<<(unsigned)rows, 256, 0, s>>>((float*)x, (const bf16*)delta, w, eps, D, (bf16*)y_bf16,
-                                                             y_f32, add, (int8_t*)yq, (float2*)yds, l2_mode);
+        TSB_CHECK_CUDA(launch_rmsnorm<float>((float*)x, (const bf16*)delta, w, eps, rows, D, (bf16*)y_bf16, y_f32, add,
+                                             (int8_t*)yq, (float2*)yds, l2_mode, s));
     else
-        rmsnorm_kernel<bf16><<<(unsigned)rows, 256, 0, s>>>((bf16*)x, (const bf16*)delta, w, eps, D, (bf16*)y_bf16,
-                                                            y_f32, add, (int8_t*)yq, (float2*)yds, l2_mode);
-    TSB_CHECK_LAUNCH();
+        TSB_CHECK_CUDA(launch_rmsnorm<bf16>((bf16*)x, (const bf16*)delta, w, eps, rows, D, (bf16*)y_bf16, y_f32, add,
+                                            (int8_t*)yq, (float2*)yds, l2_mode, s));
     return TSB_OK;
 }
 
@@ -98,6 +213,7 @@ struct QkvArgs {
     const int* pos;                     // [T]
     const long* slot;                   // [T] flat slot in the KV cache (page * page_size + offset), <0 = skip
     const float* freq_factors;          // [rot_dim/2] or null
+    const float2* cs_table;             // [T, rot_dim/2] (cos, sin) precomputed per token, or null
     bf16* q_out;                        // [T, Hq, Dh]
     bf16* k_cache; bf16* v_cache;       // [slots, Hkv, Dh]
     float q_scale;                      // multiplied into q after RoPE (1 = none)
@@ -121,7 +237,41 @@ __device__ __forceinline__ void rope_cs(const RopeParams& rp, const float* ff, i
     s *= ms;
 }
 
+// (cos, sin) of every (token, pair): computed once per forward and shared by all layers and heads.
+__global__ void rope_table_kernel(const int* pos, RopeParams rp, const float* ff, float2* out, int T) {
+    pdl_wait();
+    pdl_trigger();
+    const int half = rp.rot_dim >> 1;
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long)T * half) return;
+    const int t = (int)(i / half), pair = (int)(i % half);
+    float c, s;
+    rope_cs(rp, ff, pair, (float)pos[t], c, s);
+    out[i] = make_float2(c, s);
+}
+
+extern "C" int tsb_rope_table(const int* pos, const RopeParams* rp, const float* ff, void* out, int T, void* stream) {
+    TSB_CHECK_ARG(rp->rot_dim > 0 && rp->rot_dim % 2 == 0, "rope_table: bad rot_dim %d", rp->rot_dim);
+    const long n = (long)T * (rp->rot_dim / 2);
+    if (n == 0) return TSB_OK;
+    TSB_CHECK_CUDA(tsb_launch(rope_table_kernel, dim3((unsigned)((n + 127) / 128)), dim3(128), 0, (cudaStream_t)stream, pos,
+                              *rp, ff, (float2*)out, T));
+    return TSB_OK;
+}
+
+__device__ __forceinline__ void rope_lookup(const QkvArgs& a, int t, int pair, float pos, float& c, float& s) {
+    if (a.cs_table) {
+        const float2 cs = a.cs_table[(long)t * (a.rp.rot_dim >> 1) + pair];
+        c = cs.x;
+        s = cs.y;
+    } else {
+        rope_cs(a.rp, a.freq_factors, pair, pos, c, s);
+    }
+}
+
 __global__ void __launch_bounds__(128) qkv_rope_kernel(QkvArgs a) {
+    pdl_wait();
+    pdl_trigger();
     const int lane = threadIdx.x & 31;
     const long wid = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
     const int H = a.Hq + 2 * a.Hkv;
@@ -193,7 +343,7 @@ __global__ void __launch_bounds__(128) qkv_rope_kernel(QkvArgs a) {
             if (e < rot) {
                 const int pair = e < half ? e : e - half;
                 float c, s;
-                rope_cs(a.rp, a.freq_factors, pair, pos, c, s);
+                rope_lookup(a, t, pair, pos, c, s);
                 const float x0 = st[pair], x1 = st[pair + half];
                 o = e < half ? x0 * c - x1 * s : x0 * s + x1 * c;
             }
@@ -209,7 +359,7 @@ __global__ void __launch_bounds__(128) qkv_rope_kernel(QkvArgs a) {
             float o = v[j];
             if (e < rot) {
                 float c, s;
-                rope_cs(a.rp, a.freq_factors, e >> 1, pos, c, s);
+                rope_lookup(a, t, e >> 1, pos, c, s);
                 o = (e & 1) ? other * s + v[j] * c : v[j] * c - other * s;
             }
             dst[e] = f2bf(o * qs);
@@ -223,8 +373,7 @@ extern "C" int tsb_qkv_rope(const QkvArgs* args, void* stream) {
     TSB_CHECK_ARG(a.rp.rot_dim <= a.Dh && a.rp.rot_dim % 2 == 0, "qkv_rope: bad rot_dim %d", a.rp.rot_dim);
     const long warps = (long)a.T * (a.Hq + 2 * a.Hkv);
     if (warps == 0) return TSB_OK;
-    qkv_rope_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, (cudaStream_t)stream>>>(a);
-    TSB_CHECK_LAUNCH();
+    TSB_CHECK_CUDA(tsb_launch(qkv_rope_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, (cudaStream_t)stream, a));
     return TSB_OK;
 }
 
@@ -253,6 +402,8 @@ __device__ __forceinline__ float glu_apply(int act, float g, float u) {
 template <typename T>
 __global__ void glu_kernel(const T* gate, const T* up, long g_stride, long u_stride, int F, int act, bf16* out,
                            int8_t* yq, float2* yds, long rows) {
+    pdl_wait();
+    pdl_trigger();
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     const int fpad = (F + 31) & ~31;
     const long total = rows * fpad;
@@ -283,11 +434,11 @@ extern "C" int tsb_glu(const void* gate, const void* up, int in_f32, long g_stri
     dim3 grid((unsigned)((total + 255) / 256));
     cudaStream_t s = (cudaStream_t)stream;
     if (in_f32)
-        glu_kernel<float><<<grid, 256, 0, s>>>((const float*)gate, (const float*)up, g_stride, u_stride, F, act,
-                                               (bf16*)out, (int8_t*)yq, (float2*)yds, rows);
+        TSB_CHECK_CUDA(tsb_launch(glu_kernel<float>, grid, dim3(256), 0, s, (const float*)gate, (const float*)up, g_stride,
+                                  u_stride, F, act, (bf16*)out, (int8_t*)yq, (float2*)yds, rows));
     else
-        glu_kernel<bf16><<<grid, 256, 0, s>>>((const bf16*)gate, (const bf16*)up, g_stride, u_stride, F, act,
-                                              (bf16*)out, (int8_t*)yq, (float2*)yds, rows);
+        TSB_CHECK_CUDA(tsb_launch(glu_kernel<bf16>, grid, dim3(256), 0, s, (const bf16*)gate, (const bf16*)up, g_stride,
+                                  u_stride, F, act, (bf16*)out, (int8_t*)yq, (float2*)yds, rows));
     TSB_CHECK_LAUNCH();
     return TSB_OK;
 }
@@ -298,6 +449,8 @@ extern "C" int tsb_glu(const void* gate, const void* up, int in_f32, long g_stri
 // ------------------------------------------------------------------------------------------
 template <typename TO>
 __global__ void gather_rows_kernel(QW w, const int* ids, long n_rows, float scale, TO* out) {
+    pdl_wait();
+    pdl_trigger();
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     const int k8n = w.K >> 3;
     if (idx >= n_rows * k8n) return;
@@ -327,9 +480,9 @@ extern "C" int tsb_gather_rows(const void* p0, const void* p1, const void* p2, c
     const long total = n_rows * (K / 8);
     dim3 grid((unsigned)((total + 255) / 256));
     if (out_f32)
-        gather_rows_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>(w, ids, n_rows, scale, (float*)out);
+        TSB_CHECK_CUDA(tsb_launch(gather_rows_kernel<float>, grid, dim3(256), 0, (cudaStream_t)stream, w, ids, n_rows, scale, (float*)out));
     else
-        gather_rows_kernel<bf16><<<grid, 256, 0, (cudaStream_t)stream>>>(w, ids, n_rows, scale, (bf16*)out);
+        TSB_CHECK_CUDA(tsb_launch(gather_rows_kernel<bf16>, grid, dim3(256), 0, (cudaStream_t)stream, w, ids, n_rows, scale, (bf16*)out));
     TSB_CHECK_LAUNCH();
     return TSB_OK;
 }
@@ -342,6 +495,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* logits, long 
                                                       float* out_val) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    pdl_wait();
+    pdl_trigger();
     const float* row = logits + blockIdx.x * stride;
     float best = -INFINITY;
     int bi = 0x7fffffff;
@@ -379,7 +534,7 @@ extern "C" int tsb_argmax(const float* logits, long stride, long rows, int V, in
                           void* stream) {
     if (rows == 0) return TSB_OK;
     TSB_CHECK_ARG(V > 0, "argmax: empty vocabulary");
-    argmax_kernel<<<(unsigned)rows, 1024, 0, (cudaStream_t)stream>>>(logits, stride, V, out_idx, out_val);
+    TSB_CHECK_CUDA(tsb_launch(argmax_kernel, dim3((unsigned)rows), dim3(1024), 0, (cudaStream_t)stream, logits, stride, V, out_idx, out_val));
     TSB_CHECK_LAUNCH();
     return TSB_OK;
 }
@@ -391,6 +546,8 @@ extern "C" int tsb_argmax(const float* logits, long stride, long rows, int V, in
 // ------------------------------------------------------------------------------------------
 __global__ void decode_advance_kernel(const int* sampled, int* tokens, int* positions, int* kv_lens, long* slots,
                                       const int* block_table, int max_pages, int page_size, int B) {
+    pdl_wait();
+    pdl_trigger();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= B) return;
     tokens[b] = sampled[b];
@@ -405,8 +562,8 @@ __global__ void decode_advance_kernel(const int* sampled, int* tokens, int* posi
 extern "C" int tsb_decode_advance(const int* sampled, int* tokens, int* positions, int* kv_lens, long* slots,
                                   const int* block_table, int max_pages, int page_size, int B, void* stream) {
     if (B == 0) return TSB_OK;
-    decode_advance_kernel<<<(B + 127) / 128, 128, 0, (cudaStream_t)stream>>>(sampled, tokens, positions, kv_lens, slots,
-                                                                            block_table, max_pages, page_size, B);
+    TSB_CHECK_CUDA(tsb_launch(decode_advance_kernel, dim3((B + 127) / 128), dim3(128), 0, (cudaStream_t)stream, sampled,
+                              tokens, positions, kv_lens, slots, block_table, max_pages, page_size, B));
     TSB_CHECK_LAUNCH();
     return TSB_OK;
 }

@@ -69,6 +69,8 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();        // barrier set-up and the TMEM allocation above overlap the previous kernel's tail
+    pdl_trigger();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -193,8 +195,7 @@ static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmE
         configured = true;
     }
     dim3 grid((ep.N + 127) / 128, (ep.T + BN - 1) / BN);
-    gemm_bf16_kernel<BN, STAGES><<<grid, 192, L::TOTAL, s>>>(tw, tx, ep, K, status);
-    TSB_CHECK_LAUNCH();
+    TSB_CHECK_CUDA(tsb_launch(gemm_bf16_kernel<BN, STAGES>, grid, dim3(192), (size_t)L::TOTAL, s, tw, tx, ep, K, status));
     return TSB_OK;
 }
 

@@ -13,7 +13,7 @@ Data conventions
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Optional, Tuple
 
 import torch
@@ -67,6 +67,7 @@ class Batch:
     # host copies for the CPU path and for planning
     h_cu_q: Tuple[int, ...] = ()
     h_kv_lens: Tuple[int, ...] = ()
+    cache: dict = field(default_factory=dict)   # per-forward memo (RoPE tables); cleared by the step runner
 
     @property
     def B(self) -> int:
@@ -208,13 +209,21 @@ def qkv_rope_cache(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, Hq: int
             rp.rot_dim, rp.mode = rope.rot_dim, rope.mode
         else:
             rp.rot_dim, rp.mode, rp.theta_base, rp.freq_scale, rp.attn_factor = 0, 0, 10000.0, 1.0, 1.0
+        table = None
+        if rope is not None and rope.rot_dim > 0:
+            key = ("rope", id(rope))
+            table = batch.cache.get(key)
+            if table is None:
+                table = kk.rope_table(batch.positions, rp, rope.freq_factors)
+                batch.cache[key] = table
         q_out = torch.empty((T, Hq, Dh), dtype=torch.bfloat16, device=q.device)
         assert q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1 and q.dtype == k.dtype == v.dtype
         kk.qkv_rope(q=q, k=k, v=v, q_strides=(q.stride(0), q.stride(1)), k_strides=(k.stride(0), k.stride(1)),
                     v_strides=(v.stride(0), v.stride(1)), Hq=Hq, Hkv=Hkv if write_kv else 0, Dh=Dh,
                     pos=batch.positions, slot=batch.slots,
                     q_out=q_out, k_cache=k_cache, v_cache=v_cache, qn=qn, kn=kn, v_norm=v_norm, eps=eps, rope=rp,
-                    freq_factors=rope.freq_factors if rope is not None else None, q_scale=q_scale)
+                    freq_factors=rope.freq_factors if rope is not None else None, q_scale=q_scale,
+                    cs_table=table)
         return q_out
     qf, kf, vf = q.float(), k.float(), v.float()
     if qn is not None:

@@ -48,7 +48,7 @@ class QkvArgs(C.Structure):
                 ("q_tok", C.c_long), ("q_head", C.c_long), ("k_tok", C.c_long), ("k_head", C.c_long),
                 ("v_tok", C.c_long), ("v_head", C.c_long),
                 ("in_f32", C.c_int), ("qn", _vp), ("kn", _vp), ("v_norm", C.c_int), ("eps", C.c_float),
-                ("pos", _vp), ("slot", _vp), ("freq_factors", _vp), ("q_out", _vp), ("k_cache", _vp),
+                ("pos", _vp), ("slot", _vp), ("freq_factors", _vp), ("cs_table", _vp), ("q_out", _vp), ("k_cache", _vp),
                 ("v_cache", _vp), ("q_scale", C.c_float),
                 ("T", C.c_int), ("Hq", C.c_int), ("Hkv", C.c_int), ("Dh", C.c_int), ("rp", RopeParams)]
 
@@ -75,7 +75,7 @@ def _lib():
     lib = native.lib()
     if not _configured:
         for name in ("tsb_quantize_q8", "tsb_gemv", "tsb_rmsnorm", "tsb_qkv_rope", "tsb_glu", "tsb_gather_rows",
-                     "tsb_argmax", "tsb_decode_advance", "tsb_attn_decode", "tsb_attn_prefill", "tsb_gemm_bf16"):
+                     "tsb_argmax", "tsb_rope_table", "tsb_decode_advance", "tsb_attn_decode", "tsb_attn_prefill", "tsb_gemm_bf16"):
             getattr(lib, name).restype = C.c_int
         _configured = True
     return lib
@@ -145,7 +145,8 @@ def yarn_corr_dims(n_dims: int, n_ctx_orig: int, freq_base: float, beta_fast: fl
 
 
 def qkv_rope(*, q, k, v, q_strides, k_strides, v_strides, Hq, Hkv, Dh, pos, slot, q_out, k_cache, v_cache,
-             qn=None, kn=None, v_norm=False, eps=1e-6, rope: RopeParams, freq_factors=None, q_scale=1.0):
+             qn=None, kn=None, v_norm=False, eps=1e-6, rope: RopeParams, freq_factors=None, q_scale=1.0,
+             cs_table=None):
     T = int(pos.numel())
     a = QkvArgs()
     a.q, a.k, a.v = _p(q), _p(k), _p(v)
@@ -157,12 +158,23 @@ def qkv_rope(*, q, k, v, q_strides, k_strides, v_strides, Hq, Hkv, Dh, pos, slot
     a.v_norm = int(v_norm)
     a.eps = eps
     a.pos, a.slot, a.freq_factors = _p(pos), _p(slot), _p(freq_factors)
+    a.cs_table = _p(cs_table)
     a.q_out, a.k_cache, a.v_cache = _p(q_out), _p(k_cache), _p(v_cache)
     a.q_scale = q_scale
     a.T, a.Hq, a.Hkv, a.Dh = T, Hq, Hkv, Dh
     a.rp = rope
     native.check(_lib().tsb_qkv_rope(C.byref(a), _stream()), "qkv_rope")
     _count(1)
+
+
+def rope_table(pos: torch.Tensor, rope: RopeParams, freq_factors=None) -> torch.Tensor:
+    """(cos, sin) for every (token, rotary pair): float32 [T, rot_dim / 2, 2]."""
+    T = int(pos.numel())
+    out = torch.empty((T, rope.rot_dim // 2, 2), dtype=torch.float32, device=pos.device)
+    native.check(_lib().tsb_rope_table(_p(pos), C.byref(rope), _p(freq_factors), _p(out), C.c_int(T), _stream()),
+                 "rope_table")
+    _count(1)
+    return out
 
 
 def glu(gate: torch.Tensor, up: Optional[torch.Tensor], act: str, F: int, g_stride: int, u_stride: int, rows: int,

@@ -70,6 +70,7 @@ class DecodeGraph:
         self.batch.slots.copy_(torch.tensor(slots, dtype=torch.int64))
 
     def _step_body(self) -> None:
+        self.batch.cache.clear()
         logits = self.model.forward_batch(self.batch, True)
         self.sampled.copy_(F.argmax(logits))
         if self.model.device.type == "cuda":
