@@ -13,8 +13,10 @@ from typing import Optional
 
 import torch
 
+from ..gguf.constants import block_size
 from ..ops import functional as F
 from ..ops.functional import Batch, RopeSpec
+from ..parallel.dist import block_split, even_split, head_split
 from ..quant.qweight import QuantWeight
 from .base import ModelBase, register_architecture
 
@@ -23,20 +25,36 @@ from .base import ModelBase, register_architecture
 class Qwen3Model(ModelBase):
     def load_weights(self) -> None:
         c = self.cfg
+        tp, r = self.tp_size, self.tp_rank
+        Dh = c.head_dim
+        # tensor parallelism: heads are dealt to ranks (column-parallel QKV, row-parallel o_proj),
+        # the FFN width is dealt in units of ffn_down's quant block (column-parallel gate / up,
+        # row-parallel down), the vocabulary is dealt evenly for the lm_head
+        (q0, q1), (k0, k1) = head_split(c.n_heads, c.n_kv_heads, tp, r)
+        self.Hq, self.Hkv = q1 - q0, k1 - k0
         self.tok_emb = self.qw("token_embd.weight")
         self.out_norm = self.f32("output_norm.weight")
         self.lm_head = self.qw("output.weight", optional=True) or self.tok_emb
+        self.vocab_sharded = tp > 1 and c.vocab % tp == 0
+        if self.vocab_sharded:
+            v0, v1 = even_split(c.vocab, tp, r)
+            self.lm_head = self.lm_head.row_slice(v0, v1)
         self.layers = []
         for l in range(c.n_layers):
             p = f"blk.{l}."
             q, k, v = self.qw(p + "attn_q.weight"), self.qw(p + "attn_k.weight"), self.qw(p + "attn_v.weight")
+            wo, down = self.qw(p + "attn_output.weight"), self.qw(p + "ffn_down.weight")
+            f0, f1 = block_split(c.ffn, block_size(down.ggml_type), tp, r)
+            if tp > 1:
+                q, k, v = q.row_slice(q0 * Dh, q1 * Dh), k.row_slice(k0 * Dh, k1 * Dh), v.row_slice(k0 * Dh, k1 * Dh)
+                wo, down = wo.col_slice(q0 * Dh, q1 * Dh), down.col_slice(f0, f1)
             L = {
                 "attn_norm": self.f32(p + "attn_norm.weight"),
                 "q_norm": self.f32(p + "attn_q_norm.weight", optional=True),
                 "k_norm": self.f32(p + "attn_k_norm.weight", optional=True),
-                "wo": self.qw(p + "attn_output.weight"),
+                "wo": wo,
                 "ffn_norm": self.f32(p + "ffn_norm.weight"),
-                "down": self.qw(p + "ffn_down.weight"),
+                "down": down,
             }
             # fused QKV needs one ggml type for the three matrices (Qwen3Model.cs:67-78)
             if q.ggml_type == k.ggml_type == v.ggml_type:
@@ -44,14 +62,17 @@ class Qwen3Model(ModelBase):
             else:
                 L["wq"], L["wk"], L["wv"] = q, k, v
             g, u = self.qw(p + "ffn_gate.weight"), self.qw(p + "ffn_up.weight")
+            if tp > 1:
+                g, u = g.row_slice(f0, f1), u.row_slice(f0, f1)
             if g.ggml_type == u.ggml_type:
                 L["gate_up"] = QuantWeight.concat_rows([g, u], p + "ffn_gate_up")
             else:
                 L["gate"], L["up"] = g, u
-            for b in ("attn_q.bias", "attn_k.bias", "attn_v.bias"):
+            for b, (s0, s1) in (("attn_q.bias", (q0 * Dh, q1 * Dh)), ("attn_k.bias", (k0 * Dh, k1 * Dh)),
+                                ("attn_v.bias", (k0 * Dh, k1 * Dh))):
                 if self.has(p + b):
                     L.setdefault("qkv_bias", [])
-                    L["qkv_bias"].append(self.f32(p + b))
+                    L["qkv_bias"].append(self.f32(p + b)[s0:s1] if tp > 1 else self.f32(p + b))
             if "qkv_bias" in L:
                 L["qkv_bias"] = torch.cat(L["qkv_bias"])
             self.layers.append(L)
@@ -61,8 +82,9 @@ class Qwen3Model(ModelBase):
 
     def forward_batch(self, batch: Batch, want_logits: bool = True) -> Optional[torch.Tensor]:
         c = self.cfg
-        Hq, Hkv, Dh = c.n_heads, c.n_kv_heads, c.head_dim
+        Hq, Hkv, Dh = self.Hq, self.Hkv, c.head_dim
         T = batch.T
+        tp = self.tp_size > 1
         small = T <= F.GEMV_MAX_M
         mid = torch.float32 if small else torch.bfloat16
         h = F.embed(self.tok_emb, batch.tokens)
@@ -80,18 +102,30 @@ class Qwen3Model(ModelBase):
             qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=self.kv.k[l],
                                   v_cache=self.kv.v[l], rope=self.rope, qn=L["q_norm"], kn=L["k_norm"], eps=c.eps)
             o = F.attention(qr, self.kv.k[l], self.kv.v[l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh)
-            h = F.linear(F.as_act(o), L["wo"], residual=h)
+            h = self.row_parallel(F.as_act(o), L["wo"], h)
             a = F.norm(h, L["ffn_norm"], c.eps, want_q8=small)
             if "gate_up" in L:
                 gu = F.linear(a, L["gate_up"], act="swiglu", out_dtype=torch.bfloat16)
             else:
                 gu = F.glu("swiglu", F.linear(a, L["gate"], out_dtype=mid), F.linear(a, L["up"], out_dtype=mid))
-            h = F.linear(F.as_act(gu), L["down"], residual=h)
+            h = self.row_parallel(F.as_act(gu), L["down"], h)
         if not want_logits:
             return None
         last = h[batch.last_idx].contiguous()
         a = F.norm(last, self.out_norm, c.eps, want_q8=True)
         return self.lm_head_logits(a)
 
+    def row_parallel(self, a, w: QuantWeight, h: torch.Tensor) -> torch.Tensor:
+        """h + a @ w^T where ``w`` holds this rank's slice of the input features: the partial
+        products are summed over the tensor-parallel group before the residual add."""
+        if self.tp_size == 1:
+            return F.linear(a, w, residual=h)
+        y = F.linear(a, w)
+        self.comm.all_reduce(y)
+        return h.add_(y) if h.is_cuda else h + y
+
     def lm_head_logits(self, a) -> torch.Tensor:
-        return F.linear(a, self.lm_head, out_dtype=torch.float32)
+        logits = F.linear(a, self.lm_head, out_dtype=torch.float32)
+        if self.vocab_sharded:
+            logits = self.comm.all_gather_cat(logits, dim=1)
+        return logits

@@ -156,6 +156,22 @@ class QuantWeight:
             out.append(p[start * per:stop * per])
         return QuantWeight(self.ggml_type, stop - start, self.K, out, 1, self.name)
 
+    def col_slice(self, k0: int, k1: int) -> "QuantWeight":
+        """Columns (input features) ``[k0, k1)`` of every row as a new, contiguous weight
+        (tensor-parallel row shard).  The range must fall on block boundaries."""
+        assert self.experts == 1 or True
+        bs = block_size(self.ggml_type)
+        if k0 % bs or k1 % bs:
+            raise ValueError(f"col_slice [{k0}, {k1}) is not aligned to the {self.ggml_type.name} block of {bs}")
+        rows = self.rows
+        out = []
+        for p in self.planes:
+            per_row = p.numel() // rows
+            per_k = per_row * bs // self.K            # plane bytes per block of `bs` values
+            v = p.view(rows, per_row)
+            out.append(v[:, (k0 // bs) * per_k:(k1 // bs) * per_k].contiguous().view(-1))
+        return QuantWeight(self.ggml_type, self.N, k1 - k0, out, self.experts, self.name)
+
     @staticmethod
     def concat_rows(ws: Sequence["QuantWeight"], name: str = "") -> "QuantWeight":
         """Stack matrices with equal K and type along N (fused QKV / gate-up).

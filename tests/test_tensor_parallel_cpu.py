@@ -1,0 +1,60 @@
+"""Tensor-parallel sharding checked on CPU ranks (Gloo): two ranks must reproduce the
+single-rank logits, and the shard arithmetic must tile every dimension exactly."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from tensorsharp_b200.parallel.dist import block_split, even_split, head_split
+
+
+def test_shard_arithmetic_tiles_exactly():
+    for n, parts in ((9728, 8), (151936, 8), (10, 3), (7, 8)):
+        spans = [even_split(n, parts, r) for r in range(parts)]
+        assert spans[0][0] == 0 and spans[-1][1] == n
+        assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+    spans = [block_split(9728, 256, 8, r) for r in range(8)]          # 38 super-blocks over 8 ranks
+    assert [(e - s) // 256 for s, e in spans] == [5, 5, 5, 5, 5, 5, 4, 4]
+    assert all(s % 256 == 0 for s, _ in spans) and spans[-1][1] == 9728
+    (q, kv) = head_split(32, 8, 8, 3)
+    assert q == (12, 16) and kv == (3, 4)
+    with pytest.raises(ValueError):
+        head_split(32, 8, 3, 0)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, path, prompt, out_path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    from tensorsharp_b200.models.base import ModelBase
+    from tensorsharp_b200.parallel.dist import Communicator
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        m = ModelBase.create(path, "cpu", max_context=128, tp_rank=rank, tp_size=world, comm=Communicator(rank, world))
+        l1 = m.forward(prompt)
+        t = int(l1.argmax())
+        l2 = m.forward([t])
+        if rank == 0:
+            torch.save((l1, l2), out_path)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tp2_matches_single_rank(tiny_qwen3_path, tmp_path):
+    from tensorsharp_b200.models.base import ModelBase
+    g = torch.Generator().manual_seed(3)
+    prompt = torch.randint(0, 4096, (19,), generator=g).tolist()
+    single = ModelBase.create(tiny_qwen3_path, "cpu", max_context=128)
+    s1 = single.forward(prompt)
+    s2 = single.forward([int(s1.argmax())])
+    out = str(tmp_path / "tp.pt")
+    mp.spawn(_worker, args=(2, _free_port(), tiny_qwen3_path, prompt, out), nprocs=2, join=True)
+    l1, l2 = torch.load(out)
+    assert torch.allclose(l1, s1, atol=5e-3) and torch.allclose(l2, s2, atol=5e-3)
