@@ -238,8 +238,21 @@ def run_ours(args) -> dict:
         "clocks": clock_info,
     }
     if world > 1:
+        # Tearing an NCCL communicator down while CUDA graphs that captured its kernels are still
+        # alive blocks for ever in destroy_process_group(); print first, drop the graphs, then
+        # leave without the collective teardown (process exit releases everything).
+        import gc
+
         import torch.distributed as dist
-        dist.destroy_process_group()
+        if rank == 0:
+            print(json.dumps(res), flush=True)
+        dg.graph = None
+        del dg
+        gc.collect()
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
     return res if rank == 0 else None
 
 
@@ -253,6 +266,10 @@ def run_reference(args) -> dict:
 
 def main():
     args = parse_args()
+    dump = os.environ.get("TSB_BENCH_STACK_DUMP_AFTER")
+    if dump:          # diagnostics: print every thread's Python stack if the run is still going after N seconds
+        import faulthandler
+        faulthandler.dump_traceback_later(float(dump), repeat=False, exit=True)
     res = run_reference(args) if args.impl == "reference" else run_ours(args)
     if res is not None:
         print(json.dumps(res), flush=True)
