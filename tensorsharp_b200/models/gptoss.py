@@ -1,0 +1,143 @@
+"""GPT-OSS: alternating sliding-window / full attention with learned sinks, YaRN RoPE,
+mixture of experts (top-k on router logits, softmax over the selected), SwiGLU with clamp,
+MXFP4 expert weights, biases on every projection.
+
+Parity: TensorSharp.Models/Models/GptOss/GptOssModel.cs - metadata keys :60-75, expert bias
+split :95, gate/up fusion by concatenation :126, fused QKV + bias :182, even layers are
+sliding-window :473, RoPE NeoX + YaRN (ext_factor 1, beta_fast 32, beta_slow 1,
+freq_scale 1/scale) :683-687, sinks in the softmax :591-623, decode window :625-671,
+router :814-865, clamp activation :901-934, last layer's MoE only on the last prompt token
+:429-454.  Tensor names: attn_{q,k,v,output}.{weight,bias}, attn_sinks.weight,
+post_attention_norm.weight, ffn_gate_inp.{weight,bias}, ffn_{gate,up,down}_exps.{weight,bias}.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..ops import functional as F
+from ..ops.functional import Act, Batch, RopeSpec
+from ..ops.kernels import yarn_corr_dims
+from ..parallel.dist import even_split, head_split
+from ..quant.qweight import QuantWeight
+from .base import ModelBase, register_architecture
+
+
+@register_architecture("gpt-oss", "gptoss")
+class GptOssModel(ModelBase):
+    def parse_config(self) -> None:
+        g, a, c = self.gguf, self.arch, self.cfg
+        self.n_experts = g.get_int(f"{a}.expert_count", 0)
+        self.top_k = g.get_int(f"{a}.expert_used_count", 0)
+        self.window = g.get_int(f"{a}.attention.sliding_window", 128)
+        self.expert_ffn = g.get_int(f"{a}.expert_feed_forward_length", 0)
+        self.orig_ctx = g.get_int(f"{a}.rope.scaling.original_context_length", 4096)
+
+    def load_weights(self) -> None:
+        c = self.cfg
+        tp, r = self.tp_size, self.tp_rank
+        Dh = c.head_dim
+        (q0, q1), (k0, k1) = head_split(c.n_heads, c.n_kv_heads, tp, r)
+        self.Hq, self.Hkv = q1 - q0, k1 - k0
+        # expert parallelism: contiguous expert ranges per rank (ep defaults to the tp group)
+        ep, er = (self.ep_size, self.ep_rank) if self.ep_size > 1 else (tp, r)
+        self.e0, self.e1 = even_split(self.n_experts, ep, er)
+        self.tok_emb = self.qw("token_embd.weight")
+        self.out_norm = self.f32("output_norm.weight")
+        self.lm_head = self.qw("output.weight", optional=True) or self.tok_emb
+        self.layers = []
+        for l in range(c.n_layers):
+            p = f"blk.{l}."
+            q, k, v = self.qw(p + "attn_q.weight"), self.qw(p + "attn_k.weight"), self.qw(p + "attn_v.weight")
+            bq, bk, bv = (self.f32(p + f"attn_{n}.bias", optional=True) for n in "qkv")
+            wo = self.qw(p + "attn_output.weight")
+            sinks = self.f32(p + "attn_sinks.weight", optional=True)
+            if tp > 1:
+                q, k, v = q.row_slice(q0 * Dh, q1 * Dh), k.row_slice(k0 * Dh, k1 * Dh), v.row_slice(k0 * Dh, k1 * Dh)
+                wo = wo.col_slice(q0 * Dh, q1 * Dh)
+                if bq is not None:
+                    bq, bk, bv = bq[q0 * Dh:q1 * Dh], bk[k0 * Dh:k1 * Dh], bv[k0 * Dh:k1 * Dh]
+                if sinks is not None:
+                    sinks = sinks[q0:q1].contiguous()
+            L = {
+                "attn_norm": self.f32(p + "attn_norm.weight"),
+                "wo": wo,
+                "bo": self.f32(p + "attn_output.bias", optional=True),
+                "sinks": sinks,
+                "ffn_norm": self.f32(p + ("post_attention_norm.weight" if self.has(p + "post_attention_norm.weight")
+                                          else "ffn_norm.weight")),
+                "router": self.qw(p + "ffn_gate_inp.weight"),
+                "router_bias": self.f32(p + "ffn_gate_inp.bias", optional=True),
+            }
+            if q.ggml_type == k.ggml_type == v.ggml_type:
+                L["wqkv"] = QuantWeight.concat_rows([q, k, v], p + "attn_qkv")
+                L["bqkv"] = torch.cat([bq, bk, bv]).contiguous() if bq is not None else None
+            else:
+                L["wq"], L["wk"], L["wv"], L["bq"], L["bk"], L["bv"] = q, k, v, bq, bk, bv
+            ge, ue, de = (self.qw(p + f"ffn_{n}_exps.weight") for n in ("gate", "up", "down"))
+            gb, ub, db = (self.f32(p + f"ffn_{n}_exps.bias", optional=True) for n in ("gate", "up", "down"))
+            if self.e1 - self.e0 != self.n_experts:
+                ge, ue, de = (w.expert_range(self.e0, self.e1) for w in (ge, ue, de))
+                gb, ub, db = (b[self.e0:self.e1] if b is not None else None for b in (gb, ub, db))
+            if ge.ggml_type == ue.ggml_type:
+                L["gate_up_exps"] = QuantWeight.concat_rows_per_expert([ge, ue], p + "ffn_gate_up_exps")
+                L["gate_up_bias"] = torch.cat([gb, ub], 1).contiguous() if gb is not None else None
+            else:
+                raise ValueError(f"{p}ffn_gate_exps / ffn_up_exps have different types; cannot fuse")
+            L["down_exps"], L["down_bias"] = de, (db.contiguous() if db is not None else None)
+            self.layers.append(L)
+        scale = c.rope_scale
+        lo, hi = yarn_corr_dims(Dh, self.orig_ctx, c.rope_base, 32.0, 1.0)
+        self.rope = RopeSpec(rot_dim=Dh, theta_base=c.rope_base, mode=0, freq_scale=1.0 / scale,
+                             ext_factor=1.0 if scale != 1.0 else 0.0, attn_factor=1.0, corr_lo=lo, corr_hi=hi)
+
+    def forward_batch(self, batch: Batch, want_logits: bool = True) -> Optional[torch.Tensor]:
+        c = self.cfg
+        Hq, Hkv, Dh = self.Hq, self.Hkv, c.head_dim
+        T = batch.T
+        small = T <= F.GEMV_MAX_M
+        mid = torch.float32 if small else torch.bfloat16
+        h = F.embed(self.tok_emb, batch.tokens)
+        n_layers = len(self.layers)
+        for l, L in enumerate(self.layers):
+            a = F.norm(h, L["attn_norm"], c.eps, want_q8=small)
+            if "wqkv" in L:
+                qkv = F.linear(a, L["wqkv"], bias=L["bqkv"], out_dtype=mid)
+                q = qkv[:, :Hq * Dh].view(T, Hq, Dh)
+                k = qkv[:, Hq * Dh:(Hq + Hkv) * Dh].view(T, Hkv, Dh)
+                v = qkv[:, (Hq + Hkv) * Dh:].view(T, Hkv, Dh)
+            else:
+                q = F.linear(a, L["wq"], bias=L["bq"], out_dtype=mid).view(T, Hq, Dh)
+                k = F.linear(a, L["wk"], bias=L["bk"], out_dtype=mid).view(T, Hkv, Dh)
+                v = F.linear(a, L["wv"], bias=L["bv"], out_dtype=mid).view(T, Hkv, Dh)
+            qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=self.kv.k[l],
+                                  v_cache=self.kv.v[l], rope=self.rope, eps=c.eps)
+            o = F.attention(qr, self.kv.k[l], self.kv.v[l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh,
+                            window=self.window if l % 2 == 0 else 0, sinks=L["sinks"])
+            h = self.reduce_add(F.linear(F.as_act(o), L["wo"], bias=L["bo"] if self.tp_rank == 0 else None), h)
+            # mixture of experts; on the last layer of a prefill only the last token of each
+            # sequence feeds the logits, so only those rows are run
+            last_only = (l == n_layers - 1) and not batch.is_decode
+            hm = h[batch.last_idx].contiguous() if last_only else h
+            a = F.norm(hm, L["ffn_norm"], c.eps, want_q8=hm.shape[0] <= F.GEMV_MAX_M)
+            logits = F.linear(a, L["router"], bias=L["router_bias"], out_dtype=torch.float32)
+            ids, w = F.route_topk_softmax(logits, self.top_k)
+            y = F.moe_experts(a, ids, w, L["gate_up_exps"], L["down_exps"], act="swiglu_oai",
+                              gate_up_bias=L["gate_up_bias"], down_bias=L["down_bias"], expert_offset=self.e0)
+            if self.e1 - self.e0 != self.n_experts and self.comm is not None:
+                self.comm.all_reduce(y)
+            if last_only:
+                h = hm + y
+            else:
+                h = h + y
+        if not want_logits:
+            return None
+        last = h if (not batch.is_decode and n_layers > 0) else h[batch.last_idx].contiguous()
+        a = F.norm(last.contiguous(), self.out_norm, c.eps, want_q8=True)
+        return F.linear(a, self.lm_head, out_dtype=torch.float32)
+
+    def reduce_add(self, y: torch.Tensor, h: torch.Tensor) -> torch.Tensor:
+        if self.tp_size > 1:
+            self.comm.all_reduce(y)
+        return h + y

@@ -101,6 +101,7 @@ class Qwen3Model(ModelBase):
                 v = F.linear(a, L["wv"], out_dtype=mid).view(T, Hkv, Dh)
             qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=self.kv.k[l],
                                   v_cache=self.kv.v[l], rope=self.rope, qn=L["q_norm"], kn=L["k_norm"], eps=c.eps)
+            qr = self.q_post_scale(qr, batch)
             o = F.attention(qr, self.kv.k[l], self.kv.v[l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh)
             h = self.row_parallel(F.as_act(o), L["wo"], h)
             a = F.norm(h, L["ffn_norm"], c.eps, want_q8=small)
@@ -114,6 +115,9 @@ class Qwen3Model(ModelBase):
         last = h[batch.last_idx].contiguous()
         a = F.norm(last, self.out_norm, c.eps, want_q8=True)
         return self.lm_head_logits(a)
+
+    def q_post_scale(self, qr: torch.Tensor, batch: Batch) -> torch.Tensor:
+        return qr
 
     def row_parallel(self, a, w: QuantWeight, h: torch.Tensor) -> torch.Tensor:
         """h + a @ w^T where ``w`` holds this rank's slice of the input features: the partial

@@ -289,3 +289,140 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
 
 def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
     return torch.tanh(x / cap) * cap if cap and cap > 0 else x
+
+
+# --------------------------------------------------------------------------------------------
+# Mixture of experts
+# --------------------------------------------------------------------------------------------
+def route_topk_softmax(logits: torch.Tensor, k: int):
+    """Top-k on the router logits, then softmax over the selected k (GPT-OSS, Qwen3.5 decode;
+    GptOssModel.cs:814-865).  Equivalent to softmax over all -> top-k -> renormalise."""
+    vals, ids = torch.topk(logits.float(), k, dim=-1)
+    return ids.to(torch.int32), torch.softmax(vals, -1)
+
+
+def route_sigmoid(logits: torch.Tensor, k: int, bias: Optional[torch.Tensor], normalize: bool, scale: float):
+    """Nemotron-H router: selection on sigmoid(logits) + bias, weights are the unbiased
+    sigmoid values, optionally normalised (floor 6.1e-5) and scaled (NemotronModel.cs:822-856)."""
+    p = torch.sigmoid(logits.float())
+    sel = p + bias.float() if bias is not None else p
+    _, ids = torch.topk(sel, k, dim=-1)
+    w = p.gather(-1, ids)
+    if normalize:
+        w = w / w.sum(-1, keepdim=True).clamp_min(6.103515625e-5)
+    return ids.to(torch.int32), w * scale
+
+
+def moe_experts(a: Act, ids: torch.Tensor, weights: torch.Tensor, gate_up: QuantWeight, down: QuantWeight, *,
+                act: str, gate_up_bias: Optional[torch.Tensor] = None, down_bias: Optional[torch.Tensor] = None,
+                expert_offset: int = 0, down_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """sum_k weights[t, k] * down_e(act(gate_up_e(x_t)))  with e = ids[t, k]  -> f32 [T, D].
+
+    ``gate_up`` / ``down`` are expert stacks; when they hold only experts
+    ``[expert_offset, expert_offset + E_local)`` (expert parallelism) the other selections are
+    skipped and the caller sums the partial results over ranks.  For non-gated activations
+    (relu2) ``gate_up`` is the plain up projection."""
+    T, k = ids.shape
+    D = down.N
+    E_local = gate_up.experts
+    glu_act = act not in ("relu2", "silu")
+    F_out = gate_up.N // 2 if glu_act else gate_up.N
+    dev = ids.device
+    local = ids - expert_offset
+    if expert_offset != 0 or E_local != int(1e9):
+        local = torch.where((local >= 0) & (local < E_local), local, torch.full_like(local, -1))
+    if dev.type == "cuda" and T * k <= 4 * GEMV_MAX_M:
+        kk = _k()
+        flat = local.reshape(-1).contiguous()
+        if gate_up.uses_q8_activations:
+            _ensure_q8(a)
+            gu = torch.zeros((T * k, F_out), dtype=torch.bfloat16, device=dev)
+            kk.gemv(gate_up, xq=a.q, xds=a.ds, M=1, ids=flat, x_div=k, act=act if glu_act or act == "relu2" else None,
+                    bias=gate_up_bias, out=gu)
+        else:
+            gu = torch.zeros((T * k, F_out), dtype=torch.bfloat16, device=dev)
+            kk.gemv(gate_up, xb=a.b.contiguous(), M=1, ids=flat, x_div=k,
+                    act=act if glu_act or act == "relu2" else None, bias=gate_up_bias, out=gu)
+        if act == "silu":
+            gu, _, _ = kk.glu(gu, None, "silu", F_out, F_out, 0, T * k)
+        w = weights.reshape(-1).float().contiguous()
+        if down_scale is not None:
+            w = w * down_scale[ids.reshape(-1).long()]
+        y = torch.zeros((T * k, D), dtype=torch.float32, device=dev)
+        if down.uses_q8_activations:
+            gq, gds = kk.quantize_q8(gu)
+            kk.gemv(down, xq=gq, xds=gds, M=1, ids=flat, x_div=1, bias=down_bias, row_scale=w, out=y)
+        else:
+            kk.gemv(down, xb=gu, M=1, ids=flat, x_div=1, bias=down_bias, row_scale=w, out=y)
+        return y.view(T, k, D).sum(1)
+    # grouped path: sort the (token, slot) pairs by expert and run each expert on its rows
+    out = torch.zeros((T, D), dtype=torch.float32, device=dev)
+    flat = local.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount((flat[order] + 1).long(), minlength=E_local + 1).tolist()
+    x = a.b
+    off = counts[0]                      # skipped (non-local) selections sort first (-1)
+    wflat = weights.reshape(-1).float()
+    if down_scale is not None:
+        wflat = wflat * down_scale[ids.reshape(-1).long()]
+    for e in range(E_local):
+        n = counts[e + 1]
+        if n == 0:
+            continue
+        rows = order[off:off + n]
+        off += n
+        tok = torch.div(rows, k, rounding_mode="floor")
+        xe = Act(x[tok].contiguous())
+        gb = gate_up_bias[e] if gate_up_bias is not None else None
+        y1 = linear(xe, gate_up.expert(e), bias=gb, act=act, out_dtype=torch.bfloat16 if dev.type == "cuda" else torch.float32)
+        db = down_bias[e] if down_bias is not None else None
+        y2 = linear(as_act(y1), down.expert(e), bias=db, out_dtype=torch.float32)
+        out.index_add_(0, tok, y2 * wflat[rows].unsqueeze(1))
+    return out
+
+
+# --------------------------------------------------------------------------------------------
+# Recurrent layers (state tensors are indexed by ``batch.seq_slots``)
+# --------------------------------------------------------------------------------------------
+def causal_conv1d(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor, batch: Batch,
+                  act_silu: bool = True) -> torch.Tensor:
+    """Depth-wise causal conv over the packed tokens; ``state`` [slots, K-1, C] carries each
+    sequence's last K-1 inputs between calls.  Returns f32 [T, C]."""
+    if x.is_cuda:
+        return _k().causal_conv1d(x, w, bias, state, batch.cu_q, batch.seq_slots, batch.max_q_len, act_silu)
+    outs = []
+    slots = batch.seq_slots.tolist()
+    for b in range(batch.B):
+        q0, q1 = batch.h_cu_q[b], batch.h_cu_q[b + 1]
+        o, tail = ref.causal_conv1d(x[q0:q1], w, bias, state[slots[b]], act_silu)
+        state[slots[b]] = tail
+        outs.append(o)
+    return torch.cat(outs, 0)
+
+
+def gdn(qkv: torch.Tensor, z: torch.Tensor, beta: torch.Tensor, alpha: torch.Tensor, dt_bias, a_log, norm_w,
+        state: torch.Tensor, batch: Batch, *, Hk: int, Hv: int, Dk: int, Dv: int, eps: float) -> torch.Tensor:
+    """GatedDeltaNet recurrence over the packed tokens -> gated output [T, Hv*Dv]."""
+    if qkv.is_cuda:
+        return _k().gdn_recurrent(qkv, z, beta, alpha, dt_bias, a_log, norm_w, state, batch.cu_q, batch.seq_slots,
+                                  Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=eps)
+    outs = []
+    slots = batch.seq_slots.tolist()
+    for b in range(batch.B):
+        q0, q1 = batch.h_cu_q[b], batch.h_cu_q[b + 1]
+        outs.append(ref.gdn_recurrent(qkv[q0:q1], z[q0:q1], beta[q0:q1], alpha[q0:q1], dt_bias, a_log, norm_w,
+                                      state[slots[b]], Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=eps))
+    return torch.cat(outs, 0)
+
+
+def mamba2(xbc: torch.Tensor, dt: torch.Tensor, dt_bias, A, D, state: torch.Tensor, batch: Batch, *, H: int, P: int,
+           G: int, N: int) -> torch.Tensor:
+    """Mamba2 selective scan over the packed tokens -> y f32 [T, H*P] (before gating)."""
+    if xbc.is_cuda:
+        return _k().mamba2_recurrent(xbc, dt, dt_bias, A, D, state, batch.cu_q, batch.seq_slots, H=H, P=P, G=G, N=N)
+    outs = []
+    slots = batch.seq_slots.tolist()
+    for b in range(batch.B):
+        q0, q1 = batch.h_cu_q[b], batch.h_cu_q[b + 1]
+        outs.append(ref.mamba2_recurrent(xbc[q0:q1], dt[q0:q1], dt_bias, A, D, state[slots[b]], H=H, P=P, G=G, N=N))
+    return torch.cat(outs, 0)

@@ -75,7 +75,8 @@ def _lib():
     lib = native.lib()
     if not _configured:
         for name in ("tsb_quantize_q8", "tsb_gemv", "tsb_rmsnorm", "tsb_qkv_rope", "tsb_glu", "tsb_gather_rows",
-                     "tsb_argmax", "tsb_rope_table", "tsb_decode_advance", "tsb_attn_decode", "tsb_attn_prefill", "tsb_gemm_bf16"):
+                     "tsb_argmax", "tsb_rope_table", "tsb_decode_advance", "tsb_attn_decode", "tsb_attn_prefill", "tsb_gemm_bf16", "tsb_causal_conv1d", "tsb_gdn_recurrent",
+                     "tsb_mamba2_recurrent"):
             getattr(lib, name).restype = C.c_int
         _configured = True
     return lib
@@ -293,3 +294,69 @@ def gemm_bf16(W: torch.Tensor, X: torch.Tensor, *, out_dtype=torch.bfloat16, bia
                                       _stream()), "gemm_bf16")
     _count(1)
     return out
+
+
+# --------------------------------------------------------------------------------------------
+class ConvArgs(C.Structure):
+    _fields_ = [("x", _vp), ("xs", C.c_long), ("x_f32", C.c_int), ("w", _vp), ("bias", _vp), ("state", _vp),
+                ("cu_q", _vp), ("seq_slots", _vp), ("out", _vp), ("os", C.c_long),
+                ("C", C.c_int), ("K", C.c_int), ("B", C.c_int), ("act", C.c_int)]
+
+
+class GdnArgs(C.Structure):
+    _fields_ = [("qkv", _vp), ("qkv_s", C.c_long), ("z", _vp), ("z_s", C.c_long), ("z_f32", C.c_int),
+                ("beta", _vp), ("alpha", _vp), ("ba_s", C.c_long), ("ba_f32", C.c_int),
+                ("dt_bias", _vp), ("a", _vp), ("norm_w", _vp), ("state", _vp), ("cu_q", _vp), ("seq_slots", _vp),
+                ("out", _vp), ("out_s", C.c_long), ("eps", C.c_float),
+                ("Hk", C.c_int), ("Hv", C.c_int), ("Dk", C.c_int), ("Dv", C.c_int), ("B", C.c_int)]
+
+
+class MambaArgs(C.Structure):
+    _fields_ = [("xbc", _vp), ("xbc_s", C.c_long), ("dt", _vp), ("dt_s", C.c_long), ("dt_f32", C.c_int),
+                ("dt_bias", _vp), ("A", _vp), ("D", _vp), ("state", _vp), ("cu_q", _vp), ("seq_slots", _vp),
+                ("y", _vp), ("y_s", C.c_long),
+                ("H", C.c_int), ("P", C.c_int), ("G", C.c_int), ("N", C.c_int), ("B", C.c_int)]
+
+
+def causal_conv1d(x, w, bias, state, cu_q, seq_slots, max_q, act_silu=True) -> torch.Tensor:
+    """x [T, C] view (row stride allowed) -> f32 [T, C]; the per-slot tail ``state`` is updated."""
+    T, Cc = x.shape
+    out = torch.empty((T, Cc), dtype=torch.float32, device=x.device)
+    a = ConvArgs()
+    a.x, a.xs, a.x_f32 = _p(x), x.stride(0), int(x.dtype == torch.float32)
+    a.w, a.bias, a.state = _p(w), _p(bias), _p(state)
+    a.cu_q, a.seq_slots, a.out, a.os = _p(cu_q), _p(seq_slots), _p(out), Cc
+    a.C, a.K, a.B, a.act = Cc, w.shape[1], cu_q.numel() - 1, 1 if act_silu else 0
+    native.check(_lib().tsb_causal_conv1d(C.byref(a), C.c_int(max_q), _stream()), "causal_conv1d")
+    _count(2)
+    return out
+
+
+def gdn_recurrent(qkv, z, beta, alpha, dt_bias, a_log, norm_w, state, cu_q, seq_slots, *, Hk, Hv, Dk, Dv, eps):
+    T = qkv.shape[0]
+    out = torch.empty((T, Hv * Dv), dtype=torch.bfloat16, device=qkv.device)
+    assert qkv.dtype == torch.float32 and beta.dtype == alpha.dtype and beta.stride(0) == alpha.stride(0)
+    a = GdnArgs()
+    a.qkv, a.qkv_s = _p(qkv), qkv.stride(0)
+    a.z, a.z_s, a.z_f32 = _p(z), z.stride(0), int(z.dtype == torch.float32)
+    a.beta, a.alpha, a.ba_s, a.ba_f32 = _p(beta), _p(alpha), beta.stride(0), int(beta.dtype == torch.float32)
+    a.dt_bias, a.a, a.norm_w, a.state = _p(dt_bias), _p(a_log), _p(norm_w), _p(state)
+    a.cu_q, a.seq_slots, a.out, a.out_s, a.eps = _p(cu_q), _p(seq_slots), _p(out), Hv * Dv, eps
+    a.Hk, a.Hv, a.Dk, a.Dv, a.B = Hk, Hv, Dk, Dv, cu_q.numel() - 1
+    native.check(_lib().tsb_gdn_recurrent(C.byref(a), _stream()), "gdn_recurrent")
+    _count(1)
+    return out
+
+
+def mamba2_recurrent(xbc, dt, dt_bias, A, D, state, cu_q, seq_slots, *, H, P, G, N):
+    T = xbc.shape[0]
+    y = torch.empty((T, H * P), dtype=torch.float32, device=xbc.device)
+    a = MambaArgs()
+    a.xbc, a.xbc_s = _p(xbc), xbc.stride(0)
+    a.dt, a.dt_s, a.dt_f32 = _p(dt), dt.stride(0), int(dt.dtype == torch.float32)
+    a.dt_bias, a.A, a.D, a.state = _p(dt_bias), _p(A), _p(D), _p(state)
+    a.cu_q, a.seq_slots, a.y, a.y_s = _p(cu_q), _p(seq_slots), _p(y), H * P
+    a.H, a.P, a.G, a.N, a.B = H, P, G, N, cu_q.numel() - 1
+    native.check(_lib().tsb_mamba2_recurrent(C.byref(a), _stream()), "mamba2_recurrent")
+    _count(1)
+    return y

@@ -123,3 +123,61 @@ def quantize_q8_dequant(x: torch.Tensor) -> torch.Tensor:
     d = g.abs().amax(1, keepdim=True) / 127.0
     q = torch.where(d > 0, torch.round(g / d), torch.zeros_like(g))
     return (q * d).reshape(xf.shape)
+
+
+def causal_conv1d(x: torch.Tensor, w: torch.Tensor, bias, tail: torch.Tensor, act_silu: bool = True):
+    """One sequence.  x [n, C]; w [C, K]; tail [K-1, C] (oldest first).  Returns (out [n, C],
+    new tail).  out[t] = act(bias + sum_k w[:, k] * in[t - (K-1) + k])."""
+    K = w.shape[1]
+    ext = torch.cat([tail.float(), x.float()], 0)                     # [K-1+n, C]
+    n = x.shape[0]
+    out = torch.zeros(n, x.shape[1])
+    for k in range(K):
+        out = out + ext[k:k + n] * w[:, k].float()
+    if bias is not None:
+        out = out + bias.float()
+    if act_silu:
+        out = torch.nn.functional.silu(out)
+    return out, ext[ext.shape[0] - (K - 1):].clone()
+
+
+def gdn_recurrent(qkv, z, beta, alpha, dt_bias, a_log, norm_w, state, *, Hk, Hv, Dk, Dv, eps):
+    """One sequence, token by token.  state [Hv, Dv, Dk] is updated in place.  Returns [n, Hv*Dv]."""
+    n = qkv.shape[0]
+    out = torch.zeros(n, Hv * Dv)
+    hk = torch.arange(Hv) % Hk
+    for t in range(n):
+        q = qkv[t, :Hk * Dk].float().view(Hk, Dk)[hk]
+        k = qkv[t, Hk * Dk:2 * Hk * Dk].float().view(Hk, Dk)[hk]
+        v = qkv[t, 2 * Hk * Dk:].float().view(Hv, Dv)
+        q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + eps) * (Dv ** -0.5)
+        k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + eps)
+        g = torch.nn.functional.softplus(alpha[t].float() + dt_bias.float()) * a_log.float()
+        state.mul_(torch.exp(g).view(Hv, 1, 1))
+        b = torch.sigmoid(beta[t].float())
+        kv = torch.einsum("hvk,hk->hv", state, k)
+        delta = (v - kv) * b.view(Hv, 1)
+        state.add_(torch.einsum("hv,hk->hvk", delta, k))
+        core = torch.einsum("hvk,hk->hv", state, q)
+        core = core * torch.rsqrt(core.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float()
+        out[t] = (core * torch.nn.functional.silu(z[t].float().view(Hv, Dv))).reshape(-1)
+    return out
+
+
+def mamba2_recurrent(xbc, dt, dt_bias, A, D, state, *, H, P, G, N):
+    """One sequence.  state [H, P, N] updated in place.  Returns y [n, H*P] (before gating)."""
+    n = xbc.shape[0]
+    y = torch.zeros(n, H * P)
+    grp = torch.arange(H) // (H // G)
+    for t in range(n):
+        x = xbc[t, :H * P].float().view(H, P)
+        Bm = xbc[t, H * P:H * P + G * N].float().view(G, N)[grp]
+        Cm = xbc[t, H * P + G * N:].float().view(G, N)[grp]
+        d = torch.nn.functional.softplus(dt[t].float() + (dt_bias.float() if dt_bias is not None else 0.0))
+        dA = torch.exp(d * A.float())
+        state.mul_(dA.view(H, 1, 1)).add_(torch.einsum("hp,hn->hpn", x * d.view(H, 1), Bm))
+        yy = torch.einsum("hpn,hn->hp", state, Cm)
+        if D is not None:
+            yy = yy + D.float().view(H, 1) * x
+        y[t] = yy.reshape(-1)
+    return y

@@ -182,6 +182,26 @@ class QuantWeight:
         planes = [torch.cat([w.planes[i] for w in ws]) for i in range(len(ws[0].planes))]
         return QuantWeight(t, sum(w.N for w in ws), K, planes, 1, name)
 
+    @staticmethod
+    def concat_rows_per_expert(ws: Sequence["QuantWeight"], name: str = "") -> "QuantWeight":
+        """Per-expert row concatenation of expert stacks ``[E, N_i, K]`` -> ``[E, sum N_i, K]``
+        (fused expert gate/up: concatenation, not interleave - GptOssModel.cs:126)."""
+        t, K, E = ws[0].ggml_type, ws[0].K, ws[0].experts
+        if any(w.ggml_type != t or w.K != K or w.experts != E for w in ws):
+            raise ValueError("concat_rows_per_expert needs equal type, K and expert count")
+        planes = []
+        for i in range(len(ws[0].planes)):
+            planes.append(torch.cat([w.planes[i].view(E, -1) for w in ws], 1).contiguous().view(-1))
+        return QuantWeight(t, sum(w.N for w in ws), K, planes, E, name)
+
+    def expert_range(self, e0: int, e1: int) -> "QuantWeight":
+        """Experts ``[e0, e1)`` as a new stack sharing storage (expert-parallel shard)."""
+        out = []
+        for p in self.planes:
+            per = p.numel() // self.experts
+            out.append(p[e0 * per:e1 * per])
+        return QuantWeight(self.ggml_type, self.N, self.K, out, e1 - e0, self.name)
+
     def to(self, device) -> "QuantWeight":
         return QuantWeight(self.ggml_type, self.N, self.K, [p.to(device) for p in self.planes], self.experts,
                            self.name)

@@ -1,0 +1,73 @@
+"""Every model family on the CPU oracle path: incremental decoding, chunked prefill and
+batched execution must agree with one-shot prefill (KV cache, sliding windows, sinks,
+recurrent state carry-over, MoE routing)."""
+import pytest
+import torch
+
+from tensorsharp_b200.models import synth
+from tensorsharp_b200.models.base import ModelBase, supported_architectures
+
+FAMILIES = {
+    "gptoss": (synth.write_gptoss, {}),
+    "qwen35_moe": (synth.write_qwen35, {}),
+    "qwen35_dense": (synth.write_qwen35, {"n_experts": 0}),
+    "gemma3": (synth.write_gemma, {"arch": "gemma3"}),
+    "gemma4": (synth.write_gemma, {"arch": "gemma4", "n_layers": 8, "head_dim_global": 128, "kv_heads_global": 1,
+                                   "rot_global": 64, "shared_kv": 2, "ple_dim": 32, "n_experts": 4, "top_k": 2}),
+    "mistral3": (synth.write_mistral3, {}),
+    "nemotron_h": (synth.write_nemotron_h, {}),
+}
+
+
+@pytest.fixture(scope="module")
+def family_paths(tmp_path_factory):
+    d = tmp_path_factory.mktemp("families")
+    out = {}
+    for name, (fn, kw) in FAMILIES.items():
+        p = str(d / f"{name}.gguf")
+        fn(p, device="cpu", **kw)
+        out[name] = p
+    return out
+
+
+def test_all_seven_families_are_registered():
+    archs = set(supported_architectures())
+    assert {"qwen3", "qwen35", "qwen35moe", "gpt-oss", "gemma3", "gemma4", "nemotron_h", "mistral3"} <= archs
+
+
+@pytest.mark.parametrize("name", list(FAMILIES))
+def test_incremental_matches_one_shot(family_paths, name):
+    m = ModelBase.create(family_paths[name], "cpu", max_context=256, max_seqs=3)
+    g = torch.Generator().manual_seed(7)
+    ids = torch.randint(0, 4096, (90,), generator=g).tolist()
+    full = m.forward(ids)
+    assert torch.isfinite(full).all() and full.shape == (m.cfg.vocab,)
+    # a different prompt gives different logits (the test is not vacuous)
+    m.reset_kv_cache()
+    other = m.forward(ids[:-1] + [(ids[-1] + 1) % 4096])
+    assert float((other - full).abs().max()) > 1e-4
+    # prefix then suffix
+    m.reset_kv_cache()
+    m.forward(ids[:51], want_logits=False)
+    inc = m.forward(ids[51:])
+    assert float((inc - full).abs().max()) < 2e-2
+    # token by token for the tail
+    m.reset_kv_cache()
+    m.forward(ids[:80], want_logits=False)
+    for t in ids[80:]:
+        step = m.forward([t])
+    assert float((step - full).abs().max()) < 2e-2
+    # two sequences in one batch equal the same sequences alone
+    s1, s2 = m.kv.new_seq(), m.kv.new_seq()
+    m.reset_recurrent_state(s1.slot)
+    m.reset_recurrent_state(s2.slot)
+    lb = m.forward_batch(m.kv.build_batch([s1, s2], [ids[:33], ids]))
+    assert float((lb[1] - full).abs().max()) < 2e-2
+
+
+def test_recurrent_models_refuse_truncation(family_paths):
+    m = ModelBase.create(family_paths["qwen35_dense"], "cpu", max_context=64)
+    m.forward([1, 2, 3])
+    with pytest.raises(RuntimeError):
+        m.truncate_kv_cache(1)
+    assert ModelBase.create(family_paths["gemma3"], "cpu", max_context=64).supports_kv_truncation
