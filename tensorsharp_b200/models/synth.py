@@ -161,7 +161,7 @@ QWEN3_TINY = dict(n_layers=4, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, 
                   rope_base=1e6, tied=True)
 
 
-def write_gptoss(path: str, *, n_layers=2, hidden=256, n_heads=8, n_kv_heads=2, head_dim=32, n_experts=8, top_k=2,
+def write_gptoss(path: str, *, n_layers=2, hidden=256, n_heads=8, n_kv_heads=2, head_dim=64, n_experts=8, top_k=2,
                  expert_ffn=256, vocab=4096, window=16, attn_scheme="BF16", expert_scheme="MXFP4", rope_base=150000.0,
                  rope_scale=32.0, orig_ctx=4096, eps=1e-5, context=131072, seed=0, device=None,
                  random_codes=True) -> int:

@@ -188,6 +188,8 @@ def glu(act: str, gate: torch.Tensor, up: Optional[torch.Tensor]) -> torch.Tenso
     if not gate.is_cuda:
         return ref.glu(act, gate, up)
     T, F = gate.shape
+    if up is not None and up.dtype != gate.dtype:      # the kernel reads both operands with one element type
+        up = up.to(gate.dtype)
     out, _, _ = _k().glu(gate, up, act, F, gate.stride(0), up.stride(0) if up is not None else 0, T)
     return out
 
