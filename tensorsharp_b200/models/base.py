@@ -112,6 +112,14 @@ class ModelBase:
     def parse_config(self) -> None:
         """Architecture-specific metadata; subclasses override."""
 
+    @property
+    def tokenizer(self):
+        """The tokenizer described by the file's ``tokenizer.*`` metadata (built on first use)."""
+        if getattr(self, "_tokenizer", None) is None:
+            from ..runtime.tokenizer import tokenizer_from_gguf
+            self._tokenizer = tokenizer_from_gguf(self.gguf)
+        return self._tokenizer
+
     # ------------------------------------------------------------------ weights
     def has(self, name: str) -> bool:
         return name in self.gguf.tensors
