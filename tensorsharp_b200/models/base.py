@@ -176,6 +176,23 @@ class ModelBase:
             self.reset_recurrent_state(self._default_seq.slot)
         return self._default_seq
 
+    def new_sequence(self) -> SeqState:
+        """A fresh sequence in the KV pool (recurrent state zeroed); raises OutOfPagesError when
+        every one of the pool's ``max_seqs`` slots is in use."""
+        s = self.kv.new_seq()
+        self.reset_recurrent_state(s.slot)
+        return s
+
+    def free_sequence(self, seq: SeqState) -> None:
+        if self._default_seq is seq:
+            self._default_seq = None
+        self.kv.free_seq(seq)
+
+    def bind_sequence(self, seq: Optional[SeqState]) -> None:
+        """Make ``seq`` the one the single-sequence API (forward / reset / truncate) acts on, so a
+        host that keeps several chats resident switches between them without forwarding."""
+        self._default_seq = seq
+
     @property
     def cache_length(self) -> int:
         return self._default_seq.length if self._default_seq is not None else 0

@@ -112,6 +112,25 @@ def format_entry(ts: _dt.datetime, level: str, category: str, event: Optional[Tu
     return json.dumps(d, ensure_ascii=False, default=str)
 
 
+_LABEL = {"Trace": "TRC", "Debug": "DBG", "Information": "INF", "Warning": "WRN", "Error": "ERR", "Critical": "CRT"}
+
+
+def format_text_line(ts: _dt.datetime, level: str, category: str, event: Optional[Tuple[int, str]], message: str,
+                     exception: Optional[str], scopes, include_scopes=True) -> str:
+    """The plain-text alternative (LogEntryFormatter.cs ToTextLine):
+    ``2026-01-01T00:00:00.000Z INF [1500:ChatStarted] Category: message => Key=value``."""
+    t = ts.astimezone(_dt.timezone.utc)
+    out = [t.strftime("%Y-%m-%dT%H:%M:%S.") + "%03dZ" % (t.microsecond // 1000), " ", _LABEL.get(level, "NON"), " "]
+    if event is not None and event[0] != 0:
+        out.append(f"[{event[0]}:{event[1]}] " if event[1] else f"[{event[0]}] ")
+    out += [category, ": ", message or ""]
+    if include_scopes and scopes:
+        out.append(" =>" + "".join(f" {k}={v}" for k, v in scopes))
+    if exception:
+        out.append("\n    " + exception)
+    return "".join(out)
+
+
 class FileLoggerProvider:
     """Owns the writer thread and the current log file."""
 
@@ -227,8 +246,13 @@ class Logger:
         except (KeyError, IndexError, ValueError):
             message = template
         exc_text = "".join(traceback.format_exception(type(exc), exc, exc.__traceback__)) if exc is not None else None
-        line = format_entry(self.provider._clock(), level, self.category, event, message, exc_text, template, props,
-                            _scope.get(), self.provider.options.include_scopes)
+        o = self.provider.options
+        if o.use_json_format:
+            line = format_entry(self.provider._clock(), level, self.category, event, message, exc_text, template, props,
+                                _scope.get(), o.include_scopes)
+        else:
+            line = format_text_line(self.provider._clock(), level, self.category, event, message, exc_text, _scope.get(),
+                                    o.include_scopes)
         self.provider.enqueue(line)
 
     def info(self, event, template, **props):

@@ -1,0 +1,121 @@
+"""``python -m tensorsharp_b200.server --model x.gguf [--backend b200|cpu] [--port 5000] ...``
+
+Parity: TensorSharp.Server/Program.cs, Hosting/StartupBanner.cs, StartupModelLoader.cs,
+LoggingSetup.cs: build the options, set up the JSONL log, print the banner, load the hosted
+model (when ``--model`` was given) and warm its kernels up, then serve.
+"""
+from __future__ import annotations
+
+import os
+import sys
+import time
+
+from ..runtime import media
+from ..runtime.logging import Ev, setup_file_logging
+from .app import ServerApp, serve
+from .options import build_options, read_configured_backend_input, try_resolve_supported_backend
+
+ENDPOINT_SUMMARY = (
+    "GET  /                         - Health check",
+    "GET  /api/tags                  - List hosted models (Ollama)",
+    "POST /api/show                  - Show model details (Ollama)",
+    "POST /api/generate              - Generate text (Ollama)",
+    "POST /api/chat/ollama           - Chat completion (Ollama)",
+    "POST /v1/chat/completions       - Chat completion (OpenAI)",
+    "GET  /v1/models                 - List hosted models (OpenAI)",
+    "POST /api/chat                  - Chat (Web UI SSE)",
+    "POST /api/models/load           - Reload hosted model (Web UI)",
+    "GET  /api/models                - Show hosted model state (Web UI)",
+)
+
+USAGE = ("No startup model configured. Launch with --model <path.gguf> --backend <type> [--mmproj <path>] "
+         "[--max-tokens 20000] [--temperature F] [--top-k N] [--top-p F] [--min-p F] [--repeat-penalty F] "
+         "[--presence-penalty F] [--frequency-penalty F] [--seed N] [--stop <text>] to use the Web UI.")
+
+
+def _fmt(v: float) -> str:
+    return ("%.3f" % v).rstrip("0").rstrip(".") or "0"
+
+
+def emit_banner(log, options, listen: str, out=sys.stdout) -> None:
+    def info(ev, template, **kw):
+        log.info(ev, template, **kw)
+        print(template.format(**kw), file=out)
+    if not options.supported_backends:
+        log.warning(Ev.BackendUnavailable, "No supported backends detected on this machine.")
+    else:
+        info(Ev.BackendDetected, "Supported backends: {SupportedBackends}",
+             SupportedBackends=", ".join(b["value"] for b in options.supported_backends))
+    info(Ev.HostConfiguration, "Server configuration: hostedModel={HostedModel} hostedMmProj={HostedMmProj} "
+         "defaultWebMaxTokens={DefaultWebMaxTokens} videoMaxFrames={VideoMaxFrames} listen={ListenAddress}",
+         HostedModel=options.startup_model_path or "(none)", HostedMmProj=options.startup_mmproj_path or "(none)",
+         DefaultWebMaxTokens=options.default_web_max_tokens, VideoMaxFrames=media.get_configured_max_video_frames(),
+         ListenAddress=listen)
+    s = options.default_sampling_config
+    info(Ev.HostConfiguration, "Default sampling: temperature={Temperature} topK={TopK} topP={TopP} minP={MinP} "
+         "repeatPenalty={RepeatPenalty} presencePenalty={PresencePenalty} frequencyPenalty={FrequencyPenalty} seed={Seed} "
+         "stopSequences={StopSequences}", Temperature=_fmt(s.temperature), TopK=s.top_k, TopP=_fmt(s.top_p),
+         MinP=_fmt(s.min_p), RepeatPenalty=_fmt(s.repetition_penalty), PresencePenalty=_fmt(s.presence_penalty),
+         FrequencyPenalty=_fmt(s.frequency_penalty), Seed=s.seed,
+         StopSequences="[" + ", ".join('"%s"' % x for x in s.stop_sequences) + "]" if s.stop_sequences else "(none)")
+    info(Ev.HostStarting, "Starting TensorSharp.Server on {ListenAddress}", ListenAddress=listen)
+    for ep in ENDPOINT_SUMMARY:
+        info(Ev.HostConfiguration, "Endpoint: {Endpoint}", Endpoint=ep)
+
+
+def load_startup_model(options, svc, configured_backend, log) -> None:
+    if not options.startup_model_path:
+        log.info(Ev.HostConfiguration, USAGE)
+        print(USAGE)
+        return
+    backend, err = try_resolve_supported_backend(options, configured_backend)
+    if err:
+        raise RuntimeError(err)
+    if not os.path.isfile(options.startup_model_path):
+        raise FileNotFoundError(f"Configured model file not found: {options.startup_model_path}")
+    if options.startup_mmproj_path and not os.path.isfile(options.startup_mmproj_path):
+        raise FileNotFoundError(f"Configured mmproj file not found: {options.startup_mmproj_path}")
+    svc.load_model(options.startup_model_path, options.startup_mmproj_path, backend)
+    log.info(Ev.ModelLoadCompleted, "Startup model loaded: {Model} architecture={Architecture} backend={Backend} mmproj={MmProj}",
+             Model=svc.loaded_model_name, Architecture=svc.architecture or "unknown", Backend=svc.loaded_backend,
+             MmProj=svc.loaded_mmproj_name or "(none)")
+    warm = getattr(svc.model, "warm_up_kernels", None)
+    if warm is not None:
+        t0 = time.perf_counter()
+        warm()
+        log.info(Ev.HostConfiguration, "Kernel warmup completed in {ElapsedMs:.1f} ms", ElapsedMs=(time.perf_counter() - t0) * 1e3)
+
+
+def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    base = os.environ.get("TENSORSHARP_BASE_DIR") or os.getcwd()
+    try:
+        options = build_options(argv, base)
+    except ValueError as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 2
+    provider = setup_file_logging(options.log_directory, prefix="tensorsharp-server", enabled=options.file_logging_enabled)
+    app = ServerApp(options, log_provider=provider)
+    log = app.logger("TensorSharp.Server")
+    listen = f"http://{options.host}:{options.port}"
+    emit_banner(log, options, listen)
+    load_startup_model(options, app.svc, read_configured_backend_input(argv), log)
+    httpd = serve(app)
+    log.info(Ev.HostStarted, "TensorSharp.Server listening on {ListenAddress}", ListenAddress=listen)
+    print(f"listening on {listen}")
+    try:
+        httpd.serve_forever()
+    except KeyboardInterrupt:
+        pass
+    finally:
+        log.info(Ev.HostStopping, "TensorSharp.Server stopping")
+        httpd.server_close()
+        app.svc.close()
+        log.info(Ev.HostStopped, "TensorSharp.Server stopped")
+        if provider is not None:
+            provider.close()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
