@@ -225,6 +225,18 @@ class ModelBase:
         if self._default_seq is not None:
             self.kv.truncate(self._default_seq, n_tokens)
 
+    def warm_up_kernels(self) -> None:
+        """Run one short prefill and one decode step so lazy initialisation (cuBLAS handles,
+        tensor maps, scratch buffers) is paid before the first request, then clear the cache
+        (ModelBase.WarmUpKernels in the reference)."""
+        n = max(1, min(8, self.max_context - 2))
+        tok = min(self.cfg.vocab - 1, 100)
+        self.forward([tok] * n)
+        self.forward([tok])
+        self.reset_kv_cache()
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+
     def close(self) -> None:
         self.gguf.close()
 

@@ -361,10 +361,9 @@ class HarmonyOutputParser(_StreamParser):
                         self.channel = "final"
                     self.state = self.BODY
                     again = bool(self.buf)
-                elif not done:
-                    h = hold_back(buf, self.T_MSG)
-                    if 0 < h < len(buf):
-                        self.buf = buf[-h:]
+                # else: keep the partial header whole until "<|message|>" arrives (the reference
+                # trims it to the held-back tag prefix, which loses the channel name when the
+                # tag itself is split across pieces)
             else:
                 sink = think if self.channel == "analysis" else content
                 i = buf.find(self.T_END)

@@ -1,0 +1,158 @@
+"""Command-line tool on CPU with the tiny synthetic model: flag parsing, every batch mode, the
+interactive session's commands and multi-turn KV reuse."""
+import io
+import json
+import os
+
+import pytest
+
+from tensorsharp_b200.cli.args import parse_cli_args
+from tensorsharp_b200.cli.interactive import InteractiveSession
+from tensorsharp_b200.cli.main import Console, describe_plan, format_parsed_result, load_tools, main
+from tensorsharp_b200.runtime.chat import ToolCall
+from tensorsharp_b200.runtime.kv_cache import ReusePlan
+from tensorsharp_b200.runtime.output_parser import ParsedOutput
+from tensorsharp_b200.runtime.sampling import SamplingConfig
+
+
+def run_cli(args):
+    out, err = io.StringIO(), io.StringIO()
+    rc = main(list(args) + ["--log-file", "off"], Console(out, err))
+    return rc, out.getvalue(), err.getvalue()
+
+
+def test_parse_cli_args_defaults_and_flags(tmp_path):
+    o = parse_cli_args([])
+    assert (o.max_tokens, o.backend, o.bench_prefill, o.bench_decode, o.bench_runs) == (100, "b200", 32, 64, 1)
+    assert (o.correct_prefill, o.correct_decode, o.bench_kv_turns) == (1500, 8, 4)
+    assert o.sampling.is_greedy and o.sampling.repetition_penalty == 1.0
+    sysf = tmp_path / "sys.txt"
+    sysf.write_text("be brief")
+    o = parse_cli_args(["--model", "m.gguf", "--backend", "CUDA", "--chat", "--temperature", "0.7", "--top-k", "5", "--stop", "a",
+                        "--stop", "b", "--think", "--bench-chunked", "--system-file", str(sysf), "--log-console", "off",
+                        "--max-tokens", "7", "--wat"])
+    assert (o.model, o.backend, o.interactive, o.think, o.bench_chunked, o.system) == ("m.gguf", "cuda", True, True, True, "be brief")
+    assert (o.sampling.temperature, o.sampling.top_k, o.sampling.stop_sequences, o.max_tokens) == (0.7, 5, ["a", "b"], 7)
+    assert not o.log_console and o.unknown == ["--wat"]
+    with pytest.raises(ValueError):
+        parse_cli_args(["--max-tokens", "x"])
+    with pytest.raises(ValueError):
+        parse_cli_args(["--model"])
+
+
+def test_formatting_helpers(tmp_path):
+    p = ParsedOutput(content="Answer", thinking=" why ", tool_calls=[ToolCall("f", {"a": 1})])
+    s = format_parsed_result(p, True)
+    assert "--- Thinking ---\nwhy\n--- End Thinking ---" in s and "Answer" in s and "Function: f" in s and '"a": 1' in s
+    assert "Thinking" not in format_parsed_result(p, False)
+    assert describe_plan(ReusePlan.reuse(30, 10), 40) == "Partial reuse: keeping 30/40 tokens, forwarding 10 new (saved 75%)"
+    assert describe_plan(ReusePlan.reset(9), 9) == "Full reset: forwarding 9 tokens"
+    assert describe_plan(ReusePlan.exact_match([1.0]), 5).startswith("Exact match: reusing all 5")
+    tf = tmp_path / "tools.json"
+    tf.write_text(json.dumps([{"Name": "get", "Description": "d", "Parameters": {"x": {"Type": "string", "Enum": ["a"]}},
+                               "Required": ["x"]},
+                              {"type": "function", "function": {"name": "g", "parameters": {"properties": {"y": {"type": "integer"}}}}}]))
+    tools = load_tools(str(tf))
+    assert tools[0].name == "get" and tools[0].parameters["x"].enum == ["a"] and tools[0].required == ["x"]
+    assert tools[1].name == "g" and tools[1].parameters["y"].type == "integer"
+
+
+def test_missing_model_prints_usage():
+    rc, out, err = run_cli(["--model", "/nonexistent.gguf"])
+    assert rc == 1 and "Model file not found" in err and "Usage:" in err
+
+
+def test_one_shot_dump_prompt_and_output_file(tiny_qwen3_path, tmp_path):
+    rc, out, _ = run_cli(["--model", tiny_qwen3_path, "--backend", "cpu", "--dump-prompt"])
+    assert rc == 0 and "<|im_start|>user\nWhat is 1+1?<|im_end|>\n<|im_start|>assistant\n===" in out
+    assert "ends with: 0x74" in out              # the Jinja result is right-trimmed, as in the reference and "Token count:" in out and "First 20 tokens: [" in out
+    inp, outp = tmp_path / "in.txt", tmp_path / "out.txt"
+    inp.write_text("Say hi\n\n")
+    rc, out, _ = run_cli(["--model", tiny_qwen3_path, "--backend", "cpu", "--input", str(inp), "--output", str(outp), "--max-tokens", "5"])
+    assert rc == 0 and f"Output written to {outp}" in out and outp.exists()
+    rc, out, _ = run_cli(["--model", tiny_qwen3_path, "--backend", "cpu", "--max-tokens", "4"])
+    assert rc == 0 and "=== Generated Output ===" in out
+
+
+def test_benchmark_modes(tiny_qwen3_path):
+    rc, out, _ = run_cli(["--model", tiny_qwen3_path, "--backend", "cpu", "--benchmark", "--bench-prefill", "16", "--bench-decode", "4",
+                          "--bench-runs", "2"])
+    assert rc == 0 and "benchmark run 2/2:" in out and "benchmark summary: bestPrefillMs=" in out and "avgDecodeTps=" in out
+    rc, out, _ = run_cli(["--model", tiny_qwen3_path, "--backend", "cpu", "--test-chunked-prefill", "--correct-prefill", "200",
+                          "--correct-decode", "4"])
+    assert rc == 0 and "matched 4/4 decode tokens -> PASS" in out
+    rc, out, _ = run_cli(["--model", tiny_qwen3_path, "--backend", "cpu", "--bench-kvcache", "--bench-kv-turns", "3", "--max-tokens", "4"])
+    assert rc == 0 and "kv bench turn 3:" in out and "kv bench summary over turns 2..3" in out
+
+
+def test_jsonl_batch_and_multi_turn(tiny_qwen3_path, tmp_path):
+    req = tmp_path / "req.jsonl"
+    req.write_text("\n".join([
+        json.dumps({"id": "a", "prompt": "Hello", "max_tokens": 3}),
+        "{broken",
+        json.dumps({"messages": [{"role": "system", "content": "s"}, {"role": "user", "content": "u"}], "temperature": 0.5, "seed": 1,
+                    "stop": ["zz"]}),
+        "", json.dumps([1, 2])]))
+    res = tmp_path / "res.jsonl"
+    rc, out, _ = run_cli(["--model", tiny_qwen3_path, "--backend", "cpu", "--input-jsonl", str(req), "--output", str(res), "--max-tokens", "4"])
+    assert rc == 0
+    rows = [json.loads(l) for l in res.read_text().splitlines()]
+    assert list(rows[0]) == ["id", "output", "tokens_generated", "prefill_ms", "total_ms", "tokens_per_second"]
+    assert rows[0]["id"] == "a" and rows[0]["tokens_generated"] <= 3
+    assert rows[1]["line"] == 2 and rows[1]["error"].startswith("Invalid JSON")
+    assert rows[2]["id"] == "request_3" and rows[2]["tokens_generated"] <= 4 and "error" in rows[3]
+    mt = tmp_path / "turns.jsonl"
+    mt.write_text("\n".join([json.dumps({"content": "first question", "max_tokens": 3}), "plain second line",
+                             json.dumps({"content": "third", "force_reset": True})]))
+    rc, out, _ = run_cli(["--model", tiny_qwen3_path, "--backend", "cpu", "--multi-turn-jsonl", str(mt), "--max-tokens", "3"])
+    assert rc == 0
+    assert "[turn 1] promptTokens=" in out and "plan=Reset" in out.split("[turn 1]")[1].split("\n")[0]
+    assert "plan=PartialReuse" in out.split("[turn 2]")[1].split("\n")[0]
+    assert "plan=Reset" in out.split("[turn 3]")[1].split("\n")[0]
+
+
+def test_self_test_and_template_scan(tiny_qwen3_path, tmp_path):
+    rc, out, _ = run_cli(["--model", tiny_qwen3_path, "--backend", "cpu", "--test", "--max-tokens", "3"])
+    assert "tokenizer OK  'Hello, world!'" in out and "template rendered" in out
+    rc, out, _ = run_cli(["--test-templates", os.path.dirname(tiny_qwen3_path)])
+    assert "[single-turn] PASS" in out and "[multi-turn] PASS" in out and "[with-system] PASS" in out
+    assert "passed=1 failed=0" in out and rc == 0
+
+
+class Script:
+    def __init__(self, lines):
+        self.lines = list(lines)
+
+    def __call__(self, prompt):
+        return self.lines.pop(0) if self.lines else None
+
+
+def test_interactive_session_commands_and_kv_reuse(tiny_qwen3_path, tmp_path):
+    from tensorsharp_b200.models.base import ModelBase
+    model = ModelBase.create(tiny_qwen3_path, "cpu")
+    note = tmp_path / "note.txt"
+    note.write_text("remember 42")
+    saved = tmp_path / "chat.txt"
+    out = io.StringIO()
+    s = InteractiveSession(model, tiny_qwen3_path, "cpu", None, SamplingConfig.greedy(), None, False, 4, console=Console(out, out),
+                           read_line=Script(["/help", "/bogus", "/temp 0.5", "/temp x", "/topk 3", "/seed 7", "/stop END", "/clearstop",
+                                             "/temp 0", "/topk 0", "/max 3", "/max -1", "/think on", "/think", "/system Be brief.",
+                                             f"/text {note}", "/image /nope.png", "/info", "hello there", "and again", "/history",
+                                             f"/save {saved}", "/multiline on", "line one", "line two", ".", "/multiline off",
+                                             "/reset", "/info", "/exit"]))
+    s.run()
+    text = out.getvalue()
+    assert "Conversation:" in text and "Unknown command: /bogus" in text and "temperature updated." in text
+    assert "Could not parse 'x' as float for temperature." in text and "Seed set to 7 (deterministic)." in text
+    assert 'Added stop sequence "END". Now 1 configured.' in text and "Cleared all stop sequences." in text
+    assert "Max tokens per reply set to 3." in text and "Could not parse '-1' as a positive integer." in text
+    assert "Thinking is now on." in text and "Thinking is now off." in text
+    assert "System prompt set (9 chars). Conversation reset." in text and "Text file attached:" in text
+    assert "Image file not found: /nope.png" in text and "Architecture: qwen3" in text and "1 text file(s)." in text
+    assert "(Reset, prefill" in text and "(PartialReuse, prefill" in text            # second turn re-used the first
+    assert "--- system ---\nBe brief." in text and "[Attached file: note.txt]\nremember 42\n[End of file]" in text
+    body = saved.read_text()
+    assert body.startswith("=== System ===\nBe brief.\n=== user ===") and body.count("=== assistant ===") == 2
+    assert "Multi-line input on" in text and "Conversation history and KV cache cleared." in text and text.rstrip().endswith("Bye.")
+    assert [m.role for m in s.history] == [] and s.kv.is_empty
+    model.close()
