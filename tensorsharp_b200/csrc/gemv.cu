@@ -15,6 +15,7 @@
 // ggml-cuda.cu:3359-3790 item (5), and the per-expert unrolled graphs of
 // TensorSharp.GGML.Native/ggml_ops_fused.cpp:1766 for the single-token case.
 #include "quant_blocks.cuh"
+#include "tp_fused.cuh"
 
 enum { ACT_NONE = 0, ACT_SWIGLU = 1, ACT_GEGLU_TANH = 2, ACT_GEGLU_ERF = 3, ACT_SWIGLU_OAI = 4,
        ACT_RELU2 = 5 };
@@ -51,6 +52,8 @@ struct GemvArgs {
     int out_f32;           // 1: float output, 0: bf16
     int act;               // GLU activation; rows [0,N/2) are gate, [N/2,N) are up
     int n_out;             // N, or N/2 with GLU
+    const TpPush* push;    // tensor-parallel exchange: store the f32 result into every rank's mailbox
+                           // instead of `out` (see tp_fused.cuh); null for an ordinary GEMV
 };
 
 // Each quantised type is split into a weight *load* (global, streaming, independent of the
@@ -319,11 +322,56 @@ __device__ __forceinline__ void dot_row(const QW& w, long row, int lane, const i
     }
 }
 
+// Row-parallel projection of a tensor-parallel layer: the result is this rank's partial sum, so
+// instead of writing it to a local tensor the warp stores it (f32) into the mailbox of every
+// rank; the last CTA then raises this rank's flag everywhere (tp_publish).  GEMM -> reduce in one
+// kernel: the NVLink stores of early rows overlap the weight streaming of later rows.
+template <int M, bool GLU>
+__device__ __forceinline__ void gemv_push_body(const GemvArgs& a, int r, int lane) {
+    const TpPush* tp = a.push;
+    const int n_out = a.n_out;
+    const int orow = blockIdx.y * M;
+    const int mv = min(M, a.M - orow);
+    float acc[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[m] = 0.f;
+    unsigned epoch = 0;
+    if (r < n_out) {
+        const int K = a.w.K, kb = K >> 5;
+        const int8_t* xq = a.xq ? a.xq + (long)orow * K : nullptr;
+        const float2* xds = a.xds ? a.xds + (long)orow * kb : nullptr;
+        const bf16* xb = a.xb ? a.xb + (long)orow * K : nullptr;
+        dot_row<M>(a.w, r, lane, xq, xds, xb, acc, mv, true);
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[m] = warp_sum(acc[m]);
+    } else {
+        pdl_wait();
+        pdl_trigger();
+    }
+    epoch = *tp->epoch_send;                        // written only by the last CTA of the previous exchange
+    if (r < n_out && lane < tp->size) {
+        // lane q stores to rank q: the peers are written in parallel, one 4-byte store per row
+        float* dst = tp->mailbox[lane] + (long)(epoch % TP_SLOTS) * tp->slot_stride + (long)tp->rank * tp->src_stride;
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            if (m >= mv) break;
+            float v = acc[m];
+            if (a.bias && tp->rank == 0) v += a.bias[r];
+            dst[(long)(orow + m) * n_out + r] = v;
+        }
+    }
+    tp_publish(tp, epoch, gridDim.x * gridDim.y);
+}
+
 template <int M, bool GLU>
 __global__ void __launch_bounds__(128) gemv_kernel(GemvArgs a) {
     const int lane = threadIdx.x & 31;
     const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int n_out = a.n_out;
+    if (a.push != nullptr) {                        // every CTA must reach the publish step
+        gemv_push_body<M, GLU>(a, r, lane);
+        return;
+    }
     if (r >= n_out) return;
     const int p = blockIdx.y;                       // problem (MoE slot) or M-chunk
     int expert = 0, xrow, orow;
@@ -435,12 +483,29 @@ static int launch_gemv(const GemvArgs& a, int problems, cudaStream_t s) {
     return TSB_OK;
 }
 
+extern "C" int tsb_gemv_push(const void* p0, const void* p1, const void* p2, const void* p3, int type, int N, int K,
+                             const void* xq, const void* xds, const void* xb, void* out, const float* bias,
+                             const void* residual, const int* ids, const float* row_scale, int M, int problems,
+                             int x_div, int out_f32, int act, const void* push, void* stream);
+
 // out = act(W x + bias) * row_scale + residual.  See GemvArgs for the meaning of each field.
 extern "C" int tsb_gemv(const void* p0, const void* p1, const void* p2, const void* p3, int type, int N, int K,
                         const void* xq, const void* xds, const void* xb, void* out, const float* bias,
                         const void* residual, const int* ids, const float* row_scale, int M, int problems,
                         int x_div, int out_f32, int act, void* stream) {
+    return tsb_gemv_push(p0, p1, p2, p3, type, N, K, xq, xds, xb, out, bias, residual, ids, row_scale, M, problems, x_div,
+                         out_f32, act, nullptr, stream);
+}
+
+// Same as tsb_gemv; with `push` != null the result goes to the tensor-parallel mailboxes (f32
+// partial sums, bias added by rank 0 only) and `out`, `residual`, `ids`, `row_scale` and GLU must
+// not be given.  The row length of the mailbox layout is N.
+extern "C" int tsb_gemv_push(const void* p0, const void* p1, const void* p2, const void* p3, int type, int N, int K,
+                             const void* xq, const void* xds, const void* xb, void* out, const float* bias,
+                             const void* residual, const int* ids, const float* row_scale, int M, int problems,
+                             int x_div, int out_f32, int act, const void* push, void* stream) {
     TSB_CHECK_ARG(N > 0 && K > 0 && M >= 0, "gemv: bad shape N=%d K=%d M=%d", N, K, M);
+    TSB_CHECK_ARG(!push || (!residual && !ids && !row_scale && act == 0), "gemv: push mode takes no residual / ids / scale / act");
     const bool q8 = type_uses_q8(type);
     TSB_CHECK_ARG(!q8 || (xq && xds), "gemv: quantised weight type %d needs int8 activations", type);
     TSB_CHECK_ARG(q8 || xb, "gemv: float weight type %d needs bf16 activations", type);
@@ -455,6 +520,7 @@ extern "C" int tsb_gemv(const void* p0, const void* p1, const void* p2, const vo
     a.out = out; a.bias = bias; a.residual = residual; a.ids = ids; a.row_scale = row_scale;
     a.M = M; a.x_div = x_div > 0 ? x_div : 1; a.out_f32 = out_f32; a.act = act;
     a.n_out = glu ? N / 2 : N;
+    a.push = (const TpPush*)push;
     return glu ? launch_gemv<true>(a, problems, (cudaStream_t)stream)
                : launch_gemv<false>(a, problems, (cudaStream_t)stream);
 }

@@ -1,0 +1,176 @@
+// Peer-memory plumbing and the consumer side of the tensor-parallel exchange (see tp_fused.cuh).
+#include "tp_fused.cuh"
+
+// ------------------------------------------------------------------------------------------
+// Symmetric allocation: plain cudaMalloc memory exported with CUDA IPC.  The caller exchanges the
+// 64-byte handles between ranks (any transport) and opens each peer's handle once.
+// ------------------------------------------------------------------------------------------
+extern "C" int tsb_symm_alloc(size_t bytes, void** out) {
+    TSB_CHECK_ARG(bytes > 0 && out, "symm_alloc: bad arguments");
+    TSB_CHECK_CUDA(cudaMalloc(out, bytes));
+    TSB_CHECK_CUDA(cudaMemset(*out, 0, bytes));
+    TSB_CHECK_CUDA(cudaDeviceSynchronize());
+    return TSB_OK;
+}
+extern "C" int tsb_symm_free(void* p) {
+    if (p) TSB_CHECK_CUDA(cudaFree(p));
+    return TSB_OK;
+}
+extern "C" int tsb_ipc_handle_bytes() { return (int)sizeof(cudaIpcMemHandle_t); }
+extern "C" int tsb_ipc_get_handle(void* p, void* handle_out) {
+    TSB_CHECK_ARG(p && handle_out, "ipc_get_handle: bad arguments");
+    TSB_CHECK_CUDA(cudaIpcGetMemHandle((cudaIpcMemHandle_t*)handle_out, p));
+    return TSB_OK;
+}
+extern "C" int tsb_ipc_open(const void* handle, void** out) {
+    TSB_CHECK_ARG(handle && out, "ipc_open: bad arguments");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    TSB_CHECK_CUDA(cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess));
+    return TSB_OK;
+}
+extern "C" int tsb_ipc_close(void* p) {
+    if (p) TSB_CHECK_CUDA(cudaIpcCloseMemHandle(p));
+    return TSB_OK;
+}
+extern "C" int tsb_tp_struct_bytes() { return (int)sizeof(TpPush); }
+
+// Fill a device-resident TpPush.  `mailboxes` / `flags` hold `size` device addresses (the local
+// one at index `rank`, peers as opened through IPC); `counters` is local memory of >= 8 words:
+// [epoch_send, epoch_recv, ticket_send, ticket_recv, status].
+extern "C" int tsb_tp_init(void* tp_dev, void* const* mailboxes, void* const* flags, void* counters, int rank, int size,
+                           long max_rows, long max_d) {
+    TSB_CHECK_ARG(tp_dev && mailboxes && flags && counters, "tp_init: null argument");
+    TSB_CHECK_ARG(size >= 1 && size <= TP_MAX_RANKS && rank >= 0 && rank < size, "tp_init: rank %d of %d", rank, size);
+    TpPush h = {};
+    for (int r = 0; r < size; ++r) {
+        h.mailbox[r] = (float*)mailboxes[r];
+        h.flags[r] = (unsigned*)flags[r];
+    }
+    unsigned* c = (unsigned*)counters;
+    h.epoch_send = c; h.epoch_recv = c + 1; h.ticket_send = c + 2; h.ticket_recv = c + 3; h.status = (int*)(c + 4);
+    h.rank = rank; h.size = size;
+    h.src_stride = max_rows * max_d;
+    h.slot_stride = h.src_stride * size;
+    TSB_CHECK_CUDA(cudaMemset(counters, 0, 8 * sizeof(unsigned)));
+    TSB_CHECK_CUDA(cudaMemcpy(tp_dev, &h, sizeof(h), cudaMemcpyHostToDevice));
+    TSB_CHECK_CUDA(cudaDeviceSynchronize());
+    return TSB_OK;
+}
+extern "C" long tsb_tp_mailbox_floats(int size, long max_rows, long max_d) { return (long)TP_SLOTS * size * max_rows * max_d; }
+
+// ------------------------------------------------------------------------------------------
+// Consumer: h[m, :] += sum over ranks of partial_r[m, :]  (rank order), then optionally
+// y = RMSNorm(h) * w as bf16 and / or as int8 groups of 32 with (scale, sum), the form the
+// quantised GEMV kernels read.  One CTA per row.
+// ------------------------------------------------------------------------------------------
+template <int NT>
+__global__ void __launch_bounds__(NT) tp_reduce_norm_kernel(const TpPush* tp, float* h, const float* w, float eps, int D,
+                                                            int rows, bf16* yb, int8_t* yq, float2* yds) {
+    __shared__ float red[32];
+    __shared__ unsigned s_epoch;
+    pdl_wait();
+    pdl_trigger();
+    const int m = blockIdx.x;
+    if (threadIdx.x == 0) s_epoch = *tp->epoch_recv;
+    __syncthreads();
+    const unsigned epoch = s_epoch;
+    const int size = tp->size;
+    if ((int)threadIdx.x < size) {
+        const unsigned* f = tp->flags[tp->rank] + threadIdx.x;
+        const unsigned long long t0 = global_timer_ns();
+        while ((int)(ld_acquire_sys(f) - (epoch + 1)) < 0) {
+            if (global_timer_ns() - t0 > TP_WAIT_NS) {
+                atomicCAS(tp->status, 0, 1 + (int)threadIdx.x);
+                break;
+            }
+            __nanosleep(64);
+        }
+    }
+    __syncthreads();
+    const float* box = tp->mailbox[tp->rank] + (long)(epoch % TP_SLOTS) * tp->slot_stride + (long)m * D;
+    float* hr = h + (long)m * D;
+    float ss = 0.f;
+    for (int i = threadIdx.x * 4; i < D; i += NT * 4) {
+        float4 v = *reinterpret_cast<const float4*>(hr + i);
+        for (int r = 0; r < size; ++r) {
+            const float4 p = __ldcg(reinterpret_cast<const float4*>(box + (long)r * tp->src_stride + i));
+            v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+        }
+        *reinterpret_cast<float4*>(hr + i) = v;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    if (w != nullptr || yb != nullptr || yq != nullptr) {
+        ss = block_sum(ss, red);
+        const float inv = rsqrtf(ss / (float)D + eps);
+        // each thread re-reads the values it wrote itself: no barrier needed.  The loop bound is
+        // uniform across the warp because the q8 group reduction shuffles over all 32 lanes.
+        for (int base = 0; base < D; base += NT * 4) {
+            const int i = base + threadIdx.x * 4;
+            const bool ok = i < D;
+            float4 n = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (ok) {
+                const float4 v = *reinterpret_cast<const float4*>(hr + i);
+                n = make_float4(v.x * inv, v.y * inv, v.z * inv, v.w * inv);
+                if (w) {
+                    const float4 g = *reinterpret_cast<const float4*>(w + i);
+                    n.x *= g.x; n.y *= g.y; n.z *= g.z; n.w *= g.w;
+                }
+                if (yb) {
+                    uint2 o;
+                    *reinterpret_cast<bf162*>(&o.x) = __floats2bfloat162_rn(n.x, n.y);
+                    *reinterpret_cast<bf162*>(&o.y) = __floats2bfloat162_rn(n.z, n.w);
+                    *reinterpret_cast<uint2*>(yb + (long)m * D + i) = o;
+                }
+            }
+            if (yq) {
+                // a group of 32 values is 8 neighbouring lanes; same convention as the RMSNorm
+                // kernel: int8 = round(n * 127 / amax), stored with (amax / 127, unrounded sum)
+                float amax = fmaxf(fmaxf(fabsf(n.x), fabsf(n.y)), fmaxf(fabsf(n.z), fabsf(n.w)));
+                float sum = n.x + n.y + n.z + n.w;
+#pragma unroll
+                for (int o = 1; o < 8; o <<= 1) {
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                    sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                }
+                if (ok) {
+                    const float qi = amax > 0.f ? 127.f / amax : 0.f;
+                    char4 q;
+                    q.x = (signed char)__float2int_rn(n.x * qi);
+                    q.y = (signed char)__float2int_rn(n.y * qi);
+                    q.z = (signed char)__float2int_rn(n.z * qi);
+                    q.w = (signed char)__float2int_rn(n.w * qi);
+                    *reinterpret_cast<char4*>(yq + (long)m * D + i) = q;
+                    if ((threadIdx.x & 7) == 0) yds[(long)m * (D >> 5) + (i >> 5)] = make_float2(amax / 127.f, sum);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned t = atomicAdd(tp->ticket_recv, 1u);
+        if (t == (unsigned)rows - 1) {
+            *tp->ticket_recv = 0;
+            *tp->epoch_recv = epoch + 1;
+        }
+    }
+}
+
+extern "C" int tsb_tp_reduce_norm(const void* tp, float* h, const float* w, float eps, int rows, int D, void* y_bf16,
+                                  void* yq, void* yds, void* stream) {
+    TSB_CHECK_ARG(tp && h && rows > 0 && D > 0, "tp_reduce_norm: bad arguments");
+    TSB_CHECK_ARG(D % 32 == 0, "tp_reduce_norm: D=%d must be a multiple of 32", D);
+    TSB_CHECK_ARG(!yq || yds, "tp_reduce_norm: q8 output needs the scale buffer");
+    // NT*4 must cover whole groups of 32 per 8 lanes; D % 32 == 0 keeps all 8 lanes of a group in range together
+    TSB_CHECK_CUDA(tsb_launch(tp_reduce_norm_kernel<256>, dim3(rows), dim3(256), 0, (cudaStream_t)stream, (const TpPush*)tp, h,
+                              w, eps, D, rows, (bf16*)y_bf16, (int8_t*)yq, (float2*)yds));
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}
+
+// Host-visible status word: 0 = every wait was satisfied.
+extern "C" int tsb_tp_status(void* counters, int* out) {
+    TSB_CHECK_ARG(counters && out, "tp_status: bad arguments");
+    TSB_CHECK_CUDA(cudaMemcpy(out, (unsigned*)counters + 4, sizeof(int), cudaMemcpyDeviceToHost));
+    return TSB_OK;
+}

@@ -88,8 +88,12 @@ class Qwen3Model(ModelBase):
         small = T <= F.GEMV_MAX_M
         mid = torch.float32 if small else torch.bfloat16
         h = F.embed(self.tok_emb, batch.tokens)
+        # Tensor-parallel small batches exchange partial sums through peer memory inside the
+        # projection and norm kernels (parallel/fused.py); everything else reduces with NCCL.
+        tpx = self.tp_exchange() if (tp and small and h.is_cuda) else None
+        a = F.norm(h, self.layers[0]["attn_norm"], c.eps, want_q8=small)
+        n_layers = len(self.layers)
         for l, L in enumerate(self.layers):
-            a = F.norm(h, L["attn_norm"], c.eps, want_q8=small)
             if "wqkv" in L:
                 qkv = F.linear(a, L["wqkv"], bias=L.get("qkv_bias"), out_dtype=mid)
                 q = qkv[:, :Hq * Dh].view(T, Hq, Dh)
@@ -103,18 +107,41 @@ class Qwen3Model(ModelBase):
                                   v_cache=self.kv.v[l], rope=self.rope, qn=L["q_norm"], kn=L["k_norm"], eps=c.eps)
             qr = self.q_post_scale(qr, batch)
             o = F.attention(qr, self.kv.k[l], self.kv.v[l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh)
-            h = self.row_parallel(F.as_act(o), L["wo"], h)
-            a = F.norm(h, L["ffn_norm"], c.eps, want_q8=small)
+            if tpx is not None:
+                tpx.linear_push(F.as_act(o), L["wo"])
+                a = tpx.reduce_norm(h, L["ffn_norm"], c.eps)
+            else:
+                h = self.row_parallel(F.as_act(o), L["wo"], h)
+                a = F.norm(h, L["ffn_norm"], c.eps, want_q8=small)
             if "gate_up" in L:
                 gu = F.linear(a, L["gate_up"], act="swiglu", out_dtype=torch.bfloat16)
             else:
                 gu = F.glu("swiglu", F.linear(a, L["gate"], out_dtype=mid), F.linear(a, L["up"], out_dtype=mid))
-            h = self.row_parallel(F.as_act(gu), L["down"], h)
+            nxt = self.layers[l + 1]["attn_norm"] if l + 1 < n_layers else None
+            if tpx is not None:
+                tpx.linear_push(F.as_act(gu), L["down"])
+                a = tpx.reduce_norm(h, nxt, c.eps, norm=nxt is not None)
+            else:
+                h = self.row_parallel(F.as_act(gu), L["down"], h)
+                a = F.norm(h, nxt, c.eps, want_q8=small) if nxt is not None else None
         if not want_logits:
             return None
         last = h[batch.last_idx].contiguous()
         a = F.norm(last, self.out_norm, c.eps, want_q8=True)
         return self.lm_head_logits(a)
+
+    def tp_exchange(self):
+        """The peer-memory exchange of this tensor-parallel group (created on first use; set
+        TSB_TP_FUSED=0 to keep the NCCL all-reduce path, which is also the baseline it is
+        measured against)."""
+        if getattr(self, "_tpx", None) is None:
+            import os
+            if os.environ.get("TSB_TP_FUSED", "1") == "0":
+                self._tpx = False
+            else:
+                from ..parallel.fused import TpExchange
+                self._tpx = TpExchange(self.comm, F.GEMV_MAX_M, self.cfg.hidden)
+        return self._tpx or None
 
     def q_post_scale(self, qr: torch.Tensor, batch: Batch) -> torch.Tensor:
         return qr

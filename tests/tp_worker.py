@@ -1,0 +1,62 @@
+"""One rank of the multi-GPU tensor-parallel checks (launched by test_tp_fused_gpu.py through
+``python -m torch.distributed.run``; not collected by pytest).  Prints one ``TPCHECK`` JSON line
+on rank 0."""
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch  # noqa: E402
+
+
+def main():
+    path = sys.argv[1]
+    from tensorsharp_b200.models.base import ModelBase
+    from tensorsharp_b200.parallel.dist import init_from_env
+    from tensorsharp_b200.runtime.engine import DecodeGraph
+    comm = init_from_env()
+    rank, world = comm.rank, comm.size
+    g = torch.Generator().manual_seed(11)
+    prompt = torch.randint(0, 4096, (9,), generator=g).tolist()
+
+    def run(model, steps=6):
+        model.reset_kv_cache()
+        out = [model.forward(prompt).float().clone()]          # 9 tokens: the small-batch (exchange) path
+        for _ in range(steps):
+            out.append(model.forward([int(out[-1].argmax())]).float().clone())
+        return torch.stack(out)
+
+    model = ModelBase.create(path, comm.device, max_context=256, max_seqs=2, tp_rank=rank, tp_size=world, comm=comm)
+    fused = run(model)
+    tpx = model.tp_exchange()
+    status = tpx.status()
+    exchanges = tpx.exchanges
+    # the same steps captured as a CUDA graph: the exchange keeps its epoch in device memory
+    model.reset_kv_cache()
+    first = int(model.forward(prompt).argmax())
+    dg = DecodeGraph(model, [model._seq()], 8)
+    dg.set_tokens([first])
+    dg.capture()
+    graph_tokens = [first]
+    for _ in range(5):
+        graph_tokens.append(int(dg.step()[0]))
+    eager_tokens = [int(x.argmax()) for x in fused[:6]]
+    status |= tpx.status()
+    model._tpx = False                                          # NCCL all-reduce path on the same weights
+    nccl = run(model)
+    res = {"world": world, "status": status, "exchanges": exchanges,
+           "fused_vs_nccl": float((fused - nccl).abs().max()), "graph_tokens": graph_tokens, "eager_tokens": eager_tokens}
+    if rank == 0:
+        single = ModelBase.create(path, comm.device, max_context=256)
+        ref = run(single)
+        res["fused_vs_single"] = float((fused - ref).abs().max())
+        res["scale"] = float(ref.abs().max())
+        print("TPCHECK " + json.dumps(res), flush=True)
+    comm.barrier()
+    torch.cuda.synchronize()
+    os._exit(0)          # skip NCCL teardown: it can block while captured graphs still hold its kernels
+
+
+if __name__ == "__main__":
+    main()
