@@ -35,20 +35,17 @@ extern "C" int tsb_ipc_close(void* p) {
 }
 extern "C" int tsb_tp_struct_bytes() { return (int)sizeof(TpPush); }
 
-// Fill a device-resident TpPush.  `mailboxes` / `flags` hold `size` device addresses (the local
-// one at index `rank`, peers as opened through IPC); `counters` is local memory of >= 8 words:
-// [epoch_send, epoch_recv, ticket_send, ticket_recv, status].
-extern "C" int tsb_tp_init(void* tp_dev, void* const* mailboxes, void* const* flags, void* counters, int rank, int size,
-                           long max_rows, long max_d) {
-    TSB_CHECK_ARG(tp_dev && mailboxes && flags && counters, "tp_init: null argument");
+// Fill a device-resident TpPush.  `mailboxes` holds `size` device addresses (the local one at
+// index `rank`, peers as opened through IPC); `counters` is local memory of >= 8 words:
+// [epoch, ticket, -, -, status].
+extern "C" int tsb_tp_init(void* tp_dev, void* const* mailboxes, void* counters, int rank, int size, long max_rows,
+                           long max_d) {
+    TSB_CHECK_ARG(tp_dev && mailboxes && counters, "tp_init: null argument");
     TSB_CHECK_ARG(size >= 1 && size <= TP_MAX_RANKS && rank >= 0 && rank < size, "tp_init: rank %d of %d", rank, size);
     TpPush h = {};
-    for (int r = 0; r < size; ++r) {
-        h.mailbox[r] = (float*)mailboxes[r];
-        h.flags[r] = (unsigned*)flags[r];
-    }
+    for (int r = 0; r < size; ++r) h.mailbox[r] = (float2*)mailboxes[r];
     unsigned* c = (unsigned*)counters;
-    h.epoch_send = c; h.epoch_recv = c + 1; h.ticket_send = c + 2; h.ticket_recv = c + 3; h.status = (int*)(c + 4);
+    h.epoch = c; h.ticket = c + 1; h.status = (int*)(c + 4);
     h.rank = rank; h.size = size;
     h.src_stride = max_rows * max_d;
     h.slot_stride = h.src_stride * size;
@@ -57,45 +54,55 @@ extern "C" int tsb_tp_init(void* tp_dev, void* const* mailboxes, void* const* fl
     TSB_CHECK_CUDA(cudaDeviceSynchronize());
     return TSB_OK;
 }
-extern "C" long tsb_tp_mailbox_floats(int size, long max_rows, long max_d) { return (long)TP_SLOTS * size * max_rows * max_d; }
+extern "C" long tsb_tp_mailbox_bytes(int size, long max_rows, long max_d) {
+    return (long)TP_SLOTS * size * max_rows * max_d * (long)sizeof(float2);
+}
 
 // ------------------------------------------------------------------------------------------
 // Consumer: h[m, :] += sum over ranks of partial_r[m, :]  (rank order), then optionally
 // y = RMSNorm(h) * w as bf16 and / or as int8 groups of 32 with (scale, sum), the form the
-// quantised GEMV kernels read.  One CTA per row.
+// quantised GEMV kernels read.  One CTA per row; the last CTA advances the epoch.
 // ------------------------------------------------------------------------------------------
 template <int NT>
 __global__ void __launch_bounds__(NT) tp_reduce_norm_kernel(const TpPush* tp, float* h, const float* w, float eps, int D,
                                                             int rows, bf16* yb, int8_t* yq, float2* yds) {
     __shared__ float red[32];
-    __shared__ unsigned s_epoch;
     pdl_wait();
     pdl_trigger();
     const int m = blockIdx.x;
-    if (threadIdx.x == 0) s_epoch = *tp->epoch_recv;
-    __syncthreads();
-    const unsigned epoch = s_epoch;
+    const unsigned epoch = *tp->epoch;              // written only by the last CTA of the previous exchange
+    const unsigned tag = epoch + 1;
     const int size = tp->size;
-    if ((int)threadIdx.x < size) {
-        const unsigned* f = tp->flags[tp->rank] + threadIdx.x;
-        const unsigned long long t0 = global_timer_ns();
-        while ((int)(ld_acquire_sys(f) - (epoch + 1)) < 0) {
-            if (global_timer_ns() - t0 > TP_WAIT_NS) {
-                atomicCAS(tp->status, 0, 1 + (int)threadIdx.x);
-                break;
-            }
-            __nanosleep(64);
-        }
-    }
-    __syncthreads();
-    const float* box = tp->mailbox[tp->rank] + (long)(epoch % TP_SLOTS) * tp->slot_stride + (long)m * D;
+    const float2* box = tp->mailbox[tp->rank] + (long)(epoch % TP_SLOTS) * tp->slot_stride + (long)m * D;
     float* hr = h + (long)m * D;
     float ss = 0.f;
     for (int i = threadIdx.x * 4; i < D; i += NT * 4) {
         float4 v = *reinterpret_cast<const float4*>(hr + i);
         for (int r = 0; r < size; ++r) {
-            const float4 p = __ldcg(reinterpret_cast<const float4*>(box + (long)r * tp->src_stride + i));
-            v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+            const float2* src = box + (long)r * tp->src_stride + i;
+            uint4 a = ld_words2(src), b = ld_words2(src + 2);
+            if (a.y != tag || a.w != tag || b.y != tag || b.w != tag) {
+                const unsigned long long t0 = global_timer_ns();
+                unsigned spins = 0;
+                bool late = false;
+                do {
+                    __nanosleep(32);
+                    a = ld_words2(src);
+                    b = ld_words2(src + 2);
+                    // a wait that already ran out anywhere on this GPU ends all the others at once
+                    if ((++spins & 63u) == 0 &&
+                        (global_timer_ns() - t0 > TP_WAIT_NS || *(volatile int*)tp->status != 0)) { late = true; break; }
+                } while (a.y != tag || a.w != tag || b.y != tag || b.w != tag);
+                if (late) {
+                    atomicCAS(tp->status, 0, 1 + r);
+                    if (a.y != tag) a.x = 0u;
+                    if (a.w != tag) a.z = 0u;
+                    if (b.y != tag) b.x = 0u;
+                    if (b.w != tag) b.z = 0u;
+                }
+            }
+            v.x += __uint_as_float(a.x); v.y += __uint_as_float(a.z);
+            v.z += __uint_as_float(b.x); v.w += __uint_as_float(b.z);
         }
         *reinterpret_cast<float4*>(hr + i) = v;
         ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
@@ -148,10 +155,11 @@ __global__ void __launch_bounds__(NT) tp_reduce_norm_kernel(const TpPush* tp, fl
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        const unsigned t = atomicAdd(tp->ticket_recv, 1u);
+        const unsigned t = atomicAdd(tp->ticket, 1u);
         if (t == (unsigned)rows - 1) {
-            *tp->ticket_recv = 0;
-            *tp->epoch_recv = epoch + 1;
+            *tp->ticket = 0;
+            __threadfence();
+            *tp->epoch = epoch + 1;
         }
     }
 }

@@ -2,20 +2,22 @@
 //
 // A row-parallel projection leaves every rank with a partial sum of the same [M, D] output.
 // Instead of handing that tensor to a collective library, the producing kernel stores its
-// partial straight into a mailbox in every rank's memory and raises a flag there; the kernel
-// that consumes the sum (residual add + RMSNorm + activation quantisation) waits for the flags
-// of all ranks, adds the partials in rank order (so every rank computes bit-identical hidden
-// states) and goes on.  A decode step therefore contains no collective call and no extra
-// launch for the reduction.  The reference has no multi-GPU path at all.
+// partial straight into a mailbox in every rank's memory; the kernel that consumes the sum
+// (residual add + RMSNorm + activation quantisation) polls its own mailbox, adds the partials in
+// rank order (so every rank computes bit-identical hidden states) and goes on.  A decode step
+// therefore contains no collective call, no fence and no extra launch for the reduction.  The
+// reference has no multi-GPU path at all.
 //
-// Protocol.  Exchanges are numbered by an epoch that both sides keep in device memory (so a
-// CUDA-graph replay needs no new arguments).  Exchange e uses mailbox slot e % TP_SLOTS.  A
-// rank cannot send e+1 before it has consumed e, and cannot consume e+1 before every rank has
-// sent it, so no rank is ever more than one exchange ahead and two slots would suffice.
-// Producer CTAs: store partials to all ranks, fence at system scope, take a ticket; the last
-// CTA publishes flag[rank] = e+1 on every rank with a release store.  Consumer: acquire-load
-// its own flags until all are >= e+1, bounded by TP_WAIT_NS; on expiry it records the rank it
-// was waiting for in `status` and carries on with what is there (nothing traps or hangs).
+// Protocol: every value travels as an 8-byte word {float value, uint32 tag} written with one
+// aligned 8-byte store, which the memory system never splits, so a reader that sees the expected
+// tag also sees the value: no flag, no memory fence, no ordering between stores is needed (the
+// scheme low-latency collectives use for small messages).  Exchanges are numbered by an epoch
+// kept in device memory (so a CUDA-graph replay needs no new arguments); exchange e is tagged
+// e + 1 and uses mailbox slot e % TP_SLOTS.  A rank cannot send e + 1 before it has consumed e,
+// and cannot consume e + 1 before every rank has sent it, so no rank is ever more than one
+// exchange ahead: a slot is rewritten at the earliest TP_SLOTS - 1 exchanges after it was read.
+// The consumer's polling is bounded by TP_WAIT_NS; on expiry it records the rank it was waiting
+// for in `status`, treats the missing values as zero and carries on (nothing traps or hangs).
 #pragma once
 #include "common.cuh"
 
@@ -24,45 +26,29 @@
 #define TP_WAIT_NS 2000000000ull
 
 struct TpPush {
-    float* mailbox[TP_MAX_RANKS];      // rank r's mailbox base as mapped here: [TP_SLOTS][size][max_rows * max_d]
-    unsigned* flags[TP_MAX_RANKS];     // rank r's flag array as mapped here: [size] last epoch sent by each source
-    unsigned* epoch_send;              // local counters
-    unsigned* epoch_recv;
-    unsigned* ticket_send;
-    unsigned* ticket_recv;
-    int* status;                       // 0, or 1 + the rank whose flag never arrived
+    float2* mailbox[TP_MAX_RANKS];     // rank r's mailbox as mapped here: [TP_SLOTS][size][max_rows * max_d] words
+    unsigned* epoch;                   // local: number of exchanges completed (advanced by the consumer)
+    unsigned* ticket;                  // local: consumer CTAs that have finished the current exchange
+    int* status;                       // local: 0, or 1 + the rank whose data never arrived
     int rank, size;
-    long src_stride;                   // floats between two sources inside a slot (= max_rows * max_d)
-    long slot_stride;                  // floats between two slots (= size * src_stride)
+    long src_stride;                   // words between two sources inside a slot (= max_rows * max_d)
+    long slot_stride;                  // words between two slots (= size * src_stride)
 };
 
 #ifdef __CUDACC__
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-    unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
 __device__ __forceinline__ unsigned long long global_timer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-// Call from every thread of the CTA after its stores to peer memory.  The last CTA of the
-// grid publishes the epoch on every rank and advances the local send counter.
-__device__ __forceinline__ void tp_publish(const TpPush* tp, unsigned epoch, unsigned n_ctas) {
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned t = atomicAdd(tp->ticket_send, 1u);
-        if (t == n_ctas - 1) {
-            __threadfence_system();
-            for (int r = 0; r < tp->size; ++r) st_release_sys(tp->flags[r] + tp->rank, epoch + 1);
-            *tp->ticket_send = 0;
-            *tp->epoch_send = epoch + 1;
-        }
-    }
+// Two neighbouring {value, tag} words in one 16-byte load that bypasses L1 (the words are written
+// by other GPUs, so a cached line could be stale for ever).
+__device__ __forceinline__ uint4 ld_words2(const float2* p) {
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_word(float2* p, float value, unsigned tag) {
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(__float_as_uint(value)), "r"(tag) : "memory");
 }
 #endif

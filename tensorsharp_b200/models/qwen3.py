@@ -88,21 +88,15 @@ class Qwen3Model(ModelBase):
         small = T <= F.GEMV_MAX_M
         mid = torch.float32 if small else torch.bfloat16
         h = F.embed(self.tok_emb, batch.tokens)
+        if h.is_cuda and T <= F.FUSED_MAX_M and F.can_fuse(h, self.layers[0].get("wqkv", self.layers[0].get("wq"))):
+            return self.forward_fused_small(h, batch, want_logits)
         # Tensor-parallel small batches exchange partial sums through peer memory inside the
         # projection and norm kernels (parallel/fused.py); everything else reduces with NCCL.
         tpx = self.tp_exchange() if (tp and small and h.is_cuda) else None
         a = F.norm(h, self.layers[0]["attn_norm"], c.eps, want_q8=small)
         n_layers = len(self.layers)
         for l, L in enumerate(self.layers):
-            if "wqkv" in L:
-                qkv = F.linear(a, L["wqkv"], bias=L.get("qkv_bias"), out_dtype=mid)
-                q = qkv[:, :Hq * Dh].view(T, Hq, Dh)
-                k = qkv[:, Hq * Dh:(Hq + Hkv) * Dh].view(T, Hkv, Dh)
-                v = qkv[:, (Hq + Hkv) * Dh:].view(T, Hkv, Dh)
-            else:
-                q = F.linear(a, L["wq"], out_dtype=mid).view(T, Hq, Dh)
-                k = F.linear(a, L["wk"], out_dtype=mid).view(T, Hkv, Dh)
-                v = F.linear(a, L["wv"], out_dtype=mid).view(T, Hkv, Dh)
+            q, k, v = self.qkv_proj(a, L, T, mid)
             qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=self.kv.k[l],
                                   v_cache=self.kv.v[l], rope=self.rope, qn=L["q_norm"], kn=L["k_norm"], eps=c.eps)
             qr = self.q_post_scale(qr, batch)
@@ -129,6 +123,78 @@ class Qwen3Model(ModelBase):
         last = h[batch.last_idx].contiguous()
         a = F.norm(last, self.out_norm, c.eps, want_q8=True)
         return self.lm_head_logits(a)
+
+    def qkv_proj(self, a, L, T: int, mid):
+        Hq, Hkv, Dh = self.Hq, self.Hkv, self.cfg.head_dim
+        if "wqkv" in L:
+            qkv = F.linear(a, L["wqkv"], bias=L.get("qkv_bias"), out_dtype=mid)
+            return (qkv[:, :Hq * Dh].view(T, Hq, Dh), qkv[:, Hq * Dh:(Hq + Hkv) * Dh].view(T, Hkv, Dh),
+                    qkv[:, (Hq + Hkv) * Dh:].view(T, Hkv, Dh))
+        return (F.linear(a, L["wq"], out_dtype=mid).view(T, Hq, Dh), F.linear(a, L["wk"], out_dtype=mid).view(T, Hkv, Dh),
+                F.linear(a, L["wv"], out_dtype=mid).view(T, Hkv, Dh))
+
+    def forward_fused_small(self, h: torch.Tensor, batch: Batch, want_logits: bool) -> Optional[torch.Tensor]:
+        """Decode-sized batches (at most ``F.FUSED_MAX_M`` rows) on CUDA: every projection does its
+        own RMSNorm / cast and activation quantisation in-kernel, so a layer is QKV, RoPE + cache
+        write, attention, o_proj, gate_up and down: no norm or quantise launches.  With tensor
+        parallelism the row-parallel projections store their partial sums into the peer mailboxes
+        and one kernel per exchange adds them to the residual stream."""
+        c = self.cfg
+        Hq, Hkv, Dh = self.Hq, self.Hkv, c.head_dim
+        T = batch.T
+        tpx = self.tp_exchange() if self.tp_size > 1 else None
+        nccl = self.tp_size > 1 and tpx is None
+        a = None                                     # normalised input left behind by an exchange
+        n_layers = len(self.layers)
+        for l, L in enumerate(self.layers):
+            def proj(w, bias=None):
+                if a is not None:
+                    return F.linear(a, w, bias=bias, out_dtype=torch.float32)
+                return F.linear_fused(h, w, norm_w=L["attn_norm"], eps=c.eps, do_norm=True, bias=bias)
+            if "wqkv" in L:
+                qkv = proj(L["wqkv"], L.get("qkv_bias"))
+                q = qkv[:, :Hq * Dh].view(T, Hq, Dh)
+                k = qkv[:, Hq * Dh:(Hq + Hkv) * Dh].view(T, Hkv, Dh)
+                v = qkv[:, (Hq + Hkv) * Dh:].view(T, Hkv, Dh)
+            else:
+                q, k, v = proj(L["wq"]).view(T, Hq, Dh), proj(L["wk"]).view(T, Hkv, Dh), proj(L["wv"]).view(T, Hkv, Dh)
+            qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=self.kv.k[l],
+                                  v_cache=self.kv.v[l], rope=self.rope, qn=L["q_norm"], kn=L["k_norm"], eps=c.eps)
+            qr = self.q_post_scale(qr, batch)
+            o = F.attention(qr, self.kv.k[l], self.kv.v[l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh).view(T, Hq * Dh)
+            if tpx is not None:
+                tpx.linear_push_fused(o, L["wo"])
+                a = tpx.reduce_norm(h, L["ffn_norm"], c.eps)
+                gu = F.linear(a, L["gate_up"], act="swiglu", out_dtype=torch.bfloat16) if "gate_up" in L else None
+            else:
+                if nccl:
+                    y = F.linear_fused(o, L["wo"])
+                    self.comm.all_reduce(y)
+                    h.add_(y)
+                else:
+                    F.linear_fused(o, L["wo"], residual=h, out=h)
+                gu = (F.linear_fused(h, L["gate_up"], norm_w=L["ffn_norm"], eps=c.eps, do_norm=True, act="swiglu",
+                                     out_dtype=torch.bfloat16) if "gate_up" in L else None)
+            if gu is None:
+                an = a if tpx is not None else F.norm(h, L["ffn_norm"], c.eps, want_q8=True)
+                gu = F.glu("swiglu", F.linear(an, L["gate"]), F.linear(an, L["up"]))
+            if tpx is not None:
+                nxt = self.layers[l + 1]["attn_norm"] if l + 1 < n_layers else None
+                tpx.linear_push_fused(gu, L["down"])
+                a = tpx.reduce_norm(h, nxt, c.eps, norm=nxt is not None)
+            elif nccl:
+                y = F.linear_fused(gu, L["down"])
+                self.comm.all_reduce(y)
+                h.add_(y)
+            else:
+                F.linear_fused(gu, L["down"], residual=h, out=h)
+        if not want_logits:
+            return None
+        last = h if batch.last_idx.numel() == T else h[batch.last_idx].contiguous()
+        logits = F.linear_fused(last, self.lm_head, norm_w=self.out_norm, eps=c.eps, do_norm=True)
+        if self.vocab_sharded:
+            logits = self.comm.all_gather_cat(logits, dim=1)
+        return logits
 
     def tp_exchange(self):
         """The peer-memory exchange of this tensor-parallel group (created on first use; set

@@ -127,6 +127,37 @@ def _ensure_q8(a: Act) -> Act:
     return a
 
 
+FUSED_MAX_M = 4       # rows handled by the GEMV with the in-kernel norm / quantise prologue
+
+
+def can_fuse(x: torch.Tensor, w: QuantWeight) -> bool:
+    """Whether ``linear_fused`` has a kernel for this input (CUDA, at most FUSED_MAX_M rows, row
+    length within the shared-memory staging limit); otherwise it runs the separate ops."""
+    import os
+    return (x.is_cuda and x.numel() // x.shape[-1] <= FUSED_MAX_M and w.K % 32 == 0 and w.K <= 10240
+            and w.experts == 1 and os.environ.get("TSB_DISABLE_FUSED_GEMV", "0") != "1")
+
+
+def linear_fused(x: torch.Tensor, w: QuantWeight, *, norm_w: Optional[torch.Tensor] = None, eps: float = 0.0,
+                 do_norm: bool = False, bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+                 out_dtype=torch.float32, act: Optional[str] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``act(RMSNorm(x) * norm_w @ w^T + bias) + residual`` (the norm only with ``do_norm``) with
+    ``x`` the f32 residual stream or a bf16 activation.  One kernel for small batches on CUDA
+    (K-1 of the kernel list fused with K-5); the separate norm / linear ops otherwise."""
+    if can_fuse(x, w):
+        x = x.contiguous()
+        kw = {"x_f32": x} if x.dtype == torch.float32 else {"x_bf16": x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)}
+        return _k().fused_gemv(w, norm_w=norm_w, eps=eps, do_norm=do_norm, out_dtype=out_dtype, bias=bias,
+                               residual=residual, act=act, out=out, **kw)
+    T = x.numel() // x.shape[-1]
+    a = norm(x, norm_w, eps, want_q8=T <= GEMV_MAX_M) if do_norm else as_act(x)
+    y = linear(a, w, bias=bias, residual=residual, out_dtype=out_dtype, act=act)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
 _scratch = {}
 
 

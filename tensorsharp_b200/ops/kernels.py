@@ -75,7 +75,7 @@ def _lib():
     lib = native.lib()
     if not _configured:
         for name in ("tsb_quantize_q8", "tsb_gemv", "tsb_rmsnorm", "tsb_qkv_rope", "tsb_glu", "tsb_gather_rows",
-                     "tsb_argmax", "tsb_rope_table", "tsb_decode_advance", "tsb_attn_decode", "tsb_attn_prefill", "tsb_gemm_bf16", "tsb_causal_conv1d", "tsb_gdn_recurrent",
+                     "tsb_argmax", "tsb_rope_table", "tsb_fused_gemv", "tsb_gemv_push", "tsb_tp_reduce_norm", "tsb_decode_advance", "tsb_attn_decode", "tsb_attn_prefill", "tsb_gemm_bf16", "tsb_causal_conv1d", "tsb_gdn_recurrent",
                      "tsb_mamba2_recurrent"):
             getattr(lib, name).restype = C.c_int
         _configured = True
@@ -112,6 +112,31 @@ def gemv(w: QuantWeight, *, xq=None, xds=None, xb=None, M: int, out_dtype=torch.
                                  _p(xq), _p(xds), _p(xb), _p(out), _p(bias), _p(residual), _p(ids), _p(row_scale),
                                  C.c_int(M), C.c_int(problems), C.c_int(x_div),
                                  C.c_int(out.dtype == torch.float32), C.c_int(a), _stream()), "gemv")
+    _count(1)
+    return out
+
+
+def fused_gemv(w: QuantWeight, *, x_f32=None, x_bf16=None, norm_w=None, eps: float = 0.0, do_norm: bool = False,
+               out_dtype=torch.float32, bias=None, residual=None, act=None, out: Optional[torch.Tensor] = None,
+               push: Optional[int] = None) -> Optional[torch.Tensor]:
+    """Decode GEMV (at most 4 rows) with RMSNorm / cast + int8 quantisation of the input done
+    inside the kernel.  ``push`` is the device address of a tensor-parallel exchange descriptor:
+    the result then goes to the mailboxes and nothing is returned."""
+    x = x_f32 if x_f32 is not None else x_bf16
+    assert x.is_cuda and x.is_contiguous() and x.shape[-1] == w.K
+    M = x.numel() // w.K
+    a = ACT[act]
+    glu = 1 <= a <= 4
+    n_out = w.N // 2 if glu else w.N
+    if push is None and out is None:
+        out = torch.empty((M, n_out), dtype=out_dtype, device=w.device)
+    ps = _planes(w)
+    lib = _lib()
+    native.check(lib.tsb_fused_gemv(ps[0], ps[1], ps[2], ps[3], C.c_int(int(w.ggml_type)), C.c_int(w.N), C.c_int(w.K),
+                                    _p(x_f32), _p(x_bf16), _p(norm_w), C.c_float(eps), C.c_int(1 if do_norm else 0),
+                                    _p(out), _p(bias), _p(residual), C.c_int(M),
+                                    C.c_int(1 if (out is None or out.dtype == torch.float32) else 0), C.c_int(a),
+                                    C.c_void_p(push) if push else None, _stream()), "fused_gemv")
     _count(1)
     return out
 

@@ -2,9 +2,9 @@
 
 ``TpExchange`` replaces "row-parallel GEMV, NCCL all-reduce, residual add, RMSNorm, activation
 quantisation" (five launches and a library collective) by two kernels of this library: the GEMV
-stores its partial sums into every rank's mailbox over NVLink as its rows finish
-(``linear_push``), and one kernel waits for the flags of all ranks, adds the partials to the
-residual stream in rank order, normalises and emits the next GEMV's quantised input
+stores its partial sums, tagged with the exchange number, into every rank's mailbox over NVLink
+as its rows finish (``linear_push``), and one kernel polls its own mailbox, adds the partials to
+the residual stream in rank order, normalises and emits the next GEMV's quantised input
 (``reduce_norm``).  The wire protocol is described in csrc/tp_fused.cuh.  Used for batches of
 up to ``max_rows`` tokens (decode and short prefill); long prefill keeps the GEMM + NCCL path.
 """
@@ -26,14 +26,12 @@ class TpExchange:
         self.comm, self.max_rows, self.max_d = comm, int(max_rows), int(max_d)
         lib = _lib()
         n = comm.size
-        floats = lib.tsb_tp_mailbox_floats(C.c_int(n), C.c_long(self.max_rows), C.c_long(self.max_d))
-        self.mail = SymmetricBuffer(comm, floats * 4)
-        self.flag = SymmetricBuffer(comm, 256)
+        self.mail = SymmetricBuffer(comm, lib.tsb_tp_mailbox_bytes(C.c_int(n), C.c_long(self.max_rows), C.c_long(self.max_d)))
         dev = comm.device
         self.counters = torch.zeros(8, dtype=torch.int32, device=dev)
         self.struct = torch.zeros(lib.tsb_tp_struct_bytes(), dtype=torch.uint8, device=dev)
         arr = C.c_void_p * n
-        native.check(lib.tsb_tp_init(C.c_void_p(self.struct.data_ptr()), arr(*self.mail.ptrs), arr(*self.flag.ptrs),
+        native.check(lib.tsb_tp_init(C.c_void_p(self.struct.data_ptr()), arr(*self.mail.ptrs),
                                      C.c_void_p(self.counters.data_ptr()), C.c_int(comm.rank), C.c_int(n),
                                      C.c_long(self.max_rows), C.c_long(self.max_d)), "tp_init")
         comm.barrier()
@@ -61,6 +59,17 @@ class TpExchange:
                                        C.c_int(1), C.c_int(1), C.c_int(1), C.c_int(0),
                                        C.c_void_p(self.struct.data_ptr()), k._stream()), "gemv_push")
         k._count(1)
+
+    def linear_push_fused(self, x: torch.Tensor, w: QuantWeight, bias: Optional[torch.Tensor] = None) -> None:
+        """``linear_push`` for at most ``F.FUSED_MAX_M`` rows of a plain bf16 / f32 activation: the
+        int8 quantisation of the input happens inside the projection kernel as well."""
+        from ..ops import functional as F
+        from ..ops import kernels as k
+        if not F.can_fuse(x, w):
+            return self.linear_push(F.as_act(x), w, bias)
+        x = x.contiguous()
+        kw = {"x_f32": x} if x.dtype == torch.float32 else {"x_bf16": x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)}
+        k.fused_gemv(w, bias=bias, push=self.struct.data_ptr(), **kw)
 
     def reduce_norm(self, h: torch.Tensor, w: Optional[torch.Tensor], eps: float, want_q8: bool = True,
                     want_bf16: bool = True, norm: bool = True) -> Optional[Act]:
@@ -93,4 +102,3 @@ class TpExchange:
     def close(self) -> None:
         torch.cuda.synchronize(self.comm.device)
         self.mail.close()
-        self.flag.close()

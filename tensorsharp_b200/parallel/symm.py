@@ -21,7 +21,7 @@ def _lib():
     for name in ("tsb_symm_alloc", "tsb_symm_free", "tsb_ipc_get_handle", "tsb_ipc_open", "tsb_ipc_close",
                  "tsb_ipc_handle_bytes", "tsb_tp_struct_bytes", "tsb_tp_init", "tsb_tp_status"):
         getattr(lib, name).restype = C.c_int
-    lib.tsb_tp_mailbox_floats.restype = C.c_long
+    lib.tsb_tp_mailbox_bytes.restype = C.c_long
     return lib
 
 

@@ -275,3 +275,51 @@ def test_argmax():
     got = K().argmax(x)
     assert got.tolist() == x.argmax(-1).tolist()
     assert got[3].item() == 5
+
+
+@pytest.mark.parametrize("t", QTYPES + FTYPES)
+@pytest.mark.parametrize("M", [1, 2, 3, 4])
+def test_fused_gemv_norm_prologue(t, M):
+    """In-kernel RMSNorm + quantise prologue against the separate norm and GEMV kernels and
+    against the fp32 reference."""
+    torch.manual_seed(21)
+    N, Kd = 205, 2560
+    w = torch.randn(N, Kd, device=DEV) * 0.05
+    h = torch.randn(M, Kd, device=DEV) * 3
+    g = torch.rand(Kd, device=DEV) + 0.5
+    qw = QuantWeight.from_float(w, t)
+    bias = torch.randn(N, device=DEV)
+    res = torch.randn(M, N, device=DEV)
+    yb, _, yq, yds = K().rmsnorm(h.clone(), g, 1e-6, want_q8=True)
+    if qw.uses_q8_activations:
+        sep = K().gemv(qw, xq=yq, xds=yds, M=M, bias=bias, residual=res)
+    else:
+        sep = K().gemv(qw, xb=yb, M=M, bias=bias, residual=res)
+    got = K().fused_gemv(qw, x_f32=h, norm_w=g, eps=1e-6, do_norm=True, bias=bias, residual=res)
+    assert rel_err(got, sep) < 2e-3, rel_err(got, sep)
+    want = ref.rmsnorm(h, g, 1e-6) @ qw.dequantize().t() + bias + res
+    assert rel_err(got, want) < 1.5e-2
+    # in place on the residual stream, as the model uses it
+    stream = res.clone()
+    K().fused_gemv(qw, x_f32=h, norm_w=g, eps=1e-6, do_norm=True, bias=bias, residual=stream, out=stream)
+    assert torch.equal(stream, got)
+
+
+@pytest.mark.parametrize("Kd", [4096, 9728, 1024 + 32])
+def test_fused_gemv_cast_prologue_and_glu(Kd):
+    torch.manual_seed(22)
+    F_, M = 120, 2
+    w = torch.randn(2 * F_, Kd, device=DEV) * 0.05
+    x = torch.randn(M, Kd, device=DEV).bfloat16()
+    t = GGMLType.Q4_K if Kd % 256 == 0 else GGMLType.Q8_0
+    qw = QuantWeight.from_float(w, t)
+    y = expected_gemv(qw, x)
+    got = K().fused_gemv(qw, x_bf16=x)
+    assert rel_err(got, y) < 1e-3
+    got = K().fused_gemv(qw, x_bf16=x, act="swiglu", out_dtype=torch.bfloat16)
+    assert got.shape == (M, F_) and got.dtype == torch.bfloat16
+    assert rel_err(got, ref.glu("swiglu", y[:, :F_], y[:, F_:])) < 8e-3
+    # unweighted norm of an f32 input
+    xf = torch.randn(M, Kd, device=DEV)
+    got = K().fused_gemv(qw, x_f32=xf, eps=1e-5, do_norm=True)
+    assert rel_err(got, ref.rmsnorm(xf, None, 1e-5) @ qw.dequantize().t()) < 1.5e-2
