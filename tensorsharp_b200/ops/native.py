@@ -93,6 +93,15 @@ def build(force: bool = False, verbose: bool = False, jobs: Optional[int] = None
     return LIB_PATH
 
 
+def is_stale() -> bool:
+    """True when a source or header differs from what the objects were compiled from."""
+    for src in sources():
+        stamp = OUT_DIR / (src.stem + ".stamp")
+        if not stamp.exists() or stamp.read_text() != _stamp(src):
+            return True
+    return False
+
+
 _lib: Optional[ctypes.CDLL] = None
 
 
@@ -100,6 +109,8 @@ def lib() -> ctypes.CDLL:
     """The loaded library; raises :class:`NativeLibraryError` if it has not been built."""
     global _lib
     if _lib is None:
+        if LIB_PATH.exists() and is_stale():
+            build()                      # sources changed since the library was linked
         if not LIB_PATH.exists():
             raise NativeLibraryError(
                 f"{LIB_PATH} is missing: run `python -c 'import __graft_entry__ as g; g.build()'` "
