@@ -122,31 +122,14 @@ struct StagePrologue {
 };
 
 template <int M, bool GLU, bool FLOATW>
-__global__ void __launch_bounds__(FG_THREADS) fused_gemv_kernel(FusedGemvArgs a) {
-    extern __shared__ __align__(16) unsigned char smem[];
-    __shared__ float red[32];
-    const int K = a.w.K;
-    int8_t* sq = reinterpret_cast<int8_t*>(smem);
-    float2* sds = reinterpret_cast<float2*>(smem + (size_t)M * K);
-    bf16* sb = reinterpret_cast<bf16*>(smem);
-    const int lane = threadIdx.x & 31;
-    const int r0 = blockIdx.x * FG_ROWS + (threadIdx.x >> 5);
+__device__ __forceinline__ void fused_epilogue(const FusedGemvArgs& a, int r, int lane, int mv, float* acc, float* acc2) {
     const int n_out = a.n_out;
-    const bool live = r0 < n_out;
-    const int r = live ? r0 : n_out - 1;             // idle warps shadow a valid row: the prologue needs every thread
-    const int mv = min(M, a.M);
-    float acc[M], acc2[M];
-#pragma unroll
-    for (int m = 0; m < M; ++m) { acc[m] = 0.f; acc2[m] = 0.f; }
-    StagePrologue<M, FLOATW> pro{a, sq, sds, sb, red};
-    dot_row<M>(a.w, r, lane, sq, sds, sb, acc, mv, pro);
-    if (GLU) dot_row<M>(a.w, (long)r + n_out, lane, sq, sds, sb, acc2, mv, PdlWait{false});
 #pragma unroll
     for (int m = 0; m < M; ++m) {
         acc[m] = warp_sum(acc[m]);
         if (GLU) acc2[m] = warp_sum(acc2[m]);
     }
-    if (!live) return;
+    if (r >= n_out) return;                          // shadow row of an idle warp
     if (a.push != nullptr) {
         const TpPush* tp = a.push;
         const unsigned epoch = *tp->epoch;
@@ -188,13 +171,61 @@ __global__ void __launch_bounds__(FG_THREADS) fused_gemv_kernel(FusedGemvArgs a)
     }
 }
 
+// The grid is sized so that every warp owns `rows_per_warp` rows, strided by the number of warps
+// in the grid: the prologue is paid once per CTA and all CTAs are resident in one wave.
+template <int M, bool GLU, bool FLOATW>
+__global__ void __launch_bounds__(FG_THREADS) fused_gemv_kernel(FusedGemvArgs a, int rows_per_warp) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ float red[32];
+    const int K = a.w.K;
+    int8_t* sq = reinterpret_cast<int8_t*>(smem);
+    float2* sds = reinterpret_cast<float2*>(smem + (size_t)M * K);
+    bf16* sb = reinterpret_cast<bf16*>(smem);
+    const int lane = threadIdx.x & 31;
+    const int stride = gridDim.x * FG_ROWS;
+    int r = blockIdx.x * FG_ROWS + (threadIdx.x >> 5);
+    const int n_out = a.n_out;
+    const int mv = min(M, a.M);
+    float acc[M], acc2[M];
+    {
+        const int row = r < n_out ? r : n_out - 1;   // idle warps shadow a valid row: the prologue needs every thread
+#pragma unroll
+        for (int m = 0; m < M; ++m) { acc[m] = 0.f; acc2[m] = 0.f; }
+        StagePrologue<M, FLOATW> pro{a, sq, sds, sb, red};
+        dot_row<M>(a.w, row, lane, sq, sds, sb, acc, mv, pro);
+        if (GLU) dot_row<M>(a.w, (long)row + n_out, lane, sq, sds, sb, acc2, mv, PdlWait{false});
+        fused_epilogue<M, GLU, FLOATW>(a, r, lane, mv, acc, acc2);
+    }
+    for (int j = 1; j < rows_per_warp; ++j) {
+        r += stride;
+        if (r >= n_out) break;
+#pragma unroll
+        for (int m = 0; m < M; ++m) { acc[m] = 0.f; acc2[m] = 0.f; }
+        dot_row<M>(a.w, r, lane, sq, sds, sb, acc, mv, PdlWait{false});
+        if (GLU) dot_row<M>(a.w, (long)r + n_out, lane, sq, sds, sb, acc2, mv, PdlWait{false});
+        fused_epilogue<M, GLU, FLOATW>(a, r, lane, mv, acc, acc2);
+    }
+}
+
+static int fused_max_ctas() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0, sms = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        n = 2 * sms;
+    }
+    return n;
+}
+
 template <int M, bool GLU, bool FLOATW>
 static int launch_fused(const FusedGemvArgs& a, cudaStream_t s) {
     const size_t smem = FLOATW ? (size_t)M * a.w.K * 2 : (size_t)M * a.w.K + (size_t)M * (a.w.K >> 5) * 8;
     auto kern = fused_gemv_kernel<M, GLU, FLOATW>;
     if (smem > 48 * 1024) TSB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    dim3 grid((a.n_out + FG_ROWS - 1) / FG_ROWS);
-    TSB_CHECK_CUDA(tsb_launch(kern, grid, dim3(FG_THREADS), smem, s, a));
+    const int blocks = (a.n_out + FG_ROWS - 1) / FG_ROWS;
+    const int rpw = (blocks + fused_max_ctas() - 1) / fused_max_ctas();
+    dim3 grid((blocks + rpw - 1) / rpw);
+    TSB_CHECK_CUDA(tsb_launch(kern, grid, dim3(FG_THREADS), smem, s, a, rpw));
     TSB_CHECK_LAUNCH();
     return TSB_OK;
 }

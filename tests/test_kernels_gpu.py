@@ -315,11 +315,11 @@ def test_fused_gemv_cast_prologue_and_glu(Kd):
     qw = QuantWeight.from_float(w, t)
     y = expected_gemv(qw, x)
     got = K().fused_gemv(qw, x_bf16=x)
-    assert rel_err(got, y) < 1e-3
+    assert rel_err(got, y) < 2e-3
     got = K().fused_gemv(qw, x_bf16=x, act="swiglu", out_dtype=torch.bfloat16)
     assert got.shape == (M, F_) and got.dtype == torch.bfloat16
     assert rel_err(got, ref.glu("swiglu", y[:, :F_], y[:, F_:])) < 8e-3
     # unweighted norm of an f32 input
     xf = torch.randn(M, Kd, device=DEV)
     got = K().fused_gemv(qw, x_f32=xf, eps=1e-5, do_norm=True)
-    assert rel_err(got, ref.rmsnorm(xf, None, 1e-5) @ qw.dequantize().t()) < 1.5e-2
+    assert rel_err(got, ref.rmsnorm(xf, None, 1e-5) @ qw.dequantize().t()) < 3e-2
