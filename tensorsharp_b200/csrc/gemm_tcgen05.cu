@@ -19,6 +19,7 @@
 #include <cudaTypedefs.h>
 #include <mutex>
 #include "tcgen05.cuh"
+#include "tp_fused.cuh"
 
 struct GemmEpi {
     void* out;              // [T, ldo]
@@ -27,6 +28,10 @@ struct GemmEpi {
     long ldo;
     int T, N;               // valid tokens, valid features
     int out_f32;
+    // Tensor-parallel prefill (tp_fused.cuh); both null for an ordinary GEMM.
+    const TpSeq* rs;        // GEMM -> reduce-scatter: add the tile into the token owner's accumulator over NVLink
+    const TpSeq* ag;        // all-gather -> GEMM: X is the gathered buffer; wait for the tile's shard to arrive
+    int rs_rows;            // size * shard (host copy, for the grid)
 };
 
 template <int BN, int STAGES>
@@ -76,6 +81,14 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
         if (lane == 0) {
             tc::tma_prefetch_desc(&tmW);
             tc::tma_prefetch_desc(&tmX);
+            if (ep.ag != nullptr) {
+                // the rows of this token tile come from one rank; its stores are complete once its
+                // arrival counter here has reached the target left by the preceding gather kernel
+                const TpSeq* g = ep.ag;
+                const int owner = n0 / g->shard;
+                if (owner < g->size && !tp_wait_counter(g->ag_arrive[g->rank] + owner, *g->ag_target))
+                    atomicExch(status, 4);
+            }
             for (int kb = 0; kb < kblocks; ++kb) {
                 const int s = kb % STAGES;
                 const uint32_t ph = (kb / STAGES) & 1;
@@ -111,13 +124,29 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
         const int n = m0 + q * 32 + lane;             // feature owned by this thread
         if (tc::mbar_wait(acc_bar, 0)) {
             tc::fence_after_sync();
-            const float bias = (ep.bias && n < ep.N) ? ep.bias[n] : 0.f;
+            const float bias = (ep.bias && n < ep.N && (ep.rs == nullptr || ep.rs->rank == 0)) ? ep.bias[n] : 0.f;
+            float* rs_dst = nullptr;
+            if (ep.rs != nullptr) {
+                const TpSeq* g = ep.rs;
+                const int owner = n0 / g->shard;                    // a token tile never straddles two shards
+                if (owner < g->size)
+                    rs_dst = g->acc[owner] + (long)(*g->rs_phase & 1u) * g->shard * g->ld - (long)owner * g->shard * g->ld;
+            }
 #pragma unroll 1
             for (int c = 0; c < BN / 16; ++c) {
                 uint32_t r[16];
                 tc::tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + c * 16, r);
                 tc::tmem_ld_wait();
-                if (n < ep.N) {
+                if (rs_dst != nullptr) {
+                    if (n < ep.N) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int t = n0 + c * 16 + j;
+                            // a warp covers 32 consecutive features of one token: one 128-byte reduction packet
+                            if (t < ep.T) red_add_f32_sys(rs_dst + (long)t * ep.rs->ld + n, __uint_as_float(r[j]) + bias);
+                        }
+                    }
+                } else if (n < ep.N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int t = n0 + c * 16 + j;
@@ -138,12 +167,25 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
         } else {
             atomicExch(status, 3);
         }
+        if (ep.rs != nullptr) __threadfence_system();               // reductions visible before the arrival below
     }
     tc::fence_before_sync();
     __syncthreads();
     if (warp == 1) {
         tc::fence_after_sync();
         tc::tmem_dealloc<TMEM_COLS>(tmem_base);
+    }
+    if (ep.rs != nullptr && threadIdx.x == 0) {
+        const TpSeq* g = ep.rs;
+        const int owner = n0 / g->shard;
+        if (owner < g->size) red_release_inc_sys(g->rs_arrive[owner]);
+        const unsigned done = atomicAdd(g->ticket, 1u);
+        if (done == gridDim.x * gridDim.y - 1) {
+            // every owner receives (feature tiles) x (token tiles per shard) arrivals from each rank
+            *g->ticket = 0;
+            __threadfence();
+            *g->rs_target += (unsigned)g->size * gridDim.x * (unsigned)(g->shard / BN);
+        }
     }
 }
 
@@ -194,26 +236,47 @@ static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmE
                                             L::TOTAL));
         configured = true;
     }
-    dim3 grid((ep.N + 127) / 128, (ep.T + BN - 1) / BN);
+    // with a reduce-scatter epilogue the grid also covers the padding rows of the last shard, so
+    // that every owner sees the same number of arrivals
+    const int t_cover = ep.rs != nullptr ? ep.rs_rows : ep.T;
+    dim3 grid((ep.N + 127) / 128, (t_cover + BN - 1) / BN);
     TSB_CHECK_CUDA(tsb_launch(gemm_bf16_kernel<BN, STAGES>, grid, dim3(192), (size_t)L::TOTAL, s, tw, tx, ep, K, status));
     return TSB_OK;
 }
 
 // W: [N, K] bf16 row-major (ldw elements per row); X: [T, K] bf16 (ldx); out: [T, ldo].
 // `status` is a device int the kernel sets non-zero if one of its bounded waits gave up.
+extern "C" int tsb_gemm_bf16_tp(const void* W, long ldw, const void* X, long ldx, void* out, long ldo, int out_f32,
+                                const float* bias, const void* residual, int T, int N, int K, const void* rs,
+                                const void* ag, int shard, int size, int* status, void* stream);
+
 extern "C" int tsb_gemm_bf16(const void* W, long ldw, const void* X, long ldx, void* out, long ldo, int out_f32,
                              const float* bias, const void* residual, int T, int N, int K, int* status, void* stream) {
+    return tsb_gemm_bf16_tp(W, ldw, X, ldx, out, ldo, out_f32, bias, residual, T, N, K, nullptr, nullptr, 0, 1, status,
+                            stream);
+}
+
+// The GEMM with the tensor-parallel prefill hooks: `rs` (device TpSeq*) sends the result to the token
+// owners' accumulators instead of `out`; `ag` makes the producer wait for X's shards.  `shard` and
+// `size` repeat the descriptor's values for the host-side launch arithmetic; the token tile is
+// 128 rows so that it divides the shard.
+extern "C" int tsb_gemm_bf16_tp(const void* W, long ldw, const void* X, long ldx, void* out, long ldo, int out_f32,
+                                const float* bias, const void* residual, int T, int N, int K, const void* rs,
+                                const void* ag, int shard, int size, int* status, void* stream) {
     TSB_CHECK_ARG(T >= 0 && N > 0 && K > 0, "gemm_bf16: bad shape T=%d N=%d K=%d", T, N, K);
+    TSB_CHECK_ARG((!rs && !ag) || (shard > 0 && shard % 128 == 0 && size >= 1), "gemm_bf16: shard=%d must be a multiple of 128", shard);
+    TSB_CHECK_ARG(!rs || !residual, "gemm_bf16: reduce-scatter mode takes no residual");
     TSB_CHECK_ARG(K % 8 == 0 && ldw % 8 == 0 && ldx % 8 == 0, "gemm_bf16: K, ldw, ldx must be multiples of 8");
     TSB_CHECK_ARG(status != nullptr, "gemm_bf16: status word is required");
     if (T == 0) return TSB_OK;
-    const int bn = T <= 32 ? 32 : (T <= 64 ? 64 : (T <= 128 ? 128 : 256));
+    int bn = T <= 32 ? 32 : (T <= 64 ? 64 : (T <= 128 ? 128 : 256));
+    if (rs || ag) bn = 128;
     CUtensorMap tw, tx;
     int rc = tsb_make_tmap_2d_bf16(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 128, 64);
     if (rc) return rc;
     rc = tsb_make_tmap_2d_bf16(&tx, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, (uint32_t)bn, 64);
     if (rc) return rc;
-    GemmEpi ep{out, bias, residual, ldo, T, N, out_f32};
+    GemmEpi ep{out, bias, residual, ldo, T, N, out_f32, (const TpSeq*)rs, (const TpSeq*)ag, shard * size};
     cudaStream_t s = (cudaStream_t)stream;
     switch (bn) {
     case 32: return launch_gemm<32, 8>(tw, tx, ep, K, status, s);

@@ -182,3 +182,126 @@ extern "C" int tsb_tp_status(void* counters, int* out) {
     TSB_CHECK_CUDA(cudaMemcpy(out, (unsigned*)counters + 4, sizeof(int), cudaMemcpyDeviceToHost));
     return TSB_OK;
 }
+
+// ==========================================================================================
+// Sequence-parallel prefill (TpSeq, tp_fused.cuh)
+// ==========================================================================================
+extern "C" int tsb_tpseq_struct_bytes() { return (int)sizeof(TpSeq); }
+
+// Layout of one rank's symmetric region, in bytes from its base:
+//   [0, 256)                      counters: rs_arrive at +0, ag_arrive[size] at +64
+//   [256, 256 + 2*shard*ld*4)     the two f32 accumulators
+//   then                          xfull: size*shard*ld bf16
+extern "C" long tsb_tpseq_region_bytes(int size, int shard, long ld) {
+    return 256 + 2L * shard * ld * 4 + (long)size * shard * ld * 2;
+}
+
+// `regions` holds `size` device addresses of the symmetric regions (local one at index rank);
+// `local` is private device memory of >= 16 words: [rs_target, ag_target, rs_phase, -, ticket0,
+// ticket1, -, -, status].
+extern "C" int tsb_tpseq_init(void* dev_struct, void* const* regions, void* local, int rank, int size, int shard, long ld) {
+    TSB_CHECK_ARG(dev_struct && regions && local, "tpseq_init: null argument");
+    TSB_CHECK_ARG(size >= 1 && size <= TP_MAX_RANKS && rank >= 0 && rank < size, "tpseq_init: rank %d of %d", rank, size);
+    TSB_CHECK_ARG(shard > 0 && shard % 128 == 0 && ld > 0 && ld % 8 == 0, "tpseq_init: shard=%d ld=%ld", shard, ld);
+    TpSeq h = {};
+    for (int r = 0; r < size; ++r) {
+        unsigned char* base = (unsigned char*)regions[r];
+        h.rs_arrive[r] = (unsigned*)base;
+        h.ag_arrive[r] = (unsigned*)(base + 64);
+        h.acc[r] = (float*)(base + 256);
+        h.xfull[r] = (bf16*)(base + 256 + 2L * shard * ld * 4);
+    }
+    unsigned* c = (unsigned*)local;
+    h.rs_target = c; h.ag_target = c + 1; h.rs_phase = c + 2; h.ticket = c + 4; h.status = (int*)(c + 8);
+    h.rank = rank; h.size = size; h.shard = shard; h.ld = ld;
+    TSB_CHECK_CUDA(cudaMemset(local, 0, 16 * sizeof(unsigned)));
+    TSB_CHECK_CUDA(cudaMemcpy(dev_struct, &h, sizeof(h), cudaMemcpyHostToDevice));
+    TSB_CHECK_CUDA(cudaDeviceSynchronize());
+    return TSB_OK;
+}
+
+// One CTA per row of this rank's shard:
+//   has_acc: wait for the reduce-scatter arrivals, h[r] += acc[phase][r], clear the accumulator row
+//   then     y = RMSNorm(h[r]) * w  (bf16) stored into row (rank * shard + r) of every rank's gathered
+//            buffer, and one arrival per destination.
+// The last CTA advances the all-gather target (and the reduction phase).
+template <int NT>
+__global__ void __launch_bounds__(NT) tp_seq_norm_gather_kernel(const TpSeq* g, float* h, const float* w, float eps,
+                                                                int has_acc) {
+    __shared__ float red[32];
+    __shared__ int s_ok;
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.x, D = (int)g->ld;
+    const unsigned phase = *g->rs_phase;
+    if (has_acc) {
+        if (threadIdx.x == 0) {
+            s_ok = tp_wait_counter(g->rs_arrive[g->rank], *g->rs_target) ? 1 : 0;
+            if (!s_ok) atomicCAS(g->status, 0, 10);
+        }
+        __syncthreads();
+    }
+    float* hr = h + (long)r * D;
+    float* ar = g->acc[g->rank] + (long)(phase & 1u) * g->shard * D + (long)r * D;
+    float ss = 0.f;
+    for (int i = threadIdx.x * 4; i < D; i += NT * 4) {
+        float4 v = *reinterpret_cast<const float4*>(hr + i);
+        if (has_acc) {
+            const float4 a = __ldcg(reinterpret_cast<const float4*>(ar + i));   // written by remote reductions: skip L1
+            v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+            *reinterpret_cast<float4*>(hr + i) = v;
+            *reinterpret_cast<float4*>(ar + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)D + eps);
+    const long grow = (long)g->rank * g->shard + r;
+    for (int i = threadIdx.x * 8; i < D; i += NT * 8) {
+        const float4 a = *reinterpret_cast<const float4*>(hr + i), b = *reinterpret_cast<const float4*>(hr + i + 4);
+        float4 ga = make_float4(1.f, 1.f, 1.f, 1.f), gb = ga;
+        if (w) { ga = *reinterpret_cast<const float4*>(w + i); gb = *reinterpret_cast<const float4*>(w + i + 4); }
+        uint4 o;
+        *reinterpret_cast<bf162*>(&o.x) = __floats2bfloat162_rn(a.x * inv * ga.x, a.y * inv * ga.y);
+        *reinterpret_cast<bf162*>(&o.y) = __floats2bfloat162_rn(a.z * inv * ga.z, a.w * inv * ga.w);
+        *reinterpret_cast<bf162*>(&o.z) = __floats2bfloat162_rn(b.x * inv * gb.x, b.y * inv * gb.y);
+        *reinterpret_cast<bf162*>(&o.w) = __floats2bfloat162_rn(b.z * inv * gb.z, b.w * inv * gb.w);
+        for (int p = 0; p < g->size; ++p) *reinterpret_cast<uint4*>(g->xfull[p] + grow * D + i) = o;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int p = 0; p < g->size; ++p) red_release_inc_sys(g->ag_arrive[p] + g->rank);
+        const unsigned done = atomicAdd(g->ticket + 1, 1u);
+        if (done == gridDim.x - 1) {
+            g->ticket[1] = 0;
+            __threadfence();
+            *g->ag_target += gridDim.x;
+            if (has_acc) *g->rs_phase = phase + 1;
+        }
+    }
+}
+
+extern "C" int tsb_tpseq_norm_gather(const void* g, float* h_shard, const float* w, float eps, int shard, int D, int has_acc,
+                                     void* stream) {
+    TSB_CHECK_ARG(g && h_shard && shard > 0 && D > 0 && D % 8 == 0, "tpseq_norm_gather: bad arguments");
+    TSB_CHECK_CUDA(tsb_launch(tp_seq_norm_gather_kernel<256>, dim3(shard), dim3(256), 0, (cudaStream_t)stream,
+                              (const TpSeq*)g, h_shard, w, eps, has_acc));
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}
+
+// Wait (bounded) until every rank's gathered rows have arrived: for consumers of the gathered
+// buffer that are not the GEMM above (for example the vocabulary projection of the last row).
+__global__ void tp_seq_wait_all_kernel(const TpSeq* g) {
+    pdl_wait();
+    pdl_trigger();
+    if ((int)threadIdx.x < g->size && !tp_wait_counter(g->ag_arrive[g->rank] + threadIdx.x, *g->ag_target))
+        atomicCAS(g->status, 0, 20 + (int)threadIdx.x);
+}
+extern "C" int tsb_tpseq_wait_all(const void* g, void* stream) {
+    TSB_CHECK_ARG(g, "tpseq_wait_all: null descriptor");
+    TSB_CHECK_CUDA(tsb_launch(tp_seq_wait_all_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, (const TpSeq*)g));
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}

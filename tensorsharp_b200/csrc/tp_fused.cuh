@@ -35,7 +35,47 @@ struct TpPush {
     long slot_stride;                  // words between two slots (= size * src_stride)
 };
 
+// Sequence-parallel prefill: tokens are dealt to ranks in contiguous shards of `shard` rows.
+//  * GEMM -> reduce-scatter: the epilogue of a row-parallel GEMM adds each output tile, with f32
+//    reductions over NVLink, into the accumulator of the rank that owns the tile's tokens, then
+//    bumps that rank's arrival counter (one release per CTA).
+//  * The owner waits for `size x tiles` arrivals, folds the sum into its shard of the residual
+//    stream, normalises, and stores the bf16 rows into every rank's gathered buffer (all-gather),
+//    bumping the per-source arrival counter there.
+//  * All-gather -> GEMM: the TMA producer of the next (column-parallel) GEMM waits, per token
+//    tile, only for the shard that tile belongs to, so tiles of early shards start at once.
+// Counters only ever grow; the targets to wait for live in local device memory and are advanced
+// by the kernel that precedes the waiter in stream order, so graph replays need no new arguments.
+// Two accumulators alternate, so a fast rank's next reduction never lands in rows being read.
+struct TpSeq {
+    float* acc[TP_MAX_RANKS];            // rank r's accumulators as mapped here: [2][shard * ld] f32
+    unsigned* rs_arrive[TP_MAX_RANKS];   // rank r's reduce-scatter arrival counter (one word)
+    bf16* xfull[TP_MAX_RANKS];           // rank r's gathered activations: [size * shard, ld] bf16
+    unsigned* ag_arrive[TP_MAX_RANKS];   // rank r's all-gather arrival counters: [size], one per source
+    unsigned* rs_target;                 // local: arrivals the next consumer must see
+    unsigned* ag_target;                 // local: per-source arrivals the next GEMM must see
+    unsigned* rs_phase;                  // local: reductions consumed so far (parity picks the accumulator)
+    unsigned* ticket;                    // local: [0] GEMM CTAs done, [1] consumer CTAs done
+    int* status;                         // local: 0, or a code telling which wait ran out
+    int rank, size, shard;
+    long ld;                             // row length of acc / xfull (the hidden size)
+};
+
 #ifdef __CUDACC__
+__device__ __forceinline__ void red_add_f32_sys(float* p, float v) {
+    asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+__device__ __forceinline__ void red_release_inc_sys(unsigned* p) {
+    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns();
+// Spin until *p - target >= 0 (wrap-safe) or TP_WAIT_NS has passed; false on expiry.
+__device__ __forceinline__ bool tp_wait_counter(const unsigned* p, unsigned target);
 __device__ __forceinline__ unsigned long long global_timer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -47,6 +87,16 @@ __device__ __forceinline__ uint4 ld_words2(const float2* p) {
     uint4 v;
     asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
+}
+__device__ __forceinline__ bool tp_wait_counter(const unsigned* p, unsigned target) {
+    if ((int)(ld_acquire_sys_u32(p) - target) >= 0) return true;
+    const unsigned long long t0 = global_timer_ns();
+    unsigned spins = 0;
+    while ((int)(ld_acquire_sys_u32(p) - target) < 0) {
+        __nanosleep(64);
+        if ((++spins & 63u) == 0 && global_timer_ns() - t0 > TP_WAIT_NS) return false;
+    }
+    return true;
 }
 __device__ __forceinline__ void st_word(float2* p, float value, unsigned tag) {
     asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(__float_as_uint(value)), "r"(tag) : "memory");

@@ -90,6 +90,10 @@ class Qwen3Model(ModelBase):
         h = F.embed(self.tok_emb, batch.tokens)
         if h.is_cuda and T <= F.FUSED_MAX_M and F.can_fuse(h, self.layers[0].get("wqkv", self.layers[0].get("wq"))):
             return self.forward_fused_small(h, batch, want_logits)
+        if tp and not small and h.is_cuda and "wqkv" in self.layers[0] and "gate_up" in self.layers[0]:
+            sp = self.tp_seq(T)
+            if sp is not None:
+                return self.forward_seq_parallel(h, batch, want_logits, sp)
         # Tensor-parallel small batches exchange partial sums through peer memory inside the
         # projection and norm kernels (parallel/fused.py); everything else reduces with NCCL.
         tpx = self.tp_exchange() if (tp and small and h.is_cuda) else None
@@ -195,6 +199,57 @@ class Qwen3Model(ModelBase):
         if self.vocab_sharded:
             logits = self.comm.all_gather_cat(logits, dim=1)
         return logits
+
+    def tp_seq(self, T: int):
+        """The sequence-parallel prefill exchange, sized for at least ``T`` tokens (TSB_TP_FUSED=0
+        keeps the GEMM + NCCL all-reduce path, the baseline it is measured against)."""
+        import os
+        if os.environ.get("TSB_TP_FUSED", "1") == "0":
+            return None
+        sp = getattr(self, "_tpseq", None)
+        if sp is None or sp.shard * self.tp_size < T:
+            if sp is not None:
+                sp.close()
+            from ..parallel.fused import TpSeqParallel
+            self._tpseq = sp = TpSeqParallel(self.comm, max(T, 4096), self.cfg.hidden)
+        return sp
+
+    def forward_seq_parallel(self, h_all: torch.Tensor, batch: Batch, want_logits: bool, sp) -> Optional[torch.Tensor]:
+        """Tensor-parallel prefill with the collectives inside the kernels: every rank keeps only its
+        shard of the residual stream; o_proj and down reduce straight into the token owners'
+        accumulators from the GEMM epilogue, the owner's norm kernel scatters the normalised rows to
+        all ranks, and the QKV / gate_up GEMMs start each token tile when its shard has landed."""
+        c = self.cfg
+        Hq, Hkv, Dh = self.Hq, self.Hkv, c.head_dim
+        T = batch.T
+        r0 = self.tp_rank * sp.shard
+        mine = max(0, min(T, r0 + sp.shard) - r0)
+        h = torch.zeros((sp.shard, c.hidden), dtype=torch.float32, device=h_all.device)
+        if mine:
+            h[:mine].copy_(h_all[r0:r0 + mine])
+        sp.norm_gather(h, self.layers[0]["attn_norm"], c.eps, False)
+        n_layers = len(self.layers)
+        for l, L in enumerate(self.layers):
+            qkv = sp.gemm_ag(L["wqkv"], T, bias=L.get("qkv_bias"))
+            q = qkv[:, :Hq * Dh].view(T, Hq, Dh)
+            k = qkv[:, Hq * Dh:(Hq + Hkv) * Dh].view(T, Hkv, Dh)
+            v = qkv[:, (Hq + Hkv) * Dh:].view(T, Hkv, Dh)
+            qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=self.kv.k[l],
+                                  v_cache=self.kv.v[l], rope=self.rope, qn=L["q_norm"], kn=L["k_norm"], eps=c.eps)
+            qr = self.q_post_scale(qr, batch)
+            o = F.attention(qr, self.kv.k[l], self.kv.v[l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh)
+            sp.gemm_rs(o.view(T, Hq * Dh), L["wo"])
+            sp.norm_gather(h, L["ffn_norm"], c.eps, True)
+            y = sp.gemm_ag(L["gate_up"], T)
+            half = L["gate_up"].N // 2
+            gu = F.glu("swiglu", y[:, :half], y[:, half:])
+            sp.gemm_rs(gu, L["down"])
+            sp.norm_gather(h, self.layers[l + 1]["attn_norm"] if l + 1 < n_layers else self.out_norm, c.eps, True)
+        if not want_logits:
+            return None
+        sp.wait_all()
+        last = sp.xfull[batch.last_idx].contiguous()       # already normalised with the output norm
+        return self.lm_head_logits(F.Act(last))
 
     def tp_exchange(self):
         """The peer-memory exchange of this tensor-parallel group (created on first use; set

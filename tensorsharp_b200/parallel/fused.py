@@ -102,3 +102,104 @@ class TpExchange:
     def close(self) -> None:
         torch.cuda.synchronize(self.comm.device)
         self.mail.close()
+
+
+def tensor_from_ptr(ptr: int, shape, dtype: torch.dtype, device) -> torch.Tensor:
+    """A tensor aliasing raw device memory owned by someone else (the symmetric region)."""
+    esize = torch.empty((), dtype=dtype).element_size()
+    n = 1
+    for d in shape:
+        n *= int(d)
+
+    class _Raw:
+        __cuda_array_interface__ = {"shape": (n * esize,), "typestr": "|u1", "data": (int(ptr), False), "version": 3,
+                                    "strides": None}
+    return torch.as_tensor(_Raw(), device=device).view(dtype).view(*shape)
+
+
+class TpSeqParallel:
+    """Sequence-parallel prefill exchange (csrc/tp_fused.cuh, TpSeq): tokens are dealt to ranks in
+    shards of ``shard`` rows (a multiple of the GEMM's 128-token tile).
+
+    * ``gemm_rs``  row-parallel GEMM whose epilogue reduces every tile into the token owner's
+      accumulator over NVLink (GEMM -> reduce-scatter in one kernel),
+    * ``norm_gather``  the owner folds the sum into its shard of the residual stream, normalises and
+      stores the rows into every rank's gathered buffer (all-gather inside the norm kernel),
+    * ``gemm_ag``  column-parallel GEMM on the gathered buffer whose TMA producer waits per token
+      tile for the shard it needs (all-gather -> GEMM).
+    """
+
+    def __init__(self, comm, max_tokens: int, hidden: int):
+        self.comm, self.hidden = comm, int(hidden)
+        n = comm.size
+        self.shard = ((max_tokens + n - 1) // n + 127) // 128 * 128
+        lib = _lib()
+        for name in ("tsb_tpseq_struct_bytes", "tsb_tpseq_init", "tsb_tpseq_norm_gather", "tsb_tpseq_wait_all",
+                     "tsb_gemm_bf16_tp"):
+            getattr(lib, name).restype = C.c_int
+        lib.tsb_tpseq_region_bytes.restype = C.c_long
+        self.region = SymmetricBuffer(comm, lib.tsb_tpseq_region_bytes(C.c_int(n), C.c_int(self.shard), C.c_long(self.hidden)))
+        dev = comm.device
+        self.local = torch.zeros(16, dtype=torch.int32, device=dev)
+        self.struct = torch.zeros(lib.tsb_tpseq_struct_bytes(), dtype=torch.uint8, device=dev)
+        arr = C.c_void_p * n
+        native.check(lib.tsb_tpseq_init(C.c_void_p(self.struct.data_ptr()), arr(*self.region.ptrs),
+                                        C.c_void_p(self.local.data_ptr()), C.c_int(comm.rank), C.c_int(n),
+                                        C.c_int(self.shard), C.c_long(self.hidden)), "tpseq_init")
+        xoff = 256 + 2 * self.shard * self.hidden * 4
+        self.xfull = tensor_from_ptr(self.region.local + xoff, (n * self.shard, self.hidden), torch.bfloat16, dev)
+        comm.barrier()
+
+    @property
+    def rows(self) -> slice:
+        """This rank's rows of the token dimension."""
+        return slice(self.comm.rank * self.shard, (self.comm.rank + 1) * self.shard)
+
+    def _gemm(self, W: torch.Tensor, X: torch.Tensor, out, bias, T: int, rs: bool, ag: bool):
+        from ..ops import kernels as k
+        lib = k._lib()
+        N, K = W.shape
+        sp = C.c_void_p(self.struct.data_ptr())
+        native.check(lib.tsb_gemm_bf16_tp(k._p(W), C.c_long(W.stride(0)), k._p(X), C.c_long(X.stride(0)), k._p(out),
+                                          C.c_long(out.stride(0) if out is not None else 0),
+                                          C.c_int(1 if (out is None or out.dtype == torch.float32) else 0), k._p(bias), None,
+                                          C.c_int(T), C.c_int(N), C.c_int(K), sp if rs else None, sp if ag else None,
+                                          C.c_int(self.shard), C.c_int(self.comm.size), k._p(k.gemm_status(X.device)),
+                                          k._stream()), "gemm_bf16_tp")
+        k._count(1)
+
+    def gemm_rs(self, x: torch.Tensor, w: QuantWeight, bias: Optional[torch.Tensor] = None) -> None:
+        """Partial ``x @ w^T`` of this rank, reduced into the token owners' accumulators."""
+        from ..ops import functional as F
+        if x.dtype != torch.bfloat16:
+            x = x.to(torch.bfloat16)
+        assert x.shape[0] <= self.comm.size * self.shard and w.N == self.hidden
+        self._gemm(F._dequant_scratch(w), x.contiguous(), None, bias, x.shape[0], True, False)
+
+    def norm_gather(self, h_shard: torch.Tensor, w: Optional[torch.Tensor], eps: float, has_acc: bool) -> None:
+        from ..ops import kernels as k
+        assert h_shard.dtype == torch.float32 and h_shard.shape == (self.shard, self.hidden) and h_shard.is_contiguous()
+        native.check(k._lib().tsb_tpseq_norm_gather(C.c_void_p(self.struct.data_ptr()), k._p(h_shard), k._p(w), C.c_float(eps),
+                                                    C.c_int(self.shard), C.c_int(self.hidden), C.c_int(1 if has_acc else 0),
+                                                    k._stream()), "tpseq_norm_gather")
+        k._count(1)
+
+    def gemm_ag(self, w: QuantWeight, T: int, bias: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16) -> torch.Tensor:
+        """``gathered[:T] @ w^T`` (+ bias); tiles start as soon as their shard has arrived."""
+        from ..ops import functional as F
+        out = torch.empty((T, w.N), dtype=out_dtype, device=self.xfull.device)
+        self._gemm(F._dequant_scratch(w), self.xfull, out, bias, T, False, True)
+        return out
+
+    def wait_all(self) -> None:
+        from ..ops import kernels as k
+        native.check(k._lib().tsb_tpseq_wait_all(C.c_void_p(self.struct.data_ptr()), k._stream()), "tpseq_wait_all")
+        k._count(1)
+
+    def status(self) -> int:
+        torch.cuda.synchronize(self.comm.device)
+        return int(self.local[8].item())
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.comm.device)
+        self.region.close()

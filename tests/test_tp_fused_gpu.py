@@ -49,6 +49,10 @@ def test_fused_exchange_matches_nccl_and_single_gpu(n, kv8_model_path):
     assert r["fused_vs_nccl"] <= 2e-3 * max(1.0, r["scale"])
     assert r["fused_vs_single"] <= 2e-2 * max(1.0, r["scale"])
     assert r["graph_tokens"] == r["eager_tokens"]
+    # sequence-parallel prefill: same logits as the NCCL path and as one GPU (bf16 GEMMs on both sides)
+    assert r["seq_status"] == 0
+    assert r["seq_vs_nccl"] <= 3e-2 * max(1.0, r["scale"]) and r["seq_next_vs_nccl"] <= 3e-2 * max(1.0, r["scale"])
+    assert r["seq_vs_single"] <= 3e-2 * max(1.0, r["scale"])
 
 
 def test_wait_without_sender_times_out_with_status():

@@ -43,14 +43,29 @@ def main():
         graph_tokens.append(int(dg.step()[0]))
     eager_tokens = [int(x.argmax()) for x in fused[:6]]
     status |= tpx.status()
+    # long prompt: the sequence-parallel prefill (GEMM -> reduce-scatter, all-gather -> GEMM)
+    long_prompt = torch.randint(0, 4096, (300,), generator=g).tolist()
+    model.reset_kv_cache()
+    seq_logits = model.forward(long_prompt).float().clone()
+    seq_next = model.forward([int(seq_logits.argmax())]).float().clone()     # decode on the cache the prefill wrote
+    sp = getattr(model, "_tpseq", None)
+    seq_status = sp.status() if sp is not None else -1
     model._tpx = False                                          # NCCL all-reduce path on the same weights
+    os.environ["TSB_TP_FUSED"] = "0"
     nccl = run(model)
+    model.reset_kv_cache()
+    nccl_long = model.forward(long_prompt).float().clone()
+    nccl_next = model.forward([int(nccl_long.argmax())]).float().clone()
     res = {"world": world, "status": status, "exchanges": exchanges,
-           "fused_vs_nccl": float((fused - nccl).abs().max()), "graph_tokens": graph_tokens, "eager_tokens": eager_tokens}
+           "fused_vs_nccl": float((fused - nccl).abs().max()), "graph_tokens": graph_tokens, "eager_tokens": eager_tokens,
+           "seq_status": seq_status, "seq_vs_nccl": float((seq_logits - nccl_long).abs().max()),
+           "seq_next_vs_nccl": float((seq_next - nccl_next).abs().max())}
     if rank == 0:
         single = ModelBase.create(path, comm.device, max_context=256)
         ref = run(single)
         res["fused_vs_single"] = float((fused - ref).abs().max())
+        single.reset_kv_cache()
+        res["seq_vs_single"] = float((seq_logits - single.forward(long_prompt).float()).abs().max())
         res["scale"] = float(ref.abs().max())
         print("TPCHECK " + json.dumps(res), flush=True)
     comm.barrier()
