@@ -203,6 +203,18 @@ extern "C" int tsb_tpseq_init(void* dev_struct, void* const* regions, void* loca
     TSB_CHECK_ARG(dev_struct && regions && local, "tpseq_init: null argument");
     TSB_CHECK_ARG(size >= 1 && size <= TP_MAX_RANKS && rank >= 0 && rank < size, "tpseq_init: rank %d of %d", rank, size);
     TSB_CHECK_ARG(shard > 0 && shard % 128 == 0 && ld > 0 && ld % 8 == 0, "tpseq_init: shard=%d ld=%ld", shard, ld);
+    // the reduce-scatter epilogue issues f32 reductions on peer memory: refuse to set up where the
+    // link does not execute atomics natively
+    int me = 0;
+    TSB_CHECK_CUDA(cudaGetDevice(&me));
+    for (int r = 0; r < size; ++r) {
+        if (r == rank) continue;
+        cudaPointerAttributes pa;
+        TSB_CHECK_CUDA(cudaPointerGetAttributes(&pa, regions[r]));
+        int native_atomics = 0;
+        if (pa.device != me) TSB_CHECK_CUDA(cudaDeviceGetP2PAttribute(&native_atomics, cudaDevP2PAttrNativeAtomicSupported, me, pa.device));
+        TSB_CHECK_ARG(pa.device == me || native_atomics, "tpseq_init: no native peer atomics between device %d and %d", me, pa.device);
+    }
     TpSeq h = {};
     for (int r = 0; r < size; ++r) {
         unsigned char* base = (unsigned char*)regions[r];
