@@ -90,7 +90,7 @@ class Qwen3Model(ModelBase):
         h = F.embed(self.tok_emb, batch.tokens)
         if h.is_cuda and T <= F.FUSED_MAX_M and F.can_fuse(h, self.layers[0].get("wqkv", self.layers[0].get("wq"))):
             return self.forward_fused_small(h, batch, want_logits)
-        if tp and not small and h.is_cuda and "wqkv" in self.layers[0] and "gate_up" in self.layers[0]:
+        if tp and not small and h.is_cuda:
             sp = self.tp_seq(T)
             if sp is not None:
                 return self.forward_seq_parallel(h, batch, want_logits, sp)
@@ -230,19 +230,27 @@ class Qwen3Model(ModelBase):
         sp.norm_gather(h, self.layers[0]["attn_norm"], c.eps, False)
         n_layers = len(self.layers)
         for l, L in enumerate(self.layers):
-            qkv = sp.gemm_ag(L["wqkv"], T, bias=L.get("qkv_bias"))
-            q = qkv[:, :Hq * Dh].view(T, Hq, Dh)
-            k = qkv[:, Hq * Dh:(Hq + Hkv) * Dh].view(T, Hkv, Dh)
-            v = qkv[:, (Hq + Hkv) * Dh:].view(T, Hkv, Dh)
+            if "wqkv" in L:
+                qkv = sp.gemm_ag(L["wqkv"], T, bias=L.get("qkv_bias"))
+                q = qkv[:, :Hq * Dh].view(T, Hq, Dh)
+                k = qkv[:, Hq * Dh:(Hq + Hkv) * Dh].view(T, Hkv, Dh)
+                v = qkv[:, (Hq + Hkv) * Dh:].view(T, Hkv, Dh)
+            else:
+                q = sp.gemm_ag(L["wq"], T).view(T, Hq, Dh)
+                k = sp.gemm_ag(L["wk"], T).view(T, Hkv, Dh)
+                v = sp.gemm_ag(L["wv"], T).view(T, Hkv, Dh)
             qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=self.kv.k[l],
                                   v_cache=self.kv.v[l], rope=self.rope, qn=L["q_norm"], kn=L["k_norm"], eps=c.eps)
             qr = self.q_post_scale(qr, batch)
             o = F.attention(qr, self.kv.k[l], self.kv.v[l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh)
             sp.gemm_rs(o.view(T, Hq * Dh), L["wo"])
             sp.norm_gather(h, L["ffn_norm"], c.eps, True)
-            y = sp.gemm_ag(L["gate_up"], T)
-            half = L["gate_up"].N // 2
-            gu = F.glu("swiglu", y[:, :half], y[:, half:])
+            if "gate_up" in L:
+                y = sp.gemm_ag(L["gate_up"], T)
+                half = L["gate_up"].N // 2
+                gu = F.glu("swiglu", y[:, :half], y[:, half:])
+            else:
+                gu = F.glu("swiglu", sp.gemm_ag(L["gate"], T), sp.gemm_ag(L["up"], T))
             sp.gemm_rs(gu, L["down"])
             sp.norm_gather(h, self.layers[l + 1]["attn_norm"] if l + 1 < n_layers else self.out_norm, c.eps, True)
         if not want_logits:

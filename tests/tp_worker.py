@@ -27,7 +27,7 @@ def main():
             out.append(model.forward([int(out[-1].argmax())]).float().clone())
         return torch.stack(out)
 
-    model = ModelBase.create(path, comm.device, max_context=256, max_seqs=2, tp_rank=rank, tp_size=world, comm=comm)
+    model = ModelBase.create(path, comm.device, max_context=512, max_seqs=2, tp_rank=rank, tp_size=world, comm=comm)
     fused = run(model)
     tpx = model.tp_exchange()
     status = tpx.status()
@@ -61,7 +61,7 @@ def main():
            "seq_status": seq_status, "seq_vs_nccl": float((seq_logits - nccl_long).abs().max()),
            "seq_next_vs_nccl": float((seq_next - nccl_next).abs().max())}
     if rank == 0:
-        single = ModelBase.create(path, comm.device, max_context=256)
+        single = ModelBase.create(path, comm.device, max_context=512)
         ref = run(single)
         res["fused_vs_single"] = float((fused - ref).abs().max())
         single.reset_kv_cache()
