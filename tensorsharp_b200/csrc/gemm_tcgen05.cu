@@ -29,7 +29,7 @@ struct GemmEpi {
     int T, N;               // valid tokens, valid features
     int out_f32;
     // Tensor-parallel prefill (tp_fused.cuh); both null for an ordinary GEMM.
-    const TpSeq* rs;        // GEMM -> reduce-scatter: add the tile into the token owner's accumulator over NVLink
+    const TpSeq* rs;        // GEMM -> reduce-scatter: store the tile into the token owner's accumulator over NVLink
     const TpSeq* ag;        // all-gather -> GEMM: X is the gathered buffer; wait for the tile's shard to arrive
     int rs_rows;            // size * shard (host copy, for the grid)
 };
@@ -129,8 +129,9 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
             if (ep.rs != nullptr) {
                 const TpSeq* g = ep.rs;
                 const int owner = n0 / g->shard;                    // a token tile never straddles two shards
-                if (owner < g->size)
-                    rs_dst = g->acc[owner] + (long)(*g->rs_phase & 1u) * g->shard * g->ld - (long)owner * g->shard * g->ld;
+                if (owner < g->size)       // this rank's slot of the current accumulator, rebased to global token indices
+                    rs_dst = g->acc[owner] + ((long)(*g->rs_phase & 1u) * g->size + g->rank) * g->shard * g->ld -
+                             (long)owner * g->shard * g->ld;
             }
 #pragma unroll 1
             for (int c = 0; c < BN / 16; ++c) {
@@ -142,8 +143,10 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             const int t = n0 + c * 16 + j;
-                            // a warp covers 32 consecutive features of one token: one 128-byte reduction packet
-                            if (t < ep.T) red_add_f32_sys(rs_dst + (long)t * ep.rs->ld + n, __uint_as_float(r[j]) + bias);
+                            // a warp covers 32 consecutive features of one token: one 128-byte packet.  Rows
+                            // past T are written too (zeros from the zero-filled X tile) so the owner
+                            // never reads a stale slot row.
+                            rs_dst[(long)t * ep.rs->ld + n] = __uint_as_float(r[j]) + (t < ep.T ? bias : 0.f);
                         }
                     }
                 } else if (n < ep.N) {
@@ -270,7 +273,7 @@ extern "C" int tsb_gemm_bf16_tp(const void* W, long ldw, const void* X, long ldx
     TSB_CHECK_ARG(status != nullptr, "gemm_bf16: status word is required");
     if (T == 0) return TSB_OK;
     int bn = T <= 32 ? 32 : (T <= 64 ? 64 : (T <= 128 ? 128 : 256));
-    if (rs || ag) bn = 128;
+    if (rs || ag) bn = shard % 256 == 0 ? 256 : 128;          // a token tile must not straddle two shards
     CUtensorMap tw, tx;
     int rc = tsb_make_tmap_2d_bf16(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 128, 64);
     if (rc) return rc;

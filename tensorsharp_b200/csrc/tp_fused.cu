@@ -190,10 +190,10 @@ extern "C" int tsb_tpseq_struct_bytes() { return (int)sizeof(TpSeq); }
 
 // Layout of one rank's symmetric region, in bytes from its base:
 //   [0, 256)                      counters: rs_arrive at +0, ag_arrive[size] at +64
-//   [256, 256 + 2*shard*ld*4)     the two f32 accumulators
-//   then                          xfull: size*shard*ld bf16
+//   [256, 256 + 2*size*shard*ld*4)  the two f32 accumulators, one slot per source rank
+//   then                            xfull: size*shard*ld bf16
 extern "C" long tsb_tpseq_region_bytes(int size, int shard, long ld) {
-    return 256 + 2L * shard * ld * 4 + (long)size * shard * ld * 2;
+    return 256 + 2L * size * shard * ld * 4 + (long)size * shard * ld * 2;
 }
 
 // `regions` holds `size` device addresses of the symmetric regions (local one at index rank);
@@ -203,7 +203,7 @@ extern "C" int tsb_tpseq_init(void* dev_struct, void* const* regions, void* loca
     TSB_CHECK_ARG(dev_struct && regions && local, "tpseq_init: null argument");
     TSB_CHECK_ARG(size >= 1 && size <= TP_MAX_RANKS && rank >= 0 && rank < size, "tpseq_init: rank %d of %d", rank, size);
     TSB_CHECK_ARG(shard > 0 && shard % 128 == 0 && ld > 0 && ld % 8 == 0, "tpseq_init: shard=%d ld=%ld", shard, ld);
-    // the reduce-scatter epilogue issues f32 reductions on peer memory: refuse to set up where the
+    // the arrival counters are bumped with reductions on peer memory: refuse to set up where the
     // link does not execute atomics natively
     int me = 0;
     TSB_CHECK_CUDA(cudaGetDevice(&me));
@@ -221,7 +221,7 @@ extern "C" int tsb_tpseq_init(void* dev_struct, void* const* regions, void* loca
         h.rs_arrive[r] = (unsigned*)base;
         h.ag_arrive[r] = (unsigned*)(base + 64);
         h.acc[r] = (float*)(base + 256);
-        h.xfull[r] = (bf16*)(base + 256 + 2L * shard * ld * 4);
+        h.xfull[r] = (bf16*)(base + 256 + 2L * size * shard * ld * 4);
     }
     unsigned* c = (unsigned*)local;
     h.rs_target = c; h.ag_target = c + 1; h.rs_phase = c + 2; h.ticket = c + 4; h.status = (int*)(c + 8);
@@ -233,7 +233,7 @@ extern "C" int tsb_tpseq_init(void* dev_struct, void* const* regions, void* loca
 }
 
 // One CTA per row of this rank's shard:
-//   has_acc: wait for the reduce-scatter arrivals, h[r] += acc[phase][r], clear the accumulator row
+//   has_acc: wait for the reduce-scatter arrivals, h[r] += sum over sources of acc[phase][src][r]
 //   then     y = RMSNorm(h[r]) * w  (bf16) stored into row (rank * shard + r) of every rank's gathered
 //            buffer, and one arrival per destination.
 // The last CTA advances the all-gather target (and the reduction phase).
@@ -254,15 +254,17 @@ __global__ void __launch_bounds__(NT) tp_seq_norm_gather_kernel(const TpSeq* g, 
         __syncthreads();
     }
     float* hr = h + (long)r * D;
-    float* ar = g->acc[g->rank] + (long)(phase & 1u) * g->shard * D + (long)r * D;
+    const long slot = (long)g->shard * D;
+    const float* ar = g->acc[g->rank] + (long)(phase & 1u) * g->size * slot + (long)r * D;
     float ss = 0.f;
     for (int i = threadIdx.x * 4; i < D; i += NT * 4) {
         float4 v = *reinterpret_cast<const float4*>(hr + i);
         if (has_acc) {
-            const float4 a = __ldcg(reinterpret_cast<const float4*>(ar + i));   // written by remote reductions: skip L1
-            v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+            for (int src = 0; src < g->size; ++src) {
+                const float4 a = __ldcg(reinterpret_cast<const float4*>(ar + src * slot + i));   // remote stores: skip L1
+                v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+            }
             *reinterpret_cast<float4*>(hr + i) = v;
-            *reinterpret_cast<float4*>(ar + i) = make_float4(0.f, 0.f, 0.f, 0.f);
         }
         ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }

@@ -36,19 +36,20 @@ struct TpPush {
 };
 
 // Sequence-parallel prefill: tokens are dealt to ranks in contiguous shards of `shard` rows.
-//  * GEMM -> reduce-scatter: the epilogue of a row-parallel GEMM adds each output tile, with f32
-//    reductions over NVLink, into the accumulator of the rank that owns the tile's tokens, then
-//    bumps that rank's arrival counter (one release per CTA).
-//  * The owner waits for `size x tiles` arrivals, folds the sum into its shard of the residual
-//    stream, normalises, and stores the bf16 rows into every rank's gathered buffer (all-gather),
-//    bumping the per-source arrival counter there.
+//  * GEMM -> reduce-scatter: the epilogue of a row-parallel GEMM stores each output tile (f32,
+//    128-byte packets over NVLink) into this rank's slot of the accumulator of the rank that owns
+//    the tile's tokens, then bumps that rank's arrival counter (one release per CTA).
+//  * The owner waits for `size x tiles` arrivals, adds the slots in rank order (so the sum does not
+//    depend on arrival order) into its shard of the residual stream, normalises, and stores the
+//    bf16 rows into every rank's gathered buffer (all-gather), bumping the per-source arrival
+//    counter there.
 //  * All-gather -> GEMM: the TMA producer of the next (column-parallel) GEMM waits, per token
 //    tile, only for the shard that tile belongs to, so tiles of early shards start at once.
 // Counters only ever grow; the targets to wait for live in local device memory and are advanced
 // by the kernel that precedes the waiter in stream order, so graph replays need no new arguments.
 // Two accumulators alternate, so a fast rank's next reduction never lands in rows being read.
 struct TpSeq {
-    float* acc[TP_MAX_RANKS];            // rank r's accumulators as mapped here: [2][shard * ld] f32
+    float* acc[TP_MAX_RANKS];            // rank r's accumulators as mapped here: [2][size][shard * ld] f32, one slot per source
     unsigned* rs_arrive[TP_MAX_RANKS];   // rank r's reduce-scatter arrival counter (one word)
     bf16* xfull[TP_MAX_RANKS];           // rank r's gathered activations: [size * shard, ld] bf16
     unsigned* ag_arrive[TP_MAX_RANKS];   // rank r's all-gather arrival counters: [size], one per source
@@ -62,9 +63,6 @@ struct TpSeq {
 };
 
 #ifdef __CUDACC__
-__device__ __forceinline__ void red_add_f32_sys(float* p, float v) {
-    asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
-}
 __device__ __forceinline__ void red_release_inc_sys(unsigned* p) {
     asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p) : "memory");
 }

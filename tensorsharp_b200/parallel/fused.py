@@ -121,8 +121,8 @@ class TpSeqParallel:
     """Sequence-parallel prefill exchange (csrc/tp_fused.cuh, TpSeq): tokens are dealt to ranks in
     shards of ``shard`` rows (a multiple of the GEMM's 128-token tile).
 
-    * ``gemm_rs``  row-parallel GEMM whose epilogue reduces every tile into the token owner's
-      accumulator over NVLink (GEMM -> reduce-scatter in one kernel),
+    * ``gemm_rs``  row-parallel GEMM whose epilogue stores every tile into the token owner's
+      accumulator over NVLink (GEMM -> reduce-scatter in one kernel; the owner adds the slots),
     * ``norm_gather``  the owner folds the sum into its shard of the residual stream, normalises and
       stores the rows into every rank's gathered buffer (all-gather inside the norm kernel),
     * ``gemm_ag``  column-parallel GEMM on the gathered buffer whose TMA producer waits per token
@@ -146,7 +146,7 @@ class TpSeqParallel:
         native.check(lib.tsb_tpseq_init(C.c_void_p(self.struct.data_ptr()), arr(*self.region.ptrs),
                                         C.c_void_p(self.local.data_ptr()), C.c_int(comm.rank), C.c_int(n),
                                         C.c_int(self.shard), C.c_long(self.hidden)), "tpseq_init")
-        xoff = 256 + 2 * self.shard * self.hidden * 4
+        xoff = 256 + 2 * n * self.shard * self.hidden * 4
         self.xfull = tensor_from_ptr(self.region.local + xoff, (n * self.shard, self.hidden), torch.bfloat16, dev)
         comm.barrier()
 
