@@ -32,6 +32,7 @@ struct GemmEpi {
     const TpSeq* rs;        // GEMM -> reduce-scatter: store the tile into the token owner's accumulator over NVLink
     const TpSeq* ag;        // all-gather -> GEMM: X is the gathered buffer; wait for the tile's shard to arrive
     int rs_rows;            // size * shard (host copy, for the grid)
+    int tile_rot;           // token tiles are visited starting from this one (see tsb_gemm_bf16_tp)
 };
 
 template <int BN, int STAGES>
@@ -58,7 +59,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * 128;       // first feature (row of W)
-    const int n0 = blockIdx.y * BN;        // first token
+    const int n0 = (int)((blockIdx.y + (unsigned)ep.tile_rot) % gridDim.y) * BN;        // first token
     const int kblocks = (K + 63) / 64;
 
     if (threadIdx.x == 0) {
@@ -251,11 +252,11 @@ static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmE
 // `status` is a device int the kernel sets non-zero if one of its bounded waits gave up.
 extern "C" int tsb_gemm_bf16_tp(const void* W, long ldw, const void* X, long ldx, void* out, long ldo, int out_f32,
                                 const float* bias, const void* residual, int T, int N, int K, const void* rs,
-                                const void* ag, int shard, int size, int* status, void* stream);
+                                const void* ag, int shard, int size, int rank, int* status, void* stream);
 
 extern "C" int tsb_gemm_bf16(const void* W, long ldw, const void* X, long ldx, void* out, long ldo, int out_f32,
                              const float* bias, const void* residual, int T, int N, int K, int* status, void* stream) {
-    return tsb_gemm_bf16_tp(W, ldw, X, ldx, out, ldo, out_f32, bias, residual, T, N, K, nullptr, nullptr, 0, 1, status,
+    return tsb_gemm_bf16_tp(W, ldw, X, ldx, out, ldo, out_f32, bias, residual, T, N, K, nullptr, nullptr, 0, 1, 0, status,
                             stream);
 }
 
@@ -265,7 +266,7 @@ extern "C" int tsb_gemm_bf16(const void* W, long ldw, const void* X, long ldx, v
 // 128 rows so that it divides the shard.
 extern "C" int tsb_gemm_bf16_tp(const void* W, long ldw, const void* X, long ldx, void* out, long ldo, int out_f32,
                                 const float* bias, const void* residual, int T, int N, int K, const void* rs,
-                                const void* ag, int shard, int size, int* status, void* stream) {
+                                const void* ag, int shard, int size, int rank, int* status, void* stream) {
     TSB_CHECK_ARG(T >= 0 && N > 0 && K > 0, "gemm_bf16: bad shape T=%d N=%d K=%d", T, N, K);
     TSB_CHECK_ARG((!rs && !ag) || (shard > 0 && shard % 128 == 0 && size >= 1), "gemm_bf16: shard=%d must be a multiple of 128", shard);
     TSB_CHECK_ARG(!rs || !residual, "gemm_bf16: reduce-scatter mode takes no residual");
@@ -279,7 +280,13 @@ extern "C" int tsb_gemm_bf16_tp(const void* W, long ldw, const void* X, long ldx
     if (rc) return rc;
     rc = tsb_make_tmap_2d_bf16(&tx, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, (uint32_t)bn, 64);
     if (rc) return rc;
-    GemmEpi ep{out, bias, residual, ldo, T, N, out_f32, (const TpSeq*)rs, (const TpSeq*)ag, shard * size};
+    // Visit order of the token tiles.  all-gather -> GEMM starts with this rank's own shard (already
+    // here) so that waiting for remote shards overlaps useful work; GEMM -> reduce-scatter starts with
+    // the next rank's shard and ends with its own, so remote owners receive their tiles first.
+    int rot = 0;
+    if (ag) rot = rank * (shard / bn);
+    if (rs) rot = ((rank + 1) % size) * (shard / bn);
+    GemmEpi ep{out, bias, residual, ldo, T, N, out_f32, (const TpSeq*)rs, (const TpSeq*)ag, shard * size, rot};
     cudaStream_t s = (cudaStream_t)stream;
     switch (bn) {
     case 32: return launch_gemm<32, 8>(tw, tx, ep, K, status, s);

@@ -164,7 +164,8 @@ class TpSeqParallel:
                                           C.c_long(out.stride(0) if out is not None else 0),
                                           C.c_int(1 if (out is None or out.dtype == torch.float32) else 0), k._p(bias), None,
                                           C.c_int(T), C.c_int(N), C.c_int(K), sp if rs else None, sp if ag else None,
-                                          C.c_int(self.shard), C.c_int(self.comm.size), k._p(k.gemm_status(X.device)),
+                                          C.c_int(self.shard), C.c_int(self.comm.size), C.c_int(self.comm.rank),
+                                          k._p(k.gemm_status(X.device)),
                                           k._stream()), "gemm_bf16_tp")
         k._count(1)
 
