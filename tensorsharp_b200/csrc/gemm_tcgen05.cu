@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
         if (tc::mbar_wait(acc_bar, 0)) {
             tc::fence_after_sync();
             const float bias = (ep.bias && n < ep.N && (ep.rs == nullptr || ep.rs->rank == 0)) ? ep.bias[n] : 0.f;
-            float* rs_dst = nullptr;
+            bf16* rs_dst = nullptr;
             if (ep.rs != nullptr) {
                 const TpSeq* g = ep.rs;
                 const int owner = n0 / g->shard;                    // a token tile never straddles two shards
@@ -144,10 +144,10 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             const int t = n0 + c * 16 + j;
-                            // a warp covers 32 consecutive features of one token: one 128-byte packet.  Rows
+                            // a warp covers 32 consecutive features of one token: one 64-byte packet.  Rows
                             // past T are written too (zeros from the zero-filled X tile) so the owner
                             // never reads a stale slot row.
-                            rs_dst[(long)t * ep.rs->ld + n] = __uint_as_float(r[j]) + (t < ep.T ? bias : 0.f);
+                            rs_dst[(long)t * ep.rs->ld + n] = f2bf(__uint_as_float(r[j]) + (t < ep.T ? bias : 0.f));
                         }
                     }
                 } else if (n < ep.N) {

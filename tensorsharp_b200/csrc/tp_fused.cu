@@ -190,10 +190,10 @@ extern "C" int tsb_tpseq_struct_bytes() { return (int)sizeof(TpSeq); }
 
 // Layout of one rank's symmetric region, in bytes from its base:
 //   [0, 256)                      counters: rs_arrive at +0, ag_arrive[size] at +64
-//   [256, 256 + 2*size*shard*ld*4)  the two f32 accumulators, one slot per source rank
+//   [256, 256 + 2*size*shard*ld*2)  the two bf16 accumulators, one slot per source rank
 //   then                            xfull: size*shard*ld bf16
 extern "C" long tsb_tpseq_region_bytes(int size, int shard, long ld) {
-    return 256 + 2L * size * shard * ld * 4 + (long)size * shard * ld * 2;
+    return 256 + 2L * size * shard * ld * 2 + (long)size * shard * ld * 2;
 }
 
 // `regions` holds `size` device addresses of the symmetric regions (local one at index rank);
@@ -220,8 +220,8 @@ extern "C" int tsb_tpseq_init(void* dev_struct, void* const* regions, void* loca
         unsigned char* base = (unsigned char*)regions[r];
         h.rs_arrive[r] = (unsigned*)base;
         h.ag_arrive[r] = (unsigned*)(base + 64);
-        h.acc[r] = (float*)(base + 256);
-        h.xfull[r] = (bf16*)(base + 256 + 2L * size * shard * ld * 4);
+        h.acc[r] = (bf16*)(base + 256);
+        h.xfull[r] = (bf16*)(base + 256 + 2L * size * shard * ld * 2);
     }
     unsigned* c = (unsigned*)local;
     h.rs_target = c; h.ag_target = c + 1; h.rs_phase = c + 2; h.ticket = c + 4; h.status = (int*)(c + 8);
@@ -255,14 +255,16 @@ __global__ void __launch_bounds__(NT) tp_seq_norm_gather_kernel(const TpSeq* g, 
     }
     float* hr = h + (long)r * D;
     const long slot = (long)g->shard * D;
-    const float* ar = g->acc[g->rank] + (long)(phase & 1u) * g->size * slot + (long)r * D;
+    const bf16* ar = g->acc[g->rank] + (long)(phase & 1u) * g->size * slot + (long)r * D;
     float ss = 0.f;
     for (int i = threadIdx.x * 4; i < D; i += NT * 4) {
         float4 v = *reinterpret_cast<const float4*>(hr + i);
         if (has_acc) {
             for (int src = 0; src < g->size; ++src) {
-                const float4 a = __ldcg(reinterpret_cast<const float4*>(ar + src * slot + i));   // remote stores: skip L1
-                v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+                const uint2 a = __ldcg(reinterpret_cast<const uint2*>(ar + src * slot + i));   // remote stores: skip L1
+                const float2 lo = __bfloat1622float2(*reinterpret_cast<const bf162*>(&a.x));
+                const float2 hi = __bfloat1622float2(*reinterpret_cast<const bf162*>(&a.y));
+                v.x += lo.x; v.y += lo.y; v.z += hi.x; v.w += hi.y;
             }
             *reinterpret_cast<float4*>(hr + i) = v;
         }

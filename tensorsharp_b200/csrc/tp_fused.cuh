@@ -36,8 +36,8 @@ struct TpPush {
 };
 
 // Sequence-parallel prefill: tokens are dealt to ranks in contiguous shards of `shard` rows.
-//  * GEMM -> reduce-scatter: the epilogue of a row-parallel GEMM stores each output tile (f32,
-//    128-byte packets over NVLink) into this rank's slot of the accumulator of the rank that owns
+//  * GEMM -> reduce-scatter: the epilogue of a row-parallel GEMM stores each output tile (rounded
+//    to bf16 to halve the NVLink bytes; the owner adds in f32) into this rank's slot of the accumulator of the rank that owns
 //    the tile's tokens, then bumps that rank's arrival counter (one release per CTA).
 //  * The owner waits for `size x tiles` arrivals, adds the slots in rank order (so the sum does not
 //    depend on arrival order) into its shard of the residual stream, normalises, and stores the
@@ -49,7 +49,7 @@ struct TpPush {
 // by the kernel that precedes the waiter in stream order, so graph replays need no new arguments.
 // Two accumulators alternate, so a fast rank's next reduction never lands in rows being read.
 struct TpSeq {
-    float* acc[TP_MAX_RANKS];            // rank r's accumulators as mapped here: [2][size][shard * ld] f32, one slot per source
+    bf16* acc[TP_MAX_RANKS];             // rank r's accumulators as mapped here: [2][size][shard * ld] bf16, one slot per source
     unsigned* rs_arrive[TP_MAX_RANKS];   // rank r's reduce-scatter arrival counter (one word)
     bf16* xfull[TP_MAX_RANKS];           // rank r's gathered activations: [size * shard, ld] bf16
     unsigned* ag_arrive[TP_MAX_RANKS];   // rank r's all-gather arrival counters: [size], one per source

@@ -146,7 +146,7 @@ class TpSeqParallel:
         native.check(lib.tsb_tpseq_init(C.c_void_p(self.struct.data_ptr()), arr(*self.region.ptrs),
                                         C.c_void_p(self.local.data_ptr()), C.c_int(comm.rank), C.c_int(n),
                                         C.c_int(self.shard), C.c_long(self.hidden)), "tpseq_init")
-        xoff = 256 + 2 * n * self.shard * self.hidden * 4
+        xoff = 256 + 2 * n * self.shard * self.hidden * 2
         self.xfull = tensor_from_ptr(self.region.local + xoff, (n * self.shard, self.hidden), torch.bfloat16, dev)
         comm.barrier()
 
