@@ -18,6 +18,7 @@
 // bf16 scratch by tsb_gather_rows and consumed here.
 #include <cudaTypedefs.h>
 #include <mutex>
+#include <cstdlib>
 #include "tcgen05.cuh"
 #include "tp_fused.cuh"
 
@@ -275,6 +276,11 @@ extern "C" int tsb_gemm_bf16_tp(const void* W, long ldw, const void* X, long ldx
     if (T == 0) return TSB_OK;
     int bn = T <= 32 ? 32 : (T <= 64 ? 64 : (T <= 128 ? 128 : 256));
     if (rs || ag) bn = shard % 256 == 0 ? 256 : 128;          // a token tile must not straddle two shards
+    // Reduce-scatter epilogues stall on NVLink stores; with 128-token tiles and a 3-deep ring two
+    // CTAs fit on an SM, so one CTA's epilogue overlaps the other's main loop.
+    static const int rs_small = []() { const char* e = getenv("TSB_TP_RS_TILE"); return e ? atoi(e) : 256; }();
+    const bool two_per_sm = rs && rs_small == 128;
+    if (two_per_sm) bn = 128;
     CUtensorMap tw, tx;
     int rc = tsb_make_tmap_2d_bf16(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 128, 64);
     if (rc) return rc;
@@ -291,7 +297,7 @@ extern "C" int tsb_gemm_bf16_tp(const void* W, long ldw, const void* X, long ldx
     switch (bn) {
     case 32: return launch_gemm<32, 8>(tw, tx, ep, K, status, s);
     case 64: return launch_gemm<64, 8>(tw, tx, ep, K, status, s);
-    case 128: return launch_gemm<128, 6>(tw, tx, ep, K, status, s);
+    case 128: return two_per_sm ? launch_gemm<128, 3>(tw, tx, ep, K, status, s) : launch_gemm<128, 6>(tw, tx, ep, K, status, s);
     default: return launch_gemm<256, 4>(tw, tx, ep, K, status, s);
     }
 }
