@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
         for (int g = 0; g < G; ++g) s[g] = 0.f;
         if (valid) {
             const uint4* kp = reinterpret_cast<const uint4*>(a.k_cache + (slot * a.Hkv + hk) * DH);
-#pragma unroll 4
+#pragma unroll 8
             for (int c = 0; c < DH / 8; ++c) {
                 const uint4 kv = kp[c];
                 const bf162* k2 = reinterpret_cast<const bf162*>(&kv);

@@ -275,6 +275,20 @@ extern "C" int tsb_gemm_bf16_tp(const void* W, long ldw, const void* X, long ldx
     TSB_CHECK_ARG(status != nullptr, "gemm_bf16: status word is required");
     if (T == 0) return TSB_OK;
     int bn = T <= 32 ? 32 : (T <= 64 ? 64 : (T <= 128 ? 128 : 256));
+    if (bn == 256) {
+        // 128 x 256 tiles run one per SM; when the tile count is just over a multiple of the SM count
+        // the last wave is nearly empty (N = 2560, T = 2048: 160 tiles on 148 SMs).  Compare the two
+        // tile widths by waves x per-tile cost (a 128-token tile re-reads the weight slab, hence +64).
+        static int sms = 0;
+        if (sms == 0) {
+            int dev = 0;
+            sms = 148;
+            if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        }
+        const long mt = (N + 127) / 128;
+        const long w256 = (mt * ((T + 255) / 256) + sms - 1) / sms, w128 = (mt * ((T + 127) / 128) + sms - 1) / sms;
+        if (w128 * (128 + 64) < w256 * (256 + 64)) bn = 128;
+    }
     if (rs || ag) bn = shard % 256 == 0 ? 256 : 128;          // a token tile must not straddle two shards
     // Reduce-scatter epilogues stall on NVLink stores; with 128-token tiles and a 3-deep ring two
     // CTAs fit on an SM, so one CTA's epilogue overlaps the other's main loop.

@@ -117,6 +117,71 @@ __global__ void __launch_bounds__(128) gemv_kernel(GemvArgs a) {
     }
 }
 
+// Few output rows, long rows (o_proj, down, K / V projections at batch 1): one warp per row leaves
+// most of the GPU's warp slots empty and each warp walks its row as a chain of dependent DRAM
+// round trips.  Here the four warps of a CTA share one row (every fourth group of 32 units each)
+// and add their partial sums through shared memory, so four times as many loads are in flight.
+template <int M, bool PUSH>
+__global__ void __launch_bounds__(128) gemv_split_kernel(GemvArgs a) {
+    __shared__ float part_sum[4][M];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r = blockIdx.x;
+    const int n_out = a.n_out;
+    const int orow = blockIdx.y * M;
+    const int mv = min(M, a.M - orow);
+    const int K = a.w.K, kb = K >> 5;
+    const int8_t* xq = a.xq ? a.xq + (long)orow * K : nullptr;
+    const float2* xds = a.xds ? a.xds + (long)orow * kb : nullptr;
+    const bf16* xb = a.xb ? a.xb + (long)orow * K : nullptr;
+    float acc[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[m] = 0.f;
+    dot_row<M>(a.w, r, lane, xq, xds, xb, acc, mv, PdlWait{true}, warp, 4);
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+        acc[m] = warp_sum(acc[m]);
+        if (lane == 0) part_sum[warp][m] = acc[m];
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    if (PUSH) {
+        const TpPush* tp = a.push;
+        const unsigned epoch = *tp->epoch;
+        if (lane < tp->size) {
+            float2* dst = tp->mailbox[lane] + (long)(epoch % TP_SLOTS) * tp->slot_stride + (long)tp->rank * tp->src_stride;
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                if (m >= mv) break;
+                float v = part_sum[0][m] + part_sum[1][m] + part_sum[2][m] + part_sum[3][m];
+                if (a.bias && tp->rank == 0) v += a.bias[r];
+                st_word(dst + (long)(orow + m) * n_out + r, v, epoch + 1);
+            }
+        }
+        return;
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            if (m >= mv) break;
+            float v = part_sum[0][m] + part_sum[1][m] + part_sum[2][m] + part_sum[3][m];
+            if (a.bias) v += a.bias[r];
+            if (a.act == ACT_RELU2) {
+                v = fmaxf(v, 0.f);
+                v = v * v;
+            }
+            if (a.row_scale) v *= a.row_scale[orow + m];
+            const long o = (long)(orow + m) * n_out + r;
+            if (a.out_f32) {
+                if (a.residual) v += reinterpret_cast<const float*>(a.residual)[o];
+                reinterpret_cast<float*>(a.out)[o] = v;
+            } else {
+                if (a.residual) v += bf2f(reinterpret_cast<const bf16*>(a.residual)[o]);
+                reinterpret_cast<bf16*>(a.out)[o] = f2bf(v);
+            }
+        }
+    }
+}
+
 // x [M, K] (bf16 or f32) -> int8 groups of 32 with (scale, float sum).  One warp per group.
 template <typename T>
 __global__ void quantize_q8_kernel(const T* x, int8_t* xq, float2* xds, long n_groups) {
@@ -157,6 +222,16 @@ template <bool GLU>
 static int launch_gemv(const GemvArgs& a, int problems, cudaStream_t s) {
     const int rows = a.n_out;
     dim3 block(128);
+    // one row per CTA (4 warps share it) when one row per warp would leave the GPU mostly empty
+    if (!GLU && !a.ids && a.M <= 4 && rows <= 4096 && a.w.K >= 2048) {
+        dim3 grid(rows, 1);
+        const bool push = a.push != nullptr;
+        if (a.M <= 1) TSB_CHECK_CUDA(push ? tsb_launch(gemv_split_kernel<1, true>, grid, block, 0, s, a) : tsb_launch(gemv_split_kernel<1, false>, grid, block, 0, s, a));
+        else if (a.M <= 2) TSB_CHECK_CUDA(push ? tsb_launch(gemv_split_kernel<2, true>, grid, block, 0, s, a) : tsb_launch(gemv_split_kernel<2, false>, grid, block, 0, s, a));
+        else TSB_CHECK_CUDA(push ? tsb_launch(gemv_split_kernel<4, true>, grid, block, 0, s, a) : tsb_launch(gemv_split_kernel<4, false>, grid, block, 0, s, a));
+        TSB_CHECK_LAUNCH();
+        return TSB_OK;
+    }
     if (a.ids) {
         dim3 grid((rows + 3) / 4, problems);
         TSB_CHECK_CUDA(tsb_launch(gemv_kernel<1, GLU>, grid, block, 0, s, a));

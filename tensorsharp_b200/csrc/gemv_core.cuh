@@ -262,14 +262,14 @@ __device__ __forceinline__ void comp_q4_32(const QW& w, const WQ432& t, int u, c
 // load and the first use of the activations.
 #define TSB_ROW_LOOP(WT, LOAD, COMP, UNITS)                                        \
     {                                                                             \
-        const int units = (UNITS);                                                \
+        const int units = (UNITS), step = 32 * parts;                             \
         WT cur, nxt;                                                              \
-        int u = lane;                                                             \
+        int u = lane + 32 * part;                                                 \
         if (u < units) LOAD(w, row, u, cur);                                      \
         pre();                                                                    \
-        for (; u < units; u += 32) {                                              \
-            const bool more = u + 32 < units;                                     \
-            if (more) LOAD(w, row, u + 32, nxt);                                  \
+        for (; u < units; u += step) {                                            \
+            const bool more = u + step < units;                                   \
+            if (more) LOAD(w, row, u + step, nxt);                                \
             COMP(w, cur, u, xq, xds, acc, mv);                                    \
             if (more) cur = nxt;                                                  \
         }                                                                         \
@@ -278,10 +278,10 @@ __device__ __forceinline__ void comp_q4_32(const QW& w, const WQ432& t, int u, c
 // Float-weight types (BF16 / F16 / F32) against bf16 activations.
 template <int M, class Pre>
 __device__ __forceinline__ void dot_float(const QW& w, long row, int lane, const bf16* xb, float* acc, int mv,
-                                          Pre pre) {
+                                          Pre pre, int part = 0, int parts = 1) {
     const int K = w.K, units = K >> 3;
     pre();
-    for (int u = lane; u < units; u += 32) {
+    for (int u = lane + 32 * part; u < units; u += 32 * parts) {
         float wv[8];
         dequant8(w, row, u, wv);
 #pragma unroll
@@ -300,10 +300,11 @@ __device__ __forceinline__ void dot_float(const QW& w, long row, int lane, const
 // `pre` runs exactly once per calling thread, after the first weight loads of the row have been
 // issued and before any activation is read: the place for the kernel's dependency wait and for
 // an in-CTA activation prologue (it may contain __syncthreads: every thread of the CTA calls
-// dot_row with the same weight type).
+// dot_row with the same weight type).  With `parts` > 1 the row is shared by that many warps, warp
+// `part` taking every parts-th group of 32 units; the caller adds the partial sums.
 template <int M, class Pre>
 __device__ __forceinline__ void dot_row(const QW& w, long row, int lane, const int8_t* xq, const float2* xds,
-                                        const bf16* xb, float* acc, int mv, Pre pre) {
+                                        const bf16* xb, float* acc, int mv, Pre pre, int part = 0, int parts = 1) {
     switch (w.type) {
     case TSB_Q4_K: TSB_ROW_LOOP(WQ4K, load_q45k<false>, (comp_q45k<M, false>), (w.K >> 8) << 3) break;
     case TSB_Q5_K: TSB_ROW_LOOP(WQ4K, load_q45k<true>, (comp_q45k<M, true>), (w.K >> 8) << 3) break;
@@ -311,7 +312,7 @@ __device__ __forceinline__ void dot_row(const QW& w, long row, int lane, const i
     case TSB_Q8_0: TSB_ROW_LOOP(WQ80, load_q8_0, comp_q8_0<M>, w.K >> 5) break;
     case TSB_MXFP4: TSB_ROW_LOOP(WQ432, load_q4_32<true>, (comp_q4_32<M, true>), w.K >> 5) break;
     case TSB_Q4_0: TSB_ROW_LOOP(WQ432, load_q4_32<false>, (comp_q4_32<M, false>), w.K >> 5) break;
-    default: dot_float<M>(w, row, lane, xb, acc, mv, pre); break;
+    default: dot_float<M>(w, row, lane, xb, acc, mv, pre, part, parts); break;
     }
 }
 

@@ -323,3 +323,24 @@ def test_fused_gemv_cast_prologue_and_glu(Kd):
     xf = torch.randn(M, Kd, device=DEV)
     got = K().fused_gemv(qw, x_f32=xf, eps=1e-5, do_norm=True)
     assert rel_err(got, ref.rmsnorm(xf, None, 1e-5) @ qw.dequantize().t()) < 3e-2
+
+
+@pytest.mark.parametrize("t", [GGMLType.Q4_K, GGMLType.Q6_K, GGMLType.Q8_0, GGMLType.MXFP4, GGMLType.BF16])
+@pytest.mark.parametrize("M", [1, 2, 3, 4])
+def test_gemv_split_rows(t, M):
+    """Long rows, few of them: the four warps of a CTA share one row."""
+    torch.manual_seed(31)
+    N, Kd = 130, 4096
+    w = torch.randn(N, Kd, device=DEV) * 0.05
+    x = torch.randn(M, Kd, device=DEV).bfloat16()
+    qw = QuantWeight.from_float(w, t)
+    bias = torch.randn(N, device=DEV)
+    res = torch.randn(M, N, device=DEV)
+    if qw.uses_q8_activations:
+        xq, xds = K().quantize_q8(x)
+        want = expected_gemv(qw, x)
+        got = K().gemv(qw, xq=xq, xds=xds, M=M, bias=bias, residual=res)
+    else:
+        want = x.float() @ qw.dequantize().t()
+        got = K().gemv(qw, xb=x, M=M, bias=bias, residual=res)
+    assert rel_err(got, want + bias + res) < 2e-3
