@@ -14,6 +14,7 @@
 // quantize.cu:5), mul_mat_vec_f (mmvf.cu:8), the bias / GLU fusion of
 // ggml-cuda.cu:3359-3790 item (5), and the per-expert unrolled graphs of
 // TensorSharp.GGML.Native/ggml_ops_fused.cpp:1766 for the single-token case.
+#include <cstdlib>
 #include "gemv_core.cuh"
 
 // Row-parallel projection of a tensor-parallel layer: the result is this rank's partial sum, so
@@ -222,8 +223,11 @@ template <bool GLU>
 static int launch_gemv(const GemvArgs& a, int problems, cudaStream_t s) {
     const int rows = a.n_out;
     dim3 block(128);
-    // one row per CTA (4 warps share it) when one row per warp would leave the GPU mostly empty
-    if (!GLU && !a.ids && a.M <= 4 && rows <= 4096 && a.w.K >= 2048) {
+    // One row per CTA (4 warps share it).  Off unless TSB_GEMV_SPLIT=1 (K >= 4096) or 2 (K >= 2048):
+    // inside the graph-replayed decode step it measured slower than one warp per row (2.68 ms
+    // against 2.60 ms per step on Qwen3-4B), although each kernel alone has more loads in flight.
+    static const int split_mode = []() { const char* e = getenv("TSB_GEMV_SPLIT"); return e ? atoi(e) : 0; }();
+    if (split_mode && !GLU && !a.ids && a.M <= 4 && rows <= 4096 && a.w.K >= (split_mode == 2 ? 2048 : 4096)) {
         dim3 grid(rows, 1);
         const bool push = a.push != nullptr;
         if (a.M <= 1) TSB_CHECK_CUDA(push ? tsb_launch(gemv_split_kernel<1, true>, grid, block, 0, s, a) : tsb_launch(gemv_split_kernel<1, false>, grid, block, 0, s, a));

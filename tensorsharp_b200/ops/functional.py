@@ -284,7 +284,9 @@ def decode_splits(batch: Batch, Hkv: int, window: int) -> int:
     """Split-KV factor for decode attention: enough CTAs to cover the GPU's 148 SMs."""
     span = batch.max_kv_len if not window else min(batch.max_kv_len, window)
     want = max(1, (148 * 2) // max(1, batch.B * Hkv))
-    return int(max(1, min(want, (span + 63) // 64, 64)))
+    import os
+    per = int(os.environ.get("TSB_ATTN_SPLIT_LEN", "128"))
+    return int(max(1, min(want, (span + per - 1) // per, 64)))
 
 
 def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, batch: Batch, *, scale: float,
