@@ -84,6 +84,8 @@ class ModelBase:
         self.kv = self.make_kv_pool()
         self._default_seq: Optional[SeqState] = None
         self.timing: Dict[str, float] = {}
+        self._pending_embeddings: List[Tuple[torch.Tensor, int]] = []
+        self._multimodal = None
 
     # ------------------------------------------------------------------ configuration
     def parse_base_config(self) -> ModelConfig:
@@ -119,6 +121,38 @@ class ModelBase:
             from ..runtime.tokenizer import tokenizer_from_gguf
             self._tokenizer = tokenizer_from_gguf(self.gguf)
         return self._tokenizer
+
+    # ------------------------------------------------------------------ multimodal
+    @property
+    def multimodal(self):
+        """The injector that turns image / audio attachments into embedding spans of the prompt
+        (ModelBase.MultimodalInjector in the reference); ``None`` for text-only architectures."""
+        if self._multimodal is None and self.arch in ("gemma3", "gemma4", "qwen35", "qwen35moe", "qwen3next", "mistral3"):
+            from ..multimodal.injector import MultimodalInjector
+            self._multimodal = MultimodalInjector(self)
+        return self._multimodal
+
+    def set_vision_embeddings(self, embeddings: torch.Tensor, insert_position: int) -> None:
+        """Queue ``embeddings`` ``[n, hidden]`` to replace the token embeddings of rows
+        ``[insert_position, insert_position + n)`` of the next forward call (SetVisionEmbeddings /
+        SetAudioEmbeddings of the reference's multimodal models)."""
+        self._pending_embeddings.append((embeddings, int(insert_position)))
+
+    set_audio_embeddings = set_vision_embeddings
+
+    def inject_pending_embeddings(self, h: torch.Tensor) -> torch.Tensor:
+        """Overwrite the queued spans in the (already scaled) embedding rows ``h``; spans that
+        start before the chunk (a reused prefix) are clipped."""
+        if not self._pending_embeddings:
+            return h
+        T = h.shape[0]
+        for emb, pos in self._pending_embeddings:
+            n = emb.shape[0]
+            s, e = max(pos, 0), min(pos + n, T)
+            if e > s:
+                h[s:e] = emb[s - pos:e - pos].to(device=h.device, dtype=h.dtype)
+        self._pending_embeddings = []
+        return h
 
     # ------------------------------------------------------------------ weights
     def has(self, name: str) -> bool:

@@ -156,7 +156,7 @@ class Gemma3Model(_GemmaBase):
         c = self.cfg
         small = batch.T <= F.GEMV_MAX_M
         mid = torch.float32 if small else torch.bfloat16
-        h = F.embed(self.tok_emb, batch.tokens, scale=math.sqrt(c.hidden))
+        h = self.inject_pending_embeddings(F.embed(self.tok_emb, batch.tokens, scale=math.sqrt(c.hidden)))
         for l, L in enumerate(self.layers):
             local = self.is_local(l)
             a = F.norm(h, L["attn_norm"], c.eps, want_q8=small)
@@ -284,7 +284,7 @@ class Gemma4Model(_GemmaBase):
         c = self.cfg
         small = batch.T <= F.GEMV_MAX_M
         mid = torch.float32 if small else torch.bfloat16
-        h = F.embed(self.tok_emb, batch.tokens, scale=math.sqrt(c.hidden))
+        h = self.inject_pending_embeddings(F.embed(self.tok_emb, batch.tokens, scale=math.sqrt(c.hidden)))
         ple = self._ple(batch, h)
         for l, L in enumerate(self.layers):
             local = self.is_local(l)

@@ -87,7 +87,7 @@ class Qwen3Model(ModelBase):
         tp = self.tp_size > 1
         small = T <= F.GEMV_MAX_M
         mid = torch.float32 if small else torch.bfloat16
-        h = F.embed(self.tok_emb, batch.tokens)
+        h = self.inject_pending_embeddings(F.embed(self.tok_emb, batch.tokens))
         if h.is_cuda and T <= F.FUSED_MAX_M and F.can_fuse(h, self.layers[0].get("wqkv", self.layers[0].get("wq"))):
             return self.forward_fused_small(h, batch, want_logits)
         if tp and not small and h.is_cuda:

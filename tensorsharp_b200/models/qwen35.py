@@ -167,7 +167,7 @@ class Qwen35Model(ModelBase):
         c = self.cfg
         small = batch.T <= F.GEMV_MAX_M
         mid = torch.float32 if small else torch.bfloat16
-        h = F.embed(self.tok_emb, batch.tokens)
+        h = self.inject_pending_embeddings(F.embed(self.tok_emb, batch.tokens))
         for l, L in enumerate(self.layers):
             a = F.norm(h, L["attn_norm"], c.eps, want_q8=small)
             y = self._gdn_layer(L, a, batch, mid) if self.is_recurrent[l] else self._attn_layer(l, L, a, batch, mid)

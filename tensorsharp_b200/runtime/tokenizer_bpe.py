@@ -79,6 +79,10 @@ class BpeTokenizer:
     def eos_id(self) -> int:
         return self.eos_ids[0] if self.eos_ids else -1
 
+    def lookup_token(self, s: str) -> int:
+        """Id of the vocabulary entry spelled ``s`` (special tokens included), or -1."""
+        return self.token_to_id.get(s, -1) if hasattr(self, "token_to_id") else -1
+
     def is_eos(self, tid: int) -> bool:
         return tid in self.eos_ids
 
