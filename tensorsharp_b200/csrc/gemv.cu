@@ -17,6 +17,15 @@
 #include <cstdlib>
 #include "gemv_core.cuh"
 
+// Lane q of the calling warp stores `v`, tagged with the current exchange number, at word `index`
+// of this rank's region in rank q's mailbox.
+__device__ __forceinline__ void gemv_push_store(const TpPush* tp, int lane, long index, float v) {
+    const unsigned epoch = *tp->epoch;
+    if (lane < tp->size)
+        st_word(tp->mailbox[lane] + (long)(epoch % TP_SLOTS) * tp->slot_stride + (long)tp->rank * tp->src_stride + index, v,
+                epoch + 1);
+}
+
 // Row-parallel projection of a tensor-parallel layer: the result is this rank's partial sum, so
 // instead of writing it to a local tensor the warp stores it, tagged with the exchange number,
 // into the mailbox of every rank (tp_fused.cuh).  GEMM -> reduce in one kernel: the NVLink stores
@@ -57,7 +66,7 @@ __global__ void __launch_bounds__(128) gemv_kernel(GemvArgs a) {
     const int lane = threadIdx.x & 31;
     const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int n_out = a.n_out;
-    if (a.push != nullptr) {                        // every CTA must reach the publish step
+    if (a.push != nullptr && a.ids == nullptr) {
         gemv_push_body<M, GLU>(a, r, lane);
         return;
     }
@@ -68,7 +77,12 @@ __global__ void __launch_bounds__(128) gemv_kernel(GemvArgs a) {
         pdl_wait();                                 // expert ids come from the router kernel
         pdl_trigger();
         expert = a.ids[p];
-        if (expert < 0) return;
+        if (expert < 0) {
+            // expert-parallel combine: a slot whose expert lives on another rank still has to
+            // arrive (as zero) in every mailbox, or the consumer would wait for it
+            if (a.push != nullptr) gemv_push_store(a.push, lane, (long)p * n_out + r, 0.f);
+            return;
+        }
         xrow = p / a.x_div;
         orow = p;
     } else {
@@ -107,6 +121,10 @@ __global__ void __launch_bounds__(128) gemv_kernel(GemvArgs a) {
             }
             if (a.row_scale) v *= a.row_scale[orow + m];
             const long o = (long)(orow + m) * n_out + r;
+            if (a.push != nullptr) {                // MoE down projection: the weighted slot row goes to every rank
+                acc[m] = v;
+                continue;
+            }
             if (a.out_f32) {
                 if (a.residual) v += reinterpret_cast<const float*>(a.residual)[o];
                 reinterpret_cast<float*>(a.out)[o] = v;
@@ -115,6 +133,10 @@ __global__ void __launch_bounds__(128) gemv_kernel(GemvArgs a) {
                 reinterpret_cast<bf16*>(a.out)[o] = f2bf(v);
             }
         }
+    }
+    if (a.push != nullptr) {
+        const float v = __shfl_sync(0xffffffffu, acc[0], 0);          // ids mode runs one row per problem
+        gemv_push_store(a.push, lane, (long)orow * n_out + r, v);
     }
 }
 
@@ -272,7 +294,8 @@ extern "C" int tsb_gemv_push(const void* p0, const void* p1, const void* p2, con
                              const void* residual, const int* ids, const float* row_scale, int M, int problems,
                              int x_div, int out_f32, int act, const void* push, void* stream) {
     TSB_CHECK_ARG(N > 0 && K > 0 && M >= 0, "gemv: bad shape N=%d K=%d M=%d", N, K, M);
-    TSB_CHECK_ARG(!push || (!residual && !ids && !row_scale && act == 0), "gemv: push mode takes no residual / ids / scale / act");
+    TSB_CHECK_ARG(!push || (!residual && act == 0), "gemv: push mode takes no residual / act");
+    TSB_CHECK_ARG(!push || ids || !row_scale, "gemv: push mode takes a row scale only with expert ids");
     const bool q8 = type_uses_q8(type);
     TSB_CHECK_ARG(!q8 || (xq && xds), "gemv: quantised weight type %d needs int8 activations", type);
     TSB_CHECK_ARG(q8 || xb, "gemv: float weight type %d needs bf16 activations", type);

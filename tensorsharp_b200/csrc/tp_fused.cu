@@ -63,9 +63,11 @@ extern "C" long tsb_tp_mailbox_bytes(int size, long max_rows, long max_d) {
 // y = RMSNorm(h) * w as bf16 and / or as int8 groups of 32 with (scale, sum), the form the
 // quantised GEMV kernels read.  One CTA per row; the last CTA advances the epoch.
 // ------------------------------------------------------------------------------------------
+// `parts` > 1: every source delivers `parts` partial rows per token (the top-k slots of a mixture of
+// experts), laid out token-major, which are all added.
 template <int NT>
 __global__ void __launch_bounds__(NT) tp_reduce_norm_kernel(const TpPush* tp, float* h, const float* w, float eps, int D,
-                                                            int rows, bf16* yb, int8_t* yq, float2* yds) {
+                                                            int rows, int parts, bf16* yb, int8_t* yq, float2* yds) {
     __shared__ float red[32];
     pdl_wait();
     pdl_trigger();
@@ -73,13 +75,14 @@ __global__ void __launch_bounds__(NT) tp_reduce_norm_kernel(const TpPush* tp, fl
     const unsigned epoch = *tp->epoch;              // written only by the last CTA of the previous exchange
     const unsigned tag = epoch + 1;
     const int size = tp->size;
-    const float2* box = tp->mailbox[tp->rank] + (long)(epoch % TP_SLOTS) * tp->slot_stride + (long)m * D;
+    const float2* box = tp->mailbox[tp->rank] + (long)(epoch % TP_SLOTS) * tp->slot_stride + (long)m * parts * D;
     float* hr = h + (long)m * D;
     float ss = 0.f;
     for (int i = threadIdx.x * 4; i < D; i += NT * 4) {
         float4 v = *reinterpret_cast<const float4*>(hr + i);
-        for (int r = 0; r < size; ++r) {
-            const float2* src = box + (long)r * tp->src_stride + i;
+        for (int rp = 0; rp < size * parts; ++rp) {
+            const int r = rp / parts;
+            const float2* src = box + (long)r * tp->src_stride + (long)(rp % parts) * D + i;
             uint4 a = ld_words2(src), b = ld_words2(src + 2);
             if (a.y != tag || a.w != tag || b.y != tag || b.w != tag) {
                 const unsigned long long t0 = global_timer_ns();
@@ -164,14 +167,14 @@ __global__ void __launch_bounds__(NT) tp_reduce_norm_kernel(const TpPush* tp, fl
     }
 }
 
-extern "C" int tsb_tp_reduce_norm(const void* tp, float* h, const float* w, float eps, int rows, int D, void* y_bf16,
-                                  void* yq, void* yds, void* stream) {
-    TSB_CHECK_ARG(tp && h && rows > 0 && D > 0, "tp_reduce_norm: bad arguments");
+extern "C" int tsb_tp_reduce_norm(const void* tp, float* h, const float* w, float eps, int rows, int D, int parts,
+                                  void* y_bf16, void* yq, void* yds, void* stream) {
+    TSB_CHECK_ARG(tp && h && rows > 0 && D > 0 && parts >= 1, "tp_reduce_norm: bad arguments");
     TSB_CHECK_ARG(D % 32 == 0, "tp_reduce_norm: D=%d must be a multiple of 32", D);
     TSB_CHECK_ARG(!yq || yds, "tp_reduce_norm: q8 output needs the scale buffer");
     // NT*4 must cover whole groups of 32 per 8 lanes; D % 32 == 0 keeps all 8 lanes of a group in range together
     TSB_CHECK_CUDA(tsb_launch(tp_reduce_norm_kernel<256>, dim3(rows), dim3(256), 0, (cudaStream_t)stream, (const TpPush*)tp, h,
-                              w, eps, D, rows, (bf16*)y_bf16, (int8_t*)yq, (float2*)yds));
+                              w, eps, D, rows, parts, (bf16*)y_bf16, (int8_t*)yq, (float2*)yds));
     TSB_CHECK_LAUNCH();
     return TSB_OK;
 }
@@ -318,6 +321,54 @@ __global__ void tp_seq_wait_all_kernel(const TpSeq* g) {
 extern "C" int tsb_tpseq_wait_all(const void* g, void* stream) {
     TSB_CHECK_ARG(g, "tpseq_wait_all: null descriptor");
     TSB_CHECK_CUDA(tsb_launch(tp_seq_wait_all_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, (const TpSeq*)g));
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}
+
+// Reduce-scatter of a partial sum that no GEMM epilogue produced (the expert outputs of this rank's
+// experts, already summed over its experts): row t of `partial` goes, as bf16, into this rank's slot of
+// the accumulator of the rank that owns token t, exactly where the GEMM epilogue would have put it, and
+// the arrival counters advance the same way, so tp_seq_norm_gather consumes it unchanged.
+#define TPS_PUSH_ROWS 8
+__global__ void __launch_bounds__(256) tp_seq_push_rows_kernel(const TpSeq* g, const float* partial, int T) {
+    pdl_wait();
+    pdl_trigger();
+    const int D = (int)g->ld;
+    const int row0 = blockIdx.x * TPS_PUSH_ROWS;                    // global token index; a block never straddles shards
+    const int owner = row0 / g->shard;
+    bf16* dst = g->acc[owner] + ((long)(*g->rs_phase & 1u) * g->size + g->rank) * g->shard * D - (long)owner * g->shard * D;
+    for (int r = 0; r < TPS_PUSH_ROWS; ++r) {
+        const int t = row0 + r;
+        for (int i = threadIdx.x * 8; i < D; i += 256 * 8) {
+            uint4 o = make_uint4(0u, 0u, 0u, 0u);
+            if (t < T) {
+                const float4 a = *reinterpret_cast<const float4*>(partial + (long)t * D + i);
+                const float4 b = *reinterpret_cast<const float4*>(partial + (long)t * D + i + 4);
+                *reinterpret_cast<bf162*>(&o.x) = __floats2bfloat162_rn(a.x, a.y);
+                *reinterpret_cast<bf162*>(&o.y) = __floats2bfloat162_rn(a.z, a.w);
+                *reinterpret_cast<bf162*>(&o.z) = __floats2bfloat162_rn(b.x, b.y);
+                *reinterpret_cast<bf162*>(&o.w) = __floats2bfloat162_rn(b.z, b.w);
+            }
+            *reinterpret_cast<uint4*>(dst + (long)t * D + i) = o;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        red_release_inc_sys(g->rs_arrive[owner]);
+        const unsigned done = atomicAdd(g->ticket, 1u);
+        if (done == gridDim.x - 1) {
+            *g->ticket = 0;
+            __threadfence();
+            *g->rs_target += (unsigned)g->size * (unsigned)(g->shard / TPS_PUSH_ROWS);
+        }
+    }
+}
+
+extern "C" int tsb_tpseq_push_rows(const void* g, const float* partial, int T, int shard, int size, int D, void* stream) {
+    TSB_CHECK_ARG(g && partial && T >= 0 && shard % TPS_PUSH_ROWS == 0 && D % 8 == 0, "tpseq_push_rows: bad arguments");
+    TSB_CHECK_CUDA(tsb_launch(tp_seq_push_rows_kernel, dim3((unsigned)(shard * size / TPS_PUSH_ROWS)), dim3(256), 0,
+                              (cudaStream_t)stream, (const TpSeq*)g, partial, T));
     TSB_CHECK_LAUNCH();
     return TSB_OK;
 }

@@ -154,6 +154,33 @@ class ModelBase:
         self._pending_embeddings = []
         return h
 
+    # ------------------------------------------------------------------ tensor-parallel exchanges
+    exchange_parts = 1     # partial rows a rank sends per token in the small-batch exchange (top-k for MoE models)
+
+    def tp_exchange(self):
+        """The peer-memory exchange of this tensor-parallel group for small batches (created on first
+        use; TSB_TP_FUSED=0 keeps the NCCL all-reduce path, the baseline it is measured against)."""
+        if getattr(self, "_tpx", None) is None:
+            if os.environ.get("TSB_TP_FUSED", "1") == "0" or self.comm is None or self.device.type != "cuda":
+                self._tpx = False
+            else:
+                from ..parallel.fused import TpExchange
+                self._tpx = TpExchange(self.comm, F.GEMV_MAX_M * max(1, self.exchange_parts), self.cfg.hidden)
+        return self._tpx or None
+
+    def tp_seq(self, T: int):
+        """The sequence-parallel prefill exchange, sized for at least ``T`` tokens (TSB_TP_FUSED=0
+        keeps the GEMM + NCCL all-reduce path)."""
+        if os.environ.get("TSB_TP_FUSED", "1") == "0" or self.comm is None or self.device.type != "cuda":
+            return None
+        sp = getattr(self, "_tpseq", None)
+        if sp is None or sp.shard * self.tp_size < T:
+            if sp is not None:
+                sp.close()
+            from ..parallel.fused import TpSeqParallel
+            self._tpseq = sp = TpSeqParallel(self.comm, max(T, 4096), self.cfg.hidden)
+        return sp
+
     # ------------------------------------------------------------------ weights
     def has(self, name: str) -> bool:
         return name in self.gguf.tensors

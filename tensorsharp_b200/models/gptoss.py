@@ -92,6 +92,83 @@ class GptOssModel(ModelBase):
         self.rope = RopeSpec(rot_dim=Dh, theta_base=c.rope_base, mode=0, freq_scale=1.0 / scale,
                              ext_factor=1.0 if scale != 1.0 else 0.0, attn_factor=1.0, corr_lo=lo, corr_hi=hi)
 
+    @property
+    def exchange_parts(self) -> int:
+        return max(1, self.top_k)
+
+    def attention_block(self, a, L, l: int, batch: Batch, mid, proj) -> torch.Tensor:
+        """QKV projection (``proj(weight, bias)``), RoPE + cache write, attention -> ``[T, Hq * Dh]``."""
+        c = self.cfg
+        Hq, Hkv, Dh, T = self.Hq, self.Hkv, c.head_dim, batch.T
+        if "wqkv" in L:
+            qkv = proj(L["wqkv"], L["bqkv"])
+            q = qkv[:, :Hq * Dh].view(T, Hq, Dh)
+            k = qkv[:, Hq * Dh:(Hq + Hkv) * Dh].view(T, Hkv, Dh)
+            v = qkv[:, (Hq + Hkv) * Dh:].view(T, Hkv, Dh)
+        else:
+            q, k, v = (proj(L["wq"], L["bq"]).view(T, Hq, Dh), proj(L["wk"], L["bk"]).view(T, Hkv, Dh),
+                       proj(L["wv"], L["bv"]).view(T, Hkv, Dh))
+        qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=self.kv.k[l], v_cache=self.kv.v[l],
+                              rope=self.rope, eps=c.eps)
+        return F.attention(qr, self.kv.k[l], self.kv.v[l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh,
+                           window=self.window if l % 2 == 0 else 0, sinks=L["sinks"])
+
+    def forward_exchange_small(self, h: torch.Tensor, batch: Batch, want_logits: bool, tpx) -> Optional[torch.Tensor]:
+        """Tensor + expert parallel small batches with the collectives inside the kernels: o_proj stores
+        its partial sums into every rank's mailbox, and so does the experts' down projection (one
+        weighted row per top-k slot: the expert-parallel combine), each followed by one kernel that adds
+        the parts to the residual stream and normalises for the next projection."""
+        c = self.cfg
+        n_layers = len(self.layers)
+        a = F.norm(h, self.layers[0]["attn_norm"], c.eps, want_q8=True)
+        for l, L in enumerate(self.layers):
+            o = self.attention_block(a, L, l, batch, torch.float32,
+                                     lambda w, b: F.linear(a, w, bias=b, out_dtype=torch.float32))
+            tpx.linear_push(F.as_act(o), L["wo"], bias=L["bo"])
+            a = tpx.reduce_norm(h, L["ffn_norm"], c.eps)
+            logits = F.linear(a, L["router"], bias=L["router_bias"], out_dtype=torch.float32)
+            ids, w = F.route_topk_softmax(logits, self.top_k)
+            F.moe_experts(a, ids, w, L["gate_up_exps"], L["down_exps"], act="swiglu_oai", gate_up_bias=L["gate_up_bias"],
+                          down_bias=L["down_bias"], expert_offset=self.e0, push=tpx)
+            nxt = self.layers[l + 1]["attn_norm"] if l + 1 < n_layers else None
+            a = tpx.reduce_norm(h, nxt, c.eps, norm=nxt is not None, parts=self.top_k)
+        if not want_logits:
+            return None
+        last = h[batch.last_idx].contiguous()
+        return F.linear(F.norm(last, self.out_norm, c.eps, want_q8=True), self.lm_head, out_dtype=torch.float32)
+
+    def forward_seq_parallel(self, h_all: torch.Tensor, batch: Batch, want_logits: bool, sp) -> Optional[torch.Tensor]:
+        """Tensor + expert parallel prefill on sequence shards: o_proj reduces into the token owners from
+        its GEMM epilogue; the owners' norm kernel scatters the normalised rows to every rank, which is
+        also the expert dispatch (every rank sees every token and keeps those routed to its experts);
+        the summed outputs of a rank's experts are reduce-scattered back to the owners (the combine)."""
+        c = self.cfg
+        T = batch.T
+        r0 = self.tp_rank * sp.shard
+        mine = max(0, min(T, r0 + sp.shard) - r0)
+        h = torch.zeros((sp.shard, c.hidden), dtype=torch.float32, device=h_all.device)
+        if mine:
+            h[:mine].copy_(h_all[r0:r0 + mine])
+        sp.norm_gather(h, self.layers[0]["attn_norm"], c.eps, False)
+        n_layers = len(self.layers)
+        for l, L in enumerate(self.layers):
+            o = self.attention_block(None, L, l, batch, torch.bfloat16, lambda w, b: sp.gemm_ag(w, T, bias=b))
+            sp.gemm_rs(o.view(T, -1), L["wo"], bias=L["bo"])
+            sp.norm_gather(h, L["ffn_norm"], c.eps, True)
+            sp.wait_all()                                            # the router and the experts read the gathered rows
+            a = Act(sp.xfull[:T])
+            logits = F.linear(a, L["router"], bias=L["router_bias"], out_dtype=torch.float32)
+            ids, w = F.route_topk_softmax(logits, self.top_k)
+            y = F.moe_experts(a, ids, w, L["gate_up_exps"], L["down_exps"], act="swiglu_oai", gate_up_bias=L["gate_up_bias"],
+                              down_bias=L["down_bias"], expert_offset=self.e0)
+            sp.push_rows(y.contiguous(), T)
+            sp.norm_gather(h, self.layers[l + 1]["attn_norm"] if l + 1 < n_layers else self.out_norm, c.eps, True)
+        if not want_logits:
+            return None
+        sp.wait_all()
+        last = sp.xfull[batch.last_idx].contiguous()               # already normalised with the output norm
+        return F.linear(Act(last), self.lm_head, out_dtype=torch.float32)
+
     def forward_batch(self, batch: Batch, want_logits: bool = True) -> Optional[torch.Tensor]:
         c = self.cfg
         Hq, Hkv, Dh = self.Hq, self.Hkv, c.head_dim
@@ -100,21 +177,19 @@ class GptOssModel(ModelBase):
         mid = torch.float32 if small else torch.bfloat16
         h = F.embed(self.tok_emb, batch.tokens)
         n_layers = len(self.layers)
+        sharded = self.tp_size > 1 and (self.e1 - self.e0) != self.n_experts and self.ep_size <= 1
+        if sharded and h.is_cuda:
+            if small and T * self.top_k <= 4 * F.GEMV_MAX_M:
+                tpx = self.tp_exchange()
+                if tpx is not None:
+                    return self.forward_exchange_small(h, batch, want_logits, tpx)
+            elif not small:
+                sp = self.tp_seq(T)
+                if sp is not None:
+                    return self.forward_seq_parallel(h, batch, want_logits, sp)
         for l, L in enumerate(self.layers):
             a = F.norm(h, L["attn_norm"], c.eps, want_q8=small)
-            if "wqkv" in L:
-                qkv = F.linear(a, L["wqkv"], bias=L["bqkv"], out_dtype=mid)
-                q = qkv[:, :Hq * Dh].view(T, Hq, Dh)
-                k = qkv[:, Hq * Dh:(Hq + Hkv) * Dh].view(T, Hkv, Dh)
-                v = qkv[:, (Hq + Hkv) * Dh:].view(T, Hkv, Dh)
-            else:
-                q = F.linear(a, L["wq"], bias=L["bq"], out_dtype=mid).view(T, Hq, Dh)
-                k = F.linear(a, L["wk"], bias=L["bk"], out_dtype=mid).view(T, Hkv, Dh)
-                v = F.linear(a, L["wv"], bias=L["bv"], out_dtype=mid).view(T, Hkv, Dh)
-            qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=self.kv.k[l],
-                                  v_cache=self.kv.v[l], rope=self.rope, eps=c.eps)
-            o = F.attention(qr, self.kv.k[l], self.kv.v[l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh,
-                            window=self.window if l % 2 == 0 else 0, sinks=L["sinks"])
+            o = self.attention_block(a, L, l, batch, mid, lambda w, b: F.linear(a, w, bias=b, out_dtype=mid))
             h = self.reduce_add(F.linear(F.as_act(o), L["wo"], bias=L["bo"] if self.tp_rank == 0 else None), h)
             # mixture of experts; on the last layer of a prefill only the last token of each
             # sequence feeds the logits, so only those rows are run

@@ -200,20 +200,6 @@ class Qwen3Model(ModelBase):
             logits = self.comm.all_gather_cat(logits, dim=1)
         return logits
 
-    def tp_seq(self, T: int):
-        """The sequence-parallel prefill exchange, sized for at least ``T`` tokens (TSB_TP_FUSED=0
-        keeps the GEMM + NCCL all-reduce path, the baseline it is measured against)."""
-        import os
-        if os.environ.get("TSB_TP_FUSED", "1") == "0":
-            return None
-        sp = getattr(self, "_tpseq", None)
-        if sp is None or sp.shard * self.tp_size < T:
-            if sp is not None:
-                sp.close()
-            from ..parallel.fused import TpSeqParallel
-            self._tpseq = sp = TpSeqParallel(self.comm, max(T, 4096), self.cfg.hidden)
-        return sp
-
     def forward_seq_parallel(self, h_all: torch.Tensor, batch: Batch, want_logits: bool, sp) -> Optional[torch.Tensor]:
         """Tensor-parallel prefill with the collectives inside the kernels: every rank keeps only its
         shard of the residual stream; o_proj and down reduce straight into the token owners'
@@ -258,19 +244,6 @@ class Qwen3Model(ModelBase):
         sp.wait_all()
         last = sp.xfull[batch.last_idx].contiguous()       # already normalised with the output norm
         return self.lm_head_logits(F.Act(last))
-
-    def tp_exchange(self):
-        """The peer-memory exchange of this tensor-parallel group (created on first use; set
-        TSB_TP_FUSED=0 to keep the NCCL all-reduce path, which is also the baseline it is
-        measured against)."""
-        if getattr(self, "_tpx", None) is None:
-            import os
-            if os.environ.get("TSB_TP_FUSED", "1") == "0":
-                self._tpx = False
-            else:
-                from ..parallel.fused import TpExchange
-                self._tpx = TpExchange(self.comm, F.GEMV_MAX_M, self.cfg.hidden)
-        return self._tpx or None
 
     def q_post_scale(self, qr: torch.Tensor, batch: Batch) -> torch.Tensor:
         return qr

@@ -353,13 +353,16 @@ def route_sigmoid(logits: torch.Tensor, k: int, bias: Optional[torch.Tensor], no
 
 def moe_experts(a: Act, ids: torch.Tensor, weights: torch.Tensor, gate_up: QuantWeight, down: QuantWeight, *,
                 act: str, gate_up_bias: Optional[torch.Tensor] = None, down_bias: Optional[torch.Tensor] = None,
-                expert_offset: int = 0, down_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+                expert_offset: int = 0, down_scale: Optional[torch.Tensor] = None, push=None) -> Optional[torch.Tensor]:
     """sum_k weights[t, k] * down_e(act(gate_up_e(x_t)))  with e = ids[t, k]  -> f32 [T, D].
 
     ``gate_up`` / ``down`` are expert stacks; when they hold only experts
     ``[expert_offset, expert_offset + E_local)`` (expert parallelism) the other selections are
     skipped and the caller sums the partial results over ranks.  For non-gated activations
-    (relu2) ``gate_up`` is the plain up projection."""
+    (relu2) ``gate_up`` is the plain up projection.  ``push`` (a ``TpExchange``; small CUDA batches
+    only) makes the down projection store its weighted slot rows straight into every rank's
+    mailbox - the expert-parallel combine happens in the consumer of the exchange, which adds
+    ``k`` parts per source (``reduce_norm(parts=k)``), and nothing is returned."""
     T, k = ids.shape
     D = down.N
     E_local = gate_up.experts
@@ -386,13 +389,15 @@ def moe_experts(a: Act, ids: torch.Tensor, weights: torch.Tensor, gate_up: Quant
         w = weights.reshape(-1).float().contiguous()
         if down_scale is not None:
             w = w * down_scale[ids.reshape(-1).long()]
-        y = torch.zeros((T * k, D), dtype=torch.float32, device=dev)
+        pk = dict(push=push.struct.data_ptr()) if push is not None else dict(out=torch.zeros((T * k, D), dtype=torch.float32, device=dev))
         if down.uses_q8_activations:
             gq, gds = kk.quantize_q8(gu)
-            kk.gemv(down, xq=gq, xds=gds, M=1, ids=flat, x_div=1, bias=down_bias, row_scale=w, out=y)
+            y = kk.gemv(down, xq=gq, xds=gds, M=1, ids=flat, x_div=1, bias=down_bias, row_scale=w, **pk)
         else:
-            kk.gemv(down, xb=gu, M=1, ids=flat, x_div=1, bias=down_bias, row_scale=w, out=y)
-        return y.view(T, k, D).sum(1)
+            y = kk.gemv(down, xb=gu, M=1, ids=flat, x_div=1, bias=down_bias, row_scale=w, **pk)
+        return y.view(T, k, D).sum(1) if push is None else None
+    if push is not None:
+        raise ValueError("moe_experts(push=...) needs a CUDA batch of at most 4 * GEMV_MAX_M slots")
     # grouped path: sort the (token, slot) pairs by expert and run each expert on its rows
     out = torch.zeros((T, D), dtype=torch.float32, device=dev)
     flat = local.reshape(-1)

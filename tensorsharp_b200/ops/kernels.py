@@ -75,7 +75,7 @@ def _lib():
     lib = native.lib()
     if not _configured:
         for name in ("tsb_quantize_q8", "tsb_gemv", "tsb_rmsnorm", "tsb_qkv_rope", "tsb_glu", "tsb_gather_rows",
-                     "tsb_argmax", "tsb_rope_table", "tsb_fused_gemv", "tsb_gemv_push", "tsb_tp_reduce_norm", "tsb_decode_advance", "tsb_attn_decode", "tsb_attn_prefill", "tsb_gemm_bf16", "tsb_causal_conv1d", "tsb_gdn_recurrent",
+                     "tsb_argmax", "tsb_rope_table", "tsb_fused_gemv", "tsb_gemv_push", "tsb_tp_reduce_norm", "tsb_tpseq_push_rows", "tsb_decode_advance", "tsb_attn_decode", "tsb_attn_prefill", "tsb_gemm_bf16", "tsb_causal_conv1d", "tsb_gdn_recurrent",
                      "tsb_mamba2_recurrent"):
             getattr(lib, name).restype = C.c_int
         _configured = True
@@ -96,22 +96,26 @@ def quantize_q8(x: torch.Tensor):
 
 
 def gemv(w: QuantWeight, *, xq=None, xds=None, xb=None, M: int, out_dtype=torch.float32, bias=None, residual=None,
-         act=None, ids=None, row_scale=None, x_div: int = 1, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+         act=None, ids=None, row_scale=None, x_div: int = 1, out: Optional[torch.Tensor] = None,
+         push: Optional[int] = None) -> Optional[torch.Tensor]:
     """Small-batch matvec over quantised weights.  With ``ids`` ([P] int32) each problem p
-    uses expert ids[p], activation row p // x_div and output row p."""
+    uses expert ids[p], activation row p // x_div and output row p.  ``push`` (device address of a
+    tensor-parallel exchange descriptor) sends the f32 result to every rank's mailbox instead of
+    ``out``."""
     a = ACT[act]
     glu = 1 <= a <= 4
     n_out = w.N // 2 if glu else w.N
     problems = int(ids.numel()) if ids is not None else 1
     rows = problems if ids is not None else M
     dev = w.device
-    if out is None:
+    if out is None and push is None:
         out = torch.empty((rows, n_out), dtype=out_dtype, device=dev)
     ps = _planes(w)
-    native.check(_lib().tsb_gemv(ps[0], ps[1], ps[2], ps[3], C.c_int(int(w.ggml_type)), C.c_int(w.N), C.c_int(w.K),
-                                 _p(xq), _p(xds), _p(xb), _p(out), _p(bias), _p(residual), _p(ids), _p(row_scale),
-                                 C.c_int(M), C.c_int(problems), C.c_int(x_div),
-                                 C.c_int(out.dtype == torch.float32), C.c_int(a), _stream()), "gemv")
+    native.check(_lib().tsb_gemv_push(ps[0], ps[1], ps[2], ps[3], C.c_int(int(w.ggml_type)), C.c_int(w.N), C.c_int(w.K),
+                                      _p(xq), _p(xds), _p(xb), _p(out), _p(bias), _p(residual), _p(ids), _p(row_scale),
+                                      C.c_int(M), C.c_int(problems), C.c_int(x_div),
+                                      C.c_int(1 if (out is None or out.dtype == torch.float32) else 0), C.c_int(a),
+                                      C.c_void_p(push) if push else None, _stream()), "gemv")
     _count(1)
     return out
 

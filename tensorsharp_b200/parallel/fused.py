@@ -72,9 +72,10 @@ class TpExchange:
         k.fused_gemv(w, bias=bias, push=self.struct.data_ptr(), **kw)
 
     def reduce_norm(self, h: torch.Tensor, w: Optional[torch.Tensor], eps: float, want_q8: bool = True,
-                    want_bf16: bool = True, norm: bool = True) -> Optional[Act]:
+                    want_bf16: bool = True, norm: bool = True, parts: int = 1) -> Optional[Act]:
         """``h += sum of all ranks' partials`` (in place, f32), then ``RMSNorm(h) * w`` as the next
-        projection's input.  With ``norm=False`` only the residual stream is updated."""
+        projection's input.  With ``norm=False`` only the residual stream is updated.  ``parts`` > 1:
+        every rank sent that many partial rows per token (mixture-of-experts slots)."""
         from ..ops import kernels as k
         assert h.dtype == torch.float32 and h.is_contiguous()
         T, D = h.shape
@@ -86,8 +87,8 @@ class TpExchange:
         lib = k._lib()
         lib.tsb_tp_reduce_norm.restype = C.c_int
         native.check(lib.tsb_tp_reduce_norm(C.c_void_p(self.struct.data_ptr()), k._p(h), k._p(w if norm else None),
-                                            C.c_float(eps), C.c_int(T), C.c_int(D), k._p(yb), k._p(yq), k._p(yds),
-                                            k._stream()), "tp_reduce_norm")
+                                            C.c_float(eps), C.c_int(T), C.c_int(D), C.c_int(parts), k._p(yb), k._p(yq),
+                                            k._p(yds), k._stream()), "tp_reduce_norm")
         k._count(1)
         self.exchanges += 1
         return Act(yb, yq, yds) if norm else None
@@ -191,6 +192,16 @@ class TpSeqParallel:
         out = torch.empty((T, w.N), dtype=out_dtype, device=self.xfull.device)
         self._gemm(F._dequant_scratch(w), self.xfull, out, bias, T, False, True)
         return out
+
+    def push_rows(self, partial: torch.Tensor, T: int) -> None:
+        """Reduce-scatter a partial ``[T, hidden]`` f32 sum that no GEMM epilogue produced (the summed
+        outputs of this rank's experts): same destination and counters as ``gemm_rs``."""
+        from ..ops import kernels as k
+        assert partial.dtype == torch.float32 and partial.is_contiguous() and partial.shape[1] == self.hidden
+        native.check(k._lib().tsb_tpseq_push_rows(C.c_void_p(self.struct.data_ptr()), k._p(partial), C.c_int(T),
+                                                  C.c_int(self.shard), C.c_int(self.comm.size), C.c_int(self.hidden),
+                                                  k._stream()), "tpseq_push_rows")
+        k._count(1)
 
     def wait_all(self) -> None:
         from ..ops import kernels as k

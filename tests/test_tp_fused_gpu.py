@@ -20,14 +20,15 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _run_ranks(n, model_path):
+def _run_ranks(n, *model_paths):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
-           "--master-port", str(_free_port()), os.path.join(HERE, "tp_worker.py"), model_path]
+           "--master-port", str(_free_port()), os.path.join(HERE, "tp_worker.py"), *model_paths]
     p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     lines = [l for l in p.stdout.splitlines() if l.startswith("TPCHECK ")]
     assert p.returncode == 0 and lines, f"rc={p.returncode}\nstdout:\n{p.stdout[-3000:]}\nstderr:\n{p.stderr[-3000:]}"
-    return json.loads(lines[-1][8:])
+    assert len(lines) == len(model_paths), p.stdout[-3000:]
+    return [json.loads(l[8:]) for l in lines]
 
 
 @pytest.fixture(scope="module")
@@ -40,12 +41,28 @@ def kv8_model_path(tmp_path_factory):
     return p
 
 
+@pytest.fixture(scope="module")
+def moe_model_path(tmp_path_factory):
+    """A small GPT-OSS-shaped model (sinks, sliding window, 8 experts top-2, MXFP4 experts) with 8 KV heads."""
+    from tensorsharp_b200.models import synth
+    p = str(tmp_path_factory.mktemp("tp") / "gptoss_kv8.gguf")
+    synth.write_gptoss(p, n_layers=2, hidden=512, n_heads=16, n_kv_heads=8, head_dim=64, n_experts=8, top_k=2, device="cpu")
+    return p
+
+
 @pytest.mark.parametrize("n", [2, 4, 8])
-def test_fused_exchange_matches_nccl_and_single_gpu(n, kv8_model_path):
+def test_fused_exchange_matches_nccl_and_single_gpu(n, kv8_model_path, moe_model_path):
+    """Dense (Qwen3) and mixture-of-experts (GPT-OSS, experts sharded over the ranks) models: the
+    in-kernel exchanges give the NCCL path's and a single GPU's logits, for decode-sized batches
+    (mailbox exchange, CUDA-graph replay) and for a 300-token prefill (sequence-parallel path)."""
     if torch.cuda.device_count() < n:
         pytest.skip(f"needs {n} GPUs")
-    r = _run_ranks(n, kv8_model_path)
-    assert r["status"] == 0 and r["exchanges"] > 0
+    for r in _run_ranks(n, kv8_model_path, moe_model_path):
+        check_result(r)
+
+
+def check_result(r):
+    assert r["status"] == 0 and r["exchanges"] > 0, r
     assert r["fused_vs_nccl"] <= 1e-2 * max(1.0, r["scale"])      # different summation orders, then int8 re-quantisation
     assert r["fused_vs_single"] <= 2e-2 * max(1.0, r["scale"])
     assert r["graph_tokens"] == r["eager_tokens"]

@@ -11,12 +11,20 @@ import torch  # noqa: E402
 
 
 def main():
-    path = sys.argv[1]
-    from tensorsharp_b200.models.base import ModelBase
     from tensorsharp_b200.parallel.dist import init_from_env
-    from tensorsharp_b200.runtime.engine import DecodeGraph
     comm = init_from_env()
+    for path in sys.argv[1:]:
+        check_model(path, comm)
+    comm.barrier()
+    torch.cuda.synchronize()
+    os._exit(0)          # skip NCCL teardown: it can block while captured graphs still hold its kernels
+
+
+def check_model(path, comm):
+    from tensorsharp_b200.models.base import ModelBase
+    from tensorsharp_b200.runtime.engine import DecodeGraph
     rank, world = comm.rank, comm.size
+    os.environ["TSB_TP_FUSED"] = "1"
     g = torch.Generator().manual_seed(11)
     prompt = torch.randint(0, 4096, (9,), generator=g).tolist()
 
@@ -56,7 +64,7 @@ def main():
     model.reset_kv_cache()
     nccl_long = model.forward(long_prompt).float().clone()
     nccl_next = model.forward([int(nccl_long.argmax())]).float().clone()
-    res = {"world": world, "status": status, "exchanges": exchanges,
+    res = {"world": world, "arch": model.arch, "status": status, "exchanges": exchanges,
            "fused_vs_nccl": float((fused - nccl).abs().max()), "graph_tokens": graph_tokens, "eager_tokens": eager_tokens,
            "seq_status": seq_status, "seq_vs_nccl": float((seq_logits - nccl_long).abs().max()),
            "seq_next_vs_nccl": float((seq_next - nccl_next).abs().max())}
@@ -69,8 +77,6 @@ def main():
         res["scale"] = float(ref.abs().max())
         print("TPCHECK " + json.dumps(res), flush=True)
     comm.barrier()
-    torch.cuda.synchronize()
-    os._exit(0)          # skip NCCL teardown: it can block while captured graphs still hold its kernels
 
 
 if __name__ == "__main__":
