@@ -29,6 +29,9 @@ struct AttnArgs {
     float softcap;            // 0 = off
     int window;               // 0 = full causal
     int B, Hq, Hkv, Dh, page_size, max_pages, splits;
+    // Prefill only.  Context parallelism runs the kernel once per KV shard and merges the partial results:
+    const int* q_pos0;        // [B] cache position of each sequence's first query, or null = kv_len - q_len
+    float* lse_out;           // [Tq, Hq] log-sum-exp of the scaled scores seen by this call (-inf if none), or null
 };
 
 __device__ __forceinline__ long kv_slot(const AttnArgs& a, int b, int j) {
@@ -332,7 +335,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(AttnArgs a) {
     const int m0 = blockIdx.x * BM;
     if (m0 >= qlen) return;
     const int kvlen = a.kv_lens[b];
-    const int pos0 = kvlen - qlen;                 // cache position of the sequence's first query
+    const int pos0 = a.q_pos0 ? a.q_pos0[b] : kvlen - qlen;   // cache position of the sequence's first query
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rows = min(BM, qlen - m0);
 
@@ -340,7 +343,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(AttnArgs a) {
     const int p_last = pos0 + m0 + rows - 1;
     int j_lo = 0;
     if (a.window > 0) j_lo = max(0, pos0 + m0 - a.window + 1);
-    const int j_hi = p_last + 1;                   // exclusive
+    const int j_hi = min(p_last + 1, kvlen);       // exclusive
     const int t_lo = j_lo / BN, t_hi = (j_hi + BN - 1) / BN;
 
     // Q tile -> shared (rows beyond the sequence are zero)
@@ -487,6 +490,10 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(AttnArgs a) {
         inv[r] = ll > 0.f ? oc / ll : 0.f;
     }
     const int ra = warp * 16 + (lane >> 2), rb = ra + 8;
+    if (a.lse_out != nullptr && (lane & 3) == 0) {
+        if (ra < rows) a.lse_out[(long)(q0 + m0 + ra) * a.Hq + h] = lrow[0] > 0.f ? mrow[0] + __logf(lrow[0]) : -INFINITY;
+        if (rb < rows) a.lse_out[(long)(q0 + m0 + rb) * a.Hq + h] = lrow[1] > 0.f ? mrow[1] + __logf(lrow[1]) : -INFINITY;
+    }
 #pragma unroll
     for (int i = 0; i < DH / 8; ++i) {
         const int d = i * 8 + (lane & 3) * 2;

@@ -58,7 +58,7 @@ class AttnArgs(C.Structure):
                 ("kv_lens", _vp), ("cu_q", _vp), ("sinks", _vp), ("part_o", _vp), ("part_ml", _vp),
                 ("scale", C.c_float), ("softcap", C.c_float), ("window", C.c_int),
                 ("B", C.c_int), ("Hq", C.c_int), ("Hkv", C.c_int), ("Dh", C.c_int), ("page_size", C.c_int),
-                ("max_pages", C.c_int), ("splits", C.c_int)]
+                ("max_pages", C.c_int), ("splits", C.c_int), ("q_pos0", _vp), ("lse_out", _vp)]
 
 
 _configured = False
@@ -286,13 +286,17 @@ def attn_decode(q, k_cache, v_cache, block_table, kv_lens, *, scale, Hq, Hkv, Dh
 
 
 def attn_prefill(q, k_cache, v_cache, block_table, kv_lens, cu_q, max_q_len, *, scale, Hq, Hkv, Dh, page_size,
-                 sinks=None, softcap=0.0, window=0, out=None):
-    """q [T, Hq, Dh] bf16 packed over sequences (cu_q [B+1])."""
+                 sinks=None, softcap=0.0, window=0, out=None, q_pos0=None, lse_out=None):
+    """q [T, Hq, Dh] bf16 packed over sequences (cu_q [B+1]).  ``q_pos0`` [B] int32 overrides the cache
+    position of each sequence's first query (default kv_len - q_len); ``lse_out`` [T, Hq] f32 receives the
+    log-sum-exp of the scores, for merging partial results over KV shards."""
     B = kv_lens.shape[0]
     if out is None:
         out = torch.empty_like(q)
     a = _attn_args(q, k_cache, v_cache, out, block_table, kv_lens, cu_q, sinks, scale, softcap, window, Hq, Hkv, Dh,
                    page_size, B)
+    a.q_pos0 = q_pos0.data_ptr() if q_pos0 is not None else None
+    a.lse_out = lse_out.data_ptr() if lse_out is not None else None
     native.check(_lib().tsb_attn_prefill(C.byref(a), C.c_int(max_q_len), _stream()), "attn_prefill")
     _count(1)
     return out

@@ -1,0 +1,86 @@
+"""Context-parallel (sequence-sharded) causal attention for long prefills.
+
+Rank r holds queries, keys and values of tokens ``[r * shard, (r + 1) * shard)``.  Every rank publishes
+its K / V shard in a peer-mapped staging buffer; a rank pulls each lower rank's shard across NVLink once
+(plain peer loads in a kernel of this library), runs the flash-attention kernel on the local copy with
+every key visible, runs it causally on its own shard, and merges the partial outputs by their
+log-sum-exp weights (csrc/context_parallel.cu).  Nothing like it exists in the reference, whose long
+context path is single-device (Gemma4Model.cs:593-637 chunked prefill).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from ..ops import native
+from .symm import SymmetricBuffer, _lib
+
+
+class ContextParallelAttention:
+    def __init__(self, comm, max_shard: int, Hkv: int, Dh: int):
+        self.comm, self.max_shard, self.Hkv, self.Dh = comm, int(max_shard), Hkv, Dh
+        lib = _lib()
+        for name in ("tsb_cp_struct_bytes", "tsb_cp_init", "tsb_cp_publish", "tsb_cp_pull", "tsb_cp_merge"):
+            getattr(lib, name).restype = C.c_int
+        lib.tsb_cp_region_bytes.restype = C.c_long
+        kv_row = Hkv * Dh
+        self.region = SymmetricBuffer(comm, lib.tsb_cp_region_bytes(C.c_long(self.max_shard), C.c_long(kv_row)))
+        dev = comm.device
+        self.local = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.ticket = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.struct = torch.zeros(lib.tsb_cp_struct_bytes(), dtype=torch.uint8, device=dev)
+        arr = C.c_void_p * comm.size
+        native.check(lib.tsb_cp_init(C.c_void_p(self.struct.data_ptr()), arr(*self.region.ptrs), C.c_void_p(self.local.data_ptr()),
+                                     C.c_int(comm.rank), C.c_int(comm.size), C.c_long(self.max_shard), C.c_long(kv_row)), "cp_init")
+        self.k_pull = torch.empty((self.max_shard, Hkv, Dh), dtype=torch.bfloat16, device=dev)
+        self.v_pull = torch.empty_like(self.k_pull)
+        comm.barrier()
+
+    def attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, softcap: float = 0.0) -> torch.Tensor:
+        """``q`` ``[n, Hq, Dh]``, ``k`` / ``v`` ``[n, Hkv, Dh]`` bf16: this rank's shard (all shards the same
+        length ``n``).  Returns ``[n, Hq, Dh]``: causal attention over the whole sequence."""
+        from ..ops import kernels as kk
+        lib = kk._lib()
+        n, Hq, Dh = q.shape
+        Hkv = k.shape[1]
+        assert n <= self.max_shard and k.is_contiguous() and v.is_contiguous() and q.is_contiguous()
+        dev = q.device
+        sp = C.c_void_p(self.struct.data_ptr())
+        elems = n * Hkv * Dh
+        native.check(lib.tsb_cp_publish(sp, kk._p(k), kk._p(v), C.c_long(elems), kk._stream()), "cp_publish")
+        kk._count(2)
+        r = self.comm.rank
+        S = r + 1
+        parts = torch.empty((S, n, Hq, Dh), dtype=torch.bfloat16, device=dev)
+        lse = torch.empty((S, n, Hq), dtype=torch.float32, device=dev)
+        table = torch.zeros((1, 1), dtype=torch.int32, device=dev)
+        lens = torch.tensor([n], dtype=torch.int32, device=dev)
+        cu_q = torch.tensor([0, n], dtype=torch.int32, device=dev)
+        seen_all = torch.tensor([n], dtype=torch.int32, device=dev)          # first query sits after the whole shard
+        page = 1 << 30
+        # own shard first (needs no transfer), then the remote ones as they arrive
+        kk.attn_prefill(q, k, v, table, lens, cu_q, n, scale=scale, Hq=Hq, Hkv=Hkv, Dh=Dh, page_size=page, softcap=softcap,
+                        out=parts[r], lse_out=lse[r])
+        for s in range(r):
+            native.check(lib.tsb_cp_pull(sp, C.c_int(s), kk._p(self.k_pull), kk._p(self.v_pull), C.c_long(elems),
+                                         kk._p(self.ticket), kk._stream()), "cp_pull")
+            kk._count(1)
+            kk.attn_prefill(q, self.k_pull, self.v_pull, table, lens, cu_q, n, scale=scale, Hq=Hq, Hkv=Hkv, Dh=Dh,
+                            page_size=page, softcap=softcap, out=parts[s], lse_out=lse[s], q_pos0=seen_all)
+        if S == 1:
+            return parts[0]
+        out = torch.empty_like(q)
+        native.check(lib.tsb_cp_merge(kk._p(parts), kk._p(lse), kk._p(out), C.c_int(S), C.c_long(n * Hq), C.c_int(Dh),
+                                      kk._stream()), "cp_merge")
+        kk._count(1)
+        return out
+
+    def status(self) -> int:
+        torch.cuda.synchronize(self.comm.device)
+        return int(self.local[4].item())
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.comm.device)
+        self.region.close()

@@ -28,6 +28,8 @@ def _run_ranks(n, *model_paths):
     lines = [l for l in p.stdout.splitlines() if l.startswith("TPCHECK ")]
     assert p.returncode == 0 and lines, f"rc={p.returncode}\nstdout:\n{p.stdout[-3000:]}\nstderr:\n{p.stderr[-3000:]}"
     assert len(lines) == len(model_paths), p.stdout[-3000:]
+    cp = [json.loads(l[8:]) for l in p.stdout.splitlines() if l.startswith("CPCHECK ")]
+    assert cp and cp[0]["status"] == 0 and cp[0]["max_err"] < 3e-2, cp          # context-parallel attention
     return [json.loads(l[8:]) for l in lines]
 
 

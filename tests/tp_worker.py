@@ -13,11 +13,37 @@ import torch  # noqa: E402
 def main():
     from tensorsharp_b200.parallel.dist import init_from_env
     comm = init_from_env()
+    check_context_parallel(comm)
     for path in sys.argv[1:]:
         check_model(path, comm)
     comm.barrier()
     torch.cuda.synchronize()
     os._exit(0)          # skip NCCL teardown: it can block while captured graphs still hold its kernels
+
+
+def check_context_parallel(comm):
+    """Sequence-sharded causal attention against plain attention over the whole sequence."""
+    from tensorsharp_b200.ops import reference as ref
+    from tensorsharp_b200.parallel.context import ContextParallelAttention
+    n, Hq, Hkv, Dh = 160, 4, 2, 64
+    world, rank, dev = comm.size, comm.rank, comm.device
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(world * n, Hq, Dh, generator=g).to(dev).bfloat16()
+    k = torch.randn(world * n, Hkv, Dh, generator=g).to(dev).bfloat16()
+    v = torch.randn(world * n, Hkv, Dh, generator=g).to(dev).bfloat16()
+    cp = ContextParallelAttention(comm, 256, Hkv, Dh)
+    sl = slice(rank * n, (rank + 1) * n)
+    worst = 0.0
+    for rep in range(4):                                           # several calls: both staging halves and the back-pressure
+        out = cp.attention(q[sl].contiguous(), k[sl].contiguous(), v[sl].contiguous(), Dh ** -0.5)
+        want = ref.attention(q, k, v, torch.arange(world * n, device=dev), scale=Dh ** -0.5)[sl]
+        worst = max(worst, float((out.float() - want.reshape(out.shape)).abs().max()))
+    t = torch.tensor([worst, float(cp.status())], device=dev)
+    import torch.distributed as dist
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        print("CPCHECK " + json.dumps({"world": world, "max_err": float(t[0]), "status": int(t[1])}), flush=True)
+    cp.close()
 
 
 def check_model(path, comm):
