@@ -33,6 +33,8 @@ Conversation:
   /reset, /new           Clear conversation history and KV cache.
   /history               Print the current conversation history.
   /save <file>           Write the conversation transcript to a file.
+  /savekv <file>         Write the cached tokens and KV rows (continue later without re-prefill).
+  /loadkv <file>         Restore a KV state written by /savekv.
   /system <text>         Set (or clear when empty) the system prompt.
   /think on|off          Toggle thinking/reasoning mode for supported models.
   /multiline on|off      Toggle multi-line input (terminate with a single '.').
@@ -201,6 +203,7 @@ class InteractiveSession:
             "/multiline": self.toggle_multiline, "/save": self.save_transcript,
             "/model": self.load_different_model, "/backend": self.switch_backend,
             "/mmproj": self.load_mmproj, "/projector": self.load_mmproj,
+            "/savekv": self.save_kv_state, "/loadkv": self.load_kv_state,
         }
         sampling = {
             ("/temp", "/temperature"): ("temperature", False), ("/topk", "/top-k", "/top_k"): ("top_k", True),
@@ -393,6 +396,29 @@ class InteractiveSession:
             self.say(f"Transcript saved to {path} ({len(self.history)} message(s)).")
         except OSError as e:
             self.say(f"Failed to save transcript: {e}")
+
+    def save_kv_state(self, path: str) -> None:
+        """Write the cached tokens and their K / V rows so a later run can continue without re-prefill."""
+        if not path:
+            self.say("Usage: /savekv <file-path>")
+            return
+        from ..runtime.session_store import save_session
+        try:
+            n = save_session(path, self.model, self.kv)
+            self.say(f"KV state saved to {path} ({n} token(s)).")
+        except (OSError, RuntimeError) as e:
+            self.say(f"Failed to save KV state: {e}")
+
+    def load_kv_state(self, path: str) -> None:
+        if not path:
+            self.say("Usage: /loadkv <file-path>")
+            return
+        from ..runtime.session_store import load_session
+        try:
+            n = load_session(path, self.model, self.kv)
+            self.say(f"KV state loaded from {path} ({n} token(s)); a prompt that starts with the same tokens reuses it.")
+        except (OSError, RuntimeError, ValueError, KeyError) as e:
+            self.say(f"Failed to load KV state: {e}")
 
     def print_history(self) -> None:
         if not self.history and not self.system_prompt:

@@ -262,8 +262,31 @@ class ModelBase:
         """Append ``tokens`` to the default sequence and return the next-token logits
         (float32 ``[vocab]`` on the compute device).  IModelArchitecture.Forward."""
         batch = self.kv.build_batch([self._seq()], [list(tokens)])
-        out = self.forward_batch(batch, want_logits)
+        with self.timer.phase("decode" if len(tokens) == 1 else "prefill"):
+            out = self.forward_batch(batch, want_logits)
         return out[0] if out is not None else None
+
+    @property
+    def timer(self):
+        """Per-phase device timer (enabled by ``TSB_PROFILE=1``; NVTX ranges by ``TSB_NVTX=1``)."""
+        t = self.__dict__.get("_timer")
+        if t is None:
+            from ..runtime.profiling import PhaseTimer
+            t = self.__dict__["_timer"] = PhaseTimer(self.device)
+        return t
+
+    def print_timing_stats(self, out=None) -> None:
+        """Table of accumulated phase times (ModelBase.PrintTimingStats in the reference)."""
+        import sys
+        print(self.timer.table(), file=out or sys.stderr)
+
+    def check_exchanges(self) -> None:
+        """Raise a typed error if any in-kernel exchange of this model gave up waiting for a peer."""
+        for name in ("_tpx", "_tpseq"):
+            x = self.__dict__.get(name)
+            for e in (x.values() if isinstance(x, dict) else [x]):
+                if e is not None and hasattr(e, "check"):
+                    e.check()
 
     def forward_refill(self, tokens: Sequence[int], chunk: int = 2048) -> torch.Tensor:
         """Chunked prefill: all chunks but the last skip the logits (Qwen3Model.cs:238

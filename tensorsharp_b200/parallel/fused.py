@@ -100,6 +100,13 @@ class TpExchange:
         torch.cuda.synchronize(self.comm.device)
         return int(self.counters[4].item())
 
+    def check(self) -> None:
+        """Raise ``ExchangeTimeoutError`` if any wait so far ran out (synchronises the device)."""
+        from .errors import ExchangeTimeoutError
+        code = self.status()
+        if code:
+            raise ExchangeTimeoutError("tensor-parallel mailbox exchange", code)
+
     def close(self) -> None:
         torch.cuda.synchronize(self.comm.device)
         self.mail.close()
@@ -211,6 +218,12 @@ class TpSeqParallel:
     def status(self) -> int:
         torch.cuda.synchronize(self.comm.device)
         return int(self.local[8].item())
+
+    def check(self) -> None:
+        from .errors import ExchangeTimeoutError
+        code = self.status()
+        if code:
+            raise ExchangeTimeoutError("sequence-parallel prefill exchange", code)
 
     def close(self) -> None:
         torch.cuda.synchronize(self.comm.device)

@@ -16,6 +16,10 @@ import torch
 from ..ops import native
 
 
+GUARD = 256                  # bytes of guard band on either side of a symmetric buffer
+CANARY = 0x5A5AC3C3
+
+
 def _lib():
     lib = native.lib()
     for name in ("tsb_symm_alloc", "tsb_symm_free", "tsb_ipc_get_handle", "tsb_ipc_open", "tsb_ipc_close",
@@ -33,12 +37,26 @@ class SymmetricBuffer:
         import torch.distributed as dist
         self.comm, self.nbytes = comm, int(nbytes)
         lib = _lib()
-        local = C.c_void_p()
-        native.check(lib.tsb_symm_alloc(C.c_size_t(self.nbytes), C.byref(local)), "symm_alloc")
-        self.local = local.value
+        base = C.c_void_p()
+        # a guard band on either side holds a known pattern; check_canaries() tells whether a kernel of
+        # this rank or a peer wrote outside the buffer
+        native.check(lib.tsb_symm_alloc(C.c_size_t(self.nbytes + 2 * GUARD), C.byref(base)), "symm_alloc")
+        self._base = base.value
+        self.local = self._base + GUARD
+        self._guards = None
+        try:
+            from .fused import tensor_from_ptr
+            dev = comm.device
+            self._guards = (tensor_from_ptr(self._base, (GUARD // 4,), torch.int32, dev),
+                            tensor_from_ptr(self.local + self.nbytes, (GUARD // 4,), torch.int32, dev))
+            for gd in self._guards:
+                gd.fill_(CANARY)
+            torch.cuda.synchronize(dev)
+        except Exception:
+            self._guards = None
         hb = lib.tsb_ipc_handle_bytes()
         handle = (C.c_ubyte * hb)()
-        native.check(lib.tsb_ipc_get_handle(C.c_void_p(self.local), handle), "ipc_get_handle")
+        native.check(lib.tsb_ipc_get_handle(C.c_void_p(self._base), handle), "ipc_get_handle")
         mine = bytes(handle)
         if comm.size > 1:
             handles: List[bytes] = [b""] * comm.size
@@ -54,9 +72,16 @@ class SymmetricBuffer:
             p = C.c_void_p()
             buf = (C.c_ubyte * hb).from_buffer_copy(h)
             native.check(lib.tsb_ipc_open(buf, C.byref(p)), f"ipc_open(rank {r})")
-            self.ptrs.append(p.value)
+            self.ptrs.append(p.value + GUARD)
             self._opened.append(p.value)
         comm.barrier()
+
+    def check_canaries(self) -> bool:
+        """True while both guard bands of the local buffer still hold their pattern."""
+        if self._guards is None:
+            return True
+        torch.cuda.synchronize(self.comm.device)
+        return all(bool((gd == CANARY).all()) for gd in self._guards)
 
     def close(self) -> None:
         lib = _lib()
@@ -65,5 +90,6 @@ class SymmetricBuffer:
         self._opened = []
         self.comm.barrier()              # nobody still maps the memory that is about to be freed
         if self.local:
-            lib.tsb_symm_free(C.c_void_p(self.local))
-            self.local = 0
+            self._guards = None
+            lib.tsb_symm_free(C.c_void_p(self._base))
+            self.local = self._base = 0

@@ -1,0 +1,217 @@
+"""Auxiliary subsystems: phase timing, rank liveness (failures injected on the host), session
+persistence, typed errors, and a CPU model of the tagged-word exchange protocol."""
+import multiprocessing as mp
+import os
+import time
+
+import pytest
+import torch
+
+from tensorsharp_b200.parallel.errors import ExchangeTimeoutError, RankFailureError
+from tensorsharp_b200.parallel.watchdog import Heartbeat, Watchdog
+from tensorsharp_b200.runtime.profiling import PhaseTimer
+
+
+def test_phase_timer_table():
+    t = PhaseTimer("cpu", enabled=True)
+    for _ in range(3):
+        with t.phase("decode"):
+            time.sleep(0.001)
+    with t.phase("prefill"):
+        time.sleep(0.002)
+    s = t.stats()
+    assert s["decode"]["calls"] == 3 and s["prefill"]["calls"] == 1
+    assert s["decode"]["total_ms"] >= 3 * 0.9
+    assert "share" in t.table() and "prefill" in t.table()
+    t.reset()
+    assert t.stats() == {}
+
+
+def test_phase_timer_off_is_free():
+    t = PhaseTimer("cpu", enabled=False)
+    with t.phase("x"):
+        pass
+    assert t.stats() == {}
+
+
+class DictStore:
+    def __init__(self):
+        self.d = {}
+
+    def set(self, k, v):
+        self.d[k] = v.encode()
+
+    def get(self, k):
+        return self.d[k]
+
+    def check(self, ks):
+        return all(k in self.d for k in ks)
+
+
+def test_heartbeat_detects_silent_and_departed_rank():
+    store, now = DictStore(), [0.0]
+    hb = [Heartbeat(store, r, 3, clock=lambda: now[0]) for r in range(3)]
+    assert hb[0].stale_ranks(1.0) == set()
+    now[0] = 0.5
+    hb[1].beat(); hb[2].beat()
+    assert hb[0].stale_ranks(1.0) == set()
+    now[0] = 2.0
+    hb[1].beat()                                   # rank 2 stays silent
+    assert hb[0].stale_ranks(1.0) == {2}
+    hb[1].leave()
+    with pytest.raises(RankFailureError) as e:
+        hb[0].check(1.0)
+    assert e.value.stale == [1, 2]
+
+
+def test_watchdog_thread_reports_once():
+    store = DictStore()
+    a, b = Heartbeat(store, 0, 2), Heartbeat(store, 1, 2)
+    seen = []
+    w = Watchdog(a, timeout_s=0.15, interval_s=0.03, on_failure=lambda s: seen.append(set(s))).start()
+    t0 = time.time()
+    while time.time() - t0 < 0.1:
+        b.beat(); time.sleep(0.02)
+    assert not seen
+    time.sleep(0.4)                                # b stops beating
+    w.stop()
+    assert seen == [{1}]
+
+
+def _rank_main(rank, port, q):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    from datetime import timedelta
+    store = dist.TCPStore("127.0.0.1", port, 2, rank == 0, timeout=timedelta(seconds=20))
+    dist.init_process_group("gloo", store=store, rank=rank, world_size=2, timeout=timedelta(seconds=20))
+    hb = Heartbeat(store, rank, 2)
+    x = torch.ones(4)
+    dist.all_reduce(x)                             # step 1: both ranks alive
+    if rank == 1:
+        hb.leave()                                 # leaves between steps, nothing in flight
+        q.put(("left", float(x[0])))
+        time.sleep(1.0)                            # keep the store's client socket open while rank 0 checks
+        return
+    deadline = time.time() + 10
+    err = None
+    while time.time() < deadline and err is None:
+        try:
+            hb.check(0.5)                          # before launching step 2
+            time.sleep(0.05)
+        except RankFailureError as e:
+            err = e.stale
+    q.put(("detected", err))
+
+
+def test_rank_departure_detected_before_next_collective():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29000 + os.getpid() % 2000
+    ps = [ctx.Process(target=_rank_main, args=(r, port, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    got = dict(q.get(timeout=60) for _ in range(2))
+    for p in ps:
+        p.join(timeout=30)
+    assert got["left"] == 2.0
+    assert got["detected"] == [1]
+
+
+def test_exchange_timeout_error_fields():
+    e = ExchangeTimeoutError("x", 3)
+    assert e.code == 3 and "status 3" in str(e)
+
+
+# ---- CPU model of the tagged-word exchange: a word is valid only when its tag matches the reader's
+# epoch; slots are reused every SLOTS epochs, so a writer may run at most SLOTS - 1 epochs ahead.
+SLOTS = 4
+
+
+class Mailbox:
+    def __init__(self, ranks, words):
+        self.val = [[[0.0] * words for _ in range(ranks)] for _ in range(SLOTS)]
+        self.tag = [[[0] * words for _ in range(ranks)] for _ in range(SLOTS)]
+
+
+def _push(boxes, src, epoch, vals):
+    for mb in boxes:
+        for i, v in enumerate(vals):
+            mb.val[epoch % SLOTS][src][i] = v
+            mb.tag[epoch % SLOTS][src][i] = epoch + 1
+
+
+def _try_reduce(mb, epoch, ranks, words):
+    s = epoch % SLOTS
+    if any(mb.tag[s][r][i] != epoch + 1 for r in range(ranks) for i in range(words)):
+        return None
+    return [sum(mb.val[s][r][i] for r in range(ranks)) for i in range(words)]
+
+
+def test_tagged_word_protocol_model_interleavings():
+    import random
+    rng = random.Random(0)
+    ranks, words, epochs = 3, 2, 12
+    for trial in range(50):
+        boxes = [Mailbox(ranks, words) for _ in range(ranks)]
+        pushed = [0] * ranks                        # next epoch each rank will push
+        reduced = [0] * ranks                       # next epoch each rank will reduce
+        while min(reduced) < epochs:
+            r = rng.randrange(ranks)
+            # a rank pushes epoch e only after reducing e - 1 (one exchange per kernel pair), so it is
+            # never more than one epoch ahead of itself and at most two ahead of the slowest peer
+            if pushed[r] == reduced[r] and pushed[r] < epochs:
+                _push(boxes, r, pushed[r], [float(pushed[r] * 10 + r + i) for i in range(words)])
+                pushed[r] += 1
+            elif reduced[r] < pushed[r]:
+                out = _try_reduce(boxes[r], reduced[r], ranks, words)
+                if out is not None:
+                    e = reduced[r]
+                    assert out == [float(sum(e * 10 + q + i for q in range(ranks))) for i in range(words)]
+                    reduced[r] += 1
+            assert max(pushed) - min(reduced) < SLOTS
+
+
+def test_tagged_word_stale_slot_is_not_accepted():
+    boxes = [Mailbox(2, 1)]
+    _push(boxes, 0, 0, [1.0]); _push(boxes, 1, 0, [2.0])
+    assert _try_reduce(boxes[0], 0, 2, 1) == [3.0]
+    _push(boxes, 0, SLOTS, [5.0])                  # same slot, later epoch, peer 1 not yet there
+    assert _try_reduce(boxes[0], SLOTS, 2, 1) is None
+
+
+def test_session_store_round_trip(tiny_qwen3_path, tmp_path):
+    from tensorsharp_b200.models.base import ModelBase
+    from tensorsharp_b200.runtime.kv_cache import KVCache
+    from tensorsharp_b200.runtime.session_store import load_session, save_session
+    m = ModelBase.create(tiny_qwen3_path, device="cpu", max_context=128)
+    prompt = [5, 9, 33, 7, 21, 40, 2, 18]
+    cache = KVCache()
+    lg = m.forward(prompt)
+    cache.record_append(prompt, lg)
+    nxt = int(lg.argmax())
+    want = m.forward([nxt]).clone()
+    m.truncate_kv_cache(len(prompt))
+    path = str(tmp_path / "chat.tsbkv")
+    assert save_session(path, m, cache) == len(prompt)
+
+    m2 = ModelBase.create(tiny_qwen3_path, device="cpu", max_context=128)
+    cache2 = KVCache()
+    assert load_session(path, m2, cache2) == len(prompt)
+    assert list(cache2.tokens) == prompt and m2.cache_length == len(prompt)
+    assert torch.allclose(cache2.next_logits.float(), lg.float())
+    got = m2.forward([nxt])
+    assert torch.allclose(got, want, atol=1e-4, rtol=1e-4)
+    plan = cache2.plan_reuse(prompt + [nxt], True)
+    assert plan.reused_prefix == len(prompt) if hasattr(plan, "reused_prefix") else True
+
+
+def test_model_timing_table(tiny_qwen3_path, monkeypatch, capsys):
+    from tensorsharp_b200.models.base import ModelBase
+    monkeypatch.setenv("TSB_PROFILE", "1")
+    m = ModelBase.create(tiny_qwen3_path, device="cpu", max_context=64)
+    m.forward([1, 2, 3, 4])
+    m.forward([5]); m.forward([6])
+    s = m.timer.stats()
+    assert s["prefill"]["calls"] == 1 and s["decode"]["calls"] == 2
+    m.print_timing_stats()
+    assert "decode" in capsys.readouterr().err
