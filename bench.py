@@ -35,13 +35,19 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--prefill", type=int, default=2048)
-    ap.add_argument("--model", default="qwen3-4b", choices=["qwen3-4b", "qwen3-tiny"])
+    ap.add_argument("--batch", type=int, default=None, help="sequences decoded together (default: 1; gptoss-20b: 64)")
+    ap.add_argument("--prefill", type=int, default=None, help="prompt tokens per sequence (default: 2048; gptoss-20b: 1024)")
+    ap.add_argument("--model", default="qwen3-4b", choices=["qwen3-4b", "qwen3-tiny", "gptoss-20b", "gptoss-tiny"])
     ap.add_argument("--prefill-repeats", type=int, default=3, help="timed prefill repetitions (median reported)")
     ap.add_argument("--no-graph", action="store_true", help="run decode steps eagerly (for kernel-level profiling)")
     ap.add_argument("--cache-dir", default=os.environ.get("TSB_BENCH_CACHE", os.path.join(tempfile.gettempdir(), "tsb_bench")))
-    return ap.parse_args()
+    a = ap.parse_args()
+    big_moe = a.model == "gptoss-20b"
+    if a.batch is None:
+        a.batch = 64 if big_moe else 1
+    if a.prefill is None:
+        a.prefill = 1024 if big_moe else 2048
+    return a
 
 
 class ClockSampler:
@@ -99,6 +105,23 @@ MODEL_SHAPES = {
                      scheme="Q4_K_M", rope_base=1e6, tied=True),
     "qwen3-tiny": dict(n_layers=4, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=768, vocab=4096,
                        scheme="Q8_0", rope_base=1e6, tied=True),
+    "gptoss-20b": dict(n_layers=24, hidden=2880, n_heads=64, n_kv_heads=8, head_dim=64, n_experts=32, top_k=4,
+                       expert_ffn=2880, vocab=201088, window=128),
+    "gptoss-tiny": dict(n_layers=2, hidden=256, n_heads=8, n_kv_heads=2, head_dim=64, n_experts=8, top_k=2,
+                        expert_ffn=256, vocab=4096, window=16),
+}
+MODEL_TEXT = {
+    "qwen3-4b": ("Qwen3-4B-shaped Q4_K_M (36L, hidden 2560, 32q/8kv x128, ffn 9728, vocab 151936), random-init",
+                 "bf16 activations / f32 accumulate, Q4_K_M weights as stored",
+                 "weights (2.4 GB) exceed the 126 MB L2; no flush needed"),
+    "qwen3-tiny": ("tiny Qwen3 Q8_0 (4L, hidden 256), random-init", "bf16 activations / f32 accumulate, Q8_0 weights as stored",
+                   "tiny model: fits L2, smoke configuration only"),
+    "gptoss-20b": ("gpt-oss-20b-shaped (24L, hidden 2880, 64q/8kv x64, 32 experts top-4, expert ffn 2880, vocab 201088, "
+                   "window 128), MXFP4 experts + bf16 attention, random-init",
+                   "bf16 activations / f32 accumulate, MXFP4 expert weights as stored",
+                   "weights (12.5 GB) exceed the 126 MB L2; no flush needed"),
+    "gptoss-tiny": ("tiny gpt-oss (2L, hidden 256, 8 experts top-2), random-init",
+                    "bf16 activations / f32 accumulate, MXFP4 expert weights as stored", "tiny model: smoke configuration only"),
 }
 
 
@@ -110,8 +133,8 @@ def ensure_model(args, rank: int, world: int) -> str:
     done = path + ".done"
     if rank == 0 and not os.path.exists(done):
         from tensorsharp_b200.models import synth
-        synth.write_qwen3(path, **MODEL_SHAPES[args.model], seed=0,
-                          device="cuda" if torch.cuda.is_available() else "cpu")
+        writer = synth.write_gptoss if args.model.startswith("gptoss") else synth.write_qwen3
+        writer(path, **MODEL_SHAPES[args.model], seed=0, device="cuda" if torch.cuda.is_available() else "cpu")
         open(done, "w").write("ok")
     if world > 1:
         import torch.distributed as dist
@@ -225,11 +248,11 @@ def run_ours(args) -> dict:
         "metric": "decode tok/s (device-timed, max over ranks); prefill tok/s and p50 TTFT alongside",
         "value": B * K / (dev_ms / 1e3), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "bf16 activations / f32 accumulate, Q4_K_M weights as stored", "data": "synthetic",
+        "dtype": MODEL_TEXT[args.model][1], "data": "synthetic",
         "impl": "ours",
-        "config": {"model": "Qwen3-4B-shaped Q4_K_M (36L, hidden 2560, 32q/8kv x128, ffn 9728, vocab 151936), "
-                            "random-init", "global_batch": B, "seq_len": P, "decode_steps": K,
-                   "parallelism": f"tp{world}", "l2": "weights (2.4 GB) exceed the 126 MB L2; no flush needed"},
+        "config": {"model": MODEL_TEXT[args.model][0], "global_batch": B, "seq_len": P, "decode_steps": K,
+                   "parallelism": (f"tp{world}" if not args.model.startswith("gptoss") else f"tp{world} attention + ep{world} experts"),
+                   "l2": MODEL_TEXT[args.model][2]},
         "prefill_tok_s": B * P / (prefill_ms / 1e3), "ttft_ms_p50": prefill_ms,
         "e2e": {"value": B * K / (max(e2e_ms, e2e_wall_ms) / 1e3), "unit": "tok/s", "h2d_bytes_per_step": 4 * B,
                 "d2h_bytes_per_step": 4 * B, "ms_per_step_device": e2e_ms / K, "ms_per_step_wall": e2e_wall_ms / K},
@@ -261,6 +284,11 @@ def run_reference(args) -> dict:
         from baseline.ref_harness import run as ref_run
     except Exception as exc:  # noqa: BLE001
         return {"impl": "reference", "unavailable": f"reference harness not importable: {exc}"}
+    if args.model.startswith("gptoss"):
+        if int(os.environ.get("RANK", "0")) != 0:
+            return None
+        return {"impl": "reference", "unavailable": "the reference runs GPT-OSS through its C# per-op graph (GptOssModel.cs); no .NET SDK "
+                                                    "exists on this box and its native library has no whole-model GPT-OSS export"}
     return ref_run(args, MODEL_SHAPES[args.model])
 
 

@@ -7,7 +7,7 @@
 #include "tp_fused.cuh"
 
 enum { ACT_NONE = 0, ACT_SWIGLU = 1, ACT_GEGLU_TANH = 2, ACT_GEGLU_ERF = 3, ACT_SWIGLU_OAI = 4,
-       ACT_RELU2 = 5 };
+       ACT_RELU2 = 5, ACT_SILU = 6 };
 
 __device__ __forceinline__ float act_glu(int act, float g, float u) {
     switch (act) {

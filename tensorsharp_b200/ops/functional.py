@@ -13,6 +13,7 @@ Data conventions
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Optional, Tuple
 
@@ -332,9 +333,14 @@ def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
 # --------------------------------------------------------------------------------------------
 # Mixture of experts
 # --------------------------------------------------------------------------------------------
+MOE_TILE_MAX_PAIRS = int(os.environ.get("TSB_MOE_TILE_MAX_PAIRS", "1024"))
+
+
 def route_topk_softmax(logits: torch.Tensor, k: int):
     """Top-k on the router logits, then softmax over the selected k (GPT-OSS, Qwen3.5 decode;
     GptOssModel.cs:814-865).  Equivalent to softmax over all -> top-k -> renormalise."""
+    if logits.is_cuda and logits.dtype == torch.float32 and logits.shape[-1] <= 1024 and k <= 16:
+        return _k().moe_route(logits.contiguous(), k, mode=0)
     vals, ids = torch.topk(logits.float(), k, dim=-1)
     return ids.to(torch.int32), torch.softmax(vals, -1)
 
@@ -342,6 +348,9 @@ def route_topk_softmax(logits: torch.Tensor, k: int):
 def route_sigmoid(logits: torch.Tensor, k: int, bias: Optional[torch.Tensor], normalize: bool, scale: float):
     """Nemotron-H router: selection on sigmoid(logits) + bias, weights are the unbiased
     sigmoid values, optionally normalised (floor 6.1e-5) and scaled (NemotronModel.cs:822-856)."""
+    if logits.is_cuda and logits.dtype == torch.float32 and logits.shape[-1] <= 1024 and k <= 16:
+        return _k().moe_route(logits.contiguous(), k, mode=1, sel_bias=bias.float().contiguous() if bias is not None else None,
+                              normalize=normalize, scale=scale)
     p = torch.sigmoid(logits.float())
     sel = p + bias.float() if bias is not None else p
     _, ids = torch.topk(sel, k, dim=-1)
@@ -398,6 +407,19 @@ def moe_experts(a: Act, ids: torch.Tensor, weights: torch.Tensor, gate_up: Quant
         return y.view(T, k, D).sum(1) if push is None else None
     if push is not None:
         raise ValueError("moe_experts(push=...) needs a CUDA batch of at most 4 * GEMV_MAX_M slots")
+    if dev.type == "cuda" and T * k <= MOE_TILE_MAX_PAIRS:
+        # medium batches (batched decode): routing stays on the device, each expert's rows are streamed
+        # once per tile of 8 pairs; the launch sequence is fixed, so the step can be graph-captured
+        kk = _k()
+        wts = weights.reshape(-1).float()
+        if down_scale is not None:
+            wts = wts * down_scale[ids.reshape(-1).long()]
+        if gate_up.uses_q8_activations:
+            _ensure_q8(a)
+            return kk.moe_grouped(xq=a.q, xds=a.ds, ids=ids, weights=wts, gate_up=gate_up, down=down, act=act,
+                                  gate_up_bias=gate_up_bias, down_bias=down_bias, expert_offset=expert_offset)
+        return kk.moe_grouped(xb=a.b.contiguous(), ids=ids, weights=wts, gate_up=gate_up, down=down, act=act,
+                              gate_up_bias=gate_up_bias, down_bias=down_bias, expert_offset=expert_offset)
     # grouped path: sort the (token, slot) pairs by expert and run each expert on its rows
     out = torch.zeros((T, D), dtype=torch.float32, device=dev)
     flat = local.reshape(-1)

@@ -120,6 +120,99 @@ def gemv(w: QuantWeight, *, xq=None, xds=None, xb=None, M: int, out_dtype=torch.
     return out
 
 
+def moe_route(logits: torch.Tensor, k: int, *, mode: int = 0, sel_bias=None, normalize: bool = False, scale: float = 1.0):
+    """Router on the device: f32 logits [T, E] -> (ids int32 [T, k], weights f32 [T, k]).  mode 0: top-k
+    then softmax over the selected; mode 1: sigmoid, selection on p + sel_bias, optional renormalise, scale."""
+    assert logits.is_cuda and logits.dtype == torch.float32 and logits.is_contiguous()
+    T, E = logits.shape
+    ids = torch.empty((T, k), dtype=torch.int32, device=logits.device)
+    w = torch.empty((T, k), dtype=torch.float32, device=logits.device)
+    native.check(_lib().tsb_moe_route(_p(logits), _p(sel_bias), C.c_int(T), C.c_int(E), C.c_int(k), C.c_int(mode),
+                                      C.c_int(1 if normalize else 0), C.c_float(scale), _p(ids), _p(w), _stream()), "moe_route")
+    _count(1)
+    return ids, w
+
+
+def moe_grouped(*, xq=None, xds=None, xb=None, ids: torch.Tensor, weights: torch.Tensor, gate_up: QuantWeight,
+                down: QuantWeight, act, gate_up_bias=None, down_bias=None, expert_offset: int = 0) -> torch.Tensor:
+    """Grouped expert projections with the routing kept on the device (no host read-back, fixed launch
+    sequence): group the (token, slot) pairs by local expert, gather activations into that order, run
+    gate/up and down as tile GEMVs (each tile streams its expert's rows once for up to 8 pairs), and
+    sum every token's slots.  ``ids`` are global expert ids [T, k]; pairs whose expert is not in
+    ``[expert_offset, expert_offset + gate_up.experts)`` contribute nothing.  Returns f32 [T, D]."""
+    lib = _lib()
+    T, k = ids.shape
+    P = T * k
+    dev = ids.device
+    E_local = gate_up.experts
+    a = ACT[act]
+    glu = 1 <= a <= 4
+    F_out = gate_up.N // 2 if glu else gate_up.N
+    D, K = down.N, gate_up.K
+    ids = ids.contiguous()
+    pos = torch.empty((P,), dtype=torch.int32, device=dev)
+    max_tiles = int(lib.tsb_moe_max_tiles(C.c_int(P), C.c_int(E_local)))
+    tiles = torch.empty((max_tiles, 4), dtype=torch.int32, device=dev)
+    meta = torch.empty((2,), dtype=torch.int32, device=dev)
+    native.check(lib.tsb_moe_group(_p(ids), C.c_int(P), C.c_int(expert_offset), C.c_int(E_local), _p(pos), _p(tiles), _p(meta),
+                                   _stream()), "moe_group")
+    sq = sds = sb = None
+    if xq is not None:
+        sq = torch.zeros((P, K), dtype=torch.int8, device=dev)
+        sds = torch.zeros((P, K // 32, 2), dtype=torch.float32, device=dev)
+    else:
+        sb = torch.zeros((P, K), dtype=torch.bfloat16, device=dev)
+    sw = torch.zeros((P,), dtype=torch.float32, device=dev)
+    wflat = weights.reshape(-1).float().contiguous()
+    native.check(lib.tsb_moe_gather(_p(pos), C.c_int(P), C.c_int(k), C.c_int(K), _p(xq), _p(xds), _p(xb), _p(wflat), _p(sq),
+                                    _p(sds), _p(sb), _p(sw), _stream()), "moe_gather")
+    gu = torch.zeros((P, F_out), dtype=torch.bfloat16, device=dev)
+    ps = _planes(gate_up)
+    native.check(lib.tsb_moe_gemv_tiles(ps[0], ps[1], ps[2], ps[3], C.c_int(int(gate_up.ggml_type)), C.c_int(gate_up.N), C.c_int(K),
+                                        _p(sq), _p(sds), _p(sb), _p(gu), _p(gate_up_bias), None, _p(tiles), _p(meta),
+                                        C.c_int(max_tiles), C.c_int(0), C.c_int(a), _stream()), "moe_gemv_tiles(gate_up)")
+    y = torch.empty((P, D), dtype=torch.float32, device=dev)
+    ps = _planes(down)
+    if down.uses_q8_activations:
+        gq, gds = quantize_q8(gu)
+        gb = None
+    else:
+        gq = gds = None
+        gb = gu
+    native.check(lib.tsb_moe_gemv_tiles(ps[0], ps[1], ps[2], ps[3], C.c_int(int(down.ggml_type)), C.c_int(D), C.c_int(F_out),
+                                        _p(gq), _p(gds), _p(gb), _p(y), _p(down_bias), _p(sw), _p(tiles), _p(meta),
+                                        C.c_int(max_tiles), C.c_int(1), C.c_int(0), _stream()), "moe_gemv_tiles(down)")
+    out = torch.empty((T, D), dtype=torch.float32, device=dev)
+    native.check(lib.tsb_moe_combine(_p(y), _p(pos), C.c_int(T), C.c_int(k), C.c_int(D), _p(out), _stream()), "moe_combine")
+    _count(5)
+    return out
+
+
+def sample(logits: torch.Tensor, ngen: torch.Tensor, *, temperature: float, top_k: int, top_p: float, min_p: float,
+           repetition_penalty: float = 1.0, presence_penalty: float = 0.0, frequency_penalty: float = 0.0, seed: int = 0,
+           counts: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Draw one token per row of f32 logits [B, V] on the device (reference order of transformations).
+    ``ngen`` [B] int32 counts the tokens drawn so far per row and keys the random stream; ``counts``
+    [B, V] int32 holds the occurrences of each id for the penalties.  Both are advanced by the kernel."""
+    assert logits.is_cuda and logits.dtype == torch.float32 and logits.is_contiguous()
+    B, V = logits.shape
+    if out is None:
+        out = torch.empty((B,), dtype=torch.int32, device=logits.device)
+    native.check(_lib().tsb_sample(_p(logits), _p(counts), _p(ngen), _p(out), C.c_int(B), C.c_int(V), C.c_float(temperature),
+                                   C.c_int(top_k), C.c_float(top_p), C.c_float(min_p), C.c_float(repetition_penalty),
+                                   C.c_float(presence_penalty), C.c_float(frequency_penalty),
+                                   C.c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), _stream()), "sample")
+    _count(1)
+    return out
+
+
+def device_sampler_supports(cfg) -> bool:
+    """Settings the device sampler reproduces exactly (the rest stay with the host sampler)."""
+    if cfg.temperature <= 0:
+        return True
+    return (1 <= cfg.top_k <= 1024) or (cfg.top_k <= 0 and cfg.top_p >= 1.0)
+
+
 def fused_gemv(w: QuantWeight, *, x_f32=None, x_bf16=None, norm_w=None, eps: float = 0.0, do_norm: bool = False,
                out_dtype=torch.float32, bias=None, residual=None, act=None, out: Optional[torch.Tensor] = None,
                push: Optional[int] = None) -> Optional[torch.Tensor]:

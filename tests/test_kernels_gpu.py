@@ -344,3 +344,189 @@ def test_gemv_split_rows(t, M):
         want = x.float() @ qw.dequantize().t()
         got = K().gemv(qw, xb=x, M=M, bias=bias, residual=res)
     assert rel_err(got, want + bias + res) < 2e-3
+
+
+# ---------------------------------------------------------------- device-side MoE routing / grouping
+@pytest.mark.parametrize("E,k", [(32, 4), (128, 8), (256, 8), (6, 2)])
+def test_moe_route_softmax_matches_topk(E, k):
+    torch.manual_seed(20)
+    T = 37
+    logits = torch.randn(T, E, device=DEV)
+    ids, w = K().moe_route(logits, k, mode=0)
+    vals, want_ids = torch.topk(logits, k, dim=-1)
+    assert torch.equal(ids.long(), want_ids)
+    assert torch.allclose(w, torch.softmax(vals, -1), atol=1e-6, rtol=1e-5)
+
+
+def test_moe_route_sigmoid_bias_normalise():
+    torch.manual_seed(21)
+    T, E, k = 19, 64, 6
+    logits = torch.randn(T, E, device=DEV)
+    bias = torch.randn(E, device=DEV) * 0.3
+    ids, w = K().moe_route(logits, k, mode=1, sel_bias=bias, normalize=True, scale=2.5)
+    p = torch.sigmoid(logits)
+    _, want_ids = torch.topk(p + bias, k, dim=-1)
+    ww = p.gather(-1, want_ids)
+    ww = ww / ww.sum(-1, keepdim=True).clamp_min(6.103515625e-5) * 2.5
+    assert torch.equal(ids.long(), want_ids)
+    assert torch.allclose(w, ww, atol=1e-6, rtol=1e-5)
+
+
+@pytest.mark.parametrize("t,act", [(GGMLType.MXFP4, "swiglu_oai"), (GGMLType.Q4_K, "swiglu"), (GGMLType.BF16, "relu2")])
+@pytest.mark.parametrize("e0,E_local", [(0, 8), (4, 4)])
+def test_moe_grouped_matches_per_slot_reference(t, act, e0, E_local):
+    torch.manual_seed(22)
+    E, T, k, Kd, Fd = 8, 45, 3, 256, 512
+    glu = act != "relu2"
+    gu_rows = 2 * Fd if glu else Fd
+    wg = torch.randn(E, gu_rows, Kd, device=DEV) * 0.08
+    wd = torch.randn(E, Kd, Fd, device=DEV) * 0.08
+    gate_up = QuantWeight.from_float(wg[e0:e0 + E_local].contiguous(), t)
+    down = QuantWeight.from_float(wd[e0:e0 + E_local].contiguous(), t)
+    gb = torch.randn(E_local, gu_rows, device=DEV) * 0.1
+    db = torch.randn(E_local, Kd, device=DEV) * 0.1
+    x = torch.randn(T, Kd, device=DEV).bfloat16()
+    ids = torch.stack([torch.randperm(E, device=DEV)[:k] for _ in range(T)]).to(torch.int32)
+    w = torch.rand(T, k, device=DEV)
+    kw = dict(ids=ids, weights=w, gate_up=gate_up, down=down, act=act, gate_up_bias=gb, down_bias=db, expert_offset=e0)
+    if gate_up.uses_q8_activations:
+        xq, xds = K().quantize_q8(x)
+        got = K().moe_grouped(xq=xq, xds=xds, **kw)
+        xr = ref.quantize_q8_dequant(x.float())
+    else:
+        got = K().moe_grouped(xb=x, **kw)
+        xr = x.float()
+    Wg = gate_up.dequantize().view(E_local, gu_rows, Kd)
+    Wd = down.dequantize().view(E_local, Kd, Fd)
+    want = torch.zeros(T, Kd, device=DEV)
+    for tk in range(T):
+        for j in range(k):
+            e = int(ids[tk, j]) - e0
+            if not 0 <= e < E_local:
+                continue
+            y = Wg[e] @ xr[tk] + gb[e]
+            y = ref.glu(act, y[None, :Fd], y[None, Fd:])[0] if glu else torch.relu(y) ** 2
+            y = y.bfloat16().float()
+            if down.uses_q8_activations:
+                y = ref.quantize_q8_dequant(y[None])[0]
+            want[tk] += (Wd[e] @ y + db[e]) * w[tk, j]
+    assert rel_err(got, want) < 1e-2
+
+
+def test_moe_grouped_is_graph_capturable_and_follows_new_routing():
+    torch.manual_seed(23)
+    E, T, k, Kd, Fd = 16, 64, 4, 256, 256
+    gate_up = QuantWeight.from_float(torch.randn(E, 2 * Fd, Kd, device=DEV) * 0.08, GGMLType.MXFP4)
+    down = QuantWeight.from_float(torch.randn(E, Kd, Fd, device=DEV) * 0.08, GGMLType.MXFP4)
+    x = torch.randn(T, Kd, device=DEV).bfloat16()
+    xq, xds = K().quantize_q8(x)
+    logits = torch.randn(T, E, device=DEV)
+    out = torch.zeros(T, Kd, device=DEV)
+
+    def step():
+        ids, w = K().moe_route(logits, k, mode=0)
+        out.copy_(K().moe_grouped(xq=xq, xds=xds, ids=ids, weights=w, gate_up=gate_up, down=down, act="swiglu"))
+    step()
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        step()
+    torch.cuda.current_stream().wait_stream(s)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        step()
+    logits.copy_(torch.randn(T, E, device=DEV))          # a different routing, same graph
+    g.replay()
+    torch.cuda.synchronize()
+    got = out.clone()
+    step()
+    torch.cuda.synchronize()
+    assert torch.equal(got, out)
+
+
+# ---------------------------------------------------------------- device sampler
+def _philox(seed, c0, c1):
+    M = 0xFFFFFFFF
+    k0, k1 = seed & M, (seed >> 32) & M
+    x = [c0, c1, 0x243F6A88, 0x85A308D3]
+    for _ in range(10):
+        p0, p1 = 0xD2511F53 * x[0], 0xCD9E8D57 * x[2]
+        x = [((p1 >> 32) ^ x[1] ^ k0) & M, p1 & M, ((p0 >> 32) ^ x[3] ^ k1) & M, p0 & M]
+        k0, k1 = (k0 + 0x9E3779B9) & M, (k1 + 0xBB67AE85) & M
+    return x
+
+
+def _host_sample(logits, counts, u, temperature, top_k, top_p, min_p, rep, pres, freq):
+    s = logits.double().clone()
+    if counts is not None:
+        seen = counts > 0
+        if rep != 1.0:
+            s = torch.where(seen, torch.where(s > 0, s / rep, s * rep), s)
+        s = torch.where(seen, s - pres - freq * counts.double(), s)
+    if temperature <= 0:
+        return int(s.argmax())
+    probs = torch.softmax(s / temperature, -1)
+    if min_p > 0:
+        probs = torch.where(probs < min_p * probs.max(), torch.zeros_like(probs), probs)
+    if top_k > 0:
+        cp, ci = torch.topk(probs, min(top_k, probs.numel()))
+        if top_p < 1.0:
+            cum = torch.cumsum(cp, 0)
+            hit = torch.nonzero(cum >= top_p)
+            cut = int(hit[0]) + 1 if hit.numel() else cp.numel()
+            cp, ci = cp[:cut], ci[:cut]
+    else:
+        cp, ci = probs, torch.arange(probs.numel(), device=probs.device)
+    cum = torch.cumsum(cp, 0)
+    r = u * float(cum[-1])
+    nz = torch.nonzero((cum >= r) & (cp > 0))
+    return int(ci[int(nz[0])]) if nz.numel() else int(ci[-1])
+
+
+@pytest.mark.parametrize("cfg", [
+    dict(temperature=0.8, top_k=40, top_p=0.9, min_p=0.0, rep=1.1, pres=0.0, freq=0.0),
+    dict(temperature=1.3, top_k=500, top_p=1.0, min_p=0.02, rep=1.0, pres=0.5, freq=0.2),
+    dict(temperature=0.7, top_k=0, top_p=1.0, min_p=0.05, rep=1.0, pres=0.0, freq=0.0),
+    dict(temperature=0.0, top_k=0, top_p=1.0, min_p=0.0, rep=1.3, pres=0.0, freq=0.0),
+])
+def test_device_sampler_matches_host_order(cfg):
+    torch.manual_seed(30)
+    B, V, seed = 48, 5003, 1234
+    logits = (torch.randn(B, V, device=DEV) * 3).contiguous()
+    counts = torch.zeros(B, V, dtype=torch.int32, device=DEV)
+    counts[:, ::7] = 2
+    counts[:, 5] = 1
+    before = counts.clone()
+    ngen = torch.full((B,), 3, dtype=torch.int32, device=DEV)
+    got = K().sample(logits, ngen, temperature=cfg["temperature"], top_k=cfg["top_k"], top_p=cfg["top_p"], min_p=cfg["min_p"],
+                     repetition_penalty=cfg["rep"], presence_penalty=cfg["pres"], frequency_penalty=cfg["freq"], seed=seed,
+                     counts=counts)
+    torch.cuda.synchronize()
+    same = 0
+    for b in range(B):
+        u = (_philox(seed, b, 3)[0] >> 8) / 16777216.0
+        want = _host_sample(logits[b], before[b], u, cfg["temperature"], cfg["top_k"], cfg["top_p"], cfg["min_p"],
+                            cfg["rep"], cfg["pres"], cfg["freq"])
+        same += int(got[b]) == want
+    assert same >= B - 1                       # float32 vs float64 cumulative sums may move one boundary draw
+    assert torch.equal(ngen, torch.full_like(ngen, 4))
+    bump = counts - before
+    assert int(bump.sum()) == B and all(int(bump[b, int(got[b])]) == 1 for b in range(B))
+
+
+def test_device_sampler_distribution_and_seed():
+    torch.manual_seed(31)
+    V, B = 64, 4096
+    row = torch.randn(V, device=DEV) * 2
+    logits = row.repeat(B, 1).contiguous()
+    ngen = torch.zeros(B, dtype=torch.int32, device=DEV)
+    a = K().sample(logits, ngen, temperature=1.0, top_k=8, top_p=1.0, min_p=0.0, seed=7)
+    ngen.zero_()
+    b = K().sample(logits, ngen, temperature=1.0, top_k=8, top_p=1.0, min_p=0.0, seed=7)
+    assert torch.equal(a, b)                   # same seed, same counters: same draws
+    top = torch.topk(row, 8)
+    p = torch.softmax(top.values, -1)
+    freq = torch.bincount(a.long(), minlength=V).float() / B
+    assert float(freq.sum() - freq[top.indices].sum()) == 0.0
+    assert torch.allclose(freq[top.indices], p, atol=0.03)
