@@ -18,6 +18,7 @@
 // mmid.cu), ggml_cuda_mul_mat_id and the host-side routing loops of GptOssModel.cs:814-865,
 // Qwen35Model.cs:1931-2402 and NemotronModel.cs:822-856, which read the router output back to the
 // host for every layer.
+#include <cstdlib>
 #include "gemv_core.cuh"
 
 #define MOE_TILE_ROWS 8
@@ -29,6 +30,7 @@
 // mode 0: top-k of the logits, weights = softmax over the selected logits.
 // mode 1: p = sigmoid(logit); select on p + sel_bias; weights = p, optionally / max(sum, 6.1e-5); * scale.
 // ---------------------------------------------------------------------------------------------
+template <int PER>
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ sel_bias,
                                                         int T, int E, int k, int mode, int normalize, float scale,
                                                         int* __restrict__ ids, float* __restrict__ wts) {
@@ -36,8 +38,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     pdl_wait();
     pdl_trigger();
     if (t >= T) return;
-    constexpr int PER = MOE_MAX_E / 32;
-    float sel[PER], val[PER];
+    float sel[PER], val[PER];                   // PER = ceil(E / 32) rounded up to an instantiated size
     const float* row = logits + (long)t * E;
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
@@ -106,8 +107,14 @@ extern "C" int tsb_moe_route(const float* logits, const float* sel_bias, int T, 
     TSB_CHECK_ARG(E > 0 && E <= MOE_MAX_E, "moe_route: %d experts (limit %d)", E, MOE_MAX_E);
     TSB_CHECK_ARG(k > 0 && k <= MOE_MAX_K && k <= E, "moe_route: top-%d of %d", k, E);
     if (T == 0) return TSB_OK;
-    TSB_CHECK_CUDA(tsb_launch(moe_route_kernel, dim3((T + 3) / 4), dim3(128), 0, (cudaStream_t)stream, logits, sel_bias, T, E, k,
-                              mode, normalize, scale, ids, wts));
+    const dim3 grid((T + 3) / 4), block(128);
+    cudaStream_t st = (cudaStream_t)stream;
+#define TSB_ROUTE(P) TSB_CHECK_CUDA(tsb_launch(moe_route_kernel<P>, grid, block, 0, st, logits, sel_bias, T, E, k, mode, normalize, scale, ids, wts))
+    if (E <= 32) TSB_ROUTE(1);
+    else if (E <= 128) TSB_ROUTE(4);
+    else if (E <= 256) TSB_ROUTE(8);
+    else TSB_ROUTE(MOE_MAX_E / 32);
+#undef TSB_ROUTE
     TSB_CHECK_LAUNCH();
     return TSB_OK;
 }
@@ -288,6 +295,130 @@ __global__ void __launch_bounds__(128) gemv_tiles_kernel(TileArgs a) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Tensor-core tile GEMV for 4-bit blocks of 32 (MXFP4, Q4_0).  The 8 activation rows of a tile are
+// exactly the N of an int8 m16n8k32 MMA and one quant block is exactly its K, so a warp computes
+// 16 output rows x 8 pairs per block with one instruction: A = the block's codes decoded to int8
+// (lane (g, t) loads the 4 bytes that hold elements 4t..4t+3 and 16+4t..16+4t+3 of rows g and g+8,
+// which is the A fragment as it stands), B = the int8 activations, and the int32 result is scaled by
+// weight scale x activation scale into float accumulators.  Activations are read once per 16 rows
+// instead of once per row, which is what bounds the dp4a version at 8 rows per tile.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_s8_16x8x32(int (&c)[4], const int (&a)[4], int b0, int b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <bool MX>
+__device__ __forceinline__ void decode_q4_words(uint32_t wg, uint32_t wg8, int (&a)[4]) {
+    if (MX) {
+        a[0] = mxfp4_lut4(wg & 0x0F0F0F0Fu);
+        a[1] = mxfp4_lut4(wg8 & 0x0F0F0F0Fu);
+        a[2] = mxfp4_lut4((wg >> 4) & 0x0F0F0F0Fu);
+        a[3] = mxfp4_lut4((wg8 >> 4) & 0x0F0F0F0Fu);
+    } else {
+        a[0] = (int)__vsub4(wg & 0x0F0F0F0Fu, 0x08080808u);
+        a[1] = (int)__vsub4(wg8 & 0x0F0F0F0Fu, 0x08080808u);
+        a[2] = (int)__vsub4((wg >> 4) & 0x0F0F0F0Fu, 0x08080808u);
+        a[3] = (int)__vsub4((wg8 >> 4) & 0x0F0F0F0Fu, 0x08080808u);
+    }
+}
+
+template <bool MX>
+__device__ __forceinline__ float q4_block_scale(const QW& w, long row, int kb, int u) {
+    if (MX) return e8m0_half_scale(w.p1[row * kb + u]);
+    return __half2float(reinterpret_cast<const __half*>(w.p1)[row * kb + u]);
+}
+
+template <bool GLU, bool MX>
+__global__ void __launch_bounds__(128) gemv_tiles_mma_kernel(TileArgs a) {
+    constexpr int S = GLU ? 2 : 1;               // weight row sets per warp: gate (+ up)
+    constexpr int U = 2;                         // k-blocks in flight per iteration
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int r0 = (blockIdx.x * 4 + (threadIdx.x >> 5)) * 16;
+    pdl_wait();
+    pdl_trigger();
+    if ((int)blockIdx.y >= a.meta[0] || r0 >= a.n_out) return;
+    const int4 tile = a.tiles[blockIdx.y];
+    const int expert = tile.x, row0 = tile.y, mv = tile.z;
+    const int K = a.w.K, kb = K >> 5;
+    // weight rows of this lane (clamped at the edge; surplus rows are never stored)
+    long wr[S][2];
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+        wr[s][0] = (long)expert * a.w.N + s * a.n_out + min(r0 + g, a.n_out - 1);
+        wr[s][1] = (long)expert * a.w.N + s * a.n_out + min(r0 + g + 8, a.n_out - 1);
+    }
+    const bool bact = g < mv;
+    const int8_t* xrow = a.xq + (long)(row0 + (bact ? g : 0)) * K + 4 * t;
+    const int c0 = 2 * t, c1 = 2 * t + 1;
+    const float2* xs0 = a.xds + (long)(row0 + (c0 < mv ? c0 : 0)) * kb;
+    const float2* xs1 = a.xds + (long)(row0 + (c1 < mv ? c1 : 0)) * kb;
+    float acc[S][4];
+#pragma unroll
+    for (int s = 0; s < S; ++s)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[s][i] = 0.f;
+    for (int u0 = 0; u0 < kb; u0 += U) {
+        uint32_t wq[U][S][2];
+        float ws[U][S][2];
+        int b0[U], b1[U];
+        float xd0[U], xd1[U];
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            const int u = min(u0 + j, kb - 1);
+#pragma unroll
+            for (int s = 0; s < S; ++s)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    wq[j][s][h] = __ldg(reinterpret_cast<const uint32_t*>(a.w.p0 + wr[s][h] * (K >> 1) + u * 16 + 4 * t));
+                    ws[j][s][h] = q4_block_scale<MX>(a.w, wr[s][h], kb, u);
+                }
+            b0[j] = bact ? *reinterpret_cast<const int*>(xrow + u * 32) : 0;
+            b1[j] = bact ? *reinterpret_cast<const int*>(xrow + u * 32 + 16) : 0;
+            xd0[j] = xs0[u].x;
+            xd1[j] = xs1[u].x;
+        }
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            if (u0 + j >= kb) break;
+#pragma unroll
+            for (int s = 0; s < S; ++s) {
+                int af[4], c[4] = {0, 0, 0, 0};
+                decode_q4_words<MX>(wq[j][s][0], wq[j][s][1], af);
+                mma_s8_16x8x32(c, af, b0[j], b1[j]);
+                acc[s][0] += ws[j][s][0] * xd0[j] * (float)c[0];
+                acc[s][1] += ws[j][s][0] * xd1[j] * (float)c[1];
+                acc[s][2] += ws[j][s][1] * xd0[j] * (float)c[2];
+                acc[s][3] += ws[j][s][1] * xd1[j] * (float)c[3];
+            }
+        }
+    }
+    // thread (g, t) holds rows r0 + g, r0 + g + 8 for pairs 2t, 2t + 1
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = r0 + g + (i >> 1) * 8, col = 2 * t + (i & 1);
+        if (r >= a.n_out || col >= mv) continue;
+        float v = acc[0][i];
+        if (a.bias) v += a.bias[(long)expert * a.w.N + r];
+        if (GLU) {
+            float up = acc[S - 1][i];
+            if (a.bias) up += a.bias[(long)expert * a.w.N + r + a.n_out];
+            v = act_glu(a.act, v, up);
+        } else if (a.act == ACT_RELU2) {
+            v = fmaxf(v, 0.f);
+            v = v * v;
+        } else if (a.act == ACT_SILU) {
+            v = v / (1.f + __expf(-v));
+        }
+        if (a.row_scale) v *= a.row_scale[row0 + col];
+        const long o = (long)(row0 + col) * a.n_out + r;
+        if (a.out_f32) reinterpret_cast<float*>(a.out)[o] = v;
+        else reinterpret_cast<bf16*>(a.out)[o] = f2bf(v);
+    }
+}
+
 extern "C" int tsb_moe_gemv_tiles(const void* p0, const void* p1, const void* p2, const void* p3, int type, int N, int K,
                                   const void* xq, const void* xds, const void* xb, void* out, const float* bias,
                                   const float* row_scale, const void* tiles, const int* meta, int max_tiles, int out_f32,
@@ -308,6 +439,20 @@ extern "C" int tsb_moe_gemv_tiles(const void* p0, const void* p1, const void* p2
     a.xq = (const int8_t*)xq; a.xds = (const float2*)xds; a.xb = (const bf16*)xb;
     a.out = out; a.bias = bias; a.row_scale = row_scale; a.tiles = (const int4*)tiles; a.meta = meta;
     a.out_f32 = out_f32; a.act = act; a.n_out = glu ? N / 2 : N;
+    static const bool use_mma = []() { const char* e = getenv("TSB_MOE_MMA"); return !e || atoi(e) != 0; }();
+    if (use_mma && (type == TSB_MXFP4 || type == TSB_Q4_0)) {
+        dim3 grid((a.n_out + 63) / 64, max_tiles), block(128);
+        cudaStream_t st = (cudaStream_t)stream;
+        if (type == TSB_MXFP4) {
+            if (glu) TSB_CHECK_CUDA(tsb_launch(gemv_tiles_mma_kernel<true, true>, grid, block, 0, st, a));
+            else TSB_CHECK_CUDA(tsb_launch(gemv_tiles_mma_kernel<false, true>, grid, block, 0, st, a));
+        } else {
+            if (glu) TSB_CHECK_CUDA(tsb_launch(gemv_tiles_mma_kernel<true, false>, grid, block, 0, st, a));
+            else TSB_CHECK_CUDA(tsb_launch(gemv_tiles_mma_kernel<false, false>, grid, block, 0, st, a));
+        }
+        TSB_CHECK_LAUNCH();
+        return TSB_OK;
+    }
     dim3 grid((a.n_out + 3) / 4, max_tiles), block(128);
     if (glu) TSB_CHECK_CUDA(tsb_launch(gemv_tiles_kernel<true>, grid, block, 0, (cudaStream_t)stream, a));
     else TSB_CHECK_CUDA(tsb_launch(gemv_tiles_kernel<false>, grid, block, 0, (cudaStream_t)stream, a));
