@@ -32,6 +32,10 @@ struct AttnArgs {
     // Prefill only.  Context parallelism runs the kernel once per KV shard and merges the partial results:
     const int* q_pos0;        // [B] cache position of each sequence's first query, or null = kv_len - q_len
     float* lse_out;           // [Tq, Hq] log-sum-exp of the scaled scores seen by this call (-inf if none), or null
+    // Decode only: the output again as int8 groups of 32 with (scale, sum), the form the following
+    // quantised projection reads, so that no separate quantise launch is needed.  Null = not wanted.
+    int8_t* out_q;            // [B, Hq * Dh]
+    float2* out_ds;           // [B, Hq * Dh / 32]
 };
 
 __device__ __forceinline__ long kv_slot(const AttnArgs& a, int b, int j) {
@@ -203,7 +207,20 @@ __global__ void attn_combine_kernel(AttnArgs a) {
         ll += a.part_ml[(base + s) * 2 + 1] * c;
         if (d < a.Dh) o += a.part_o[(base + s) * a.Dh + d] * c;
     }
-    if (d < a.Dh) a.out[((long)b * a.Hq + h) * a.Dh + d] = f2bf(ll > 0.f ? o / ll : 0.f);
+    const bf16 ob = f2bf(ll > 0.f ? o / ll : 0.f);
+    if (d < a.Dh) a.out[((long)b * a.Hq + h) * a.Dh + d] = ob;
+    if (a.out_q != nullptr) {
+        // a warp holds 32 consecutive dims = one group (Dh is a multiple of 32); same arithmetic as quantize_q8_kernel
+        const float v = d < a.Dh ? bf2f(ob) : 0.f;
+        const float amax = warp_max(fabsf(v));
+        const float sum = warp_sum(v);
+        const float dq = amax / 127.f;
+        const long e = ((long)b * a.Hq + h) * a.Dh + d;
+        if (d < a.Dh) {
+            a.out_q[e] = (int8_t)__float2int_rn(amax > 0.f ? v / dq : 0.f);
+            if ((d & 31) == 0) a.out_ds[e >> 5] = make_float2(dq, sum);
+        }
+    }
 }
 
 template <int DH>

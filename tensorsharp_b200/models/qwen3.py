@@ -104,7 +104,8 @@ class Qwen3Model(ModelBase):
             qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=self.kv.k[l],
                                   v_cache=self.kv.v[l], rope=self.rope, qn=L["q_norm"], kn=L["k_norm"], eps=c.eps)
             qr = self.q_post_scale(qr, batch)
-            o = F.attention(qr, self.kv.k[l], self.kv.v[l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh)
+            o = F.attention(qr, self.kv.k[l], self.kv.v[l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh,
+                            as_act=small and L["wo"].uses_q8_activations)
             if tpx is not None:
                 tpx.linear_push(F.as_act(o), L["wo"])
                 a = tpx.reduce_norm(h, L["ffn_norm"], c.eps)
@@ -134,8 +135,8 @@ class Qwen3Model(ModelBase):
             qkv = F.linear(a, L["wqkv"], bias=L.get("qkv_bias"), out_dtype=mid)
             return (qkv[:, :Hq * Dh].view(T, Hq, Dh), qkv[:, Hq * Dh:(Hq + Hkv) * Dh].view(T, Hkv, Dh),
                     qkv[:, (Hq + Hkv) * Dh:].view(T, Hkv, Dh))
-        return (F.linear(a, L["wq"], out_dtype=mid).view(T, Hq, Dh), F.linear(a, L["wk"], out_dtype=mid).view(T, Hkv, Dh),
-                F.linear(a, L["wv"], out_dtype=mid).view(T, Hkv, Dh))
+        q, k, v = F.linear_multi(a, (L["wq"], L["wk"], L["wv"]), out_dtype=mid)
+        return q.view(T, Hq, Dh), k.view(T, Hkv, Dh), v.view(T, Hkv, Dh)
 
     def forward_fused_small(self, h: torch.Tensor, batch: Batch, want_logits: bool) -> Optional[torch.Tensor]:
         """Decode-sized batches (at most ``F.FUSED_MAX_M`` rows) on CUDA: every projection does its

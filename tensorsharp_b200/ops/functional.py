@@ -114,12 +114,17 @@ def norm_add(x: torch.Tensor, w: Optional[torch.Tensor], eps: float, h: torch.Te
     return h + ref.rmsnorm(x, w, eps)
 
 
-def as_act(x: torch.Tensor, w: Optional[QuantWeight] = None) -> Act:
-    """Wrap a plain activation tensor; quantises to q8 on CUDA when the weight needs it."""
+def as_act(x, w: Optional[QuantWeight] = None) -> Act:
+    """Wrap a plain activation tensor (an ``Act`` passes through)."""
+    if isinstance(x, Act):
+        return x
     if not x.is_cuda:
         return Act(x.float())
     a = Act(x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16))
     return a
+
+
+as_act_of = as_act
 
 
 def _ensure_q8(a: Act) -> Act:
@@ -218,6 +223,27 @@ def linear(a: Act, w: QuantWeight, *, bias: Optional[torch.Tensor] = None, resid
     return out if out.dtype == out_dtype else out.to(out_dtype)
 
 
+def linear_multi(a: Act, ws, *, out_dtype=torch.float32):
+    """``[a @ w^T for w in ws]`` for matrices that share the input.  Decode-sized CUDA batches run them
+    as one launch (the separate Q / K / V projections of files whose tensors differ in quantisation
+    type); anything else is the plain sequence of ``linear`` calls."""
+    ws = list(ws)
+    T = a.T
+    if (ws[0].device.type == "cuda" and T <= GEMV_MAX_M and 2 <= len(ws) <= 3 and all(w.experts == 1 and w.K == ws[0].K for w in ws)
+            and len({w.uses_q8_activations for w in ws}) == 1):
+        if ws[0].uses_q8_activations:
+            _ensure_q8(a)
+            y = _k().gemv_multi(ws, xq=a.q, xds=a.ds, M=T, out_dtype=out_dtype)
+        else:
+            y = _k().gemv_multi(ws, xb=a.b.contiguous(), M=T, out_dtype=out_dtype)
+        outs, o = [], 0
+        for w in ws:
+            outs.append(y[:, o:o + w.N])
+            o += w.N
+        return outs
+    return [linear(a, w, out_dtype=out_dtype) for w in ws]
+
+
 def glu(act: str, gate: torch.Tensor, up: Optional[torch.Tensor]) -> torch.Tensor:
     """Standalone gated activation on two [T, F] tensors (row-strided views allowed)."""
     if not gate.is_cuda:
@@ -292,9 +318,19 @@ def decode_splits(batch: Batch, Hkv: int, window: int) -> int:
 
 def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, batch: Batch, *, scale: float,
               Hq: int, Hkv: int, Dh: int, window: int = 0, sinks: Optional[torch.Tensor] = None,
-              softcap: float = 0.0) -> torch.Tensor:
-    """Causal attention of the packed queries against the paged cache -> [T, Hq * Dh]."""
+              softcap: float = 0.0, as_act: bool = False):
+    """Causal attention of the packed queries against the paged cache -> [T, Hq * Dh].  ``as_act`` returns an
+    ``Act``; on the CUDA decode path it already carries the int8 form written by the combine kernel, so
+    the quantised projection that follows needs no quantise launch."""
     T = q.shape[0]
+    if as_act:
+        if q.is_cuda and batch.is_decode and (Hq // Hkv) in (1, 2, 4, 8) and Dh % 32 == 0:
+            out, oq, ods = _k().attn_decode(q, k_cache, v_cache, batch.block_table, batch.kv_lens, scale=scale, Hq=Hq, Hkv=Hkv,
+                                            Dh=Dh, page_size=batch.page_size, splits=decode_splits(batch, Hkv, window),
+                                            sinks=sinks, softcap=softcap, window=window, want_q8=True)
+            return Act(out.view(T, Hq * Dh), oq, ods)
+        return as_act_of(attention(q, k_cache, v_cache, batch, scale=scale, Hq=Hq, Hkv=Hkv, Dh=Dh, window=window, sinks=sinks,
+                                   softcap=softcap))
     if q.is_cuda:
         kk = _k()
         G = Hq // Hkv

@@ -58,7 +58,8 @@ class AttnArgs(C.Structure):
                 ("kv_lens", _vp), ("cu_q", _vp), ("sinks", _vp), ("part_o", _vp), ("part_ml", _vp),
                 ("scale", C.c_float), ("softcap", C.c_float), ("window", C.c_int),
                 ("B", C.c_int), ("Hq", C.c_int), ("Hkv", C.c_int), ("Dh", C.c_int), ("page_size", C.c_int),
-                ("max_pages", C.c_int), ("splits", C.c_int), ("q_pos0", _vp), ("lse_out", _vp)]
+                ("max_pages", C.c_int), ("splits", C.c_int), ("q_pos0", _vp), ("lse_out", _vp),
+                ("out_q", _vp), ("out_ds", _vp)]
 
 
 _configured = False
@@ -116,6 +117,23 @@ def gemv(w: QuantWeight, *, xq=None, xds=None, xb=None, M: int, out_dtype=torch.
                                       C.c_int(M), C.c_int(problems), C.c_int(x_div),
                                       C.c_int(1 if (out is None or out.dtype == torch.float32) else 0), C.c_int(a),
                                       C.c_void_p(push) if push else None, _stream()), "gemv")
+    _count(1)
+    return out
+
+
+def gemv_multi(ws, *, xq=None, xds=None, xb=None, M: int, out_dtype=torch.float32) -> torch.Tensor:
+    """Two or three weight matrices over the same activations in one launch -> [M, sum of rows]."""
+    n = len(ws)
+    planes = (C.c_void_p * (4 * n))()
+    for i, w in enumerate(ws):
+        for j, p in enumerate(_planes(w)):
+            planes[4 * i + j] = p.value if hasattr(p, "value") else p
+    types = (C.c_int * n)(*[int(w.ggml_type) for w in ws])
+    rows = (C.c_int * n)(*[w.N for w in ws])
+    total = sum(w.N for w in ws)
+    out = torch.empty((M, total), dtype=out_dtype, device=ws[0].device)
+    native.check(_lib().tsb_gemv_multi(planes, types, rows, C.c_int(n), C.c_int(ws[0].K), _p(xq), _p(xds), _p(xb), _p(out),
+                                       C.c_int(M), C.c_int(1 if out_dtype == torch.float32 else 0), _stream()), "gemv_multi")
     _count(1)
     return out
 
@@ -362,8 +380,9 @@ def _attn_args(q, k_cache, v_cache, out, block_table, kv_lens, cu_q, sinks, scal
 
 
 def attn_decode(q, k_cache, v_cache, block_table, kv_lens, *, scale, Hq, Hkv, Dh, page_size, splits, sinks=None,
-                softcap=0.0, window=0, out=None):
-    """q [B, Hq, Dh] bf16; one query per sequence against the paged cache."""
+                softcap=0.0, window=0, out=None, want_q8=False):
+    """q [B, Hq, Dh] bf16; one query per sequence against the paged cache.  ``want_q8`` also returns the
+    output as int8 groups of 32 with (scale, sum) written by the combine kernel: (out, q, ds)."""
     B = q.shape[0]
     if out is None:
         out = torch.empty_like(q)
@@ -373,9 +392,14 @@ def attn_decode(q, k_cache, v_cache, block_table, kv_lens, *, scale, Hq, Hkv, Dh
     part_o = torch.empty((B, Hq, splits, Dh), dtype=torch.float32, device=q.device)
     part_ml = torch.empty((B, Hq, splits, 2), dtype=torch.float32, device=q.device)
     a.part_o, a.part_ml = _p(part_o), _p(part_ml)
+    oq = ods = None
+    if want_q8 and Dh % 32 == 0:
+        oq = torch.empty((B, Hq * Dh), dtype=torch.int8, device=q.device)
+        ods = torch.empty((B, Hq * Dh // 32, 2), dtype=torch.float32, device=q.device)
+        a.out_q, a.out_ds = oq.data_ptr(), ods.data_ptr()
     native.check(_lib().tsb_attn_decode(C.byref(a), _stream()), "attn_decode")
     _count(2)
-    return out
+    return (out, oq, ods) if want_q8 else out
 
 
 def attn_prefill(q, k_cache, v_cache, block_table, kv_lens, cu_q, max_q_len, *, scale, Hq, Hkv, Dh, page_size,

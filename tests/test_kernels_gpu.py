@@ -530,3 +530,38 @@ def test_device_sampler_distribution_and_seed():
     freq = torch.bincount(a.long(), minlength=V).float() / B
     assert float(freq.sum() - freq[top.indices].sum()) == 0.0
     assert torch.allclose(freq[top.indices], p, atol=0.03)
+
+
+def test_gemv_multi_matches_separate_launches():
+    torch.manual_seed(40)
+    Kd = 512
+    ws = [QuantWeight.from_float(torch.randn(n, Kd, device=DEV) * 0.05, t)
+          for n, t in ((96, GGMLType.Q4_K), (32, GGMLType.Q4_K), (40, GGMLType.Q6_K))]
+    for M in (1, 3, 8, 11):
+        x = torch.randn(M, Kd, device=DEV).bfloat16()
+        xq, xds = K().quantize_q8(x)
+        got = K().gemv_multi(ws, xq=xq, xds=xds, M=M)
+        want = torch.cat([K().gemv(w, xq=xq, xds=xds, M=M) for w in ws], 1)
+        assert torch.equal(got, want)
+    wf = [QuantWeight.from_float(torch.randn(n, Kd, device=DEV) * 0.05, GGMLType.BF16) for n in (24, 8)]
+    x = torch.randn(2, Kd, device=DEV).bfloat16()
+    got = K().gemv_multi(wf, xb=x, M=2, out_dtype=torch.bfloat16)
+    want = torch.cat([K().gemv(w, xb=x, M=2, out_dtype=torch.bfloat16) for w in wf], 1)
+    assert torch.equal(got, want)
+
+
+def test_attn_decode_q8_output_equals_separate_quantise():
+    torch.manual_seed(41)
+    B, Hq, Hkv, Dh, ps, ctx = 3, 8, 2, 128, 64, 200
+    n_pages = B * 4
+    kc = torch.randn(n_pages * ps, Hkv, Dh, device=DEV).bfloat16()
+    vc = torch.randn(n_pages * ps, Hkv, Dh, device=DEV).bfloat16()
+    table = torch.arange(n_pages, dtype=torch.int32, device=DEV).view(B, 4)
+    lens = torch.tensor([ctx, 77, 130], dtype=torch.int32, device=DEV)
+    q = torch.randn(B, Hq, Dh, device=DEV).bfloat16()
+    kw = dict(scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh, page_size=ps, splits=3)
+    plain = K().attn_decode(q, kc, vc, table, lens, **kw)
+    out, oq, ods = K().attn_decode(q, kc, vc, table, lens, want_q8=True, **kw)
+    assert torch.equal(out, plain)
+    wq, wds = K().quantize_q8(plain.view(B, Hq * Dh))
+    assert torch.equal(oq, wq) and torch.equal(ods, wds)
