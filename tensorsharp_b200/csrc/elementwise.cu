@@ -530,10 +530,91 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* logits, long 
     }
 }
 
+// Large vocabularies: the row is cut into chunks of 4096 logits, one CTA each; every CTA leaves its
+// best (value, index) in a per-device scratch and takes a ticket, and the CTA that draws the last
+// ticket of a row merges the chunk results and resets the ticket counter for the next call.  Calls
+// on one device share the scratch, so they must be ordered (same stream), as the decode loop's are.
+#define ARGMAX_CHUNK 4096
+#define ARGMAX_MAX_CHUNKS 128
+#define ARGMAX_MAX_ROWS 1024
+static __device__ float g_argmax_val[ARGMAX_MAX_ROWS * ARGMAX_MAX_CHUNKS];
+static __device__ int g_argmax_idx[ARGMAX_MAX_ROWS * ARGMAX_MAX_CHUNKS];
+static __device__ unsigned g_argmax_ticket[ARGMAX_MAX_ROWS];
+
+__global__ void __launch_bounds__(256) argmax_chunk_kernel(const float* logits, long stride, int V, int chunks, int* out_idx,
+                                                           float* out_val) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    __shared__ bool last;
+    pdl_wait();
+    pdl_trigger();
+    const int row = blockIdx.y, ch = blockIdx.x, lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const float* r = logits + row * stride;
+    const int i0 = ch * ARGMAX_CHUNK, i1 = min(V, i0 + ARGMAX_CHUNK);
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = i0 + threadIdx.x * 4; i < i1; i += 1024) {
+        if (i + 3 < i1 && ((reinterpret_cast<size_t>(r + i) & 15) == 0)) {
+            const float4 v = *reinterpret_cast<const float4*>(r + i);
+            const float vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (vv[j] > best) { best = vv[j]; bi = i + j; }
+        } else {
+            for (int j = i; j < min(i + 4, i1); ++j)
+                if (r[j] > best) { best = r[j]; bi = j; }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) { sv[w] = best; si[w] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int i = 1; i < 8; ++i)
+            if (sv[i] > best || (sv[i] == best && si[i] < bi)) { best = sv[i]; bi = si[i]; }
+        g_argmax_val[row * ARGMAX_MAX_CHUNKS + ch] = best;
+        g_argmax_idx[row * ARGMAX_MAX_CHUNKS + ch] = bi;
+        __threadfence();
+        last = atomicAdd(&g_argmax_ticket[row], 1u) == (unsigned)chunks - 1u;
+    }
+    __syncthreads();
+    if (!last || w != 0) return;
+    __threadfence();
+    best = -INFINITY;
+    bi = 0x7fffffff;
+    for (int c = lane; c < chunks; c += 32) {
+        const float v = __ldcg(&g_argmax_val[row * ARGMAX_MAX_CHUNKS + c]);
+        const int i = __ldcg(&g_argmax_idx[row * ARGMAX_MAX_CHUNKS + c]);
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) {
+        out_idx[row] = bi == 0x7fffffff ? 0 : bi;
+        if (out_val) out_val[row] = best;
+        g_argmax_ticket[row] = 0u;
+    }
+}
+
 extern "C" int tsb_argmax(const float* logits, long stride, long rows, int V, int* out_idx, float* out_val,
                           void* stream) {
     if (rows == 0) return TSB_OK;
     TSB_CHECK_ARG(V > 0, "argmax: empty vocabulary");
+    const int chunks = (V + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
+    if (chunks >= 4 && chunks <= ARGMAX_MAX_CHUNKS && rows <= ARGMAX_MAX_ROWS) {
+        TSB_CHECK_CUDA(tsb_launch(argmax_chunk_kernel, dim3(chunks, (unsigned)rows), dim3(256), 0, (cudaStream_t)stream, logits,
+                                  stride, V, chunks, out_idx, out_val));
+        TSB_CHECK_LAUNCH();
+        return TSB_OK;
+    }
     TSB_CHECK_CUDA(tsb_launch(argmax_kernel, dim3((unsigned)rows), dim3(1024), 0, (cudaStream_t)stream, logits, stride, V, out_idx, out_val));
     TSB_CHECK_LAUNCH();
     return TSB_OK;

@@ -98,8 +98,11 @@ __global__ void __launch_bounds__(128) gemv_kernel(GemvArgs a) {
 #pragma unroll
     for (int m = 0; m < M; ++m) { acc[m] = 0.f; acc2[m] = 0.f; }
     const int mv = a.ids ? 1 : min(M, a.M - orow);
-    dot_row<M>(a.w, wrow, lane, xq, xds, xb, acc, mv, PdlWait{a.ids == nullptr});
-    if (GLU) dot_row<M>(a.w, wrow + n_out, lane, xq, xds, xb, acc2, mv, PdlWait{false});
+    if (GLU && M <= 4) dot_row2<M>(a.w, wrow, wrow + n_out, lane, xq, xds, xb, acc, acc2, mv, PdlWait{a.ids == nullptr});
+    else {
+        dot_row<M>(a.w, wrow, lane, xq, xds, xb, acc, mv, PdlWait{a.ids == nullptr});
+        if (GLU) dot_row<M>(a.w, wrow + n_out, lane, xq, xds, xb, acc2, mv, PdlWait{false});
+    }
 #pragma unroll
     for (int m = 0; m < M; ++m) {
         acc[m] = warp_sum(acc[m]);
@@ -287,6 +290,9 @@ extern "C" int tsb_quantize_q8(const void* x, int x_is_f32, void* xq, void* xds,
     return TSB_OK;
 }
 
+bool tsb_gemv_stream_eligible(const GemvArgs& a);                     // gemv_stream.cu
+int tsb_gemv_stream_launch(const GemvArgs& a, bool glu, cudaStream_t s);
+
 template <bool GLU>
 static int launch_gemv(const GemvArgs& a, int problems, cudaStream_t s) {
     const int rows = a.n_out;
@@ -357,6 +363,7 @@ extern "C" int tsb_gemv_push(const void* p0, const void* p1, const void* p2, con
     a.M = M; a.x_div = x_div > 0 ? x_div : 1; a.out_f32 = out_f32; a.act = act;
     a.n_out = glu ? N / 2 : N;
     a.push = (const TpPush*)push;
+    if (tsb_gemv_stream_eligible(a)) return tsb_gemv_stream_launch(a, glu, (cudaStream_t)stream);
     return glu ? launch_gemv<true>(a, problems, (cudaStream_t)stream)
                : launch_gemv<false>(a, problems, (cudaStream_t)stream);
 }

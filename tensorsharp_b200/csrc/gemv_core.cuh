@@ -323,3 +323,38 @@ struct PdlWait {
         if (on) { pdl_wait(); pdl_trigger(); }
     }
 };
+
+// Two rows of the same matrix against the same activations (the gate and up rows of a GLU pair) in
+// one loop: both rows' loads are in flight together, so the pair costs one latency chain, not two.
+#define TSB_ROW_LOOP2(WT, LOAD, COMP, UNITS)                                       \
+    {                                                                             \
+        const int units = (UNITS);                                                \
+        WT ca, cb, na, nb;                                                        \
+        int u = lane;                                                             \
+        if (u < units) { LOAD(w, row_a, u, ca); LOAD(w, row_b, u, cb); }          \
+        pre();                                                                    \
+        for (; u < units; u += 32) {                                              \
+            const bool more = u + 32 < units;                                     \
+            if (more) { LOAD(w, row_a, u + 32, na); LOAD(w, row_b, u + 32, nb); } \
+            COMP(w, ca, u, xq, xds, acc_a, mv);                                   \
+            COMP(w, cb, u, xq, xds, acc_b, mv);                                   \
+            if (more) { ca = na; cb = nb; }                                       \
+        }                                                                         \
+    }
+
+template <int M, class Pre>
+__device__ __forceinline__ void dot_row2(const QW& w, long row_a, long row_b, int lane, const int8_t* xq, const float2* xds,
+                                         const bf16* xb, float* acc_a, float* acc_b, int mv, Pre pre) {
+    switch (w.type) {
+    case TSB_Q4_K: TSB_ROW_LOOP2(WQ4K, load_q45k<false>, (comp_q45k<M, false>), (w.K >> 8) << 3) break;
+    case TSB_Q5_K: TSB_ROW_LOOP2(WQ4K, load_q45k<true>, (comp_q45k<M, true>), (w.K >> 8) << 3) break;
+    case TSB_Q6_K: TSB_ROW_LOOP2(WQ6K, load_q6k, comp_q6k<M>, (w.K >> 8) << 2) break;
+    case TSB_Q8_0: TSB_ROW_LOOP2(WQ80, load_q8_0, comp_q8_0<M>, w.K >> 5) break;
+    case TSB_MXFP4: TSB_ROW_LOOP2(WQ432, load_q4_32<true>, (comp_q4_32<M, true>), w.K >> 5) break;
+    case TSB_Q4_0: TSB_ROW_LOOP2(WQ432, load_q4_32<false>, (comp_q4_32<M, false>), w.K >> 5) break;
+    default:
+        dot_float<M>(w, row_a, lane, xb, acc_a, mv, pre);
+        dot_float<M>(w, row_b, lane, xb, acc_b, mv, PdlWait{false});
+        break;
+    }
+}
