@@ -11,6 +11,7 @@
 // flash_attn_mask_to_KV_max (:576), soft_max_f32 with sinks (softmax.cu:47), the batched
 // cuBLAS QK^T / PV of the non-flash prefill path (ggml-cuda.cu:2084) and the host-built masks
 // of TensorSharp.GGML.Native/ggml_ops_norm_attn.cpp:1699-1884.  Scores are never materialised.
+#include <cstdlib>
 #include "common.cuh"
 #include "tsb_noalloc.h"
 
@@ -36,6 +37,9 @@ struct AttnArgs {
     // quantised projection reads, so that no separate quantise launch is needed.  Null = not wanted.
     int8_t* out_q;            // [B, Hq * Dh]
     float2* out_ds;           // [B, Hq * Dh / 32]
+    // Set by the launcher, not the caller: per (sequence, KV head) arrival counters.  When present, the
+    // CTA that finishes a head group last merges the split partials itself and no combine kernel runs.
+    unsigned* ticket;
 };
 
 __device__ __forceinline__ long kv_slot(const AttnArgs& a, int b, int j) {
@@ -84,29 +88,57 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
         float s[G];
 #pragma unroll
         for (int g = 0; g < G; ++g) s[g] = 0.f;
-        if (valid) {
+        // All of this chunk's K rows (one per lane) and, for head sizes up to 128, all of its V rows are
+        // requested before anything is used: a CTA has the SM to itself (the grid is about one CTA per SM),
+        // so registers are free and the chunk costs one DRAM round trip instead of six.
+        constexpr bool PREFETCH_V = DPL <= 4;
+        constexpr int KCH = DH / 8;
+        uint4 kreg[KCH <= 16 ? KCH : 1];
+        uint2 vreg[PREFETCH_V ? 32 : 1];
+        const int cnt = min(32, s1 - base);
+        if (KCH <= 16) {
             const uint4* kp = reinterpret_cast<const uint4*>(a.k_cache + (slot * a.Hkv + hk) * DH);
-#pragma unroll 8
-            for (int c = 0; c < DH / 8; ++c) {
-                const uint4 kv = kp[c];
-                const bf162* k2 = reinterpret_cast<const bf162*>(&kv);
-                float kf[8];
+#pragma unroll
+            for (int c = 0; c < KCH; ++c) kreg[c] = valid ? kp[c] : make_uint4(0u, 0u, 0u, 0u);
+        }
+        if (PREFETCH_V) {
+#pragma unroll
+            for (int u = 0; u < 32; ++u) {
+                const long sl = __shfl_sync(0xffffffffu, slot, u);
+                const bf16* vp = a.v_cache + (sl * a.Hkv + hk) * DH + lane * DPL;
+                if (DPL == 4) vreg[u] = u < cnt ? *reinterpret_cast<const uint2*>(vp) : make_uint2(0u, 0u);
+                else if (DPL == 2) vreg[u] = u < cnt ? make_uint2(*reinterpret_cast<const unsigned*>(vp), 0u) : make_uint2(0u, 0u);
+                else vreg[u] = u < cnt ? make_uint2((unsigned)*reinterpret_cast<const unsigned short*>(vp), 0u) : make_uint2(0u, 0u);
+            }
+        }
+        auto dot_chunk = [&](const uint4 kv, int c) {
+            const bf162* k2 = reinterpret_cast<const bf162*>(&kv);
+            float kf[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(k2[i]);
+                kf[2 * i] = f.x;
+                kf[2 * i + 1] = f.y;
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const uint4 qv = *reinterpret_cast<const uint4*>(&qs[g][c * 8]);
+                const bf162* q2 = reinterpret_cast<const bf162*>(&qv);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const float2 f = __bfloat1622float2(k2[i]);
-                    kf[2 * i] = f.x;
-                    kf[2 * i + 1] = f.y;
+                    const float2 f = __bfloat1622float2(q2[i]);
+                    s[g] += f.x * kf[2 * i] + f.y * kf[2 * i + 1];
                 }
+            }
+        };
+        if (valid) {
+            if (KCH <= 16) {
 #pragma unroll
-                for (int g = 0; g < G; ++g) {
-                    const uint4 qv = *reinterpret_cast<const uint4*>(&qs[g][c * 8]);
-                    const bf162* q2 = reinterpret_cast<const bf162*>(&qv);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float2 f = __bfloat1622float2(q2[i]);
-                        s[g] += f.x * kf[2 * i] + f.y * kf[2 * i + 1];
-                    }
-                }
+                for (int c = 0; c < (KCH <= 16 ? KCH : 1); ++c) dot_chunk(kreg[c], c);     // fully unrolled: kreg stays in registers
+            } else {
+                const uint4* kp = reinterpret_cast<const uint4*>(a.k_cache + (slot * a.Hkv + hk) * DH);
+#pragma unroll 8
+                for (int c = 0; c < KCH; ++c) dot_chunk(kp[c], c);
             }
         }
         float p[G];
@@ -123,8 +155,25 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
 #pragma unroll
             for (int d = 0; d < DPL; ++d) acc[g][d] *= corr;
         }
+        if (PREFETCH_V) {
+#pragma unroll
+            for (int u = 0; u < 32; ++u) {
+                float vf[DPL];                          // bf16 -> f32 is a 16-bit shift; no address of the register array is taken
+                vf[0] = __uint_as_float(vreg[u].x << 16);
+                if (DPL >= 2) vf[1 % DPL] = __uint_as_float(vreg[u].x & 0xffff0000u);
+                if (DPL >= 4) {
+                    vf[2 % DPL] = __uint_as_float(vreg[u].y << 16);
+                    vf[3 % DPL] = __uint_as_float(vreg[u].y & 0xffff0000u);
+                }
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const float pg = __shfl_sync(0xffffffffu, p[g], u);
+#pragma unroll
+                    for (int d = 0; d < DPL; ++d) acc[g][d] += pg * vf[d];
+                }
+            }
+        } else {
         // P V: eight value rows are fetched before any of them is used, so the loads overlap
-        const int cnt = min(32, s1 - base);
         for (int t0 = 0; t0 < cnt; t0 += 8) {
             float vf[8][DPL];
 #pragma unroll
@@ -132,12 +181,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
                 const long sl = __shfl_sync(0xffffffffu, slot, (t0 + u) & 31);
                 const bf16* vp = a.v_cache + (sl * a.Hkv + hk) * DH + lane * DPL;
                 if (t0 + u < cnt) {
-                    if (DPL == 4) {
-                        const uint2 vv = *reinterpret_cast<const uint2*>(vp);
-                        const bf162* v2 = reinterpret_cast<const bf162*>(&vv);
-                        const float2 f0 = __bfloat1622float2(v2[0]), f1 = __bfloat1622float2(v2[1]);
-                        vf[u][0] = f0.x; vf[u][1 % DPL] = f0.y; vf[u][2 % DPL] = f1.x; vf[u][3 % DPL] = f1.y;
-                    } else if (DPL == 8) {
+                    if (DPL == 8) {
                         const uint4 vv = *reinterpret_cast<const uint4*>(vp);
                         const bf162* v2 = reinterpret_cast<const bf162*>(&vv);
 #pragma unroll
@@ -165,6 +209,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
                 }
             }
         }
+        }
     }
     // merge the four warps
 #pragma unroll
@@ -190,6 +235,40 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
         a.part_o[pi * DH + d] = o;
         if (d == 0) { a.part_ml[pi * 2] = mm; a.part_ml[pi * 2 + 1] = ll; }
     }
+    if (a.ticket == nullptr) return;
+    // The CTA that finishes this (sequence, KV head) last merges the splits: no combine launch.
+    __shared__ bool last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last = atomicAdd(&a.ticket[b * a.Hkv + hk], 1u) == (unsigned)a.splits - 1u;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    for (int i = threadIdx.x; i < G * DH; i += 128) {
+        const int g = i / DH, d = i % DH, h = hk * G + g;
+        const long pb = ((long)b * a.Hq + h) * a.splits;
+        float mm = a.sinks ? a.sinks[h] : -INFINITY;
+        for (int sp = 0; sp < a.splits; ++sp) mm = fmaxf(mm, __ldcg(&a.part_ml[(pb + sp) * 2]));
+        float ll = a.sinks ? __expf(a.sinks[h] - mm) : 0.f, o = 0.f;
+        for (int sp = 0; sp < a.splits; ++sp) {
+            const float ms = __ldcg(&a.part_ml[(pb + sp) * 2]);
+            const float c = (ms == -INFINITY) ? 0.f : __expf(ms - mm);
+            ll += __ldcg(&a.part_ml[(pb + sp) * 2 + 1]) * c;
+            o += __ldcg(&a.part_o[(pb + sp) * DH + d]) * c;
+        }
+        const bf16 ob = f2bf(ll > 0.f ? o / ll : 0.f);
+        const long e = ((long)b * a.Hq + h) * DH + d;
+        a.out[e] = ob;
+        if (a.out_q != nullptr) {                      // a warp holds one group of 32 dims; arithmetic of quantize_q8_kernel
+            const float v = bf2f(ob);
+            const float amax = warp_max(fabsf(v));
+            const float sum = warp_sum(v);
+            const float dq = amax / 127.f;
+            a.out_q[e] = (int8_t)__float2int_rn(amax > 0.f ? v / dq : 0.f);
+            if ((d & 31) == 0) a.out_ds[e >> 5] = make_float2(dq, sum);
+        }
+    }
+    if (threadIdx.x == 0) a.ticket[b * a.Hkv + hk] = 0u;     // ready for the next launch on this stream
 }
 
 // grid (Hq, B), DH threads (rounded up to 32): merge split partials, apply the sink, normalise.
@@ -240,8 +319,31 @@ static int launch_decode_g(const AttnArgs& a, cudaStream_t s) {
 }
 
 // Query heads per KV head above 8 are handled by the caller splitting the head group.
+// Arrival counters of the fused split merge: one per (sequence, KV head), zero between launches (the
+// merging CTA resets its counter).  Launches that share a device must be ordered, as a decode loop's are.
+#define ATTN_MAX_TICKETS 65536
+static __device__ unsigned g_attn_ticket[ATTN_MAX_TICKETS];
+static unsigned* g_attn_ticket_ptr[64] = {nullptr};
+
+static unsigned* attn_ticket_for_current_device() {
+    // Off unless TSB_ATTN_FUSED_COMBINE=1: inside the decode step the in-kernel merge measured slower than the
+    // separate combine launch (2.57 ms against 2.23 ms per step on Qwen3-4B): the fences and the serial merge by
+    // one CTA sit on the critical path, while the combine kernel's launch overlaps the attention kernel's tail.
+    static const bool on = []() { const char* e = getenv("TSB_ATTN_FUSED_COMBINE"); return e && atoi(e) != 0; }();
+    if (!on) return nullptr;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (g_attn_ticket_ptr[dev] == nullptr) {
+        unsigned* p = nullptr;
+        if (cudaGetSymbolAddress((void**)&p, g_attn_ticket) != cudaSuccess) return nullptr;
+        g_attn_ticket_ptr[dev] = p;
+    }
+    return g_attn_ticket_ptr[dev];
+}
+
 extern "C" int tsb_attn_decode(const AttnArgs* args, void* stream) {
     AttnArgs a = *args;
+    a.ticket = (a.splits >= 1 && (long)a.B * a.Hkv <= ATTN_MAX_TICKETS) ? attn_ticket_for_current_device() : nullptr;
     TSB_CHECK_ARG(a.Hkv > 0 && a.Hq % a.Hkv == 0, "attn_decode: Hq=%d not a multiple of Hkv=%d", a.Hq, a.Hkv);
     TSB_CHECK_ARG(a.splits >= 1 && a.part_o && a.part_ml, "attn_decode: scratch for %d splits missing", a.splits);
     if (a.B == 0) return TSB_OK;
@@ -257,8 +359,10 @@ extern "C" int tsb_attn_decode(const AttnArgs* args, void* stream) {
     }
     if (rc != TSB_OK) return rc;
     TSB_CHECK_LAUNCH();
-    TSB_CHECK_CUDA(tsb_launch(attn_combine_kernel, dim3(a.Hq, a.B), dim3((a.Dh + 31) & ~31), 0, s, a));
-    TSB_CHECK_LAUNCH();
+    if (a.ticket == nullptr) {
+        TSB_CHECK_CUDA(tsb_launch(attn_combine_kernel, dim3(a.Hq, a.B), dim3((a.Dh + 31) & ~31), 0, s, a));
+        TSB_CHECK_LAUNCH();
+    }
     return TSB_OK;
 }
 
@@ -277,6 +381,7 @@ extern "C" long tsb_attn_decode_noalloc_capacity(void) { return (long)TSB_ATTN_N
 extern "C" int tsb_attn_decode_noalloc(const AttnArgs* args, void* stream) {
     TSB_CHECK_ARG(args != nullptr, "attn_decode_noalloc: null arguments");
     AttnArgs a = *args;
+    a.ticket = nullptr;                 // this entry point keeps the two-kernel form
     TSB_CHECK_ARG(a.B >= 0 && a.Hq > 0 && a.Dh > 0 && a.splits >= 1, "attn_decode_noalloc: bad sizes B=%d Hq=%d Dh=%d splits=%d",
                   a.B, a.Hq, a.Dh, a.splits);
     const long slots = (long)a.B * a.Hq * a.splits;

@@ -299,20 +299,35 @@ __global__ void __launch_bounds__(128) qkv_rope_kernel(QkvArgs a) {
         ss += x * x;
     }
     const float* nw = kind == 0 ? a.qn : (kind == 1 ? a.kn : nullptr);
+    // Everything else this warp will read (norm weights, cos / sin of its pairs) is requested here, next to
+    // the inputs, so the kernel is one memory round trip deep instead of three.
+    const int rot = a.rp.rot_dim;
+    const bool tab = a.cs_table != nullptr && kind != 2 && rot > 0;
+    float nwv[16];
+    float2 csv[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const int e = lane + 32 * j;
+        nwv[j] = (nw && e < Dh) ? nw[e] : 1.f;
+        csv[j] = make_float2(1.f, 0.f);
+        if (tab && e < rot) {
+            const int pair = a.rp.mode == 0 ? (e < (rot >> 1) ? e : e - (rot >> 1)) : (e >> 1);
+            csv[j] = a.cs_table[(long)t * (rot >> 1) + pair];
+        }
+    }
     if (nw || (kind == 2 && a.v_norm)) {
         ss = warp_sum(ss);
         const float rs = rsqrtf(ss / (float)Dh + a.eps);
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const int e = lane + 32 * j;
-            if (e < Dh) v[j] *= rs * (nw ? nw[e] : 1.f);
+            if (e < Dh) v[j] *= rs * nwv[j];
         }
     }
     bf16* dst;
     if (kind == 0) dst = a.q_out + ((long)t * a.Hq + h) * Dh;
     else if (kind == 1) dst = a.k_cache + (slot * a.Hkv + (h - a.Hq)) * Dh;
     else dst = a.v_cache + (slot * a.Hkv + (h - a.Hq - a.Hkv)) * Dh;
-    const int rot = a.rp.rot_dim;
     if (kind == 2 || rot == 0) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
@@ -342,8 +357,8 @@ __global__ void __launch_bounds__(128) qkv_rope_kernel(QkvArgs a) {
             float o = v[j];
             if (e < rot) {
                 const int pair = e < half ? e : e - half;
-                float c, s;
-                rope_lookup(a, t, pair, pos, c, s);
+                float c = csv[j].x, s = csv[j].y;
+                if (!tab) rope_lookup(a, t, pair, pos, c, s);
                 const float x0 = st[pair], x1 = st[pair + half];
                 o = e < half ? x0 * c - x1 * s : x0 * s + x1 * c;
             }
@@ -358,8 +373,8 @@ __global__ void __launch_bounds__(128) qkv_rope_kernel(QkvArgs a) {
             if (e >= Dh) continue;
             float o = v[j];
             if (e < rot) {
-                float c, s;
-                rope_lookup(a, t, e >> 1, pos, c, s);
+                float c = csv[j].x, s = csv[j].y;
+                if (!tab) rope_lookup(a, t, e >> 1, pos, c, s);
                 o = (e & 1) ? other * s + v[j] * c : v[j] * c - other * s;
             }
             dst[e] = f2bf(o * qs);

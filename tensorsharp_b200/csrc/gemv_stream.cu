@@ -327,6 +327,173 @@ static int launch_stream_m(const GemvArgs& a, int ppw, int ctas, size_t smem, cu
     return launch_stream<4, GLU, Q5, D>(a, ppw, ctas, smem, s);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Single-token Q6_K (the V projection, half of the down projections and the output matrix of a
+// Q4_K_M file).  The weight lives in four planes (low nibbles, high bit pairs, int8 scales, half
+// super-scales); a ring buffer holds the four row segments back to back.  A unit is 32 values
+// (8 bytes of each of la / lb / hv), so that a quarter row splits evenly over a warp.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gsrc) : "memory");
+}
+
+template <int NJ, int KS>
+__global__ void __launch_bounds__(128) gemv_stream_q6k_m1_kernel(GemvArgs a, int ppw) {
+    extern __shared__ uint4 stream_smem[];
+    __shared__ float part[2][4];
+    constexpr int D = 4;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int K = a.w.K, nb = K >> 8;
+    // even block boundaries keep the 2-byte super-scales 4-byte aligned for cp.async
+    const int bs = KS == 1 ? 0 : ((nb * warp) / KS) & ~1, be = KS == 1 ? nb : (warp == KS - 1 ? nb : ((nb * (warp + 1)) / KS) & ~1);
+    const int nblk = be - bs;
+    const int max_blocks = KS == 1 ? nb : ((nb + KS - 1) / KS + 2);
+    const int stage_bytes = max_blocks * 208 + ((max_blocks * 2 + 15) & ~15);
+    uint8_t* ring = reinterpret_cast<uint8_t*>(stream_smem) + (long)warp * D * stage_bytes;
+    const int N = a.w.N;
+    const int owner = KS == 1 ? blockIdx.x * 4 + warp : blockIdx.x;
+    const int r0 = owner * ppw, r1 = min(N, r0 + ppw);
+    const int ntask = r1 > r0 ? r1 - r0 : 0;
+    const int off_qh = nblk * 128, off_sc = nblk * 192, off_d = nblk * 208;
+    auto issue = [&](int i) {
+        if (i < ntask) {
+            const long blk0 = (long)(r0 + i) * nb + bs;
+            uint8_t* dst = ring + (long)(i % D) * stage_bytes;
+            const uint8_t* ql = a.w.p0 + blk0 * 128;
+            const uint8_t* qh = a.w.p1 + blk0 * 64;
+            const uint8_t* sc = a.w.p2 + blk0 * 16;
+            const uint8_t* dd = a.w.p3 + blk0 * 2;
+            for (int c = lane; c < nblk * 8; c += 32) cp_async16(dst + c * 16, ql + c * 16);
+            for (int c = lane; c < nblk * 4; c += 32) cp_async16(dst + off_qh + c * 16, qh + c * 16);
+            for (int c = lane; c < nblk; c += 32) cp_async16(dst + off_sc + c * 16, sc + c * 16);
+            for (int c = lane; c < nblk / 2; c += 32) cp_async4(dst + off_d + c * 4, dd + c * 4);
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int i = 0; i < D - 1; ++i) issue(i);
+    pdl_wait();
+    pdl_trigger();
+
+    const int units = nblk << 3;
+    int xr[NJ][8], o_la[NJ], o_hv[NJ], o_sc[NJ], o_d[NJ];
+    float xd[NJ][4];
+    unsigned bsel[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+        const int u = lane + 32 * j;
+        const bool ok = u < units;
+        const int uc = ok ? u : 0;
+        const int bl = uc >> 3, b = bs + bl, rem = uc & 7, n = rem >> 2, h = (rem >> 1) & 1, hh = rem & 1;
+        const int xoff = b * 256 + 128 * n + 16 * h + 8 * hh;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int2 xv = *reinterpret_cast<const int2*>(a.xq + xoff + 32 * k);
+            xr[j][2 * k] = xv.x;
+            xr[j][2 * k + 1] = xv.y;
+            xd[j][k] = ok ? a.xds[b * 8 + 4 * n + k].x : 0.f;
+        }
+        o_la[j] = bl * 128 + 64 * n + 16 * h + 8 * hh;
+        o_hv[j] = off_qh + bl * 64 + 32 * n + 16 * h + 8 * hh;
+        o_sc[j] = off_sc + bl * 16 + 8 * n;
+        o_d[j] = off_d + bl * 2;
+        bsel[j] = 8u * h;                                 // scales of this unit: bytes h, h + 2, h + 4, h + 6 of the 8
+    }
+
+    for (int i = 0; i < ntask; ++i) {
+        issue(i + D - 1);
+        cp_async_wait<D - 1>();
+        __syncwarp();
+        const uint8_t* st = ring + (long)(i % D) * stage_bytes;
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) {
+            const uint2 la = *reinterpret_cast<const uint2*>(st + o_la[j]);
+            const uint2 lb = *reinterpret_cast<const uint2*>(st + o_la[j] + 32);
+            const uint2 hv = *reinterpret_cast<const uint2*>(st + o_hv[j]);
+            const uint2 sc8 = *reinterpret_cast<const uint2*>(st + o_sc[j]);
+            const float d = __half2float(*reinterpret_cast<const __half*>(st + o_d[j]));
+            const uint32_t A[2] = {la.x, la.y}, B[2] = {lb.x, lb.y}, H[2] = {hv.x, hv.y};
+            int t0 = 0, t1 = 0, t2 = 0, t3 = 0;
+#pragma unroll
+            for (int w = 0; w < 2; ++w) {
+                const int q0 = __vsub4((A[w] & 0x0F0F0F0Fu) | ((H[w] & 0x03030303u) << 4), 0x20202020u);
+                const int q1 = __vsub4((B[w] & 0x0F0F0F0Fu) | (((H[w] >> 2) & 0x03030303u) << 4), 0x20202020u);
+                const int q2 = __vsub4(((A[w] >> 4) & 0x0F0F0F0Fu) | (((H[w] >> 4) & 0x03030303u) << 4), 0x20202020u);
+                const int q3 = __vsub4(((B[w] >> 4) & 0x0F0F0F0Fu) | (((H[w] >> 6) & 0x03030303u) << 4), 0x20202020u);
+                t0 = __dp4a(q0, xr[j][w], t0);
+                t1 = __dp4a(q1, xr[j][2 + w], t1);
+                t2 = __dp4a(q2, xr[j][4 + w], t2);
+                t3 = __dp4a(q3, xr[j][6 + w], t3);
+            }
+            // int8 scales: bytes h and h + 2 of the low word, h and h + 2 of the high word
+            const int s0 = (int)(int8_t)(sc8.x >> bsel[j]), s1 = (int)(int8_t)(sc8.x >> (bsel[j] + 16u));
+            const int s2 = (int)(int8_t)(sc8.y >> bsel[j]), s3 = (int)(int8_t)(sc8.y >> (bsel[j] + 16u));
+            const float A4 = i2f_small(t0 * s0) * xd[j][0] + i2f_small(t1 * s1) * xd[j][1] + i2f_small(t2 * s2) * xd[j][2] +
+                             i2f_small(t3 * s3) * xd[j][3];
+            acc += d * A4;
+        }
+        acc = warp_sum(acc);
+        __syncwarp();
+        if (KS > 1) {
+            if (lane == 0) part[i & 1][warp] = acc;
+            __syncthreads();
+            acc = part[i & 1][0] + part[i & 1][1] + part[i & 1][2] + part[i & 1][3];
+            if (warp != 0) continue;
+        }
+        if (lane != 0) continue;
+        const int col = r0 + i;
+        float v = acc;
+        if (a.bias) v += a.bias[col];
+        if (a.act == ACT_RELU2) { v = fmaxf(v, 0.f); v = v * v; }
+        if (a.row_scale) v *= a.row_scale[0];
+        if (a.out_f32) {
+            if (a.residual) v += reinterpret_cast<const float*>(a.residual)[col];
+            reinterpret_cast<float*>(a.out)[col] = v;
+        } else {
+            if (a.residual) v += bf2f(reinterpret_cast<const bf16*>(a.residual)[col]);
+            reinterpret_cast<bf16*>(a.out)[col] = f2bf(v);
+        }
+    }
+    cp_async_wait<0>();
+}
+
+template <int NJ, int KS>
+static int launch_q6k(const GemvArgs& a, int ppw, int ctas, size_t smem, cudaStream_t s) {
+    static bool attr = false;
+    if (!attr) {
+        TSB_CHECK_CUDA(cudaFuncSetAttribute(gemv_stream_q6k_m1_kernel<NJ, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr = true;
+    }
+    TSB_CHECK_CUDA(tsb_launch(gemv_stream_q6k_m1_kernel<NJ, KS>, dim3(ctas), dim3(128), smem, s, a, ppw));
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}
+
+static bool q6k_ok(const GemvArgs& a, bool glu) {
+    const int nb = a.w.K >> 8;
+    return a.w.type == TSB_Q6_K && !glu && a.M == 1 && nb >= 2 && nb % 2 == 0 && nb <= 64 && a.w.N >= 64;
+}
+
+static int launch_q6k_any(const GemvArgs& a, cudaStream_t s) {
+    const int nb = a.w.K >> 8;
+    const int ks = nb * 8 <= 128 ? 1 : 4;
+    const int max_blocks = ks == 1 ? nb : ((nb + ks - 1) / ks + 2);
+    const int nj = (max_blocks * 8 + 31) / 32;
+    const size_t stage = (size_t)max_blocks * 208 + (((size_t)max_blocks * 2 + 15) & ~(size_t)15);
+    const size_t smem = stage * 4 * 4;
+    int per_sm = (int)((220 * 1024) / (smem + 1024));
+    per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
+    const int owners = 148 * per_sm * (ks == 1 ? 4 : 1);
+    const int ppw = (a.w.N + owners - 1) / owners;
+    const int ctas = ks == 1 ? (a.w.N + 4 * ppw - 1) / (4 * ppw) : (a.w.N + ppw - 1) / ppw;
+#define TSB_Q6(NJV, KSV) return launch_q6k<NJV, KSV>(a, ppw, ctas, smem, s)
+    if (ks == 1) { if (nj <= 1) TSB_Q6(1, 1); if (nj == 2) TSB_Q6(2, 1); if (nj == 3) TSB_Q6(3, 1); TSB_Q6(4, 1); }
+    if (nj <= 2) TSB_Q6(2, 4); if (nj == 3) TSB_Q6(3, 4); if (nj == 4) TSB_Q6(4, 4); TSB_Q6(5, 4);
+#undef TSB_Q6
+}
+
 // Whether the row pipeline takes this GEMV (called by tsb_gemv_push before the plain launch).  By default
 // only the single-token Q4_K form runs here; the generic form (M <= 4, Q5_K, any row length) measured
 // slower than the plain kernel inside the decode step and is kept behind TSB_GEMV_STREAM=2.
@@ -345,6 +512,7 @@ bool tsb_gemv_stream_eligible(const GemvArgs& a) {
     const int mode = stream_mode();
     if (!mode || a.ids || a.push || a.M > 4 || a.M < 1) return false;
     if (fast_ok(a)) return true;
+    if (q6k_ok(a, a.act >= ACT_SWIGLU && a.act <= ACT_SWIGLU_OAI)) return true;
     if (mode < 2 || (a.w.type != TSB_Q4_K && a.w.type != TSB_Q5_K)) return false;
     const size_t rowbytes = (size_t)(a.w.K >> 8) * (a.w.type == TSB_Q5_K ? 176 : 144);
     return rowbytes * 4 * 4 <= 200 * 1024 && a.w.N >= 64;           // four warps x four buffers must fit
@@ -352,6 +520,7 @@ bool tsb_gemv_stream_eligible(const GemvArgs& a) {
 
 int tsb_gemv_stream_launch(const GemvArgs& a, bool glu, cudaStream_t s) {
     if (fast_ok(a)) return launch_fast(a, glu, s);
+    if (q6k_ok(a, glu)) return launch_q6k_any(a, s);
     const bool q5 = a.w.type == TSB_Q5_K;
     const size_t rowbytes = (size_t)(a.w.K >> 8) * (q5 ? 176 : 144);
     const size_t smem = rowbytes * 4 * 4;

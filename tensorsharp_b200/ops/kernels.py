@@ -59,7 +59,7 @@ class AttnArgs(C.Structure):
                 ("scale", C.c_float), ("softcap", C.c_float), ("window", C.c_int),
                 ("B", C.c_int), ("Hq", C.c_int), ("Hkv", C.c_int), ("Dh", C.c_int), ("page_size", C.c_int),
                 ("max_pages", C.c_int), ("splits", C.c_int), ("q_pos0", _vp), ("lse_out", _vp),
-                ("out_q", _vp), ("out_ds", _vp)]
+                ("out_q", _vp), ("out_ds", _vp), ("ticket", _vp)]
 
 
 _configured = False

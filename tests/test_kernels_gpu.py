@@ -572,8 +572,9 @@ def test_attn_decode_q8_output_equals_separate_quantise():
     assert torch.equal(oq, wq) and torch.equal(ods, wds)
 
 
-@pytest.mark.parametrize("t", [GGMLType.Q4_K, GGMLType.Q5_K])
-@pytest.mark.parametrize("N,Kd,act", [(2048, 2560, "swiglu"), (2560, 9728, None), (1021, 4096, None), (66, 256, "swiglu")])
+@pytest.mark.parametrize("t", [GGMLType.Q4_K, GGMLType.Q5_K, GGMLType.Q6_K])
+@pytest.mark.parametrize("N,Kd,act", [(2048, 2560, "swiglu"), (2560, 9728, None), (1021, 4096, None), (66, 256, "swiglu"),
+                                      (4099, 2560, None), (300, 512, None)])
 @pytest.mark.parametrize("M", [1, 2, 4])
 def test_gemv_row_pipeline_shapes(t, N, Kd, act, M):
     """Decode shapes that take the shared-memory row pipeline: long and short rows, odd row counts,
