@@ -40,6 +40,9 @@ def parse_args():
     ap.add_argument("--model", default="qwen3-4b", choices=["qwen3-4b", "qwen3-tiny", "gptoss-20b", "gptoss-tiny"])
     ap.add_argument("--prefill-repeats", type=int, default=3, help="timed prefill repetitions (median reported)")
     ap.add_argument("--no-graph", action="store_true", help="run decode steps eagerly (for kernel-level profiling)")
+    ap.add_argument("--trace", default=None, metavar="FILE",
+                    help="after the timed runs, record three more graph replays with the CUDA activity tracer, write the "
+                         "kernel events of the middle one to FILE (JSON) and print its per-kernel table to stderr")
     ap.add_argument("--cache-dir", default=os.environ.get("TSB_BENCH_CACHE", os.path.join(tempfile.gettempdir(), "tsb_bench")))
     a = ap.parse_args()
     big_moe = a.model == "gptoss-20b"
@@ -140,6 +143,41 @@ def ensure_model(args, rank: int, world: int) -> str:
         import torch.distributed as dist
         dist.barrier()
     return path
+
+
+def trace_step(dg, path: str) -> None:
+    """Kernel timeline of one decode step inside the captured graph.  Kernels overlap under programmatic
+    dependent launch (a kernel is resident and waiting before its predecessor ends), so besides each
+    kernel's own duration the table gives its *exclusive* time: the part of it after every earlier
+    kernel had finished, which is what it adds to the step."""
+    import collections
+    import re
+
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            dg.step()
+        torch.cuda.synchronize()
+    ev = sorted(((e.name, e.time_range.start, e.time_range.end) for e in prof.events()
+                 if e.device_type == torch.autograd.DeviceType.CUDA), key=lambda x: x[1])
+    n = len(ev) // 3
+    step = ev[n:2 * n]
+    with open(path, "w") as f:
+        json.dump(step, f)
+    t0, prev = step[0][1], step[0][1]
+    rows = collections.OrderedDict()
+    for name, s, e in step:
+        k = re.sub(r"\(.*", "", name)[:48]
+        r = rows.setdefault(k, [0, 0.0, 0.0])
+        r[0] += 1
+        r[1] += e - s
+        r[2] += max(0.0, e - max(prev, s))
+        prev = max(prev, e)
+    print(f"decode step: {n} kernels, {prev - t0:.1f} us", file=sys.stderr)
+    print(f"{'kernel':50s}{'n':>4s}{'sum us':>9s}{'excl us':>9s}{'excl/n':>8s}", file=sys.stderr)
+    for k, (c, du, ex) in sorted(rows.items(), key=lambda kv: -kv[1][2]):
+        print(f"{k:50s}{c:4d}{du:9.1f}{ex:9.1f}{ex / c:8.2f}", file=sys.stderr)
 
 
 def run_ours(args) -> dict:
@@ -243,6 +281,8 @@ def run_ours(args) -> dict:
     e2e_wall_ms = (time.perf_counter() - t0) * 1e3
     clock_info = clocks.stop() if rank == 0 else {}
 
+    if args.trace and rank == 0:
+        trace_step(dg, args.trace)
     vals = torch.tensor([dev_ms, e2e_ms, prefill_ms, e2e_wall_ms], dtype=torch.float64, device=dev)
     if world > 1:
         import torch.distributed as dist

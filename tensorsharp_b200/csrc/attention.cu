@@ -58,19 +58,24 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
     pdl_trigger();
     const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __shared__ __align__(16) bf16 qs[G][DH];
+    __shared__ float red_m[4][G], red_l[4][G];
+    __shared__ float red_o[4][G][DH];
+    // the query rows and the sequence length are requested together (the G heads of a KV head are contiguous)
+    constexpr int QV = G * DH / 8;                     // 16-byte pieces of the query rows
+    const uint4* qsrc = reinterpret_cast<const uint4*>(a.q + ((long)b * a.Hq + hk * G) * DH);
+    uint4 qreg[(QV + 127) / 128];
+#pragma unroll
+    for (int i = 0; i < (QV + 127) / 128; ++i)
+        if (threadIdx.x + i * 128 < QV) qreg[i] = qsrc[threadIdx.x + i * 128];
     const int len = a.kv_lens[b];
+#pragma unroll
+    for (int i = 0; i < (QV + 127) / 128; ++i)
+        if (threadIdx.x + i * 128 < QV) reinterpret_cast<uint4*>(&qs[0][0])[threadIdx.x + i * 128] = qreg[i];
     const int lo = (a.window > 0 && len > a.window) ? len - a.window : 0;
     const int span = len - lo;
     const int per = (((span + a.splits - 1) / a.splits) + 31) & ~31;
     const int s0 = lo + split * per, s1 = min(len, s0 + per);
-
-    __shared__ __align__(16) bf16 qs[G][DH];
-    __shared__ float red_m[4][G], red_l[4][G];
-    __shared__ float red_o[4][G][DH];
-    for (int i = threadIdx.x; i < G * DH; i += 128) {
-        const int g = i / DH, d = i % DH;
-        qs[g][d] = a.q[((long)b * a.Hq + hk * G + g) * DH + d];
-    }
     __syncthreads();
 
     float m[G], l[G], acc[G][DPL];
@@ -272,19 +277,33 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
 }
 
 // grid (Hq, B), DH threads (rounded up to 32): merge split partials, apply the sink, normalise.
+// Latency is all that matters here (a few KB per block), so nothing is read in a dependent loop: each
+// lane fetches the (max, sum) of two splits at once, the warp reduces them, and the partial outputs
+// are fetched sixteen splits at a time before any is used.  At most 64 splits.
 __global__ void attn_combine_kernel(AttnArgs a) {
     pdl_wait();
     pdl_trigger();
-    const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x, lane = threadIdx.x & 31;
     const long base = ((long)b * a.Hq + h) * a.splits;
-    float mm = a.sinks ? a.sinks[h] : -INFINITY;
-    for (int s = 0; s < a.splits; ++s) mm = fmaxf(mm, a.part_ml[(base + s) * 2]);
-    float ll = a.sinks ? __expf(a.sinks[h] - mm) : 0.f, o = 0.f;
-    for (int s = 0; s < a.splits; ++s) {
-        const float ms = a.part_ml[(base + s) * 2];
-        const float c = (ms == -INFINITY) ? 0.f : __expf(ms - mm);
-        ll += a.part_ml[(base + s) * 2 + 1] * c;
-        if (d < a.Dh) o += a.part_o[(base + s) * a.Dh + d] * c;
+    const bool in0 = lane < a.splits, in1 = lane + 32 < a.splits;
+    const float2 ml0 = in0 ? *reinterpret_cast<const float2*>(a.part_ml + (base + lane) * 2) : make_float2(-INFINITY, 0.f);
+    const float2 ml1 = in1 ? *reinterpret_cast<const float2*>(a.part_ml + (base + lane + 32) * 2) : make_float2(-INFINITY, 0.f);
+    const float sink = a.sinks ? a.sinks[h] : -INFINITY;
+    const float mm = fmaxf(sink, warp_max(fmaxf(ml0.x, ml1.x)));
+    const float c0 = (ml0.x == -INFINITY) ? 0.f : __expf(ml0.x - mm), c1 = (ml1.x == -INFINITY) ? 0.f : __expf(ml1.x - mm);
+    const float ll = warp_sum(ml0.y * c0 + ml1.y * c1) + (a.sinks ? __expf(sink - mm) : 0.f);
+    float o = 0.f;
+    const int dd = d < a.Dh ? d : 0;
+    for (int s0 = 0; s0 < a.splits; s0 += 16) {
+        float pv[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) pv[i] = (s0 + i < a.splits) ? a.part_o[(base + s0 + i) * a.Dh + dd] : 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int sp = s0 + i;
+            const float c = __shfl_sync(0xffffffffu, sp < 32 ? c0 : c1, sp & 31);
+            o += pv[i] * c;
+        }
     }
     const bf16 ob = f2bf(ll > 0.f ? o / ll : 0.f);
     if (d < a.Dh) a.out[((long)b * a.Hq + h) * a.Dh + d] = ob;
@@ -346,6 +365,7 @@ extern "C" int tsb_attn_decode(const AttnArgs* args, void* stream) {
     a.ticket = (a.splits >= 1 && (long)a.B * a.Hkv <= ATTN_MAX_TICKETS) ? attn_ticket_for_current_device() : nullptr;
     TSB_CHECK_ARG(a.Hkv > 0 && a.Hq % a.Hkv == 0, "attn_decode: Hq=%d not a multiple of Hkv=%d", a.Hq, a.Hkv);
     TSB_CHECK_ARG(a.splits >= 1 && a.part_o && a.part_ml, "attn_decode: scratch for %d splits missing", a.splits);
+    TSB_CHECK_ARG(a.splits <= 64, "attn_decode: %d splits (limit 64)", a.splits);
     if (a.B == 0) return TSB_OK;
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
@@ -384,6 +404,7 @@ extern "C" int tsb_attn_decode_noalloc(const AttnArgs* args, void* stream) {
     a.ticket = nullptr;                 // this entry point keeps the two-kernel form
     TSB_CHECK_ARG(a.B >= 0 && a.Hq > 0 && a.Dh > 0 && a.splits >= 1, "attn_decode_noalloc: bad sizes B=%d Hq=%d Dh=%d splits=%d",
                   a.B, a.Hq, a.Dh, a.splits);
+    TSB_CHECK_ARG(a.splits <= 64, "attn_decode_noalloc: %d splits (limit 64)", a.splits);
     const long slots = (long)a.B * a.Hq * a.splits;
     const long need = slots * (a.Dh + 2);
     TSB_CHECK_ARG(need <= (long)TSB_ATTN_NOALLOC_MAX_FLOATS,

@@ -17,15 +17,6 @@
 #include <cstdlib>
 #include "gemv_core.cuh"
 
-// Lane q of the calling warp stores `v`, tagged with the current exchange number, at word `index`
-// of this rank's region in rank q's mailbox.
-__device__ __forceinline__ void gemv_push_store(const TpPush* tp, int lane, long index, float v) {
-    const unsigned epoch = *tp->epoch;
-    if (lane < tp->size)
-        st_word(tp->mailbox[lane] + (long)(epoch % TP_SLOTS) * tp->slot_stride + (long)tp->rank * tp->src_stride + index, v,
-                epoch + 1);
-}
-
 // Row-parallel projection of a tensor-parallel layer: the result is this rank's partial sum, so
 // instead of writing it to a local tensor the warp stores it, tagged with the exchange number,
 // into the mailbox of every rank (tp_fused.cuh).  GEMM -> reduce in one kernel: the NVLink stores

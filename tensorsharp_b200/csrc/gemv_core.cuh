@@ -317,6 +317,15 @@ __device__ __forceinline__ void dot_row(const QW& w, long row, int lane, const i
 }
 
 
+// Lane q of the calling warp stores `v`, tagged with the current exchange number, at word `index`
+// of this rank's region in rank q's mailbox.
+__device__ __forceinline__ void gemv_push_store(const TpPush* tp, int lane, long index, float v) {
+    const unsigned epoch = *tp->epoch;
+    if (lane < tp->size)
+        st_word(tp->mailbox[lane] + (long)(epoch % TP_SLOTS) * tp->slot_stride + (long)tp->rank * tp->src_stride + index, v,
+                epoch + 1);
+}
+
 struct PdlWait {
     bool on;
     __device__ __forceinline__ void operator()() const {

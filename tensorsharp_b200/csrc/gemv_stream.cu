@@ -245,6 +245,12 @@ __global__ void __launch_bounds__(128) gemv_stream_q4k_m1_kernel(GemvArgs a, int
             if (warp != 0) continue;
         }
         if (GLU && !(i & 1)) { keep = acc; continue; }
+        if (!GLU && a.push != nullptr) {
+            // row-parallel projection of a tensor-parallel layer: every lane holds the sum; lane q stores it,
+            // tagged with the exchange number, into rank q's mailbox
+            if (r >= 0) gemv_push_store(a.push, lane, r, (a.bias && a.push->rank == 0) ? acc + a.bias[r] : acc);
+            continue;
+        }
         if (lane != 0 || r < 0) continue;
         const int col = GLU ? p0 + (i >> 1) : r;
         float v;
@@ -442,6 +448,10 @@ __global__ void __launch_bounds__(128) gemv_stream_q6k_m1_kernel(GemvArgs a, int
             acc = part[i & 1][0] + part[i & 1][1] + part[i & 1][2] + part[i & 1][3];
             if (warp != 0) continue;
         }
+        if (a.push != nullptr) {
+            gemv_push_store(a.push, lane, r0 + i, (a.bias && a.push->rank == 0) ? acc + a.bias[r0 + i] : acc);
+            continue;
+        }
         if (lane != 0) continue;
         const int col = r0 + i;
         float v = acc;
@@ -510,10 +520,11 @@ static bool fast_ok(const GemvArgs& a) {
 
 bool tsb_gemv_stream_eligible(const GemvArgs& a) {
     const int mode = stream_mode();
-    if (!mode || a.ids || a.push || a.M > 4 || a.M < 1) return false;
-    if (fast_ok(a)) return true;
-    if (q6k_ok(a, a.act >= ACT_SWIGLU && a.act <= ACT_SWIGLU_OAI)) return true;
-    if (mode < 2 || (a.w.type != TSB_Q4_K && a.w.type != TSB_Q5_K)) return false;
+    if (!mode || a.ids || a.M > 4 || a.M < 1) return false;
+    const bool glu = a.act >= ACT_SWIGLU && a.act <= ACT_SWIGLU_OAI;
+    if (fast_ok(a) && !(glu && a.push)) return true;
+    if (q6k_ok(a, glu)) return true;
+    if (a.push || mode < 2 || (a.w.type != TSB_Q4_K && a.w.type != TSB_Q5_K)) return false;
     const size_t rowbytes = (size_t)(a.w.K >> 8) * (a.w.type == TSB_Q5_K ? 176 : 144);
     return rowbytes * 4 * 4 <= 200 * 1024 && a.w.N >= 64;           // four warps x four buffers must fit
 }
