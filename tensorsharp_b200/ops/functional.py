@@ -168,17 +168,54 @@ def linear_fused(x: torch.Tensor, w: QuantWeight, *, norm_w: Optional[torch.Tens
 
 
 _scratch = {}
+_bf16_used = {}          # device index -> bytes of bf16 weight copies held
+_bf16_auto = {}          # device index -> default budget
 
 
-def _dequant_scratch(w: QuantWeight) -> torch.Tensor:
-    """bf16 copy of ``w`` for the tensor-core GEMM.  Quantised weights are decoded into a
-    per-device scratch that is reused by every layer (it stays L2-resident between the
-    decode and the GEMM that follows); bf16 weights are used in place."""
+def _bf16_budget(device) -> int:
+    """Bytes of spare HBM the prefill path may spend on bf16 copies of quantised weights.
+    ``TSB_BF16_WEIGHT_CACHE_GB`` sets it (0 turns the copies off); the default is 35 % of the device's
+    memory, at most 64 GB: a B200 holds a 4-bit 20 B-parameter model and its bf16 copy several times over."""
+    env = os.environ.get("TSB_BF16_WEIGHT_CACHE_GB")
+    if env is not None:
+        return int(float(env) * (1 << 30))
+    key = torch.device(device).index or 0
+    if key not in _bf16_auto:
+        _bf16_auto[key] = int(min(64 << 30, 0.35 * torch.cuda.get_device_properties(device).total_memory))
+    return _bf16_auto[key]
+
+
+def _release_bf16(dev_index: int, nbytes: int) -> None:
+    _bf16_used[dev_index] = _bf16_used.get(dev_index, 0) - nbytes
+
+
+def _dequant_scratch(w: QuantWeight, holder: Optional[QuantWeight] = None, slot: int = 0) -> torch.Tensor:
+    """bf16 form of ``w`` for the tensor-core GEMM; bf16 weights are used in place.
+
+    A quantised weight is decoded once and the copy is kept with the weight object (with ``holder`` and
+    ``slot``: with the expert stack that ``w`` is a view of, so the copy outlives the temporary view) for
+    as long as the budget of ``_bf16_budget`` lasts: prefill then reads weights the way a bf16 model would,
+    while decode keeps streaming the GGUF blocks.  Past the budget the weight is decoded into a per-device
+    scratch that every layer reuses (it stays L2-resident between the decode and the GEMM that follows)."""
     from ..gguf.constants import GGMLType
     if w.ggml_type == GGMLType.BF16:
         return w.planes[0].view(torch.bfloat16).view(w.rows, w.K)
-    key = (w.device.index, )
+    owner = holder if holder is not None else w
+    cache = owner.__dict__.setdefault("_bf16_copies", {})
+    hit = cache.get(slot)
+    if hit is not None:
+        return hit
     need = w.rows * w.K
+    dev = w.device.index or 0
+    if _bf16_used.get(dev, 0) + 2 * need <= _bf16_budget(w.device):
+        import weakref
+        out = torch.empty((w.rows, w.K), dtype=torch.bfloat16, device=w.device)
+        _k().gather_rows(w, None, 1.0, out=out)
+        cache[slot] = out
+        _bf16_used[dev] = _bf16_used.get(dev, 0) + 2 * need
+        weakref.finalize(out, _release_bf16, dev, 2 * need)
+        return out
+    key = (w.device.index, )
     buf = _scratch.get(key)
     if buf is None or buf.numel() < need:
         buf = torch.empty(max(need, 32 << 20), dtype=torch.bfloat16, device=w.device)

@@ -138,14 +138,19 @@ class QuantWeight:
         return codecs.dequantize(self.raw_blocks(), self.ggml_type, (self.rows, self.K)).to(dtype)
 
     def expert(self, e: int) -> "QuantWeight":
-        """View of one expert's ``[N, K]`` matrix (no copy)."""
+        """View of one expert's ``[N, K]`` matrix (no copy).  The view object is created once per expert, so
+        state attached to it (a decoded copy for the tensor-core path) lives as long as the stack does."""
         if self.experts == 1:
             return self
+        views = self.__dict__.setdefault("_expert_views", {})
+        if e in views:
+            return views[e]
         out = []
         for p in self.planes:
             per = p.numel() // self.experts
             out.append(p[e * per:(e + 1) * per])
-        return QuantWeight(self.ggml_type, self.N, self.K, out, 1, f"{self.name}.{e}")
+        views[e] = QuantWeight(self.ggml_type, self.N, self.K, out, 1, f"{self.name}.{e}")
+        return views[e]
 
     def row_slice(self, start: int, stop: int) -> "QuantWeight":
         """Rows ``[start, stop)`` as a new weight sharing storage (tensor-parallel column shard)."""
