@@ -183,7 +183,7 @@ class GptOssModel(ModelBase):
                 tpx = self.tp_exchange()
                 if tpx is not None:
                     return self.forward_exchange_small(h, batch, want_logits, tpx)
-            elif not small:
+            elif not small and not batch.is_decode:      # sequence shards pay off for prompts, not for decode batches
                 sp = self.tp_seq(T)
                 if sp is not None:
                     return self.forward_seq_parallel(h, batch, want_logits, sp)

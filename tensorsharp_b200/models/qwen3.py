@@ -90,7 +90,7 @@ class Qwen3Model(ModelBase):
         h = self.inject_pending_embeddings(F.embed(self.tok_emb, batch.tokens))
         if h.is_cuda and T <= F.FUSED_MAX_M and F.can_fuse(h, self.layers[0].get("wqkv", self.layers[0].get("wq"))):
             return self.forward_fused_small(h, batch, want_logits)
-        if tp and not small and h.is_cuda:
+        if tp and not small and not batch.is_decode and h.is_cuda:     # prompts only: decode batches stay on the GEMV / GEMM + all-reduce path
             sp = self.tp_seq(T)
             if sp is not None:
                 return self.forward_seq_parallel(h, batch, want_logits, sp)
