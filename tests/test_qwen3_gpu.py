@@ -38,3 +38,35 @@ def test_batched_decode_matches_single(tiny_qwen3_path):
         m.reset_kv_cache()
         ls = m.forward(p).cpu()
         assert float((ls - lb[i]).norm() / ls.norm()) < 2e-2
+
+
+def test_sampled_decode_inside_the_graph(tiny_qwen3_path):
+    """Sampling runs inside the captured step: the same seed reproduces the run, another seed does not,
+    every drawn id is inside the vocabulary, and the penalty table counts exactly the drawn tokens."""
+    from tensorsharp_b200.ops import functional as F
+    from tensorsharp_b200.runtime.engine import DecodeGraph
+    from tensorsharp_b200.runtime.sampling import SamplingConfig
+
+    def run(seed):
+        m = ModelBase.create(tiny_qwen3_path, "cuda", max_context=256, max_seqs=4)
+        g = torch.Generator().manual_seed(3)
+        prompts = [torch.randint(0, 4096, (n,), generator=g).tolist() for n in (9, 21)]
+        seqs = [m.kv.new_seq() for _ in prompts]
+        first = F.argmax(m.forward_batch(m.kv.build_batch(seqs, prompts)))
+        cfg = SamplingConfig(temperature=0.9, top_k=50, top_p=0.95, min_p=0.0, repetition_penalty=1.1, seed=seed)
+        dg = DecodeGraph(m, seqs, 40, sampling=cfg)
+        dg.set_tokens(first.tolist())
+        dg.capture()
+        out = [dg.step().clone() for _ in range(24)]
+        torch.cuda.synchronize()
+        return torch.stack(out).cpu(), dg.counts.cpu(), dg.ngen.cpu()
+
+    a, ca, na = run(5)
+    b, _, _ = run(5)
+    c, _, _ = run(6)
+    assert torch.equal(a, b)
+    assert not torch.equal(a, c)
+    assert int(a.min()) >= 0 and int(a.max()) < 4096
+    assert na.tolist() == [24, 24]
+    for r in range(2):
+        assert torch.equal(torch.bincount(a[:, r].long(), minlength=ca.shape[1])[:ca.shape[1]].int(), ca[r])
