@@ -37,7 +37,7 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=None, help="sequences decoded together (default: 1; gptoss-20b: 64)")
     ap.add_argument("--prefill", type=int, default=None, help="prompt tokens per sequence (default: 2048; gptoss-20b: 1024)")
-    ap.add_argument("--model", default="qwen3-4b", choices=["qwen3-4b", "qwen3-tiny", "gptoss-20b", "gptoss-tiny"])
+    ap.add_argument("--model", default="qwen3-4b", choices=["qwen3-4b", "qwen3-tiny", "gptoss-20b", "gptoss-tiny", "qwen35-35b-a3b"])
     ap.add_argument("--prefill-repeats", type=int, default=3, help="timed prefill repetitions (median reported)")
     ap.add_argument("--no-graph", action="store_true", help="run decode steps eagerly (for kernel-level profiling)")
     ap.add_argument("--trace", default=None, metavar="FILE",
@@ -45,11 +45,10 @@ def parse_args():
                          "kernel events of the middle one to FILE (JSON) and print its per-kernel table to stderr")
     ap.add_argument("--cache-dir", default=os.environ.get("TSB_BENCH_CACHE", os.path.join(tempfile.gettempdir(), "tsb_bench")))
     a = ap.parse_args()
-    big_moe = a.model == "gptoss-20b"
     if a.batch is None:
-        a.batch = 64 if big_moe else 1
+        a.batch = {"gptoss-20b": 64, "qwen35-35b-a3b": 8}.get(a.model, 1)
     if a.prefill is None:
-        a.prefill = 1024 if big_moe else 2048
+        a.prefill = {"gptoss-20b": 1024, "qwen35-35b-a3b": 8192}.get(a.model, 2048)
     return a
 
 
@@ -112,6 +111,9 @@ MODEL_SHAPES = {
                        expert_ffn=2880, vocab=201088, window=128),
     "gptoss-tiny": dict(n_layers=2, hidden=256, n_heads=8, n_kv_heads=2, head_dim=64, n_experts=8, top_k=2,
                         expert_ffn=256, vocab=4096, window=16),
+    "qwen35-35b-a3b": dict(n_layers=40, hidden=2048, n_heads=16, n_kv_heads=2, head_dim=256, rope_dims=64, interval=4,
+                           hk=16, hv=32, dk=128, dv=128, conv_k=4, n_experts=256, top_k=8, expert_ffn=512, shared_ffn=512,
+                           ffn=6144, vocab=151936, scheme="Q4_K_M"),
 }
 MODEL_TEXT = {
     "qwen3-4b": ("Qwen3-4B-shaped Q4_K_M (36L, hidden 2560, 32q/8kv x128, ffn 9728, vocab 151936), random-init",
@@ -123,6 +125,10 @@ MODEL_TEXT = {
                    "window 128), MXFP4 experts + bf16 attention, random-init",
                    "bf16 activations / f32 accumulate, MXFP4 expert weights as stored",
                    "weights (12.5 GB) exceed the 126 MB L2; no flush needed"),
+    "qwen35-35b-a3b": ("Qwen3.5-35B-A3B-shaped Q4_K_M (40L, hidden 2048, GatedDeltaNet 16 QK / 32 V heads x128 on 3 of 4 layers, "
+                       "attention 16q/2kv x256, 256 experts top-8 + shared, expert ffn 512, vocab 151936), random-init",
+                       "bf16 activations / f32 accumulate, Q4_K_M weights as stored",
+                       "weights (about 20 GB) exceed the 126 MB L2; no flush needed"),
     "gptoss-tiny": ("tiny gpt-oss (2L, hidden 256, 8 experts top-2), random-init",
                     "bf16 activations / f32 accumulate, MXFP4 expert weights as stored", "tiny model: smoke configuration only"),
 }
@@ -136,7 +142,8 @@ def ensure_model(args, rank: int, world: int) -> str:
     done = path + ".done"
     if rank == 0 and not os.path.exists(done):
         from tensorsharp_b200.models import synth
-        writer = synth.write_gptoss if args.model.startswith("gptoss") else synth.write_qwen3
+        writer = (synth.write_gptoss if args.model.startswith("gptoss") else
+                  synth.write_qwen35 if args.model.startswith("qwen35") else synth.write_qwen3)
         writer(path, **MODEL_SHAPES[args.model], seed=0, device="cuda" if torch.cuda.is_available() else "cpu")
         open(done, "w").write("ok")
     if world > 1:
@@ -297,7 +304,7 @@ def run_ours(args) -> dict:
         "dtype": MODEL_TEXT[args.model][1], "data": "synthetic",
         "impl": "ours",
         "config": {"model": MODEL_TEXT[args.model][0], "global_batch": B, "seq_len": P, "decode_steps": K,
-                   "parallelism": (f"tp{world}" if not args.model.startswith("gptoss") else f"tp{world} attention + ep{world} experts"),
+                   "parallelism": (f"tp{world}" if args.model.startswith("qwen3-") else f"tp{world} attention + ep{world} experts"),
                    "l2": MODEL_TEXT[args.model][2],
                    "prefill_weights": "GEMMs of the prefill read a bf16 copy of each quantised matrix, decoded once at first use "
                                       "and kept in spare HBM (TSB_BF16_WEIGHT_CACHE_GB); decode streams the GGUF blocks"},
@@ -332,6 +339,11 @@ def run_reference(args) -> dict:
         from baseline.ref_harness import run as ref_run
     except Exception as exc:  # noqa: BLE001
         return {"impl": "reference", "unavailable": f"reference harness not importable: {exc}"}
+    if args.model.startswith("qwen35"):
+        if int(os.environ.get("RANK", "0")) != 0:
+            return None
+        return {"impl": "reference", "unavailable": "the reference runs Qwen3.5 through its C# per-op graph (Qwen35Model.cs) with the recurrent "
+                                                    "step on the host; no .NET SDK exists on this box"}
     if args.model.startswith("gptoss"):
         if int(os.environ.get("RANK", "0")) != 0:
             return None
