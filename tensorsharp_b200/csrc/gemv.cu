@@ -283,6 +283,8 @@ extern "C" int tsb_quantize_q8(const void* x, int x_is_f32, void* xq, void* xds,
 
 bool tsb_gemv_stream_eligible(const GemvArgs& a);                     // gemv_stream.cu
 int tsb_gemv_stream_launch(const GemvArgs& a, bool glu, cudaStream_t s);
+bool tsb_gemv_mma_eligible(const GemvArgs& a);                        // gemv_mma.cu
+int tsb_gemv_mma_launch(const GemvArgs& a, bool glu, cudaStream_t s);
 
 template <bool GLU>
 static int launch_gemv(const GemvArgs& a, int problems, cudaStream_t s) {
@@ -354,6 +356,7 @@ extern "C" int tsb_gemv_push(const void* p0, const void* p1, const void* p2, con
     a.M = M; a.x_div = x_div > 0 ? x_div : 1; a.out_f32 = out_f32; a.act = act;
     a.n_out = glu ? N / 2 : N;
     a.push = (const TpPush*)push;
+    if (tsb_gemv_mma_eligible(a)) return tsb_gemv_mma_launch(a, glu, (cudaStream_t)stream);
     if (tsb_gemv_stream_eligible(a)) return tsb_gemv_stream_launch(a, glu, (cudaStream_t)stream);
     return glu ? launch_gemv<true>(a, problems, (cudaStream_t)stream)
                : launch_gemv<false>(a, problems, (cudaStream_t)stream);

@@ -595,3 +595,27 @@ def test_gemv_row_pipeline_shapes(t, N, Kd, act, M):
         res = torch.randn(M, N, device=DEV)
         got = K().gemv(qw, xq=xq, xds=xds, M=M, bias=bias, residual=res)
         assert rel_err(got, y + res) < 3e-3
+
+
+@pytest.mark.parametrize("N,Kd,act", [(2048, 2560, "swiglu"), (2560, 4096, None), (1000, 1024, None), (40, 256, "swiglu")])
+@pytest.mark.parametrize("M", [5, 8, 11, 16])
+def test_gemv_tensor_core_batches_q4k(N, Kd, act, M):
+    """Batches of 5 to 16 rows over Q4_K weights run on the int8 tensor-core path: ragged row counts,
+    gated pairs, bias, residual, row scale."""
+    torch.manual_seed(60)
+    qw = QuantWeight.from_float(torch.randn(N, Kd, device=DEV) * 0.05, GGMLType.Q4_K)
+    x = torch.randn(M, Kd, device=DEV).bfloat16()
+    xq, xds = K().quantize_q8(x)
+    bias = torch.randn(N, device=DEV) * 0.1
+    y = expected_gemv(qw, x) + bias
+    if act:
+        F = N // 2
+        want = ref.glu(act, y[:, :F], y[:, F:])
+        got = K().gemv(qw, xq=xq, xds=xds, M=M, act=act, bias=bias, out_dtype=torch.bfloat16)
+        assert got.shape == (M, F)
+        assert rel_err(got, want) < 6e-3
+    else:
+        res = torch.randn(M, N, device=DEV)
+        scale = torch.rand(M, device=DEV) + 0.5
+        got = K().gemv(qw, xq=xq, xds=xds, M=M, bias=bias, residual=res, row_scale=scale)
+        assert rel_err(got, y * scale[:, None] + res) < 3e-3
