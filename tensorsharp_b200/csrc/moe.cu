@@ -313,10 +313,8 @@ __device__ __forceinline__ void mma_s8_16x8x32(int (&c)[4], const int (&a)[4], i
 template <bool MX>
 __device__ __forceinline__ void decode_q4_words(uint32_t wg, uint32_t wg8, int (&a)[4]) {
     if (MX) {
-        a[0] = mxfp4_lut4(wg & 0x0F0F0F0Fu);
-        a[1] = mxfp4_lut4(wg8 & 0x0F0F0F0Fu);
-        a[2] = mxfp4_lut4((wg >> 4) & 0x0F0F0F0Fu);
-        a[3] = mxfp4_lut4((wg8 >> 4) & 0x0F0F0F0Fu);
+        mxfp4_decode8(wg, a[0], a[2]);
+        mxfp4_decode8(wg8, a[1], a[3]);
     } else {
         a[0] = (int)__vsub4(wg & 0x0F0F0F0Fu, 0x08080808u);
         a[1] = (int)__vsub4(wg8 & 0x0F0F0F0Fu, 0x08080808u);
