@@ -269,6 +269,8 @@ __device__ __forceinline__ void rope_lookup(const QkvArgs& a, int t, int pair, f
     }
 }
 
+// NJ = 32-element slices a lane holds (head size up to 32 * NJ): the loops below run NJ times, not 16.
+template <int NJ>
 __global__ void __launch_bounds__(128) qkv_rope_kernel(QkvArgs a) {
     pdl_wait();
     pdl_trigger();
@@ -286,11 +288,11 @@ __global__ void __launch_bounds__(128) qkv_rope_kernel(QkvArgs a) {
     else { kind = 2; src = a.v; off = t * a.v_tok + (h - a.Hq - a.Hkv) * a.v_head; }
     const long slot = a.slot ? a.slot[t] : -1;
     if (kind != 0 && slot < 0) return;
-    // each lane holds up to 16 values: element e = lane + 32 * j
-    float v[16];
+    // each lane holds up to NJ values: element e = lane + 32 * j
+    float v[NJ];
     float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
+    for (int j = 0; j < NJ; ++j) {
         const int e = lane + 32 * j;
         float x = 0.f;
         if (e < Dh) x = a.in_f32 ? reinterpret_cast<const float*>(src)[off + e]
@@ -303,10 +305,10 @@ __global__ void __launch_bounds__(128) qkv_rope_kernel(QkvArgs a) {
     // the inputs, so the kernel is one memory round trip deep instead of three.
     const int rot = a.rp.rot_dim;
     const bool tab = a.cs_table != nullptr && kind != 2 && rot > 0;
-    float nwv[16];
-    float2 csv[16];
+    float nwv[NJ];
+    float2 csv[NJ];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
+    for (int j = 0; j < NJ; ++j) {
         const int e = lane + 32 * j;
         nwv[j] = (nw && e < Dh) ? nw[e] : 1.f;
         csv[j] = make_float2(1.f, 0.f);
@@ -319,7 +321,7 @@ __global__ void __launch_bounds__(128) qkv_rope_kernel(QkvArgs a) {
         ss = warp_sum(ss);
         const float rs = rsqrtf(ss / (float)Dh + a.eps);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
+        for (int j = 0; j < NJ; ++j) {
             const int e = lane + 32 * j;
             if (e < Dh) v[j] *= rs * nwv[j];
         }
@@ -330,7 +332,7 @@ __global__ void __launch_bounds__(128) qkv_rope_kernel(QkvArgs a) {
     else dst = a.v_cache + (slot * a.Hkv + (h - a.Hq - a.Hkv)) * Dh;
     if (kind == 2 || rot == 0) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
+        for (int j = 0; j < NJ; ++j) {
             const int e = lane + 32 * j;
             if (e < Dh) dst[e] = f2bf(kind == 0 ? v[j] * a.q_scale : v[j]);
         }
@@ -344,14 +346,14 @@ __global__ void __launch_bounds__(128) qkv_rope_kernel(QkvArgs a) {
         __shared__ float stage[4][512];
         float* st = stage[threadIdx.x >> 5];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
+        for (int j = 0; j < NJ; ++j) {
             const int e = lane + 32 * j;
             if (e < Dh) st[e] = v[j];
         }
         __syncwarp();
         const int half = rot >> 1;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
+        for (int j = 0; j < NJ; ++j) {
             const int e = lane + 32 * j;
             if (e >= Dh) continue;
             float o = v[j];
@@ -367,7 +369,7 @@ __global__ void __launch_bounds__(128) qkv_rope_kernel(QkvArgs a) {
     } else {
         // adjacent pairs (2i, 2i+1): the partner is in the neighbouring lane
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
+        for (int j = 0; j < NJ; ++j) {
             const int e = lane + 32 * j;
             const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
             if (e >= Dh) continue;
@@ -388,7 +390,12 @@ extern "C" int tsb_qkv_rope(const QkvArgs* args, void* stream) {
     TSB_CHECK_ARG(a.rp.rot_dim <= a.Dh && a.rp.rot_dim % 2 == 0, "qkv_rope: bad rot_dim %d", a.rp.rot_dim);
     const long warps = (long)a.T * (a.Hq + 2 * a.Hkv);
     if (warps == 0) return TSB_OK;
-    TSB_CHECK_CUDA(tsb_launch(qkv_rope_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, (cudaStream_t)stream, a));
+    const dim3 grid((unsigned)((warps + 3) / 4)), block(128);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (a.Dh <= 64) TSB_CHECK_CUDA(tsb_launch(qkv_rope_kernel<2>, grid, block, 0, st, a));
+    else if (a.Dh <= 128) TSB_CHECK_CUDA(tsb_launch(qkv_rope_kernel<4>, grid, block, 0, st, a));
+    else if (a.Dh <= 256) TSB_CHECK_CUDA(tsb_launch(qkv_rope_kernel<8>, grid, block, 0, st, a));
+    else TSB_CHECK_CUDA(tsb_launch(qkv_rope_kernel<16>, grid, block, 0, st, a));
     return TSB_OK;
 }
 
