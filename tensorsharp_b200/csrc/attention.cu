@@ -40,6 +40,9 @@ struct AttnArgs {
     // Set by the launcher, not the caller: per (sequence, KV head) arrival counters.  When present, the
     // CTA that finishes a head group last merges the split partials itself and no combine kernel runs.
     unsigned* ticket;
+    // Decode: positions per split fixed by the caller (a multiple of 32), so that a CTA's range and its block-table
+    // entries do not wait for the sequence length; 0 = derive it from the length (ceil(span / splits), rounded to 32).
+    int split_len;
 };
 
 __device__ __forceinline__ long kv_slot(const AttnArgs& a, int b, int j) {
@@ -68,13 +71,23 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
 #pragma unroll
     for (int i = 0; i < (QV + 127) / 128; ++i)
         if (threadIdx.x + i * 128 < QV) qreg[i] = qsrc[threadIdx.x + i * 128];
+    // With a caller-fixed split length and no window, the first chunk's cache slot does not depend on the
+    // sequence length either: its block-table entry is requested now (the table row is max_pages long and
+    // zero beyond the reserved pages, so the read is always in bounds) and validated against the length later.
+    const bool fixed = a.split_len > 0 && a.window == 0;
+    long slot_first = 0;
+    if (fixed) {
+        const int j0 = split * a.split_len + warp * 32 + lane;
+        const int page = min(j0 / a.page_size, a.max_pages - 1);
+        slot_first = (long)a.block_table[(long)b * a.max_pages + page] * a.page_size + j0 % a.page_size;
+    }
     const int len = a.kv_lens[b];
 #pragma unroll
     for (int i = 0; i < (QV + 127) / 128; ++i)
         if (threadIdx.x + i * 128 < QV) reinterpret_cast<uint4*>(&qs[0][0])[threadIdx.x + i * 128] = qreg[i];
     const int lo = (a.window > 0 && len > a.window) ? len - a.window : 0;
     const int span = len - lo;
-    const int per = (((span + a.splits - 1) / a.splits) + 31) & ~31;
+    const int per = a.split_len > 0 ? a.split_len : ((((span + a.splits - 1) / a.splits) + 31) & ~31);
     const int s0 = lo + split * per, s1 = min(len, s0 + per);
     __syncthreads();
 
@@ -89,7 +102,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
     for (int base = s0 + warp * 32; base < s1; base += 128) {
         const int j = base + lane;
         const bool valid = j < s1;
-        const long slot = valid ? kv_slot(a, b, j) : 0;
+        const long slot = !valid ? 0 : ((fixed && base == s0 + warp * 32) ? slot_first : kv_slot(a, b, j));
         float s[G];
 #pragma unroll
         for (int g = 0; g < G; ++g) s[g] = 0.f;
@@ -279,7 +292,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
 // grid (Hq, B), DH threads (rounded up to 32): merge split partials, apply the sink, normalise.
 // Latency is all that matters here (a few KB per block), so nothing is read in a dependent loop: each
 // lane fetches the (max, sum) of two splits at once, the warp reduces them, and the partial outputs
-// are fetched sixteen splits at a time before any is used.  At most 64 splits.
+// are fetched thirty-two splits at a time before any is used.  At most 64 splits.
 __global__ void attn_combine_kernel(AttnArgs a) {
     pdl_wait();
     pdl_trigger();
@@ -294,12 +307,12 @@ __global__ void attn_combine_kernel(AttnArgs a) {
     const float ll = warp_sum(ml0.y * c0 + ml1.y * c1) + (a.sinks ? __expf(sink - mm) : 0.f);
     float o = 0.f;
     const int dd = d < a.Dh ? d : 0;
-    for (int s0 = 0; s0 < a.splits; s0 += 16) {
-        float pv[16];
+    for (int s0 = 0; s0 < a.splits; s0 += 32) {
+        float pv[32];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) pv[i] = (s0 + i < a.splits) ? a.part_o[(base + s0 + i) * a.Dh + dd] : 0.f;
+        for (int i = 0; i < 32; ++i) pv[i] = (s0 + i < a.splits) ? a.part_o[(base + s0 + i) * a.Dh + dd] : 0.f;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
+        for (int i = 0; i < 32; ++i) {
             const int sp = s0 + i;
             const float c = __shfl_sync(0xffffffffu, sp < 32 ? c0 : c1, sp & 31);
             o += pv[i] * c;

@@ -344,6 +344,14 @@ def qkv_rope_cache(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, Hq: int
     return qf * q_scale
 
 
+def decode_split_len(batch: Batch, splits: int, window: int) -> int:
+    """Positions per split fixed on the host from the reserved maximum length (0 with a sliding window, whose
+    start depends on the actual length): the kernel then knows its range before it has read the length."""
+    if window:
+        return 0
+    return ((batch.max_kv_len + splits - 1) // splits + 31) & ~31
+
+
 def decode_splits(batch: Batch, Hkv: int, window: int) -> int:
     """Split-KV factor for decode attention: enough CTAs to cover the GPU's 148 SMs."""
     span = batch.max_kv_len if not window else min(batch.max_kv_len, window)
@@ -362,8 +370,9 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
     T = q.shape[0]
     if as_act:
         if q.is_cuda and batch.is_decode and (Hq // Hkv) in (1, 2, 4, 8) and Dh % 32 == 0:
+            sp = decode_splits(batch, Hkv, window)
             out, oq, ods = _k().attn_decode(q, k_cache, v_cache, batch.block_table, batch.kv_lens, scale=scale, Hq=Hq, Hkv=Hkv,
-                                            Dh=Dh, page_size=batch.page_size, splits=decode_splits(batch, Hkv, window),
+                                            Dh=Dh, page_size=batch.page_size, splits=sp, split_len=decode_split_len(batch, sp, window),
                                             sinks=sinks, softcap=softcap, window=window, want_q8=True)
             return Act(out.view(T, Hq * Dh), oq, ods)
         return as_act_of(attention(q, k_cache, v_cache, batch, scale=scale, Hq=Hq, Hkv=Hkv, Dh=Dh, window=window, sinks=sinks,
@@ -372,8 +381,9 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
         kk = _k()
         G = Hq // Hkv
         if batch.is_decode and G in (1, 2, 4, 8):
+            sp = decode_splits(batch, Hkv, window)
             out = kk.attn_decode(q, k_cache, v_cache, batch.block_table, batch.kv_lens, scale=scale, Hq=Hq, Hkv=Hkv,
-                                 Dh=Dh, page_size=batch.page_size, splits=decode_splits(batch, Hkv, window),
+                                 Dh=Dh, page_size=batch.page_size, splits=sp, split_len=decode_split_len(batch, sp, window),
                                  sinks=sinks, softcap=softcap, window=window)
         else:
             out = kk.attn_prefill(q, k_cache, v_cache, batch.block_table, batch.kv_lens, batch.cu_q, batch.max_q_len,

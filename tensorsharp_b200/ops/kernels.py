@@ -59,7 +59,7 @@ class AttnArgs(C.Structure):
                 ("scale", C.c_float), ("softcap", C.c_float), ("window", C.c_int),
                 ("B", C.c_int), ("Hq", C.c_int), ("Hkv", C.c_int), ("Dh", C.c_int), ("page_size", C.c_int),
                 ("max_pages", C.c_int), ("splits", C.c_int), ("q_pos0", _vp), ("lse_out", _vp),
-                ("out_q", _vp), ("out_ds", _vp), ("ticket", _vp)]
+                ("out_q", _vp), ("out_ds", _vp), ("ticket", _vp), ("split_len", C.c_int)]
 
 
 _configured = False
@@ -380,7 +380,7 @@ def _attn_args(q, k_cache, v_cache, out, block_table, kv_lens, cu_q, sinks, scal
 
 
 def attn_decode(q, k_cache, v_cache, block_table, kv_lens, *, scale, Hq, Hkv, Dh, page_size, splits, sinks=None,
-                softcap=0.0, window=0, out=None, want_q8=False):
+                softcap=0.0, window=0, out=None, want_q8=False, split_len=0):
     """q [B, Hq, Dh] bf16; one query per sequence against the paged cache.  ``want_q8`` also returns the
     output as int8 groups of 32 with (scale, sum) written by the combine kernel: (out, q, ds)."""
     B = q.shape[0]
@@ -389,6 +389,7 @@ def attn_decode(q, k_cache, v_cache, block_table, kv_lens, *, scale, Hq, Hkv, Dh
     a = _attn_args(q, k_cache, v_cache, out, block_table, kv_lens, None, sinks, scale, softcap, window, Hq, Hkv, Dh,
                    page_size, B)
     a.splits = splits
+    a.split_len = split_len
     part_o = torch.empty((B, Hq, splits, Dh), dtype=torch.float32, device=q.device)
     part_ml = torch.empty((B, Hq, splits, 2), dtype=torch.float32, device=q.device)
     a.part_o, a.part_ml = _p(part_o), _p(part_ml)
