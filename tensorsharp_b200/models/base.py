@@ -62,14 +62,22 @@ def supported_architectures() -> List[str]:
 
 class ModelBase:
     supports_kv_truncation = True
+    supports_pipeline = False
 
     def __init__(self, path: str, device="cuda", *, max_context: Optional[int] = None, max_seqs: int = 1,
                  page_size: int = 64, kv_dtype: Optional[torch.dtype] = None, tp_rank: int = 0, tp_size: int = 1,
-                 ep_rank: int = 0, ep_size: int = 1, comm=None):
+                 ep_rank: int = 0, ep_size: int = 1, comm=None, pp_rank: int = 0, pp_size: int = 1, pp_comm=None):
         self.path = path
         self.device = torch.device(device)
         self.gguf = GGUFFile(path)
         self.tp_rank, self.tp_size, self.ep_rank, self.ep_size, self.comm = tp_rank, tp_size, ep_rank, ep_size, comm
+        # pipeline parallelism: this process holds a contiguous range of layers (and only their KV cache);
+        # the first stage owns the embedding, the last one the output norm and lm_head
+        self.pp_rank, self.pp_size, self.pp_comm = pp_rank, pp_size, pp_comm
+        if pp_size > 1 and not self.supports_pipeline:
+            raise ValueError(f"{type(self).__name__} has no pipeline-parallel path")
+        if pp_size > 1 and tp_size > 1:
+            raise ValueError("pipeline stages are not combined with tensor parallelism")
         g = self.gguf
         self.arch = g.get_str("general.architecture", "")
         self.cfg = self.parse_base_config()
@@ -209,9 +217,24 @@ class ModelBase:
         raise NotImplementedError
 
     # ------------------------------------------------------------------ KV pool
+    @property
+    def layer_range(self) -> Tuple[int, int]:
+        """[first, last + 1) of the layers this pipeline stage runs (all of them without pipelining)."""
+        from ..parallel.dist import even_split
+        return even_split(self.cfg.n_layers, self.pp_size, self.pp_rank)
+
+    @property
+    def is_first_stage(self) -> bool:
+        return self.pp_rank == 0
+
+    @property
+    def is_last_stage(self) -> bool:
+        return self.pp_rank == self.pp_size - 1
+
     def kv_layer_shapes(self) -> List[Optional[Tuple[int, int]]]:
         c = self.cfg
-        return [(c.n_kv_heads // self.tp_size, c.head_dim)] * c.n_layers
+        l0, l1 = self.layer_range
+        return [(c.n_kv_heads // self.tp_size, c.head_dim) if l0 <= l < l1 else None for l in range(c.n_layers)]
 
     def kv_donors(self) -> Dict[int, int]:
         return {}

@@ -23,6 +23,8 @@ from .base import ModelBase, register_architecture
 
 @register_architecture("qwen3", "qwen2", "llama")
 class Qwen3Model(ModelBase):
+    supports_pipeline = True
+
     def load_weights(self) -> None:
         c = self.cfg
         tp, r = self.tp_size, self.tp_rank
@@ -32,15 +34,20 @@ class Qwen3Model(ModelBase):
         # row-parallel down), the vocabulary is dealt evenly for the lm_head
         (q0, q1), (k0, k1) = head_split(c.n_heads, c.n_kv_heads, tp, r)
         self.Hq, self.Hkv = q1 - q0, k1 - k0
-        self.tok_emb = self.qw("token_embd.weight")
-        self.out_norm = self.f32("output_norm.weight")
-        self.lm_head = self.qw("output.weight", optional=True) or self.tok_emb
-        self.vocab_sharded = tp > 1 and c.vocab % tp == 0
+        # pipeline stages: the embedding lives on the first stage (and on the last one when the lm_head is tied
+        # to it), the output norm and lm_head on the last
+        l0, l1 = self.layer_range
+        self.l0 = l0
+        tied = not self.has("output.weight")
+        self.tok_emb = self.qw("token_embd.weight") if (self.is_first_stage or (self.is_last_stage and tied)) else None
+        self.out_norm = self.f32("output_norm.weight") if self.is_last_stage else None
+        self.lm_head = (self.qw("output.weight", optional=True) or self.tok_emb) if self.is_last_stage else None
+        self.vocab_sharded = tp > 1 and c.vocab % tp == 0 and self.lm_head is not None
         if self.vocab_sharded:
             v0, v1 = even_split(c.vocab, tp, r)
             self.lm_head = self.lm_head.row_slice(v0, v1)
         self.layers = []
-        for l in range(c.n_layers):
+        for l in range(l0, l1):
             p = f"blk.{l}."
             q, k, v = self.qw(p + "attn_q.weight"), self.qw(p + "attn_k.weight"), self.qw(p + "attn_v.weight")
             wo, down = self.qw(p + "attn_output.weight"), self.qw(p + "ffn_down.weight")
@@ -87,6 +94,8 @@ class Qwen3Model(ModelBase):
         tp = self.tp_size > 1
         small = T <= F.GEMV_MAX_M
         mid = torch.float32 if small else torch.bfloat16
+        if self.pp_size > 1:
+            return self.forward_stage(batch, want_logits)
         h = self.inject_pending_embeddings(F.embed(self.tok_emb, batch.tokens))
         if h.is_cuda and T <= F.FUSED_MAX_M and F.can_fuse(h, self.layers[0].get("wqkv", self.layers[0].get("wq"))):
             return self.forward_fused_small(h, batch, want_logits)
@@ -101,10 +110,10 @@ class Qwen3Model(ModelBase):
         n_layers = len(self.layers)
         for l, L in enumerate(self.layers):
             q, k, v = self.qkv_proj(a, L, T, mid)
-            qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=self.kv.k[l],
-                                  v_cache=self.kv.v[l], rope=self.rope, qn=L["q_norm"], kn=L["k_norm"], eps=c.eps)
+            qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=self.kv.k[self.l0 + l],
+                                  v_cache=self.kv.v[self.l0 + l], rope=self.rope, qn=L["q_norm"], kn=L["k_norm"], eps=c.eps)
             qr = self.q_post_scale(qr, batch)
-            o = F.attention(qr, self.kv.k[l], self.kv.v[l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh,
+            o = F.attention(qr, self.kv.k[self.l0 + l], self.kv.v[self.l0 + l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh,
                             as_act=small and L["wo"].uses_q8_activations)
             if tpx is not None:
                 tpx.linear_push(F.as_act(o), L["wo"])
@@ -128,6 +137,41 @@ class Qwen3Model(ModelBase):
         last = h[batch.last_idx].contiguous()
         a = F.norm(last, self.out_norm, c.eps, want_q8=True)
         return self.lm_head_logits(a)
+
+    def forward_stage(self, batch: Batch, want_logits: bool) -> Optional[torch.Tensor]:
+        """One pipeline stage: the residual stream comes from the previous stage (or from the embedding on
+        the first), runs through this stage's layers and goes to the next stage; the last stage returns the
+        logits, the others ``None``.  Every stage is called with the same batch."""
+        from ..parallel.pipeline import recv_hidden, send_hidden
+        c = self.cfg
+        Hq, Hkv, Dh, T = self.Hq, self.Hkv, c.head_dim, batch.T
+        small = T <= F.GEMV_MAX_M
+        mid = torch.float32 if small else torch.bfloat16
+        if self.is_first_stage:
+            h = self.inject_pending_embeddings(F.embed(self.tok_emb, batch.tokens))
+        else:
+            h = recv_hidden(self.pp_comm, self.pp_rank - 1, (T, c.hidden), self.device)
+        for l, L in enumerate(self.layers):
+            a = F.norm(h, L["attn_norm"], c.eps, want_q8=small)
+            q, k, v = self.qkv_proj(a, L, T, mid)
+            qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=self.kv.k[self.l0 + l],
+                                  v_cache=self.kv.v[self.l0 + l], rope=self.rope, qn=L["q_norm"], kn=L["k_norm"], eps=c.eps)
+            qr = self.q_post_scale(qr, batch)
+            o = F.attention(qr, self.kv.k[self.l0 + l], self.kv.v[self.l0 + l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh)
+            h = self.row_parallel(F.as_act(o), L["wo"], h)
+            a = F.norm(h, L["ffn_norm"], c.eps, want_q8=small)
+            if "gate_up" in L:
+                gu = F.linear(a, L["gate_up"], act="swiglu", out_dtype=torch.bfloat16)
+            else:
+                gu = F.glu("swiglu", F.linear(a, L["gate"], out_dtype=mid), F.linear(a, L["up"], out_dtype=mid))
+            h = self.row_parallel(F.as_act(gu), L["down"], h)
+        if not self.is_last_stage:
+            send_hidden(self.pp_comm, self.pp_rank + 1, h)
+            return None
+        if not want_logits:
+            return None
+        last = h[batch.last_idx].contiguous()
+        return self.lm_head_logits(F.norm(last, self.out_norm, c.eps, want_q8=True))
 
     def qkv_proj(self, a, L, T: int, mid):
         Hq, Hkv, Dh = self.Hq, self.Hkv, self.cfg.head_dim
@@ -163,10 +207,10 @@ class Qwen3Model(ModelBase):
                 v = qkv[:, (Hq + Hkv) * Dh:].view(T, Hkv, Dh)
             else:
                 q, k, v = proj(L["wq"]).view(T, Hq, Dh), proj(L["wk"]).view(T, Hkv, Dh), proj(L["wv"]).view(T, Hkv, Dh)
-            qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=self.kv.k[l],
-                                  v_cache=self.kv.v[l], rope=self.rope, qn=L["q_norm"], kn=L["k_norm"], eps=c.eps)
+            qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=self.kv.k[self.l0 + l],
+                                  v_cache=self.kv.v[self.l0 + l], rope=self.rope, qn=L["q_norm"], kn=L["k_norm"], eps=c.eps)
             qr = self.q_post_scale(qr, batch)
-            o = F.attention(qr, self.kv.k[l], self.kv.v[l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh).view(T, Hq * Dh)
+            o = F.attention(qr, self.kv.k[self.l0 + l], self.kv.v[self.l0 + l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh).view(T, Hq * Dh)
             if tpx is not None:
                 tpx.linear_push_fused(o, L["wo"])
                 a = tpx.reduce_norm(h, L["ffn_norm"], c.eps)
@@ -226,10 +270,10 @@ class Qwen3Model(ModelBase):
                 q = sp.gemm_ag(L["wq"], T).view(T, Hq, Dh)
                 k = sp.gemm_ag(L["wk"], T).view(T, Hkv, Dh)
                 v = sp.gemm_ag(L["wv"], T).view(T, Hkv, Dh)
-            qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=self.kv.k[l],
-                                  v_cache=self.kv.v[l], rope=self.rope, qn=L["q_norm"], kn=L["k_norm"], eps=c.eps)
+            qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=self.kv.k[self.l0 + l],
+                                  v_cache=self.kv.v[self.l0 + l], rope=self.rope, qn=L["q_norm"], kn=L["k_norm"], eps=c.eps)
             qr = self.q_post_scale(qr, batch)
-            o = F.attention(qr, self.kv.k[l], self.kv.v[l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh)
+            o = F.attention(qr, self.kv.k[self.l0 + l], self.kv.v[self.l0 + l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh)
             sp.gemm_rs(o.view(T, Hq * Dh), L["wo"])
             sp.norm_gather(h, L["ffn_norm"], c.eps, True)
             if "gate_up" in L:

@@ -58,3 +58,53 @@ def test_tp2_matches_single_rank(tiny_qwen3_path, tmp_path):
     mp.spawn(_worker, args=(2, _free_port(), tiny_qwen3_path, prompt, out), nprocs=2, join=True)
     l1, l2 = torch.load(out)
     assert torch.allclose(l1, s1, atol=5e-3) and torch.allclose(l2, s2, atol=5e-3)
+
+
+def _pp_worker(rank, world, port, path, prompt, n_new, out_path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    from tensorsharp_b200.models.base import ModelBase
+    from tensorsharp_b200.parallel import pipeline
+    from tensorsharp_b200.parallel.dist import Communicator
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        m = ModelBase.create(path, "cpu", max_context=128, pp_rank=rank, pp_size=world, pp_comm=Communicator(rank, world))
+        held = [k is not None for k in m.kv.k]
+        toks = pipeline.generate(m, prompt, n_new, prefill_chunk=8)       # chunked prefill crosses the stages too
+        torch.save((toks, held, m.layer_range, m.tok_emb is not None, m.lm_head is not None), f"{out_path}.{rank}")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_pipeline_stages_match_single_process(tiny_qwen3_path, tmp_path, world):
+    """Layer ranges on successive gloo ranks, the residual stream sent stage to stage, the sampled token
+    broadcast back: every rank returns the tokens the single-process model generates, and each stage
+    holds only its own layers' KV cache."""
+    from tensorsharp_b200.models.base import ModelBase
+    from tensorsharp_b200.runtime.engine import generate
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, 4096, (21,), generator=g).tolist()
+    single = ModelBase.create(tiny_qwen3_path, "cpu", max_context=128)
+    want = generate(single, prompt, 6)
+    out = str(tmp_path / "pp.pt")
+    mp.spawn(_pp_worker, args=(world, _free_port(), tiny_qwen3_path, prompt, 6, out), nprocs=world, join=True)
+    n_layers = single.cfg.n_layers
+    covered = []
+    for r in range(world):
+        toks, held, (l0, l1), has_emb, has_head = torch.load(f"{out}.{r}")
+        assert toks == want
+        assert held == [l0 <= l < l1 for l in range(n_layers)]
+        covered += list(range(l0, l1))
+        assert has_head == (r == world - 1)
+        assert has_emb == (r == 0 or r == world - 1)          # tied embeddings: the last stage needs them for the lm_head
+    assert covered == list(range(n_layers))
+
+
+def test_pipeline_rejects_models_without_a_stage_path(tmp_path):
+    from tensorsharp_b200.models import synth
+    from tensorsharp_b200.models.base import ModelBase
+    p = str(tmp_path / "g.gguf")
+    synth.write_gptoss(p, device="cpu")
+    with pytest.raises(ValueError):
+        ModelBase.create(p, "cpu", max_context=64, pp_rank=0, pp_size=2)

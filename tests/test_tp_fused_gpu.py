@@ -118,3 +118,18 @@ def test_single_rank_push_then_reduce_round_trip():
         assert torch.allclose(a.ds, ref.ds, atol=1e-3, rtol=1e-3)
     assert tpx.status() == 0
     tpx.close()
+
+
+def test_pipeline_stages_over_nccl(kv8_model_path):
+    """Two pipeline stages on two GPUs (NCCL send / recv of the residual stream, token broadcast back)
+    generate what one GPU generates."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TSB_WORKER_MODE="pipeline")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(HERE, "tp_worker.py"), kv8_model_path]
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    lines = [l for l in p.stdout.splitlines() if l.startswith("PPCHECK ")]
+    assert p.returncode == 0 and lines, f"rc={p.returncode}\nstdout:\n{p.stdout[-3000:]}\nstderr:\n{p.stderr[-3000:]}"
+    r = json.loads(lines[0][8:])
+    assert r["ranks_agree"] == 2 and r["tokens"] == r["want"], r

@@ -13,12 +13,36 @@ import torch  # noqa: E402
 def main():
     from tensorsharp_b200.parallel.dist import init_from_env
     comm = init_from_env()
+    if os.environ.get("TSB_WORKER_MODE") == "pipeline":
+        check_pipeline(sys.argv[1], comm)
+        comm.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
     check_context_parallel(comm)
     for path in sys.argv[1:]:
         check_model(path, comm)
     comm.barrier()
     torch.cuda.synchronize()
     os._exit(0)          # skip NCCL teardown: it can block while captured graphs still hold its kernels
+
+
+def check_pipeline(path, comm):
+    """Layer ranges on successive GPUs with NCCL point-to-point hand-off: every rank must produce the
+    tokens one GPU generates."""
+    from tensorsharp_b200.models.base import ModelBase
+    from tensorsharp_b200.parallel import pipeline
+    from tensorsharp_b200.runtime.engine import generate
+    g = torch.Generator().manual_seed(9)
+    prompt = torch.randint(0, 4096, (150,), generator=g).tolist()
+    single = ModelBase.create(path, comm.device, max_context=256)
+    want = generate(single, prompt, 8)
+    del single
+    m = ModelBase.create(path, comm.device, max_context=256, pp_rank=comm.rank, pp_size=comm.size, pp_comm=comm)
+    got = pipeline.generate(m, prompt, 8, prefill_chunk=64)
+    same = torch.tensor([int(got == want)], device=comm.device)
+    comm.all_reduce(same)
+    if comm.rank == 0:
+        print("PPCHECK " + json.dumps({"world": comm.size, "ranks_agree": int(same[0]), "tokens": got, "want": want}), flush=True)
 
 
 def check_context_parallel(comm):
