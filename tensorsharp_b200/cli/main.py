@@ -523,6 +523,17 @@ def load_model(o: CliOptions, log):
     kw: Dict[str, Any] = {}
     if o.max_context:
         kw["max_context"] = o.max_context
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if o.tp > 1 or world > 1:
+        # one process per GPU, started by ``python -m torch.distributed.run --nproc-per-node N -m tensorsharp_b200.cli --tp N``
+        if world != max(o.tp, 1):
+            raise ValueError(f"--tp {o.tp} needs {o.tp} processes (WORLD_SIZE is {world}); start the CLI with "
+                             f"python -m torch.distributed.run --nproc-per-node {max(o.tp, 2)} --master-addr 127.0.0.1 "
+                             f"-m tensorsharp_b200.cli --tp {max(o.tp, 2)} ...")
+        from ..parallel.dist import init_from_env
+        comm = init_from_env("gloo" if device == "cpu" else None)
+        device = str(comm.device) if device != "cpu" else "cpu"
+        kw.update(tp_rank=comm.rank, tp_size=comm.size, comm=comm)
     log.info(Ev.ModelLoadStarted, "Loading model {ModelFile} on backend {Backend} (path={ModelPath})",
              ModelFile=os.path.basename(o.model), Backend=o.backend, ModelPath=o.model)
     t0 = time.perf_counter()
@@ -590,6 +601,8 @@ def _run(o: CliOptions, con: Console, log) -> int:
         con.error(USAGE)
         return 1
     model = load_model(o, log)
+    if getattr(model, "tp_rank", 0) != 0:
+        con = Console(open(os.devnull, "w"), con.err)          # every rank runs the same steps; rank 0 does the talking
     try:
         attach_projector(model, o, log)
         if o.run_test:

@@ -156,3 +156,10 @@ def test_interactive_session_commands_and_kv_reuse(tiny_qwen3_path, tmp_path):
     assert "Multi-line input on" in text and "Conversation history and KV cache cleared." in text and text.rstrip().endswith("Bye.")
     assert [m.role for m in s.history] == [] and s.kv.is_empty
     model.close()
+
+
+def test_tp_flag_needs_matching_process_count(tiny_qwen3_path, monkeypatch):
+    """``--tp 2`` in a single process explains how to start the job instead of silently running unsharded."""
+    monkeypatch.delenv("WORLD_SIZE", raising=False)
+    rc, out, err = run_cli(["--model", tiny_qwen3_path, "--backend", "cpu", "--tp", "2", "--benchmark"])
+    assert rc == 1 and "torch.distributed.run" in err
