@@ -94,8 +94,24 @@ def main(argv=None) -> int:
     except ValueError as e:
         print(f"error: {e}", file=sys.stderr)
         return 2
+    # Tensor-parallel serving: started as ``python -m torch.distributed.run --nproc-per-node N -m tensorsharp_b200.server ...``
+    # every process holds one shard; rank 0 runs the HTTP front end and announces each model call, the others mirror it.
+    comm = None
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        from ..parallel.dist import init_from_env
+        from ..parallel.replicated import follower_main, leader_factory, shutdown_followers
+        cpu_only = (try_resolve_supported_backend(options, read_configured_backend_input(argv))[0] or "") == "cpu"
+        comm = init_from_env("gloo" if cpu_only else None)
+        if comm.rank != 0:
+            follower_main(comm)
+            return 0
     provider = setup_file_logging(options.log_directory, prefix="tensorsharp-server", enabled=options.file_logging_enabled)
-    app = ServerApp(options, log_provider=provider)
+    svc = None
+    if comm is not None:
+        from .model_service import ModelService
+        svc = ModelService(None, model_factory=leader_factory(comm), max_context=options.max_context,
+                           max_sessions=options.max_sessions)
+    app = ServerApp(options, svc=svc, log_provider=provider)
     log = app.logger("TensorSharp.Server")
     listen = f"http://{options.host}:{options.port}"
     emit_banner(log, options, listen)
@@ -111,6 +127,8 @@ def main(argv=None) -> int:
         log.info(Ev.HostStopping, "TensorSharp.Server stopping")
         httpd.server_close()
         app.svc.close()
+        if comm is not None:
+            shutdown_followers(comm)
         log.info(Ev.HostStopped, "TensorSharp.Server stopped")
         if provider is not None:
             provider.close()

@@ -108,3 +108,53 @@ def test_pipeline_rejects_models_without_a_stage_path(tmp_path):
     synth.write_gptoss(p, device="cpu")
     with pytest.raises(ValueError):
         ModelBase.create(p, "cpu", max_context=64, pp_rank=0, pp_size=2)
+
+
+def _serve_worker(rank, world, port, path, out_path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    from tensorsharp_b200.parallel.dist import Communicator
+    from tensorsharp_b200.parallel.replicated import follower_main, leader_factory, shutdown_followers
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    comm = Communicator(rank, world)
+    try:
+        if rank != 0:
+            n = follower_main(comm)
+            torch.save(n, f"{out_path}.{rank}")
+            return
+        from tensorsharp_b200.runtime.chat import ChatMessage
+        from tensorsharp_b200.runtime.sampling import SamplingConfig
+        from tensorsharp_b200.server.model_service import ModelService
+        svc = ModelService(model_factory=leader_factory(comm), max_context=256)
+        svc.load_model(path, None, "cpu")
+        greedy = SamplingConfig.greedy()
+        hist = [ChatMessage(role="user", content="Hello there")]
+        first = "".join(svc.chat_stream(hist, 6, sampling=greedy))
+        hist += [ChatMessage(role="assistant", content=first), ChatMessage(role="user", content="and again")]
+        items = list(svc.chat_stream_with_metrics(hist, 5, sampling=greedy))
+        second = "".join(i.piece for i in items if i.piece)
+        svc.close()
+        shutdown_followers(comm)
+        torch.save((first, second), f"{out_path}.0")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_front_end_on_rank0_with_follower_shards(tiny_qwen3_path, tmp_path):
+    """The model service runs on rank 0 only; the follower rank mirrors every call on its shard, so a
+    two-turn chat (prefill, decode, KV reuse on the second turn) gives the single-process text."""
+    from tensorsharp_b200.runtime.chat import ChatMessage
+    from tensorsharp_b200.runtime.sampling import SamplingConfig
+    from tensorsharp_b200.server.model_service import ModelService
+    svc = ModelService(max_context=256)
+    svc.load_model(tiny_qwen3_path, None, "cpu")
+    greedy = SamplingConfig.greedy()
+    hist = [ChatMessage(role="user", content="Hello there")]
+    first = "".join(svc.chat_stream(hist, 6, sampling=greedy))
+    hist += [ChatMessage(role="assistant", content=first), ChatMessage(role="user", content="and again")]
+    second = "".join(svc.chat_stream(hist, 5, sampling=greedy))
+    svc.close()
+    out = str(tmp_path / "serve.pt")
+    mp.spawn(_serve_worker, args=(2, _free_port(), tiny_qwen3_path, out), nprocs=2, join=True)
+    assert torch.load(f"{out}.0") == (first, second)
+    assert torch.load(f"{out}.1") > 10          # the follower executed the leader's commands
