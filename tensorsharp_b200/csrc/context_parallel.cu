@@ -66,6 +66,7 @@ __global__ void __launch_bounds__(256) cp_publish_kernel(const CpRing* g, const 
         }
     }
     __syncthreads();
+    if (!s_ok) return;                  // a reader may still be inside this half: leave it alone, the status word says why
     bf16* dst = g->stage[g->rank] + (long)(e & 1u) * g->half_stride;
     const long vecs = n_elems / 8;
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < vecs; i += (long)gridDim.x * blockDim.x) {

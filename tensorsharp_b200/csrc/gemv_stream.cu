@@ -27,7 +27,7 @@ template <int M, bool GLU, bool Q5, int D>
 __global__ void __launch_bounds__(128) gemv_stream_kernel(GemvArgs a, int ppw) {
     extern __shared__ uint4 stream_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int K = a.w.K, nb = K >> 8, kb = K >> 5;
+    const int K = a.w.K, nb = K >> 8;
     constexpr int BLK16 = Q5 ? 11 : 9;                 // 16-byte chunks per 256-value block
     const int chunks = nb * BLK16;                     // per row
     uint4* ring = stream_smem + (long)warp * D * chunks;
