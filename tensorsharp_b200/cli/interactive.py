@@ -165,6 +165,9 @@ class InteractiveSession:
             return None
 
     def print_banner(self) -> None:
+        from ..runtime.banner import render_banner
+        out = getattr(self.con, "out", None)
+        self.say(render_banner(["B200-native GGUF inference"], stream=out))
         self.say(f"TensorSharp B200 interactive chat - model {os.path.basename(self.model_path or '(unknown)')} "
                  f"[{self.model.arch}] on {self.backend}")
         self.say("Type /help for commands, /exit to quit.")

@@ -118,6 +118,9 @@ def main(argv=None) -> int:
     load_startup_model(options, app.svc, read_configured_backend_input(argv), log)
     httpd = serve(app)
     log.info(Ev.HostStarted, "TensorSharp.Server listening on {ListenAddress}", ListenAddress=listen)
+    from ..runtime.banner import print_banner
+    print_banner(["B200-native GGUF inference server", f"model: {app.svc.loaded_model_name or '(none loaded)'}",
+                  f"backend: {app.svc.loaded_backend or '(none)'}"])
     print(f"listening on {listen}")
     try:
         httpd.serve_forever()

@@ -450,3 +450,25 @@ def test_media_helpers(monkeypatch, tmp_path):
     img.save(path)
     t = media.load_image_rgb(str(path))
     assert t.shape == (2, 4, 3) and t.dtype == torch.uint8 and int(t.min()) == 255       # transparent -> white
+
+
+def test_banner_colour_rules_and_layout():
+    import io
+
+    from tensorsharp_b200.runtime.banner import color_allowed, render_banner, wordmark_rows
+
+    class Tty(io.StringIO):
+        def isatty(self):
+            return True
+    assert color_allowed(Tty(), env={}) is True
+    assert color_allowed(Tty(), env={"NO_COLOR": ""}) is False           # presence counts, whatever the value
+    assert color_allowed(Tty(), env={"TERM": "dumb"}) is False
+    assert color_allowed(io.StringIO(), env={}) is False                  # redirected output
+    rows = wordmark_rows()
+    assert len(rows) == 5 and len({len(r) for r in rows}) <= 2
+    plain = render_banner(["model: x.gguf"], color=False)
+    assert "\x1b[" not in plain and "model: x.gguf" in plain
+    colored = render_banner(["model: x.gguf"], color=True)
+    assert "\x1b[38;2;" in colored and colored.count("\x1b[0m") >= 6
+    strip = __import__("re").sub(r"\x1b\[[0-9;]*m", "", colored)
+    assert strip == plain
