@@ -5,7 +5,8 @@ Parity: TensorSharp.Cli/Program.cs:60-150 — the same flags with the same defau
 64 decode / 1 run, chunked-prefill correctness 1500 / 8, KV-cache bench 4 turns) and
 Logging/CliLoggingSetup (``--log-level --log-dir --log-file off --log-console off``).  The
 default backend is ``b200`` (falls back to ``cpu`` without a CUDA device); the reference's
-backend names are accepted as aliases.  ``--tp N`` is this build's tensor-parallel switch.
+backend names are accepted as aliases.  ``--tp N`` is this build's tensor-parallel switch and
+``--batch-size N`` decodes up to N requests of ``--input-jsonl`` together.
 """
 from __future__ import annotations
 
@@ -61,6 +62,7 @@ class CliOptions:
     log_file: bool = True
     log_console: bool = True
     tp: int = 1
+    batch_size: int = 1               # JSONL mode: requests decoded together (continuous batching)
     max_context: Optional[int] = None
     unknown: List[str] = field(default_factory=list)
 
@@ -71,7 +73,8 @@ _STR = {"--model": "model", "--input": "input_file", "--input-jsonl": "input_jso
         "--system": "system", "--log-level": "log_level", "--log-dir": "log_dir"}
 _INT = {"--max-tokens": "max_tokens", "--bench-prefill": "bench_prefill", "--bench-decode": "bench_decode",
         "--bench-runs": "bench_runs", "--correct-prefill": "correct_prefill", "--correct-decode": "correct_decode",
-        "--bench-kv-turns": "bench_kv_turns", "--tp": "tp", "--max-context": "max_context"}
+        "--bench-kv-turns": "bench_kv_turns", "--tp": "tp", "--max-context": "max_context",
+        "--batch-size": "batch_size"}
 _BOOL = {"--test": "run_test", "--think": "think", "--dump-prompt": "dump_prompt", "--benchmark": "benchmark",
          "--bench-chunked": "bench_chunked", "--test-chunked-prefill": "test_chunked_prefill",
          "--bench-kvcache": "bench_kvcache", "--interactive": "interactive", "--chat": "interactive"}

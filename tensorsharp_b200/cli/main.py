@@ -388,14 +388,69 @@ def parse_batch_sampling(root: Dict[str, Any], fallback: SamplingConfig) -> Samp
     return cfg if any_set else fallback
 
 
+def run_jsonl_batch_concurrent(model, lines: List[str], default_max_tokens: int, default_sampling: SamplingConfig,
+                               think: bool, batch_size: int, log) -> List[str]:
+    """``--batch-size N``: the requests of the file share decode steps, up to N at a time (text-only
+    requests; one with attachments falls back to a turn of its own).  Result lines keep the file's order
+    and the sequential mode's fields."""
+    from ..runtime.batching import ContinuousBatcher, GenRequest
+    slots: List[Any] = []                       # per input line: a result string, or a GenRequest
+    for idx, line in enumerate(lines):
+        line = line.strip()
+        if not line:
+            continue
+        try:
+            root = json.loads(line)
+            if not isinstance(root, dict):
+                raise ValueError("request must be a JSON object")
+        except ValueError as e:
+            slots.append(dotnet_json({"line": idx + 1, "error": f"Invalid JSON: {e}"}))
+            continue
+        rid = root.get("id") or f"request_{idx + 1}"
+        try:
+            messages = parse_batch_messages(root)
+            if any(m.image_paths or m.audio_paths for m in messages):
+                raise ValueError("attachments are not supported with --batch-size > 1")
+            cfg = parse_batch_sampling(root, default_sampling)
+            req_think = think or root.get("enable_thinking") is True
+            rendered = PROMPT_RENDERER.render(model.cfg.chat_template, messages, True, model.arch, None, req_think)
+            tokens = model.tokenizer.encode(rendered, add_special=True)
+            slots.append(GenRequest(tokens, int(root.get("max_tokens", default_max_tokens)), cfg, tag=rid))
+        except Exception as e:
+            log.error(Ev.CliFailed, "batch request {Index} id={Id} failed: {Error}", exc=e, Index=idx + 1, Id=rid, Error=str(e))
+            slots.append(dotnet_json({"id": rid, "error": str(e)}))
+    eng = ContinuousBatcher(model, batch_size)
+    model.reset_kv_cache()
+    eng.run([s for s in slots if isinstance(s, GenRequest)])
+    log.info(Ev.CliBatchProgress, "continuous batching: {Steps} decode steps, mean batch {Mean:.2f}", Steps=eng.steps,
+             Mean=eng.step_rows / max(1, eng.steps))
+    out: List[str] = []
+    for s in slots:
+        if not isinstance(s, GenRequest):
+            out.append(s)
+        elif s.error is not None:
+            out.append(dotnet_json({"id": s.tag, "error": s.error}))
+        else:
+            out.append(dotnet_json({"id": s.tag, "output": s.text, "tokens_generated": len(s.ids),
+                                    "prefill_ms": round(s.prefill_ms, 2), "total_ms": round(s.total_ms, 2),
+                                    "tokens_per_second": round(len(s.ids) / (s.total_ms / 1e3), 2) if s.total_ms > 0 else 0.0}))
+    return out
+
+
 def run_jsonl_batch(model, path: str, output_file: Optional[str], default_max_tokens: int, default_sampling: SamplingConfig,
-                    think: bool, con: Console, log) -> int:
+                    think: bool, con: Console, log, batch_size: int = 1) -> int:
     if not os.path.isfile(path):
         log.error(Ev.CliFailed, "Input JSONL not found: {File}", File=path)
         con.error(f"Input JSONL not found: {path}")
         return 1
     with open(path, "r", encoding="utf-8") as f:
         lines = f.read().splitlines()
+    if batch_size > 1:
+        t_all = time.perf_counter()
+        results = run_jsonl_batch_concurrent(model, lines, default_max_tokens, default_sampling, think, batch_size, log)
+        log.info(Ev.CliCompleted, "batch completed: {Completed}/{Total} in {Seconds:.1f}s",
+                 Completed=sum('"error"' not in r for r in results), Total=len(lines), Seconds=time.perf_counter() - t_all)
+        return _emit_jsonl_results(results, output_file, con)
     results: List[str] = []
     done = 0
     t_all = time.perf_counter()
@@ -439,6 +494,10 @@ def run_jsonl_batch(model, path: str, output_file: Optional[str], default_max_to
             results.append(dotnet_json({"id": rid, "error": str(e)}))
     log.info(Ev.CliCompleted, "batch completed: {Completed}/{Total} in {Seconds:.1f}s", Completed=done, Total=len(lines),
              Seconds=time.perf_counter() - t_all)
+    return _emit_jsonl_results(results, output_file, con)
+
+
+def _emit_jsonl_results(results: List[str], output_file: Optional[str], con: Console) -> int:
     if output_file:
         with open(output_file, "w", encoding="utf-8") as f:
             f.write("\n".join(results) + "\n")
@@ -523,6 +582,8 @@ def load_model(o: CliOptions, log):
     kw: Dict[str, Any] = {}
     if o.max_context:
         kw["max_context"] = o.max_context
+    if o.batch_size > 1:
+        kw["max_seqs"] = o.batch_size + 1          # one KV sequence per request in flight, plus the default one
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if o.tp > 1 or world > 1:
         # one process per GPU, started by ``python -m torch.distributed.run --nproc-per-node N -m tensorsharp_b200.cli --tp N``
@@ -618,7 +679,8 @@ def _run(o: CliOptions, con: Console, log) -> int:
         if o.multi_turn_jsonl is not None:
             return run_multi_turn_test(model, o.multi_turn_jsonl, o.max_tokens, o.sampling, o.think, con, log)
         if o.input_jsonl is not None:
-            return run_jsonl_batch(model, o.input_jsonl, o.output_file, o.max_tokens, o.sampling, o.think, con, log)
+            return run_jsonl_batch(model, o.input_jsonl, o.output_file, o.max_tokens, o.sampling, o.think, con, log,
+                                   batch_size=o.batch_size)
         if o.interactive:
             from .interactive import InteractiveSession
             s = InteractiveSession(model, o.model, o.backend, o.mmproj, o.sampling, tools, o.think,

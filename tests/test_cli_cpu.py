@@ -5,6 +5,7 @@ import json
 import os
 
 import pytest
+import torch
 
 from tensorsharp_b200.cli.args import parse_cli_args
 from tensorsharp_b200.cli.interactive import InteractiveSession
@@ -163,3 +164,49 @@ def test_tp_flag_needs_matching_process_count(tiny_qwen3_path, monkeypatch):
     monkeypatch.delenv("WORLD_SIZE", raising=False)
     rc, out, err = run_cli(["--model", tiny_qwen3_path, "--backend", "cpu", "--tp", "2", "--benchmark"])
     assert rc == 1 and "torch.distributed.run" in err
+
+
+def test_jsonl_batch_size_gives_the_sequential_outputs(tiny_qwen3_path, tmp_path):
+    """--batch-size N decodes the requests together; every request's text and token count equal the
+    one-at-a-time run (greedy), bad lines stay where they were, and the file's order is kept."""
+    prompts = ["Hello", "Tell me about the sea", "One two three four five six", "x", "What is 2+2?", "Goodbye now"]
+    lines = [json.dumps({"id": f"r{i}", "prompt": p, "max_tokens": 3 + 2 * (i % 3)}) for i, p in enumerate(prompts)]
+    lines.insert(2, "{broken")
+    lines.append(json.dumps({"id": "stop", "prompt": "Hello", "max_tokens": 6, "stop": ["<|tok"]}))
+    req = tmp_path / "req.jsonl"
+    req.write_text("\n".join(lines))
+    outs = {}
+    for bs in (1, 3):
+        res = tmp_path / f"res{bs}.jsonl"
+        rc, _, err = run_cli(["--model", tiny_qwen3_path, "--backend", "cpu", "--input-jsonl", str(req), "--output", str(res),
+                              "--max-tokens", "4", "--batch-size", str(bs)])
+        assert rc == 0, err
+        outs[bs] = [json.loads(l) for l in res.read_text().splitlines()]
+    assert len(outs[1]) == len(outs[3]) == len(lines)
+    for a, b in zip(outs[1], outs[3]):
+        assert list(a) == list(b)
+        for k in ("id", "line", "output", "tokens_generated"):
+            assert a.get(k) == b.get(k), (a, b)
+    assert outs[3][2]["error"].startswith("Invalid JSON")
+
+
+def test_continuous_batcher_refills_the_batch(tiny_qwen3_path):
+    from tensorsharp_b200.models.base import ModelBase
+    from tensorsharp_b200.runtime.batching import ContinuousBatcher, GenRequest
+    from tensorsharp_b200.runtime.engine import generate
+    m = ModelBase.create(tiny_qwen3_path, "cpu", max_context=128, max_seqs=4)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(5, 4000, (n,), generator=g).tolist() for n in (7, 19, 3, 11, 26)]
+    lens = [5, 2, 9, 1, 6]
+    pieces = []
+    reqs = [GenRequest(p, n, on_piece=(pieces.append if i == 0 else None), tag=i) for i, (p, n) in enumerate(zip(prompts, lens))]
+    eng = ContinuousBatcher(m, max_batch=3, prefill_chunk=8)
+    free0 = m.kv.free_pages
+    eng.run(reqs)
+    assert m.kv.free_pages == free0                         # every sequence gave its pages back
+    assert eng.steps < sum(lens) and eng.step_rows / eng.steps > 1.5
+    eos = [t for t in range(m.cfg.vocab) if m.tokenizer.is_eos(t)]
+    for r, p, n in zip(reqs, prompts, lens):
+        m.reset_kv_cache()
+        assert r.error is None and r.ids == generate(m, p, n, eos_ids=eos)
+    assert "".join(pieces) == reqs[0].text
