@@ -177,9 +177,14 @@ class ServerApp:
                  log_provider: Optional[FileLoggerProvider] = None, queue_poll_s: float = 1.0):
         self.options = options
         self._provider = log_provider
+        n_batch = max(1, int(getattr(options, "max_batch", 1) or 1))
+        self.queue = queue or InferenceQueue(self.logger("TensorSharp.Server.InferenceQueue"), capacity=n_batch)
+        if svc is None and n_batch > 1:
+            # concurrent requests: one service per running slot over one loaded model, model calls merged per step
+            from .service_pool import ServicePool
+            svc = ServicePool(self.logger("TensorSharp.Server.ModelService"), self.queue, n_batch, max_context=options.max_context)
         self.svc = svc or ModelService(self.logger("TensorSharp.Server.ModelService"), max_context=options.max_context,
                                        max_sessions=options.max_sessions)
-        self.queue = queue or InferenceQueue(self.logger("TensorSharp.Server.InferenceQueue"))
         self.sessions = sessions or SessionManager(self.logger("TensorSharp.Server.SessionManager"))
         self.queue_poll_s = queue_poll_s
         self._http_log = self.logger("TensorSharp.Server.Logging.RequestLoggingMiddleware")

@@ -1,4 +1,5 @@
-"""FIFO admission queue: one inference runs at a time, later requests wait with a visible position.
+"""FIFO admission queue: one inference runs at a time (or ``capacity`` of them when the server batches
+concurrent requests), later requests wait with a visible position.
 
 Parity: TensorSharp.Server/InferenceQueue.cs (Enqueue :43, Release :76, RemoveCancelled :99,
 ActivateNext :118, GetStatus :159, QueueTicket :189-262).  Tickets are context managers; a
@@ -65,6 +66,8 @@ class QueueTicket:
         self._ready = threading.Event()
         self._wake = threading.Event()          # set on ready or cancel: ends wait() early
         self.position = 0
+        self.slot = -1                          # which of the queue's running slots this ticket holds once ready
+        self.thread_id = threading.get_ident()  # the request thread that asked for it
         self._disposed = False
         self._queued = False
         ct.register(self._on_cancel)
@@ -112,9 +115,12 @@ class QueueTicket:
 
 
 class InferenceQueue:
-    def __init__(self, logger=None):
+    def __init__(self, logger=None, capacity: int = 1):
         self._lock = threading.RLock()
         self._waiters: Deque[QueueTicket] = collections.deque()
+        self._capacity = max(1, int(capacity))
+        self._free_slots = list(range(self._capacity - 1, -1, -1))
+        self._running = {}                      # ticket -> slot
         self._busy = False
         self._total = 0
         self._current: Optional[str] = None
@@ -137,10 +143,10 @@ class InferenceQueue:
     def enqueue(self, ct: Optional[CancellationToken] = None, request_id: Optional[str] = None) -> QueueTicket:
         with self._lock:
             t = QueueTicket(self, ct or NEVER, request_id)
-            if not self._busy:
+            if len(self._running) < self._capacity:
                 self._busy, self._current = True, request_id
                 t.position = 0
-                t._mark_ready()
+                self._start(t)
                 self._log.debug(Ev.QueueReady, "Inference slot acquired immediately for request {RequestId}",
                                 RequestId=request_id or "(none)")
                 return t
@@ -155,6 +161,9 @@ class InferenceQueue:
     def _release(self, done: QueueTicket) -> None:
         with self._lock:
             self._total += 1
+            slot = self._running.pop(done, None)
+            if slot is not None:
+                self._free_slots.append(slot)
             if done._queued:
                 self._discard(done)
             self._log.debug(Ev.QueueReleased, "Inference slot released for request {RequestId} (totalProcessed="
@@ -177,20 +186,34 @@ class InferenceQueue:
                 self._log.info(Ev.QueueCancelled, "Cancelled queued request {RequestId} (pending={PendingCount})",
                                RequestId=t.request_id or "(none)", PendingCount=len(self._waiters))
 
+    def _start(self, t: QueueTicket) -> None:
+        t.slot = self._free_slots.pop()
+        self._running[t] = t.slot
+        t._mark_ready()
+
+    def slot_for_thread(self, thread_id: Optional[int] = None) -> int:
+        """The running slot held by a ticket that ``thread_id`` (default: the caller) enqueued, or -1."""
+        tid = threading.get_ident() if thread_id is None else thread_id
+        with self._lock:
+            for t, slot in self._running.items():
+                if t.thread_id == tid:
+                    return slot
+        return -1
+
     def _activate_next(self) -> None:
-        while self._waiters:
+        while self._waiters and len(self._running) < self._capacity:
             nxt = self._waiters.popleft()
             nxt._queued = False
             if nxt.is_cancelled:
                 continue
             self._current = nxt.request_id
             nxt.position = 0
-            nxt._mark_ready()
+            self._start(nxt)
             self._update_positions()
             self._log.info(Ev.QueueReady, "Activated queued request {RequestId} (pending={PendingCount})",
                            RequestId=nxt.request_id or "(none)", PendingCount=len(self._waiters))
-            return
-        self._busy, self._current = False, None
+        if not self._running:
+            self._busy, self._current = False, None
 
     def _update_positions(self) -> None:
         for i, t in enumerate(self._waiters):

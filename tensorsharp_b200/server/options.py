@@ -11,7 +11,8 @@ Hosting/HostedModelGuard.cs.
 Backends here are ``b200`` (the sm_100a kernels) and ``cpu`` (the fp32 oracle path); the
 reference's names ``cuda`` / ``ggml_cuda`` are accepted as aliases of ``b200`` and
 ``ggml_cpu`` of ``cpu`` so existing launch scripts keep working.  This build adds
-``--host --port --max-context --max-sessions --tp``.
+``--host --port --max-context --max-sessions --max-batch`` (tensor parallelism comes from the
+process count of the launch).
 """
 from __future__ import annotations
 
@@ -78,6 +79,7 @@ class ServerHostingOptions:
     port: int = 5000
     max_context: Optional[int] = None
     max_sessions: int = 1
+    max_batch: int = 1                 # requests that run together (their model calls share steps)
     web_root: Optional[str] = None
 
     @property
@@ -133,7 +135,8 @@ _SAMPLING_FLAGS = (
 def parse_args(args: Sequence[str]) -> Dict[str, object]:
     out: Dict[str, object] = {"sampling": {}, "stop": None}
     plain = (("--model", "model"), ("--mmproj", "mmproj"), ("--backend", "backend"), ("--host", "host"))
-    ints = (("--port", "port"), ("--max-context", "max_context"), ("--max-sessions", "max_sessions"))
+    ints = (("--port", "port"), ("--max-context", "max_context"), ("--max-sessions", "max_sessions"),
+            ("--max-batch", "max_batch"))
     i = 0
     while i < len(args):
         matched = False
@@ -231,7 +234,8 @@ def build_options(args: Sequence[str], base_directory: str, env=None,
         default_sampling_config=resolve_default_sampling(p["sampling"], p["stop"], env),
         host=p.get("host") or env.get("TENSORSHARP_HOST") or "127.0.0.1",
         port=int(p.get("port") or _pos_int(env.get("PORT")) or 5000),
-        max_context=p.get("max_context"), max_sessions=int(p.get("max_sessions") or 1))
+        max_context=p.get("max_context"), max_sessions=int(p.get("max_sessions") or 1),
+        max_batch=int(p.get("max_batch") or _pos_int(env.get("TENSORSHARP_MAX_BATCH")) or 1))
 
 
 def read_configured_backend_input(args: Sequence[str], env=None) -> Optional[str]:

@@ -110,3 +110,53 @@ def test_load_of_corrupt_model_keeps_server_usable(live, tmp_path):
     assert st >= 400 or "error" in data.lower()
     st, data = _post(port, "/api/generate", {"model": name, "prompt": "Hi", "stream": False, "options": {"num_predict": 2}})
     assert st == 200 and json.loads(data)["done"]
+
+
+def test_concurrent_requests_share_steps_and_match_sequential(tmp_path, tiny_qwen3_path):
+    """--max-batch 3: three clients at once are served together (the stepper's mean batch exceeds one), every
+    answer equals what the one-at-a-time server gives, a fourth request waits in the queue, and a follow-up
+    turn of a web-UI session still finds its KV cache."""
+    name = os.path.basename(tiny_qwen3_path)
+    args = ["--model", tiny_qwen3_path, "--backend", "cpu", "--port", "0", "--temperature", "0", "--top-k", "0", "--top-p", "1",
+            "--repeat-penalty", "1"]
+    prompts = ["Hello", "Tell me about the sea", "One two three", "What is this?", "Again and again"]
+
+    def run_all(extra, concurrent):
+        opts = build_options(args + extra, str(tmp_path), env={"TENSORSHARP_LOG_FILE": "0"})
+        app = ServerApp(opts)
+        httpd = serve(app, "127.0.0.1", 0)
+        port = httpd.server_address[1]
+        threading.Thread(target=httpd.serve_forever, daemon=True).start()
+        out = {}
+        try:
+            st, _ = _post(port, "/api/generate", {"model": name, "prompt": "warm", "stream": False, "options": {"num_predict": 1}})
+            assert st == 200
+
+            def one(i):
+                st, data = _post(port, "/api/generate", {"model": name, "prompt": prompts[i], "stream": False,
+                                                         "options": {"num_predict": 6 + i}})
+                out[i] = (st, json.loads(data)["response"])
+            if concurrent:
+                ths = [threading.Thread(target=one, args=(i,)) for i in range(len(prompts))]
+                for t in ths:
+                    t.start()
+                for t in ths:
+                    t.join(timeout=120)
+            else:
+                for i in range(len(prompts)):
+                    one(i)
+            gather = getattr(app.svc, "gather", None)
+            mean = gather.step_rows / max(1, gather.steps) if gather is not None else 1.0
+            q = _wait_idle(port)
+            return out, mean, q
+        finally:
+            httpd.shutdown()
+            httpd.server_close()
+            app.svc.close()
+
+    seq, _, _ = run_all([], False)
+    par, mean, q = run_all(["--max-batch", "3"], True)
+    assert all(st == 200 for st, _ in par.values())
+    assert {i: r for i, (_, r) in par.items()} == {i: r for i, (_, r) in seq.items()}
+    assert mean > 1.2, mean
+    assert q["total_processed"] == len(prompts) + 1
