@@ -268,6 +268,7 @@ class ModelBase:
         return s
 
     def free_sequence(self, seq: SeqState) -> None:
+        self.__dict__.get("_steppers", {}).pop(seq.seq_id, None)
         if self._default_seq is seq:
             self._default_seq = None
         self.kv.free_seq(seq)
@@ -284,10 +285,36 @@ class ModelBase:
     def forward(self, tokens: Sequence[int], want_logits: bool = True) -> Optional[torch.Tensor]:
         """Append ``tokens`` to the default sequence and return the next-token logits
         (float32 ``[vocab]`` on the compute device).  IModelArchitecture.Forward."""
+        if len(tokens) == 1 and self._graph_forward_ok():
+            with self.timer.phase("decode"):
+                out = self._graph_stepper().step(tokens[0])
+            if out is not None:
+                return out if want_logits else None
         batch = self.kv.build_batch([self._seq()], [list(tokens)])
         with self.timer.phase("decode" if len(tokens) == 1 else "prefill"):
             out = self.forward_batch(batch, want_logits)
         return out[0] if out is not None else None
+
+    def _graph_forward_ok(self) -> bool:
+        """Single-token ``forward`` replays a captured graph on one GPU (TSB_GRAPH_FORWARD=0 keeps it eager):
+        not with tensor / pipeline parallel shards (their hosts drive the steps themselves), not for models
+        with recurrent state, and not while multimodal embeddings wait to be injected."""
+        if self.device.type != "cuda" or self.tp_size > 1 or self.pp_size > 1 or self._pending_embeddings:
+            return False
+        if not self.supports_kv_truncation:             # recurrent state: the capture's warm-up step would advance it
+            return False
+        return os.environ.get("TSB_GRAPH_FORWARD", "1") != "0"
+
+    def _graph_stepper(self):
+        from ..runtime.engine import GraphStepper
+        seq = self._seq()
+        steppers = self.__dict__.setdefault("_steppers", {})
+        st = steppers.get(seq.seq_id)
+        if st is None or st.seq is not seq:
+            if len(steppers) > 8:                       # sequences come and go (sessions): keep the table small
+                steppers.clear()
+            st = steppers[seq.seq_id] = GraphStepper(self, seq)
+        return st
 
     @property
     def timer(self):

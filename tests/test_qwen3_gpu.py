@@ -70,3 +70,36 @@ def test_sampled_decode_inside_the_graph(tiny_qwen3_path):
     assert na.tolist() == [24, 24]
     for r in range(2):
         assert torch.equal(torch.bincount(a[:, r].long(), minlength=ca.shape[1])[:ca.shape[1]].int(), ca[r])
+
+
+def test_single_token_forward_replays_a_graph(tiny_qwen3_path, monkeypatch):
+    """``forward([t])`` goes through a captured graph: same logits as the eager step, across a truncation,
+    a further prefill and the growth of the context past the captured bucket."""
+    from tensorsharp_b200.runtime import engine
+    monkeypatch.setattr(engine.GraphStepper, "MIN_BUCKET", 64)
+    g = torch.Generator().manual_seed(8)
+    prompt = torch.randint(0, 4096, (40,), generator=g).tolist()
+
+    def run(graph: bool):
+        monkeypatch.setenv("TSB_GRAPH_FORWARD", "1" if graph else "0")
+        m = ModelBase.create(tiny_qwen3_path, "cuda", max_context=512)
+        out = [m.forward(prompt).clone()]
+        t = int(out[-1].argmax())
+        for _ in range(40):                                   # 40 + 40 tokens: crosses the 64-position bucket
+            out.append(m.forward([t]).clone())
+            t = int(out[-1].argmax())
+        m.truncate_kv_cache(30)                               # an edited turn: shorter cache, then new tokens
+        out.append(m.forward(prompt[30:36]).clone())
+        t = int(out[-1].argmax())
+        for _ in range(5):
+            out.append(m.forward([t]).clone())
+            t = int(out[-1].argmax())
+        m.reset_kv_cache()
+        out.append(m.forward([7]).clone())                    # a single-token prompt on an empty cache
+        return torch.stack(out).cpu(), ("_steppers" in m.__dict__)
+
+    eager, used0 = run(False)
+    graph, used1 = run(True)
+    assert used1 and not used0
+    err = (eager - graph).norm(dim=1) / eager.norm(dim=1)
+    assert float(err.max()) < 2e-2, err
