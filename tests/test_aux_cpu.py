@@ -215,3 +215,46 @@ def test_model_timing_table(tiny_qwen3_path, monkeypatch, capsys):
     assert s["prefill"]["calls"] == 1 and s["decode"]["calls"] == 2
     m.print_timing_stats()
     assert "decode" in capsys.readouterr().err
+
+
+def test_gathered_model_merges_threads_and_propagates_errors(tiny_qwen3_path):
+    import threading
+
+    from tensorsharp_b200.models.base import ModelBase
+    from tensorsharp_b200.runtime.engine import generate
+    from tensorsharp_b200.runtime.gather import GatheredModel
+    real = ModelBase.create(tiny_qwen3_path, "cpu", max_context=128, max_seqs=5)
+    g = GatheredModel(real, 4, window_s=0.05)
+    gen = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(5, 4000, (n,), generator=gen).tolist() for n in (9, 17, 4, 12)]
+    eos = [t for t in range(real.cfg.vocab) if real.tokenizer.is_eos(t)]
+    got = {}
+
+    def worker(i):
+        with g.slot(i) as m:                                  # the bracket tells the stepper how many callers to expect
+            got[i] = generate(m, prompts[i], 6, eos_ids=eos, prefill_chunk=8)
+    ths = [threading.Thread(target=worker, args=(i,)) for i in range(4)]
+    for t in ths:
+        t.start()
+    for t in ths:
+        t.join(timeout=120)
+    assert g.step_rows / g.steps > 1.5                        # steps were shared
+    for i, p in enumerate(prompts):
+        real.reset_kv_cache()
+        assert got[i] == generate(real, p, 6, eos_ids=eos)
+    # slot state is per slot: truncation and reset act on that slot's sequence only
+    s0, s1 = g.slot(0), g.slot(1)
+    l0, l1 = s0.cache_length, s1.cache_length
+    s0.truncate_kv_cache(3)
+    assert s0.cache_length == 3 and s1.cache_length == l1 and l0 > 3
+    s1.reset_kv_cache()
+    assert s1.cache_length == 0
+    # a failing step reaches the caller as an exception, and the stepper keeps running
+    with pytest.raises(Exception):
+        s0.forward([10 ** 9])                                 # token id outside the vocabulary
+    assert s1.forward([5]) is not None
+    free_before = real.kv.free_pages
+    g.close()
+    assert real.kv.free_pages > free_before                   # slots gave their sequences back
+    with pytest.raises(RuntimeError):
+        s1.forward([5])

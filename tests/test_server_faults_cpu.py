@@ -160,3 +160,33 @@ def test_concurrent_requests_share_steps_and_match_sequential(tmp_path, tiny_qwe
     assert {i: r for i, (_, r) in par.items()} == {i: r for i, (_, r) in seq.items()}
     assert mean > 1.2, mean
     assert q["total_processed"] == len(prompts) + 1
+
+
+def test_pool_reload_and_web_session_turns(tmp_path, tiny_qwen3_path):
+    """With --max-batch the hosted model can be reloaded through /api/models/load (every slot moves to the
+    new model, the old one gives its memory back) and a web-UI session's second turn is answered."""
+    name = os.path.basename(tiny_qwen3_path)
+    opts = build_options(["--model", tiny_qwen3_path, "--backend", "cpu", "--port", "0", "--max-batch", "2", "--temperature", "0",
+                          "--top-k", "0", "--top-p", "1", "--repeat-penalty", "1"], str(tmp_path), env={"TENSORSHARP_LOG_FILE": "0"})
+    app = ServerApp(opts)
+    httpd = serve(app, "127.0.0.1", 0)
+    port = httpd.server_address[1]
+    threading.Thread(target=httpd.serve_forever, daemon=True).start()
+    try:
+        st, data = _post(port, "/api/models/load", {"model": name})
+        assert st == 200 and json.loads(data)["ok"] is True
+        first = app.svc.gather
+        st, data = _post(port, "/api/models/load", {"model": name})
+        assert st == 200 and app.svc.gather is not first and first._stop
+        st, data = _post(port, "/api/chat", {"messages": [{"role": "user", "content": "Hello"}], "maxTokens": 4})
+        ev = [json.loads(l[6:]) for l in data.split("\n\n") if l.startswith("data: ")]
+        assert st == 200 and ev[-1]["done"] and ev[-1]["error"] is None
+        reply = "".join(e.get("token", "") for e in ev)
+        st, data = _post(port, "/api/chat", {"messages": [{"role": "user", "content": "Hello"}, {"role": "assistant", "content": reply},
+                                                          {"role": "user", "content": "again"}], "maxTokens": 3})
+        ev2 = [json.loads(l[6:]) for l in data.split("\n\n") if l.startswith("data: ")]
+        assert st == 200 and ev2[-1]["done"] and ev2[-1]["error"] is None and ev2[-1]["promptTokens"] > ev[-1]["promptTokens"]
+    finally:
+        httpd.shutdown()
+        httpd.server_close()
+        app.svc.close()
