@@ -732,7 +732,8 @@ class ServerApp:
         tools = P.parse_tools_ollama(body) if isinstance(body.get("tools"), list) else None
         messages = P.parse_messages_webui(body["messages"])
         ex.begin_stream("text/event-stream", SSE_HEADERS)
-        with self.queue.enqueue(ex.cancel, ex.request_id) as ticket:
+        prefer = getattr(self.svc, "preferred_slot", None)
+        with self.queue.enqueue(ex.cancel, ex.request_id, prefer_slot=prefer(session) if prefer else -1) as ticket:
             self._wait_with_progress(ex, ticket, lambda p, n: sse_event(WebUi.queue_progress(p, n)))
             t0 = time.perf_counter()
             count = 0

@@ -140,9 +140,13 @@ class InferenceQueue:
         with self._lock:
             return self._busy
 
-    def enqueue(self, ct: Optional[CancellationToken] = None, request_id: Optional[str] = None) -> QueueTicket:
+    def enqueue(self, ct: Optional[CancellationToken] = None, request_id: Optional[str] = None,
+                prefer_slot: int = -1) -> QueueTicket:
+        """``prefer_slot``: the running slot to take if it is free when this request starts (a chat session
+        returning to the slot that still holds its KV cache); any free slot otherwise."""
         with self._lock:
             t = QueueTicket(self, ct or NEVER, request_id)
+            t.prefer_slot = prefer_slot
             if len(self._running) < self._capacity:
                 self._busy, self._current = True, request_id
                 t.position = 0
@@ -187,7 +191,12 @@ class InferenceQueue:
                                RequestId=t.request_id or "(none)", PendingCount=len(self._waiters))
 
     def _start(self, t: QueueTicket) -> None:
-        t.slot = self._free_slots.pop()
+        want = getattr(t, "prefer_slot", -1)
+        if want in self._free_slots:
+            self._free_slots.remove(want)
+            t.slot = want
+        else:
+            t.slot = self._free_slots.pop()
         self._running[t] = t.slot
         t._mark_ready()
 

@@ -25,6 +25,7 @@ class ServicePool:
         self._queue, self._n = queue, max(1, int(n_slots))
         self._max_context, self._factory = max_context, model_factory
         self._gather: Optional[GatheredModel] = None
+        self._session_slot = {}
         self._slots: List[ModelService] = [
             ModelService(logger, model_factory=self._slot_factory(i), max_context=max_context, max_sessions=1) for i in range(self._n)]
 
@@ -90,9 +91,16 @@ class ServicePool:
         # anything else (available_models, is_mmproj helpers ...) is the same on every slot
         return getattr(self._slots[0], name)
 
-    def _mine(self) -> ModelService:
+    def _mine(self, session=None) -> ModelService:
         slot = self._queue.slot_for_thread()
-        return self._slots[slot if 0 <= slot < self._n else 0]
+        slot = slot if 0 <= slot < self._n else 0
+        if session is not None:
+            self._session_slot[getattr(session, "id", None)] = slot
+        return self._slots[slot]
+
+    def preferred_slot(self, session) -> int:
+        """The slot that served this chat session last (it still holds the session's KV cache), or -1."""
+        return self._session_slot.get(getattr(session, "id", None), -1)
 
     def _bracket(self, svc: ModelService, it: Iterator) -> Iterator:
         slot_model = svc.model
@@ -106,7 +114,7 @@ class ServicePool:
                 slot_model.__exit__(None, None, None)
 
     def chat_stream_with_metrics(self, *a, **k) -> Iterator:
-        svc = self._mine()
+        svc = self._mine(k.get("session"))
         return self._bracket(svc, svc.chat_stream_with_metrics(*a, **k))
 
     def chat_stream(self, *a, **k) -> Iterator:
@@ -122,5 +130,6 @@ class ServicePool:
             s.reset_session(session)
 
     def dispose_session(self, session) -> None:
+        self._session_slot.pop(getattr(session, "id", None), None)
         for s in self._slots:
             s.dispose_session(session)

@@ -790,3 +790,21 @@ def test_http_loopback_with_tiny_qwen3(tmp_path, tiny_qwen3_path):
         httpd.shutdown()
         httpd.server_close()
         app.svc.close()
+
+
+def test_queue_capacity_and_preferred_slots():
+    """With capacity N the queue runs N tickets at once, hands a ticket its preferred running slot when that
+    slot is free, and makes the next one wait with position 1 until a slot is released."""
+    q = InferenceQueue(capacity=3)
+    a, b, c = q.enqueue(prefer_slot=2), q.enqueue(prefer_slot=2), q.enqueue()
+    assert (a.is_ready, b.is_ready, c.is_ready) == (True, True, True)
+    assert a.slot == 2 and sorted([b.slot, c.slot]) == [0, 1]
+    d = q.enqueue(prefer_slot=2)
+    assert not d.is_ready and d.position == 1 and q.pending_count == 1
+    assert q.slot_for_thread() in (0, 1, 2)
+    a.dispose()
+    assert d.is_ready and d.slot == 2 and q.pending_count == 0
+    for t in (b, c, d):
+        t.dispose()
+    st = q.get_status()
+    assert st.busy is False and st.total_processed == 4

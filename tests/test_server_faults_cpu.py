@@ -186,6 +186,8 @@ def test_pool_reload_and_web_session_turns(tmp_path, tiny_qwen3_path):
                                                           {"role": "user", "content": "again"}], "maxTokens": 3})
         ev2 = [json.loads(l[6:]) for l in data.split("\n\n") if l.startswith("data: ")]
         assert st == 200 and ev2[-1]["done"] and ev2[-1]["error"] is None and ev2[-1]["promptTokens"] > ev[-1]["promptTokens"]
+        # the session went back to the slot that holds its cache: the second turn re-used the first turn's tokens
+        assert ev2[-1]["kvReusedTokens"] >= ev[-1]["promptTokens"]
     finally:
         httpd.shutdown()
         httpd.server_close()
