@@ -62,6 +62,7 @@ class CliOptions:
     log_file: bool = True
     log_console: bool = True
     tp: int = 1
+    pp: int = 1                       # pipeline stages (one process per stage)
     batch_size: int = 1               # JSONL mode: requests decoded together (continuous batching)
     max_context: Optional[int] = None
     unknown: List[str] = field(default_factory=list)
@@ -74,7 +75,7 @@ _STR = {"--model": "model", "--input": "input_file", "--input-jsonl": "input_jso
 _INT = {"--max-tokens": "max_tokens", "--bench-prefill": "bench_prefill", "--bench-decode": "bench_decode",
         "--bench-runs": "bench_runs", "--correct-prefill": "correct_prefill", "--correct-decode": "correct_decode",
         "--bench-kv-turns": "bench_kv_turns", "--tp": "tp", "--max-context": "max_context",
-        "--batch-size": "batch_size"}
+        "--batch-size": "batch_size", "--pp": "pp"}
 _BOOL = {"--test": "run_test", "--think": "think", "--dump-prompt": "dump_prompt", "--benchmark": "benchmark",
          "--bench-chunked": "bench_chunked", "--test-chunked-prefill": "test_chunked_prefill",
          "--bench-kvcache": "bench_kvcache", "--interactive": "interactive", "--chat": "interactive"}

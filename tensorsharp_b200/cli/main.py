@@ -585,6 +585,20 @@ def load_model(o: CliOptions, log):
     if o.batch_size > 1:
         kw["max_seqs"] = o.batch_size + 1          # one KV sequence per request in flight, plus the default one
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if o.pp > 1:
+        # layer ranges on successive processes: python -m torch.distributed.run --nproc-per-node N -m tensorsharp_b200.cli --pp N
+        if world != o.pp or o.tp > 1:
+            raise ValueError(f"--pp {o.pp} needs {o.pp} processes and no --tp (WORLD_SIZE is {world}); start the CLI with "
+                             f"python -m torch.distributed.run --nproc-per-node {o.pp} --master-addr 127.0.0.1 "
+                             f"-m tensorsharp_b200.cli --pp {o.pp} ...")
+        from ..parallel.dist import init_from_env
+        from ..parallel.pipeline import PipelinedModel
+        comm = init_from_env("gloo" if device == "cpu" else None)
+        device = str(comm.device) if device != "cpu" else "cpu"
+        stage = ModelBase.create(o.model, device, pp_rank=comm.rank, pp_size=comm.size, pp_comm=comm, **kw)
+        model = PipelinedModel(stage)
+        model.warm_up_kernels()
+        return model
     if o.tp > 1 or world > 1:
         # one process per GPU, started by ``python -m torch.distributed.run --nproc-per-node N -m tensorsharp_b200.cli --tp N``
         if world != max(o.tp, 1):
@@ -662,7 +676,7 @@ def _run(o: CliOptions, con: Console, log) -> int:
         con.error(USAGE)
         return 1
     model = load_model(o, log)
-    if getattr(model, "tp_rank", 0) != 0:
+    if getattr(model, "tp_rank", 0) != 0 or getattr(model, "pp_rank", 0) != 0:
         con = Console(open(os.devnull, "w"), con.err)          # every rank runs the same steps; rank 0 does the talking
     try:
         attach_projector(model, o, log)

@@ -56,3 +56,47 @@ def generate(model, prompt: Sequence[int], max_tokens: int, pick: Optional[Calla
         out.append(t)
         logits = model.forward([t])
     return out
+
+
+class PipelinedModel:
+    """A pipeline stage with the plain single-process model surface: ``forward`` returns the logits on
+    every rank (the last stage computes them and broadcasts the row), so a host that samples on the CPU
+    with a shared seed (the CLI's loops, the server's token loop on rank 0 with followers mirroring it)
+    runs unchanged on top of a pipeline.  Costs one broadcast of ``vocab`` floats per step."""
+
+    def __init__(self, stage):
+        self.__dict__["_stage"] = stage
+
+    def __getattr__(self, name):
+        return getattr(self.__dict__["_stage"], name)
+
+    def __setattr__(self, name, value):
+        setattr(self.__dict__["_stage"], name, value)
+
+    def forward(self, tokens: Sequence[int], want_logits: bool = True):
+        import torch.distributed as dist
+        st = self._stage
+        out = st.forward(tokens, want_logits)
+        if not want_logits:
+            return None
+        comm = st.pp_comm
+        if out is None:
+            out = torch.empty(st.cfg.vocab, dtype=torch.float32, device=st.device)
+        else:
+            out = out[:st.cfg.vocab].float().contiguous()
+        dist.broadcast(out, _global_rank(comm, comm.size - 1), group=comm.group)
+        return out
+
+    def forward_refill(self, tokens: Sequence[int], chunk: int = 2048):
+        tokens = list(tokens)
+        out = None
+        for i in range(0, len(tokens), chunk):
+            out = self.forward(tokens[i:i + chunk], want_logits=i + chunk >= len(tokens))
+        return out
+
+    def warm_up_kernels(self) -> None:
+        n = max(1, min(8, self.max_context - 2))
+        tok = min(self.cfg.vocab - 1, 100)
+        self.forward([tok] * n)
+        self.forward([tok])
+        self.reset_kv_cache()

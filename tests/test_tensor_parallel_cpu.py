@@ -158,3 +158,33 @@ def test_front_end_on_rank0_with_follower_shards(tiny_qwen3_path, tmp_path):
     mp.spawn(_serve_worker, args=(2, _free_port(), tiny_qwen3_path, out), nprocs=2, join=True)
     assert torch.load(f"{out}.0") == (first, second)
     assert torch.load(f"{out}.1") > 10          # the follower executed the leader's commands
+
+
+def _cli_pp_worker(rank, world, port, path, prompt_file, out_path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+    import io
+
+    from tensorsharp_b200.cli.main import Console, main
+    out, err = io.StringIO(), io.StringIO()
+    rc = main(["--model", path, "--backend", "cpu", "--pp", str(world), "--input", prompt_file, "--max-tokens", "5",
+               "--log-file", "off"], Console(out, err))
+    torch.save((rc, out.getvalue(), err.getvalue()), f"{out_path}.{rank}")
+
+
+def test_cli_over_pipeline_stages(tiny_qwen3_path, tmp_path):
+    """``--pp 2``: the CLI's own token loop runs on every stage (the last stage broadcasts the logits), rank 0
+    prints what the single-process CLI prints, the other rank stays silent."""
+    import io
+
+    from tensorsharp_b200.cli.main import Console, main
+    prompt = tmp_path / "p.txt"
+    prompt.write_text("Hello there")
+    out = io.StringIO()
+    assert main(["--model", tiny_qwen3_path, "--backend", "cpu", "--input", str(prompt), "--max-tokens", "5", "--log-file", "off"],
+                Console(out, io.StringIO())) == 0
+    res = str(tmp_path / "cli_pp")
+    mp.spawn(_cli_pp_worker, args=(2, _free_port(), tiny_qwen3_path, str(prompt), res), nprocs=2, join=True)
+    rc0, out0, err0 = torch.load(f"{res}.0")
+    rc1, out1, _ = torch.load(f"{res}.1")
+    assert rc0 == 0 and rc1 == 0, err0
+    assert out0 == out.getvalue() and out1 == ""
