@@ -23,7 +23,9 @@ USAGE = ("Usage: python -m tensorsharp_b200.cli --model <path.gguf> [--input <in
          "[--frequency-penalty F] [--seed N] [--stop <text>] [--think] [--tools <tools.json>] [--dump-prompt] "
          "[--benchmark [--bench-prefill N] [--bench-decode N] [--bench-runs N] [--bench-chunked]] "
          "[--test-chunked-prefill [--correct-prefill N] [--correct-decode N]] [--bench-kvcache [--bench-kv-turns N]] "
-         "[--test-templates <dir>] [--log-level info|debug|trace] [--log-dir <path>] [--log-file off] [--log-console off]")
+         "[--test-templates <dir>] [--log-level info|debug|trace] [--log-dir <path>] [--log-file off] [--log-console off] "
+         "[--batch-size N] [--max-context N] [--tp N | --pp N  (one process per GPU: python -m torch.distributed.run "
+         "--nproc-per-node N -m tensorsharp_b200.cli ...)]")
 
 
 @dataclass
