@@ -210,3 +210,28 @@ def test_continuous_batcher_refills_the_batch(tiny_qwen3_path):
         m.reset_kv_cache()
         assert r.error is None and r.ids == generate(m, p, n, eos_ids=eos)
     assert "".join(pieces) == reqs[0].text
+
+
+TESTDATA = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "tensorsharp_b200", "cli", "testdata")
+
+
+def test_shipped_fixtures_run_through_the_cli(tiny_qwen3_path, tmp_path):
+    """The fixtures that ship with the CLI (tool definitions in both accepted shapes, a JSONL batch, a
+    multi-turn script, prompt files) load and run."""
+    units = load_tools(os.path.join(TESTDATA, "tools_units.json"))
+    cal = load_tools(os.path.join(TESTDATA, "tools_calendar.json"))
+    assert [t.name for t in units] == ["convert_length", "list_units"] and units[0].required == ["value", "from_unit", "to_unit"]
+    assert units[0].parameters["from_unit"].enum == ["m", "km", "ft", "mi"]
+    assert cal[0].name == "days_between" and set(cal[0].parameters) == {"start", "end"}
+    res = tmp_path / "res.jsonl"
+    rc, _, err = run_cli(["--model", tiny_qwen3_path, "--backend", "cpu", "--input-jsonl", os.path.join(TESTDATA, "batch_requests.jsonl"),
+                          "--output", str(res), "--max-tokens", "4", "--batch-size", "2"])
+    assert rc == 0, err
+    rows = [json.loads(l) for l in res.read_text().splitlines()]
+    assert [r["id"] for r in rows] == ["sum", "chat", "stop", "think"] and not any("error" in r for r in rows)
+    rc, out, err = run_cli(["--model", tiny_qwen3_path, "--backend", "cpu", "--multi-turn-jsonl", os.path.join(TESTDATA, "multi_turn.jsonl"),
+                            "--max-tokens", "3"])
+    assert rc == 0 and "[turn 4]" in out and "plan=Reset" in out.split("[turn 4]")[1].split("\n")[0], err
+    rc, out, err = run_cli(["--model", tiny_qwen3_path, "--backend", "cpu", "--input", os.path.join(TESTDATA, "input_tool_convert.txt"),
+                            "--tools", os.path.join(TESTDATA, "tools_units.json"), "--dump-prompt", "--max-tokens", "2"])
+    assert rc == 0 and "3.2 kilometres" in out, err          # (the synthetic model's template has no tool section)
