@@ -17,6 +17,7 @@ from .options import build_options, read_configured_backend_input, try_resolve_s
 
 ENDPOINT_SUMMARY = (
     "GET  /                         - Health check",
+    "GET  /metrics                   - Serving totals (Prometheus text format)",
     "GET  /api/tags                  - List hosted models (Ollama)",
     "POST /api/show                  - Show model details (Ollama)",
     "POST /api/generate              - Generate text (Ollama)",

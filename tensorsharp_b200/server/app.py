@@ -10,6 +10,7 @@ label by path, 4xx -> Warning, 5xx -> Error), WebUiChatPolicy.cs, TextUploadHelp
     POST /v1/chat/completions   GET  /v1/models           POST /api/sessions
     DELETE /api/sessions/{id}   POST /api/upload          GET  /api/queue/status
     GET  /api/models            POST /api/models/load     POST /api/chat
+    GET  /metrics  (totals in the Prometheus text format; not in the reference)
     (anything else: the web UI's index.html)
 
 Built on the standard library's threading HTTP server: one thread per connection, responses
@@ -36,6 +37,7 @@ from ..runtime.structured import apply_to_messages, normalize_output, validate_s
 from . import parsers as P
 from .inference_queue import CancellationToken, InferenceQueue
 from .model_service import ModelService
+from .metrics import METRICS
 from .options import (ServerHostingOptions, try_ensure_hosted_model_loaded, try_resolve_hosted_model_request,
                       try_resolve_supported_backend, try_validate_hosted_mmproj_request)
 from .responses import SSE_DONE, Ollama, OpenAI, WebUi, ndjson_line, serialize, sse_event
@@ -188,7 +190,7 @@ class ServerApp:
         self.sessions = sessions or SessionManager(self.logger("TensorSharp.Server.SessionManager"))
         self.queue_poll_s = queue_poll_s
         self._http_log = self.logger("TensorSharp.Server.Logging.RequestLoggingMiddleware")
-        self.low_noise_paths = {"/api/queue/status"}
+        self.low_noise_paths = {"/api/queue/status", "/metrics"}
         self.web_root = options.web_root or os.path.join(os.path.dirname(__file__), "wwwroot")
         self._routes: List[Tuple[str, str, Callable]] = [
             ("GET", "/", self.root), ("GET", "/api/version", self.version), ("GET", "/api/tags", self.ollama_tags),
@@ -196,7 +198,7 @@ class ServerApp:
             ("POST", "/api/chat/ollama", self.ollama_chat), ("POST", "/v1/chat/completions", self.openai_chat),
             ("GET", "/v1/models", self.openai_models), ("POST", "/api/sessions", self.create_session),
             ("DELETE", "/api/sessions/{id}", self.dispose_session), ("POST", "/api/upload", self.upload),
-            ("GET", "/api/queue/status", self.queue_status), ("GET", "/api/models", self.webui_models),
+            ("GET", "/api/queue/status", self.queue_status), ("GET", "/metrics", self.metrics), ("GET", "/api/models", self.webui_models),
             ("POST", "/api/models/load", self.webui_load_model), ("POST", "/api/chat", self.webui_chat)]
 
     def logger(self, category: str) -> Logger:
@@ -249,7 +251,9 @@ class ServerApp:
                                    ExceptionType=type(e).__name__, ElapsedMs=(time.perf_counter() - t0) * 1e3)
                 if not ex.started:
                     ex.send_json({"error": str(e)}, 500)
+                METRICS.record_http(client, 500)
                 return
+            METRICS.record_http(client, ex.status)
             level = "Error" if ex.status >= 500 else "Warning" if ex.status >= 400 else "Debug" if low else "Information"
             self._http_log.log(level, Ev.HttpRequestRejected if ex.status >= 400 else Ev.HttpRequestCompleted,
                                "HTTP {Method} {Path} -> {StatusCode} in {ElapsedMs:.1f} ms (response content-type="
@@ -284,6 +288,10 @@ class ServerApp:
     def queue_status(self, ex: Exchange) -> None:
         s = self.queue.get_status()
         ex.send_json({"busy": s.busy, "pending_requests": s.pending_requests, "total_processed": s.total_processed})
+
+    def metrics(self, ex: Exchange) -> None:
+        text = METRICS.render(self.queue, getattr(self.svc, "gather", None))
+        ex.send_bytes(text.encode("utf-8"), "text/plain; version=0.0.4; charset=utf-8")
 
     def create_session(self, ex: Exchange) -> None:
         s = self.sessions.create_session()

@@ -25,6 +25,7 @@ from ..runtime.kv_cache import ReusePlanKind
 from ..runtime.logging import Ev, NULL_LOGGER, log_scope
 from ..runtime.prompt_renderer import GgufPromptRenderer, KVCachePromptRenderer
 from ..runtime.sampling import SamplingConfig, TokenSampler
+from .metrics import METRICS
 from .options import backend_device, canonicalize_backend
 from .sessions import ChatSession, _utcnow
 
@@ -554,6 +555,8 @@ class ModelService:
                                TimeToFirstTokenMs=state.get("ttft_ns", 0) // 1_000_000, ElapsedMs=total_ns / 1e6,
                                TokensPerSec=(len(generated) / eval_s if eval_s > 0 and generated else 0.0),
                                FinishReason=state["finish"], AssistantContent=sanitize_for_log(text))
+            METRICS.record_generation(n_prompt, len(generated), reused, prompt_ns, state.get("eval_ns", 0),
+                                      bool(state.get("cancelled")))
             if with_metrics:
                 yield StreamItem("", True, n_prompt, len(generated), reused, total_ns, prompt_ns, state.get("eval_ns", 0))
 
@@ -601,6 +604,7 @@ class ModelService:
                                "\"{Completion}\"", Tokens=len(generated), PromptTokens=len(tokens), ElapsedMs=total_ns / 1e6,
                                TokensPerSec=(len(generated) / eval_s if eval_s > 0 and generated else 0.0),
                                FinishReason=state["finish"], Completion=sanitize_for_log(text))
+            METRICS.record_generation(len(tokens), len(generated), 0, prompt_ns, state.get("eval_ns", 0), bool(state.get("cancelled")))
             yield StreamItem("", True, len(tokens), len(generated), 0, total_ns, prompt_ns, state.get("eval_ns", 0))
 
     # ------------------------------------------------------------------ misc

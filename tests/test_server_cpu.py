@@ -808,3 +808,21 @@ def test_queue_capacity_and_preferred_slots():
         t.dispose()
     st = q.get_status()
     assert st.busy is False and st.total_processed == 4
+
+
+def test_metrics_endpoint_counts_generations(tmp_path):
+    from tensorsharp_b200.server.metrics import METRICS
+    app, holder, _ = make_app(tmp_path)
+    app.svc.load_model(app.options.startup_model_path, None, "cpu")
+    METRICS.reset()
+    r = call(app, "POST", "/api/generate", {"model": app.svc.loaded_model_name, "prompt": "hi", "stream": False, "options": {"num_predict": 3}})
+    assert r.status == 200
+    assert call(app, "POST", "/api/generate", {"prompt": "x"}).status == 400
+    m = call(app, "GET", "/metrics")
+    assert m.status == 200 and m.content_type.startswith("text/plain")
+    vals = {l.split(" ")[0]: l.split(" ")[1] for l in m.text.splitlines() if l and not l.startswith("#")}
+    assert vals["tensorsharp_generations_total"] == "1" and int(vals["tensorsharp_generated_tokens_total"]) == json.loads(r.text)["eval_count"]
+    assert int(vals["tensorsharp_prompt_tokens_total"]) >= 1 and vals["tensorsharp_queue_busy"] == "0"
+    assert vals['tensorsharp_http_responses_total{client="ollama",status="2xx"}'] == "1"
+    assert vals['tensorsharp_http_responses_total{client="ollama",status="4xx"}'] == "1"
+    assert "# TYPE tensorsharp_generated_tokens_total counter" in m.text
