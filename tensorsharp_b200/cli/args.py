@@ -24,7 +24,7 @@ USAGE = ("Usage: python -m tensorsharp_b200.cli --model <path.gguf> [--input <in
          "[--benchmark [--bench-prefill N] [--bench-decode N] [--bench-runs N] [--bench-chunked]] "
          "[--test-chunked-prefill [--correct-prefill N] [--correct-decode N]] [--bench-kvcache [--bench-kv-turns N]] "
          "[--test-templates <dir>] [--log-level info|debug|trace] [--log-dir <path>] [--log-file off] [--log-console off] "
-         "[--batch-size N] [--max-context N] [--tp N | --pp N  (one process per GPU: python -m torch.distributed.run "
+         "[--batch-size N] [--max-context N] [--tp N | --pp N | --cp N  (one process per GPU: python -m torch.distributed.run "
          "--nproc-per-node N -m tensorsharp_b200.cli ...)]")
 
 
@@ -65,6 +65,7 @@ class CliOptions:
     log_console: bool = True
     tp: int = 1
     pp: int = 1                       # pipeline stages (one process per stage)
+    cp: int = 1                       # context-parallel ranks: long prompts are dealt to them slice by slice
     batch_size: int = 1               # JSONL mode: requests decoded together (continuous batching)
     max_context: Optional[int] = None
     unknown: List[str] = field(default_factory=list)
@@ -77,7 +78,7 @@ _STR = {"--model": "model", "--input": "input_file", "--input-jsonl": "input_jso
 _INT = {"--max-tokens": "max_tokens", "--bench-prefill": "bench_prefill", "--bench-decode": "bench_decode",
         "--bench-runs": "bench_runs", "--correct-prefill": "correct_prefill", "--correct-decode": "correct_decode",
         "--bench-kv-turns": "bench_kv_turns", "--tp": "tp", "--max-context": "max_context",
-        "--batch-size": "batch_size", "--pp": "pp"}
+        "--batch-size": "batch_size", "--pp": "pp", "--cp": "cp"}
 _BOOL = {"--test": "run_test", "--think": "think", "--dump-prompt": "dump_prompt", "--benchmark": "benchmark",
          "--bench-chunked": "bench_chunked", "--test-chunked-prefill": "test_chunked_prefill",
          "--bench-kvcache": "bench_kvcache", "--interactive": "interactive", "--chat": "interactive"}

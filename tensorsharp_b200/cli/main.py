@@ -599,7 +599,17 @@ def load_model(o: CliOptions, log):
         model = PipelinedModel(stage)
         model.warm_up_kernels()
         return model
-    if o.tp > 1 or world > 1:
+    if o.cp > 1:
+        # every process holds the whole model; prompts of TSB_CP_MIN_TOKENS tokens or more are dealt to the processes
+        if world != o.cp or o.tp > 1:
+            raise ValueError(f"--cp {o.cp} needs {o.cp} processes and no --tp (WORLD_SIZE is {world}); start the CLI with "
+                             f"python -m torch.distributed.run --nproc-per-node {o.cp} --master-addr 127.0.0.1 "
+                             f"-m tensorsharp_b200.cli --cp {o.cp} ...")
+        from ..parallel.dist import init_from_env
+        comm = init_from_env("gloo" if device == "cpu" else None)
+        device = str(comm.device) if device != "cpu" else "cpu"
+        kw.update(cp_comm=comm)
+    elif o.tp > 1 or world > 1:
         # one process per GPU, started by ``python -m torch.distributed.run --nproc-per-node N -m tensorsharp_b200.cli --tp N``
         if world != max(o.tp, 1):
             raise ValueError(f"--tp {o.tp} needs {o.tp} processes (WORLD_SIZE is {world}); start the CLI with "
@@ -676,7 +686,8 @@ def _run(o: CliOptions, con: Console, log) -> int:
         con.error(USAGE)
         return 1
     model = load_model(o, log)
-    if getattr(model, "tp_rank", 0) != 0 or getattr(model, "pp_rank", 0) != 0:
+    cp_comm = getattr(model, "cp_comm", None)
+    if getattr(model, "tp_rank", 0) != 0 or getattr(model, "pp_rank", 0) != 0 or (cp_comm is not None and cp_comm.rank != 0):
         con = Console(open(os.devnull, "w"), con.err)          # every rank runs the same steps; rank 0 does the talking
     try:
         attach_projector(model, o, log)

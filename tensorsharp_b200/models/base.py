@@ -63,10 +63,12 @@ def supported_architectures() -> List[str]:
 class ModelBase:
     supports_kv_truncation = True
     supports_pipeline = False
+    supports_context_parallel = False
 
     def __init__(self, path: str, device="cuda", *, max_context: Optional[int] = None, max_seqs: int = 1,
                  page_size: int = 64, kv_dtype: Optional[torch.dtype] = None, tp_rank: int = 0, tp_size: int = 1,
-                 ep_rank: int = 0, ep_size: int = 1, comm=None, pp_rank: int = 0, pp_size: int = 1, pp_comm=None):
+                 ep_rank: int = 0, ep_size: int = 1, comm=None, pp_rank: int = 0, pp_size: int = 1, pp_comm=None,
+                 cp_comm=None):
         self.path = path
         self.device = torch.device(device)
         self.gguf = GGUFFile(path)
@@ -76,6 +78,13 @@ class ModelBase:
         self.pp_rank, self.pp_size, self.pp_comm = pp_rank, pp_size, pp_comm
         if pp_size > 1 and not self.supports_pipeline:
             raise ValueError(f"{type(self).__name__} has no pipeline-parallel path")
+        # context parallelism: every rank of ``cp_comm`` holds all the weights; a long prompt is dealt to the ranks
+        # in order, each runs the layers on its slice and the K / V rows are exchanged layer by layer
+        self.cp_comm = cp_comm if (cp_comm is not None and cp_comm.size > 1) else None
+        if self.cp_comm is not None and not self.supports_context_parallel:
+            raise ValueError(f"{type(self).__name__} has no context-parallel prefill")
+        if self.cp_comm is not None and (tp_size > 1 or pp_size > 1):
+            raise ValueError("context parallelism is not combined with tensor or pipeline parallelism")
         if pp_size > 1 and tp_size > 1:
             raise ValueError("pipeline stages are not combined with tensor parallelism")
         g = self.gguf
@@ -188,6 +197,26 @@ class ModelBase:
             from ..parallel.fused import TpSeqParallel
             self._tpseq = sp = TpSeqParallel(self.comm, max(T, 4096), self.cfg.hidden)
         return sp
+
+    def cp_wanted(self, batch) -> bool:
+        """A prompt goes through the context-parallel path when the model was given a group for it, the batch is
+        one sequence's prompt and it has at least ``TSB_CP_MIN_TOKENS`` tokens (default 2048) and one per rank."""
+        if self.cp_comm is None or batch.B != 1 or batch.is_decode or self._pending_embeddings:
+            return False
+        return batch.T >= max(self.cp_comm.size, int(os.environ.get("TSB_CP_MIN_TOKENS", "2048")))
+
+    def cp_attention(self, n: int, Hkv: int, Dh: int):
+        """The peer-memory attention of the context-parallel group for shards of ``n`` tokens (CUDA only,
+        created on first use and regrown on demand; TSB_CP_FUSED=0 keeps the all-gather + local attention path)."""
+        if self.device.type != "cuda" or os.environ.get("TSB_CP_FUSED", "1") == "0":
+            return None
+        cpa = self.__dict__.get("_cpa")
+        if cpa is None or cpa.max_shard < n or (cpa.Hkv, cpa.Dh) != (Hkv, Dh):
+            if cpa is not None:
+                cpa.close()
+            from ..parallel.context import ContextParallelAttention
+            cpa = self.__dict__["_cpa"] = ContextParallelAttention(self.cp_comm, max(n, 4096), Hkv, Dh)
+        return cpa
 
     # ------------------------------------------------------------------ weights
     def has(self, name: str) -> bool:

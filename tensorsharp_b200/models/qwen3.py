@@ -24,6 +24,7 @@ from .base import ModelBase, register_architecture
 @register_architecture("qwen3", "qwen2", "llama")
 class Qwen3Model(ModelBase):
     supports_pipeline = True
+    supports_context_parallel = True
 
     def load_weights(self) -> None:
         c = self.cfg
@@ -96,6 +97,8 @@ class Qwen3Model(ModelBase):
         mid = torch.float32 if small else torch.bfloat16
         if self.pp_size > 1:
             return self.forward_stage(batch, want_logits)
+        if self.cp_wanted(batch):
+            return self.forward_context_parallel(batch, want_logits)
         h = self.inject_pending_embeddings(F.embed(self.tok_emb, batch.tokens))
         if h.is_cuda and T <= F.FUSED_MAX_M and F.can_fuse(h, self.layers[0].get("wqkv", self.layers[0].get("wq"))):
             return self.forward_fused_small(h, batch, want_logits)
@@ -172,6 +175,51 @@ class Qwen3Model(ModelBase):
             return None
         last = h[batch.last_idx].contiguous()
         return self.lm_head_logits(F.norm(last, self.out_norm, c.eps, want_q8=True))
+
+    def forward_context_parallel(self, batch: Batch, want_logits: bool) -> Optional[torch.Tensor]:
+        """A long prompt over a context-parallel group: this rank runs every layer on its slice of the tokens.
+        Attention needs the keys and values of the earlier slices: on GPUs, when the sequence is new and the
+        slices are equal, they are pulled from the peers' memory inside the attention kernels
+        (parallel/context.py); otherwise they are taken from this rank's cache after the exchange.  The exchange
+        runs in every layer either way, so that all ranks end with the whole cache and decode alike."""
+        from ..parallel.context import exchange_kv_shards, shard_batch, shard_bounds
+        c, cp = self.cfg, self.cp_comm
+        Hq, Hkv, Dh = self.Hq, self.Hkv, c.head_dim
+        bounds = [shard_bounds(batch.T, cp.size, s) for s in range(cp.size)]
+        t0, t1 = bounds[cp.rank]
+        sub = shard_batch(batch, t0, t1)
+        n = sub.T
+        small = n <= F.GEMV_MAX_M
+        mid = torch.float32 if small else torch.bfloat16
+        fresh = batch.h_kv_lens[0] == batch.T and all(b - a == n for a, b in bounds)
+        cpa = self.cp_attention(n, Hkv, Dh) if fresh else None
+        h = F.embed(self.tok_emb, sub.tokens)
+        for l, L in enumerate(self.layers):
+            kc, vc = self.kv.k[self.l0 + l], self.kv.v[self.l0 + l]
+            a = F.norm(h, L["attn_norm"], c.eps, want_q8=small)
+            q, k, v = self.qkv_proj(a, L, n, mid)
+            qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=sub, k_cache=kc, v_cache=vc, rope=self.rope,
+                                  qn=L["q_norm"], kn=L["k_norm"], eps=c.eps)
+            qr = self.q_post_scale(qr, sub)
+            if cpa is not None:
+                o = cpa.attention(qr, kc.index_select(0, sub.slots), vc.index_select(0, sub.slots), Dh ** -0.5).view(n, Hq * Dh)
+                exchange_kv_shards(cp, batch, bounds, kc, vc)
+            else:
+                exchange_kv_shards(cp, batch, bounds, kc, vc)
+                o = F.attention(qr, kc, vc, sub, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh)
+            h = F.linear(F.as_act(o), L["wo"], residual=h)
+            a = F.norm(h, L["ffn_norm"], c.eps, want_q8=small)
+            if "gate_up" in L:
+                gu = F.linear(a, L["gate_up"], act="swiglu", out_dtype=torch.bfloat16)
+            else:
+                gu = F.glu("swiglu", F.linear(a, L["gate"], out_dtype=mid), F.linear(a, L["up"], out_dtype=mid))
+            h = F.linear(F.as_act(gu), L["down"], residual=h)
+        if not want_logits:
+            return None
+        # the prompt's last token sits on the last rank; the others compute a row of the same shape and take its
+        last = h[sub.last_idx].contiguous()
+        logits = F.linear(F.norm(last, self.out_norm, c.eps, want_q8=True), self.lm_head, out_dtype=torch.float32)
+        return cp.all_gather_list(logits)[cp.size - 1]
 
     def qkv_proj(self, a, L, T: int, mid):
         Hq, Hkv, Dh = self.Hq, self.Hkv, self.cfg.head_dim

@@ -84,3 +84,51 @@ class ContextParallelAttention:
     def close(self) -> None:
         torch.cuda.synchronize(self.comm.device)
         self.region.close()
+
+
+# ---------------------------------------------------------------------------------------------------
+# Context-parallel prefill of a whole model: the pieces that are the same for every architecture.
+# Each rank of the group holds all the weights and runs the layers on its slice of the prompt; after a
+# layer's K / V rows are computed they are exchanged, so that every rank ends with the full cache and
+# the decode steps that follow can run on every rank alike (or on any one of them).
+
+def shard_bounds(T: int, size: int, rank: int):
+    """Token range of ``rank`` when ``T`` prompt tokens are dealt to ``size`` ranks in order (sizes differ by one at most)."""
+    base, rem = divmod(T, size)
+    t0 = rank * base + min(rank, rem)
+    return t0, t0 + base + (1 if rank < rem else 0)
+
+
+def shard_batch(batch, t0: int, t1: int):
+    """Tokens ``[t0, t1)`` of a one-sequence batch as a batch of their own: they see the cache up to their
+    last position, as a chunk of a chunked prefill does."""
+    from ..ops.functional import Batch
+    assert batch.B == 1 and 0 <= t0 < t1 <= batch.T
+    n = t1 - t0
+    kv_len = batch.h_kv_lens[0] - (batch.T - t1)
+    dev = batch.tokens.device
+    return Batch(tokens=batch.tokens[t0:t1].contiguous(), positions=batch.positions[t0:t1].contiguous(),
+                 slots=batch.slots[t0:t1].contiguous(), cu_q=torch.tensor([0, n], dtype=torch.int32, device=dev),
+                 kv_lens=torch.tensor([kv_len], dtype=torch.int32, device=dev), block_table=batch.block_table,
+                 last_idx=torch.tensor([n - 1], dtype=torch.int64, device=dev), seq_slots=batch.seq_slots,
+                 max_q_len=n, max_kv_len=kv_len, is_decode=False, page_size=batch.page_size,
+                 h_cu_q=(0, n), h_kv_lens=(kv_len,))
+
+
+def exchange_kv_shards(comm, batch, rank_bounds, k_cache: torch.Tensor, v_cache: torch.Tensor) -> None:
+    """Every rank has written the K / V rows of its own tokens into its cache; fetch the other ranks' rows
+    (one all-gather of the padded shards) and write them at the same tokens' slots of this rank's cache."""
+    r = comm.rank
+    t0, t1 = rank_bounds[r]
+    n_max = max(b - a for a, b in rank_bounds)
+    mine = torch.zeros((2, n_max) + tuple(k_cache.shape[1:]), dtype=k_cache.dtype, device=k_cache.device)
+    own = batch.slots[t0:t1]
+    mine[0, :t1 - t0] = k_cache.index_select(0, own)
+    mine[1, :t1 - t0] = v_cache.index_select(0, own)
+    for s, part in enumerate(comm.all_gather_list(mine)):
+        if s == r:
+            continue
+        a, b = rank_bounds[s]
+        idx = batch.slots[a:b]
+        k_cache.index_copy_(0, idx, part[0, :b - a])
+        v_cache.index_copy_(0, idx, part[1, :b - a])

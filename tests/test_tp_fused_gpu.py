@@ -133,3 +133,19 @@ def test_pipeline_stages_over_nccl(kv8_model_path):
     assert p.returncode == 0 and lines, f"rc={p.returncode}\nstdout:\n{p.stdout[-3000:]}\nstderr:\n{p.stderr[-3000:]}"
     r = json.loads(lines[0][8:])
     assert r["ranks_agree"] == 2 and r["tokens"] == r["want"], r
+
+
+def test_context_parallel_prefill_over_peer_memory(kv8_model_path):
+    """A prompt dealt to two GPUs (keys and values of the earlier slice pulled from the peer inside the attention
+    kernels, caches completed by an all-gather per layer) gives the logits of one GPU, for the prompt, a decode
+    step and a second prompt on the same sequence."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TSB_WORKER_MODE="cp_model")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(HERE, "tp_worker.py"), kv8_model_path]
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    lines = [l for l in p.stdout.splitlines() if l.startswith("CPMODEL ")]
+    assert p.returncode == 0 and lines, f"rc={p.returncode}\nstdout:\n{p.stdout[-3000:]}\nstderr:\n{p.stderr[-3000:]}"
+    r = json.loads(lines[0][8:])
+    assert r["status"] == 0 and max(r["rel_err"]) < 5e-2, r

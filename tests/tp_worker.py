@@ -18,6 +18,11 @@ def main():
         comm.barrier()
         torch.cuda.synchronize()
         os._exit(0)
+    if os.environ.get("TSB_WORKER_MODE") == "cp_model":
+        check_context_parallel_model(sys.argv[1], comm)
+        comm.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
     check_context_parallel(comm)
     for path in sys.argv[1:]:
         check_model(path, comm)
@@ -68,6 +73,34 @@ def check_context_parallel(comm):
     if rank == 0:
         print("CPCHECK " + json.dumps({"world": world, "max_err": float(t[0]), "status": int(t[1])}), flush=True)
     cp.close()
+
+
+def check_context_parallel_model(path, comm):
+    """A prompt dealt to the ranks of a context-parallel group against one GPU running it whole: the first prompt
+    takes the peer-memory attention (new sequence, equal slices), the second one the exchange + local attention
+    (sequence not empty, slices of unequal length); decode steps run on every rank from its own cache."""
+    from tensorsharp_b200.models.base import ModelBase
+    os.environ["TSB_CP_MIN_TOKENS"] = "64"
+    g = torch.Generator().manual_seed(21)
+    world = comm.size
+    prompt = torch.randint(0, 4096, (256 * world,), generator=g).tolist()
+    more = torch.randint(0, 4096, (100 * world + 1,), generator=g).tolist()
+    single = ModelBase.create(path, comm.device, max_context=2048)
+    want = [single.forward(prompt).float().clone()]
+    want.append(single.forward([int(want[0].argmax())]).float().clone())
+    want.append(single.forward(more).float().clone())
+    del single
+    m = ModelBase.create(path, comm.device, max_context=2048, cp_comm=comm)
+    got = [m.forward(prompt).float().clone()]
+    got.append(m.forward([int(want[0].argmax())]).float().clone())
+    got.append(m.forward(more).float().clone())
+    errs = [float((a - b).abs().max() / b.abs().max()) for a, b in zip(got, want)]
+    cpa = m.__dict__.get("_cpa")
+    t = torch.tensor(errs + [float(cpa.status()) if cpa is not None else -1.0], device=comm.device)
+    import torch.distributed as dist
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if comm.rank == 0:
+        print("CPMODEL " + json.dumps({"world": world, "rel_err": [float(x) for x in t[:3]], "status": int(t[3])}), flush=True)
 
 
 def check_model(path, comm):
