@@ -4,8 +4,9 @@ The reference keeps one contiguous F32 cache ``[kvHeads, maxSeqLen, headDim]`` p
 for its single sequence (TensorSharp.Models/ModelBase.cs:1340 CopyToCache, :302-408
 context sizing).  Here the cache is paged (``[n_pages * page_size, Hkv, Dh]`` bf16 per
 layer) so that many sequences share one pool, a sequence can be truncated to any prefix
-in O(1) (multi-turn prefix reuse, ModelBase.TruncateKVCache) and sliding-window layers
-can give pages back.  Layers that share KV with a donor layer (Gemma 4) alias the donor's
+in O(1) (multi-turn prefix reuse, ModelBase.TruncateKVCache).  All layers of a sequence
+share one block table, so a sliding-window layer keeps its pages and masks by position
+(the reference's circular window caches, Gemma4Model.cs:1927, have no counterpart).  Layers that share KV with a donor layer (Gemma 4) alias the donor's
 tensors.  Recurrent layers (GatedDeltaNet, Mamba2) get fixed-size state slots instead.
 """
 from __future__ import annotations
