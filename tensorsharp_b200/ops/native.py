@@ -93,6 +93,27 @@ def build(force: bool = False, verbose: bool = False, jobs: Optional[int] = None
     return LIB_PATH
 
 
+def build_tests(force: bool = False) -> List[Path]:
+    """Compile the stand-alone C++ test programs under ``csrc/tests`` against the library (``_native/<name>``, found
+    next to the library at run time through an ``$ORIGIN`` run path).  They take no Python: ``_native/native_check``."""
+    lib_path = build()
+    nvcc = _nvcc()
+    out: List[Path] = []
+    for src in sorted((CSRC / "tests").glob("*.cu")):
+        exe = OUT_DIR / src.stem
+        stamp = OUT_DIR / (src.stem + ".stamp")
+        want = hashlib.sha1(src.read_bytes()).hexdigest()
+        if force or not exe.exists() or not stamp.exists() or stamp.read_text() != want or exe.stat().st_mtime < lib_path.stat().st_mtime:
+            cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O2", "-std=c++17", str(src), "-o", str(exe),
+                   "-L", str(OUT_DIR), "-ltsb200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                raise NativeLibraryError(f"nvcc failed for tests/{src.name}:\n{r.stderr[-4000:]}")
+            stamp.write_text(want)
+        out.append(exe)
+    return out
+
+
 def is_stale() -> bool:
     """True when a source or header differs from what the objects were compiled from."""
     for src in sources():
