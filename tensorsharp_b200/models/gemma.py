@@ -307,3 +307,14 @@ class Gemma4Model(_GemmaBase):
             if L["out_scale"] != 1.0:
                 h = h * L["out_scale"]
         return self._logits(h, batch) if want_logits else None
+
+    def prefill_chunk(self, requested: int) -> int:
+        """Gemma 4 prefills in chunks of min(2048, max(2 * window, 1024)) tokens, or ``TS_PREFILL_CHUNK`` when set
+        (Gemma4Model.cs:593-637); a caller may ask for smaller chunks, not larger ones."""
+        import os
+        env = os.environ.get("TS_PREFILL_CHUNK")
+        own = int(env) if env and env.isdigit() and int(env) > 0 else min(2048, max(2 * self.window, 1024))
+        return max(1, min(requested, own))
+
+    def forward_refill(self, tokens, chunk: int = 2048):
+        return super().forward_refill(tokens, self.prefill_chunk(chunk))

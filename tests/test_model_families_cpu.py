@@ -71,3 +71,23 @@ def test_recurrent_models_refuse_truncation(family_paths):
     with pytest.raises(RuntimeError):
         m.truncate_kv_cache(1)
     assert ModelBase.create(family_paths["gemma3"], "cpu", max_context=64).supports_kv_truncation
+
+
+def test_gemma4_prefill_chunk_policy(tmp_path, monkeypatch):
+    """Gemma 4 caps the prefill chunk at min(2048, max(2 * window, 1024)); TS_PREFILL_CHUNK overrides the cap; the
+    chunked prefill gives the logits of the one-shot prefill."""
+    from tensorsharp_b200.models import synth
+    from tensorsharp_b200.models.base import ModelBase
+    p = str(tmp_path / "g4.gguf")
+    synth.write_gemma(p, arch="gemma4", device="cpu")
+    m = ModelBase.create(p, "cpu", max_context=256)
+    monkeypatch.delenv("TS_PREFILL_CHUNK", raising=False)
+    assert m.prefill_chunk(5120) == min(2048, max(2 * m.window, 1024)) and m.prefill_chunk(64) == 64
+    monkeypatch.setenv("TS_PREFILL_CHUNK", "16")
+    assert m.prefill_chunk(5120) == 16
+    g = torch.Generator().manual_seed(4)
+    toks = torch.randint(0, 4096, (50,), generator=g).tolist()
+    chunked = m.forward_refill(toks, 5120).clone()          # 16 tokens at a time
+    m.reset_kv_cache()
+    whole = m.forward(toks)
+    assert torch.allclose(chunked, whole, atol=3e-2)              # 16-row chunks take the int8-activation path

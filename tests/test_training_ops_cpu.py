@@ -12,7 +12,7 @@ def test_cross_entropy_matches_torch_with_label_smoothing():
     for ls in (0.0, 0.1):
         want = torch.nn.functional.cross_entropy(logits, tgt, label_smoothing=ls)
         probs = torch.softmax(logits.detach(), -1)
-        assert abs(T.cross_entropy_loss(probs, tgt, label_smooth=ls) - float(want)) < 1e-5
+        assert abs(T.cross_entropy_loss(probs, tgt, label_smooth=ls) - float(want.detach())) < 1e-5
         (g,) = torch.autograd.grad(want, logits)
         got = T.cross_entropy_loss_backward(probs, tgt, label_smooth=ls)
         assert torch.allclose(got, g, atol=1e-6)
