@@ -198,6 +198,31 @@ class ModelBase:
             self._tpseq = sp = TpSeqParallel(self.comm, max(T, 4096), self.cfg.hidden)
         return sp
 
+    def stage_tensors(self):
+        """(embedding, output norm, lm_head) as this pipeline stage needs them: the embedding on the first stage (and on
+        the last one when the lm_head is tied to it), norm and head on the last; everything without stages."""
+        tied = not self.has("output.weight")
+        emb = self.qw("token_embd.weight") if (self.is_first_stage or (self.is_last_stage and tied)) else None
+        norm = self.f32("output_norm.weight") if self.is_last_stage else None
+        head = (self.qw("output.weight", optional=True) or emb) if self.is_last_stage else None
+        return emb, norm, head
+
+    def stage_input(self, batch, embed):
+        """The residual stream entering this process's layers: ``embed()`` on the first (or only) stage, else the
+        previous stage's output (float32 ``[T, hidden]``)."""
+        if self.pp_size > 1 and not self.is_first_stage:
+            from ..parallel.pipeline import recv_hidden
+            return recv_hidden(self.pp_comm, self.pp_rank - 1, (batch.T, self.cfg.hidden), self.device)
+        return embed()
+
+    def stage_handoff(self, h) -> bool:
+        """On every stage but the last: send the residual stream on and return True (the caller returns ``None``)."""
+        if self.pp_size > 1 and not self.is_last_stage:
+            from ..parallel.pipeline import send_hidden
+            send_hidden(self.pp_comm, self.pp_rank + 1, h.float())
+            return True
+        return False
+
     def cp_wanted(self, batch) -> bool:
         """A prompt goes through the context-parallel path when the model was given a group for it, the batch is
         one sequence's prompt and it has at least ``TSB_CP_MIN_TOKENS`` tokens (default 2048) and one per rank."""

@@ -48,7 +48,9 @@ class _GemmaBase(ModelBase):
         return self.cfg.n_kv_heads
 
     def kv_layer_shapes(self):
-        return [(self.kv_heads_of(l) // self.tp_size, self.head_dim_of(l)) for l in range(self.cfg.n_layers)]
+        l0, l1 = self.layer_range
+        return [(self.kv_heads_of(l) // self.tp_size, self.head_dim_of(l)) if l0 <= l < l1 else None
+                for l in range(self.cfg.n_layers)]
 
     def _load_common_layer(self, l: int) -> Dict:
         c = self.cfg
@@ -131,6 +133,8 @@ class _GemmaBase(ModelBase):
 
 @register_architecture("gemma3", "gemma2")
 class Gemma3Model(_GemmaBase):
+    supports_pipeline = True
+
     def parse_config(self) -> None:
         g, a, c = self.gguf, self.arch, self.cfg
         c.head_dim = g.get_int(f"{a}.attention.key_length", 0) or 256
@@ -144,10 +148,9 @@ class Gemma3Model(_GemmaBase):
 
     def load_weights(self) -> None:
         c = self.cfg
-        self.tok_emb = self.qw("token_embd.weight")
-        self.out_norm = self.f32("output_norm.weight")
-        self.lm_head = self.qw("output.weight", optional=True) or self.tok_emb
-        self.layers = [self._load_common_layer(l) for l in range(c.n_layers)]
+        self.tok_emb, self.out_norm, self.lm_head = self.stage_tensors()
+        self.l0, l1 = self.layer_range
+        self.layers = [self._load_common_layer(l) for l in range(self.l0, l1)]
         Dh = c.head_dim
         self.rope_l = RopeSpec(rot_dim=Dh, theta_base=self.rope_local, mode=0)
         self.rope_g = RopeSpec(rot_dim=Dh, theta_base=c.rope_base, mode=0, freq_scale=1.0 / self.rope_scale)
@@ -156,8 +159,10 @@ class Gemma3Model(_GemmaBase):
         c = self.cfg
         small = batch.T <= F.GEMV_MAX_M
         mid = torch.float32 if small else torch.bfloat16
-        h = self.inject_pending_embeddings(F.embed(self.tok_emb, batch.tokens, scale=math.sqrt(c.hidden)))
-        for l, L in enumerate(self.layers):
+        h = self.stage_input(batch, lambda: self.inject_pending_embeddings(
+            F.embed(self.tok_emb, batch.tokens, scale=math.sqrt(c.hidden))))
+        for i, L in enumerate(self.layers):
+            l = self.l0 + i
             local = self.is_local(l)
             a = F.norm(h, L["attn_norm"], c.eps, want_q8=small)
             y = self._attention(l, L, a, batch, mid, self.rope_l if local else self.rope_g, L["Dh"] ** -0.5,
@@ -165,6 +170,8 @@ class Gemma3Model(_GemmaBase):
             h = F.norm_add(y, L["post_attn_norm"], c.eps, h)
             a = F.norm(h, L["ffn_norm"], c.eps, want_q8=small)
             h = F.norm_add(self._mlp(L, a, mid), L["post_ffn_norm"], c.eps, h)
+        if self.stage_handoff(h):
+            return None
         return self._logits(h, batch) if want_logits else None
 
 

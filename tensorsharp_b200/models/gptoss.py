@@ -26,6 +26,8 @@ from .base import ModelBase, register_architecture
 
 @register_architecture("gpt-oss", "gptoss")
 class GptOssModel(ModelBase):
+    supports_pipeline = True
+
     def parse_config(self) -> None:
         g, a, c = self.gguf, self.arch, self.cfg
         self.n_experts = g.get_int(f"{a}.expert_count", 0)
@@ -43,11 +45,16 @@ class GptOssModel(ModelBase):
         # expert parallelism: contiguous expert ranges per rank (ep defaults to the tp group)
         ep, er = (self.ep_size, self.ep_rank) if self.ep_size > 1 else (tp, r)
         self.e0, self.e1 = even_split(self.n_experts, ep, er)
-        self.tok_emb = self.qw("token_embd.weight")
-        self.out_norm = self.f32("output_norm.weight")
-        self.lm_head = self.qw("output.weight", optional=True) or self.tok_emb
+        # pipeline stages hold a contiguous range of layers; the embedding lives on the first stage (and on the last
+        # one when the lm_head is tied to it), the output norm and lm_head on the last
+        l0, l1 = self.layer_range
+        self.l0 = l0
+        tied = not self.has("output.weight")
+        self.tok_emb = self.qw("token_embd.weight") if (self.is_first_stage or (self.is_last_stage and tied)) else None
+        self.out_norm = self.f32("output_norm.weight") if self.is_last_stage else None
+        self.lm_head = (self.qw("output.weight", optional=True) or self.tok_emb) if self.is_last_stage else None
         self.layers = []
-        for l in range(c.n_layers):
+        for l in range(l0, l1):
             p = f"blk.{l}."
             q, k, v = self.qw(p + "attn_q.weight"), self.qw(p + "attn_k.weight"), self.qw(p + "attn_v.weight")
             bq, bk, bv = (self.f32(p + f"attn_{n}.bias", optional=True) for n in "qkv")
@@ -175,7 +182,12 @@ class GptOssModel(ModelBase):
         T = batch.T
         small = T <= F.GEMV_MAX_M
         mid = torch.float32 if small else torch.bfloat16
+        if self.pp_size > 1 and not self.is_first_stage:
+            from ..parallel.pipeline import recv_hidden
+            return self.run_layers(recv_hidden(self.pp_comm, self.pp_rank - 1, (T, c.hidden), self.device), batch, want_logits)
         h = F.embed(self.tok_emb, batch.tokens)
+        if self.pp_size > 1:
+            return self.run_layers(h, batch, want_logits)
         n_layers = len(self.layers)
         sharded = self.tp_size > 1 and (self.e1 - self.e0) != self.n_experts and self.ep_size <= 1
         if sharded and h.is_cuda:
@@ -187,13 +199,22 @@ class GptOssModel(ModelBase):
                 sp = self.tp_seq(T)
                 if sp is not None:
                     return self.forward_seq_parallel(h, batch, want_logits, sp)
+        return self.run_layers(h, batch, want_logits)
+
+    def run_layers(self, h: torch.Tensor, batch: Batch, want_logits: bool) -> Optional[torch.Tensor]:
+        """This process's layers on the residual stream ``h``; on the last (or only) pipeline stage the logits."""
+        c = self.cfg
+        T = batch.T
+        small = T <= F.GEMV_MAX_M
+        mid = torch.float32 if small else torch.bfloat16
+        n_layers = len(self.layers)
         for l, L in enumerate(self.layers):
             a = F.norm(h, L["attn_norm"], c.eps, want_q8=small)
-            o = self.attention_block(a, L, l, batch, mid, lambda w, b: F.linear(a, w, bias=b, out_dtype=mid))
+            o = self.attention_block(a, L, self.l0 + l, batch, mid, lambda w, b: F.linear(a, w, bias=b, out_dtype=mid))
             h = self.reduce_add(F.linear(F.as_act(o), L["wo"], bias=L["bo"] if self.tp_rank == 0 else None), h)
             # mixture of experts; on the last layer of a prefill only the last token of each
             # sequence feeds the logits, so only those rows are run
-            last_only = (l == n_layers - 1) and not batch.is_decode
+            last_only = self.is_last_stage and (l == n_layers - 1) and not batch.is_decode
             hm = h[batch.last_idx].contiguous() if last_only else h
             a = F.norm(hm, L["ffn_norm"], c.eps, want_q8=hm.shape[0] <= F.GEMV_MAX_M)
             logits = F.linear(a, L["router"], bias=L["router_bias"], out_dtype=torch.float32)
@@ -206,6 +227,10 @@ class GptOssModel(ModelBase):
                 h = hm + y
             else:
                 h = h + y
+        if not self.is_last_stage:
+            from ..parallel.pipeline import send_hidden
+            send_hidden(self.pp_comm, self.pp_rank + 1, h)
+            return None
         if not want_logits:
             return None
         last = h if (not batch.is_decode and n_layers > 0) else h[batch.last_idx].contiguous()

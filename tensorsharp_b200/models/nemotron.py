@@ -28,6 +28,7 @@ from .base import ModelBase, register_architecture
 @register_architecture("nemotron_h", "nemotron_h_moe", "nemotronh")
 class NemotronHModel(ModelBase):
     supports_kv_truncation = False
+    supports_pipeline = True
 
     def parse_config(self) -> None:
         g, a, c = self.gguf, self.arch, self.cfg
@@ -61,17 +62,17 @@ class NemotronHModel(ModelBase):
 
     def kv_layer_shapes(self):
         c = self.cfg
-        return [(self.layer_kv[l], c.head_dim) if self.layer_type[l] == "attn" else None for l in range(c.n_layers)]
+        l0, l1 = self.layer_range
+        return [(self.layer_kv[l], c.head_dim) if (self.layer_type[l] == "attn" and l0 <= l < l1) else None for l in range(c.n_layers)]
 
     def load_weights(self) -> None:
         c = self.cfg
-        self.tok_emb = self.qw("token_embd.weight")
-        self.out_norm = self.f32("output_norm.weight")
-        self.lm_head = self.qw("output.weight", optional=True) or self.tok_emb
+        self.tok_emb, self.out_norm, self.lm_head = self.stage_tensors()
+        self.l0, l1 = self.layer_range
         self.layers = []
         S = max(self.max_seqs, 1)
         xbc = self.d_inner + 2 * self.n_group * self.d_state
-        for l in range(c.n_layers):
+        for l in range(self.l0, l1):
             p = f"blk.{l}."
             L = {"norm": self.f32(p + "attn_norm.weight"), "type": self.layer_type[l]}
             if L["type"] == "mamba":
@@ -158,17 +159,17 @@ class NemotronHModel(ModelBase):
         c = self.cfg
         small = batch.T <= F.GEMV_MAX_M
         mid = torch.float32 if small else torch.bfloat16
-        h = F.embed(self.tok_emb, batch.tokens)
-        for l, L in enumerate(self.layers):
+        h = self.stage_input(batch, lambda: F.embed(self.tok_emb, batch.tokens))
+        for i, L in enumerate(self.layers):
             a = F.norm(h, L["norm"], c.eps, want_q8=small)
             if L["type"] == "mamba":
                 y = self._mamba(L, a, batch)
             elif L["type"] == "attn":
-                y = self._attn(l, L, a, batch, mid)
+                y = self._attn(self.l0 + i, L, a, batch, mid)
             else:
                 y = self._ffn(L, a, mid)
             h = h + y
-        if not want_logits:
+        if self.stage_handoff(h) or not want_logits:
             return None
         last = h[batch.last_idx].contiguous()
         a = F.norm(last, self.out_norm, c.eps, want_q8=True)

@@ -28,6 +28,7 @@ from .base import ModelBase, register_architecture
 @register_architecture("qwen35", "qwen35moe", "qwen3next")
 class Qwen35Model(ModelBase):
     supports_kv_truncation = False
+    supports_pipeline = True
 
     def parse_config(self) -> None:
         g, a, c = self.gguf, self.arch, self.cfg
@@ -46,20 +47,20 @@ class Qwen35Model(ModelBase):
 
     def kv_layer_shapes(self):
         c = self.cfg
-        return [None if self.is_recurrent[l] else (c.n_kv_heads, c.head_dim) for l in range(c.n_layers)]
+        l0, l1 = self.layer_range
+        return [None if (self.is_recurrent[l] or not l0 <= l < l1) else (c.n_kv_heads, c.head_dim) for l in range(c.n_layers)]
 
     def load_weights(self) -> None:
         c = self.cfg
         ep, er = (self.ep_size, self.ep_rank) if self.ep_size > 1 else (self.tp_size, self.tp_rank)
         self.e0, self.e1 = even_split(self.n_experts, ep, er) if self.n_experts else (0, 0)
-        self.tok_emb = self.qw("token_embd.weight")
-        self.out_norm = self.f32("output_norm.weight")
-        self.lm_head = self.qw("output.weight", optional=True) or self.tok_emb
+        self.tok_emb, self.out_norm, self.lm_head = self.stage_tensors()
+        self.l0, l1 = self.layer_range
         self.layers = []
         qkv_dim = 2 * self.Hk * self.Dk + self.Hv * self.Dv
         dev = self.device
         S = max(self.max_seqs, 1)
-        for l in range(c.n_layers):
+        for l in range(self.l0, l1):
             p = f"blk.{l}."
             L = {"attn_norm": self.f32(p + "attn_norm.weight"),
                  "post_norm": self.f32(p + "post_attention_norm.weight")}
@@ -167,14 +168,15 @@ class Qwen35Model(ModelBase):
         c = self.cfg
         small = batch.T <= F.GEMV_MAX_M
         mid = torch.float32 if small else torch.bfloat16
-        h = self.inject_pending_embeddings(F.embed(self.tok_emb, batch.tokens))
-        for l, L in enumerate(self.layers):
+        h = self.stage_input(batch, lambda: self.inject_pending_embeddings(F.embed(self.tok_emb, batch.tokens)))
+        for i, L in enumerate(self.layers):
+            l = self.l0 + i
             a = F.norm(h, L["attn_norm"], c.eps, want_q8=small)
             y = self._gdn_layer(L, a, batch, mid) if self.is_recurrent[l] else self._attn_layer(l, L, a, batch, mid)
             h = h + y
             a = F.norm(h, L["post_norm"], c.eps, want_q8=small)
             h = h + self._ffn(L, a, mid)
-        if not want_logits:
+        if self.stage_handoff(h) or not want_logits:
             return None
         last = h[batch.last_idx].contiguous()
         a = F.norm(last, self.out_norm, c.eps, want_q8=True)

@@ -101,11 +101,41 @@ def test_pipeline_stages_match_single_process(tiny_qwen3_path, tmp_path, world):
     assert covered == list(range(n_layers))
 
 
+@pytest.mark.parametrize("family", ["gptoss", "qwen35", "nemotron", "gemma3"])
+def test_other_families_pipeline_stages_match_single_process(tmp_path, family):
+    """The mixture-of-experts family (sliding windows follow the global layer index, the last layer's last-token
+    shortcut runs on the last stage only) and the two families with recurrent layers (state slots live with their
+    layers' stage) over two stages."""
+    from tensorsharp_b200.models import synth
+    from tensorsharp_b200.models.base import ModelBase
+    from tensorsharp_b200.runtime.engine import generate
+    p = str(tmp_path / "m.gguf")
+    if family == "gptoss":
+        synth.write_gptoss(p, n_layers=3, device="cpu")
+    elif family == "qwen35":
+        synth.write_qwen35(p, device="cpu")
+    elif family == "gemma3":
+        synth.write_gemma(p, arch="gemma3", device="cpu")
+    else:
+        synth.write_nemotron_h(p, device="cpu")
+    g = torch.Generator().manual_seed(6)
+    prompt = torch.randint(0, 4096, (21,), generator=g).tolist()
+    single = ModelBase.create(p, "cpu", max_context=128)
+    want = generate(single, prompt, 5)
+    has_kv = [k is not None for k in single.kv.k]
+    out = str(tmp_path / "pp_moe.pt")
+    mp.spawn(_pp_worker, args=(2, _free_port(), p, prompt, 5, out), nprocs=2, join=True)
+    for r in range(2):
+        toks, held, (l0, l1), _, has_head = torch.load(f"{out}.{r}")
+        assert toks == want and has_head == (r == 1)
+        assert held == [has_kv[l] and l0 <= l < l1 for l in range(single.cfg.n_layers)]
+
+
 def test_pipeline_rejects_models_without_a_stage_path(tmp_path):
     from tensorsharp_b200.models import synth
     from tensorsharp_b200.models.base import ModelBase
     p = str(tmp_path / "g.gguf")
-    synth.write_gptoss(p, device="cpu")
+    synth.write_gemma(p, arch="gemma4", device="cpu")
     with pytest.raises(ValueError):
         ModelBase.create(p, "cpu", max_context=64, pp_rank=0, pp_size=2)
 
