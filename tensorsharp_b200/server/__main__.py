@@ -87,6 +87,35 @@ def load_startup_model(options, svc, configured_backend, log) -> None:
         log.info(Ev.HostConfiguration, "Kernel warmup completed in {ElapsedMs:.1f} ms", ElapsedMs=(time.perf_counter() - t0) * 1e3)
 
 
+def run_replicated(argv, options) -> int:
+    """``--replicas N``: N server processes (one per GPU) and the routing front end on the public address."""
+    from .replicas import Router, serve_front, spawn_replicas, stop_replicas
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        print("error: --replicas starts its own processes; do not combine it with torch.distributed.run", file=sys.stderr)
+        return 2
+    backend = try_resolve_supported_backend(options, read_configured_backend_input(argv))[0] or "cpu"
+    log_dir = options.log_directory if options.file_logging_enabled else None
+    if log_dir:
+        os.makedirs(log_dir, exist_ok=True)
+    import signal
+
+    def on_term(signum, frame):                  # end like Ctrl-C so that the replica processes are stopped too
+        raise KeyboardInterrupt
+    signal.signal(signal.SIGTERM, on_term)
+    replicas = spawn_replicas(argv, options.replicas, use_gpus=backend != "cpu", log_dir=log_dir)
+    front = serve_front(Router(replicas), options.host, options.port)
+    print(f"{len(replicas)} replicas ready ({', '.join(str(r.port) for r in replicas)}); listening on "
+          f"http://{options.host}:{front.server_address[1]}", flush=True)
+    try:
+        front.serve_forever()
+    except KeyboardInterrupt:
+        pass
+    finally:
+        front.server_close()
+        stop_replicas(replicas)
+    return 0
+
+
 def main(argv=None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     base = os.environ.get("TENSORSHARP_BASE_DIR") or os.getcwd()
@@ -95,6 +124,8 @@ def main(argv=None) -> int:
     except ValueError as e:
         print(f"error: {e}", file=sys.stderr)
         return 2
+    if options.replicas > 1:
+        return run_replicated(argv, options)
     # Tensor-parallel serving: started as ``python -m torch.distributed.run --nproc-per-node N -m tensorsharp_b200.server ...``
     # every process holds one shard; rank 0 runs the HTTP front end and announces each model call, the others mirror it.
     comm = None

@@ -11,7 +11,7 @@ Hosting/HostedModelGuard.cs.
 Backends here are ``b200`` (the sm_100a kernels) and ``cpu`` (the fp32 oracle path); the
 reference's names ``cuda`` / ``ggml_cuda`` are accepted as aliases of ``b200`` and
 ``ggml_cpu`` of ``cpu`` so existing launch scripts keep working.  This build adds
-``--host --port --max-context --max-sessions --max-batch`` (tensor parallelism comes from the
+``--host --port --max-context --max-sessions --max-batch --replicas`` (tensor parallelism comes from the
 process count of the launch).
 """
 from __future__ import annotations
@@ -80,6 +80,7 @@ class ServerHostingOptions:
     max_context: Optional[int] = None
     max_sessions: int = 1
     max_batch: int = 1                 # requests that run together (their model calls share steps)
+    replicas: int = 1                  # server processes (one per GPU) behind the one address
     web_root: Optional[str] = None
 
     @property
@@ -136,7 +137,7 @@ def parse_args(args: Sequence[str]) -> Dict[str, object]:
     out: Dict[str, object] = {"sampling": {}, "stop": None}
     plain = (("--model", "model"), ("--mmproj", "mmproj"), ("--backend", "backend"), ("--host", "host"))
     ints = (("--port", "port"), ("--max-context", "max_context"), ("--max-sessions", "max_sessions"),
-            ("--max-batch", "max_batch"))
+            ("--max-batch", "max_batch"), ("--replicas", "replicas"))
     i = 0
     while i < len(args):
         matched = False
@@ -235,7 +236,8 @@ def build_options(args: Sequence[str], base_directory: str, env=None,
         host=p.get("host") or env.get("TENSORSHARP_HOST") or "127.0.0.1",
         port=int(p.get("port") or _pos_int(env.get("PORT")) or 5000),
         max_context=p.get("max_context"), max_sessions=int(p.get("max_sessions") or 1),
-        max_batch=int(p.get("max_batch") or _pos_int(env.get("TENSORSHARP_MAX_BATCH")) or 1))
+        max_batch=int(p.get("max_batch") or _pos_int(env.get("TENSORSHARP_MAX_BATCH")) or 1),
+        replicas=int(p.get("replicas") or _pos_int(env.get("TENSORSHARP_REPLICAS")) or 1))
 
 
 def read_configured_backend_input(args: Sequence[str], env=None) -> Optional[str]:
