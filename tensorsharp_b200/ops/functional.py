@@ -548,29 +548,50 @@ def causal_conv1d(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
     return torch.cat(outs, 0)
 
 
+def _gdn_chunk_min() -> int:
+    """Prompts of at least this many tokens take the chunked form of the recurrence (the reference's
+    GDN_CHUNK_PREFILL_MIN_SEQ_LEN, default 64; GDN_DISABLE_CHUNKED_PREFILL=1 keeps the token-by-token scan)."""
+    import os
+    if os.environ.get("GDN_DISABLE_CHUNKED_PREFILL", "0") not in ("", "0"):
+        return 1 << 62
+    return max(2, int(os.environ.get("GDN_CHUNK_PREFILL_MIN_SEQ_LEN", "64") or 64))
+
+
 def gdn(qkv: torch.Tensor, z: torch.Tensor, beta: torch.Tensor, alpha: torch.Tensor, dt_bias, a_log, norm_w,
         state: torch.Tensor, batch: Batch, *, Hk: int, Hv: int, Dk: int, Dv: int, eps: float) -> torch.Tensor:
-    """GatedDeltaNet recurrence over the packed tokens -> gated output [T, Hv*Dv]."""
-    if qkv.is_cuda:
+    """GatedDeltaNet recurrence over the packed tokens -> gated output [T, Hv*Dv].  Decode steps and short prompts
+    run the token-by-token scan (one kernel on CUDA); prompts of ``_gdn_chunk_min()`` tokens or more run the chunked
+    form (matrix products over heads x chunks) on CPU, and on CUDA when ``TSB_GDN_CHUNKED=1``."""
+    import os
+    chunk_min = _gdn_chunk_min()
+    chunked = batch.max_q_len >= chunk_min and (not qkv.is_cuda or os.environ.get("TSB_GDN_CHUNKED", "0") == "1")
+    if qkv.is_cuda and not chunked:
         return _k().gdn_recurrent(qkv, z, beta, alpha, dt_bias, a_log, norm_w, state, batch.cu_q, batch.seq_slots,
                                   Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=eps)
     outs = []
     slots = batch.seq_slots.tolist()
     for b in range(batch.B):
         q0, q1 = batch.h_cu_q[b], batch.h_cu_q[b + 1]
-        outs.append(ref.gdn_recurrent(qkv[q0:q1], z[q0:q1], beta[q0:q1], alpha[q0:q1], dt_bias, a_log, norm_w,
-                                      state[slots[b]], Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=eps))
-    return torch.cat(outs, 0)
+        args = (qkv[q0:q1], z[q0:q1], beta[q0:q1], alpha[q0:q1], dt_bias, a_log, norm_w, state[slots[b]])
+        if chunked:                             # every sequence of a batch that took this route, short ones included
+            outs.append(ref.gdn_chunked(*args, Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=eps))
+        else:
+            outs.append(ref.gdn_recurrent(*args, Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=eps))
+    return torch.cat(outs, 0).to(torch.bfloat16 if qkv.is_cuda else torch.float32)     # the kernel's output types
 
 
 def mamba2(xbc: torch.Tensor, dt: torch.Tensor, dt_bias, A, D, state: torch.Tensor, batch: Batch, *, H: int, P: int,
            G: int, N: int) -> torch.Tensor:
-    """Mamba2 selective scan over the packed tokens -> y f32 [T, H*P] (before gating)."""
-    if xbc.is_cuda:
+    """Mamba2 selective scan over the packed tokens -> y f32 [T, H*P] (before gating).  Prompts of
+    ``_gdn_chunk_min()`` tokens or more take the chunked form on CPU, and on CUDA when ``TSB_MAMBA_CHUNKED=1``."""
+    import os
+    chunked = batch.max_q_len >= _gdn_chunk_min() and (not xbc.is_cuda or os.environ.get("TSB_MAMBA_CHUNKED", "0") == "1")
+    if xbc.is_cuda and not chunked:
         return _k().mamba2_recurrent(xbc, dt, dt_bias, A, D, state, batch.cu_q, batch.seq_slots, H=H, P=P, G=G, N=N)
     outs = []
     slots = batch.seq_slots.tolist()
+    scan = ref.mamba2_chunked if chunked else ref.mamba2_recurrent
     for b in range(batch.B):
         q0, q1 = batch.h_cu_q[b], batch.h_cu_q[b + 1]
-        outs.append(ref.mamba2_recurrent(xbc[q0:q1], dt[q0:q1], dt_bias, A, D, state[slots[b]], H=H, P=P, G=G, N=N))
+        outs.append(scan(xbc[q0:q1], dt[q0:q1], dt_bias, A, D, state[slots[b]], H=H, P=P, G=G, N=N))
     return torch.cat(outs, 0)

@@ -164,6 +164,58 @@ def gdn_recurrent(qkv, z, beta, alpha, dt_bias, a_log, norm_w, state, *, Hk, Hv,
     return out
 
 
+def gdn_chunked(qkv, z, beta, alpha, dt_bias, a_log, norm_w, state, *, Hk, Hv, Dk, Dv, eps, chunk: int = 64):
+    """The recurrence of :func:`gdn_recurrent` in chunked form (Qwen35Model.cs:888-1192 does its prefill the same way):
+    inside a chunk of ``chunk`` tokens the delta-rule updates are solved at once as a unit lower-triangular system
+    (the WY form), so the work is matrix products over (heads x chunks) and only three small products per chunk run
+    in sequence to carry the state.  One sequence; ``state`` [Hv, Dv, Dk] is updated in place; plain tensor ops, so it
+    runs on whichever device the inputs live on.  Returns [n, Hv*Dv]."""
+    n = qkv.shape[0]
+    dev = qkv.device
+    C = chunk
+    nc = (n + C - 1) // C
+    pad = nc * C - n
+    hk = torch.arange(Hv, device=dev) % Hk
+    q = qkv[:, :Hk * Dk].float().view(n, Hk, Dk)[:, hk]                    # [n, Hv, Dk]
+    k = qkv[:, Hk * Dk:2 * Hk * Dk].float().view(n, Hk, Dk)[:, hk]
+    v = qkv[:, 2 * Hk * Dk:].float().view(n, Hv, Dv)
+    q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + eps) * (Dv ** -0.5)
+    k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + eps)
+    g = torch.nn.functional.softplus(alpha.float() + dt_bias.float()) * a_log.float()      # [n, Hv], log of the decay
+    b = torch.sigmoid(beta.float())                                                         # [n, Hv]
+
+    def chunks(t):                      # [n, Hv, ...] -> [Hv, nc, C, ...]; padded tokens change nothing (zero k, v, beta, g)
+        if pad:
+            t = torch.cat([t, t.new_zeros((pad,) + tuple(t.shape[1:]))], 0)
+        return t.view(nc, C, *t.shape[1:]).movedim(2, 0)
+    Q, K, V = chunks(q), chunks(k), chunks(v)
+    G, B = chunks(g), chunks(b)                                              # [Hv, nc, C]
+    cum = G.cumsum(-1)
+    tril = torch.ones(C, C, dtype=torch.bool, device=dev).tril()
+    M = torch.where(tril, torch.exp((cum.unsqueeze(-1) - cum.unsqueeze(-2)).clamp(max=0.0)), torch.zeros((), device=dev))
+    KK = K @ K.transpose(-1, -2)
+    A = (B.unsqueeze(-1) * KK * M).tril(-1)                                  # strictly lower: token i sees tokens j < i
+    lhs = A + torch.eye(C, device=dev)
+    decay = torch.exp(cum).unsqueeze(-1)                                     # decay from the chunk's start to each token
+    U0 = torch.linalg.solve_triangular(lhs, B.unsqueeze(-1) * V, upper=False, unitriangular=True)          # [.., C, Dv]
+    W = torch.linalg.solve_triangular(lhs, B.unsqueeze(-1) * decay * K, upper=False, unitriangular=True)   # [.., C, Dk]
+    P = (Q @ K.transpose(-1, -2)) * M
+    Qd = Q * decay
+    Kd = K * torch.exp(cum[..., -1:] - cum).unsqueeze(-1)
+    gamma = torch.exp(cum[..., -1])                                          # [Hv, nc]
+    S = state.float()
+    outs = []
+    for c in range(nc):
+        St = S.transpose(-1, -2)                                             # [Hv, Dk, Dv]
+        U = U0[:, c] - W[:, c] @ St
+        outs.append(Qd[:, c] @ St + P[:, c] @ U)                             # [Hv, C, Dv]
+        S = gamma[:, c].view(Hv, 1, 1) * S + U.transpose(-1, -2) @ Kd[:, c]
+    state.copy_(S)
+    core = torch.stack(outs, 1).reshape(Hv, nc * C, Dv)[:, :n].transpose(0, 1)          # [n, Hv, Dv]
+    core = core * torch.rsqrt(core.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float()
+    return (core * torch.nn.functional.silu(z.float().view(n, Hv, Dv))).reshape(n, Hv * Dv)
+
+
 def mamba2_recurrent(xbc, dt, dt_bias, A, D, state, *, H, P, G, N):
     """One sequence.  state [H, P, N] updated in place.  Returns y [n, H*P] (before gating)."""
     n = xbc.shape[0]
@@ -181,3 +233,44 @@ def mamba2_recurrent(xbc, dt, dt_bias, A, D, state, *, H, P, G, N):
             yy = yy + D.float().view(H, 1) * x
         y[t] = yy.reshape(-1)
     return y
+
+
+def mamba2_chunked(xbc, dt, dt_bias, A, D, state, *, H, P, G, N, chunk: int = 64):
+    """:func:`mamba2_recurrent` in chunked (state-space duality) form: inside a chunk the outputs are one masked
+    matrix product ``(decay * C B^T) (dt * x)``, the state is carried from chunk to chunk by two small products.
+    One sequence; ``state`` [H, P, N] is updated in place; runs on the inputs' device.  Returns y [n, H*P]."""
+    n = xbc.shape[0]
+    dev = xbc.device
+    Cn = chunk
+    nc = (n + Cn - 1) // Cn
+    pad = nc * Cn - n
+    grp = torch.arange(H, device=dev) // (H // G)
+    x = xbc[:, :H * P].float().view(n, H, P)
+    Bm = xbc[:, H * P:H * P + G * N].float().view(n, G, N)[:, grp]           # [n, H, N]
+    Cm = xbc[:, H * P + G * N:].float().view(n, G, N)[:, grp]
+    d = torch.nn.functional.softplus(dt.float() + (dt_bias.float() if dt_bias is not None else 0.0))    # [n, H]
+    la = d * A.float()                                                        # log of the per-token decay
+
+    def chunks(t):                      # [n, H, ...] -> [H, nc, Cn, ...]; padded tokens: zero input, decay 1
+        if pad:
+            t = torch.cat([t, t.new_zeros((pad,) + tuple(t.shape[1:]))], 0)
+        return t.view(nc, Cn, *t.shape[1:]).movedim(2, 0)
+    X, Bc, Cc = chunks(x * d.unsqueeze(-1)), chunks(Bm), chunks(Cm)
+    cum = chunks(la).cumsum(-1)                                               # [H, nc, Cn]
+    tril = torch.ones(Cn, Cn, dtype=torch.bool, device=dev).tril()
+    M = torch.where(tril, torch.exp((cum.unsqueeze(-1) - cum.unsqueeze(-2)).clamp(max=0.0)), torch.zeros((), device=dev))
+    Y_in = ((Cc @ Bc.transpose(-1, -2)) * M) @ X                              # contributions from inside the chunk
+    Cd = Cc * torch.exp(cum).unsqueeze(-1)                                    # reads of the incoming state
+    Xd = X * torch.exp(cum[..., -1:] - cum).unsqueeze(-1)                     # writes that survive to the chunk's end
+    gamma = torch.exp(cum[..., -1])
+    S = state.float()                                                         # [H, P, N]
+    outs = []
+    for c in range(nc):
+        outs.append(Y_in[:, c] + Cd[:, c] @ S.transpose(-1, -2))              # [H, Cn, P]
+        S = gamma[:, c].view(H, 1, 1) * S + Xd[:, c].transpose(-1, -2) @ Bc[:, c]
+    state.copy_(S)
+    y = torch.stack(outs, 1).reshape(H, nc * Cn, P)[:, :n].transpose(0, 1)    # [n, H, P]
+    if D is not None:
+        y = y + D.float().view(1, H, 1) * x
+    return y.reshape(n, H * P)
+

@@ -91,3 +91,60 @@ def test_gemma4_prefill_chunk_policy(tmp_path, monkeypatch):
     m.reset_kv_cache()
     whole = m.forward(toks)
     assert torch.allclose(chunked, whole, atol=3e-2)              # 16-row chunks take the int8-activation path
+
+
+def test_gdn_chunked_form_matches_the_token_scan(tmp_path, monkeypatch):
+    """The chunked (WY) form of the gated delta rule against the token-by-token recurrence: the op alone on ragged
+    lengths, then a Qwen3.5-shaped model whose 150-token prompt takes the chunked route and whose decode step
+    continues from the state it left."""
+    from tensorsharp_b200.ops import reference as ref
+    torch.manual_seed(0)
+    Hk, Hv, Dk, Dv = 2, 4, 16, 8
+    for n in (1, 63, 64, 65, 200):
+        qkv, z = torch.randn(n, 2 * Hk * Dk + Hv * Dv), torch.randn(n, Hv * Dv)
+        beta, alpha, dt_bias = torch.randn(n, Hv), torch.randn(n, Hv), torch.randn(Hv)
+        a_log, norm_w = -torch.rand(Hv) * 2, torch.rand(Dv) + 0.5
+        s1 = torch.randn(Hv, Dv, Dk) * 0.3
+        s2 = s1.clone()
+        kw = dict(Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=1e-6)
+        o1 = ref.gdn_recurrent(qkv, z, beta, alpha, dt_bias, a_log, norm_w, s1, **kw)
+        o2 = ref.gdn_chunked(qkv, z, beta, alpha, dt_bias, a_log, norm_w, s2, chunk=64, **kw)
+        assert torch.allclose(o1, o2, atol=1e-4) and torch.allclose(s1, s2, atol=1e-5), n
+    p = str(tmp_path / "q35.gguf")
+    synth.write_qwen35(p, device="cpu")
+    g = torch.Generator().manual_seed(8)
+    toks = torch.randint(0, 4096, (150,), generator=g).tolist()
+    out = {}
+    for mode in ("chunked", "scan"):
+        monkeypatch.setenv("GDN_DISABLE_CHUNKED_PREFILL", "0" if mode == "chunked" else "1")
+        m = ModelBase.create(p, "cpu", max_context=256)
+        l1 = m.forward(toks)
+        out[mode] = (l1, m.forward([int(l1.argmax())]))
+    assert torch.allclose(out["chunked"][0], out["scan"][0], atol=2e-3)
+    assert torch.allclose(out["chunked"][1], out["scan"][1], atol=2e-3)
+
+
+def test_mamba2_chunked_form_matches_the_token_scan(tmp_path, monkeypatch):
+    from tensorsharp_b200.ops import reference as ref
+    torch.manual_seed(1)
+    H, P, G, N = 4, 8, 2, 16
+    for n in (1, 63, 64, 65, 200):
+        xbc, dt, dtb = torch.randn(n, H * P + 2 * G * N), torch.randn(n, H), torch.randn(H)
+        A, D = -torch.rand(H) * 2, torch.randn(H)
+        s1 = torch.randn(H, P, N) * 0.3
+        s2 = s1.clone()
+        y1 = ref.mamba2_recurrent(xbc, dt, dtb, A, D, s1, H=H, P=P, G=G, N=N)
+        y2 = ref.mamba2_chunked(xbc, dt, dtb, A, D, s2, H=H, P=P, G=G, N=N)
+        assert torch.allclose(y1, y2, atol=5e-4) and torch.allclose(s1, s2, atol=1e-4), n
+    p = str(tmp_path / "nem.gguf")
+    synth.write_nemotron_h(p, device="cpu")
+    g = torch.Generator().manual_seed(9)
+    toks = torch.randint(0, 4096, (150,), generator=g).tolist()
+    out = {}
+    for mode in ("chunked", "scan"):
+        monkeypatch.setenv("GDN_DISABLE_CHUNKED_PREFILL", "0" if mode == "chunked" else "1")
+        m = ModelBase.create(p, "cpu", max_context=256)
+        l1 = m.forward(toks)
+        out[mode] = (l1, m.forward([int(l1.argmax())]))
+    assert torch.allclose(out["chunked"][0], out["scan"][0], atol=2e-3)
+    assert torch.allclose(out["chunked"][1], out["scan"][1], atol=2e-3)

@@ -1,0 +1,55 @@
+"""The chunked forms of the GatedDeltaNet and Mamba2 recurrences on the GPU (tensor ops, opt-in by environment)
+against the token-by-token kernels."""
+import pytest
+import torch
+
+from tensorsharp_b200.ops import functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+def _batch(lens, dev):
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    T = cu[-1]
+    z = torch.zeros(T, dtype=torch.int32)
+    return F.Batch(tokens=z.to(dev), positions=z.to(dev), slots=torch.zeros(T, dtype=torch.int64, device=dev),
+                   cu_q=torch.tensor(cu, dtype=torch.int32, device=dev),
+                   kv_lens=torch.tensor(lens, dtype=torch.int32, device=dev), block_table=None, last_idx=None,
+                   seq_slots=torch.tensor([1, 0][:len(lens)], dtype=torch.int64, device=dev), max_q_len=max(lens),
+                   max_kv_len=max(lens), is_decode=False, page_size=16, h_cu_q=tuple(cu), h_kv_lens=tuple(lens))
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-6))
+
+
+def test_chunked_routes_match_the_scan_kernels(monkeypatch):
+    torch.manual_seed(0)
+    lens = [200, 70]
+    T = sum(lens)
+    dev = "cuda"
+    Hk, Hv, Dk, Dv = 2, 4, 64, 64
+    qkv = torch.randn(T, 2 * Hk * Dk + Hv * Dv, device=dev)
+    z, beta, alpha = torch.randn(T, Hv * Dv, device=dev), torch.randn(T, Hv, device=dev), torch.randn(T, Hv, device=dev)
+    dtb, a_log, nw = torch.randn(Hv, device=dev) * 0.5, -torch.rand(Hv, device=dev), torch.rand(Dv, device=dev) + 0.5
+    s0 = torch.randn(2, Hv, Dv, Dk, device=dev) * 0.1
+    outs, states = {}, {}
+    for mode in ("0", "1"):
+        monkeypatch.setenv("TSB_GDN_CHUNKED", mode)
+        st = s0.clone()
+        outs[mode] = F.gdn(qkv, z, beta, alpha, dtb, a_log, nw, st, _batch(lens, dev), Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=1e-6)
+        states[mode] = st
+    assert outs["1"].dtype == outs["0"].dtype
+    assert _rel(outs["1"], outs["0"]) < 2e-2 and _rel(states["1"], states["0"]) < 1e-3
+    H, P, G, N = 4, 64, 2, 64
+    xbc, dt = torch.randn(T, H * P + 2 * G * N, device=dev), torch.randn(T, H, device=dev)
+    A, D, dtb = -torch.rand(H, device=dev), torch.randn(H, device=dev), torch.randn(H, device=dev) * 0.5
+    s0 = torch.randn(2, H, P, N, device=dev) * 0.1
+    for mode in ("0", "1"):
+        monkeypatch.setenv("TSB_MAMBA_CHUNKED", mode)
+        st = s0.clone()
+        outs[mode] = F.mamba2(xbc, dt, dtb, A, D, st, _batch(lens, dev), H=H, P=P, G=G, N=N)
+        states[mode] = st
+    assert _rel(outs["1"], outs["0"]) < 1e-3 and _rel(states["1"], states["0"]) < 1e-3
