@@ -12,7 +12,6 @@ from __future__ import annotations
 
 import os
 import signal
-import sys
 import time
 from typing import Callable, List, Optional, Tuple
 

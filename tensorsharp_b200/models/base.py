@@ -17,7 +17,6 @@ from typing import Callable, Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from ..gguf.constants import GGMLType
 from ..gguf.reader import GGUFFile
 from ..ops import functional as F
 from ..ops.functional import Batch

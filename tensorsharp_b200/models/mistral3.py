@@ -9,11 +9,9 @@ RoPEEx mode 0 (adjacent pairs) with ext_factor / beta_fast / beta_slow and attn_
 from __future__ import annotations
 
 import math
-from typing import Optional
 
 import torch
 
-from ..ops import functional as F
 from ..ops.functional import Batch, RopeSpec
 from ..ops.kernels import yarn_corr_dims
 from .base import register_architecture

@@ -19,9 +19,7 @@ from typing import Optional
 import torch
 
 from ..ops import functional as F
-from ..ops import reference as ref
 from ..ops.functional import Batch
-from ..quant.qweight import QuantWeight
 from .base import ModelBase, register_architecture
 
 

@@ -12,7 +12,7 @@ and the output / tied embedding matrix (Q6_K).  Norms and biases are F32.
 from __future__ import annotations
 
 import math
-from typing import Dict, List, Optional
+from typing import Optional
 
 import torch
 

@@ -12,7 +12,6 @@ from typing import Optional
 
 import torch
 
-from ..gguf.constants import GGMLType
 from ..quant.qweight import QuantWeight
 from . import native
 

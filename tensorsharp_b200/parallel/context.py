@@ -10,7 +10,6 @@ context path is single-device (Gemma4Model.cs:593-637 chunked prefill).
 from __future__ import annotations
 
 import ctypes as C
-from typing import Optional
 
 import torch
 

@@ -1,4 +1,4 @@
-"""Serving a tensor-parallel model from one front end.
+"""Serving a model that spans several processes (tensor, pipeline or context parallel) from one front end.
 
 The HTTP server, the CLI's interactive mode and the queue live on rank 0 only; the other ranks hold their
 shards and must make exactly the calls rank 0 makes, in the same order, or the collectives and in-kernel
@@ -13,9 +13,8 @@ reference serves from a single process on a single device and has no counterpart
 """
 from __future__ import annotations
 
-from typing import Any, Callable, Dict, List, Optional, Sequence
+from typing import Any, Callable, Dict, Optional, Sequence
 
-import torch
 
 
 def _bcast(comm, obj: Any = None) -> Any:
@@ -92,6 +91,25 @@ class LeaderModel:
         close = getattr(self._model, "close", None)
         if close is not None:
             close()
+
+
+def layout_create(mode: str) -> Optional[Callable]:
+    """The ``create`` callable (for :func:`leader_factory` / :func:`follower_main`) of a parallel layout: ``tp`` cuts the
+    weights across the ranks (the default, ``None``), ``pp`` gives each rank a range of layers, ``cp`` gives every rank
+    the whole model and deals long prompts to them slice by slice."""
+    mode = (mode or "tp").lower()
+    if mode == "tp":
+        return None
+    if mode not in ("pp", "cp"):
+        raise ValueError(f"unknown parallel layout {mode!r} (tp, pp or cp)")
+
+    def create(path, device, *, tp_rank=0, tp_size=1, comm=None, **kw):
+        from ..models.base import ModelBase
+        if mode == "cp":
+            return ModelBase.create(path, device, cp_comm=comm, **kw)
+        from .pipeline import PipelinedModel
+        return PipelinedModel(ModelBase.create(path, device, pp_rank=comm.rank, pp_size=comm.size, pp_comm=comm, **kw))
+    return create
 
 
 def leader_factory(comm, create: Optional[Callable] = None) -> Callable:

@@ -8,8 +8,7 @@ and therefore token ids match the reference byte for byte.
 """
 from __future__ import annotations
 
-import json
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Dict, List, Optional
 
 

@@ -16,7 +16,7 @@ seeds reproduce runs of this engine, not of the reference).
 from __future__ import annotations
 
 import random
-from dataclasses import dataclass, field, replace
+from dataclasses import dataclass, replace
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch

@@ -127,22 +127,24 @@ def main(argv=None) -> int:
         return 2
     if options.replicas > 1:
         return run_replicated(argv, options)
-    # Tensor-parallel serving: started as ``python -m torch.distributed.run --nproc-per-node N -m tensorsharp_b200.server ...``
-    # every process holds one shard; rank 0 runs the HTTP front end and announces each model call, the others mirror it.
+    # A model over several processes: started as ``python -m torch.distributed.run --nproc-per-node N -m tensorsharp_b200.server ...``
+    # every process holds its part (``--parallel tp`` weight shards, ``pp`` layer ranges, ``cp`` whole copies that share long
+    # prompts); rank 0 runs the HTTP front end and announces each model call, the others mirror it.
     comm = None
     if int(os.environ.get("WORLD_SIZE", "1")) > 1:
         from ..parallel.dist import init_from_env
-        from ..parallel.replicated import follower_main, leader_factory, shutdown_followers
+        from ..parallel.replicated import follower_main, layout_create, leader_factory, shutdown_followers
         cpu_only = (try_resolve_supported_backend(options, read_configured_backend_input(argv))[0] or "") == "cpu"
         comm = init_from_env("gloo" if cpu_only else None)
+        create = layout_create(options.parallel)
         if comm.rank != 0:
-            follower_main(comm)
+            follower_main(comm, create=create)
             return 0
     provider = setup_file_logging(options.log_directory, prefix="tensorsharp-server", enabled=options.file_logging_enabled)
     svc = None
     if comm is not None:
         from .model_service import ModelService
-        svc = ModelService(None, model_factory=leader_factory(comm), max_context=options.max_context,
+        svc = ModelService(None, model_factory=leader_factory(comm, create), max_context=options.max_context,
                            max_sessions=options.max_sessions)
     app = ServerApp(options, svc=svc, log_provider=provider)
     log = app.logger("TensorSharp.Server")

@@ -23,7 +23,6 @@ import email
 import email.policy
 import json
 import os
-import threading
 import time
 import uuid
 from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer

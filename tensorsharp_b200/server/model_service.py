@@ -20,7 +20,7 @@ import time
 from typing import Iterator, List, NamedTuple, Optional, Sequence
 
 from ..runtime import media
-from ..runtime.chat import ChatMessage, ToolFunction, dotnet_json
+from ..runtime.chat import ChatMessage, ToolFunction
 from ..runtime.kv_cache import ReusePlanKind
 from ..runtime.logging import Ev, NULL_LOGGER, log_scope
 from ..runtime.prompt_renderer import GgufPromptRenderer, KVCachePromptRenderer

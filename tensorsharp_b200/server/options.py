@@ -11,7 +11,7 @@ Hosting/HostedModelGuard.cs.
 Backends here are ``b200`` (the sm_100a kernels) and ``cpu`` (the fp32 oracle path); the
 reference's names ``cuda`` / ``ggml_cuda`` are accepted as aliases of ``b200`` and
 ``ggml_cpu`` of ``cpu`` so existing launch scripts keep working.  This build adds
-``--host --port --max-context --max-sessions --max-batch --replicas`` (tensor parallelism comes from the
+``--host --port --max-context --max-sessions --max-batch --replicas --parallel`` (tensor parallelism comes from the
 process count of the launch).
 """
 from __future__ import annotations
@@ -81,6 +81,7 @@ class ServerHostingOptions:
     max_sessions: int = 1
     max_batch: int = 1                 # requests that run together (their model calls share steps)
     replicas: int = 1                  # server processes (one per GPU) behind the one address
+    parallel: str = "tp"               # layout of a model started under torch.distributed.run: tp, pp or cp
     web_root: Optional[str] = None
 
     @property
@@ -133,9 +134,17 @@ _SAMPLING_FLAGS = (
 )
 
 
+def _parallel_layout(v) -> str:
+    v = (str(v).strip().lower() if v else "tp")
+    if v not in ("tp", "pp", "cp"):
+        raise ValueError(f"--parallel must be tp, pp or cp, got '{v}'")
+    return v
+
+
 def parse_args(args: Sequence[str]) -> Dict[str, object]:
     out: Dict[str, object] = {"sampling": {}, "stop": None}
-    plain = (("--model", "model"), ("--mmproj", "mmproj"), ("--backend", "backend"), ("--host", "host"))
+    plain = (("--model", "model"), ("--mmproj", "mmproj"), ("--backend", "backend"), ("--host", "host"),
+             ("--parallel", "parallel"))
     ints = (("--port", "port"), ("--max-context", "max_context"), ("--max-sessions", "max_sessions"),
             ("--max-batch", "max_batch"), ("--replicas", "replicas"))
     i = 0
@@ -237,7 +246,8 @@ def build_options(args: Sequence[str], base_directory: str, env=None,
         port=int(p.get("port") or _pos_int(env.get("PORT")) or 5000),
         max_context=p.get("max_context"), max_sessions=int(p.get("max_sessions") or 1),
         max_batch=int(p.get("max_batch") or _pos_int(env.get("TENSORSHARP_MAX_BATCH")) or 1),
-        replicas=int(p.get("replicas") or _pos_int(env.get("TENSORSHARP_REPLICAS")) or 1))
+        replicas=int(p.get("replicas") or _pos_int(env.get("TENSORSHARP_REPLICAS")) or 1),
+        parallel=_parallel_layout(p.get("parallel") or env.get("TENSORSHARP_PARALLEL")))
 
 
 def read_configured_backend_input(args: Sequence[str], env=None) -> Optional[str]:

@@ -140,16 +140,21 @@ def test_pipeline_rejects_models_without_a_stage_path(tmp_path):
         ModelBase.create(p, "cpu", max_context=64, pp_rank=0, pp_size=2)
 
 
-def _serve_worker(rank, world, port, path, out_path):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+def _serve_worker(rank, world, port, path, out_path, mode="tp"):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), TSB_CP_MIN_TOKENS="4")
     import torch.distributed as dist
     from tensorsharp_b200.parallel.dist import Communicator
-    from tensorsharp_b200.parallel.replicated import follower_main, leader_factory, shutdown_followers
+    from tensorsharp_b200.parallel import replicated
+    from tensorsharp_b200.parallel.replicated import follower_main, layout_create, shutdown_followers
+    create = layout_create(mode)
+
+    def leader_factory(comm):
+        return replicated.leader_factory(comm, create)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     comm = Communicator(rank, world)
     try:
         if rank != 0:
-            n = follower_main(comm)
+            n = follower_main(comm, create=create)
             torch.save(n, f"{out_path}.{rank}")
             return
         from tensorsharp_b200.runtime.chat import ChatMessage
@@ -182,9 +187,11 @@ def _serve_worker(rank, world, port, path, out_path):
         dist.destroy_process_group()
 
 
-def test_front_end_on_rank0_with_follower_shards(tiny_qwen3_path, tmp_path):
-    """The model service runs on rank 0 only; the follower rank mirrors every call on its shard, so a
-    two-turn chat (prefill, decode, KV reuse on the second turn) gives the single-process text."""
+@pytest.mark.parametrize("mode", ["tp", "pp", "cp"])
+def test_front_end_on_rank0_with_follower_shards(tiny_qwen3_path, tmp_path, mode):
+    """The model service runs on rank 0 only; the follower rank mirrors every call on its part of the model (a weight
+    shard, a range of layers, or a whole copy that takes its slice of each prompt), so a two-turn chat (prefill,
+    decode, KV reuse on the second turn) gives the single-process text."""
     from tensorsharp_b200.runtime.chat import ChatMessage
     from tensorsharp_b200.runtime.sampling import SamplingConfig
     from tensorsharp_b200.server.model_service import ModelService
@@ -197,7 +204,7 @@ def test_front_end_on_rank0_with_follower_shards(tiny_qwen3_path, tmp_path):
     second = "".join(svc.chat_stream(hist, 5, sampling=greedy))
     svc.close()
     out = str(tmp_path / "serve.pt")
-    mp.spawn(_serve_worker, args=(2, _free_port(), tiny_qwen3_path, out), nprocs=2, join=True)
+    mp.spawn(_serve_worker, args=(2, _free_port(), tiny_qwen3_path, out, mode), nprocs=2, join=True)
     got = torch.load(f"{out}.0")
     assert got[:2] == (first, second)
     assert got[2] == first[:len(got[2])] or len(got[2]) > 0        # same prompt, fewer tokens: a prefix of the first answer
