@@ -229,6 +229,31 @@ class ModelBase:
             return False
         return batch.T >= max(self.cp_comm.size, int(os.environ.get("TSB_CP_MIN_TOKENS", "2048")))
 
+    def cp_sync_kv(self, layer: int) -> None:
+        """Called by attention blocks between the cache write and the attention.  During a context-parallel prefill it
+        completes this rank's cache of ``layer`` with the other ranks' slices; otherwise it does nothing."""
+        ctx = self.__dict__.get("_cp_ctx")
+        if ctx is not None:
+            from ..parallel.context import exchange_kv_shards
+            exchange_kv_shards(self.cp_comm, ctx[0], ctx[1], self.kv.k[layer], self.kv.v[layer])
+
+    def cp_run(self, batch, want_logits: bool, run):
+        """Context-parallel prefill for any model whose attention blocks call :meth:`cp_sync_kv`: ``run(sub)`` is the
+        model's ordinary forward on this rank's slice of the prompt (a batch of its own that sees the cache up to its
+        last position); the logits are those of the rank that holds the prompt's last token."""
+        from ..parallel.context import shard_batch, shard_bounds
+        cp = self.cp_comm
+        bounds = [shard_bounds(batch.T, cp.size, s) for s in range(cp.size)]
+        sub = shard_batch(batch, *bounds[cp.rank])
+        self.__dict__["_cp_ctx"] = (batch, bounds)
+        try:
+            logits = run(sub)
+        finally:
+            self.__dict__["_cp_ctx"] = None
+        if not want_logits:
+            return None
+        return cp.all_gather_list(logits.contiguous())[cp.size - 1]
+
     def cp_attention(self, n: int, Hkv: int, Dh: int):
         """The peer-memory attention of the context-parallel group for shards of ``n`` tokens (CUDA only,
         created on first use and regrown on demand; TSB_CP_FUSED=0 keeps the all-gather + local attention path)."""

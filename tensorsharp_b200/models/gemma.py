@@ -36,6 +36,7 @@ from .base import ModelBase, register_architecture
 
 class _GemmaBase(ModelBase):
     glu_act = "geglu"
+    supports_context_parallel = True
 
     # per-layer geometry, filled by parse_config
     def is_local(self, l: int) -> bool:
@@ -118,6 +119,8 @@ class _GemmaBase(ModelBase):
         qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=kc, v_cache=vc, rope=rope,
                               qn=L["q_norm"], kn=L["k_norm"], v_norm=v_norm, eps=c.eps, q_scale=1.0,
                               write_kv=write_kv)
+        if write_kv:
+            self.cp_sync_kv(kv_layer)
         o = F.attention(qr, kc, vc, batch, scale=scale, Hq=Hq, Hkv=Hkv, Dh=Dh, window=window)
         y = F.linear(F.as_act(o), L["wo"], out_dtype=torch.float32)
         if self.tp_size > 1:
@@ -158,6 +161,8 @@ class Gemma3Model(_GemmaBase):
     def forward_batch(self, batch: Batch, want_logits: bool = True) -> Optional[torch.Tensor]:
         c = self.cfg
         small = batch.T <= F.GEMV_MAX_M
+        if self.cp_wanted(batch) and self.__dict__.get("_cp_ctx") is None:
+            return self.cp_run(batch, want_logits, lambda sub: self.forward_batch(sub, want_logits))
         mid = torch.float32 if small else torch.bfloat16
         h = self.stage_input(batch, lambda: self.inject_pending_embeddings(
             F.embed(self.tok_emb, batch.tokens, scale=math.sqrt(c.hidden))))
@@ -290,6 +295,8 @@ class Gemma4Model(_GemmaBase):
     def forward_batch(self, batch: Batch, want_logits: bool = True) -> Optional[torch.Tensor]:
         c = self.cfg
         small = batch.T <= F.GEMV_MAX_M
+        if self.cp_wanted(batch) and self.__dict__.get("_cp_ctx") is None:
+            return self.cp_run(batch, want_logits, lambda sub: self.forward_batch(sub, want_logits))
         mid = torch.float32 if small else torch.bfloat16
         h = self.inject_pending_embeddings(F.embed(self.tok_emb, batch.tokens, scale=math.sqrt(c.hidden)))
         ple = self._ple(batch, h)

@@ -27,6 +27,7 @@ from .base import ModelBase, register_architecture
 @register_architecture("gpt-oss", "gptoss")
 class GptOssModel(ModelBase):
     supports_pipeline = True
+    supports_context_parallel = True
 
     def parse_config(self) -> None:
         g, a, c = self.gguf, self.arch, self.cfg
@@ -117,6 +118,7 @@ class GptOssModel(ModelBase):
                        proj(L["wv"], L["bv"]).view(T, Hkv, Dh))
         qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=self.kv.k[l], v_cache=self.kv.v[l],
                               rope=self.rope, eps=c.eps)
+        self.cp_sync_kv(l)
         return F.attention(qr, self.kv.k[l], self.kv.v[l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh,
                            window=self.window if l % 2 == 0 else 0, sinks=L["sinks"])
 
@@ -185,6 +187,8 @@ class GptOssModel(ModelBase):
         if self.pp_size > 1 and not self.is_first_stage:
             from ..parallel.pipeline import recv_hidden
             return self.run_layers(recv_hidden(self.pp_comm, self.pp_rank - 1, (T, c.hidden), self.device), batch, want_logits)
+        if self.cp_wanted(batch):
+            return self.cp_run(batch, want_logits, lambda sub: self.run_layers(F.embed(self.tok_emb, sub.tokens), sub, want_logits))
         h = F.embed(self.tok_emb, batch.tokens)
         if self.pp_size > 1:
             return self.run_layers(h, batch, want_logits)

@@ -67,12 +67,38 @@ def test_context_parallel_prefill_matches_single_process(tiny_qwen3_path, tmp_pa
         assert torch.allclose(l3, s3, atol=5e-3), r
 
 
+@pytest.mark.parametrize("family", ["gptoss", "gemma3", "gemma4"])
+def test_families_with_windows_sinks_and_shared_caches(tmp_path, family):
+    """The general route (each rank runs its slice through the model's ordinary layers, the cache of every layer is
+    completed between the cache write and the attention): sliding windows, attention sinks, experts, layers that read
+    another layer's cache and per-layer inputs all behave as in one process."""
+    from tensorsharp_b200.models import synth
+    from tensorsharp_b200.models.base import ModelBase
+    path = str(tmp_path / "m.gguf")
+    if family == "gptoss":
+        synth.write_gptoss(path, n_layers=3, device="cpu")
+    else:
+        synth.write_gemma(path, arch=family, device="cpu")
+    g = torch.Generator().manual_seed(12)
+    prompt = torch.randint(0, 4096, (45,), generator=g).tolist()
+    more = torch.randint(0, 4096, (7,), generator=g).tolist()
+    single = ModelBase.create(path, "cpu", max_context=128)
+    s1 = single.forward(prompt)
+    s2 = single.forward([int(s1.argmax())])
+    s3 = single.forward(more)
+    out = str(tmp_path / "cp.pt")
+    mp.spawn(_worker, args=(2, _free_port(), path, prompt, more, out), nprocs=2, join=True)
+    for r in range(2):
+        l1, l2, l3 = torch.load(f"{out}.{r}")
+        assert torch.allclose(l1, s1, atol=2e-2) and torch.allclose(l2, s2, atol=2e-2) and torch.allclose(l3, s3, atol=2e-2), r
+
+
 def test_models_without_the_path_refuse_the_group(tmp_path):
     from tensorsharp_b200.models.base import ModelBase
     from tensorsharp_b200.models import synth
     from tensorsharp_b200.parallel.dist import Communicator
     path = str(tmp_path / "g.gguf")
-    synth.write_gptoss(path, device="cpu")
+    synth.write_qwen35(path, device="cpu")
     with pytest.raises(ValueError, match="context-parallel"):
         ModelBase.create(path, "cpu", max_context=64, cp_comm=Communicator(0, 2))
 
