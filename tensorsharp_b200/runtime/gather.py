@@ -40,6 +40,14 @@ class GatheredModel:
         self.model_lock = threading.RLock()          # held while the graph runs and while a slot edits its cache
         self.steps = 0
         self.step_rows = 0
+        self.graph_steps = 0
+        # TSB_GATHER_GRAPH=1: steps in which every caller brings one token replay a captured graph (engine.py:
+        # BatchGraphStepper); off by default until it has been timed against the eager merged step
+        import os
+        self._stepper = None
+        if os.environ.get("TSB_GATHER_GRAPH", "0") == "1":
+            from .engine import BatchGraphStepper
+            self._stepper = BatchGraphStepper(model, n_slots)
         self._slots = [SlotModel(self, i) for i in range(n_slots)]
         self._thread = threading.Thread(target=self._run, name="tsb-gather", daemon=True)
         self._thread.start()
@@ -98,8 +106,13 @@ class GatheredModel:
             try:
                 with self.model_lock:
                     m = self.model
-                    batch = m.kv.build_batch([c.seq for c in calls], [c.tokens for c in calls])
-                    logits = m.forward_batch(batch, any(c.want for c in calls))
+                    logits = None
+                    if self._stepper is not None and all(len(c.tokens) == 1 for c in calls):
+                        logits = self._stepper.step([c.seq for c in calls], [c.tokens[0] for c in calls])
+                        self.graph_steps += logits is not None
+                    if logits is None:
+                        batch = m.kv.build_batch([c.seq for c in calls], [c.tokens for c in calls])
+                        logits = m.forward_batch(batch, any(c.want for c in calls))
                     if m.device.type == "cuda":
                         import torch
                         torch.cuda.synchronize(m.device)

@@ -258,3 +258,49 @@ def test_gathered_model_merges_threads_and_propagates_errors(tiny_qwen3_path):
     assert real.kv.free_pages > free_before                   # slots gave their sequences back
     with pytest.raises(RuntimeError):
         s1.forward([5])
+
+
+def test_batch_stepper_follows_changing_membership(tiny_qwen3_path, monkeypatch):
+    """Single-token steps of several sequences through the static batch of ``BatchGraphStepper`` (eager on CPU) give the
+    logits of the ordinary batched step while sequences join, leave and cross a page boundary; with TSB_GATHER_GRAPH=1
+    the merged steps of concurrent callers go through it."""
+    import threading
+
+    from tensorsharp_b200.models.base import ModelBase
+    from tensorsharp_b200.runtime.engine import BatchGraphStepper, generate
+    from tensorsharp_b200.runtime.gather import GatheredModel
+    a = ModelBase.create(tiny_qwen3_path, "cpu", max_context=256, max_seqs=4, page_size=16)
+    b = ModelBase.create(tiny_qwen3_path, "cpu", max_context=256, max_seqs=4, page_size=16)
+    st = BatchGraphStepper(a, 3)
+    gen = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(5, 4000, (n,), generator=gen).tolist() for n in (13, 30, 7)]
+    sa, sb = [a.new_sequence() for _ in prompts], [b.new_sequence() for _ in prompts]
+    for m, seqs in ((a, sa), (b, sb)):
+        for s, p in zip(seqs, prompts):
+            m.forward_batch(m.kv.build_batch([s], [p]), False)
+    members = [[0, 1, 2], [0, 1, 2], [0, 2], [2], [1, 2, 0], [1, 0]] + [[0, 1, 2]] * 6        # sequence 0 crosses position 16
+    for step, idx in enumerate(members):
+        toks = [100 + step + i for i in idx]
+        got = st.step([sa[i] for i in idx], toks)
+        want = b.forward_batch(b.kv.build_batch([sb[i] for i in idx], [[t] for t in toks]), True)
+        assert got is not None and torch.allclose(got, want, atol=1e-5), step
+        assert [sa[i].length for i in idx] == [sb[i].length for i in idx]
+    assert st.step([sa[0]] * 4, [1, 2, 3, 4]) is None                   # more sequences than the stepper was sized for
+    # through the gatherer
+    monkeypatch.setenv("TSB_GATHER_GRAPH", "1")
+    real = ModelBase.create(tiny_qwen3_path, "cpu", max_context=128, max_seqs=4)
+    g = GatheredModel(real, 3, window_s=0.05)
+    eos = [t for t in range(real.cfg.vocab) if real.tokenizer.is_eos(t)]
+    got = {}
+
+    def worker(i):
+        with g.slot(i) as m:
+            got[i] = generate(m, prompts[i], 6, eos_ids=eos, prefill_chunk=8)
+    ths = [threading.Thread(target=worker, args=(i,)) for i in range(3)]
+    [t.start() for t in ths]
+    [t.join(timeout=120) for t in ths]
+    assert g.graph_steps > 0
+    for i, p in enumerate(prompts):
+        real.reset_kv_cache()
+        assert got[i] == generate(real, p, 6, eos_ids=eos)
+    g.close()
