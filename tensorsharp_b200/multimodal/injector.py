@@ -317,3 +317,37 @@ class MultimodalInjector:
                     setter(s.entry.embeddings.clone(), s.insert_position - reusable_prefix)
                 queued = True
         return queued
+
+
+class SlotInjector(MultimodalInjector):
+    """The injector of one request slot when several requests share a loaded model: its own prepared spans and its
+    own queue (``model`` is the slot, whose ``set_vision_embeddings`` travels with the slot's next forward call), the
+    encoders and the embedding caches of the shared model's injector."""
+
+    def __init__(self, slot, shared: MultimodalInjector):
+        super().__init__(slot)
+        self.__dict__["_shared"] = shared
+        self._vision_cache, self._audio_cache = shared._vision_cache, shared._audio_cache
+
+    @property
+    def vision(self):
+        return self._shared.vision
+
+    @vision.setter
+    def vision(self, value):               # the base constructor's ``self.vision = None``: the encoders live on the shared injector
+        pass
+
+    @property
+    def audio(self):
+        return self._shared.audio
+
+    @audio.setter
+    def audio(self, value):
+        pass
+
+    def load_projectors(self, path: str) -> None:
+        self._shared.load_projectors(path)
+
+    def unload(self) -> None:
+        self.clear_prepared()
+

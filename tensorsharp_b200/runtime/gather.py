@@ -19,10 +19,10 @@ from typing import List, Optional, Sequence
 
 
 class _Call:
-    __slots__ = ("seq", "tokens", "want", "done", "result", "error")
+    __slots__ = ("seq", "tokens", "want", "embeddings", "done", "result", "error")
 
-    def __init__(self, seq, tokens, want):
-        self.seq, self.tokens, self.want = seq, tokens, want
+    def __init__(self, seq, tokens, want, embeddings=None):
+        self.seq, self.tokens, self.want, self.embeddings = seq, tokens, want, embeddings
         self.done = threading.Event()
         self.result = None
         self.error: Optional[BaseException] = None
@@ -65,8 +65,8 @@ class GatheredModel:
             self._busy = max(0, self._busy - 1)
             self._cv.notify_all()
 
-    def submit(self, seq, tokens: Sequence[int], want: bool):
-        c = _Call(seq, list(tokens), want)
+    def submit(self, seq, tokens: Sequence[int], want: bool, embeddings=None):
+        c = _Call(seq, list(tokens), want, embeddings)
         with self._cv:
             if self._stop:
                 raise RuntimeError("the model has been closed")
@@ -103,28 +103,39 @@ class GatheredModel:
                     c.error = RuntimeError("the model has been closed")
                     c.done.set()
                 return
-            try:
-                with self.model_lock:
-                    m = self.model
-                    logits = None
-                    if self._stepper is not None and all(len(c.tokens) == 1 for c in calls):
-                        logits = self._stepper.step([c.seq for c in calls], [c.tokens[0] for c in calls])
-                        self.graph_steps += logits is not None
-                    if logits is None:
-                        batch = m.kv.build_batch([c.seq for c in calls], [c.tokens for c in calls])
-                        logits = m.forward_batch(batch, any(c.want for c in calls))
-                    if m.device.type == "cuda":
-                        import torch
-                        torch.cuda.synchronize(m.device)
-                self.steps += 1
-                self.step_rows += len(calls)
-                for i, c in enumerate(calls):
-                    c.result = logits[i] if (c.want and logits is not None) else None
-            except BaseException as e:                     # hand the failure to every caller of this step
-                for c in calls:
-                    c.error = e
+            # a call that carries image / audio embeddings runs by itself (the spans are positions of its own prompt);
+            # all the others share one step
+            alone = [c for c in calls if c.embeddings]
+            shared = [c for c in calls if not c.embeddings]
+            for group in [[c] for c in alone] + ([shared] if shared else []):
+                self._step(group)
             for c in calls:
                 c.done.set()
+
+    def _step(self, calls: List[_Call]) -> None:
+        try:
+            with self.model_lock:
+                m = self.model
+                logits = None
+                if calls[0].embeddings:
+                    for emb, pos in calls[0].embeddings:
+                        m.set_vision_embeddings(emb, pos)
+                elif self._stepper is not None and all(len(c.tokens) == 1 for c in calls):
+                    logits = self._stepper.step([c.seq for c in calls], [c.tokens[0] for c in calls])
+                    self.graph_steps += logits is not None
+                if logits is None:
+                    batch = m.kv.build_batch([c.seq for c in calls], [c.tokens for c in calls])
+                    logits = m.forward_batch(batch, any(c.want for c in calls))
+                if m.device.type == "cuda":
+                    import torch
+                    torch.cuda.synchronize(m.device)
+            self.steps += 1
+            self.step_rows += len(calls)
+            for i, c in enumerate(calls):
+                c.result = logits[i] if (c.want and logits is not None) else None
+        except BaseException as e:                     # hand the failure to every caller of this step
+            for c in calls:
+                c.error = e
 
     def close(self) -> None:
         with self._cv:
@@ -145,6 +156,8 @@ class SlotModel:
         self.__dict__["_owner"] = owner
         self.__dict__["_index"] = index
         self.__dict__["_seq"] = None
+        self.__dict__["_pending"] = []
+        self.__dict__["_injector"] = None
 
     # configuration, tokenizer, architecture ... come from the shared model
     def __getattr__(self, name):
@@ -158,14 +171,28 @@ class SlotModel:
 
     @property
     def multimodal(self):
-        return None                       # attachments are not routed through shared steps
+        """This slot's injector (its own prepared spans and queue) over the encoders the shared model has loaded;
+        ``None`` for text-only architectures."""
+        shared = self._owner.model.multimodal
+        if shared is None:
+            return None
+        if self._injector is None:
+            from ..multimodal.injector import SlotInjector
+            self.__dict__["_injector"] = SlotInjector(self, shared)
+        return self._injector
+
+    def set_vision_embeddings(self, embeddings, insert_position: int) -> None:
+        self._pending.append((embeddings, int(insert_position)))
+
+    set_audio_embeddings = set_vision_embeddings
 
     @property
     def cache_length(self) -> int:
         return self._seq.length if self._seq is not None else 0
 
     def forward(self, tokens: Sequence[int], want_logits: bool = True):
-        return self._owner.submit(self._sequence(), tokens, want_logits)
+        emb, self.__dict__["_pending"] = self._pending, []
+        return self._owner.submit(self._sequence(), tokens, want_logits, emb or None)
 
     def forward_refill(self, tokens: Sequence[int], chunk: int = 2048):
         tokens = list(tokens)

@@ -46,8 +46,10 @@ class ServicePool:
         b = canonicalize_backend(backend) or "cpu"
         real = make(model_path, backend_device(b if b in ("b200", "cpu") else "cpu"), **kw)
         previous, self._gather = self._gather, GatheredModel(real, self._n)
-        for s in self._slots:
-            s.load_model(model_path, None, backend)        # each service lets go of its old slot and takes the new one
+        for i, s in enumerate(self._slots):
+            # each service lets go of its old slot and takes the new one; the first one also loads the multimodal
+            # projector, once, into the shared model's injector (the other slots find the encoders there)
+            s.load_model(model_path, mmproj_path if i == 0 else None, backend)
         if previous is not None:
             previous.close()
 
@@ -69,7 +71,7 @@ class ServicePool:
 
     @property
     def loaded_mmproj_name(self):
-        return None
+        return self._slots[0].loaded_mmproj_name
 
     @property
     def loaded_backend(self):

@@ -396,3 +396,52 @@ def test_model_injects_pending_embeddings(tiny_qwen3_path):
     assert not torch.allclose(m.forward(toks), base, atol=1e-3) and m._pending_embeddings == []
     assert m.multimodal is None
     m.close()
+
+
+def test_slots_of_a_shared_model_carry_their_own_embeddings(tiny_qwen3_path, tmp_path):
+    """With several requests over one loaded model, a slot's queued image embeddings travel with that slot's next
+    forward call (run by itself, not merged), another slot's text-only call is untouched, and the slot's injector
+    uses the encoders and caches of the shared model's injector."""
+    import threading
+
+    from tensorsharp_b200.models.base import ModelBase
+    from tensorsharp_b200.runtime.gather import GatheredModel
+    single = ModelBase.create(tiny_qwen3_path, "cpu", max_context=64)
+    toks = [5, 6, 7, 8, 9, 10, 11]
+    plain = single.forward(toks).clone()
+    single.reset_kv_cache()
+    emb = torch.randn(3, single.cfg.hidden) * 0.1
+    single.set_vision_embeddings(emb, 2)
+    with_img = single.forward(toks).clone()
+    assert not torch.allclose(plain, with_img, atol=1e-3)
+    real = ModelBase.create(tiny_qwen3_path, "cpu", max_context=64, max_seqs=3)
+    g = GatheredModel(real, 2, window_s=0.05)
+    out = {}
+
+    def with_image():
+        with g.slot(0) as m:
+            m.set_vision_embeddings(emb, 2)
+            out["img"] = m.forward(toks)
+
+    def text_only():
+        with g.slot(1) as m:
+            out["txt"] = m.forward(toks)
+    ths = [threading.Thread(target=f) for f in (with_image, text_only)]
+    [t.start() for t in ths]
+    [t.join(60) for t in ths]
+    assert torch.allclose(out["img"], with_img, atol=1e-4) and torch.allclose(out["txt"], plain, atol=1e-4)
+    assert real._pending_embeddings == [] and g.slot(0).multimodal is None          # a text-only architecture has no injector
+    g.close()
+    # the slot injector: own spans and queue, shared encoders and caches
+    shared_model = FakeModel("qwen35", {"<|image_pad|>": 77})
+    shared = J.MultimodalInjector(shared_model)
+    shared.vision = FakeVision()
+    slot = FakeModel("qwen35", {"<|image_pad|>": 77})
+    inj = J.SlotInjector(slot, shared)
+    a = save_png(tmp_path / "a.png", 64, 64)
+    hist = [ChatMessage(role="user", content="x", image_paths=[a])]
+    assert inj.process_prompt_tokens(hist, [1, 77, 2]) == [1] + [77] * 6 + [2]
+    assert inj.vision is shared.vision and shared.vision.calls == 1 and shared.vision_spans == []
+    assert inj.queue_prompt_embeddings(0) and slot.queued == [("v", 6, 1)] and shared_model.queued == []
+    shared.process_prompt_tokens(hist, [1, 77, 2])
+    assert shared.vision.calls == 1                                                 # the encoding came from the common cache
