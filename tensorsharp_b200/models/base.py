@@ -151,7 +151,9 @@ class ModelBase:
     def set_vision_embeddings(self, embeddings: torch.Tensor, insert_position: int) -> None:
         """Queue ``embeddings`` ``[n, hidden]`` to replace the token embeddings of rows
         ``[insert_position, insert_position + n)`` of the next forward call (SetVisionEmbeddings /
-        SetAudioEmbeddings of the reference's multimodal models)."""
+        SetAudioEmbeddings of the reference's multimodal models).  Only the pipeline stage that embeds tokens keeps them."""
+        if self.pp_size > 1 and not self.is_first_stage:
+            return
         self._pending_embeddings.append((embeddings, int(insert_position)))
 
     set_audio_embeddings = set_vision_embeddings

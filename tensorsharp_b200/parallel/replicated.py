@@ -80,9 +80,22 @@ class LeaderModel:
         self._tell("bind_seq", seq.seq_id if seq is not None else None)
         self._model.bind_sequence(seq)
 
-    # ------------------------------------------------------------------ what the followers cannot mirror
-    def set_vision_embeddings(self, *a, **k):
-        raise NotImplementedError("multimodal inputs are not supported with a tensor-parallel front end")
+    # ------------------------------------------------------------------ image / audio embeddings
+    @property
+    def multimodal(self):
+        """The injector runs on rank 0 only (it owns the encoders); its embeddings reach the model through
+        :meth:`set_vision_embeddings` below, which also hands them to the followers."""
+        if self._model.multimodal is None:
+            return None
+        inj = self.__dict__.get("_injector")
+        if inj is None:
+            from ..multimodal.injector import MultimodalInjector
+            inj = self.__dict__["_injector"] = MultimodalInjector(self)
+        return inj
+
+    def set_vision_embeddings(self, embeddings, insert_position: int) -> None:
+        self._tell("embed", embeddings.detach().float().cpu(), int(insert_position))
+        self._model.set_vision_embeddings(embeddings, insert_position)
 
     set_audio_embeddings = set_vision_embeddings
 
@@ -153,6 +166,8 @@ def follower_main(comm, create: Optional[Callable] = None, device=None) -> int:
             raise RuntimeError(f"follower received {op!r} before a model was loaded")
         elif op == "forward":
             model.forward(args[0], args[1])
+        elif op == "embed":
+            model.set_vision_embeddings(args[0].to(model.device), args[1])
         elif op == "warm_up":
             model.warm_up_kernels()
         elif op == "reset":

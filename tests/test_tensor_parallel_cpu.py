@@ -240,3 +240,38 @@ def test_cli_over_pipeline_stages(tiny_qwen3_path, tmp_path):
     rc1, out1, _ = torch.load(f"{res}.1")
     assert rc0 == 0 and rc1 == 0, err0
     assert out0 == out.getvalue() and out1 == ""
+
+
+def _embed_worker(rank, world, port, path, mode, out_path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    from tensorsharp_b200.parallel.dist import Communicator
+    from tensorsharp_b200.parallel.replicated import follower_main, layout_create, leader_factory, shutdown_followers
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    comm = Communicator(rank, world)
+    try:
+        create = layout_create(mode)
+        if rank != 0:
+            follower_main(comm, create=create)
+            return
+        m = leader_factory(comm, create)(path, "cpu", max_context=64)
+        torch.manual_seed(3)
+        m.set_vision_embeddings(torch.randn(3, m.cfg.hidden) * 0.1, 2)
+        out = m.forward([5, 6, 7, 8, 9, 10, 11]).clone()
+        m.close()
+        shutdown_followers(comm)
+        torch.save(out, out_path)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", ["tp", "pp"])
+def test_leader_hands_image_embeddings_to_the_followers(tiny_qwen3_path, tmp_path, mode):
+    from tensorsharp_b200.models.base import ModelBase
+    single = ModelBase.create(tiny_qwen3_path, "cpu", max_context=64)
+    torch.manual_seed(3)
+    single.set_vision_embeddings(torch.randn(3, single.cfg.hidden) * 0.1, 2)
+    want = single.forward([5, 6, 7, 8, 9, 10, 11])
+    out = str(tmp_path / "emb.pt")
+    mp.spawn(_embed_worker, args=(2, _free_port(), tiny_qwen3_path, mode, out), nprocs=2, join=True)
+    assert torch.allclose(torch.load(out), want, atol=5e-3)
