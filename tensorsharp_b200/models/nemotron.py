@@ -67,6 +67,11 @@ class NemotronHModel(ModelBase):
         c = self.cfg
         self.tok_emb, self.out_norm, self.lm_head = self.stage_tensors()
         self.l0, l1 = self.layer_range
+        # expert parallelism: each rank of the group keeps a contiguous range of the routed experts (everything else is
+        # replicated); the experts' contributions are summed over the group
+        from ..parallel.dist import even_split
+        ep, er = (self.ep_size, self.ep_rank) if self.ep_size > 1 else (self.tp_size, self.tp_rank)
+        self.e0, self.e1 = even_split(self.n_experts, ep, er) if self.n_experts else (0, 0)
         self.layers = []
         S = max(self.max_seqs, 1)
         xbc = self.d_inner + 2 * self.n_group * self.d_state
@@ -94,6 +99,8 @@ class NemotronHModel(ModelBase):
                 b = self.f32(p + "exp_probs_b.bias", optional=True)
                 L["router_bias"] = b if b is not None else self.f32(p + "exp_probs_b", optional=True)
                 L["up_exps"], L["down_exps"] = self.qw(p + "ffn_up_exps.weight"), self.qw(p + "ffn_down_exps.weight")
+                if self.e1 - self.e0 != self.n_experts:
+                    L["up_exps"], L["down_exps"] = (w.expert_range(self.e0, self.e1) for w in (L["up_exps"], L["down_exps"]))
                 L["latent_in"] = self.qw(p + "ffn_latent_in.weight", optional=True)
                 L["latent_out"] = self.qw(p + "ffn_latent_out.weight", optional=True)
                 L["sh_up"] = self.qw(p + "ffn_up_shexp.weight", optional=True)
@@ -145,7 +152,9 @@ class NemotronHModel(ModelBase):
         x = a
         if L["latent_in"] is not None:
             x = F.as_act(F.linear(a, L["latent_in"], out_dtype=torch.float32))
-        y = F.moe_experts(x, ids, w, L["up_exps"], L["down_exps"], act="relu2")
+        y = F.moe_experts(x, ids, w, L["up_exps"], L["down_exps"], act="relu2", expert_offset=self.e0)
+        if self.e1 - self.e0 != self.n_experts and self.comm is not None:
+            self.comm.all_reduce(y)
         if L["latent_out"] is not None:
             y = F.linear(F.as_act(y), L["latent_out"], out_dtype=torch.float32)
         if L["sh_up"] is not None:

@@ -60,6 +60,33 @@ def test_tp2_matches_single_rank(tiny_qwen3_path, tmp_path):
     assert torch.allclose(l1, s1, atol=5e-3) and torch.allclose(l2, s2, atol=5e-3)
 
 
+@pytest.mark.parametrize("family", ["gptoss", "qwen35", "nemotron", "gemma3", "gemma4"])
+def test_other_families_shard_over_two_ranks(tmp_path, family):
+    """Head / FFN shards (Gemma, GPT-OSS attention) and expert ranges (GPT-OSS, Qwen3.5, Nemotron-H, Gemma 4) on two gloo
+    ranks give the logits of one process, for a prompt and a decode step."""
+    from tensorsharp_b200.models import synth
+    from tensorsharp_b200.models.base import ModelBase
+    p = str(tmp_path / "m.gguf")
+    if family == "gptoss":
+        synth.write_gptoss(p, n_layers=2, device="cpu")
+    elif family == "qwen35":
+        synth.write_qwen35(p, device="cpu")
+    elif family == "nemotron":
+        synth.write_nemotron_h(p, device="cpu")
+    else:
+        synth.write_gemma(p, arch=family, device="cpu")
+    g = torch.Generator().manual_seed(7)
+    prompt = torch.randint(0, 4096, (19,), generator=g).tolist()
+    single = ModelBase.create(p, "cpu", max_context=128)
+    s1 = single.forward(prompt)
+    s2 = single.forward([int(s1.argmax())])
+    out = str(tmp_path / "tp.pt")
+    mp.spawn(_worker, args=(2, _free_port(), p, prompt, out), nprocs=2, join=True)
+    l1, l2 = torch.load(out)
+    scale = float(s1.abs().max())
+    assert float((l1 - s1).abs().max()) < 2e-2 * scale and float((l2 - s2).abs().max()) < 2e-2 * scale
+
+
 def _pp_worker(rank, world, port, path, prompt, n_new, out_path):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     import torch.distributed as dist
