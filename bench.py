@@ -37,7 +37,12 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=None, help="sequences decoded together (default: 1; gptoss-20b: 64)")
     ap.add_argument("--prefill", type=int, default=None, help="prompt tokens per sequence (default: 2048; gptoss-20b: 1024)")
-    ap.add_argument("--model", default="qwen3-4b", choices=["qwen3-4b", "qwen3-tiny", "gptoss-20b", "gptoss-tiny", "qwen35-35b-a3b"])
+    ap.add_argument("--model", default="qwen3-4b", choices=["qwen3-4b", "qwen3-tiny", "gptoss-20b", "gptoss-tiny", "qwen35-35b-a3b",
+                                                           "gemma4-31b", "gemma-tiny"])
+    ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],
+                    help="cpu: the tiny Qwen3 config on the CPU backend (prompt 64, 32 greedy tokens, wall clock)")
+    ap.add_argument("--reuse-prefix", type=int, default=None,
+                    help="gemma configs: tokens of the first turn's cache that the second turn keeps (default 30000 of 32768 + 512)")
     ap.add_argument("--prefill-repeats", type=int, default=3, help="timed prefill repetitions (median reported)")
     ap.add_argument("--no-graph", action="store_true", help="run decode steps eagerly (for kernel-level profiling)")
     ap.add_argument("--trace", default=None, metavar="FILE",
@@ -48,7 +53,9 @@ def parse_args():
     if a.batch is None:
         a.batch = {"gptoss-20b": 64, "qwen35-35b-a3b": 8}.get(a.model, 1)
     if a.prefill is None:
-        a.prefill = {"gptoss-20b": 1024, "qwen35-35b-a3b": 8192}.get(a.model, 2048)
+        a.prefill = {"gptoss-20b": 1024, "qwen35-35b-a3b": 8192, "gemma4-31b": 32768, "gemma-tiny": 96}.get(a.model, 2048)
+    if a.reuse_prefix is None:
+        a.reuse_prefix = {"gemma4-31b": 30000, "gemma-tiny": 80}.get(a.model)
     return a
 
 
@@ -114,6 +121,10 @@ MODEL_SHAPES = {
     "qwen35-35b-a3b": dict(n_layers=40, hidden=2048, n_heads=16, n_kv_heads=2, head_dim=256, rope_dims=64, interval=4,
                            hk=16, hv=32, dk=128, dv=128, conv_k=4, n_experts=256, top_k=8, expert_ffn=512, shared_ffn=512,
                            ffn=6144, vocab=151936, scheme="Q4_K_M"),
+    "gemma4-31b": dict(arch="gemma3", n_layers=60, hidden=5376, n_heads=32, n_kv_heads=16, head_dim=128, ffn=21504, vocab=262144,
+                       window=1024, scheme="Q8_0", softcap=30.0),
+    "gemma-tiny": dict(arch="gemma3", n_layers=6, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512, vocab=4096,
+                       window=16, scheme="Q8_0", softcap=30.0),
 }
 MODEL_TEXT = {
     "qwen3-4b": ("Qwen3-4B-shaped Q4_K_M (36L, hidden 2560, 32q/8kv x128, ffn 9728, vocab 151936), random-init",
@@ -129,6 +140,11 @@ MODEL_TEXT = {
                        "attention 16q/2kv x256, 256 experts top-8 + shared, expert ffn 512, vocab 151936), random-init",
                        "bf16 activations / f32 accumulate, Q4_K_M weights as stored",
                        "weights (about 20 GB) exceed the 126 MB L2; no flush needed"),
+    "gemma4-31b": ("Gemma-4-31B-class dense Q8_0 (60L, hidden 5376, 32q/16kv x128, GeGLU 21504, 5 sliding(1024) : 1 global, "
+                   "logit softcap, vocab 262144), random-init",
+                   "bf16 activations / f32 accumulate, Q8_0 weights as stored", "weights (about 28 GB) exceed the 126 MB L2; no flush needed"),
+    "gemma-tiny": ("tiny Gemma 3 Q8_0 (6L, hidden 256, window 16), random-init", "bf16 activations / f32 accumulate, Q8_0 weights as stored",
+                   "tiny model: smoke configuration only"),
     "gptoss-tiny": ("tiny gpt-oss (2L, hidden 256, 8 experts top-2), random-init",
                     "bf16 activations / f32 accumulate, MXFP4 expert weights as stored", "tiny model: smoke configuration only"),
 }
@@ -143,7 +159,8 @@ def ensure_model(args, rank: int, world: int) -> str:
     if rank == 0 and not os.path.exists(done):
         from tensorsharp_b200.models import synth
         writer = (synth.write_gptoss if args.model.startswith("gptoss") else
-                  synth.write_qwen35 if args.model.startswith("qwen35") else synth.write_qwen3)
+                  synth.write_qwen35 if args.model.startswith("qwen35") else
+                  synth.write_gemma if args.model.startswith("gemma") else synth.write_qwen3)
         writer(path, **MODEL_SHAPES[args.model], seed=0, device="cuda" if torch.cuda.is_available() else "cpu")
         open(done, "w").write("ok")
     if world > 1:
@@ -291,11 +308,29 @@ def run_ours(args) -> dict:
 
     if args.trace and rank == 0:
         trace_step(dg, args.trace)
-    vals = torch.tensor([dev_ms, e2e_ms, prefill_ms, e2e_wall_ms], dtype=torch.float64, device=dev)
+
+    # ---- second turn (long-context configs): keep a prefix of the first turn's cache, prefill what follows it
+    turn2_ms, turn2_new = 0.0, 0
+    if args.reuse_prefix and B == 1:
+        seq = seqs[0]
+        total = seq.length
+        keep = min(args.reuse_prefix, total - 1)
+        tail = (prompts[0] + [int(t) % model.cfg.vocab for t in range(total)])[keep:total]      # same length as the turn it replaces
+        turn2_new = len(tail)
+        dg.graph = None                                # the captured steps hold this sequence's pages
+        model.kv.truncate(seq, keep)
+        barrier()
+        e0.record()
+        F.argmax(model.forward_batch(model.kv.build_batch([seq], [tail])))
+        e1.record()
+        barrier()
+        turn2_ms = e0.elapsed_time(e1)
+
+    vals = torch.tensor([dev_ms, e2e_ms, prefill_ms, e2e_wall_ms, turn2_ms], dtype=torch.float64, device=dev)
     if world > 1:
         import torch.distributed as dist
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms, prefill_ms, e2e_wall_ms = vals.tolist()
+    dev_ms, e2e_ms, prefill_ms, e2e_wall_ms, turn2_ms = vals.tolist()
     status = int(kernels.gemm_status(dev).item())
     res = {
         "metric": "decode tok/s (device-timed, max over ranks); prefill tok/s and p50 TTFT alongside",
@@ -304,7 +339,7 @@ def run_ours(args) -> dict:
         "dtype": MODEL_TEXT[args.model][1], "data": "synthetic",
         "impl": "ours",
         "config": {"model": MODEL_TEXT[args.model][0], "global_batch": B, "seq_len": P, "decode_steps": K,
-                   "parallelism": (f"tp{world}" if args.model.startswith("qwen3-") else f"tp{world} attention + ep{world} experts"),
+                   "parallelism": (f"tp{world}" if args.model.startswith(("qwen3-", "gemma")) else f"tp{world} attention + ep{world} experts"),
                    "l2": MODEL_TEXT[args.model][2],
                    "prefill_weights": "GEMMs of the prefill read a bf16 copy of each quantised matrix, decoded once at first use "
                                       "and kept in spare HBM (TSB_BF16_WEIGHT_CACHE_GB); decode streams the GGUF blocks"},
@@ -312,6 +347,8 @@ def run_ours(args) -> dict:
         "e2e": {"value": B * K / (max(e2e_ms, e2e_wall_ms) / 1e3), "unit": "tok/s", "h2d_bytes_per_step": 4 * B,
                 "d2h_bytes_per_step": 4 * B, "ms_per_step_device": e2e_ms / K, "ms_per_step_wall": e2e_wall_ms / K},
         "gpu_launches": (dg.launches_per_step or launches_eager) * K,
+        "second_turn": ({"kv_reused_tokens": int(args.reuse_prefix), "new_tokens": turn2_new, "ttft_ms": turn2_ms}
+                        if turn2_new else None),
         "kernel_status": status,
         "clocks": clock_info,
     }
@@ -334,6 +371,45 @@ def run_ours(args) -> dict:
     return res if rank == 0 else None
 
 
+def run_cpu(args) -> dict:
+    """The tiny Qwen3 configuration on the CPU backend (the fp32 oracle of every op): batch 1, a 64-token prompt,
+    32 greedy decode tokens, wall clock.  No GPU is touched."""
+    import torch
+    from tensorsharp_b200.models import synth
+    from tensorsharp_b200.models.base import ModelBase
+    if args.model != "qwen3-tiny":
+        raise SystemExit("--device cpu runs the qwen3-tiny configuration only")
+    os.makedirs(args.cache_dir, exist_ok=True)
+    path = os.path.join(args.cache_dir, "qwen3-tiny-cpu.gguf")
+    if not os.path.exists(path + ".done"):
+        synth.write_qwen3(path, **MODEL_SHAPES["qwen3-tiny"], seed=0, device="cpu")
+        open(path + ".done", "w").write("ok")
+    P, K, W = 64, 32, max(3, args.warmup)
+    model = ModelBase.create(path, "cpu", max_context=P + K + W + 8)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, model.cfg.vocab, (P,), generator=g).tolist()
+
+    def one_run():
+        model.reset_kv_cache()
+        t0 = time.perf_counter()
+        logits = model.forward(prompt)
+        t1 = time.perf_counter()
+        ids = []
+        for _ in range(K):
+            ids.append(int(logits.argmax()))
+            logits = model.forward([ids[-1]])
+        return (t1 - t0) * 1e3, (time.perf_counter() - t1) * 1e3, ids
+    for _ in range(W):
+        one_run()
+    runs = sorted(one_run()[:2] for _ in range(3))
+    prefill_ms, decode_ms = runs[1]
+    return {"metric": "decode tok/s (CPU backend, wall clock); prefill tok/s alongside", "value": K / (decode_ms / 1e3), "unit": "tok/s",
+            "n_gpus": 0, "steps": K, "warmup": W, "ms_per_step": decode_ms / K, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "fp32 oracle, Q8_0 weights as stored", "data": "synthetic", "impl": "ours", "device": "cpu",
+            "config": {"model": MODEL_TEXT["qwen3-tiny"][0], "global_batch": 1, "seq_len": P, "decode_steps": K, "parallelism": "none"},
+            "prefill_tok_s": P / (prefill_ms / 1e3), "ttft_ms_p50": prefill_ms, "gpu_launches": 0}
+
+
 def run_reference(args) -> dict:
     try:
         from baseline.ref_harness import run as ref_run
@@ -344,6 +420,11 @@ def run_reference(args) -> dict:
             return None
         return {"impl": "reference", "unavailable": "the reference runs Qwen3.5 through its C# per-op graph (Qwen35Model.cs) with the recurrent "
                                                     "step on the host; no .NET SDK exists on this box"}
+    if args.model.startswith("gemma"):
+        if int(os.environ.get("RANK", "0")) != 0:
+            return None
+        return {"impl": "reference", "unavailable": "the reference runs Gemma through its C# per-op graph (Gemma3Model.cs / Gemma4Model.cs); "
+                                                    "no .NET SDK exists on this box"}
     if args.model.startswith("gptoss"):
         if int(os.environ.get("RANK", "0")) != 0:
             return None
@@ -358,7 +439,12 @@ def main():
     if dump:          # diagnostics: print every thread's Python stack if the run is still going after N seconds
         import faulthandler
         faulthandler.dump_traceback_later(float(dump), repeat=False, exit=True)
-    res = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.device == "cpu" and args.impl == "reference":
+        res = {"impl": "reference", "unavailable": "the reference's CPU backend is its C# code; no .NET SDK exists on this box"}
+    elif args.device == "cpu":
+        res = run_cpu(args)
+    else:
+        res = run_reference(args) if args.impl == "reference" else run_ours(args)
     if res is not None:
         print(json.dumps(res), flush=True)
 

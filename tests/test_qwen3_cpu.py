@@ -53,3 +53,20 @@ def test_generate_and_benchmark(tiny_qwen3_path):
     r = run_benchmark(m, prefill=8, decode=4, runs=2)
     assert len(r) == 2 and r[0].decode_tokens == 4 and r[0].prefill_tps > 0
     assert synthetic_prompt(20, 50)[:3] == [49, 49, 49] and synthetic_prompt(3, 4096) == [100, 101, 102]
+
+
+def test_bench_cpu_configuration_prints_one_json_line(tmp_path):
+    """``bench.py --model qwen3-tiny --device cpu``: the tiny configuration on the CPU backend (prompt 64, 32 greedy tokens)."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--model", "qwen3-tiny", "--device", "cpu",
+                        "--cache-dir", str(tmp_path)], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    r = json.loads(p.stdout.strip().splitlines()[-1])
+    assert r["device"] == "cpu" and r["steps"] == 32 and r["config"]["seq_len"] == 64 and r["value"] > 0 and r["prefill_tok_s"] > 0
+    p = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--model", "qwen3-tiny", "--device", "cpu", "--impl", "reference"],
+                       capture_output=True, text=True, timeout=600)
+    assert json.loads(p.stdout.strip().splitlines()[-1])["impl"] == "reference"
