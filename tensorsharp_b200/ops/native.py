@@ -151,5 +151,27 @@ def check(rc: int, what: str = "") -> None:
         raise NativeLibraryError(f"{what or 'native call'} failed (code {rc}): {msg}")
 
 
+def main(argv: Optional[List[str]] = None) -> int:
+    """``python -m tensorsharp_b200.ops.native [--force] [--tests] [--jobs N] [--quiet]``: build the library (and the
+    stand-alone test programs) from the command line, as the reference's ``build-linux.sh --cuda --tests`` does for its
+    native bridge.  The target is always sm_100a."""
+    import argparse
+    ap = argparse.ArgumentParser(description="Build the sm_100a library in place")
+    ap.add_argument("--force", action="store_true", help="recompile every source")
+    ap.add_argument("--tests", action="store_true", help="also build the stand-alone C++ test programs")
+    ap.add_argument("--jobs", type=int, default=None, help="parallel compiler processes (default: min(8, cores))")
+    ap.add_argument("--quiet", action="store_true")
+    a = ap.parse_args(argv)
+    try:
+        path = build(force=a.force, verbose=not a.quiet, jobs=a.jobs)
+        built = [path] + (build_tests(force=a.force) if a.tests else [])
+    except NativeLibraryError as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 1
+    for b in built:
+        print(b)
+    return 0
+
+
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose=True))
+    sys.exit(main())
