@@ -142,7 +142,6 @@ def can_fuse(x: torch.Tensor, w: QuantWeight) -> bool:
     TSB_FUSED_GEMV=1: on B200 the in-CTA prologue measured slower than the separate norm /
     quantise launches (Qwen3-4B decode 3.8 ms per step against 2.6 ms), because redoing the
     prologue per CTA costs more L2 traffic and occupancy than the two launches it removes."""
-    import os
     return (os.environ.get("TSB_FUSED_GEMV", "0") == "1" and x.is_cuda and x.numel() // x.shape[-1] <= FUSED_MAX_M
             and w.K % 32 == 0 and w.K <= 10240 and w.experts == 1)
 
@@ -356,7 +355,6 @@ def decode_splits(batch: Batch, Hkv: int, window: int) -> int:
     """Split-KV factor for decode attention: enough CTAs to cover the GPU's 148 SMs."""
     span = batch.max_kv_len if not window else min(batch.max_kv_len, window)
     want = max(1, (148 * 2) // max(1, batch.B * Hkv))
-    import os
     per = int(os.environ.get("TSB_ATTN_SPLIT_LEN", "128"))
     return int(max(1, min(want, (span + per - 1) // per, 64)))
 
@@ -551,7 +549,6 @@ def causal_conv1d(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
 def _gdn_chunk_min() -> int:
     """Prompts of at least this many tokens take the chunked form of the recurrence (the reference's
     GDN_CHUNK_PREFILL_MIN_SEQ_LEN, default 64; GDN_DISABLE_CHUNKED_PREFILL=1 keeps the token-by-token scan)."""
-    import os
     if os.environ.get("GDN_DISABLE_CHUNKED_PREFILL", "0") not in ("", "0"):
         return 1 << 62
     return max(2, int(os.environ.get("GDN_CHUNK_PREFILL_MIN_SEQ_LEN", "64") or 64))
@@ -562,7 +559,6 @@ def gdn(qkv: torch.Tensor, z: torch.Tensor, beta: torch.Tensor, alpha: torch.Ten
     """GatedDeltaNet recurrence over the packed tokens -> gated output [T, Hv*Dv].  Decode steps and short prompts
     run the token-by-token scan (one kernel on CUDA); prompts of ``_gdn_chunk_min()`` tokens or more run the chunked
     form (matrix products over heads x chunks) on CPU, and on CUDA when ``TSB_GDN_CHUNKED=1``."""
-    import os
     chunk_min = _gdn_chunk_min()
     chunked = batch.max_q_len >= chunk_min and (not qkv.is_cuda or os.environ.get("TSB_GDN_CHUNKED", "0") == "1")
     if qkv.is_cuda and not chunked:
@@ -584,7 +580,6 @@ def mamba2(xbc: torch.Tensor, dt: torch.Tensor, dt_bias, A, D, state: torch.Tens
            G: int, N: int) -> torch.Tensor:
     """Mamba2 selective scan over the packed tokens -> y f32 [T, H*P] (before gating).  Prompts of
     ``_gdn_chunk_min()`` tokens or more take the chunked form on CPU, and on CUDA when ``TSB_MAMBA_CHUNKED=1``."""
-    import os
     chunked = batch.max_q_len >= _gdn_chunk_min() and (not xbc.is_cuda or os.environ.get("TSB_MAMBA_CHUNKED", "0") == "1")
     if xbc.is_cuda and not chunked:
         return _k().mamba2_recurrent(xbc, dt, dt_bias, A, D, state, batch.cu_q, batch.seq_slots, H=H, P=P, G=G, N=N)
