@@ -243,10 +243,10 @@ class ModelBase:
         """Context-parallel prefill for any model whose attention blocks call :meth:`cp_sync_kv`: ``run(sub)`` is the
         model's ordinary forward on this rank's slice of the prompt (a batch of its own that sees the cache up to its
         last position); the logits are those of the rank that holds the prompt's last token."""
-        from ..parallel.context import shard_batch, shard_bounds
+        from ..parallel.context import balanced_ranges, shard_batch
         cp = self.cp_comm
-        bounds = [shard_bounds(batch.T, cp.size, s) for s in range(cp.size)]
-        sub = shard_batch(batch, *bounds[cp.rank])
+        bounds = [balanced_ranges(batch.T, cp.size, s) for s in range(cp.size)]      # two pieces per rank: equal causal work
+        sub = shard_batch(batch, bounds[cp.rank])
         self.__dict__["_cp_ctx"] = (batch, bounds)
         try:
             logits = run(sub)
@@ -254,7 +254,9 @@ class ModelBase:
             self.__dict__["_cp_ctx"] = None
         if not want_logits:
             return None
-        return cp.all_gather_list(logits.contiguous())[cp.size - 1]
+        # the prompt's last token is the end of one rank's last piece: that rank's last row is the answer
+        owner = next(s for s in range(cp.size) if bounds[s][-1][1] == batch.T)
+        return cp.all_gather_list(logits[-1:].contiguous())[owner]
 
     def cp_attention(self, n: int, Hkv: int, Dh: int):
         """The peer-memory attention of the context-parallel group for shards of ``n`` tokens (CUDA only,

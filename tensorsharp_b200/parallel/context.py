@@ -98,36 +98,56 @@ def shard_bounds(T: int, size: int, rank: int):
     return t0, t0 + base + (1 if rank < rem else 0)
 
 
-def shard_batch(batch, t0: int, t1: int):
-    """Tokens ``[t0, t1)`` of a one-sequence batch as a batch of their own: they see the cache up to their
-    last position, as a chunk of a chunked prefill does."""
+def balanced_ranges(T: int, size: int, rank: int):
+    """Token ranges of ``rank`` when the prompt is cut into ``2 * size`` pieces and rank r takes piece r and piece
+    ``2 * size - 1 - r``: under a causal mask every rank then attends to about the same number of keys (with whole
+    contiguous slices the last rank would do almost twice the average).  Falls back to one contiguous slice when the
+    prompt has fewer than ``2 * size`` tokens."""
+    if T < 2 * size:
+        return [shard_bounds(T, size, rank)]
+    return [shard_bounds(T, 2 * size, rank), shard_bounds(T, 2 * size, 2 * size - 1 - rank)]
+
+
+def shard_batch(batch, t0, t1=None):
+    """Tokens ``[t0, t1)`` of a one-sequence batch (or several such ranges, given as a list of pairs) as a batch of their
+    own: each range is a packed row that sees the cache up to its own last position, as a chunk of a chunked prefill
+    does; the rows share the sequence's block table."""
     from ..ops.functional import Batch
-    assert batch.B == 1 and 0 <= t0 < t1 <= batch.T
-    n = t1 - t0
-    kv_len = batch.h_kv_lens[0] - (batch.T - t1)
+    ranges = [(t0, t1)] if t1 is not None else list(t0)
+    assert batch.B == 1 and all(0 <= a < b <= batch.T for a, b in ranges)
     dev = batch.tokens.device
-    return Batch(tokens=batch.tokens[t0:t1].contiguous(), positions=batch.positions[t0:t1].contiguous(),
-                 slots=batch.slots[t0:t1].contiguous(), cu_q=torch.tensor([0, n], dtype=torch.int32, device=dev),
-                 kv_lens=torch.tensor([kv_len], dtype=torch.int32, device=dev), block_table=batch.block_table,
-                 last_idx=torch.tensor([n - 1], dtype=torch.int64, device=dev), seq_slots=batch.seq_slots,
-                 max_q_len=n, max_kv_len=kv_len, is_decode=False, page_size=batch.page_size,
-                 h_cu_q=(0, n), h_kv_lens=(kv_len,))
+    lens = [b - a for a, b in ranges]
+    kv = [batch.h_kv_lens[0] - (batch.T - b) for _, b in ranges]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    pick = lambda t: torch.cat([t[a:b] for a, b in ranges]).contiguous()                      # noqa: E731
+    R = len(ranges)
+    return Batch(tokens=pick(batch.tokens), positions=pick(batch.positions), slots=pick(batch.slots),
+                 cu_q=torch.tensor(cu, dtype=torch.int32, device=dev), kv_lens=torch.tensor(kv, dtype=torch.int32, device=dev),
+                 block_table=batch.block_table.expand(R, -1).contiguous(),
+                 last_idx=torch.tensor([c - 1 for c in cu[1:]], dtype=torch.int64, device=dev),
+                 seq_slots=batch.seq_slots.expand(R).contiguous(), max_q_len=max(lens), max_kv_len=max(kv), is_decode=False,
+                 page_size=batch.page_size, h_cu_q=tuple(cu), h_kv_lens=tuple(kv))
 
 
 def exchange_kv_shards(comm, batch, rank_bounds, k_cache: torch.Tensor, v_cache: torch.Tensor) -> None:
     """Every rank has written the K / V rows of its own tokens into its cache; fetch the other ranks' rows
-    (one all-gather of the padded shards) and write them at the same tokens' slots of this rank's cache."""
+    (one all-gather of the padded shards) and write them at the same tokens' slots of this rank's cache.
+    ``rank_bounds[r]`` is rank r's range ``(t0, t1)`` or its list of ranges."""
+    as_list = lambda x: [x] if isinstance(x[0], int) else list(x)                             # noqa: E731
+    per_rank = [as_list(b) for b in rank_bounds]
+    slots_of = lambda rs: torch.cat([batch.slots[a:b] for a, b in rs])                        # noqa: E731
+    count = [sum(b - a for a, b in rs) for rs in per_rank]
     r = comm.rank
-    t0, t1 = rank_bounds[r]
-    n_max = max(b - a for a, b in rank_bounds)
+    n_max = max(count)
     mine = torch.zeros((2, n_max) + tuple(k_cache.shape[1:]), dtype=k_cache.dtype, device=k_cache.device)
-    own = batch.slots[t0:t1]
-    mine[0, :t1 - t0] = k_cache.index_select(0, own)
-    mine[1, :t1 - t0] = v_cache.index_select(0, own)
+    own = slots_of(per_rank[r])
+    mine[0, :count[r]] = k_cache.index_select(0, own)
+    mine[1, :count[r]] = v_cache.index_select(0, own)
     for s, part in enumerate(comm.all_gather_list(mine)):
         if s == r:
             continue
-        a, b = rank_bounds[s]
-        idx = batch.slots[a:b]
-        k_cache.index_copy_(0, idx, part[0, :b - a])
-        v_cache.index_copy_(0, idx, part[1, :b - a])
+        idx = slots_of(per_rank[s])
+        k_cache.index_copy_(0, idx, part[0, :count[s]])
+        v_cache.index_copy_(0, idx, part[1, :count[s]])

@@ -21,6 +21,14 @@ def test_shard_bounds_and_shard_batch(tiny_qwen3_path):
         b = [shard_bounds(T, n, r) for r in range(n)]
         assert b[0][0] == 0 and b[-1][1] == T and all(b[i][1] == b[i + 1][0] for i in range(n - 1))
         assert max(y - x for x, y in b) - min(y - x for x, y in b) <= 1
+    from tensorsharp_b200.parallel.context import balanced_ranges
+    for T, n in ((64, 4), (45, 2), (1000, 8)):
+        pieces = sorted(r for k in range(n) for r in balanced_ranges(T, n, k))
+        assert pieces[0][0] == 0 and pieces[-1][1] == T and all(a[1] == b[0] for a, b in zip(pieces, pieces[1:]))
+        # keys seen under a causal mask: every rank within a few percent of the mean
+        work = [sum((b - a) * (a + b) / 2 for a, b in balanced_ranges(T, n, k)) for k in range(n)]
+        assert max(work) / (sum(work) / n) < 1.1
+    assert balanced_ranges(5, 4, 3) == [(4, 5)]                           # too short to cut twice per rank: one slice each
     m = ModelBase.create(tiny_qwen3_path, "cpu", max_context=128)
     seq = m.new_sequence()
     m.kv.build_batch([seq], [[1, 2, 3]])
@@ -29,6 +37,9 @@ def test_shard_bounds_and_shard_batch(tiny_qwen3_path):
     assert sub.tokens.tolist() == [14, 15, 16] and sub.positions.tolist() == [7, 8, 9]
     assert sub.h_kv_lens == (10,) and sub.max_q_len == 3 and not sub.is_decode
     assert sub.slots.tolist() == batch.slots[4:7].tolist()
+    two = shard_batch(batch, [(0, 2), (8, 10)])                           # two pieces: two packed rows over one block table
+    assert two.tokens.tolist() == [10, 11, 18, 19] and two.h_cu_q == (0, 2, 4) and two.h_kv_lens == (5, 13)
+    assert two.last_idx.tolist() == [1, 3] and two.block_table.shape[0] == 2 and two.max_q_len == 2
 
 
 def _worker(rank, world, port, path, prompt, more, out_path):
