@@ -9,6 +9,7 @@ output.weight (optional), token_embd.weight.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -97,10 +98,17 @@ class Qwen3Model(ModelBase):
         mid = torch.float32 if small else torch.bfloat16
         if self.pp_size > 1:
             return self.forward_stage(batch, want_logits)
-        if self.cp_wanted(batch):
-            return self.forward_context_parallel(batch, want_logits)
+        in_cp = self.__dict__.get("_cp_ctx") is not None
+        if self.cp_wanted(batch) and not in_cp:
+            # new sequence, equal slices, GPUs: attention pulls the earlier slices from peer memory; otherwise the general
+            # route (two balanced pieces per rank, caches completed layer by layer)
+            fused = (self.device.type == "cuda" and os.environ.get("TSB_CP_FUSED", "1") != "0"
+                     and batch.h_kv_lens[0] == batch.T and batch.T % self.cp_comm.size == 0)
+            if fused:
+                return self.forward_context_parallel(batch, want_logits)
+            return self.cp_run(batch, want_logits, lambda sub: self.forward_batch(sub, want_logits))
         h = self.inject_pending_embeddings(F.embed(self.tok_emb, batch.tokens))
-        if h.is_cuda and T <= F.FUSED_MAX_M and F.can_fuse(h, self.layers[0].get("wqkv", self.layers[0].get("wq"))):
+        if h.is_cuda and not in_cp and T <= F.FUSED_MAX_M and F.can_fuse(h, self.layers[0].get("wqkv", self.layers[0].get("wq"))):
             return self.forward_fused_small(h, batch, want_logits)
         if tp and not small and not batch.is_decode and h.is_cuda:     # prompts only: decode batches stay on the GEMV / GEMM + all-reduce path
             sp = self.tp_seq(T)
@@ -116,6 +124,7 @@ class Qwen3Model(ModelBase):
             qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=self.kv.k[self.l0 + l],
                                   v_cache=self.kv.v[self.l0 + l], rope=self.rope, qn=L["q_norm"], kn=L["k_norm"], eps=c.eps)
             qr = self.q_post_scale(qr, batch)
+            self.cp_sync_kv(self.l0 + l)
             o = F.attention(qr, self.kv.k[self.l0 + l], self.kv.v[self.l0 + l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh,
                             as_act=small and L["wo"].uses_q8_activations)
             if tpx is not None:
