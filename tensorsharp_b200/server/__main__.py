@@ -90,7 +90,7 @@ def load_startup_model(options, svc, configured_backend, log) -> None:
 
 def run_replicated(argv, options) -> int:
     """``--replicas N``: N server processes (one per GPU) and the routing front end on the public address."""
-    from .replicas import Router, serve_front, spawn_replicas, stop_replicas
+    from .replicas import Router, Supervisor, serve_front, spawn_replicas, stop_replicas
     if int(os.environ.get("WORLD_SIZE", "1")) > 1:
         print("error: --replicas starts its own processes; do not combine it with torch.distributed.run", file=sys.stderr)
         return 2
@@ -104,7 +104,9 @@ def run_replicated(argv, options) -> int:
         raise KeyboardInterrupt
     signal.signal(signal.SIGTERM, on_term)
     replicas = spawn_replicas(argv, options.replicas, use_gpus=backend != "cpu", log_dir=log_dir)
-    front = serve_front(Router(replicas), options.host, options.port)
+    router = Router(replicas)
+    supervisor = Supervisor(router).start()          # a replica that dies is started again
+    front = serve_front(router, options.host, options.port)
     print(f"{len(replicas)} replicas ready ({', '.join(str(r.port) for r in replicas)}); listening on "
           f"http://{options.host}:{front.server_address[1]}", flush=True)
     try:
@@ -112,6 +114,7 @@ def run_replicated(argv, options) -> int:
     except KeyboardInterrupt:
         pass
     finally:
+        supervisor.stop()
         front.server_close()
         stop_replicas(replicas)
     return 0

@@ -37,6 +37,16 @@ class Replica:
         self.index, self.host, self.port, self.process = index, host, port, process
         self.in_flight = 0
         self.served = 0
+        self.down_until = 0.0             # monotonic time until which the router avoids this replica
+        self.restarts = 0
+        self.launch = None                # () -> Popen: how to start this replica's process again
+
+    @property
+    def up(self) -> bool:
+        return time.monotonic() >= self.down_until
+
+    def mark_down(self, seconds: float = 5.0) -> None:
+        self.down_until = time.monotonic() + seconds
 
     def connect(self, timeout: float = 600.0) -> http.client.HTTPConnection:
         return http.client.HTTPConnection(self.host, self.port, timeout=timeout)
@@ -71,7 +81,7 @@ class Router:
 
     def _least_busy(self) -> Replica:
         n = len(self.replicas)
-        best = min(range(n), key=lambda i: (self.replicas[i].in_flight, (i - self._rr) % n))
+        best = min(range(n), key=lambda i: (not self.replicas[i].up, self.replicas[i].in_flight, (i - self._rr) % n))
         self._rr = (best + 1) % n
         return self.replicas[best]
 
@@ -91,7 +101,17 @@ class Router:
             elif method == "POST" and (path.rstrip("/") in GENERATION_PATHS or path.rstrip("/") == "/api/sessions"):
                 r = self._least_busy()
             else:
-                r = self.replicas[0]
+                r = next((x for x in self.replicas if x.up), self.replicas[0])
+            r.in_flight += 1
+            return r
+
+    def another(self, failed: Replica) -> Optional[Replica]:
+        """A different replica that is up, for one more try of a request that is not tied to a session."""
+        with self._lock:
+            rest = [x for x in self.replicas if x is not failed and x.up]
+            if not rest:
+                return None
+            r = min(rest, key=lambda x: x.in_flight)
             r.in_flight += 1
             return r
 
@@ -107,6 +127,11 @@ class Router:
     def drop_session(self, sid: str) -> None:
         with self._lock:
             self._session_owner.pop(sid, None)
+
+    def forget_sessions_of(self, r: Replica) -> None:
+        with self._lock:
+            for sid in [k for k, v in self._session_owner.items() if v == r.index]:
+                del self._session_owner[sid]
 
     def owner(self, sid: str) -> int:
         with self._lock:
@@ -163,7 +188,8 @@ def merged_status(replicas: Sequence[Replica]) -> Dict[str, object]:
             q = q if st == 200 and isinstance(q, dict) else {}
         except (OSError, ValueError, http.client.HTTPException):
             q = {"unreachable": True}
-        rows.append({"replica": r.index, "in_flight": r.in_flight, **q})
+        rows.append({"replica": r.index, "in_flight": r.in_flight, "up": r.up and not q.get("unreachable", False),
+                     "restarts": r.restarts, **q})
     return {"busy": any(x.get("busy") for x in rows),
             "pending_requests": sum(int(x.get("pending_requests", 0) or 0) for x in rows),
             "total_processed": sum(int(x.get("total_processed", 0) or 0) for x in rows),
@@ -202,9 +228,22 @@ def make_front_handler(router: Router):
                 return self._broadcast(path, body)
             replica = router.pick(self.command, path, body)
             try:
-                self._forward(replica, path, body)
+                reached = self._forward(replica, path, body)
             finally:
                 router.done(replica)
+            if reached is False:
+                # nothing was sent to the client yet: a request that no session ties to the dead replica goes to another
+                replica.mark_down()
+                sticky = path.startswith("/api/sessions/") or (path.rstrip("/") == "/api/chat" and b'"sessionId"' in body)
+                other = None if sticky else router.another(replica)
+                if other is None:
+                    return self._send(502, "application/json", json.dumps({"error": f"replica {replica.index} is not reachable"}).encode())
+                try:
+                    if self._forward(other, path, body) is False:
+                        other.mark_down()
+                        self._send(502, "application/json", json.dumps({"error": "no replica is reachable"}).encode())
+                finally:
+                    router.done(other)
 
         def _headers_out(self) -> Dict[str, str]:
             keep = ("content-type", "x-tensorsharp-request-id", "accept", "authorization")
@@ -224,14 +263,15 @@ def make_front_handler(router: Router):
                     first = got                      # the first failure wins, else replica 0's answer
             self._send(*first)
 
-        def _forward(self, replica: Replica, path: str, body: bytes) -> None:
+        def _forward(self, replica: Replica, path: str, body: bytes) -> Optional[bool]:
+            """Relay to ``replica``; False when it could not be reached (and nothing has been sent to the client)."""
             up = replica.connect()
             try:
                 try:
                     up.request(self.command, self.path, body if body else None, self._headers_out())
                     resp = up.getresponse()
-                except (OSError, http.client.HTTPException) as e:
-                    return self._send(502, "application/json", json.dumps({"error": f"replica {replica.index}: {e}"}).encode())
+                except (OSError, http.client.HTTPException):
+                    return False
                 streamed = (resp.getheader("Transfer-Encoding") or "").lower() == "chunked"
                 self.send_response(resp.status)
                 for k, v in resp.getheaders():
@@ -329,10 +369,13 @@ def spawn_replicas(argv: Sequence[str], n: int, *, use_gpus: bool, ready_timeout
             env.pop("WORLD_SIZE", None)
             if use_gpus:
                 env["CUDA_VISIBLE_DEVICES"] = gpu_ids[i]
-            out = open(os.path.join(log_dir, f"replica-{i}.log"), "ab") if log_dir else subprocess.DEVNULL
-            p = subprocess.Popen([sys.executable, "-m", "tensorsharp_b200.server", *replica_argv(argv, port)], env=env,
-                                 stdout=out, stderr=subprocess.STDOUT)
-            replicas.append(Replica(i, "127.0.0.1", port, p))
+            def launch(i=i, port=port, env=env):
+                out = open(os.path.join(log_dir, f"replica-{i}.log"), "ab") if log_dir else subprocess.DEVNULL
+                return subprocess.Popen([sys.executable, "-m", "tensorsharp_b200.server", *replica_argv(argv, port)], env=env,
+                                        stdout=out, stderr=subprocess.STDOUT)
+            r = Replica(i, "127.0.0.1", port, launch())
+            r.launch = launch
+            replicas.append(r)
         deadline = time.monotonic() + ready_timeout_s
         for r in replicas:
             while True:
@@ -350,6 +393,44 @@ def spawn_replicas(argv: Sequence[str], n: int, *, use_gpus: bool, ready_timeout
     except BaseException:
         stop_replicas(replicas)
         raise
+
+
+class Supervisor:
+    """Restarts replica processes that exited (a crash, an out-of-memory kill): checks once a second, keeps the replica
+    out of the rotation until it answers again.  Sessions that lived on it are gone (their caches were its memory); the
+    front end then opens them anew on whichever replica the next request reaches."""
+
+    def __init__(self, router: "Router", poll_s: float = 1.0, ready_timeout_s: float = 600.0):
+        self.router, self.poll_s, self.ready_timeout_s = router, poll_s, ready_timeout_s
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, name="tsb-replica-supervisor", daemon=True)
+
+    def start(self) -> "Supervisor":
+        self._thread.start()
+        return self
+
+    def stop(self) -> None:
+        self._stop.set()
+        self._thread.join(timeout=5)
+
+    def _run(self) -> None:
+        while not self._stop.wait(self.poll_s):
+            for r in self.router.replicas:
+                if r.process is None or r.launch is None or r.process.poll() is None:
+                    continue
+                r.mark_down(self.ready_timeout_s)
+                self.router.forget_sessions_of(r)
+                r.process = r.launch()
+                r.restarts += 1
+                deadline = time.monotonic() + self.ready_timeout_s
+                while not self._stop.is_set() and time.monotonic() < deadline and r.process.poll() is None:
+                    try:
+                        if r.get_json("/api/version", timeout=2.0)[0] == 200:
+                            r.down_until = 0.0
+                            break
+                    except (OSError, ValueError, http.client.HTTPException):
+                        pass
+                    time.sleep(0.2)
 
 
 def stop_replicas(replicas: Sequence[Replica], grace_s: float = 10.0) -> None:

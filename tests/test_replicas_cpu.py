@@ -156,3 +156,48 @@ def test_the_server_entry_point_starts_and_stops_its_replicas(tmp_path, tiny_qwe
     finally:
         if p.poll() is None:
             p.kill()
+
+
+def test_a_dead_replica_is_avoided_and_started_again(tmp_path, tiny_qwen3_path):
+    """A replica process that dies: requests that reach it before the front end knows are retried on the other one,
+    the supervisor starts it again, and it takes work again once it answers."""
+    import time
+    argv = ["--model", tiny_qwen3_path, "--backend", "cpu", "--temperature", "0", "--replicas", "2"]
+    env_before = dict(os.environ)
+    os.environ.update(TENSORSHARP_BASE_DIR=str(tmp_path), TENSORSHARP_LOG_FILE="0")
+    try:
+        reps = R.spawn_replicas(argv, 2, use_gpus=False, ready_timeout_s=300)
+    finally:
+        os.environ.clear()
+        os.environ.update(env_before)
+    router = R.Router(reps)
+    sup = R.Supervisor(router, poll_s=0.2, ready_timeout_s=300).start()
+    httpd = R.serve_front(router, "127.0.0.1", 0)
+    threading.Thread(target=httpd.serve_forever, daemon=True).start()
+    url = f"http://127.0.0.1:{httpd.server_address[1]}"
+    name = os.path.basename(tiny_qwen3_path)
+    ask = {"model": name, "prompt": "hello", "stream": False, "options": {"num_predict": 4}}
+    try:
+        first_pid = reps[1].process.pid
+        reps[1].process.terminate()
+        reps[1].process.wait(30)
+        for _ in range(3):                                    # some of these are dealt to the dead replica first
+            st, d = _post(url, "/api/generate", ask)
+            assert st == 200 and json.loads(d)["done"]
+        deadline = time.monotonic() + 300
+        while not (reps[1].restarts >= 1 and reps[1].up) and time.monotonic() < deadline:
+            time.sleep(0.2)
+        assert reps[1].restarts == 1 and reps[1].up and reps[1].process.pid != first_pid and reps[1].process.poll() is None
+        for _ in range(4):
+            assert _post(url, "/api/generate", ask)[0] == 200
+        st, q = reps[1].get_json("/api/queue/status")
+        assert st == 200 and q["total_processed"] >= 1         # the new process is in the rotation again
+        # a session that lived on a replica that is gone is forgotten by the router
+        router.bind_session("s-old", reps[1])
+        router.forget_sessions_of(reps[1])
+        assert router.owner("s-old") == -1
+    finally:
+        sup.stop()
+        httpd.shutdown()
+        httpd.server_close()
+        R.stop_replicas(reps)
