@@ -28,9 +28,10 @@ def _bcast(comm, obj: Any = None) -> Any:
 class LeaderModel:
     """Rank 0's shard, announcing every state-changing call to the followers before making it."""
 
-    def __init__(self, model, comm):
+    def __init__(self, model, comm, watchdog=None):
         self.__dict__["_model"] = model
         self.__dict__["_comm"] = comm
+        self.__dict__["_watchdog"] = watchdog
 
     # everything not listed below (cfg, tokenizer, arch, kv, cache_length, ...) is the local shard's
     def __getattr__(self, name):
@@ -40,6 +41,12 @@ class LeaderModel:
         setattr(self.__dict__["_model"], name, value)
 
     def _tell(self, op: str, *args) -> None:
+        # a follower that has gone quiet (or said it leaves) would make the broadcast below wait for ever: fail the
+        # call with a typed error instead, before anything is launched
+        wd = self._watchdog
+        if wd is not None and wd.failed:
+            from .errors import RankFailureError
+            raise RankFailureError(wd.failed)
         _bcast(self._comm, (op, args))
 
     # ------------------------------------------------------------------ graph execution
@@ -125,7 +132,22 @@ def layout_create(mode: str) -> Optional[Callable]:
     return create
 
 
-def leader_factory(comm, create: Optional[Callable] = None) -> Callable:
+def start_watchdog(comm, timeout_s: float, store=None, on_failure: Optional[Callable] = None):
+    """Heartbeats of this job's ranks over its key-value store (the process group's own store unless one is given):
+    returns the started ``Watchdog``, or ``None`` when ``timeout_s`` is 0 or no store can be had."""
+    if timeout_s <= 0:
+        return None
+    from .watchdog import Heartbeat, Watchdog
+    if store is None:
+        try:
+            from torch.distributed.distributed_c10d import _get_default_store
+            store = _get_default_store()
+        except Exception:
+            return None
+    return Watchdog(Heartbeat(store, comm.rank, comm.size), timeout_s, on_failure=on_failure).start()
+
+
+def leader_factory(comm, create: Optional[Callable] = None, watchdog=None) -> Callable:
     """A ``model_factory`` for ``ModelService`` (or any host) on rank 0: tells the followers which file to
     load, loads rank 0's shard and returns it wrapped."""
     def factory(path: str, device, **kw):
@@ -134,7 +156,7 @@ def leader_factory(comm, create: Optional[Callable] = None) -> Callable:
         _bcast(comm, ("load", (path, plain)))
         make = create or ModelBase.create
         dev = comm.device if comm.device.type == "cuda" else device
-        return LeaderModel(make(path, dev, tp_rank=comm.rank, tp_size=comm.size, comm=comm, **kw), comm)
+        return LeaderModel(make(path, dev, tp_rank=comm.rank, tp_size=comm.size, comm=comm, **kw), comm, watchdog)
     return factory
 
 

@@ -140,14 +140,22 @@ def main(argv=None) -> int:
         cpu_only = (try_resolve_supported_backend(options, read_configured_backend_input(argv))[0] or "") == "cpu"
         comm = init_from_env("gloo" if cpu_only else None)
         create = layout_create(options.parallel)
+        from ..parallel.replicated import start_watchdog
+        hb_timeout = float(os.environ.get("TSB_WATCHDOG_S", "30") or 0)
         if comm.rank != 0:
+            def leader_gone(stale):              # rank 0 went quiet: nothing will ever tell this process to stop
+                if 0 in stale:
+                    print(f"rank {comm.rank}: the front end (rank 0) stopped answering; exiting", file=sys.stderr, flush=True)
+                    os._exit(3)
+            start_watchdog(comm, hb_timeout, on_failure=leader_gone)
             follower_main(comm, create=create)
             return 0
+        watchdog = start_watchdog(comm, hb_timeout)
     provider = setup_file_logging(options.log_directory, prefix="tensorsharp-server", enabled=options.file_logging_enabled)
     svc = None
     if comm is not None:
         from .model_service import ModelService
-        svc = ModelService(None, model_factory=leader_factory(comm, create), max_context=options.max_context,
+        svc = ModelService(None, model_factory=leader_factory(comm, create, watchdog), max_context=options.max_context,
                            max_sessions=options.max_sessions)
     app = ServerApp(options, svc=svc, log_provider=provider)
     log = app.logger("TensorSharp.Server")

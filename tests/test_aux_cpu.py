@@ -304,3 +304,53 @@ def test_batch_stepper_follows_changing_membership(tiny_qwen3_path, monkeypatch)
         real.reset_kv_cache()
         assert got[i] == generate(real, p, 6, eos_ids=eos)
     g.close()
+
+
+def _leader_follower_main(rank, port, path, q):
+    import torch.distributed as dist
+    from datetime import timedelta
+
+    from tensorsharp_b200.parallel.dist import Communicator
+    from tensorsharp_b200.parallel.replicated import leader_factory, start_watchdog
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    store = dist.TCPStore("127.0.0.1", port, 2, rank == 0, timeout=timedelta(seconds=30))
+    dist.init_process_group("gloo", store=store, rank=rank, world_size=2, timeout=timedelta(seconds=30))
+    comm = Communicator(rank, 2)
+    wd = start_watchdog(comm, 0.6, store=store)
+    if rank == 1:
+        from tensorsharp_b200.models.base import ModelBase
+        from tensorsharp_b200.parallel.replicated import _bcast
+        op, args = _bcast(comm)                         # "load"
+        m = ModelBase.create(args[0], "cpu", tp_rank=1, tp_size=2, comm=comm, **args[1])
+        op, args = _bcast(comm)                         # the first forward: mirrored
+        m.forward(args[0], args[1])
+        wd.stop()
+        wd.hb.leave()                                   # leaves between steps, nothing in flight
+        q.put(("left", op))
+        time.sleep(3.0)
+        return
+    m = leader_factory(comm, watchdog=wd)(path, "cpu", max_context=64)
+    first = m.forward([5, 6, 7])
+    err = None
+    deadline = time.time() + 20
+    while err is None and time.time() < deadline:
+        try:
+            time.sleep(1.5)                             # several watchdog periods: the departure has been seen
+            m.forward([8])                              # must not hang: the follower is gone
+        except RankFailureError as e:
+            err = sorted(e.stale)
+    q.put(("leader", (first is not None, err)))
+
+
+def test_front_end_fails_a_call_instead_of_waiting_for_a_departed_follower(tiny_qwen3_path):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31000 + os.getpid() % 2000
+    ps = [ctx.Process(target=_leader_follower_main, args=(r, port, tiny_qwen3_path, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    got = dict(q.get(timeout=120) for _ in range(2))
+    for p in ps:
+        p.join(timeout=30)
+    assert got["left"] == "forward"
+    assert got["leader"] == (True, [1])
