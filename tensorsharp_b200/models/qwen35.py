@@ -20,7 +20,7 @@ import torch
 
 from ..ops import functional as F
 from ..ops.functional import Batch, RopeSpec
-from ..parallel.dist import even_split
+from ..parallel.dist import even_split, head_split
 from ..quant.qweight import QuantWeight
 from .base import ModelBase, register_architecture
 
@@ -48,7 +48,8 @@ class Qwen35Model(ModelBase):
     def kv_layer_shapes(self):
         c = self.cfg
         l0, l1 = self.layer_range
-        return [None if (self.is_recurrent[l] or not l0 <= l < l1) else (c.n_kv_heads, c.head_dim) for l in range(c.n_layers)]
+        (_, _), (k0, k1) = head_split(c.n_heads, c.n_kv_heads, self.tp_size, self.tp_rank)
+        return [None if (self.is_recurrent[l] or not l0 <= l < l1) else (k1 - k0, c.head_dim) for l in range(c.n_layers)]
 
     def load_weights(self) -> None:
         c = self.cfg
@@ -56,6 +57,7 @@ class Qwen35Model(ModelBase):
         self.e0, self.e1 = even_split(self.n_experts, ep, er) if self.n_experts else (0, 0)
         self.tok_emb, self.out_norm, self.lm_head = self.stage_tensors()
         self.l0, l1 = self.layer_range
+        (self.q0, self.q1), (self.k0, self.k1) = head_split(c.n_heads, c.n_kv_heads, self.tp_size, self.tp_rank)
         self.layers = []
         qkv_dim = 2 * self.Hk * self.Dk + self.Hv * self.Dv
         dev = self.device
@@ -83,6 +85,13 @@ class Qwen35Model(ModelBase):
                 L["q_norm"] = self.f32(p + "attn_q_norm.weight", optional=True)
                 L["k_norm"] = self.f32(p + "attn_k_norm.weight", optional=True)
                 L["wo"] = self.qw(p + "attn_output.weight")
+                if self.tp_size > 1:
+                    # attention heads are dealt to the ranks (a query row holds the head's query and its gate); with fewer
+                    # KV heads than ranks a KV head is held by several ranks
+                    Dh = c.head_dim
+                    L["wq"] = L["wq"].row_slice(self.q0 * 2 * Dh, self.q1 * 2 * Dh)
+                    L["wk"], L["wv"] = L["wk"].row_slice(self.k0 * Dh, self.k1 * Dh), L["wv"].row_slice(self.k0 * Dh, self.k1 * Dh)
+                    L["wo"] = L["wo"].col_slice(self.q0 * Dh, self.q1 * Dh)
             if self.has(p + "ffn_gate_inp.weight"):
                 L["router"] = self.qw(p + "ffn_gate_inp.weight")
                 ge, ue, de = (self.qw(p + f"ffn_{n}_exps.weight") for n in ("gate", "up", "down"))
@@ -152,7 +161,7 @@ class Qwen35Model(ModelBase):
 
     def _attn_layer(self, l, L, a, batch: Batch, mid) -> torch.Tensor:
         c = self.cfg
-        Hq, Hkv, Dh = c.n_heads, c.n_kv_heads, c.head_dim
+        Hq, Hkv, Dh = self.q1 - self.q0, self.k1 - self.k0, c.head_dim
         T = batch.T
         qg = F.linear(a, L["wq"], out_dtype=mid).view(T, Hq, 2 * Dh)
         k = F.linear(a, L["wk"], out_dtype=mid).view(T, Hkv, Dh)
@@ -162,7 +171,10 @@ class Qwen35Model(ModelBase):
                               v_cache=self.kv.v[l], rope=self.rope, qn=L["q_norm"], kn=L["k_norm"], eps=c.eps)
         o = F.attention(qr, self.kv.k[l], self.kv.v[l], batch, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh)
         o = F.glu("sigmoid_mul", gate.reshape(T, Hq * Dh).contiguous(), o)
-        return F.linear(F.as_act(o), L["wo"], out_dtype=torch.float32)
+        y = F.linear(F.as_act(o), L["wo"], out_dtype=torch.float32)
+        if self.tp_size > 1:
+            self.comm.all_reduce(y)
+        return y
 
     def forward_batch(self, batch: Batch, want_logits: bool = True) -> Optional[torch.Tensor]:
         c = self.cfg

@@ -95,10 +95,17 @@ def block_split(n: int, block: int, parts: int, rank: int) -> Tuple[int, int]:
 
 
 def head_split(n_heads: int, n_kv_heads: int, parts: int, rank: int):
-    """Query / KV head ranges of ``rank``.  KV heads are dealt evenly; each rank takes the
-    query heads that attend to its KV heads, so no KV head is replicated."""
-    if n_kv_heads % parts:
-        raise ValueError(f"{n_kv_heads} KV heads cannot be split over {parts} ranks")
+    """Query / KV head ranges of ``rank``.  KV heads are dealt evenly and each rank takes the query heads that attend
+    to its KV heads, so no KV head is replicated; when there are fewer KV heads than ranks (and the ranks divide evenly
+    among them) a KV head is held by several ranks, which share its group of query heads."""
     g = n_heads // n_kv_heads
-    k0, k1 = even_split(n_kv_heads, parts, rank)
-    return (k0 * g, k1 * g), (k0, k1)
+    if n_kv_heads % parts == 0:
+        k0, k1 = even_split(n_kv_heads, parts, rank)
+        return (k0 * g, k1 * g), (k0, k1)
+    if parts % n_kv_heads == 0 and g % (parts // n_kv_heads) == 0:
+        rep = parts // n_kv_heads
+        per = g // rep
+        k = rank // rep
+        q0 = k * g + (rank % rep) * per
+        return (q0, q0 + per), (k, k + 1)
+    raise ValueError(f"{n_kv_heads} KV heads (of {n_heads} query heads) cannot be split over {parts} ranks")

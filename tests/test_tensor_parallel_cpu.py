@@ -60,7 +60,17 @@ def test_tp2_matches_single_rank(tiny_qwen3_path, tmp_path):
     assert torch.allclose(l1, s1, atol=5e-3) and torch.allclose(l2, s2, atol=5e-3)
 
 
-@pytest.mark.parametrize("family", ["gptoss", "qwen35", "nemotron", "gemma3", "gemma4"])
+def test_head_split_replicates_kv_heads_when_ranks_outnumber_them():
+    from tensorsharp_b200.parallel.dist import head_split
+    assert head_split(32, 8, 4, 1) == ((8, 16), (2, 4))                       # the usual case: KV heads dealt, none shared
+    got = [head_split(16, 2, 8, r) for r in range(8)]                         # 2 KV heads over 8 ranks: 4 ranks share each
+    assert [q for q, _ in got] == [(2 * r, 2 * r + 2) for r in range(8)]
+    assert [k for _, k in got] == [(0, 1)] * 4 + [(1, 2)] * 4
+    with pytest.raises(ValueError):
+        head_split(16, 2, 3, 0)
+
+
+@pytest.mark.parametrize("family", ["gptoss", "qwen35", "qwen35_one_kv_head", "nemotron", "gemma3", "gemma4"])
 def test_other_families_shard_over_two_ranks(tmp_path, family):
     """Head / FFN shards (Gemma, GPT-OSS attention) and expert ranges (GPT-OSS, Qwen3.5, Nemotron-H, Gemma 4) on two gloo
     ranks give the logits of one process, for a prompt and a decode step."""
@@ -71,6 +81,8 @@ def test_other_families_shard_over_two_ranks(tmp_path, family):
         synth.write_gptoss(p, n_layers=2, device="cpu")
     elif family == "qwen35":
         synth.write_qwen35(p, device="cpu")
+    elif family == "qwen35_one_kv_head":
+        synth.write_qwen35(p, n_kv_heads=1, device="cpu")                     # both ranks hold the KV head, two query heads each
     elif family == "nemotron":
         synth.write_nemotron_h(p, device="cpu")
     else:
