@@ -7,7 +7,9 @@ When a slot calls ``forward`` the call is parked; a stepper thread collects the 
 at that moment (it waits a moment for the other busy slots to arrive, so that decode steps stay in
 lockstep), packs them into one batch (prefill chunks and single decode tokens mix freely), runs the
 graph once and hands every caller its own row of logits.  The request code cannot tell that it shared
-the step; on a B200 a decode step for eight sequences costs about what it costs for one.
+the step; on a B200 a decode step for eight sequences costs about what it costs for one.  A call that carries image or
+audio embeddings runs by itself (its spans are positions of its own prompt); steps in which every caller brings one
+token can replay a captured graph (``TSB_GATHER_GRAPH=1``, engine.py: BatchGraphStepper).
 
 The reference runs one inference at a time (TensorSharp.Server/InferenceQueue.cs) and has no counterpart.
 """
