@@ -152,8 +152,8 @@ class ModelBase:
         """Queue ``embeddings`` ``[n, hidden]`` to replace the token embeddings of rows
         ``[insert_position, insert_position + n)`` of the next forward call (SetVisionEmbeddings /
         SetAudioEmbeddings of the reference's multimodal models).  Only the pipeline stage that embeds tokens keeps them."""
-        if self.pp_size > 1 and not self.is_first_stage:
-            return
+        if self.pp_size > 1 and not self.is_first_stage and not getattr(self, "ple_dim", 0):
+            return                                   # (stages that derive per-layer inputs from the embedded tokens keep them too)
         self._pending_embeddings.append((embeddings, int(insert_position)))
 
     set_audio_embeddings = set_vision_embeddings

@@ -182,6 +182,8 @@ class Gemma3Model(_GemmaBase):
 
 @register_architecture("gemma4", "gemma3n")
 class Gemma4Model(_GemmaBase):
+    supports_pipeline = True
+
     def parse_config(self) -> None:
         g, a, c = self.gguf, self.arch, self.cfg
         pat = g.get_array(f"{a}.attention.sliding_window_pattern")
@@ -226,15 +228,21 @@ class Gemma4Model(_GemmaBase):
         return self.cfg.n_kv_heads if self.is_local(l) else self.kv_global
 
     def kv_donors(self) -> Dict[int, int]:
-        return dict(self.donors)
+        l0, l1 = self.layer_range
+        return {l: d for l, d in self.donors.items() if l0 <= l < l1}
 
     def load_weights(self) -> None:
         c = self.cfg
-        self.tok_emb = self.qw("token_embd.weight")
-        self.out_norm = self.f32("output_norm.weight")
-        self.lm_head = self.qw("output.weight", optional=True) or self.tok_emb
+        self.l0, l1 = self.layer_range
+        for l, d in self.donors.items():
+            if self.l0 <= l < l1 and not self.l0 <= d < l1:
+                raise ValueError(f"pipeline stage {self.pp_rank} holds layers {self.l0}..{l1 - 1}, but layer {l} reads the KV cache of "
+                                 f"layer {d}: choose a number of stages that keeps shared-KV layers with their donors")
+        self.tok_emb, self.out_norm, self.lm_head = self.stage_tensors()
+        if self.tok_emb is None and self.ple_dim:
+            self.tok_emb = self.qw("token_embd.weight")        # every stage derives its per-layer inputs from the embedded tokens
         self.layers = []
-        for l in range(c.n_layers):
+        for l in range(self.l0, l1):
             L = self._load_common_layer(l)
             p = f"blk.{l}."
             sc = self.f32(p + "layer_output_scale.weight", optional=True)
@@ -298,9 +306,13 @@ class Gemma4Model(_GemmaBase):
         if self.cp_wanted(batch) and self.__dict__.get("_cp_ctx") is None:
             return self.cp_run(batch, want_logits, lambda sub: self.forward_batch(sub, want_logits))
         mid = torch.float32 if small else torch.bfloat16
-        h = self.inject_pending_embeddings(F.embed(self.tok_emb, batch.tokens, scale=math.sqrt(c.hidden)))
-        ple = self._ple(batch, h)
-        for l, L in enumerate(self.layers):
+        h0 = None
+        if self.is_first_stage or self.ple_dim:
+            h0 = self.inject_pending_embeddings(F.embed(self.tok_emb, batch.tokens, scale=math.sqrt(c.hidden)))
+        ple = self._ple(batch, h0) if h0 is not None else None
+        h = self.stage_input(batch, lambda: h0)
+        for i, L in enumerate(self.layers):
+            l = self.l0 + i
             local = self.is_local(l)
             a = F.norm(h, L["attn_norm"], c.eps, want_q8=small)
             donor = self.donors.get(l)
@@ -320,6 +332,8 @@ class Gemma4Model(_GemmaBase):
                 h = F.norm_add(pr, L["ple_norm"], c.eps, h)
             if L["out_scale"] != 1.0:
                 h = h * L["out_scale"]
+        if self.stage_handoff(h):
+            return None
         return self._logits(h, batch) if want_logits else None
 
     def prefill_chunk(self, requested: int) -> int:

@@ -140,7 +140,10 @@ def test_pipeline_stages_match_single_process(tiny_qwen3_path, tmp_path, world):
     assert covered == list(range(n_layers))
 
 
-@pytest.mark.parametrize("family", ["gptoss", "qwen35", "nemotron", "gemma3"])
+G4 = dict(arch="gemma4", n_layers=8, head_dim_global=128, kv_heads_global=1, rot_global=64, shared_kv=2, ple_dim=32, n_experts=4, top_k=2)
+
+
+@pytest.mark.parametrize("family", ["gptoss", "qwen35", "nemotron", "gemma3", "gemma4"])
 def test_other_families_pipeline_stages_match_single_process(tmp_path, family):
     """The mixture-of-experts family (sliding windows follow the global layer index, the last layer's last-token
     shortcut runs on the last stage only) and the two families with recurrent layers (state slots live with their
@@ -155,6 +158,8 @@ def test_other_families_pipeline_stages_match_single_process(tmp_path, family):
         synth.write_qwen35(p, device="cpu")
     elif family == "gemma3":
         synth.write_gemma(p, arch="gemma3", device="cpu")
+    elif family == "gemma4":
+        synth.write_gemma(p, device="cpu", **G4)      # shared-KV layers 6, 7 read layer 4: all on the second stage; per-layer inputs on both
     else:
         synth.write_nemotron_h(p, device="cpu")
     g = torch.Generator().manual_seed(6)
@@ -167,16 +172,19 @@ def test_other_families_pipeline_stages_match_single_process(tmp_path, family):
     for r in range(2):
         toks, held, (l0, l1), _, has_head = torch.load(f"{out}.{r}")
         assert toks == want and has_head == (r == 1)
-        assert held == [has_kv[l] and l0 <= l < l1 for l in range(single.cfg.n_layers)]
+        if family != "gemma4":                          # (its shared-KV layers alias their donor's tensors)
+            assert held == [has_kv[l] and l0 <= l < l1 for l in range(single.cfg.n_layers)]
 
 
-def test_pipeline_rejects_models_without_a_stage_path(tmp_path):
+def test_pipeline_refuses_a_cut_between_a_shared_kv_layer_and_its_donor(tmp_path):
     from tensorsharp_b200.models import synth
     from tensorsharp_b200.models.base import ModelBase
     p = str(tmp_path / "g.gguf")
-    synth.write_gemma(p, arch="gemma4", device="cpu")
+    synth.write_gemma(p, device="cpu", **G4)
+    with pytest.raises(ValueError, match="shared-KV"):
+        ModelBase.create(p, "cpu", max_context=64, pp_rank=3, pp_size=4)          # layers 6, 7 without layer 4
     with pytest.raises(ValueError):
-        ModelBase.create(p, "cpu", max_context=64, pp_rank=0, pp_size=2)
+        ModelBase.create(p, "cpu", max_context=64, pp_rank=0, pp_size=2, tp_size=2)   # stages are not combined with weight shards
 
 
 def _serve_worker(rank, world, port, path, out_path, mode="tp"):
