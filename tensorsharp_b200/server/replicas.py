@@ -366,7 +366,8 @@ def spawn_replicas(argv: Sequence[str], n: int, *, use_gpus: bool, ready_timeout
         for i in range(n):
             port = _free_port()
             env = dict(os.environ)
-            env.pop("WORLD_SIZE", None)
+            for k in ("WORLD_SIZE", "RANK", "LOCAL_RANK", "TENSORSHARP_REPLICAS"):      # a replica is a plain single-process server
+                env.pop(k, None)
             if use_gpus:
                 env["CUDA_VISIBLE_DEVICES"] = gpu_ids[i]
             def launch(i=i, port=port, env=env):
