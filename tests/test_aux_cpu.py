@@ -272,6 +272,7 @@ def test_batch_stepper_follows_changing_membership(tiny_qwen3_path, monkeypatch)
     a = ModelBase.create(tiny_qwen3_path, "cpu", max_context=256, max_seqs=4, page_size=16)
     b = ModelBase.create(tiny_qwen3_path, "cpu", max_context=256, max_seqs=4, page_size=16)
     st = BatchGraphStepper(a, 3)
+    st.MIN_BUCKET = 32                                   # small context buckets: the longest sequence outgrows one during the test
     gen = torch.Generator().manual_seed(2)
     prompts = [torch.randint(5, 4000, (n,), generator=gen).tolist() for n in (13, 30, 7)]
     sa, sb = [a.new_sequence() for _ in prompts], [b.new_sequence() for _ in prompts]
@@ -285,6 +286,7 @@ def test_batch_stepper_follows_changing_membership(tiny_qwen3_path, monkeypatch)
         want = b.forward_batch(b.kv.build_batch([sb[i] for i in idx], [[t] for t in toks]), True)
         assert got is not None and torch.allclose(got, want, atol=1e-5), step
         assert [sa[i].length for i in idx] == [sb[i].length for i in idx]
+    assert len({b for _, b in st._state}) >= 2                           # more than one context bucket was used
     assert st.step([sa[0]] * 4, [1, 2, 3, 4]) is None                   # more sequences than the stepper was sized for
     # through the gatherer
     monkeypatch.setenv("TSB_GATHER_GRAPH", "1")
