@@ -47,6 +47,14 @@ class ContinuousBatcher:
         self.model, self.max_batch, self.prefill_chunk = model, max_batch, prefill_chunk
         self.steps = 0                 # decode steps run
         self.step_rows = 0             # sequences advanced over all steps (step_rows / steps = mean batch)
+        self.graph_steps = 0
+        # TSB_GATHER_GRAPH=1: decode steps replay captured graphs (engine.py: BatchGraphStepper), as the merged steps of the
+        # concurrent server do
+        import os
+        self._stepper = None
+        if os.environ.get("TSB_GATHER_GRAPH", "0") == "1":
+            from .engine import BatchGraphStepper
+            self._stepper = BatchGraphStepper(model, max_batch)
 
     # ------------------------------------------------------------------ one request's life
     def _sync(self) -> None:
@@ -119,8 +127,13 @@ class ContinuousBatcher:
                     self._finish(r)
             if not active:
                 continue
-            batch = m.kv.build_batch([r._seq for r in active], [[r._next] for r in active])
-            logits = m.forward_batch(batch, True)
+            logits = None
+            if self._stepper is not None:
+                logits = self._stepper.step([r._seq for r in active], [r._next for r in active])
+                self.graph_steps += logits is not None
+            if logits is None:
+                batch = m.kv.build_batch([r._seq for r in active], [[r._next] for r in active])
+                logits = m.forward_batch(batch, True)
             self.steps += 1
             self.step_rows += len(active)
             still: List[GenRequest] = []

@@ -190,7 +190,10 @@ def test_jsonl_batch_size_gives_the_sequential_outputs(tiny_qwen3_path, tmp_path
     assert outs[3][2]["error"].startswith("Invalid JSON")
 
 
-def test_continuous_batcher_refills_the_batch(tiny_qwen3_path):
+@pytest.mark.parametrize("graph_steps", ["0", "1"])
+def test_continuous_batcher_refills_the_batch(tiny_qwen3_path, monkeypatch, graph_steps):
+    """``graph_steps`` = 1: the decode steps go through the static batch of the graph stepper (eager on CPU)."""
+    monkeypatch.setenv("TSB_GATHER_GRAPH", graph_steps)
     from tensorsharp_b200.models.base import ModelBase
     from tensorsharp_b200.runtime.batching import ContinuousBatcher, GenRequest
     from tensorsharp_b200.runtime.engine import generate
@@ -205,6 +208,7 @@ def test_continuous_batcher_refills_the_batch(tiny_qwen3_path):
     eng.run(reqs)
     assert m.kv.free_pages == free0                         # every sequence gave its pages back
     assert eng.steps < sum(lens) and eng.step_rows / eng.steps > 1.5
+    assert (eng.graph_steps == eng.steps) if graph_steps == "1" else eng.graph_steps == 0
     eos = [t for t in range(m.cfg.vocab) if m.tokenizer.is_eos(t)]
     for r, p, n in zip(reqs, prompts, lens):
         m.reset_kv_cache()
