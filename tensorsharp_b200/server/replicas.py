@@ -419,6 +419,9 @@ class Supervisor:
             for r in self.router.replicas:
                 if r.process is None or r.launch is None or r.process.poll() is None:
                     continue
+                if time.monotonic() < getattr(r, "next_restart", 0.0):
+                    continue                         # it died again right after the last restart: wait before the next try
+                r.next_restart = time.monotonic() + min(60.0, 2.0 ** min(r.restarts, 6))
                 r.mark_down(self.ready_timeout_s)
                 self.router.forget_sessions_of(r)
                 r.process = r.launch()
