@@ -353,6 +353,17 @@ def replica_argv(argv: Sequence[str], port: int) -> List[str]:
     return out + ["--host", "127.0.0.1", "--port", str(port)]
 
 
+def replica_env(base, gpu: Optional[str]) -> Dict[str, str]:
+    """The environment of one replica process: a plain single-process server (no rank variables, no replica count of
+    its own, which would make it start replicas in turn) that sees ``gpu`` only."""
+    env = dict(base)
+    for k in ("WORLD_SIZE", "RANK", "LOCAL_RANK", "TENSORSHARP_REPLICAS"):
+        env.pop(k, None)
+    if gpu is not None:
+        env["CUDA_VISIBLE_DEVICES"] = gpu
+    return env
+
+
 def spawn_replicas(argv: Sequence[str], n: int, *, use_gpus: bool, ready_timeout_s: float = 600.0,
                    log_dir: Optional[str] = None) -> List[Replica]:
     """Start ``n`` server processes and wait until each answers ``GET /api/version``.  With ``use_gpus`` replica ``i``
@@ -365,11 +376,7 @@ def spawn_replicas(argv: Sequence[str], n: int, *, use_gpus: bool, ready_timeout
     try:
         for i in range(n):
             port = _free_port()
-            env = dict(os.environ)
-            for k in ("WORLD_SIZE", "RANK", "LOCAL_RANK", "TENSORSHARP_REPLICAS"):      # a replica is a plain single-process server
-                env.pop(k, None)
-            if use_gpus:
-                env["CUDA_VISIBLE_DEVICES"] = gpu_ids[i]
+            env = replica_env(os.environ, gpu_ids[i] if use_gpus else None)
             def launch(i=i, port=port, env=env):
                 out = open(os.path.join(log_dir, f"replica-{i}.log"), "ab") if log_dir else subprocess.DEVNULL
                 return subprocess.Popen([sys.executable, "-m", "tensorsharp_b200.server", *replica_argv(argv, port)], env=env,

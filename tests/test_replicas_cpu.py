@@ -30,6 +30,9 @@ def test_router_prefers_idle_replicas_and_keeps_sessions_where_they_are():
     assert router.pick("GET", "/api/tags", b"") is reps[0]           # everything else: replica 0
     assert R.replica_argv(["--model", "m", "--replicas", "2", "--port=5000", "--host", "0.0.0.0"], 7001) == \
         ["--model", "m", "--host", "127.0.0.1", "--port", "7001"]
+    env = R.replica_env({"TENSORSHARP_REPLICAS": "4", "WORLD_SIZE": "2", "RANK": "1", "HOME": "/h", "CUDA_VISIBLE_DEVICES": "0,1"}, "1")
+    assert env == {"HOME": "/h", "CUDA_VISIBLE_DEVICES": "1"}                 # a replica must not start replicas of its own
+    assert R.replica_env({"CUDA_VISIBLE_DEVICES": "0,1"}, None) == {"CUDA_VISIBLE_DEVICES": "0,1"}
 
 
 def test_merge_metrics_labels_samples_by_replica():
