@@ -3,6 +3,8 @@
 
     python bench.py --gpus N --steps K --warmup W            # this engine
     python bench.py --impl reference --gpus N ...            # the reference's own GGML-CUDA library
+    python bench.py --model gptoss-20b | qwen35-35b-a3b | gemma4-31b   # the other named configurations
+    python bench.py --model qwen3-tiny --device cpu          # the tiny configuration on the CPU backend
 
 A *step* is one greedy decode step of the whole batch (batch 1 by default, as the
 reference benchmark is; ``--batch 16`` gives the batched config).  The model is random-init
