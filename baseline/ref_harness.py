@@ -35,6 +35,12 @@ import time
 import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+try:
+    from . import METRIC
+except ImportError:                      # run as a script
+    import sys
+    sys.path.insert(0, ROOT)
+    from baseline import METRIC
 LIB = os.path.join(ROOT, "baseline", "_ref", "libGgmlOps.so")
 BACKEND_CUDA = 3
 
@@ -202,17 +208,22 @@ def run(args, shape: dict) -> dict:
         for _ in range(W):
             tok = step(tok, pos)
             pos += 1
+        per_step = []
         t0 = time.perf_counter()
         for _ in range(K):
+            t1 = time.perf_counter()
             tok = step(tok, pos)
             pos += 1
+            per_step.append((time.perf_counter() - t1) * 1e3)
         dt = time.perf_counter() - t0
     except RuntimeError as exc:
         return unavailable(str(exc))
     ms = dt * 1e3 / K
     return {
         "impl": "reference",
-        "metric": "decode tok/s (host wall clock around the reference's own calls, as its --benchmark does)",
+        "metric": METRIC,
+        "timing": "host wall clock around the reference's own calls, as its --benchmark does (every call ends with a backend "
+                  "synchronise and a download, so device time is included)",
         "value": 1e3 / ms, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32 activations, Q4_K weights (uniform; see module docstring), f32 KV cache", "data": "synthetic",
@@ -220,6 +231,9 @@ def run(args, shape: dict) -> dict:
                    "decode_steps": K, "parallelism": "single GPU (the reference has no multi-GPU path)",
                    "path": "TSGgml_TransformerModelDecode + TSGgml_NormF32 + TSGgml_AddmmQuantF32"},
         "prefill_tok_s": None,
+        # spread of the timed steps: the path is host-bound (a 36-layer ggml graph is rebuilt, allocated and scheduled
+        # on the host for every token), so the mean moves with the box's CPU and with what else runs on it
+        "ms_per_step_min": min(per_step), "ms_per_step_median": sorted(per_step)[len(per_step) // 2],
         "e2e": {"value": 1e3 / ms, "unit": "tok/s", "h2d_bytes_per_step": D * 4 + 4, "d2h_bytes_per_step": D * 4 + V * 4},
     }
 

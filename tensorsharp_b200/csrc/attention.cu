@@ -12,6 +12,7 @@
 // cuBLAS QK^T / PV of the non-flash prefill path (ggml-cuda.cu:2084) and the host-built masks
 // of TensorSharp.GGML.Native/ggml_ops_norm_attn.cpp:1699-1884.  Scores are never materialised.
 #include <cstdlib>
+#include <mutex>
 #include "common.cuh"
 #include "tsb_noalloc.h"
 
@@ -356,6 +357,7 @@ static int launch_decode_g(const AttnArgs& a, cudaStream_t s) {
 #define ATTN_MAX_TICKETS 65536
 static __device__ unsigned g_attn_ticket[ATTN_MAX_TICKETS];
 static unsigned* g_attn_ticket_ptr[64] = {nullptr};
+static std::once_flag g_attn_ticket_once[64];
 
 static unsigned* attn_ticket_for_current_device() {
     // Off unless TSB_ATTN_FUSED_COMBINE=1: inside the decode step the in-kernel merge measured slower than the
@@ -365,17 +367,18 @@ static unsigned* attn_ticket_for_current_device() {
     if (!on) return nullptr;
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    if (g_attn_ticket_ptr[dev] == nullptr) {
+    // once per device, whichever host thread gets here first (the device is current in that thread)
+    std::call_once(g_attn_ticket_once[dev], [dev]() {
         unsigned* p = nullptr;
-        if (cudaGetSymbolAddress((void**)&p, g_attn_ticket) != cudaSuccess) return nullptr;
-        g_attn_ticket_ptr[dev] = p;
-    }
+        if (cudaGetSymbolAddress((void**)&p, g_attn_ticket) == cudaSuccess) g_attn_ticket_ptr[dev] = p;
+    });
     return g_attn_ticket_ptr[dev];
 }
 
-extern "C" int tsb_attn_decode(const AttnArgs* args, void* stream) {
+// `allow_fused`: whether this call may use the in-kernel split merge (and with it the shared arrival tickets).
+static int attn_decode_impl(const AttnArgs* args, void* stream, bool allow_fused) {
     AttnArgs a = *args;
-    a.ticket = (a.splits >= 1 && (long)a.B * a.Hkv <= ATTN_MAX_TICKETS) ? attn_ticket_for_current_device() : nullptr;
+    a.ticket = (allow_fused && a.splits >= 1 && (long)a.B * a.Hkv <= ATTN_MAX_TICKETS) ? attn_ticket_for_current_device() : nullptr;
     TSB_CHECK_ARG(a.Hkv > 0 && a.Hq % a.Hkv == 0, "attn_decode: Hq=%d not a multiple of Hkv=%d", a.Hq, a.Hkv);
     TSB_CHECK_ARG(a.splits >= 1 && a.part_o && a.part_ml, "attn_decode: scratch for %d splits missing", a.splits);
     TSB_CHECK_ARG(a.splits <= 64, "attn_decode: %d splits (limit 64)", a.splits);
@@ -399,6 +402,8 @@ extern "C" int tsb_attn_decode(const AttnArgs* args, void* stream) {
     return TSB_OK;
 }
 
+extern "C" int tsb_attn_decode(const AttnArgs* args, void* stream) { return attn_decode_impl(args, stream, true); }
+
 // ------------------------------------------------------------------------------------------
 // Allocation-free variant (see tsb_noalloc.h): the split-KV partials live in a file-scope
 // device array instead of caller scratch.  In host code the array's name is only a handle
@@ -408,13 +413,14 @@ extern "C" int tsb_attn_decode(const AttnArgs* args, void* stream) {
 static __device__ __align__(256) float g_attn_noalloc_scratch[TSB_ATTN_NOALLOC_MAX_FLOATS];
 
 static float* g_attn_noalloc_ptr[64] = {nullptr};
+static cudaError_t g_attn_noalloc_err[64];
+static std::once_flag g_attn_noalloc_once[64];
 
 extern "C" long tsb_attn_decode_noalloc_capacity(void) { return (long)TSB_ATTN_NOALLOC_MAX_FLOATS; }
 
 extern "C" int tsb_attn_decode_noalloc(const AttnArgs* args, void* stream) {
     TSB_CHECK_ARG(args != nullptr, "attn_decode_noalloc: null arguments");
     AttnArgs a = *args;
-    a.ticket = nullptr;                 // this entry point keeps the two-kernel form
     TSB_CHECK_ARG(a.B >= 0 && a.Hq > 0 && a.Dh > 0 && a.splits >= 1, "attn_decode_noalloc: bad sizes B=%d Hq=%d Dh=%d splits=%d",
                   a.B, a.Hq, a.Dh, a.splits);
     TSB_CHECK_ARG(a.splits <= 64, "attn_decode_noalloc: %d splits (limit 64)", a.splits);
@@ -426,16 +432,19 @@ extern "C" int tsb_attn_decode_noalloc(const AttnArgs* args, void* stream) {
     int dev = -1;
     TSB_CHECK_CUDA(cudaGetDevice(&dev));
     TSB_CHECK_ARG(dev >= 0 && dev < 64, "attn_decode_noalloc: device ordinal %d out of range", dev);
-    if (g_attn_noalloc_ptr[dev] == nullptr) {
-        // one-time set-up for this device (current device == dev): resolve the device address
+    // one-time set-up for this device (current device == dev): resolve the array's device address.  call_once makes
+    // two host threads that reach their first call on one device together agree on one lookup.
+    std::call_once(g_attn_noalloc_once[dev], [dev]() {
         float* p = nullptr;
-        TSB_CHECK_CUDA(cudaGetSymbolAddress((void**)&p, g_attn_noalloc_scratch));
-        g_attn_noalloc_ptr[dev] = p;
-    }
+        g_attn_noalloc_err[dev] = cudaGetSymbolAddress((void**)&p, g_attn_noalloc_scratch);
+        if (g_attn_noalloc_err[dev] == cudaSuccess) g_attn_noalloc_ptr[dev] = p;
+    });
+    TSB_CHECK_CUDA(g_attn_noalloc_err[dev]);
     float* base = g_attn_noalloc_ptr[dev];
     a.part_o = base;                       // [B, Hq, splits, Dh]
     a.part_ml = base + slots * a.Dh;       // [B, Hq, splits, 2]
-    return tsb_attn_decode(&a, stream);
+    // always the two-kernel form: the in-kernel split merge would bring in a second shared array (its arrival tickets)
+    return attn_decode_impl(&a, stream, false);
 }
 
 // ------------------------------------------------------------------------------------------

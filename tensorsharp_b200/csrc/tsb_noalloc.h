@@ -20,11 +20,14 @@
 //     library holds those 16 MiB until the process exits.
 //   * The first call on each device looks up the array's device address
 //     (cudaGetSymbolAddress, with that device current) and caches it; make that first call
-//     before starting any stream capture.
+//     before starting any stream capture.  The lookup is guarded per device (std::call_once),
+//     so host threads may race to that first call.
 //   * All calls on a device share the one array and it keeps the previous call's contents.
 //     Nothing in it has to start at zero: every slot the combine pass reads is written by
 //     the partial pass of the same call first.  Two calls that overlap on the GPU (different
-//     streams, no ordering between them) race on the array; order them.
+//     streams, no ordering between them) race on the array; order them.  This entry point
+//     always runs the two-kernel form (partials, then combine), whatever TSB_ATTN_FUSED_COMBINE
+//     says, so the scratch array is the only state that calls share.
 //   * args->part_o and args->part_ml are ignored; everything else in AttnArgs (inputs,
 //     output, sizes) is passed by the caller exactly as for tsb_attn_decode().
 #pragma once

@@ -367,6 +367,7 @@ class ModelBase:
     def forward(self, tokens: Sequence[int], want_logits: bool = True) -> Optional[torch.Tensor]:
         """Append ``tokens`` to the default sequence and return the next-token logits
         (float32 ``[vocab]`` on the compute device).  IModelArchitecture.Forward."""
+        self.poll_status()
         if len(tokens) == 1 and self._graph_forward_ok():
             with self.timer.phase("decode"):
                 out = self._graph_stepper().step(tokens[0])
@@ -420,6 +421,65 @@ class ModelBase:
                 if e is not None and hasattr(e, "check"):
                     e.check()
 
+    # Status words of the bounded device-side waits.  A wait that ran out makes its kernel carry on with zeros and
+    # leaves a code in a device word; nothing on the device stops.  The token loops therefore look at those words
+    # themselves: every ``STATUS_POLL_EVERY`` calls of ``forward`` the words are copied to pinned host memory behind
+    # the step (no synchronisation), and the copy made by an earlier call, long complete by then because the host
+    # has read that call's logits since, is examined.  A non-zero word ends the request with ExchangeTimeoutError
+    # (HTTP 500 on the front end; a follower process leaves its loop and exits).
+    STATUS_POLL_EVERY = 16
+
+    def status_sources(self):
+        """``(name, int32 device tensor of one element)`` for every status word this model's kernels may set."""
+        out = []
+        if self.device.type != "cuda":
+            return out
+        from ..ops import kernels
+        out.append(("tcgen05 GEMM pipeline", kernels.gemm_status(self.device)))
+        x = self.__dict__.get("_tpx")
+        if x:
+            out.append(("tensor-parallel mailbox exchange", x.counters[4:5]))
+        x = self.__dict__.get("_tpseq")
+        if x:
+            out.append(("sequence-parallel prefill exchange", x.local[8:9]))
+        x = self.__dict__.get("_cpa")
+        if x is not None:
+            out.append(("context-parallel attention", x.local[4:5]))
+        x = self.__dict__.get("_mega")
+        if x:
+            out.append(("fused decode step", x.status_word))
+        return out
+
+    def raise_on_status(self, names, values) -> None:
+        from ..parallel.errors import ExchangeTimeoutError
+        for name, v in zip(names, values):
+            if int(v):
+                raise ExchangeTimeoutError(name, int(v))
+
+    def poll_status(self, force: bool = False) -> None:
+        """See the note above ``STATUS_POLL_EVERY``.  ``force`` synchronises and checks the words as they are now."""
+        st = self.__dict__.setdefault("_status_poll", {"n": 0, "pending": None})
+        if force or self.device.type != "cuda":
+            src = self.status_sources()                 # host tensors (a test's stand-in) are read as they are
+            if src:
+                if self.device.type == "cuda":
+                    torch.cuda.synchronize(self.device)
+                self.raise_on_status([n for n, _ in src], [int(t.item()) for _, t in src])
+            return
+        pend = st["pending"]
+        if pend is not None and pend[2].query():
+            st["pending"] = None
+            self.raise_on_status(pend[0], pend[1].tolist())
+        st["n"] += 1
+        if st["pending"] is None and st["n"] % self.STATUS_POLL_EVERY == 1:
+            src = self.status_sources()
+            if src:
+                host = torch.empty(len(src), dtype=torch.int32).pin_memory()
+                host.copy_(torch.cat([t.reshape(1) for _, t in src]), non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record()
+                st["pending"] = ([n for n, _ in src], host, ev)
+
     def forward_refill(self, tokens: Sequence[int], chunk: int = 2048) -> torch.Tensor:
         """Chunked prefill: all chunks but the last skip the logits (Qwen3Model.cs:238
         ForwardRefill; chunk size policy TensorSharp.Server/ModelService.cs:791-801)."""
@@ -436,10 +496,15 @@ class ModelBase:
             self.reset_recurrent_state(self._default_seq.slot)
 
     def truncate_kv_cache(self, n_tokens: int) -> None:
+        """Keep the first ``n_tokens`` of the default sequence.  Keeping everything is always allowed (the second
+        turn of a chat re-uses the whole cache: ModelBase.TruncateKVCache is a no-op there); a model with recurrent
+        state refuses only a real shrink, which its state cannot follow."""
+        seq = self._default_seq
+        if seq is None or n_tokens >= seq.length:
+            return
         if not self.supports_kv_truncation:
             raise RuntimeError(f"{type(self).__name__} cannot truncate its cache (recurrent state)")
-        if self._default_seq is not None:
-            self.kv.truncate(self._default_seq, n_tokens)
+        self.kv.truncate(seq, n_tokens)
 
     def warm_up_kernels(self) -> None:
         """Run one short prefill and one decode step so lazy initialisation (cuBLAS handles,

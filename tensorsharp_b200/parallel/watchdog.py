@@ -52,13 +52,13 @@ class Heartbeat:
             if v == "left":
                 stale.add(r)
                 continue
+            # a key that is still absent (the peer has not registered yet) is one more unchanged value: the peer
+            # is stale only once nothing has changed for ``timeout_s``, so start-up skew within the timeout is fine
             last = self._seen.get(r)
             if last is None or last[0] != v:
                 self._seen[r] = (v, now)
-            elif v is None or now - last[1] > timeout_s:
+            elif now - last[1] > timeout_s:
                 stale.add(r)
-            if v is None and last is None:
-                self._seen[r] = (None, now)
         return stale
 
     def check(self, timeout_s: float) -> None:

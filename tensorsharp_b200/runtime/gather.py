@@ -212,11 +212,12 @@ class SlotModel:
 
     def truncate_kv_cache(self, n_tokens: int) -> None:
         m = self._owner.model
+        if self._seq is None or n_tokens >= self._seq.length:      # keeping the whole cache is not a truncation
+            return
         if not m.supports_kv_truncation:
             raise RuntimeError(f"{type(m).__name__} cannot truncate its cache (recurrent state)")
-        if self._seq is not None:
-            with self._owner.model_lock:
-                m.kv.truncate(self._seq, n_tokens)
+        with self._owner.model_lock:
+            m.kv.truncate(self._seq, n_tokens)
 
     def warm_up_kernels(self) -> None:
         if self._index == 0:

@@ -356,3 +356,47 @@ def test_front_end_fails_a_call_instead_of_waiting_for_a_departed_follower(tiny_
         p.join(timeout=30)
     assert got["left"] == "forward"
     assert got["leader"] == (True, [1])
+
+
+def test_heartbeat_tolerates_a_peer_that_registers_late():
+    """A peer whose key is still absent counts as one more unchanged value: it is stale only after ``timeout_s``."""
+    store, now = DictStore(), [0.0]
+    hb0, hb1 = Heartbeat(store, 0, 2, clock=lambda: now[0]), Heartbeat(store, 1, 2, clock=lambda: now[0])
+    hb0.beat()
+    for t in (0.0, 0.2, 0.4, 5.0, 29.0):            # polls while rank 1 has not registered: inside the timeout
+        now[0] = t
+        assert hb0.stale_ranks(30.0) == set()
+    now[0] = 29.5
+    hb1.beat()                                      # registers late, but in time
+    assert hb0.stale_ranks(30.0) == set()
+    now[0] = 55.0
+    assert hb0.stale_ranks(30.0) == set()           # 25.5 s since its first beat
+    now[0] = 61.0
+    assert hb0.stale_ranks(30.0) == {1}
+    # a peer that never registers is reported once the timeout has passed
+    store2 = DictStore()
+    lone = Heartbeat(store2, 0, 2, clock=lambda: now[0])
+    now[0] = 100.0
+    assert lone.stale_ranks(30.0) == set()
+    now[0] = 131.0
+    assert lone.stale_ranks(30.0) == {1}
+
+
+def test_token_loop_raises_when_a_device_wait_ran_out(tmp_path):
+    """The kernels' bounded waits only leave a status word behind; the token loop has to look at it.  With a stand-in
+    status word set, the next ``forward`` ends in ExchangeTimeoutError instead of streaming tokens computed from zeros."""
+    import torch
+    from tensorsharp_b200.models import synth
+    from tensorsharp_b200.models.base import ModelBase
+    from tensorsharp_b200.parallel.errors import ExchangeTimeoutError
+    p = str(tmp_path / "m.gguf")
+    synth.write_qwen3(p, **synth.QWEN3_TINY, device="cpu")
+    m = ModelBase.create(p, device="cpu")
+    word = torch.zeros(1, dtype=torch.int32)
+    m.status_sources = lambda: [("stand-in exchange", word)]
+    m.forward([1, 2, 3])                              # healthy: nothing raised
+    word[0] = 3
+    with pytest.raises(ExchangeTimeoutError) as e:
+        m.forward([4])
+    assert e.value.code == 3 and "stand-in exchange" in str(e.value)
+    m.close()

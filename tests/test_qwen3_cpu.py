@@ -1,4 +1,5 @@
 """Tiny Qwen3 on the CPU oracle path: cache consistency, truncation, chunked prefill."""
+import pytest
 import torch
 
 from tensorsharp_b200.models.base import ModelBase
@@ -44,6 +45,10 @@ def test_batched_equals_single(tiny_qwen3_path):
         l = m.forward([t])
         t = int(l.argmax())
         assert got[s][1] == t
+    # the step runner refuses to go past the context it reserved (longest prompt 20 + 4 new tokens + 1)
+    dg.step(); dg.step()
+    with pytest.raises(RuntimeError, match="sized for a context"):
+        dg.step()
 
 
 def test_generate_and_benchmark(tiny_qwen3_path):

@@ -826,3 +826,60 @@ def test_metrics_endpoint_counts_generations(tmp_path):
     assert vals['tensorsharp_http_responses_total{client="ollama",status="2xx"}'] == "1"
     assert vals['tensorsharp_http_responses_total{client="ollama",status="4xx"}'] == "1"
     assert "# TYPE tensorsharp_generated_tokens_total counter" in m.text
+
+
+@pytest.mark.parametrize("family", ["qwen35", "nemotron_h"])
+def test_second_turn_on_models_that_cannot_truncate(tmp_path, family):
+    """A model with recurrent state refuses to shrink its cache, but the second turn of a chat only extends it: the
+    re-use plan keeps the whole cache and the turn must go through (server path and CLI path, real synthetic models)."""
+    from tensorsharp_b200.cli.main import apply_reuse_plan
+    from tensorsharp_b200.models import synth
+    from tensorsharp_b200.models.base import ModelBase
+    from tensorsharp_b200.runtime.kv_cache import KVCache, ReusePlanKind
+    path = str(tmp_path / f"{family}.gguf")
+    getattr(synth, "write_" + family)(path, device="cpu")
+    opts = build_options(["--model", path, "--backend", "cpu", "--port", "0", "--temperature", "0", "--top-k", "0",
+                          "--top-p", "1", "--repeat-penalty", "1"], str(tmp_path), env={"TENSORSHARP_LOG_FILE": "0"})
+    app = ServerApp(opts)
+    httpd = serve(app, "127.0.0.1", 0)
+    port = httpd.server_address[1]
+    th = threading.Thread(target=httpd.serve_forever, daemon=True)
+    th.start()
+    try:
+        def chat(messages, n):
+            c = http.client.HTTPConnection("127.0.0.1", port, timeout=120)
+            c.request("POST", "/api/chat", json.dumps({"messages": messages, "maxTokens": n}), {"Content-Type": "application/json"})
+            data = c.getresponse().read().decode()
+            c.close()
+            return [json.loads(l[6:]) for l in data.split("\n\n") if l.startswith("data: ")]
+        c = http.client.HTTPConnection("127.0.0.1", port, timeout=120)       # the first request that names the model loads it
+        c.request("POST", "/api/generate", json.dumps({"model": os.path.basename(path), "prompt": "Hi", "stream": False,
+                                                       "options": {"num_predict": 2}}), {"Content-Type": "application/json"})
+        assert c.getresponse().status == 200
+        c.close()
+        ev = chat([{"role": "user", "content": "Hello"}], 4)
+        assert ev[-1]["done"] and ev[-1]["error"] is None
+        reply = "".join(e.get("token", "") for e in ev)
+        ev2 = chat([{"role": "user", "content": "Hello"}, {"role": "assistant", "content": reply},
+                    {"role": "user", "content": "again"}], 3)
+        assert ev2[-1]["done"] and ev2[-1]["error"] is None
+        assert ev2[-1]["kvReusedTokens"] >= ev[-1]["promptTokens"]
+    finally:
+        httpd.shutdown()
+        httpd.server_close()
+        app.svc.close()
+    # the CLI's re-use path on the same kind of model
+    model = ModelBase.create(path, device="cpu")
+    assert not model.supports_kv_truncation
+    kv = KVCache()
+    first = [5, 6, 7, 8, 9]
+    logits = model.forward(first)
+    kv.record_append(first, logits)
+    second = first + [10, 11]
+    plan = kv.plan_reuse(second, model.supports_kv_truncation)
+    assert plan.kind == ReusePlanKind.PARTIAL_REUSE and plan.reused_prefix_length == len(first)
+    out = apply_reuse_plan(model, kv, plan, second)
+    assert out is not None and kv.count == len(second)
+    with pytest.raises(RuntimeError):
+        model.truncate_kv_cache(2)                  # a real shrink is still refused
+    model.close()
