@@ -99,6 +99,16 @@ class Qwen3Model(ModelBase):
         if self.pp_size > 1:
             return self.forward_stage(batch, want_logits)
         in_cp = self.__dict__.get("_cp_ctx") is not None
+        if T == 1 and batch.is_decode and batch.B == 1 and not in_cp and not self._pending_embeddings:
+            mega = self.mega_decoder()
+            if mega is not None:
+                # one sequence, one token: the whole step is one persistent kernel (ops/mega.py)
+                logits = mega.step(batch)
+                if not want_logits:
+                    return None
+                if self.vocab_sharded:
+                    return self.comm.all_gather_cat(logits, dim=1)
+                return logits if torch.cuda.is_current_stream_capturing() else logits.clone()
         if self.cp_wanted(batch) and not in_cp:
             # new sequence, equal slices, GPUs: attention pulls the earlier slices from peer memory; otherwise the general
             # route (two balanced pieces per rank, caches completed layer by layer)
@@ -349,6 +359,21 @@ class Qwen3Model(ModelBase):
 
     def q_post_scale(self, qr: torch.Tensor, batch: Batch) -> torch.Tensor:
         return qr
+
+    def mega_decoder(self):
+        """The one-kernel decode step for this model, or ``None`` when it does not apply (CPU, pipeline stages, a
+        graph or weight types the kernel does not cover, ``TSB_MEGA=0``).  Built on first use."""
+        m = self.__dict__.get("_mega")
+        if m is None:
+            m = False
+            ok = (self.device.type == "cuda" and self.pp_size == 1 and os.environ.get("TSB_MEGA", "1") != "0"
+                  and type(self).q_post_scale is Qwen3Model.q_post_scale and self.kv_dtype == torch.bfloat16
+                  and (self.tp_size == 1 or os.environ.get("TSB_TP_FUSED", "1") != "0"))
+            if ok:
+                from ..ops.mega import MegaDecoder
+                m = MegaDecoder.try_create(self) or False
+            self.__dict__["_mega"] = m
+        return m or None
 
     def row_parallel(self, a, w: QuantWeight, h: torch.Tensor) -> torch.Tensor:
         """h + a @ w^T where ``w`` holds this rank's slice of the input features: the partial
