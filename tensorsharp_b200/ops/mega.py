@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 from typing import List, Optional
 
 import torch
@@ -46,7 +47,7 @@ class MegaArgs(C.Structure):
                 ("xbuf", C.c_void_p * MAX_RANKS), ("rank", C.c_int), ("size", C.c_int),
                 ("off_qkv", C.c_long), ("off_part", C.c_long), ("off_attn", C.c_long), ("off_opr", C.c_long),
                 ("off_act", C.c_long), ("off_dwn", C.c_long), ("step", C.c_void_p), ("status", C.c_void_p), ("prof", C.c_void_p),
-                ("splits", C.c_int), ("grid", C.c_int), ("stage_bytes", C.c_int), ("n_stages", C.c_int),
+                ("debug", C.c_int), ("splits", C.c_int), ("grid", C.c_int), ("stage_bytes", C.c_int), ("n_stages", C.c_int),
                 ("off_h", C.c_int), ("off_xq", C.c_int), ("off_xds", C.c_int), ("off_bsum_words", C.c_int), ("off_qs", C.c_int), ("off_red", C.c_int),
                 ("off_ring", C.c_int), ("smem_bytes", C.c_int)]
 
@@ -145,6 +146,7 @@ class MegaDecoder:
         a.rope_freq, a.rope_mscale = self.rope_freq.data_ptr(), rope_mscale(rope)
         a.rot_dim, a.rope_mode, a.act = int(rope.rot_dim), int(rope.mode), ACT[act]
         a.rank, a.size = (comm.rank, comm.size) if comm is not None else (0, 1)
+        a.debug = int(os.environ.get("TSB_MEGA_DEBUG", "0"))
         words = lib.tsb_mega_xbuf_words(C.byref(a))
         if comm is not None:
             from ..parallel.symm import SymmetricBuffer
@@ -178,14 +180,16 @@ class MegaDecoder:
         q.p0, q.p1, q.p2, q.p3 = (p.data_ptr() if p is not None else None for p in ps)
         q.type, q.N, q.K = int(w.ggml_type), w.N, w.K
 
-    PROFILE_SLOTS = ("-", "wait down + norm", "qkv rows", "attention", "merge", "wait attention", "o_proj rows", "-",
+    PROFILE_SLOTS = ("of the rows: hoisting", "wait down + norm", "qkv rows", "attention", "merge", "wait attention", "o_proj rows",
+                     "of the rows: dot products",
                      "wait o_proj + norm", "gate/up rows", "wait activations", "down rows", "final wait + norm", "lm_head rows",
-                     "of the rows: waiting for stages", "tasks (count)")
+                     "of the rows: waiting for stages", "tasks (count)", "attention: wait for q", "attention: norm + rope",
+                     "attention: keys and values", "attention: merge of the warps")
 
     def enable_profile(self) -> torch.Tensor:
         """Diagnostics: from now on every step overwrites a ``[grid, 16]`` table of nanoseconds that thread 0 of each
         CTA spent per phase (summed over the layers; slot names in ``PROFILE_SLOTS``).  Costs a timer read per phase."""
-        self.prof = torch.zeros((self.args.grid, 16), dtype=torch.int64, device=self.model.device)
+        self.prof = torch.zeros((self.args.grid, 24), dtype=torch.int64, device=self.model.device)
         self.args.prof = self.prof.data_ptr()
         return self.prof
 

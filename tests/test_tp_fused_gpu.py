@@ -149,3 +149,28 @@ def test_context_parallel_prefill_over_peer_memory(kv8_model_path):
     assert p.returncode == 0 and lines, f"rc={p.returncode}\nstdout:\n{p.stdout[-3000:]}\nstderr:\n{p.stderr[-3000:]}"
     r = json.loads(lines[0][8:])
     assert r["status"] == 0 and max(r["rel_err"]) < 5e-2, r
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+def test_fused_decode_step_with_tensor_parallel_ranks(n, tmp_path_factory):
+    """The one-kernel decode step on N ranks: partial sums of o_proj / down cross NVLink as tagged words written by
+    the kernel itself.  Same logits as one GPU (fused step and per-op path), identical on all ranks, no wait ran out,
+    and a captured graph reproduces the eager tokens."""
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+    from tensorsharp_b200.models import synth
+    path = str(tmp_path_factory.mktemp("mega") / "qwen3_q4km.gguf")
+    synth.write_qwen3(path, n_layers=2, hidden=1024, n_heads=32, n_kv_heads=8, head_dim=64, ffn=4096, vocab=8192, scheme="Q4_K_M",
+                      device="cpu")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TSB_WORKER_MODE="mega")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(HERE, "tp_worker.py"), path]
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    lines = [l for l in p.stdout.splitlines() if l.startswith("MEGACHECK ")]
+    assert p.returncode == 0 and lines, f"rc={p.returncode}\nstdout:\n{p.stdout[-3000:]}\nstderr:\n{p.stderr[-3000:]}"
+    r = json.loads(lines[0][10:])
+    print(r)
+    assert r["engaged"] and r["status"] == 0, r
+    assert r["spread"] == 0.0, r
+    assert r["tp_vs_single_mega"] < 0.05 and r["tp_vs_single_plain"] < 0.12, (r["tp_vs_single_mega"], r["tp_vs_single_plain"], r["mega_vs_plain"])
+    assert r["graph_tokens"] == r["eager_tokens"], r

@@ -18,6 +18,11 @@ def main():
         comm.barrier()
         torch.cuda.synchronize()
         os._exit(0)
+    if os.environ.get("TSB_WORKER_MODE") == "mega":
+        check_mega(sys.argv[1], comm)
+        comm.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
     if os.environ.get("TSB_WORKER_MODE") == "cp_model":
         check_context_parallel_model(sys.argv[1], comm)
         comm.barrier()
@@ -101,6 +106,62 @@ def check_context_parallel_model(path, comm):
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     if comm.rank == 0:
         print("CPMODEL " + json.dumps({"world": world, "rel_err": [float(x) for x in t[:3]], "status": int(t[3])}), flush=True)
+
+
+def check_mega(path, comm):
+    """The one-kernel decode step with tensor parallelism: the row-parallel projections store their tagged partial
+    sums into every rank's buffer from inside the kernel.  Logits against one GPU (per-op path and fused step),
+    bit-equality across ranks, and the same tokens through a captured graph."""
+    from tensorsharp_b200.models.base import ModelBase
+    from tensorsharp_b200.runtime.engine import DecodeGraph
+    rank, world = comm.rank, comm.size
+    os.environ["TSB_GRAPH_FORWARD"] = "0"
+    g = torch.Generator().manual_seed(13)
+    prompt = torch.randint(0, 8192, (70,), generator=g).tolist()
+
+    follow = [int(t) for t in torch.randint(0, 8192, (6,), generator=g)]     # every run is fed the same tokens
+
+    def run(model):
+        model.reset_kv_cache()
+        out = [model.forward(prompt).float().clone()]
+        for t in follow:
+            out.append(model.forward([t]).float().clone())
+        return torch.stack(out)
+
+    model = ModelBase.create(path, comm.device, max_context=512, max_seqs=2, tp_rank=rank, tp_size=world, comm=comm)
+    md = model.mega_decoder()
+    tp = run(model)
+    status = md.status() if md is not None else -1
+    # every rank must hold the same logits bit for bit (same sums in the same order everywhere)
+    lo, hi = tp.clone(), tp.clone()
+    import torch.distributed as dist
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    spread = float((hi - lo).abs().max())
+    model.reset_kv_cache()
+    first = int(model.forward(prompt).argmax())
+    dg = DecodeGraph(model, [model._seq()], 8)
+    dg.set_tokens([first])
+    dg.capture()
+    graph_tokens = [first] + [int(dg.step()[0]) for _ in range(5)]
+    model.reset_kv_cache()                                    # the same greedy run, one eager step at a time
+    eager_tokens = [int(model.forward(prompt).argmax())]
+    for _ in range(5):
+        eager_tokens.append(int(model.forward([eager_tokens[-1]]).argmax()))
+    status |= md.status() if md is not None else 0
+    res = {"world": world, "engaged": md is not None, "status": status, "spread": spread, "graph_tokens": graph_tokens,
+           "eager_tokens": eager_tokens, "launches_per_step": dg.launches_per_step}
+    if rank == 0:
+        single = ModelBase.create(path, comm.device, max_context=512)
+        ref_mega = run(single)
+        single.__dict__["_mega"] = False
+        ref_plain = run(single)
+        rel = lambda a, b: float((a - b).norm() / b.norm())
+        res["tp_vs_single_mega"] = rel(tp[1:], ref_mega[1:])
+        res["tp_vs_single_plain"] = rel(tp[1:], ref_plain[1:])
+        res["mega_vs_plain"] = rel(ref_mega[1:], ref_plain[1:])
+        print("MEGACHECK " + json.dumps(res), flush=True)
+    comm.barrier()
 
 
 def check_model(path, comm):
