@@ -288,7 +288,6 @@ struct Producer {
     unsigned t;                    // tasks issued
     Ctl ctl;
     int stage, round;              // stage of the next task and how many times the ring has wrapped
-
     __device__ bool task(const MegaMat& m, int row0, int n, int glu_F) {
         if (*ctl.dead) return false;
         const int s = stage;
@@ -386,8 +385,10 @@ __device__ __forceinline__ void mg_mbar_wait_addr(uint32_t addr, uint32_t parity
 // Shared-space addresses of a local row's data inside the stage.
 struct RowPtr { uint32_t p0, p1, p2, p3; };
 
-// The activation vector in shared memory: int8 values, one scale per 256, sums of the int8 values per 16.
-struct ActMem { uint32_t xq, xd, bsum; };
+// The activation vector in shared memory: int8 values, one scale per 256, sums of the int8 values per 16.  The
+// values are stored in 16-byte chunks, chunk (block b, c) at ((c & 3) * 4 nb + 4 b + (c >> 2)) * 16: the lanes of a
+// warp work on neighbouring 64-value units, and this way their 16-byte loads fall on different banks.
+struct ActMem { uint32_t xq, xd, bsum, plane; };                   // plane = 4 nb * 16 bytes
 
 // Dot product of one 64-value unit of a row with the activations, scaled by the activation scale of its block.
 //   Q4_K unit = (block b, pair sub): sub-blocks 2 sub and 2 sub + 1; the low nibbles go with the first 32
@@ -397,11 +398,11 @@ template <bool Q6>
 __device__ __forceinline__ float unit_dot(const ActMem& am, const RowPtr& r, int b, int sub) {
     const float xd = __uint_as_float(lds32(am.xd + 4u * b));
     if (!Q6) {
-        const uint32_t xo = am.xq + 256u * b + 64u * sub;
+        const uint32_t xo = am.xq + 64u * b + 16u * sub;
         const uint4 hdr = lds128(r.p0 + 144u * b);
         const uint4 qa = lds128(r.p0 + 144u * b + 16u + 32u * sub);
         const uint4 qb = lds128(r.p0 + 144u * b + 32u + 32u * sub);
-        const uint4 x0 = lds128(xo), x1 = lds128(xo + 16), x2 = lds128(xo + 32), x3 = lds128(xo + 48);
+        const uint4 x0 = lds128(xo), x1 = lds128(xo + am.plane), x2 = lds128(xo + 2u * am.plane), x3 = lds128(xo + 3u * am.plane);
         const uint4 bq = lds128(am.bsum + 64u * b + 16u * sub);
         int s0 = 0, s1 = 0;
         s0 = dp4a_us(qa.x & 0x0F0F0F0Fu, (int)x0.x, s0); s0 = dp4a_us(qa.y & 0x0F0F0F0Fu, (int)x0.y, s0);
@@ -425,14 +426,14 @@ __device__ __forceinline__ float unit_dot(const ActMem& am, const RowPtr& r, int
         return xd * (dd.x * 0.0625f * (float)iS - dd.y * (float)iM);
     } else {
         const int n = sub >> 1, h = sub & 1;
-        const uint32_t xo = am.xq + 256u * b + 128u * n + 16u * h;
+        const uint32_t xo = am.xq + 64u * b + 32u * n + h * am.plane;          // group k: chunk 8 n + 2 k + h
         const uint32_t o0 = 128u * b + 64u * n + 16u * h;
         const uint4 A = lds128(r.p0 + o0);
         const uint4 B = lds128(r.p0 + o0 + 32);
         const uint4 H = lds128(r.p1 + 64u * b + 32u * n + 16u * h);
         const uint2 sc8 = lds64(r.p2 + 16u * b + 8u * n);
         const float d = __half2float(__ushort_as_half(lds16(r.p3 + 2u * b)));
-        const uint4 x0 = lds128(xo), x1 = lds128(xo + 32), x2 = lds128(xo + 64), x3 = lds128(xo + 96);
+        const uint4 x0 = lds128(xo), x1 = lds128(xo + 2u * am.plane), x2 = lds128(xo + 16u), x3 = lds128(xo + 16u + 2u * am.plane);
         const uint4 ba = lds128(am.bsum + 64u * b + 32u * n), bb = lds128(am.bsum + 64u * b + 32u * n + 16u);
         const uint32_t a[4] = {A.x, A.y, A.z, A.w}, bw[4] = {B.x, B.y, B.z, B.w}, hw[4] = {H.x, H.y, H.z, H.w};
         const int xa[4] = {(int)x0.x, (int)x0.y, (int)x0.z, (int)x0.w}, xb[4] = {(int)x1.x, (int)x1.y, (int)x1.z, (int)x1.w};
@@ -515,7 +516,7 @@ __device__ __forceinline__ void run_rows(Consumer& c, int K, int r0, int r1, int
     const int up = (be - bs) * 4;                                    // units per row part, <= 64
     const int total = rw * up;                                       // items of a warp's share of a task, <= 256
     const unsigned inv = (65536u + up - 1) / up;                     // (it * inv) >> 16 == it / up for it < 256
-    const ActMem am{tc::smem_u32(c.xq), tc::smem_u32(c.xd), tc::smem_u32(c.bsum)};
+    const ActMem am{tc::smem_u32(c.xq), tc::smem_u32(c.xd), tc::smem_u32(c.bsum), (uint32_t)nb * 64u};
     const int step = glu_F > 0 ? rt / 2 : rt;
     const uint32_t rb0 = Q6 ? nb * 128u : nb * 144u, rb1 = nb * 64u, rb2 = nb * 16u, rb3 = nb * 2u;
     for (int r = r0; r < r1; r += step) {
@@ -601,7 +602,7 @@ __device__ __forceinline__ void run_rows(Consumer& c, int K, int r0, int r1, int
 }
 
 // 256 values (8 consecutive per lane) -> one int8 block: scale amax / 127, sums of the int8 values per 16.
-__device__ __forceinline__ void quant_block(const float (&v)[8], int8_t* xq, float* xd, int* bsum, int block, int lane) {
+__device__ __forceinline__ void quant_block(const float (&v)[8], int8_t* xq, float* xd, int* bsum, int block, int nblk, int lane) {
     float am = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) am = fmaxf(am, fabsf(v[i]));
@@ -613,7 +614,8 @@ __device__ __forceinline__ void quant_block(const float (&v)[8], int8_t* xq, flo
     uint2 pk;
     pk.x = (uint32_t)(q[0] & 0xFF) | ((uint32_t)(q[1] & 0xFF) << 8) | ((uint32_t)(q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
     pk.y = (uint32_t)(q[4] & 0xFF) | ((uint32_t)(q[5] & 0xFF) << 8) | ((uint32_t)(q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
-    *reinterpret_cast<uint2*>(xq + block * 256 + lane * 8) = pk;
+    const int cb = lane >> 1;                                          // chunk within the block; see ActMem for the layout
+    *reinterpret_cast<uint2*>(xq + (((cb & 3) * 4 * nblk + 4 * block + (cb >> 2)) << 4) + (lane & 1) * 8) = pk;
     s += __shfl_xor_sync(0xffffffffu, s, 1);
     if (!(lane & 1)) bsum[block * 16 + (lane >> 1)] = s;
     if (lane == 0) xd[block] = am / 127.f;
@@ -975,7 +977,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const MegaAr
                     float v[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) v[i] = hv[j][i] * rs * wv[j][i];
-                    quant_block(v, xq, xd, bsum, b, lane);
+                    quant_block(v, xq, xd, bsum, b, nblk, lane);
                 }
             }
         } else {
@@ -997,7 +999,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const MegaAr
                 float v[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) v[i] = h[b * 256 + lane * 8 + i] * rs * w[b * 256 + lane * 8 + i];
-                quant_block(v, xq, xd, bsum, b, lane);
+                quant_block(v, xq, xd, bsum, b, nblk, lane);
             }
         }
         cons_sync();
@@ -1024,7 +1026,7 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const MegaAr
                         x[2 * i] = __uint_as_float(w << 16);
                         x[2 * i + 1] = __uint_as_float(w & 0xffff0000u);
                     }
-                    quant_block(x, xq, xd, bsum, b, lane);
+                    quant_block(x, xq, xd, bsum, b, nblk, lane);
                 }
             }
         }

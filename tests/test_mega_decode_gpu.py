@@ -25,6 +25,7 @@ def _rel(a, b):
 @pytest.mark.parametrize("name", list(SHAPES))
 def test_fused_step_matches_per_op_path_and_oracle(tmp_path, name, monkeypatch):
     monkeypatch.setenv("TSB_GRAPH_FORWARD", "0")         # eager single-token steps: the kernel is launched directly
+    monkeypatch.setenv("TSB_MEGA", "1")                  # on one GPU the fused step is opt-in
     p = str(tmp_path / "m.gguf")
     synth.write_qwen3(p, **SHAPES[name], scheme="Q4_K_M", device="cpu")
     cpu = ModelBase.create(p, "cpu", max_context=512)
@@ -59,8 +60,9 @@ def test_fused_step_matches_per_op_path_and_oracle(tmp_path, name, monkeypatch):
     assert _rel(nxt, again) < 0.12
 
 
-def test_fused_step_inside_a_captured_graph(tmp_path):
+def test_fused_step_inside_a_captured_graph(tmp_path, monkeypatch):
     """Greedy decode through DecodeGraph (the captured step contains the fused kernel) follows the eager per-op run."""
+    monkeypatch.setenv("TSB_MEGA", "1")
     from tensorsharp_b200.ops import functional as F
     from tensorsharp_b200.runtime.engine import DecodeGraph
     p = str(tmp_path / "m.gguf")

@@ -152,6 +152,7 @@ def check_mega(path, comm):
     res = {"world": world, "engaged": md is not None, "status": status, "spread": spread, "graph_tokens": graph_tokens,
            "eager_tokens": eager_tokens, "launches_per_step": dg.launches_per_step}
     if rank == 0:
+        os.environ["TSB_MEGA"] = "1"
         single = ModelBase.create(path, comm.device, max_context=512)
         ref_mega = run(single)
         single.__dict__["_mega"] = False
