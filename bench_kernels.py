@@ -3,6 +3,8 @@
 
     python bench_kernels.py gemv --type Q4_K --n 19456 --k 2560 --glu --m 1
     python bench_kernels.py gemv --type Q4_K --n 2560 --k 9728
+    python bench_kernels.py recurrent --op gdn --t 2048
+    python bench_kernels.py recurrent --op mamba2 --t 2048
 
 Each call cycles through enough copies of the weight matrix to exceed the 126 MB L2, so every launch
 streams from HBM; the figure printed is the mean over ``--iters`` launches between two CUDA events,
@@ -20,9 +22,80 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 
+def time_us(fn, iters: int, warmup: int) -> float:
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / iters
+
+
+def recurrent(args):
+    """The token-by-token scan kernel against the chunked form (tensor ops) on one prompt of ``--t`` tokens, at the
+    Qwen3.5-35B-A3B GatedDeltaNet shape (16 QK / 32 V heads x 128) or the Nemotron-H Mamba2 shape (64 heads x 64,
+    8 groups, state 128).  Prints both times and the distance between the two outputs."""
+    import torch
+    from tensorsharp_b200.ops import kernels
+    from tensorsharp_b200.ops import reference as ref
+    dev, T = "cuda", args.t
+    torch.manual_seed(0)
+    cu_q = torch.tensor([0, T], dtype=torch.int32, device=dev)
+    slots = torch.zeros(1, dtype=torch.int32, device=dev)
+    if args.op == "gdn":
+        Hk, Hv, Dk, Dv = 16, 32, 128, 128
+        qkv = torch.randn(T, 2 * Hk * Dk + Hv * Dv, device=dev)
+        z = torch.randn(T, Hv * Dv, device=dev)
+        beta, alpha = torch.randn(T, Hv, device=dev), torch.randn(T, Hv, device=dev)
+        dt_bias, a_log = torch.randn(Hv, device=dev) * 0.1, -torch.rand(Hv, device=dev)
+        norm_w = torch.ones(Dv, device=dev)
+        kw = dict(Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=1e-6)
+        s0 = torch.zeros(1, Hv, Dv, Dk, device=dev)
+        s1 = torch.zeros(Hv, Dv, Dk, device=dev)
+
+        def scan():
+            s0.zero_()
+            return kernels.gdn_recurrent(qkv, z, beta, alpha, dt_bias, a_log, norm_w, s0, cu_q, slots, **kw)
+
+        def chunked():
+            s1.zero_()
+            return ref.gdn_chunked(qkv, z, beta, alpha, dt_bias, a_log, norm_w, s1, chunk=args.chunk, **kw)
+    else:
+        H, P, G, N = 64, 64, 8, 128
+        xbc = torch.randn(T, H * P + 2 * G * N, device=dev)
+        dt = torch.randn(T, H, device=dev)
+        dt_bias, A, D = torch.randn(H, device=dev) * 0.1, -torch.rand(H, device=dev), torch.randn(H, device=dev)
+        kw = dict(H=H, P=P, G=G, N=N)
+        s0 = torch.zeros(1, H, P, N, device=dev)
+        s1 = torch.zeros(H, P, N, device=dev)
+
+        def scan():
+            s0.zero_()
+            return kernels.mamba2_recurrent(xbc, dt, dt_bias, A, D, s0, cu_q, slots, **kw)
+
+        def chunked():
+            s1.zero_()
+            return ref.mamba2_chunked(xbc, dt, dt_bias, A, D, s1, chunk=args.chunk, **kw)
+    a, b = scan().float(), chunked().float()
+    rel = float((a - b).norm() / b.norm())
+    srel = float((s0[0] - s1).norm() / s1.norm())
+    print(json.dumps({"kernel": "recurrent", "op": args.op, "T": T, "chunk": args.chunk,
+                      "scan_us": time_us(scan, args.iters, args.warmup),
+                      "chunked_us": time_us(chunked, args.iters, args.warmup),
+                      "rel_diff_out": rel, "rel_diff_state": srel}))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv"])
+    ap.add_argument("what", choices=["gemv", "recurrent"])
+    ap.add_argument("--op", default="gdn", choices=["gdn", "mamba2"])
+    ap.add_argument("--t", type=int, default=2048)
+    ap.add_argument("--chunk", type=int, default=64)
     ap.add_argument("--type", default="Q4_K")
     ap.add_argument("--n", type=int, default=19456)
     ap.add_argument("--k", type=int, default=2560)
@@ -31,6 +104,8 @@ def main():
     ap.add_argument("--iters", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     args = ap.parse_args()
+    if args.what == "recurrent":
+        return recurrent(args)
     import torch
     from tensorsharp_b200.gguf.constants import GGMLType
     from tensorsharp_b200.ops import kernels

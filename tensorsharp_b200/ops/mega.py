@@ -215,3 +215,41 @@ class MegaDecoder:
     def close(self) -> None:
         if hasattr(self.xbuf, "close"):
             self.xbuf.close()
+
+
+def phase_table(model, context: int = 2048, steps: int = 5) -> str:
+    """Per-phase time table of the fused decode step on ``model`` (one GPU): prefill ``context`` random tokens, run
+    ``steps`` decode steps with the in-kernel timers on and report, per slot of ``PROFILE_SLOTS``, the min / median /
+    max over the CTAs of the microseconds that thread 0 of the CTA spent there in the last step."""
+    md = model.mega_decoder()
+    if md is None:
+        raise RuntimeError("the fused decode step does not accept this model (set TSB_MEGA=1 on one GPU)")
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, model.cfg.vocab, (context,), generator=g).tolist()
+    t = int(model.forward(prompt).argmax())
+    prof = md.enable_profile()
+    for _ in range(steps):
+        t = int(model.forward([t]).argmax())
+    torch.cuda.synchronize()
+    us = prof.cpu().double() / 1e3
+    a = md.args
+    lines = [f"grid {a.grid}  stages {a.n_stages} x {a.stage_bytes} B  shared memory {a.smem_bytes} B  attention splits {a.splits}"]
+    tot = us[:, [1, 2, 3, 4, 5, 6, 8, 9, 10, 11, 12, 13]].sum(1)
+    lines.append("phases per CTA, us: min %.1f  median %.1f  max %.1f" % (tot.min(), tot.median(), tot.max()))
+    for i, name in enumerate(md.PROFILE_SLOTS):
+        c = us[:, i] * (1e3 if "count" in name else 1.0)
+        lines.append("%-34s min %8.1f  median %8.1f  max %8.1f" % (name, c.min(), c.median(), c.max()))
+    return "\n".join(lines)
+
+
+if __name__ == "__main__":
+    import argparse
+    import os
+    ap = argparse.ArgumentParser(description="phase table of the fused decode step for a GGUF model on cuda:0")
+    ap.add_argument("model")
+    ap.add_argument("--context", type=int, default=2048)
+    cli = ap.parse_args()
+    os.environ["TSB_MEGA"] = "1"
+    os.environ["TSB_GRAPH_FORWARD"] = "0"
+    from ..models.base import ModelBase
+    print(phase_table(ModelBase.create(cli.model, "cuda", max_context=cli.context + 256), cli.context))

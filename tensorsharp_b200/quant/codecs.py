@@ -7,7 +7,8 @@ hand-packed blocks on the CPU.
 
 Parity: TensorSharp.Models/ManagedQuantizedOps.cs:411 (Q8_0), :447-479 + :685 (Q4_K and
 its 6-bit scale/min unpacking), :520 (Q6_K), :579-598 + :678 (MXFP4 and its E8M0
-half-scale); ExternalProjects/ggml/src/ggml-quants.c for the remaining layouts.
+half-scale); ExternalProjects/ggml/src/ggml-quants.c for the remaining layouts (Q2_K, Q3_K, Q5_*, Q8_K, IQ4_NL / IQ4_XS,
+the codebook formats IQ2_* / IQ3_* / IQ1_*, the ternary TQ1_0 / TQ2_0).
 The quantisers are simple min/max fitters (not ggml's iterative search); they emit
 valid blocks, which is all a random-weight benchmark needs.
 """
@@ -54,6 +55,86 @@ def e8m0_to_fp32_half(e: torch.Tensor) -> torch.Tensor:
     bits = torch.where(e < 2, torch.tensor(0x00200000, dtype=torch.int32, device=e.device) << e,
                        (e - 1) << 23)
     return bits.view(torch.float32)
+
+
+def _dequantize_codebook(b: torch.Tensor, t: GGMLType) -> torch.Tensor:
+    """The IQ formats: 256-value blocks of codebook indices (vectors of 8 or 4 magnitudes, ``iq_grids.py``), sign
+    fields, and 3- or 4-bit scales per 32 (or 16) values (ggml-quants.c: dequantize_row_iq2_xxs ... dequantize_row_iq1_m)."""
+    from . import iq_grids
+    dev = b.device
+    nb = b.shape[0]
+    i32 = lambda x: x.to(torch.int32)
+    u16 = lambda x: x.contiguous().view(torch.int16).to(torch.int32) & 0xFFFF
+    u32 = lambda x: x.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    bit8 = torch.arange(8, device=dev, dtype=torch.int32)
+    sign_of = lambda byte: 1.0 - 2.0 * ((byte.unsqueeze(-1) >> bit8) & 1).float()          # [..., 8] from a sign byte
+    if t == GGMLType.IQ2_XXS:
+        d = _f16(b[:, 0:2])
+        w = u32(b[:, 2:66]).view(nb, 8, 2)                                # per 32 values: 4 index bytes, then signs + scale
+        idx = (w[:, :, 0:1] >> (8 * torch.arange(4, device=dev))) & 0xFF                       # [nb, 8, 4]
+        sg = (w[:, :, 1:2] >> (7 * torch.arange(4, device=dev))) & 127
+        db = d * (0.5 + (w[:, :, 1] >> 28).float()) * 0.25                                     # [nb, 8]
+        vals = iq_grids.grid("iq2xxs").to(dev)[idx] * iq_grids.signs7().to(dev)[sg]            # [nb, 8, 4, 8]
+        return db.view(nb, 8, 1, 1) * vals
+    if t == GGMLType.IQ2_XS:
+        d = _f16(b[:, 0:2])
+        q = u16(b[:, 2:66]).to(torch.int64).view(nb, 8, 4)
+        sc = i32(b[:, 66:74])
+        db = d.unsqueeze(2) * (0.5 + torch.stack([sc & 0xF, sc >> 4], 2).float()) * 0.25       # [nb, 8, 2]
+        vals = iq_grids.grid("iq2xs").to(dev)[q & 511] * iq_grids.signs7().to(dev)[q >> 9]
+        return db.repeat_interleave(2, dim=2).unsqueeze(3) * vals
+    if t == GGMLType.IQ2_S:
+        d = _f16(b[:, 0:2])
+        lo = i32(b[:, 2:34]).view(nb, 8, 4)
+        sg = i32(b[:, 34:66]).view(nb, 8, 4)
+        qh = i32(b[:, 66:74]).view(nb, 8, 1)
+        sc = i32(b[:, 74:82])
+        l = torch.arange(4, device=dev, dtype=torch.int32)
+        idx = (lo | ((qh << (8 - 2 * l)) & 0x300)).to(torch.int64)
+        db = d.unsqueeze(2) * (0.5 + torch.stack([sc & 0xF, sc >> 4], 2).float()) * 0.25
+        vals = iq_grids.grid("iq2s").to(dev)[idx] * sign_of(sg)
+        return db.repeat_interleave(2, dim=2).unsqueeze(3) * vals
+    if t == GGMLType.IQ3_XXS:
+        d = _f16(b[:, 0:2])
+        idx = b[:, 2:66].to(torch.int64).view(nb, 8, 4, 2)                 # two 4-value vectors per 8 values
+        w = u32(b[:, 66:98]).view(nb, 8, 1)
+        sg = (w >> (7 * torch.arange(4, device=dev))) & 127                                    # [nb, 8, 4]
+        db = d * (0.5 + (w[:, :, 0] >> 28).float()) * 0.5
+        vals = iq_grids.grid("iq3xxs").to(dev)[idx].reshape(nb, 8, 4, 8) * iq_grids.signs7().to(dev)[sg]
+        return db.view(nb, 8, 1, 1) * vals
+    if t == GGMLType.IQ3_S:
+        d = _f16(b[:, 0:2])
+        lo = i32(b[:, 2:66]).view(nb, 8, 8)                                # per 32 values: 8 index bytes
+        qh = i32(b[:, 66:74]).view(nb, 8, 1)
+        sg = i32(b[:, 74:106]).view(nb, 8, 4)
+        sc = i32(b[:, 106:110])
+        idx = (lo | (((qh >> torch.arange(8, device=dev, dtype=torch.int32)) & 1) << 8)).to(torch.int64)
+        db = d.unsqueeze(2) * (1 + 2 * torch.stack([sc & 0xF, sc >> 4], 2)).float()            # [nb, 4, 2] -> per 32
+        vals = iq_grids.grid("iq3s").to(dev)[idx].reshape(nb, 8, 4, 8) * sign_of(sg)
+        return db.reshape(nb, 8, 1, 1) * vals
+    grid1 = iq_grids.grid("iq1s").to(dev)
+    if t == GGMLType.IQ1_S:
+        d = _f16(b[:, 0:2])
+        lo = i32(b[:, 2:34]).view(nb, 8, 4)
+        qh = u16(b[:, 34:50]).view(nb, 8, 1)
+        idx = (lo | (((qh >> (3 * torch.arange(4, device=dev, dtype=torch.int32))) & 7) << 8)).to(torch.int64)
+        dl = d * (2 * ((qh[:, :, 0] >> 12) & 7) + 1).float()
+        delta = torch.where((qh & 0x8000) != 0, -0.125, 0.125)                                 # [nb, 8, 1]
+        return dl.view(nb, 8, 1, 1) * (grid1[idx] + delta.unsqueeze(3))
+    # IQ1_M: the block's half-precision scale is spread over the top nibbles of the four 16-bit scale words
+    lo = i32(b[:, 0:32]).view(nb, 8, 4)
+    qh = i32(b[:, 32:48]).view(nb, 8, 2).repeat_interleave(2, dim=2)       # byte l // 2 serves vectors l = 0..3
+    sc = u16(b[:, 48:56])                                                  # [nb, 4]
+    dbits = (sc[:, 0] >> 12) | ((sc[:, 1] >> 8) & 0x00F0) | ((sc[:, 2] >> 4) & 0x0F00) | (sc[:, 3] & 0xF000)
+    d = dbits.to(torch.int16).view(torch.float16).float().view(nb, 1, 1)
+    odd = (torch.arange(4, device=dev, dtype=torch.int32) % 2).view(1, 1, 4)
+    idx = (lo | ((qh << (8 - 4 * odd)) & 0x700)).to(torch.int64)
+    delta = torch.where((qh & (0x08 << (4 * odd))) != 0, -0.125, 0.125)
+    ib = torch.arange(8, device=dev)
+    half = torch.arange(2, device=dev, dtype=torch.int32).view(1, 1, 2)
+    s3 = (sc[:, ib // 2].unsqueeze(2) >> (6 * (ib % 2).view(1, 8, 1).to(torch.int32) + 3 * half)) & 7      # [nb, 8, 2]
+    dl = d * (2 * s3 + 1).float()
+    return dl.repeat_interleave(2, dim=2).unsqueeze(3) * (grid1[idx] + delta.unsqueeze(3))
 
 
 def dequantize(raw: torch.Tensor, t: GGMLType, shape: Sequence[int] = None) -> torch.Tensor:
@@ -140,6 +221,49 @@ def dequantize(raw: torch.Tensor, t: GGMLType, shape: Sequence[int] = None) -> t
             dl = d * (scb & 0xF).float()
             ml = dmin * (scb >> 4).float()
             out = dl.unsqueeze(2) * q - ml.unsqueeze(2)
+        elif t == GGMLType.Q3_K:
+            hm = b[:, 0:32].to(torch.int32)
+            qs = b[:, 32:96].to(torch.int32).view(-1, 2, 1, 32)
+            scb = b[:, 96:108].to(torch.int32)
+            d = _f16(b[:, 108:110])
+            j = torch.arange(16, device=dev)
+            low = torch.where(j < 8, scb[:, j % 8] & 0xF, scb[:, j % 8] >> 4)
+            high = (scb[:, 8 + j % 4] >> (2 * (j // 4))) & 3
+            sc = ((low | (high << 4)) - 32).float()                       # 16 six-bit scales, each for 16 values
+            sh = (2 * torch.arange(4, device=dev, dtype=torch.int32)).view(1, 1, 4, 1)
+            bit = torch.arange(8, device=dev, dtype=torch.int32).view(1, 8, 1)
+            q = ((qs >> sh) & 3).reshape(-1, 8, 32)                       # group g = half * 4 + shift index
+            hi = (hm.unsqueeze(1) >> bit) & 1                             # bit g of hmask[l]: set = no offset
+            vals = (q - 4 * (1 - hi)).float().reshape(-1, 16, 16)
+            out = (d * sc).unsqueeze(2) * vals
+        elif t == GGMLType.Q8_K:
+            d = b[:, 0:4].contiguous().view(torch.float32)
+            out = d * b[:, 4:260].view(torch.int8).float()
+        elif t == GGMLType.IQ4_XS:
+            d = _f16(b[:, 0:2])
+            sh = b[:, 2:4].contiguous().view(torch.int16).to(torch.int32) & 0xFFFF          # [nb, 1]
+            sl = b[:, 4:8].to(torch.int32)
+            ib = torch.arange(8, device=dev)
+            ls = ((sl[:, ib // 2] >> (4 * (ib % 2))) & 0xF) | (((sh >> (2 * ib)) & 3) << 4)
+            q = b[:, 8:136].to(torch.int64).view(-1, 8, 16)
+            tab = torch.tensor(_IQ4NL_VALUES, dtype=torch.float32, device=dev)
+            out = (d * (ls - 32).float()).unsqueeze(2) * tab[torch.cat([q & 0xF, q >> 4], 2)]
+        elif t == GGMLType.TQ2_0:
+            qs = b[:, 0:64].to(torch.int32).view(-1, 2, 1, 32)
+            sh = (2 * torch.arange(4, device=dev, dtype=torch.int32)).view(1, 1, 4, 1)
+            out = _f16(b[:, 64:66]) * (((qs >> sh) & 3) - 1).float().reshape(-1, 256)
+        elif t == GGMLType.TQ1_0:
+            # five ternary digits per byte (four in the last four bytes), most significant first: digit n of byte q is
+            # ((q * 3^n mod 256) * 3) >> 8
+            def trits(x, n):
+                p3 = torch.tensor([1, 3, 9, 27, 81][:n], device=dev, dtype=torch.int32).view(1, n, 1)
+                return ((((x.to(torch.int32).unsqueeze(1) * p3) & 0xFF) * 3) >> 8) - 1
+            vals = torch.cat([trits(b[:, 0:32], 5).reshape(-1, 160), trits(b[:, 32:48], 5).reshape(-1, 80),
+                              trits(b[:, 48:52], 4).reshape(-1, 16)], 1)
+            out = _f16(b[:, 52:54]) * vals.float()
+        elif t in (GGMLType.IQ2_XXS, GGMLType.IQ2_XS, GGMLType.IQ2_S, GGMLType.IQ3_XXS, GGMLType.IQ3_S, GGMLType.IQ1_S,
+                   GGMLType.IQ1_M):
+            out = _dequantize_codebook(b, t)
         else:
             raise NotImplementedError(f"dequantize: unsupported GGML type {t.name}")
     out = out.reshape(-1)

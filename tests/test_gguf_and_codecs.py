@@ -149,3 +149,38 @@ def test_plane_split_is_lossless(t):
     assert torch.equal(sl.dequantize(), qw.dequantize()[2:5])
     cat = QuantWeight.concat_rows([qw, sl])
     assert torch.equal(cat.dequantize(), torch.cat([qw.dequantize(), sl.dequantize()]))
+
+
+GOLDEN_TYPES = ["Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q8_0", "Q2_K", "Q3_K", "Q4_K", "Q5_K", "Q6_K", "Q8_K", "IQ4_NL", "IQ4_XS", "MXFP4",
+                "TQ1_0", "TQ2_0", "IQ2_XXS", "IQ2_XS", "IQ2_S", "IQ3_XXS", "IQ3_S", "IQ1_S", "IQ1_M"]
+
+
+@pytest.mark.parametrize("name", GOLDEN_TYPES)
+def test_codec_matches_golden_vectors_of_ggml(name):
+    """``tests/data/codec_golden.npz`` holds, per block type, a few blocks of random bytes and the values that ggml's own
+    ``dequantize_row_*`` (ExternalProjects/ggml/src/ggml-quants.c) decodes them to; the codecs here reproduce them."""
+    import os
+
+    import numpy as np
+    from tensorsharp_b200.gguf.constants import GGMLType
+    from tensorsharp_b200.quant import codecs
+    gold = np.load(os.path.join(os.path.dirname(__file__), "data", "codec_golden.npz"))
+    raw, want = gold[name + "_raw"], gold[name + "_f32"]
+    got = codecs.dequantize(torch.from_numpy(raw.copy()), GGMLType[name]).numpy()
+    assert got.shape == want.shape
+    assert np.abs(got - want).max() <= 1e-6 * np.abs(want).max(), name
+
+
+@pytest.mark.parametrize("name", ["Q3_K", "IQ4_XS", "IQ2_XS", "IQ3_S", "IQ1_M", "TQ2_0"])
+def test_weight_of_a_type_without_a_kernel_loads_as_bf16(name):
+    """Block types that no kernel reads directly are decoded once at load (QuantWeight.from_raw) and served as bf16."""
+    import os
+
+    import numpy as np
+    from tensorsharp_b200.gguf.constants import GGMLType
+    from tensorsharp_b200.quant.qweight import QuantWeight
+    gold = np.load(os.path.join(os.path.dirname(__file__), "data", "codec_golden.npz"))
+    raw, want = gold[name + "_raw"], torch.from_numpy(gold[name + "_f32"])
+    w = QuantWeight.from_raw(raw, GGMLType[name], (3, 256))
+    assert w.ggml_type == GGMLType.BF16 and (w.N, w.K) == (3, 256)
+    assert torch.equal(w.dequantize().reshape(-1), want.bfloat16().float())

@@ -24,7 +24,8 @@ def ref_lib():
         pytest.skip(str(exc))
 
 
-CODEC_TYPES = ["Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q8_0", "Q2_K", "Q4_K", "Q5_K", "Q6_K", "IQ4_NL", "MXFP4", "F16", "BF16"]
+CODEC_TYPES = ["Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q8_0", "Q2_K", "Q3_K", "Q4_K", "Q5_K", "Q6_K", "IQ4_NL", "IQ4_XS", "MXFP4", "F16", "BF16",
+               "TQ1_0", "TQ2_0", "IQ2_XXS", "IQ2_XS", "IQ2_S", "IQ3_XXS", "IQ3_S", "IQ1_S", "IQ1_M"]
 
 
 @pytest.mark.parametrize("name", CODEC_TYPES)
