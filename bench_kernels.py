@@ -39,7 +39,8 @@ def time_us(fn, iters: int, warmup: int) -> float:
 def recurrent(args):
     """The token-by-token scan kernel against the chunked form (tensor ops) on one prompt of ``--t`` tokens, at the
     Qwen3.5-35B-A3B GatedDeltaNet shape (16 QK / 32 V heads x 128) or the Nemotron-H Mamba2 shape (64 heads x 64,
-    8 groups, state 128).  Prints both times and the distance between the two outputs."""
+    8 groups, state 128).  Prints both times and the distance between the two outputs; for GatedDeltaNet also the
+    chunked form with its chunk-after-chunk part as one kernel (csrc/gdn_chunk.cu)."""
     import torch
     from tensorsharp_b200.ops import kernels
     from tensorsharp_b200.ops import reference as ref
@@ -81,12 +82,21 @@ def recurrent(args):
         def chunked():
             s1.zero_()
             return ref.mamba2_chunked(xbc, dt, dt_bias, A, D, s1, chunk=args.chunk, **kw)
+    fused = None
+    if args.op == "gdn":
+        s2 = torch.zeros_like(s1)
+
+        def fused():
+            s2.zero_()
+            return ref.gdn_chunked(qkv, z, beta, alpha, dt_bias, a_log, norm_w, s2, chunk=64, carry=kernels.gdn_chunk_carry, **kw)
     a, b = scan().float(), chunked().float()
     rel = float((a - b).norm() / b.norm())
     srel = float((s0[0] - s1).norm() / s1.norm())
     print(json.dumps({"kernel": "recurrent", "op": args.op, "T": T, "chunk": args.chunk,
                       "scan_us": time_us(scan, args.iters, args.warmup),
                       "chunked_us": time_us(chunked, args.iters, args.warmup),
+                      "chunked_carry_kernel_us": time_us(fused, args.iters, args.warmup) if fused else None,
+                      "rel_diff_out_carry_kernel": float((fused().float() - b).norm() / b.norm()) if fused else None,
                       "rel_diff_out": rel, "rel_diff_state": srel}))
 
 

@@ -52,22 +52,26 @@ __device__ __forceinline__ long kv_slot(const AttnArgs& a, int b, int j) {
 }
 
 // ------------------------------------------------------------------------------------------
-// Decode: grid (splits, Hkv, B), 128 threads.  All G = Hq / Hkv query heads of a KV head share
-// the K / V traffic.  Lane = token for QK^T, lane = dim slice for PV.
+// Decode: grid (splits, Hkv * chunks, B), 128 threads.  A CTA serves G query heads of one KV head, which share the
+// K / V traffic; the Hq / Hkv heads of a KV head are dealt to `chunks` CTAs of G heads each (one chunk when the
+// group size is 1, 2, 4 or 8; other group sizes and head size 512 take several).  Lane = token for QK^T,
+// lane = dim slice for PV.
 // ------------------------------------------------------------------------------------------
 template <int DH, int G>
 __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
     constexpr int DPL = DH / 32;             // output dims per lane
     pdl_wait();
     pdl_trigger();
-    const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int split = blockIdx.x, b = blockIdx.z;
+    const int heads_per_kv = a.Hq / a.Hkv, chunks = heads_per_kv / G;
+    const int hk = blockIdx.y / chunks, h0 = hk * heads_per_kv + (blockIdx.y % chunks) * G;     // first query head of this CTA
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     __shared__ __align__(16) bf16 qs[G][DH];
     __shared__ float red_m[4][G], red_l[4][G];
     __shared__ float red_o[4][G][DH];
     // the query rows and the sequence length are requested together (the G heads of a KV head are contiguous)
     constexpr int QV = G * DH / 8;                     // 16-byte pieces of the query rows
-    const uint4* qsrc = reinterpret_cast<const uint4*>(a.q + ((long)b * a.Hq + hk * G) * DH);
+    const uint4* qsrc = reinterpret_cast<const uint4*>(a.q + ((long)b * a.Hq + h0) * DH);
     uint4 qreg[(QV + 127) / 128];
 #pragma unroll
     for (int i = 0; i < (QV + 127) / 128; ++i)
@@ -193,21 +197,25 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
             }
         } else {
         // P V: eight value rows are fetched before any of them is used, so the loads overlap
-        for (int t0 = 0; t0 < cnt; t0 += 8) {
-            float vf[8][DPL];
+        constexpr int VB = DPL > 8 ? 4 : 8;             // value rows in flight (fewer for the widest heads: registers)
+        for (int t0 = 0; t0 < cnt; t0 += VB) {
+            float vf[VB][DPL];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+            for (int u = 0; u < VB; ++u) {
                 const long sl = __shfl_sync(0xffffffffu, slot, (t0 + u) & 31);
                 const bf16* vp = a.v_cache + (sl * a.Hkv + hk) * DH + lane * DPL;
                 if (t0 + u < cnt) {
-                    if (DPL == 8) {
-                        const uint4 vv = *reinterpret_cast<const uint4*>(vp);
-                        const bf162* v2 = reinterpret_cast<const bf162*>(&vv);
+                    if (DPL % 8 == 0) {
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const float2 f = __bfloat1622float2(v2[i]);
-                            vf[u][(2 * i) % DPL] = f.x;
-                            vf[u][(2 * i + 1) % DPL] = f.y;
+                        for (int c8 = 0; c8 < DPL / 8; ++c8) {
+                            const uint4 vv = reinterpret_cast<const uint4*>(vp)[c8];
+                            const bf162* v2 = reinterpret_cast<const bf162*>(&vv);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float2 f = __bfloat1622float2(v2[i]);
+                                vf[u][(c8 * 8 + 2 * i) % DPL] = f.x;
+                                vf[u][(c8 * 8 + 2 * i + 1) % DPL] = f.y;
+                            }
                         }
                     } else {
 #pragma unroll
@@ -219,7 +227,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
                 }
             }
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+            for (int u = 0; u < VB; ++u) {
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
                     const float pg = __shfl_sync(0xffffffffu, p[g], (t0 + u) & 31);
@@ -250,7 +258,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
             ll += red_l[w][g] * c;
             o += red_o[w][g][d] * c;
         }
-        const long pi = ((long)b * a.Hq + hk * G + g) * a.splits + split;
+        const long pi = ((long)b * a.Hq + h0 + g) * a.splits + split;
         a.part_o[pi * DH + d] = o;
         if (d == 0) { a.part_ml[pi * 2] = mm; a.part_ml[pi * 2 + 1] = ll; }
     }
@@ -264,7 +272,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
     if (!last) return;
     __threadfence();
     for (int i = threadIdx.x; i < G * DH; i += 128) {
-        const int g = i / DH, d = i % DH, h = hk * G + g;
+        const int g = i / DH, d = i % DH, h = h0 + g;       // (the in-kernel merge runs with one chunk per KV head only)
         const long pb = ((long)b * a.Hq + h) * a.splits;
         float mm = a.sinks ? a.sinks[h] : -INFINITY;
         for (int sp = 0; sp < a.splits; ++sp) mm = fmaxf(mm, __ldcg(&a.part_ml[(pb + sp) * 2]));
@@ -335,23 +343,36 @@ __global__ void attn_combine_kernel(AttnArgs a) {
     }
 }
 
+// Heads of a KV head that one CTA serves: the largest of 8, 4, 2, 1 that divides the group (at most 2 for head size
+// 512, whose accumulators and merge buffers are four times those of head size 128).
+static int attn_decode_chunk(int heads_per_kv, int Dh) {
+    const int cap = Dh > 256 ? 2 : 8;
+    for (int g = cap; g > 1; g >>= 1)
+        if (heads_per_kv % g == 0) return g;
+    return 1;
+}
+
 template <int DH>
 static int launch_decode_g(const AttnArgs& a, cudaStream_t s) {
-    dim3 grid(a.splits, a.Hkv, a.B);
-    const int G = a.Hq / a.Hkv;
+    const int G = attn_decode_chunk(a.Hq / a.Hkv, DH);
+    dim3 grid(a.splits, a.Hkv * ((a.Hq / a.Hkv) / G), a.B);
     switch (G) {
     case 1: if (tsb_launch(attn_decode_kernel<DH, 1>, grid, dim3(128), 0, s, a) != cudaSuccess) return TSB_ERR_CUDA; break;
     case 2: if (tsb_launch(attn_decode_kernel<DH, 2>, grid, dim3(128), 0, s, a) != cudaSuccess) return TSB_ERR_CUDA; break;
-    case 4: if (tsb_launch(attn_decode_kernel<DH, 4>, grid, dim3(128), 0, s, a) != cudaSuccess) return TSB_ERR_CUDA; break;
-    case 8: if (tsb_launch(attn_decode_kernel<DH, 8>, grid, dim3(128), 0, s, a) != cudaSuccess) return TSB_ERR_CUDA; break;
+    case 4:
+        if constexpr (DH <= 256) {
+            if (tsb_launch(attn_decode_kernel<DH, 4>, grid, dim3(128), 0, s, a) != cudaSuccess) return TSB_ERR_CUDA;
+        }
+        break;
     default:
-        tsb_set_error("attn_decode: unsupported GQA group size %d (supported 1, 2, 4, 8)", G);
-        return TSB_ERR_UNSUPPORTED;
+        if constexpr (DH <= 256) {
+            if (tsb_launch(attn_decode_kernel<DH, 8>, grid, dim3(128), 0, s, a) != cudaSuccess) return TSB_ERR_CUDA;
+        }
+        break;
     }
     return TSB_OK;
 }
 
-// Query heads per KV head above 8 are handled by the caller splitting the head group.
 // Arrival counters of the fused split merge: one per (sequence, KV head), zero between launches (the
 // merging CTA resets its counter).  Launches that share a device must be ordered, as a decode loop's are.
 #define ATTN_MAX_TICKETS 65536
@@ -378,8 +399,10 @@ static unsigned* attn_ticket_for_current_device() {
 // `allow_fused`: whether this call may use the in-kernel split merge (and with it the shared arrival tickets).
 static int attn_decode_impl(const AttnArgs* args, void* stream, bool allow_fused) {
     AttnArgs a = *args;
-    a.ticket = (allow_fused && a.splits >= 1 && (long)a.B * a.Hkv <= ATTN_MAX_TICKETS) ? attn_ticket_for_current_device() : nullptr;
     TSB_CHECK_ARG(a.Hkv > 0 && a.Hq % a.Hkv == 0, "attn_decode: Hq=%d not a multiple of Hkv=%d", a.Hq, a.Hkv);
+    // the in-kernel merge counts arrivals per KV head: only when one CTA serves the whole head group
+    const bool one_chunk = attn_decode_chunk(a.Hq / a.Hkv, a.Dh) == a.Hq / a.Hkv;
+    a.ticket = (allow_fused && one_chunk && a.splits >= 1 && (long)a.B * a.Hkv <= ATTN_MAX_TICKETS) ? attn_ticket_for_current_device() : nullptr;
     TSB_CHECK_ARG(a.splits >= 1 && a.part_o && a.part_ml, "attn_decode: scratch for %d splits missing", a.splits);
     TSB_CHECK_ARG(a.splits <= 64, "attn_decode: %d splits (limit 64)", a.splits);
     if (a.B == 0) return TSB_OK;
@@ -389,8 +412,9 @@ static int attn_decode_impl(const AttnArgs* args, void* stream, bool allow_fused
     case 64: rc = launch_decode_g<64>(a, s); break;
     case 128: rc = launch_decode_g<128>(a, s); break;
     case 256: rc = launch_decode_g<256>(a, s); break;
+    case 512: rc = launch_decode_g<512>(a, s); break;
     default:
-        tsb_set_error("attn_decode: unsupported head dim %d (supported 64, 128, 256)", a.Dh);
+        tsb_set_error("attn_decode: unsupported head dim %d (supported 64, 128, 256, 512)", a.Dh);
         return TSB_ERR_UNSUPPORTED;
     }
     if (rc != TSB_OK) return rc;
@@ -485,9 +509,12 @@ __device__ __forceinline__ bf16* tile_ptr(bf16* base, int r, int c) {
     return base + r * DH + ((c ^ (r & 7)) << 3);
 }
 
-template <int DH>
-__global__ void __launch_bounds__(128) attn_prefill_kernel(AttnArgs a) {
-    constexpr int BM = 64, BN = 64, CH = DH / 8;   // CH = 16-byte chunks per row
+// DS > 1 (head size 512): DS sets of four warps share the tiles and the score arithmetic, each set keeps DH / DS of the
+// output columns, so that a thread's accumulators stay at the head-size-256 count.
+template <int DH, int BN, int DS>
+__global__ void __launch_bounds__(128 * DS) attn_prefill_kernel(AttnArgs a) {
+    constexpr int BM = 64, CH = DH / 8;   // CH = 16-byte chunks per row
+    constexpr int NT = 128 * DS, DO = DH / DS;     // threads; output columns per warp set
     pdl_wait();
     pdl_trigger();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -501,7 +528,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(AttnArgs a) {
     if (m0 >= qlen) return;
     const int kvlen = a.kv_lens[b];
     const int pos0 = a.q_pos0 ? a.q_pos0[b] : kvlen - qlen;   // cache position of the sequence's first query
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = (threadIdx.x >> 5) & 3, lane = threadIdx.x & 31, dset = threadIdx.x >> 7;
     const int rows = min(BM, qlen - m0);
 
     // KV range needed by this query tile
@@ -512,7 +539,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(AttnArgs a) {
     const int t_lo = j_lo / BN, t_hi = (j_hi + BN - 1) / BN;
 
     // Q tile -> shared (rows beyond the sequence are zero)
-    for (int i = threadIdx.x; i < BM * CH; i += 128) {
+    for (int i = threadIdx.x; i < BM * CH; i += NT) {
         const int r = i / CH, c = i % CH;
         bf16* dst = tile_ptr<DH>(sQ, r, c);
         if (r < rows) cp_async16(dst, a.q + ((long)(q0 + m0 + r) * a.Hq + h) * DH + c * 8);
@@ -521,7 +548,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(AttnArgs a) {
     auto load_kv = [&](int t, int stage) {
         bf16* dk = sK + stage * BN * DH;
         bf16* dv = sV + stage * BN * DH;
-        for (int i = threadIdx.x; i < BN * CH; i += 128) {
+        for (int i = threadIdx.x; i < BN * CH; i += NT) {
             const int r = i / CH, c = i % CH;
             const int j = t * BN + r;
             bf16* pk = tile_ptr<DH>(dk, r, c);
@@ -539,9 +566,9 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(AttnArgs a) {
     load_kv(t_lo, 0);
     cp_async_commit();
 
-    float o[DH / 8][4];
+    float o[DO / 8][4];
 #pragma unroll
-    for (int i = 0; i < DH / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    for (int i = 0; i < DO / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
     const int r_lo = warp * 16 + (lane >> 2);      // this thread's two query rows: r_lo, r_lo + 8
     const int qpos_a = pos0 + m0 + r_lo, qpos_b = qpos_a + 8;
@@ -612,7 +639,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(AttnArgs a) {
 #pragma unroll
         for (int r = 0; r < 2; ++r) lrow[r] = lrow[r] * corr[r] + rsum[r];
 #pragma unroll
-        for (int i = 0; i < DH / 8; ++i) {
+        for (int i = 0; i < DO / 8; ++i) {
             o[i][0] *= corr[0]; o[i][1] *= corr[0];
             o[i][2] *= corr[1]; o[i][3] *= corr[1];
         }
@@ -625,10 +652,10 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(AttnArgs a) {
             pa[2] = pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]);
             pa[3] = pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3]);
 #pragma unroll
-            for (int dt = 0; dt < DH / 16; ++dt) {
+            for (int dt = 0; dt < DO / 16; ++dt) {
                 uint32_t vb[4];
                 const int tok = kt * 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
-                ldsm_x4_t(vb, tile_ptr<DH>(const_cast<bf16*>(tV), tok, dt * 2 + (lane >> 4)));
+                ldsm_x4_t(vb, tile_ptr<DH>(const_cast<bf16*>(tV), tok, (dset * (DO / 16) + dt) * 2 + (lane >> 4)));
                 mma_bf16(o[2 * dt], pa, vb[0], vb[1]);
                 mma_bf16(o[2 * dt + 1], pa, vb[2], vb[3]);
             }
@@ -655,13 +682,13 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(AttnArgs a) {
         inv[r] = ll > 0.f ? oc / ll : 0.f;
     }
     const int ra = warp * 16 + (lane >> 2), rb = ra + 8;
-    if (a.lse_out != nullptr && (lane & 3) == 0) {
+    if (a.lse_out != nullptr && (lane & 3) == 0 && dset == 0) {
         if (ra < rows) a.lse_out[(long)(q0 + m0 + ra) * a.Hq + h] = lrow[0] > 0.f ? mrow[0] + __logf(lrow[0]) : -INFINITY;
         if (rb < rows) a.lse_out[(long)(q0 + m0 + rb) * a.Hq + h] = lrow[1] > 0.f ? mrow[1] + __logf(lrow[1]) : -INFINITY;
     }
 #pragma unroll
-    for (int i = 0; i < DH / 8; ++i) {
-        const int d = i * 8 + (lane & 3) * 2;
+    for (int i = 0; i < DO / 8; ++i) {
+        const int d = dset * DO + i * 8 + (lane & 3) * 2;
         if (ra < rows)
             *reinterpret_cast<uint32_t*>(a.out + ((long)(q0 + m0 + ra) * a.Hq + h) * DH + d) =
                 pack_bf16(o[i][0] * inv[0], o[i][1] * inv[0]);
@@ -673,15 +700,17 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(AttnArgs a) {
 
 template <int DH>
 static int launch_prefill(const AttnArgs& a, int max_q, cudaStream_t s) {
-    const size_t smem = (size_t)(64 + 4 * 64) * DH * sizeof(bf16);
+    // head size 512: 32-key tiles (query tile 64 KB + two stages of K and V 128 KB) and two warp sets
+    constexpr int BN = DH > 256 ? 32 : 64, DS = DH > 256 ? 2 : 1;
+    const size_t smem = (size_t)(64 + 4 * BN) * DH * sizeof(bf16);
     static bool configured = false;
     if (!configured) {
-        TSB_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        TSB_CHECK_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<DH, BN, DS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             (int)smem));
         configured = true;
     }
     dim3 grid((max_q + 63) / 64, a.Hq, a.B);
-    TSB_CHECK_CUDA(tsb_launch(attn_prefill_kernel<DH>, grid, dim3(128), smem, s, a));
+    TSB_CHECK_CUDA(tsb_launch(attn_prefill_kernel<DH, BN, DS>, grid, dim3(128 * DS), smem, s, a));
     TSB_CHECK_LAUNCH();
     return TSB_OK;
 }
@@ -696,8 +725,9 @@ extern "C" int tsb_attn_prefill(const AttnArgs* args, int max_q_len, void* strea
     case 64: return launch_prefill<64>(a, max_q_len, s);
     case 128: return launch_prefill<128>(a, max_q_len, s);
     case 256: return launch_prefill<256>(a, max_q_len, s);
+    case 512: return launch_prefill<512>(a, max_q_len, s);
     default:
-        tsb_set_error("attn_prefill: unsupported head dim %d (supported 64, 128, 256)", a.Dh);
+        tsb_set_error("attn_prefill: unsupported head dim %d (supported 64, 128, 256, 512)", a.Dh);
         return TSB_ERR_UNSUPPORTED;
     }
 }

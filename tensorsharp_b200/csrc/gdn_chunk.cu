@@ -1,0 +1,245 @@
+// Chunked GatedDeltaNet prefill: the part that has to run chunk after chunk, as one kernel.
+//
+// In the chunked (WY) form of the delta rule the work inside a chunk of 64 tokens is batched matrix algebra over
+// (heads x chunks) that has no dependency between chunks (the decay mask, K K^T, the unit-triangular solve, Q K^T);
+// what remains sequential is carrying the state S [Dv, Dk] of each head across the chunks:
+//
+//     U_c   = U0_c - W_c S^T                     [64, Dv]   the chunk's value updates, corrected by the state
+//     O_c   = Qd_c S^T + P_c U_c                 [64, Dv]   outputs: state term + intra-chunk term
+//     S    <- gamma_c S + U_c^T Kd_c             [Dv, Dk]
+//
+// The reference builds a ggml graph of about forty nodes per chunk for this
+// (TensorSharp.GGML.Native/ggml_ops_gated_delta_net.cpp:178-615); as tensor ops it is three small batched products per
+// chunk, launch-bound.  Here a CTA owns one head and a slice of 32 value dimensions, keeps its slice of S in shared
+// memory for the whole prompt, and walks the chunks: the three products run on the tensor cores (mma.sync m16n8k8,
+// tf32 operands, f32 accumulation; the state itself stays f32), the operands of the next chunk stream in with cp.async
+// while the current one is multiplied (each operand buffer is refilled as soon as its product is done).
+#include "common.cuh"
+
+struct GdnCarryArgs {
+    const float* U0;      // [Hv, nc, 64, Dv]
+    const float* W;       // [Hv, nc, 64, Dk]
+    const float* Qd;      // [Hv, nc, 64, Dk]
+    const float* Kd;      // [Hv, nc, 64, Dk]
+    const float* P;       // [Hv, nc, 64, 64]
+    const float* gamma;   // [Hv, nc]
+    float* state;         // [Hv, Dv, Dk], updated in place
+    float* out;           // [Hv, nc, 64, Dv]
+    int Hv, nc, Dk, Dv;
+};
+
+namespace {
+constexpr int GC = 64;        // tokens per chunk
+constexpr int DVS = 32;       // value dimensions per CTA
+
+__device__ __forceinline__ uint32_t tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp16(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;"); }
+__device__ __forceinline__ void cp_wait2() { asm volatile("cp.async.wait_group 2;"); }
+
+// rows x cols f32 from global (row stride gs) into shared (row stride ss), 16 bytes per copy, all 256 threads
+__device__ __forceinline__ void stage(float* dst, int ss, const float* src, int gs, int rows, int cols) {
+    const int per = cols / 4;
+    for (int i = threadIdx.x; i < rows * per; i += 256) {
+        const int r = i / per, c = (i % per) * 4;
+        cp16(dst + r * ss + c, src + (long)r * gs + c);
+    }
+}
+
+// Shared-memory row strides (floats), chosen so that the fragment loads below touch 32 different banks:
+// operands read as A[row g][k t] or B[n g][k t] want stride = 4 (mod 32); operands read as [k t][n g] want 8 (mod 32).
+template <int DK> struct Lay {
+    static constexpr int LW = DK + 4;      // W, Qd, S: [row][k]
+    static constexpr int LK = DK + 8;      // Kd: [t][k] read as B[k = t][n = k]
+    static constexpr int LP = GC + 4;      // P: [t][j]
+    static constexpr int LU = DVS + 8;     // U: [j][v] read as B[k = j][n = v] and as A[m = v][k = j]
+    static constexpr int floats = DVS * LW + 2 * GC * LW + GC * LK + GC * LP + GC * LU;
+};
+}  // namespace
+
+template <int DK>
+__global__ void __launch_bounds__(256) gdn_chunk_carry_kernel(GdnCarryArgs a) {
+    using L = Lay<DK>;
+    extern __shared__ __align__(16) float sm[];
+    float* sS = sm;                       // [DVS][LW]   state slice
+    float* sW = sS + DVS * L::LW;         // [64][LW]
+    float* sQ = sW + GC * L::LW;          // [64][LW]
+    float* sK = sQ + GC * L::LW;          // [64][LK]
+    float* sP = sK + GC * L::LK;          // [64][LP]
+    float* sU = sP + GC * L::LP;          // [64][LU]
+    const int h = blockIdx.y, dv0 = blockIdx.x * DVS;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int Dv = a.Dv, nc = a.nc;
+    float* Sg = a.state + ((long)h * Dv + dv0) * DK;
+    const long hc = (long)h * nc;
+    // prologue: the state slice and the first chunk's operands, in the commit order W | Qd + P | Kd kept below
+    stage(sS, L::LW, Sg, DK, DVS, DK);
+    stage(sW, L::LW, a.W + hc * GC * DK, DK, GC, DK);
+    cp_commit();
+    stage(sQ, L::LW, a.Qd + hc * GC * DK, DK, GC, DK);
+    stage(sP, L::LP, a.P + hc * GC * GC, GC, GC, GC);
+    cp_commit();
+    stage(sK, L::LK, a.Kd + hc * GC * DK, DK, GC, DK);
+    cp_commit();
+
+    // tiles of the [64, 32] products: warp -> 16 rows (mt) x 16 columns (two n-tiles of 8)
+    const int mt = warp >> 1, nb = (warp & 1) * 2;
+    for (int c = 0; c < nc; ++c) {
+        const long ch = hc + c;
+        const bool more = c + 1 < nc;
+        // U0 fragments straight from global (requested before the wait)
+        float u[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const float* p0 = a.U0 + (ch * GC + mt * 16 + g) * Dv + dv0 + (nb + j) * 8 + 2 * t;
+            const float2 lo = *reinterpret_cast<const float2*>(p0), hi = *reinterpret_cast<const float2*>(p0 + 8L * Dv);
+            u[j][0] = lo.x; u[j][1] = lo.y; u[j][2] = hi.x; u[j][3] = hi.y;
+        }
+        const float gam = a.gamma[ch];
+        cp_wait2();                       // W of this chunk (and, for c = 0, the state) has landed
+        __syncthreads();
+        // ---- U = U0 - W S^T
+        {
+            float acc[2][4] = {};
+#pragma unroll 4
+            for (int k0 = 0; k0 < DK; k0 += 8) {
+                uint32_t af[4];
+                const float* ap = sW + (mt * 16 + g) * L::LW + k0 + t;
+                af[0] = tf32(ap[0]); af[1] = tf32(ap[8 * L::LW]); af[2] = tf32(ap[4]); af[3] = tf32(ap[8 * L::LW + 4]);
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const float* bp = sS + ((nb + j) * 8 + g) * L::LW + k0 + t;
+                    mma_tf32(acc[j], af, tf32(bp[0]), tf32(bp[4]));
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                float* up = sU + (mt * 16 + g) * L::LU + (nb + j) * 8 + 2 * t;
+                up[0] = u[j][0] - acc[j][0]; up[1] = u[j][1] - acc[j][1];
+                up[8 * L::LU] = u[j][2] - acc[j][2]; up[8 * L::LU + 1] = u[j][3] - acc[j][3];
+            }
+        }
+        __syncthreads();                  // U complete, W free
+        if (more) stage(sW, L::LW, a.W + (ch + 1) * GC * DK, DK, GC, DK);
+        cp_commit();
+        cp_wait2();                       // Qd and P of this chunk
+        __syncthreads();
+        // ---- O = Qd S^T + P U
+        {
+            float acc[2][4] = {};
+#pragma unroll 4
+            for (int k0 = 0; k0 < DK; k0 += 8) {
+                uint32_t af[4];
+                const float* ap = sQ + (mt * 16 + g) * L::LW + k0 + t;
+                af[0] = tf32(ap[0]); af[1] = tf32(ap[8 * L::LW]); af[2] = tf32(ap[4]); af[3] = tf32(ap[8 * L::LW + 4]);
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const float* bp = sS + ((nb + j) * 8 + g) * L::LW + k0 + t;
+                    mma_tf32(acc[j], af, tf32(bp[0]), tf32(bp[4]));
+                }
+            }
+#pragma unroll 4
+            for (int k0 = 0; k0 < GC; k0 += 8) {
+                uint32_t af[4];
+                const float* ap = sP + (mt * 16 + g) * L::LP + k0 + t;
+                af[0] = tf32(ap[0]); af[1] = tf32(ap[8 * L::LP]); af[2] = tf32(ap[4]); af[3] = tf32(ap[8 * L::LP + 4]);
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const float* bp = sU + (k0 + t) * L::LU + (nb + j) * 8 + g;
+                    mma_tf32(acc[j], af, tf32(bp[0]), tf32(bp[4 * L::LU]));
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                float* op = a.out + (ch * GC + mt * 16 + g) * Dv + dv0 + (nb + j) * 8 + 2 * t;
+                *reinterpret_cast<float2*>(op) = make_float2(acc[j][0], acc[j][1]);
+                *reinterpret_cast<float2*>(op + 8L * Dv) = make_float2(acc[j][2], acc[j][3]);
+            }
+        }
+        __syncthreads();                  // Qd, P free; every read of the old state is done
+        if (more) {
+            stage(sQ, L::LW, a.Qd + (ch + 1) * GC * DK, DK, GC, DK);
+            stage(sP, L::LP, a.P + (ch + 1) * GC * GC, GC, GC, GC);
+        }
+        cp_commit();
+        cp_wait2();                       // Kd of this chunk
+        __syncthreads();
+        // ---- S = gamma S + U^T Kd: [32, DK] as 2 x (DK / 8) tiles, warp -> one 16-row half and DK / 32 column tiles
+        {
+            constexpr int NT = DK / 32;                   // n-tiles per warp
+            const int m2 = warp & 1, n0 = (warp >> 1) * NT;
+            float acc[NT][4];
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const float* sp = sS + (m2 * 16 + g) * L::LW + (n0 + j) * 8 + 2 * t;
+                acc[j][0] = gam * sp[0]; acc[j][1] = gam * sp[1];
+                acc[j][2] = gam * sp[8 * L::LW]; acc[j][3] = gam * sp[8 * L::LW + 1];
+            }
+#pragma unroll 2
+            for (int k0 = 0; k0 < GC; k0 += 8) {
+                uint32_t af[4];                           // A[m = v][k = token] = U[token][v]
+                const float* ap = sU + (k0 + t) * L::LU + m2 * 16 + g;
+                af[0] = tf32(ap[0]); af[1] = tf32(ap[8]); af[2] = tf32(ap[4 * L::LU]); af[3] = tf32(ap[4 * L::LU + 8]);
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    const float* bp = sK + (k0 + t) * L::LK + (n0 + j) * 8 + g;
+                    mma_tf32(acc[j], af, tf32(bp[0]), tf32(bp[4 * L::LK]));
+                }
+            }
+            // each warp reads only the state rows and columns it writes, so no barrier between the read above and this
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                float* sp = sS + (m2 * 16 + g) * L::LW + (n0 + j) * 8 + 2 * t;
+                sp[0] = acc[j][0]; sp[1] = acc[j][1];
+                sp[8 * L::LW] = acc[j][2]; sp[8 * L::LW + 1] = acc[j][3];
+            }
+        }
+        __syncthreads();                  // new state visible, Kd and U free
+        if (more) stage(sK, L::LK, a.Kd + (ch + 1) * GC * DK, DK, GC, DK);
+        cp_commit();
+    }
+    asm volatile("cp.async.wait_group 0;");
+    for (int i = threadIdx.x; i < DVS * (DK / 4); i += 256) {
+        const int r = i / (DK / 4), c4 = (i % (DK / 4)) * 4;
+        *reinterpret_cast<float4*>(Sg + (long)r * DK + c4) = *reinterpret_cast<const float4*>(sS + r * L::LW + c4);
+    }
+}
+
+template <int DK>
+static int launch_carry(const GdnCarryArgs& a, cudaStream_t s) {
+    const size_t smem = (size_t)Lay<DK>::floats * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        TSB_CHECK_CUDA(cudaFuncSetAttribute(gdn_chunk_carry_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    gdn_chunk_carry_kernel<DK><<<dim3(a.Dv / DVS, a.Hv), 256, smem, s>>>(a);
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}
+
+// One sequence: carries `state` through `nc` chunks of 64 tokens and writes the chunk outputs.
+extern "C" int tsb_gdn_chunk_carry(const GdnCarryArgs* args, void* stream) {
+    TSB_CHECK_ARG(args != nullptr, "gdn_chunk_carry: null arguments");
+    const GdnCarryArgs& a = *args;
+    TSB_CHECK_ARG(a.Hv > 0 && a.nc > 0, "gdn_chunk_carry: Hv=%d chunks=%d", a.Hv, a.nc);
+    TSB_CHECK_ARG(a.Dv % DVS == 0 && a.Dv > 0, "gdn_chunk_carry: value head size %d is not a multiple of %d", a.Dv, DVS);
+    switch (a.Dk) {
+    case 64: return launch_carry<64>(a, (cudaStream_t)stream);
+    case 128: return launch_carry<128>(a, (cudaStream_t)stream);
+    default:
+        tsb_set_error("gdn_chunk_carry: key head size %d unsupported (64, 128)", a.Dk);
+        return TSB_ERR_UNSUPPORTED;
+    }
+}

@@ -179,6 +179,83 @@ extern "C" int tsb_tp_reduce_norm(const void* tp, float* h, const float* w, floa
     return TSB_OK;
 }
 
+// ------------------------------------------------------------------------------------------
+// All-reduce of a small tensor y [rows, D] (f32, in place) over the same mailboxes: every CTA first stores
+// its row to every peer (tagged words), then polls its own mailbox and adds the ranks' rows in rank order, its
+// own row taken from registers.  A CTA waits only for stores that the peers issue before their own waits, so
+// CTAs need not be resident together.  The drop-in form of the exchange for model graphs that have no fused
+// projection + norm pair (sandwich norms, recurrent layers, shared experts).
+// ------------------------------------------------------------------------------------------
+template <int NT>
+__global__ void __launch_bounds__(NT) tp_all_reduce_kernel(const TpPush* tp, float* y, int D, int rows) {
+    pdl_wait();
+    pdl_trigger();
+    const int m = blockIdx.x;
+    const unsigned epoch = *tp->epoch;
+    const unsigned tag = epoch + 1;
+    const int size = tp->size, rank = tp->rank;
+    const long slot = (long)(epoch % TP_SLOTS) * tp->slot_stride;
+    float* yr = y + (long)m * D;
+    for (int i = threadIdx.x * 4; i < D; i += NT * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(yr + i);
+        for (int r = 0; r < size; ++r) {
+            if (r == rank) continue;
+            float2* dst = tp->mailbox[r] + slot + (long)rank * tp->src_stride + (long)m * D + i;
+            st_word(dst, v.x, tag); st_word(dst + 1, v.y, tag); st_word(dst + 2, v.z, tag); st_word(dst + 3, v.w, tag);
+        }
+    }
+    const float2* box = tp->mailbox[rank] + slot + (long)m * D;
+    for (int i = threadIdx.x * 4; i < D; i += NT * 4) {
+        const float4 own = *reinterpret_cast<const float4*>(yr + i);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < size; ++r) {
+            if (r == rank) { acc.x += own.x; acc.y += own.y; acc.z += own.z; acc.w += own.w; continue; }
+            const float2* src = box + (long)r * tp->src_stride + i;
+            uint4 a = ld_words2(src), b = ld_words2(src + 2);
+            if (a.y != tag || a.w != tag || b.y != tag || b.w != tag) {
+                const unsigned long long t0 = global_timer_ns();
+                unsigned spins = 0;
+                bool late = false;
+                do {
+                    __nanosleep(32);
+                    a = ld_words2(src);
+                    b = ld_words2(src + 2);
+                    if ((++spins & 63u) == 0 &&
+                        (global_timer_ns() - t0 > TP_WAIT_NS || *(volatile int*)tp->status != 0)) { late = true; break; }
+                } while (a.y != tag || a.w != tag || b.y != tag || b.w != tag);
+                if (late) {
+                    atomicCAS(tp->status, 0, 1 + r);
+                    if (a.y != tag) a.x = 0u;
+                    if (a.w != tag) a.z = 0u;
+                    if (b.y != tag) b.x = 0u;
+                    if (b.w != tag) b.z = 0u;
+                }
+            }
+            acc.x += __uint_as_float(a.x); acc.y += __uint_as_float(a.z);
+            acc.z += __uint_as_float(b.x); acc.w += __uint_as_float(b.z);
+        }
+        *reinterpret_cast<float4*>(yr + i) = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned t = atomicAdd(tp->ticket, 1u);
+        if (t == (unsigned)rows - 1) {
+            *tp->ticket = 0;
+            __threadfence();
+            *tp->epoch = epoch + 1;
+        }
+    }
+}
+
+extern "C" int tsb_tp_all_reduce(const void* tp, float* y, int rows, int D, void* stream) {
+    TSB_CHECK_ARG(tp && y && rows > 0 && D > 0, "tp_all_reduce: bad arguments");
+    TSB_CHECK_ARG(D % 4 == 0, "tp_all_reduce: D=%d must be a multiple of 4", D);
+    TSB_CHECK_ARG(((uintptr_t)y & 15) == 0, "tp_all_reduce: y must be 16-byte aligned");
+    TSB_CHECK_CUDA(tsb_launch(tp_all_reduce_kernel<256>, dim3(rows), dim3(256), 0, (cudaStream_t)stream, (const TpPush*)tp, y, D, rows));
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}
+
 // Host-visible status word: 0 = every wait was satisfied.
 extern "C" int tsb_tp_status(void* counters, int* out) {
     TSB_CHECK_ARG(counters && out, "tp_status: bad arguments");

@@ -186,6 +186,16 @@ class ModelBase:
                 self._tpx = TpExchange(self.comm, F.GEMV_MAX_M * max(1, self.exchange_parts), self.cfg.hidden)
         return self._tpx or None
 
+    def tp_all_reduce(self, y: torch.Tensor) -> torch.Tensor:
+        """Sum a row-parallel projection's output over the tensor-parallel group in place: through the peer-memory
+        mailboxes for small batches (decode, short prompts), through NCCL otherwise (long prompts, CPU, TSB_TP_FUSED=0)."""
+        if self.comm is None or self.comm.size <= 1:
+            return y
+        x = self.tp_exchange() if y.is_cuda else None
+        if x is not None and x.fits(y):
+            return x.all_reduce(y)
+        return self.comm.all_reduce(y)
+
     def tp_seq(self, T: int):
         """The sequence-parallel prefill exchange, sized for at least ``T`` tokens (TSB_TP_FUSED=0
         keeps the GEMM + NCCL all-reduce path)."""

@@ -95,7 +95,7 @@ class _GemmaBase(ModelBase):
             gu = F.glu(self.glu_act, F.linear(a, L["gate"], out_dtype=mid), F.linear(a, L["up"], out_dtype=mid))
         y = F.linear(F.as_act(gu), L["down"], out_dtype=torch.float32)
         if self.tp_size > 1:
-            self.comm.all_reduce(y)
+            self.tp_all_reduce(y)
         return y
 
     def _attention(self, l, L, a, batch: Batch, mid, rope: RopeSpec, scale: float, window: int, v_norm: bool,
@@ -124,7 +124,7 @@ class _GemmaBase(ModelBase):
         o = F.attention(qr, kc, vc, batch, scale=scale, Hq=Hq, Hkv=Hkv, Dh=Dh, window=window)
         y = F.linear(F.as_act(o), L["wo"], out_dtype=torch.float32)
         if self.tp_size > 1:
-            self.comm.all_reduce(y)
+            self.tp_all_reduce(y)
         return y
 
     def _logits(self, h, batch: Batch) -> torch.Tensor:

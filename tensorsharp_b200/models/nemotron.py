@@ -154,7 +154,7 @@ class NemotronHModel(ModelBase):
             x = F.as_act(F.linear(a, L["latent_in"], out_dtype=torch.float32))
         y = F.moe_experts(x, ids, w, L["up_exps"], L["down_exps"], act="relu2", expert_offset=self.e0)
         if self.e1 - self.e0 != self.n_experts and self.comm is not None:
-            self.comm.all_reduce(y)
+            self.tp_all_reduce(y)
         if L["latent_out"] is not None:
             y = F.linear(F.as_act(y), L["latent_out"], out_dtype=torch.float32)
         if L["sh_up"] is not None:

@@ -134,7 +134,7 @@ class Qwen35Model(ModelBase):
         ids, w = F.route_topk_softmax(logits, self.top_k)
         y = F.moe_experts(a, ids, w, L["gate_up_exps"], L["down_exps"], act="swiglu", expert_offset=self.e0)
         if self.e1 - self.e0 != self.n_experts and self.comm is not None:
-            self.comm.all_reduce(y)
+            self.tp_all_reduce(y)
         if "sh_down" in L:
             s = self._swiglu(a, L["sh_gate_up"], L["sh_gate"], L["sh_up"], L["sh_down"], mid)
             if L.get("sh_inp") is not None:
@@ -173,7 +173,7 @@ class Qwen35Model(ModelBase):
         o = F.glu("sigmoid_mul", gate.reshape(T, Hq * Dh).contiguous(), o)
         y = F.linear(F.as_act(o), L["wo"], out_dtype=torch.float32)
         if self.tp_size > 1:
-            self.comm.all_reduce(y)
+            self.tp_all_reduce(y)
         return y
 
     def forward_batch(self, batch: Batch, want_logits: bool = True) -> Optional[torch.Tensor]:

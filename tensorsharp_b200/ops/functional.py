@@ -367,7 +367,7 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
     the quantised projection that follows needs no quantise launch."""
     T = q.shape[0]
     if as_act:
-        if q.is_cuda and batch.is_decode and (Hq // Hkv) in (1, 2, 4, 8) and Dh % 32 == 0:
+        if q.is_cuda and batch.is_decode and Dh % 32 == 0:
             sp = decode_splits(batch, Hkv, window)
             out, oq, ods = _k().attn_decode(q, k_cache, v_cache, batch.block_table, batch.kv_lens, scale=scale, Hq=Hq, Hkv=Hkv,
                                             Dh=Dh, page_size=batch.page_size, splits=sp, split_len=decode_split_len(batch, sp, window),
@@ -377,8 +377,7 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
                                    softcap=softcap))
     if q.is_cuda:
         kk = _k()
-        G = Hq // Hkv
-        if batch.is_decode and G in (1, 2, 4, 8):
+        if batch.is_decode:
             sp = decode_splits(batch, Hkv, window)
             out = kk.attn_decode(q, k_cache, v_cache, batch.block_table, batch.kv_lens, scale=scale, Hq=Hq, Hkv=Hkv,
                                  Dh=Dh, page_size=batch.page_size, splits=sp, split_len=decode_split_len(batch, sp, window),
@@ -554,13 +553,28 @@ def _gdn_chunk_min() -> int:
     return max(2, int(os.environ.get("GDN_CHUNK_PREFILL_MIN_SEQ_LEN", "64") or 64))
 
 
+CUDA_CHUNKED_MIN_TOKENS = 1024
+
+
+def _use_chunked_scan(batch: Batch, on_cuda: bool, switch: str) -> bool:
+    """Whether a recurrent layer runs its chunked form for this batch.  CPU: prompts of ``_gdn_chunk_min()`` tokens or
+    more.  CUDA: prompts of ``CUDA_CHUNKED_MIN_TOKENS`` or more (one B200, 2048 tokens: GatedDeltaNet 5.9 ms as a scan,
+    3.6 ms chunked; Mamba2 3.3 against 2.9 ms; at 8192 tokens 23.8 / 12.9 and 18.8 / 8.1 ms; at 512 the scan wins);
+    ``<switch>=1`` lowers the bar to the CPU's, ``=0`` keeps the scan kernel."""
+    if not on_cuda:
+        return batch.max_q_len >= _gdn_chunk_min()
+    mode = os.environ.get(switch, "")
+    if mode == "0":
+        return False
+    return batch.max_q_len >= (_gdn_chunk_min() if mode == "1" else max(CUDA_CHUNKED_MIN_TOKENS, _gdn_chunk_min()))
+
+
 def gdn(qkv: torch.Tensor, z: torch.Tensor, beta: torch.Tensor, alpha: torch.Tensor, dt_bias, a_log, norm_w,
         state: torch.Tensor, batch: Batch, *, Hk: int, Hv: int, Dk: int, Dv: int, eps: float) -> torch.Tensor:
     """GatedDeltaNet recurrence over the packed tokens -> gated output [T, Hv*Dv].  Decode steps and short prompts
-    run the token-by-token scan (one kernel on CUDA); prompts of ``_gdn_chunk_min()`` tokens or more run the chunked
-    form (matrix products over heads x chunks) on CPU, and on CUDA when ``TSB_GDN_CHUNKED=1``."""
-    chunk_min = _gdn_chunk_min()
-    chunked = batch.max_q_len >= chunk_min and (not qkv.is_cuda or os.environ.get("TSB_GDN_CHUNKED", "0") == "1")
+    run the token-by-token scan (one kernel on CUDA); longer prompts run the chunked form (matrix products over heads x
+    chunks; thresholds in :func:`_use_chunked_scan`)."""
+    chunked = _use_chunked_scan(batch, qkv.is_cuda, "TSB_GDN_CHUNKED")
     if qkv.is_cuda and not chunked:
         return _k().gdn_recurrent(qkv, z, beta, alpha, dt_bias, a_log, norm_w, state, batch.cu_q, batch.seq_slots,
                                   Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=eps)
@@ -570,7 +584,11 @@ def gdn(qkv: torch.Tensor, z: torch.Tensor, beta: torch.Tensor, alpha: torch.Ten
         q0, q1 = batch.h_cu_q[b], batch.h_cu_q[b + 1]
         args = (qkv[q0:q1], z[q0:q1], beta[q0:q1], alpha[q0:q1], dt_bias, a_log, norm_w, state[slots[b]])
         if chunked:                             # every sequence of a batch that took this route, short ones included
-            outs.append(ref.gdn_chunked(*args, Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=eps))
+            carry = None
+            if qkv.is_cuda and os.environ.get("TSB_GDN_CARRY_KERNEL", "1") != "0" and _k().gdn_chunk_carry_supported(Dk, Dv, 64) \
+                    and args[-1].is_contiguous():
+                carry = _k().gdn_chunk_carry
+            outs.append(ref.gdn_chunked(*args, Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=eps, carry=carry))
         else:
             outs.append(ref.gdn_recurrent(*args, Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=eps))
     return torch.cat(outs, 0).to(torch.bfloat16 if qkv.is_cuda else torch.float32)     # the kernel's output types
@@ -579,8 +597,8 @@ def gdn(qkv: torch.Tensor, z: torch.Tensor, beta: torch.Tensor, alpha: torch.Ten
 def mamba2(xbc: torch.Tensor, dt: torch.Tensor, dt_bias, A, D, state: torch.Tensor, batch: Batch, *, H: int, P: int,
            G: int, N: int) -> torch.Tensor:
     """Mamba2 selective scan over the packed tokens -> y f32 [T, H*P] (before gating).  Prompts of
-    ``_gdn_chunk_min()`` tokens or more take the chunked form on CPU, and on CUDA when ``TSB_MAMBA_CHUNKED=1``."""
-    chunked = batch.max_q_len >= _gdn_chunk_min() and (not xbc.is_cuda or os.environ.get("TSB_MAMBA_CHUNKED", "0") == "1")
+    long prompts take the chunked form (thresholds in :func:`_use_chunked_scan`)."""
+    chunked = _use_chunked_scan(batch, xbc.is_cuda, "TSB_MAMBA_CHUNKED")
     if xbc.is_cuda and not chunked:
         return _k().mamba2_recurrent(xbc, dt, dt_bias, A, D, state, batch.cu_q, batch.seq_slots, H=H, P=P, G=G, N=N)
     outs = []

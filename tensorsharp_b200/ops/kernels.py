@@ -461,6 +461,11 @@ class GdnArgs(C.Structure):
                 ("Hk", C.c_int), ("Hv", C.c_int), ("Dk", C.c_int), ("Dv", C.c_int), ("B", C.c_int)]
 
 
+class GdnCarryArgs(C.Structure):
+    _fields_ = [("U0", _vp), ("W", _vp), ("Qd", _vp), ("Kd", _vp), ("P", _vp), ("gamma", _vp), ("state", _vp), ("out", _vp),
+                ("Hv", C.c_int), ("nc", C.c_int), ("Dk", C.c_int), ("Dv", C.c_int)]
+
+
 class MambaArgs(C.Structure):
     _fields_ = [("xbc", _vp), ("xbc_s", C.c_long), ("dt", _vp), ("dt_s", C.c_long), ("dt_f32", C.c_int),
                 ("dt_bias", _vp), ("A", _vp), ("D", _vp), ("state", _vp), ("cu_q", _vp), ("seq_slots", _vp),
@@ -494,6 +499,27 @@ def gdn_recurrent(qkv, z, beta, alpha, dt_bias, a_log, norm_w, state, cu_q, seq_
     a.cu_q, a.seq_slots, a.out, a.out_s, a.eps = _p(cu_q), _p(seq_slots), _p(out), Hv * Dv, eps
     a.Hk, a.Hv, a.Dk, a.Dv, a.B = Hk, Hv, Dk, Dv, cu_q.numel() - 1
     native.check(_lib().tsb_gdn_recurrent(C.byref(a), _stream()), "gdn_recurrent")
+    _count(1)
+    return out
+
+
+def gdn_chunk_carry_supported(Dk: int, Dv: int, chunk: int) -> bool:
+    return chunk == 64 and Dk in (64, 128) and Dv % 32 == 0
+
+
+def gdn_chunk_carry(U0, W, Qd, Kd, P, gamma, state) -> torch.Tensor:
+    """The sequential part of the chunked GatedDeltaNet prefill for one sequence: ``state`` [Hv, Dv, Dk] f32 (contiguous,
+    updated in place) carried through the chunks of U0 [Hv, nc, 64, Dv], W / Qd / Kd [Hv, nc, 64, Dk], P [Hv, nc, 64, 64],
+    gamma [Hv, nc] -> outputs [Hv, nc, 64, Dv] f32."""
+    U0, W, Qd, Kd, P, gamma = (t.float().contiguous() for t in (U0, W, Qd, Kd, P, gamma))
+    Hv, nc, Cn, Dv = U0.shape
+    Dk = W.shape[-1]
+    assert Cn == 64 and state.dtype == torch.float32 and state.is_contiguous() and state.shape == (Hv, Dv, Dk)
+    out = torch.empty((Hv, nc, Cn, Dv), dtype=torch.float32, device=U0.device)
+    a = GdnCarryArgs()
+    a.U0, a.W, a.Qd, a.Kd, a.P, a.gamma, a.state, a.out = _p(U0), _p(W), _p(Qd), _p(Kd), _p(P), _p(gamma), _p(state), _p(out)
+    a.Hv, a.nc, a.Dk, a.Dv = Hv, nc, Dk, Dv
+    native.check(_lib().tsb_gdn_chunk_carry(C.byref(a), _stream()), "gdn_chunk_carry")
     _count(1)
     return out
 

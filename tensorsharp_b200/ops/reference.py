@@ -164,12 +164,13 @@ def gdn_recurrent(qkv, z, beta, alpha, dt_bias, a_log, norm_w, state, *, Hk, Hv,
     return out
 
 
-def gdn_chunked(qkv, z, beta, alpha, dt_bias, a_log, norm_w, state, *, Hk, Hv, Dk, Dv, eps, chunk: int = 64):
+def gdn_chunked(qkv, z, beta, alpha, dt_bias, a_log, norm_w, state, *, Hk, Hv, Dk, Dv, eps, chunk: int = 64, carry=None):
     """The recurrence of :func:`gdn_recurrent` in chunked form (Qwen35Model.cs:888-1192 does its prefill the same way):
     inside a chunk of ``chunk`` tokens the delta-rule updates are solved at once as a unit lower-triangular system
     (the WY form), so the work is matrix products over (heads x chunks) and only three small products per chunk run
     in sequence to carry the state.  One sequence; ``state`` [Hv, Dv, Dk] is updated in place; plain tensor ops, so it
-    runs on whichever device the inputs live on.  Returns [n, Hv*Dv]."""
+    runs on whichever device the inputs live on.  ``carry`` replaces the loop over the chunks (a kernel on CUDA).
+    Returns [n, Hv*Dv]."""
     n = qkv.shape[0]
     dev = qkv.device
     C = chunk
@@ -203,15 +204,19 @@ def gdn_chunked(qkv, z, beta, alpha, dt_bias, a_log, norm_w, state, *, Hk, Hv, D
     Qd = Q * decay
     Kd = K * torch.exp(cum[..., -1:] - cum).unsqueeze(-1)
     gamma = torch.exp(cum[..., -1])                                          # [Hv, nc]
-    S = state.float()
-    outs = []
-    for c in range(nc):
-        St = S.transpose(-1, -2)                                             # [Hv, Dk, Dv]
-        U = U0[:, c] - W[:, c] @ St
-        outs.append(Qd[:, c] @ St + P[:, c] @ U)                             # [Hv, C, Dv]
-        S = gamma[:, c].view(Hv, 1, 1) * S + U.transpose(-1, -2) @ Kd[:, c]
-    state.copy_(S)
-    core = torch.stack(outs, 1).reshape(Hv, nc * C, Dv)[:, :n].transpose(0, 1)          # [n, Hv, Dv]
+    if carry is not None:                # the chunk-after-chunk part as one kernel (csrc/gdn_chunk.cu)
+        core = carry(U0, W, Qd, Kd, P, gamma, state)                         # [Hv, nc, C, Dv]; state updated in place
+    else:
+        S = state.float()
+        outs = []
+        for c in range(nc):
+            St = S.transpose(-1, -2)                                         # [Hv, Dk, Dv]
+            U = U0[:, c] - W[:, c] @ St
+            outs.append(Qd[:, c] @ St + P[:, c] @ U)                         # [Hv, C, Dv]
+            S = gamma[:, c].view(Hv, 1, 1) * S + U.transpose(-1, -2) @ Kd[:, c]
+        state.copy_(S)
+        core = torch.stack(outs, 1)
+    core = core.reshape(Hv, nc * C, Dv)[:, :n].transpose(0, 1)                           # [n, Hv, Dv]
     core = core * torch.rsqrt(core.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float()
     return (core * torch.nn.functional.silu(z.float().view(n, Hv, Dv))).reshape(n, Hv * Dv)
 

@@ -93,6 +93,24 @@ class TpExchange:
         self.exchanges += 1
         return Act(yb, yq, yds) if norm else None
 
+    def fits(self, y: torch.Tensor) -> bool:
+        """Whether :meth:`all_reduce` takes ``y``: f32, contiguous, 2-D, within the mailbox's rows and row length."""
+        return (y.is_cuda and y.dtype == torch.float32 and y.dim() == 2 and y.is_contiguous() and 0 < y.shape[0] <= self.max_rows
+                and y.shape[1] <= self.max_d and y.shape[1] % 4 == 0 and y.data_ptr() % 16 == 0)
+
+    def all_reduce(self, y: torch.Tensor) -> torch.Tensor:
+        """Sum ``y`` [rows, D] over the ranks in place (rank order, so every rank holds the same bits): one kernel
+        that stores its rows into every peer's mailbox and adds what the peers stored into its own."""
+        from ..ops import kernels as k
+        lib = k._lib()
+        lib.tsb_tp_all_reduce.restype = C.c_int
+        native.check(lib.tsb_tp_all_reduce(C.c_void_p(self.struct.data_ptr()), k._p(y), C.c_int(y.shape[0]), C.c_int(y.shape[1]),
+                                           k._stream()), "tp_all_reduce")
+        k._count(1)
+        self.exchanges += 1
+        self.comm.bytes_reduced += y.numel() * 4
+        return y
+
     # ------------------------------------------------------------------ health
     def status(self) -> int:
         """0 when every wait so far was satisfied, else 1 + the rank whose flag did not arrive

@@ -194,7 +194,8 @@ def _gather(kc, table, b, L, ps):
     return kc[idx]
 
 
-@pytest.mark.parametrize("Hq,Hkv,Dh", [(8, 2, 128), (4, 4, 64), (16, 2, 256), (2, 1, 64)])
+@pytest.mark.parametrize("Hq,Hkv,Dh", [(8, 2, 128), (4, 4, 64), (16, 2, 256), (2, 1, 64), (8, 2, 512), (6, 2, 128), (12, 1, 64),
+                                       (5, 1, 128), (32, 2, 64), (2, 2, 512)])
 @pytest.mark.parametrize("window,sinks,softcap", [(0, False, 0.0), (100, True, 0.0), (0, False, 30.0)])
 def test_attn_decode(Hq, Hkv, Dh, window, sinks, softcap):
     torch.manual_seed(7)
@@ -214,7 +215,7 @@ def test_attn_decode(Hq, Hkv, Dh, window, sinks, softcap):
             assert rel_err(got[b], want[0]) < 1e-2, (b, splits, rel_err(got[b], want[0]))
 
 
-@pytest.mark.parametrize("Hq,Hkv,Dh", [(4, 2, 128), (2, 2, 64), (4, 1, 256)])
+@pytest.mark.parametrize("Hq,Hkv,Dh", [(4, 2, 128), (2, 2, 64), (4, 1, 256), (4, 2, 512), (3, 1, 128)])
 @pytest.mark.parametrize("window,sinks,softcap", [(0, False, 0.0), (70, True, 0.0), (0, False, 50.0)])
 def test_attn_prefill(Hq, Hkv, Dh, window, sinks, softcap):
     torch.manual_seed(8)

@@ -14,6 +14,9 @@ FAMILIES = {
     "gemma3": (synth.write_gemma, {"arch": "gemma3"}),
     "gemma4": (synth.write_gemma, {"arch": "gemma4", "n_layers": 8, "head_dim_global": 128, "kv_heads_global": 1,
                                    "rot_global": 64, "shared_kv": 2, "ple_dim": 32, "n_experts": 4, "top_k": 2}),
+    # global layers with 512-wide heads and four query heads per KV head (Gemma 4's full-size layout)
+    "gemma4_wide_heads": (synth.write_gemma, {"arch": "gemma4", "n_layers": 6, "head_dim_global": 512, "kv_heads_global": 1,
+                                              "rot_global": 128}),
     "mistral3": (synth.write_mistral3, {}),
     "nemotron_h": (synth.write_nemotron_h, {}),
 }

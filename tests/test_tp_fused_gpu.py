@@ -174,3 +174,29 @@ def test_fused_decode_step_with_tensor_parallel_ranks(n, tmp_path_factory):
     assert r["spread"] == 0.0, r
     assert r["tp_vs_single_mega"] < 0.05 and r["tp_vs_single_plain"] < 0.12, (r["tp_vs_single_mega"], r["tp_vs_single_plain"], r["mega_vs_plain"])
     assert r["graph_tokens"] == r["eager_tokens"], r
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_mailbox_all_reduce_in_gemma_qwen35_nemotron(n, tmp_path_factory):
+    """The families without a fused projection + norm pair sum their row-parallel projections (attention output, MLP,
+    experts) with the mailbox all-reduce kernel for decode-sized batches: same logits as the NCCL path and as one GPU,
+    and the captured decode graph follows the eager tokens."""
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+    from tensorsharp_b200.models import synth
+    d = tmp_path_factory.mktemp("tpfam")
+    paths = [str(d / "gemma3.gguf"), str(d / "qwen35.gguf"), str(d / "nemotron.gguf")]
+    synth.write_gemma(paths[0], arch="gemma3", n_heads=8, n_kv_heads=4, device="cpu")
+    synth.write_qwen35(paths[1], device="cpu") if n == 2 else synth.write_qwen35(paths[1], n_heads=8, n_kv_heads=4, device="cpu")
+    synth.write_nemotron_h(paths[2], device="cpu")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TSB_WORKER_MODE="families")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(HERE, "tp_worker.py"), *paths]
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    res = [json.loads(l[8:]) for l in p.stdout.splitlines() if l.startswith("TPCHECK ")]
+    assert p.returncode == 0 and len(res) == 3, f"rc={p.returncode}\nstdout:\n{p.stdout[-3000:]}\nstderr:\n{p.stderr[-3000:]}"
+    for r in res:
+        assert r["status"] == 0 and r["exchanges"] > 0, r
+        assert r["fused_vs_nccl"] <= 1e-2 * max(1.0, r["scale"]), r
+        assert r["fused_vs_single"] <= 3e-2 * max(1.0, r["scale"]), r
+        assert r["graph_tokens"] == r["eager_tokens"], r

@@ -53,3 +53,31 @@ def test_chunked_routes_match_the_scan_kernels(monkeypatch):
         outs[mode] = F.mamba2(xbc, dt, dtb, A, D, st, _batch(lens, dev), H=H, P=P, G=G, N=N)
         states[mode] = st
     assert _rel(outs["1"], outs["0"]) < 1e-3 and _rel(states["1"], states["0"]) < 1e-3
+
+
+@pytest.mark.parametrize("Hk,Hv,Dk,Dv", [(2, 4, 128, 128), (1, 2, 64, 96)])
+def test_chunk_carry_kernel_matches_the_scan_across_chunk_and_call_boundaries(monkeypatch, Hk, Hv, Dk, Dv):
+    """csrc/gdn_chunk.cu (state carried chunk after chunk on the tensor cores, tf32 operands) against the token-by-token
+    scan kernel and against the same chunked algebra as tensor ops: odd lengths, a state that is not zero, and a second
+    call that continues from the state the first one left."""
+    torch.manual_seed(1)
+    dev = "cuda"
+    dtb, a_log, nw = torch.randn(Hv, device=dev) * 0.5, -torch.rand(Hv, device=dev), torch.rand(Dv, device=dev) + 0.5
+    s0 = torch.randn(2, Hv, Dv, Dk, device=dev) * 0.1
+    results = {}
+    for mode, carry in (("0", "1"), ("1", "0"), ("1", "1")):        # scan kernel; chunked tensor ops; chunked + carry kernel
+        monkeypatch.setenv("TSB_GDN_CHUNKED", mode)
+        monkeypatch.setenv("TSB_GDN_CARRY_KERNEL", carry)
+        torch.manual_seed(2)
+        st = s0.clone()
+        outs = []
+        for lens in ([333], [129, 64], [70]):                       # the first sequence slot continues over three calls
+            T = sum(lens)
+            qkv = torch.randn(T, 2 * Hk * Dk + Hv * Dv, device=dev)
+            z, beta, alpha = torch.randn(T, Hv * Dv, device=dev), torch.randn(T, Hv, device=dev), torch.randn(T, Hv, device=dev)
+            b = _batch(lens, dev)
+            outs.append(F.gdn(qkv, z, beta, alpha, dtb, a_log, nw, st, b, Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=1e-6).float())
+        results[(mode, carry)] = (torch.cat(outs), st)
+    scan, loop, kern = results[("0", "1")], results[("1", "0")], results[("1", "1")]
+    assert _rel(kern[0], loop[0]) < 1e-2 and _rel(kern[1], loop[1]) < 3e-3, (_rel(kern[0], loop[0]), _rel(kern[1], loop[1]))
+    assert _rel(kern[0], scan[0]) < 2e-2 and _rel(kern[1], scan[1]) < 3e-3, (_rel(kern[0], scan[0]), _rel(kern[1], scan[1]))

@@ -23,6 +23,12 @@ def main():
         comm.barrier()
         torch.cuda.synchronize()
         os._exit(0)
+    if os.environ.get("TSB_WORKER_MODE") == "families":
+        for path in sys.argv[1:]:
+            check_family(path, comm)
+        comm.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
     if os.environ.get("TSB_WORKER_MODE") == "cp_model":
         check_context_parallel_model(sys.argv[1], comm)
         comm.barrier()
@@ -162,6 +168,49 @@ def check_mega(path, comm):
         res["tp_vs_single_plain"] = rel(tp[1:], ref_plain[1:])
         res["mega_vs_plain"] = rel(ref_mega[1:], ref_plain[1:])
         print("MEGACHECK " + json.dumps(res), flush=True)
+    comm.barrier()
+
+
+def check_family(path, comm):
+    """Families whose row-parallel projections are summed by the mailbox all-reduce kernel (Gemma, Qwen3.5, Nemotron-H):
+    decode-sized batches through the mailboxes against the NCCL path and one GPU, eagerly and inside a captured graph."""
+    from tensorsharp_b200.models.base import ModelBase
+    from tensorsharp_b200.runtime.engine import DecodeGraph
+    rank, world = comm.rank, comm.size
+    os.environ["TSB_TP_FUSED"] = "1"
+    g = torch.Generator().manual_seed(12)
+    prompt = torch.randint(0, 4096, (9,), generator=g).tolist()
+
+    def run(model, steps=5):
+        model.reset_kv_cache()
+        out = [model.forward(prompt).float().clone()]
+        for _ in range(steps):
+            out.append(model.forward([int(out[-1].argmax())]).float().clone())
+        return torch.stack(out)
+
+    model = ModelBase.create(path, comm.device, max_context=256, max_seqs=2, tp_rank=rank, tp_size=world, comm=comm)
+    fused = run(model)
+    tpx = model.tp_exchange()
+    status, exchanges = tpx.status(), tpx.exchanges
+    model.reset_kv_cache()
+    first = int(model.forward(prompt).argmax())
+    dg = DecodeGraph(model, [model._seq()], 8)
+    dg.set_tokens([first])
+    dg.capture()
+    graph_tokens = [first] + [int(dg.step()[0]) for _ in range(4)]
+    eager_tokens = [int(x.argmax()) for x in fused[:5]]
+    status |= tpx.status()
+    model._tpx = False
+    os.environ["TSB_TP_FUSED"] = "0"
+    nccl = run(model)
+    res = {"world": world, "arch": model.arch, "status": status, "exchanges": exchanges,
+           "fused_vs_nccl": float((fused - nccl).abs().max()), "graph_tokens": graph_tokens, "eager_tokens": eager_tokens}
+    if rank == 0:
+        single = ModelBase.create(path, comm.device, max_context=256)
+        ref = run(single)
+        res["fused_vs_single"] = float((fused - ref).abs().max())
+        res["scale"] = float(ref.abs().max())
+        print("TPCHECK " + json.dumps(res), flush=True)
     comm.barrier()
 
 
