@@ -34,6 +34,10 @@ struct GemmEpi {
     const TpSeq* ag;        // all-gather -> GEMM: X is the gathered buffer; wait for the tile's shard to arrive
     int rs_rows;            // size * shard (host copy, for the grid)
     int tile_rot;           // token tiles are visited starting from this one (see tsb_gemm_bf16_tp)
+    // Grouped mode (mixture of experts): W is a stack of matrices of N rows each, X holds the rows of all groups sorted
+    // by group, and token tile y of the grid is described by groups[3 * y .. 3 * y + 2] = {matrix index or -1 for an
+    // unused tile, first row, end row}.  The list is built on the device, so the host never learns the group sizes.
+    const int* groups;
 };
 
 template <int BN, int STAGES>
@@ -60,7 +64,10 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * 128;       // first feature (row of W)
-    const int n0 = (int)((blockIdx.y + (unsigned)ep.tile_rot) % gridDim.y) * BN;        // first token
+    int n0 = (int)((blockIdx.y + (unsigned)ep.tile_rot) % gridDim.y) * BN;        // first token
+    int t_end = ep.T;                      // tokens at or past this row are not stored
+    int w_row0 = m0;                       // row of the (stacked) weight matrix where this tile's features start
+    bool active = true;
     const int kblocks = (K + 63) / 64;
 
     if (threadIdx.x == 0) {
@@ -78,8 +85,19 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();        // barrier set-up and the TMEM allocation above overlap the previous kernel's tail
     pdl_trigger();
+    int group = 0;
+    if (ep.groups != nullptr) {
+        const int* gt = ep.groups + 3 * blockIdx.y;
+        group = gt[0];
+        active = group >= 0;
+        n0 = gt[1];
+        t_end = gt[2];
+        w_row0 = group * ep.N + m0;
+    }
 
-    if (warp == 0) {
+    if (!active) {
+        // an unused entry of the tile list: nothing to load, multiply or store
+    } else if (warp == 0) {
         if (lane == 0) {
             tc::tma_prefetch_desc(&tmW);
             tc::tma_prefetch_desc(&tmX);
@@ -97,7 +115,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                 if (!tc::mbar_wait(&empty_bar[s], ph ^ 1)) { atomicExch(status, 1); break; }
                 unsigned char* a = smem + s * L::STAGE_BYTES;
                 tc::mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
-                tc::tma_load_2d(a, &tmW, &full_bar[s], kb * 64, m0);
+                tc::tma_load_2d(a, &tmW, &full_bar[s], kb * 64, w_row0);
                 tc::tma_load_2d(a + L::A_BYTES, &tmX, &full_bar[s], kb * 64, n0);
             }
         }
@@ -126,7 +144,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
         const int n = m0 + q * 32 + lane;             // feature owned by this thread
         if (tc::mbar_wait(acc_bar, 0)) {
             tc::fence_after_sync();
-            const float bias = (ep.bias && n < ep.N && (ep.rs == nullptr || ep.rs->rank == 0)) ? ep.bias[n] : 0.f;
+            const float bias = (ep.bias && n < ep.N && (ep.rs == nullptr || ep.rs->rank == 0)) ? ep.bias[(long)group * ep.N + n] : 0.f;
             bf16* rs_dst = nullptr;
             if (ep.rs != nullptr) {
                 const TpSeq* g = ep.rs;
@@ -155,7 +173,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int t = n0 + c * 16 + j;
-                        if (t < ep.T) {
+                        if (t < t_end) {
                             float v = __uint_as_float(r[j]) + bias;
                             const long o = (long)t * ep.ldo + n;
                             if (ep.out_f32) {
@@ -312,6 +330,33 @@ extern "C" int tsb_gemm_bf16_tp(const void* W, long ldw, const void* X, long ldx
     case 32: return launch_gemm<32, 8>(tw, tx, ep, K, status, s);
     case 64: return launch_gemm<64, 8>(tw, tx, ep, K, status, s);
     case 128: return two_per_sm ? launch_gemm<128, 3>(tw, tx, ep, K, status, s) : launch_gemm<128, 6>(tw, tx, ep, K, status, s);
+    default: return launch_gemm<256, 4>(tw, tx, ep, K, status, s);
+    }
+}
+
+// Grouped GEMM over a stack of matrices (mixture-of-experts prefill): W [E * N, K] bf16, X [P, K] bf16 with the rows of
+// each group contiguous, `groups` a device list of `n_tiles` entries {matrix index or -1, first row, end row} whose
+// tiles hold at most `bn` rows (32, 64, 128 or 256).  out [P, ldo]; bias [E, N] or null.  Rows that no tile covers are
+// left as they are.  The host passes only upper bounds (P, n_tiles): the list itself is built by device code.
+extern "C" int tsb_gemm_bf16_grouped(const void* W, long ldw, int E, const void* X, long ldx, void* out, long ldo, int out_f32,
+                                     const float* bias, int P, int N, int K, const int* groups, int n_tiles, int bn,
+                                     int* status, void* stream) {
+    TSB_CHECK_ARG(P >= 0 && N > 0 && K > 0 && E > 0 && n_tiles >= 0, "gemm_bf16_grouped: bad shape P=%d N=%d K=%d E=%d", P, N, K, E);
+    TSB_CHECK_ARG(K % 8 == 0 && ldw % 8 == 0 && ldx % 8 == 0, "gemm_bf16_grouped: K, ldw, ldx must be multiples of 8");
+    TSB_CHECK_ARG(bn == 32 || bn == 64 || bn == 128 || bn == 256, "gemm_bf16_grouped: tile of %d rows", bn);
+    TSB_CHECK_ARG(status != nullptr && groups != nullptr, "gemm_bf16_grouped: status word and tile list are required");
+    if (P == 0 || n_tiles == 0) return TSB_OK;
+    CUtensorMap tw, tx;
+    int rc = tsb_make_tmap_2d_bf16(&tw, W, (uint64_t)E * N, (uint64_t)K, (uint64_t)ldw, 128, 64);
+    if (rc) return rc;
+    rc = tsb_make_tmap_2d_bf16(&tx, X, (uint64_t)P, (uint64_t)K, (uint64_t)ldx, (uint32_t)bn, 64);
+    if (rc) return rc;
+    GemmEpi ep{out, bias, nullptr, ldo, n_tiles * bn, N, out_f32, nullptr, nullptr, 0, 0, groups};
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (bn) {
+    case 32: return launch_gemm<32, 8>(tw, tx, ep, K, status, s);
+    case 64: return launch_gemm<64, 8>(tw, tx, ep, K, status, s);
+    case 128: return launch_gemm<128, 6>(tw, tx, ep, K, status, s);
     default: return launch_gemm<256, 4>(tw, tx, ep, K, status, s);
     }
 }

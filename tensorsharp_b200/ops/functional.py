@@ -500,7 +500,10 @@ def moe_experts(a: Act, ids: torch.Tensor, weights: torch.Tensor, gate_up: Quant
                                   gate_up_bias=gate_up_bias, down_bias=down_bias, expert_offset=expert_offset)
         return kk.moe_grouped(xb=a.b.contiguous(), ids=ids, weights=wts, gate_up=gate_up, down=down, act=act,
                               gate_up_bias=gate_up_bias, down_bias=down_bias, expert_offset=expert_offset)
-    # grouped path: sort the (token, slot) pairs by expert and run each expert on its rows
+    if dev.type == "cuda" and os.environ.get("TSB_MOE_GROUPED_GEMM", "1") != "0" and gate_up.K % 8 == 0 and down.K % 8 == 0:
+        return _moe_grouped_gemm(a, ids, local, weights, gate_up, down, act, gate_up_bias, down_bias, down_scale)
+    # per-expert path (CPU oracle, and CUDA with TSB_MOE_GROUPED_GEMM=0): sort the (token, slot) pairs by expert on the
+    # host and run each expert on its rows
     out = torch.zeros((T, D), dtype=torch.float32, device=dev)
     flat = local.reshape(-1)
     order = torch.argsort(flat, stable=True)
@@ -523,6 +526,63 @@ def moe_experts(a: Act, ids: torch.Tensor, weights: torch.Tensor, gate_up: Quant
         db = down_bias[e] if down_bias is not None else None
         y2 = linear(as_act(y1), down.expert(e), bias=db, out_dtype=torch.float32)
         out.index_add_(0, tok, y2 * wflat[rows].unsqueeze(1))
+    return out
+
+
+def moe_tile_list(flat: torch.Tensor, n_groups: int, bn: int):
+    """Device-side work list of a grouped GEMM.  ``flat`` [P]: group of every row, -1 = skipped.  Returns ``(order,
+    tiles)``: ``order`` sorts the rows by group (skipped rows first), ``tiles`` int32 [ceil(P / bn) + n_groups, 3] holds
+    (group or -1, first sorted row, end sorted row) per tile of at most ``bn`` rows.  Nothing is read back to the host:
+    the list has a fixed upper-bound length and unused entries are marked -1."""
+    P = flat.numel()
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount((flat + 1).long(), minlength=n_groups + 1)
+    starts = torch.cumsum(counts, 0) - counts
+    cnt, st = counts[1:], starts[1:]
+    per = (cnt + bn - 1) // bn
+    cum = torch.cumsum(per, 0)
+    n_tiles = (P + bn - 1) // bn + n_groups
+    t = torch.arange(n_tiles, device=flat.device)
+    e = torch.searchsorted(cum, t, right=True)
+    valid = e < n_groups
+    ec = e.clamp(max=n_groups - 1)
+    first = st[ec] + (t - (cum[ec] - per[ec])) * bn
+    tiles = torch.stack([torch.where(valid, e, torch.full_like(e, -1)), first, st[ec] + cnt[ec]], 1).to(torch.int32)
+    return order, tiles.contiguous()
+
+
+def _moe_grouped_gemm(a: Act, ids, local, weights, gate_up: QuantWeight, down: QuantWeight, act, gate_up_bias, down_bias,
+                      down_scale) -> torch.Tensor:
+    """Large batches (prefill): the (token, slot) pairs are sorted by expert on the device, both projections run as one
+    grouped tensor-core GEMM each over a device-built tile list (no host read-back, two GEMM launches whatever the
+    number of experts), and the weighted rows are added back to their tokens."""
+    kk = _k()
+    T, k = ids.shape
+    D, E = down.N, gate_up.experts
+    P = T * k
+    avg = max(1, P // max(1, E))
+    bn = 32 if avg <= 32 else 64 if avg <= 64 else 128 if avg <= 128 else 256
+    flat = local.reshape(-1)
+    order, tiles = moe_tile_list(flat, E, bn)
+    tok = torch.div(order, k, rounding_mode="floor")
+    x = a.b if a.b.dtype == torch.bfloat16 else a.b.to(torch.bfloat16)
+    xs = x[tok].contiguous()                                         # rows in expert order
+    glu_act = act not in ("relu2", "silu")
+    y1 = kk.gemm_bf16_grouped(_dequant_scratch(gate_up), E, xs, tiles, bn, out_dtype=torch.bfloat16,
+                              bias=gate_up_bias.float().contiguous() if gate_up_bias is not None else None)
+    if glu_act:
+        half = gate_up.N // 2
+        h, _, _ = kk.glu(y1, y1[:, half:], act, half, gate_up.N, gate_up.N, P)
+    else:
+        h, _, _ = kk.glu(y1, None, act, gate_up.N, gate_up.N, 0, P)
+    y2 = kk.gemm_bf16_grouped(_dequant_scratch(down), E, h, tiles, bn, out_dtype=torch.float32,
+                              bias=down_bias.float().contiguous() if down_bias is not None else None)
+    w = weights.reshape(-1).float()
+    if down_scale is not None:
+        w = w * down_scale[ids.reshape(-1).long()]
+    w = torch.where(flat >= 0, w, torch.zeros_like(w))[order]         # skipped pairs contribute nothing
+    out = torch.zeros((T, D), dtype=torch.float32, device=ids.device)
+    out.index_add_(0, tok, y2 * w.unsqueeze(1))
     return out
 
 
@@ -578,26 +638,26 @@ def gdn(qkv: torch.Tensor, z: torch.Tensor, beta: torch.Tensor, alpha: torch.Ten
     if qkv.is_cuda and not chunked:
         return _k().gdn_recurrent(qkv, z, beta, alpha, dt_bias, a_log, norm_w, state, batch.cu_q, batch.seq_slots,
                                   Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=eps)
-    outs = []
     slots = batch.seq_slots.tolist()
+    if chunked:                                 # every sequence of a batch that took this route, short ones included
+        carry = None
+        if qkv.is_cuda and os.environ.get("TSB_GDN_CARRY_KERNEL", "1") != "0" and _k().gdn_chunk_carry_supported(Dk, Dv, 64):
+            carry = _k().gdn_chunk_carry
+        out = ref.gdn_chunked_batch(qkv, z, beta, alpha, dt_bias, a_log, norm_w, [state[sl] for sl in slots], list(batch.h_cu_q),
+                                    Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=eps, carry=carry)
+        return out.to(torch.bfloat16 if qkv.is_cuda else torch.float32)
+    outs = []
     for b in range(batch.B):
         q0, q1 = batch.h_cu_q[b], batch.h_cu_q[b + 1]
-        args = (qkv[q0:q1], z[q0:q1], beta[q0:q1], alpha[q0:q1], dt_bias, a_log, norm_w, state[slots[b]])
-        if chunked:                             # every sequence of a batch that took this route, short ones included
-            carry = None
-            if qkv.is_cuda and os.environ.get("TSB_GDN_CARRY_KERNEL", "1") != "0" and _k().gdn_chunk_carry_supported(Dk, Dv, 64) \
-                    and args[-1].is_contiguous():
-                carry = _k().gdn_chunk_carry
-            outs.append(ref.gdn_chunked(*args, Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=eps, carry=carry))
-        else:
-            outs.append(ref.gdn_recurrent(*args, Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=eps))
+        outs.append(ref.gdn_recurrent(qkv[q0:q1], z[q0:q1], beta[q0:q1], alpha[q0:q1], dt_bias, a_log, norm_w, state[slots[b]],
+                                      Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=eps))
     return torch.cat(outs, 0).to(torch.bfloat16 if qkv.is_cuda else torch.float32)     # the kernel's output types
 
 
 def mamba2(xbc: torch.Tensor, dt: torch.Tensor, dt_bias, A, D, state: torch.Tensor, batch: Batch, *, H: int, P: int,
            G: int, N: int) -> torch.Tensor:
-    """Mamba2 selective scan over the packed tokens -> y f32 [T, H*P] (before gating).  Prompts of
-    long prompts take the chunked form (thresholds in :func:`_use_chunked_scan`)."""
+    """Mamba2 selective scan over the packed tokens -> y f32 [T, H*P] (before gating).  Long prompts take
+    the chunked form (thresholds in :func:`_use_chunked_scan`)."""
     chunked = _use_chunked_scan(batch, xbc.is_cuda, "TSB_MAMBA_CHUNKED")
     if xbc.is_cuda and not chunked:
         return _k().mamba2_recurrent(xbc, dt, dt_bias, A, D, state, batch.cu_q, batch.seq_slots, H=H, P=P, G=G, N=N)

@@ -446,6 +446,26 @@ def gemm_bf16(W: torch.Tensor, X: torch.Tensor, *, out_dtype=torch.bfloat16, bia
     return out
 
 
+def gemm_bf16_grouped(W: torch.Tensor, E: int, X: torch.Tensor, tiles: torch.Tensor, bn: int, *, out_dtype=torch.bfloat16,
+                      bias=None) -> torch.Tensor:
+    """Grouped GEMM over a stack of ``E`` matrices: W [E * N, K] bf16, X [P, K] bf16 with each group's rows contiguous,
+    ``tiles`` int32 [n_tiles, 3] on the device = (matrix index or -1, first row, end row) with at most ``bn`` rows per
+    tile -> out [P, N], zero where no tile covers a row."""
+    assert W.dtype == torch.bfloat16 and X.dtype == torch.bfloat16 and W.stride(1) == 1 and X.stride(1) == 1
+    assert tiles.dtype == torch.int32 and tiles.is_contiguous() and tiles.shape[1] == 3
+    N, K = W.shape[0] // E, W.shape[1]
+    P = X.shape[0]
+    out = torch.zeros((P, N), dtype=out_dtype, device=X.device)
+    lib = _lib()
+    lib.tsb_gemm_bf16_grouped.restype = C.c_int
+    native.check(lib.tsb_gemm_bf16_grouped(_p(W), C.c_long(W.stride(0)), C.c_int(E), _p(X), C.c_long(X.stride(0)), _p(out),
+                                           C.c_long(out.stride(0)), C.c_int(out.dtype == torch.float32), _p(bias), C.c_int(P),
+                                           C.c_int(N), C.c_int(K), _p(tiles), C.c_int(tiles.shape[0]), C.c_int(bn),
+                                           _p(gemm_status(X.device)), _stream()), "gemm_bf16_grouped")
+    _count(1)
+    return out
+
+
 # --------------------------------------------------------------------------------------------
 class ConvArgs(C.Structure):
     _fields_ = [("x", _vp), ("xs", C.c_long), ("x_f32", C.c_int), ("w", _vp), ("bias", _vp), ("state", _vp),

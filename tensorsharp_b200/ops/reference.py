@@ -172,53 +172,87 @@ def gdn_chunked(qkv, z, beta, alpha, dt_bias, a_log, norm_w, state, *, Hk, Hv, D
     runs on whichever device the inputs live on.  ``carry`` replaces the loop over the chunks (a kernel on CUDA).
     Returns [n, Hv*Dv]."""
     n = qkv.shape[0]
+    return gdn_chunked_batch(qkv, z, beta, alpha, dt_bias, a_log, norm_w, [state], [0, n], Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=eps,
+                             chunk=chunk, carry=carry)
+
+
+def gdn_chunked_batch(qkv, z, beta, alpha, dt_bias, a_log, norm_w, states, cu, *, Hk, Hv, Dk, Dv, eps, chunk: int = 64, carry=None):
+    """:func:`gdn_chunked` for several sequences packed along the token axis (``cu``: host list of the B + 1 row offsets):
+    the sequences are padded to a common number of chunks and stacked beside the heads, so that every tensor op and the
+    chunk loop (or the ``carry`` kernel) runs once for the whole batch.  ``states``: one ``[Hv, Dv, Dk]`` tensor per
+    sequence, each updated in place.  Returns [T, Hv*Dv]."""
+    T = qkv.shape[0]
     dev = qkv.device
     C = chunk
-    nc = (n + C - 1) // C
-    pad = nc * C - n
+    B = len(cu) - 1
+    lens = [cu[i + 1] - cu[i] for i in range(B)]
+    nc = (max(lens) + C - 1) // C
+    L = nc * C
     hk = torch.arange(Hv, device=dev) % Hk
-    q = qkv[:, :Hk * Dk].float().view(n, Hk, Dk)[:, hk]                    # [n, Hv, Dk]
-    k = qkv[:, Hk * Dk:2 * Hk * Dk].float().view(n, Hk, Dk)[:, hk]
-    v = qkv[:, 2 * Hk * Dk:].float().view(n, Hv, Dv)
+    q = qkv[:, :Hk * Dk].float().view(T, Hk, Dk)
+    k = qkv[:, Hk * Dk:2 * Hk * Dk].float().view(T, Hk, Dk)
+    v = qkv[:, 2 * Hk * Dk:].float().view(T, Hv, Dv)
     q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + eps) * (Dv ** -0.5)
     k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + eps)
-    g = torch.nn.functional.softplus(alpha.float() + dt_bias.float()) * a_log.float()      # [n, Hv], log of the decay
-    b = torch.sigmoid(beta.float())                                                         # [n, Hv]
+    g = torch.nn.functional.softplus(alpha.float() + dt_bias.float()) * a_log.float()      # [T, Hv], log of the decay
+    b = torch.sigmoid(beta.float())                                                         # [T, Hv]
+    # row index of every (sequence, padded position); padding points at one appended row of zeros: a padded token has
+    # zero k, v, beta and log-decay, so it changes neither the state nor any real token's output
+    if B == 1 and lens[0] == L:
+        idx = None
+    else:
+        pos = torch.arange(L, device=dev).unsqueeze(0)
+        start = torch.tensor(cu[:-1], device=dev).unsqueeze(1)
+        ln = torch.tensor(lens, device=dev).unsqueeze(1)
+        idx = torch.where(pos < ln, start + pos, torch.full((), T, device=dev))            # [B, L]
 
-    def chunks(t):                      # [n, Hv, ...] -> [Hv, nc, C, ...]; padded tokens change nothing (zero k, v, beta, g)
-        if pad:
-            t = torch.cat([t, t.new_zeros((pad,) + tuple(t.shape[1:]))], 0)
-        return t.view(nc, C, *t.shape[1:]).movedim(2, 0)
-    Q, K, V = chunks(q), chunks(k), chunks(v)
-    G, B = chunks(g), chunks(b)                                              # [Hv, nc, C]
+    def chunks(t, per_kv_head=False):   # [T, H, ...] -> [B * Hv, nc, C, ...]
+        if idx is not None:
+            t = torch.cat([t, t.new_zeros((1,) + tuple(t.shape[1:]))], 0)[idx]              # [B, L, H, ...]
+        else:
+            t = t.unsqueeze(0)
+        if per_kv_head:
+            t = t[:, :, hk]
+        t = t.reshape(B, nc, C, *t.shape[2:]).movedim(3, 1)                                  # [B, Hv, nc, C, ...]
+        return t.reshape(B * Hv, nc, C, *t.shape[4:])
+    Q, K, V = chunks(q, True), chunks(k, True), chunks(v)
+    G, Bt = chunks(g), chunks(b)                                             # [B * Hv, nc, C]
     cum = G.cumsum(-1)
     tril = torch.ones(C, C, dtype=torch.bool, device=dev).tril()
     M = torch.where(tril, torch.exp((cum.unsqueeze(-1) - cum.unsqueeze(-2)).clamp(max=0.0)), torch.zeros((), device=dev))
-    KK = K @ K.transpose(-1, -2)
-    A = (B.unsqueeze(-1) * KK * M).tril(-1)                                  # strictly lower: token i sees tokens j < i
+    KT = K.transpose(-1, -2)
+    A = (Bt.unsqueeze(-1) * (K @ KT) * M).tril(-1)                           # strictly lower: token i sees tokens j < i
     lhs = A + torch.eye(C, device=dev)
     decay = torch.exp(cum).unsqueeze(-1)                                     # decay from the chunk's start to each token
-    U0 = torch.linalg.solve_triangular(lhs, B.unsqueeze(-1) * V, upper=False, unitriangular=True)          # [.., C, Dv]
-    W = torch.linalg.solve_triangular(lhs, B.unsqueeze(-1) * decay * K, upper=False, unitriangular=True)   # [.., C, Dk]
-    P = (Q @ K.transpose(-1, -2)) * M
+    rhs = torch.cat([Bt.unsqueeze(-1) * V, Bt.unsqueeze(-1) * decay * K], -1)
+    sol = torch.linalg.solve_triangular(lhs, rhs, upper=False, unitriangular=True)          # [.., C, Dv + Dk]
+    U0, W = sol[..., :Dv], sol[..., Dv:]
+    P = (Q @ KT) * M
     Qd = Q * decay
     Kd = K * torch.exp(cum[..., -1:] - cum).unsqueeze(-1)
-    gamma = torch.exp(cum[..., -1])                                          # [Hv, nc]
+    gamma = torch.exp(cum[..., -1])                                          # [B * Hv, nc]
+    S = states[0].float() if B == 1 else torch.cat([st.float() for st in states], 0)        # [B * Hv, Dv, Dk]
     if carry is not None:                # the chunk-after-chunk part as one kernel (csrc/gdn_chunk.cu)
-        core = carry(U0, W, Qd, Kd, P, gamma, state)                         # [Hv, nc, C, Dv]; state updated in place
+        S = S.contiguous()
+        core = carry(U0, W, Qd, Kd, P, gamma, S)                             # [B * Hv, nc, C, Dv]; S updated in place
     else:
-        S = state.float()
         outs = []
         for c in range(nc):
-            St = S.transpose(-1, -2)                                         # [Hv, Dk, Dv]
+            St = S.transpose(-1, -2)                                         # [.., Dk, Dv]
             U = U0[:, c] - W[:, c] @ St
-            outs.append(Qd[:, c] @ St + P[:, c] @ U)                         # [Hv, C, Dv]
-            S = gamma[:, c].view(Hv, 1, 1) * S + U.transpose(-1, -2) @ Kd[:, c]
-        state.copy_(S)
+            outs.append(Qd[:, c] @ St + P[:, c] @ U)                         # [.., C, Dv]
+            S = gamma[:, c].view(-1, 1, 1) * S + U.transpose(-1, -2) @ Kd[:, c]
         core = torch.stack(outs, 1)
-    core = core.reshape(Hv, nc * C, Dv)[:, :n].transpose(0, 1)                           # [n, Hv, Dv]
+    for i, st in enumerate(states):
+        if st.data_ptr() != S.data_ptr():
+            st.copy_(S[i * Hv:(i + 1) * Hv])
+    core = core.reshape(B, Hv, L, Dv).transpose(1, 2)                        # [B, L, Hv, Dv]
+    if idx is None:
+        core = core.reshape(T, Hv, Dv)
+    else:
+        core = torch.cat([core[i, :lens[i]] for i in range(B)], 0)           # back to packed rows
     core = core * torch.rsqrt(core.pow(2).mean(-1, keepdim=True) + eps) * norm_w.float()
-    return (core * torch.nn.functional.silu(z.float().view(n, Hv, Dv))).reshape(n, Hv * Dv)
+    return (core * torch.nn.functional.silu(z.float().view(T, Hv, Dv))).reshape(T, Hv * Dv)
 
 
 def mamba2_recurrent(xbc, dt, dt_bias, A, D, state, *, H, P, G, N):

@@ -400,3 +400,26 @@ def test_token_loop_raises_when_a_device_wait_ran_out(tmp_path):
         m.forward([4])
     assert e.value.code == 3 and "stand-in exchange" in str(e.value)
     m.close()
+
+
+def test_moe_tile_list_covers_every_routed_row_once():
+    """The device-side work list of the grouped expert GEMM (no host read-back): every row of a local expert is in exactly
+    one tile of its expert, tiles hold at most ``bn`` rows, skipped rows (-1) are in none, unused entries are marked -1."""
+    import torch
+    from tensorsharp_b200.ops.functional import moe_tile_list
+    g = torch.Generator().manual_seed(5)
+    for n_groups, P, bn in ((4, 100, 32), (8, 37, 64), (3, 1000, 128), (5, 64, 32)):
+        flat = torch.randint(-1, n_groups, (P,), generator=g)
+        flat[flat == 1] = 0                                   # one group without rows
+        order, tiles = moe_tile_list(flat, n_groups, bn)
+        assert tiles.dtype == torch.int32 and tiles.shape == ((P + bn - 1) // bn + n_groups, 3)
+        sorted_groups = flat[order]
+        seen = torch.zeros(P, dtype=torch.int32)
+        for e, a, b in tiles.tolist():
+            if e < 0:
+                continue
+            assert 0 < b - a and a >= 0 and b <= P
+            rows = min(bn, b - a)
+            assert (sorted_groups[a:a + rows] == e).all()
+            seen[a:a + rows] += 1
+        assert torch.equal(seen, (sorted_groups >= 0).to(torch.int32))

@@ -419,6 +419,34 @@ def test_moe_grouped_matches_per_slot_reference(t, act, e0, E_local, Kd, Fd):
     assert rel_err(got, want) < 1e-2
 
 
+@pytest.mark.parametrize("t,act", [(GGMLType.MXFP4, "swiglu_oai"), (GGMLType.Q4_K, "swiglu"), (GGMLType.BF16, "relu2")])
+@pytest.mark.parametrize("e0,E_local,T,k", [(0, 8, 700, 2), (4, 4, 900, 3), (0, 8, 40, 2)])
+def test_moe_prefill_grouped_gemm_matches_per_expert_route(monkeypatch, t, act, e0, E_local, T, k):
+    """Large batches: both expert projections as one grouped tensor-core GEMM each over a device-built tile list
+    (F.moe_experts above MOE_TILE_MAX_PAIRS) against the route that sorts on the host and runs expert after expert;
+    experts with no rows, experts held elsewhere, uneven group sizes."""
+    from tensorsharp_b200.ops import functional as F
+    torch.manual_seed(24)
+    E, Kd, Fd = 8, 256, 512
+    glu = act != "relu2"
+    gu_rows = 2 * Fd if glu else Fd
+    gate_up = QuantWeight.from_float(torch.randn(E_local, gu_rows, Kd, device=DEV) * 0.08, t)
+    down = QuantWeight.from_float(torch.randn(E_local, Kd, Fd, device=DEV) * 0.08, t)
+    gb = torch.randn(E_local, gu_rows, device=DEV) * 0.1
+    db = torch.randn(E_local, Kd, device=DEV) * 0.1
+    x = torch.randn(T, Kd, device=DEV).bfloat16()
+    ids = torch.stack([torch.randperm(E - 1, device=DEV)[:k] for _ in range(T)]).to(torch.int32)     # expert 7 gets no rows
+    w = torch.rand(T, k, device=DEV)
+    monkeypatch.setattr(F, "MOE_TILE_MAX_PAIRS", 0)
+    monkeypatch.setattr(F, "GEMV_MAX_M", 0)
+    outs = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("TSB_MOE_GROUPED_GEMM", mode)
+        outs[mode] = F.moe_experts(F.Act(x), ids, w, gate_up, down, act=act, gate_up_bias=gb, down_bias=db, expert_offset=e0)
+    assert rel_err(outs["1"], outs["0"]) < 1e-2, rel_err(outs["1"], outs["0"])
+    assert int(K().gemm_status(x.device).item()) == 0
+
+
 def test_moe_grouped_is_graph_capturable_and_follows_new_routing():
     torch.manual_seed(23)
     E, T, k, Kd, Fd = 16, 64, 4, 256, 256

@@ -127,6 +127,31 @@ def test_gdn_chunked_form_matches_the_token_scan(tmp_path, monkeypatch):
     assert torch.allclose(out["chunked"][1], out["scan"][1], atol=2e-3)
 
 
+def test_gdn_chunked_batch_equals_the_sequences_one_by_one():
+    """Several packed sequences of ragged lengths through the batched chunked form (padded to a common chunk count,
+    stacked beside the heads) give each sequence's own result and final state."""
+    from tensorsharp_b200.ops import reference as ref
+    torch.manual_seed(3)
+    Hk, Hv, Dk, Dv = 2, 4, 16, 8
+    lens = [130, 1, 64, 77]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    T = cu[-1]
+    qkv, z = torch.randn(T, 2 * Hk * Dk + Hv * Dv), torch.randn(T, Hv * Dv)
+    beta, alpha, dt_bias = torch.randn(T, Hv), torch.randn(T, Hv), torch.randn(Hv)
+    a_log, norm_w = -torch.rand(Hv) * 2, torch.rand(Dv) + 0.5
+    kw = dict(Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=1e-6)
+    pool = torch.randn(6, Hv, Dv, Dk) * 0.3
+    slots = [4, 0, 5, 2]
+    want_pool = pool.clone()
+    want = torch.cat([ref.gdn_chunked(qkv[cu[i]:cu[i + 1]], z[cu[i]:cu[i + 1]], beta[cu[i]:cu[i + 1]], alpha[cu[i]:cu[i + 1]],
+                                      dt_bias, a_log, norm_w, want_pool[slots[i]], **kw) for i in range(len(lens))])
+    got = ref.gdn_chunked_batch(qkv, z, beta, alpha, dt_bias, a_log, norm_w, [pool[sl] for sl in slots], cu, **kw)
+    assert torch.allclose(got, want, atol=1e-5)
+    assert torch.allclose(pool, want_pool, atol=1e-6)
+
+
 def test_mamba2_chunked_form_matches_the_token_scan(tmp_path, monkeypatch):
     from tensorsharp_b200.ops import reference as ref
     torch.manual_seed(1)
