@@ -342,6 +342,11 @@ class ModelBase:
         every sequence (or ``None`` when ``want_logits`` is false: prefill chunks)."""
         raise NotImplementedError
 
+    def recurrent_state_tensors(self) -> list:
+        """The per-slot recurrent state tensors (first dimension = sequence slot) of models with linear-attention / SSM
+        layers; empty for attention-only models.  A CUDA-graph capture snapshots them around its warm-up step."""
+        return []
+
     def reset_recurrent_state(self, slot: int) -> None:
         """Zero per-sequence recurrent state (models with linear-attention / SSM layers)."""
 

@@ -109,6 +109,9 @@ class NemotronHModel(ModelBase):
                 L["up"], L["down"] = self.qw(p + "ffn_up.weight"), self.qw(p + "ffn_down.weight")
             self.layers.append(L)
 
+    def recurrent_state_tensors(self) -> list:
+        return [L[k] for L in self.layers if "conv_state" in L for k in ("conv_state", "ssm_state")]
+
     def reset_recurrent_state(self, slot: int) -> None:
         for L in self.layers:
             if "conv_state" in L:

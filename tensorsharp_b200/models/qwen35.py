@@ -113,6 +113,9 @@ class Qwen35Model(ModelBase):
             self.layers.append(L)
         self.rope = RopeSpec(rot_dim=self.rope_dims, theta_base=c.rope_base, mode=0, freq_scale=1.0 / c.rope_scale)
 
+    def recurrent_state_tensors(self) -> list:
+        return [L[k] for L in self.layers if "conv_state" in L for k in ("conv_state", "delta_state")]
+
     def reset_recurrent_state(self, slot: int) -> None:
         for L in self.layers:
             if "conv_state" in L:

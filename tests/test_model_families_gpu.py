@@ -39,6 +39,29 @@ def test_cuda_matches_cpu_oracle(family_paths, name):
         t = int(lc.argmax())
 
 
+@pytest.mark.parametrize("name", list(FAMILIES))
+def test_captured_decode_graph_follows_eager_steps(family_paths, name):
+    """Greedy decode through DecodeGraph (one replay per token) gives the eager tokens in every family; for the families
+    with recurrent layers this also checks that the capture's warm-up step leaves their state where it was."""
+    from tensorsharp_b200.runtime.engine import DecodeGraph
+    g = torch.Generator().manual_seed(12)
+    prompt = torch.randint(0, 4096, (40,), generator=g).tolist()
+    eager = ModelBase.create(family_paths[name], "cuda", max_context=256)
+    t = int(eager.forward(prompt).argmax())
+    want = [t]
+    for _ in range(6):
+        t = int(eager.forward([t]).argmax())
+        want.append(t)
+    m = ModelBase.create(family_paths[name], "cuda", max_context=256)
+    seq = m.new_sequence()
+    first = int(F.argmax(m.forward_batch(m.kv.build_batch([seq], [prompt])))[0])
+    dg = DecodeGraph(m, [seq], 8)
+    dg.set_tokens([first])
+    dg.capture()
+    got = [first] + [int(dg.step()[0]) for _ in range(6)]
+    assert got == want
+
+
 def _batch(lens, dev):
     cu = [0]
     for n in lens:
