@@ -89,6 +89,13 @@ def recurrent(args):
         def fused():
             s2.zero_()
             return ref.gdn_chunked(qkv, z, beta, alpha, dt_bias, a_log, norm_w, s2, chunk=64, carry=kernels.gdn_chunk_carry, **kw)
+    kern3 = None
+    if args.op == "gdn":
+        s3 = torch.zeros(1, Hv, Dv, Dk, device=dev)
+
+        def kern3():
+            s3.zero_()
+            return kernels.gdn_chunked(qkv, z, beta, alpha, dt_bias, a_log, norm_w, s3, cu_q, [0, T], [0], **kw)
     a, b = scan().float(), chunked().float()
     rel = float((a - b).norm() / b.norm())
     srel = float((s0[0] - s1).norm() / s1.norm())
@@ -97,6 +104,8 @@ def recurrent(args):
                       "chunked_us": time_us(chunked, args.iters, args.warmup),
                       "chunked_carry_kernel_us": time_us(fused, args.iters, args.warmup) if fused else None,
                       "rel_diff_out_carry_kernel": float((fused().float() - b).norm() / b.norm()) if fused else None,
+                      "chunk_kernels_us": time_us(kern3, args.iters, args.warmup) if kern3 else None,
+                      "rel_diff_out_chunk_kernels": float((kern3().float() - b).norm() / b.norm()) if kern3 else None,
                       "rel_diff_out": rel, "rel_diff_state": srel}))
 
 

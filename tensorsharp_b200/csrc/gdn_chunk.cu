@@ -243,3 +243,245 @@ extern "C" int tsb_gdn_chunk_carry(const GdnCarryArgs* args, void* stream) {
         return TSB_ERR_UNSUPPORTED;
     }
 }
+
+// ==========================================================================================
+// The chunk-parallel part: everything the carry kernel consumes, from the layer's packed projections.
+//
+// One CTA per (sequence, value head, chunk of 64 tokens).  With k, q the L2-normalised key / query rows (q also times
+// Dv^-1/2), g the log-decay and b the write strength of each token, c_i the running sum of g inside the chunk:
+//     A[i][j]  = b_i (k_i . k_j) exp(c_i - c_j)        j <  i      (strictly lower triangular)
+//     P[i][j]  =     (q_i . k_j) exp(c_i - c_j)        j <= i
+//     (I + A) [U0 | W] = [b v | b exp(c) k]            forward substitution, one right-hand-side column per thread
+//     Qd = q exp(c),   Kd = k exp(c_last - c),   gamma = exp(c_last)
+// The two Gram products run on the tensor cores with split tf32 operands (hi + lo parts, three products), which keeps
+// f32-level accuracy in the matrix that the substitution then inverts.  Tokens past a sequence's end are zero rows
+// (b = 0, g = 0): they leave state and outputs untouched, so ragged batches share one launch.
+// ==========================================================================================
+struct GdnPrepArgs {
+    const float* qkv; long qkv_s;          // [T, 2 Hk Dk + Hv Dv] rows: q heads | k heads | v heads
+    const void* beta; const void* alpha; long ba_s; int ba_f32;      // [T, Hv]
+    const float* dt_bias; const float* a_log;                        // [Hv]
+    const int* cu_q;                       // [B + 1] first row of each sequence
+    float* U0; float* W; float* Qd; float* Kd; float* P; float* gamma;
+    int Hk, Hv, Dk, Dv, B, nc;
+    float eps;
+};
+
+namespace {
+__device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
+    hi = tf32(x);
+    lo = tf32(x - __uint_as_float(hi));
+}
+__device__ __forceinline__ float ld_ba(const void* p, long i, int f32) {
+    return f32 ? reinterpret_cast<const float*>(p)[i] : bf2f(reinterpret_cast<const bf16*>(p)[i]);
+}
+}  // namespace
+
+template <int DK>
+__global__ void __launch_bounds__(256) gdn_chunk_prep_kernel(GdnPrepArgs a) {
+    constexpr int LQ = DK + 4;             // row stride of the q / k tiles (fragment loads hit 32 banks)
+    constexpr int LA = GC + 1;
+    extern __shared__ __align__(16) float sm[];
+    const int Dv = a.Dv, NX = Dv + DK, LX = NX + 4;
+    float* sK = sm;                        // [64][LQ] normalised keys
+    float* sQ = sK + GC * LQ;              // [64][LQ] normalised, scaled queries
+    float* sX = sQ + GC * LQ;              // [64][LX] right-hand sides [b v | b exp(c) k]
+    float* sA = sX + GC * LX;              // [64][LA] strictly lower triangular A
+    float* sc = sA + GC * LA;              // [64] running log-decay
+    float* sb = sc + GC;                   // [64] write strength
+    const int c = blockIdx.x, bh = blockIdx.y, b = bh / a.Hv, h = bh % a.Hv, hk = h % a.Hk;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = a.cu_q[b], len = a.cu_q[b + 1] - row0;
+    const int valid = max(0, min(GC, len - c * GC));           // tokens of this chunk that exist
+    const long tok0 = (long)row0 + (long)c * GC;
+    const float qscale = rsqrtf((float)Dv);
+    // ---- rows: normalise q and k, stage v, per-token scalars
+    for (int r = warp; r < GC; r += 8) {
+        const bool ok = r < valid;
+        const float* row = a.qkv + (tok0 + r) * a.qkv_s;
+        float qs = 0.f, ks = 0.f;
+        float qv[DK / 32], kv[DK / 32];
+#pragma unroll
+        for (int i = 0; i < DK / 32; ++i) {
+            qv[i] = ok ? row[hk * DK + lane + 32 * i] : 0.f;
+            kv[i] = ok ? row[(long)a.Hk * DK + hk * DK + lane + 32 * i] : 0.f;
+            qs += qv[i] * qv[i];
+            ks += kv[i] * kv[i];
+        }
+        qs = warp_sum(qs);
+        ks = warp_sum(ks);
+        const float qn = ok ? qscale * rsqrtf(qs + a.eps) : 0.f, kn = ok ? rsqrtf(ks + a.eps) : 0.f;
+#pragma unroll
+        for (int i = 0; i < DK / 32; ++i) {
+            sQ[r * LQ + lane + 32 * i] = qv[i] * qn;
+            sK[r * LQ + lane + 32 * i] = kv[i] * kn;
+        }
+        for (int d = lane; d < Dv; d += 32) sX[r * LX + d] = ok ? row[2L * a.Hk * DK + (long)h * Dv + d] : 0.f;
+        if (lane == 0) {
+            float g = 0.f, be = 0.f;
+            if (ok) {
+                const float al = ld_ba(a.alpha, (tok0 + r) * a.ba_s + h, a.ba_f32) + a.dt_bias[h];
+                g = (al > 20.f ? al : log1pf(__expf(al))) * a.a_log[h];
+                be = 1.f / (1.f + __expf(-ld_ba(a.beta, (tok0 + r) * a.ba_s + h, a.ba_f32)));
+            }
+            sc[r] = g;
+            sb[r] = be;
+        }
+    }
+    __syncthreads();
+    if (warp == 0) {                       // inclusive running sum over the 64 tokens
+        float x0 = sc[lane], x1 = sc[lane + 32];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float y0 = __shfl_up_sync(0xffffffffu, x0, o), y1 = __shfl_up_sync(0xffffffffu, x1, o);
+            if (lane >= o) { x0 += y0; x1 += y1; }
+        }
+        x1 += __shfl_sync(0xffffffffu, x0, 31);
+        sc[lane] = x0;
+        sc[lane + 32] = x1;
+    }
+    __syncthreads();
+    const float c_last = sc[GC - 1];
+    const long ch = (long)bh * a.nc + c;
+    // ---- Gram products k k^T and q k^T: warp -> rows mt * 16 .. + 15, columns nq * 32 .. + 31 of both
+    {
+        const int g = lane >> 2, t = lane & 3, mt = warp & 3, nq = warp >> 2;
+        float kk[4][4] = {}, qk[4][4] = {};
+#pragma unroll 2
+        for (int k0 = 0; k0 < DK; k0 += 8) {
+            uint32_t ah[4], al[4], qh[4], ql[4];
+            const float* ap = sK + (mt * 16 + g) * LQ + k0 + t;
+            const float* qp = sQ + (mt * 16 + g) * LQ + k0 + t;
+            split_tf32(ap[0], ah[0], al[0]); split_tf32(ap[8 * LQ], ah[1], al[1]);
+            split_tf32(ap[4], ah[2], al[2]); split_tf32(ap[8 * LQ + 4], ah[3], al[3]);
+            split_tf32(qp[0], qh[0], ql[0]); split_tf32(qp[8 * LQ], qh[1], ql[1]);
+            split_tf32(qp[4], qh[2], ql[2]); split_tf32(qp[8 * LQ + 4], qh[3], ql[3]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float* bp = sK + ((nq * 4 + j) * 8 + g) * LQ + k0 + t;
+                uint32_t b0h, b0l, b1h, b1l;
+                split_tf32(bp[0], b0h, b0l);
+                split_tf32(bp[4], b1h, b1l);
+                mma_tf32(kk[j], al, b0h, b1h); mma_tf32(kk[j], ah, b0l, b1l); mma_tf32(kk[j], ah, b0h, b1h);
+                mma_tf32(qk[j], ql, b0h, b1h); mma_tf32(qk[j], qh, b0l, b1l); mma_tf32(qk[j], qh, b0h, b1h);
+            }
+        }
+        float* Pg = a.P + ch * GC * GC;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = mt * 16 + g + (e >> 1) * 8, jj = (nq * 4 + j) * 8 + 2 * t + (e & 1);
+                const float m = jj <= i ? __expf(fminf(sc[i] - sc[jj], 0.f)) : 0.f;
+                sA[i * LA + jj] = jj < i ? sb[i] * kk[j][e] * m : 0.f;
+                Pg[i * GC + jj] = qk[j][e] * m;
+            }
+        }
+    }
+    // ---- right-hand sides (the v part is staged already), Qd, Kd, gamma
+    for (int r = warp; r < GC; r += 8) {
+        const float be = sb[r], dec = __expf(sc[r]), tail = __expf(c_last - sc[r]);
+        for (int d = lane; d < Dv; d += 32) sX[r * LX + d] *= be;
+#pragma unroll
+        for (int i = 0; i < DK / 32; ++i) {
+            const int d = lane + 32 * i;
+            const float kv = sK[r * LQ + d];
+            sX[r * LX + Dv + d] = be * dec * kv;
+            a.Kd[(ch * GC + r) * DK + d] = kv * tail;
+            a.Qd[(ch * GC + r) * DK + d] = sQ[r * LQ + d] * dec;
+        }
+    }
+    if (threadIdx.x == 0) a.gamma[ch] = __expf(c_last);
+    __syncthreads();
+    // ---- (I + A) X = RHS by forward substitution; a thread owns one column and keeps its solution in registers
+    for (int col = threadIdx.x; col < NX; col += 256) {
+        float x[GC];
+#pragma unroll
+        for (int i = 0; i < GC; ++i) {
+            float acc = sX[i * LX + col];
+#pragma unroll
+            for (int j = 0; j < i; ++j) acc -= sA[i * LA + j] * x[j];
+            x[i] = acc;
+            if (col < Dv) a.U0[(ch * GC + i) * Dv + col] = acc;
+            else a.W[(ch * GC + i) * DK + col - Dv] = acc;
+        }
+    }
+}
+
+// Gated output: core [B * Hv, nc, 64, Dv] -> out[t, h * Dv + d] = rmsnorm(core) * norm_w[d] * silu(z[t, h * Dv + d]) (bf16).
+struct GdnFinishArgs {
+    const float* core; const void* z; long z_s; int z_f32;
+    const float* norm_w; const int* cu_q;
+    bf16* out; long out_s;
+    int Hv, Dv, B, nc;
+    float eps;
+};
+
+__global__ void __launch_bounds__(256) gdn_chunk_finish_kernel(GdnFinishArgs a) {
+    const int c = blockIdx.x, bh = blockIdx.y, b = bh / a.Hv, h = bh % a.Hv;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = a.cu_q[b], len = a.cu_q[b + 1] - row0;
+    const int Dv = a.Dv;
+    for (int r = warp; r < GC; r += 8) {
+        const int pos = c * GC + r;
+        if (pos >= len) break;
+        const float* src = a.core + (((long)bh * a.nc + c) * GC + r) * Dv;
+        float v[8], ss = 0.f;                                  // Dv <= 256
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int d = lane + 32 * i;
+            v[i] = d < Dv ? src[d] : 0.f;
+            ss += v[i] * v[i];
+        }
+        ss = warp_sum(ss);
+        const float rs = rsqrtf(ss / (float)Dv + a.eps);
+        const long t = (long)row0 + pos;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int d = lane + 32 * i;
+            if (d < Dv) {
+                const long zi = t * a.z_s + (long)h * Dv + d;
+                const float zz = a.z_f32 ? reinterpret_cast<const float*>(a.z)[zi] : bf2f(reinterpret_cast<const bf16*>(a.z)[zi]);
+                a.out[t * a.out_s + (long)h * Dv + d] = f2bf(v[i] * rs * a.norm_w[d] * (zz / (1.f + __expf(-zz))));
+            }
+        }
+    }
+}
+
+template <int DK>
+static int launch_prep(const GdnPrepArgs& a, cudaStream_t s) {
+    const size_t smem = sizeof(float) * ((size_t)2 * GC * (DK + 4) + (size_t)GC * (a.Dv + DK + 4) + (size_t)GC * (GC + 1) + 2 * GC);
+    static size_t configured = 0;
+    if (smem > configured) {
+        TSB_CHECK_CUDA(cudaFuncSetAttribute(gdn_chunk_prep_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
+    }
+    gdn_chunk_prep_kernel<DK><<<dim3(a.nc, a.B * a.Hv), 256, smem, s>>>(a);
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}
+
+extern "C" int tsb_gdn_chunk_prep(const GdnPrepArgs* args, void* stream) {
+    TSB_CHECK_ARG(args != nullptr, "gdn_chunk_prep: null arguments");
+    const GdnPrepArgs& a = *args;
+    TSB_CHECK_ARG(a.B > 0 && a.nc > 0 && a.Hv > 0 && a.Hk > 0, "gdn_chunk_prep: B=%d chunks=%d heads=%d/%d", a.B, a.nc, a.Hk, a.Hv);
+    TSB_CHECK_ARG(a.Dv % 32 == 0 && a.Dv > 0 && a.Dv <= 128, "gdn_chunk_prep: value head size %d (multiples of 32 up to 128)", a.Dv);
+    TSB_CHECK_ARG((long)a.B * a.Hv <= 65535, "gdn_chunk_prep: %d x %d sequence-heads exceed the grid", a.B, a.Hv);
+    switch (a.Dk) {
+    case 64: return launch_prep<64>(a, (cudaStream_t)stream);
+    case 128: return launch_prep<128>(a, (cudaStream_t)stream);
+    default:
+        tsb_set_error("gdn_chunk_prep: key head size %d unsupported (64, 128)", a.Dk);
+        return TSB_ERR_UNSUPPORTED;
+    }
+}
+
+extern "C" int tsb_gdn_chunk_finish(const GdnFinishArgs* args, void* stream) {
+    TSB_CHECK_ARG(args != nullptr, "gdn_chunk_finish: null arguments");
+    const GdnFinishArgs& a = *args;
+    TSB_CHECK_ARG(a.Dv > 0 && a.Dv <= 256 && a.B > 0 && a.nc > 0, "gdn_chunk_finish: Dv=%d B=%d chunks=%d", a.Dv, a.B, a.nc);
+    TSB_CHECK_ARG((long)a.B * a.Hv <= 65535, "gdn_chunk_finish: %d x %d sequence-heads exceed the grid", a.B, a.Hv);
+    gdn_chunk_finish_kernel<<<dim3(a.nc, a.B * a.Hv), 256, 0, (cudaStream_t)stream>>>(a);
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}

@@ -459,10 +459,10 @@ extern "C" int tsb_moe_gemv_tiles(const void* p0, const void* p1, const void* p2
 }
 
 // ---------------------------------------------------------------------------------------------
-// Combine: out[t, :] = sum_j y[pos[t * k + j], :]  (pairs held by other ranks have pos < 0).
+// Combine: out[t, :] = sum_j w[t * k + j] * y[pos[t * k + j], :]  (pairs held by other ranks have pos < 0; w null = 1).
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos, int k, int D,
-                                                          float* __restrict__ out) {
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos,
+                                                          const float* __restrict__ w, int k, int D, float* __restrict__ out) {
     const int t = blockIdx.x;
     pdl_wait();
     pdl_trigger();
@@ -472,7 +472,8 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
             const int p = pos[t * k + j];
             if (p < 0) continue;
             const float4 v = *reinterpret_cast<const float4*>(y + (long)p * D + c);
-            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+            const float wj = w ? w[t * k + j] : 1.f;
+            s.x += wj * v.x; s.y += wj * v.y; s.z += wj * v.z; s.w += wj * v.w;
         }
         *reinterpret_cast<float4*>(out + (long)t * D + c) = s;
     }
@@ -481,7 +482,16 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
 extern "C" int tsb_moe_combine(const float* y, const int* pos, int T, int k, int D, float* out, void* stream) {
     TSB_CHECK_ARG(D % 4 == 0, "moe_combine: D=%d is not a multiple of 4", D);
     if (T == 0) return TSB_OK;
-    TSB_CHECK_CUDA(tsb_launch(moe_combine_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, y, pos, k, D, out));
+    TSB_CHECK_CUDA(tsb_launch(moe_combine_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, y, pos, (const float*)nullptr, k, D, out));
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}
+
+// The same with a weight per (token, slot), for projections that did not scale their rows themselves.
+extern "C" int tsb_moe_combine_weighted(const float* y, const int* pos, const float* w, int T, int k, int D, float* out, void* stream) {
+    TSB_CHECK_ARG(D % 4 == 0 && y && pos && w && out, "moe_combine_weighted: D=%d or a null argument", D);
+    if (T == 0) return TSB_OK;
+    TSB_CHECK_CUDA(tsb_launch(moe_combine_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, y, pos, w, k, D, out));
     TSB_CHECK_LAUNCH();
     return TSB_OK;
 }

@@ -580,7 +580,13 @@ def _moe_grouped_gemm(a: Act, ids, local, weights, gate_up: QuantWeight, down: Q
     w = weights.reshape(-1).float()
     if down_scale is not None:
         w = w * down_scale[ids.reshape(-1).long()]
-    w = torch.where(flat >= 0, w, torch.zeros_like(w))[order]         # skipped pairs contribute nothing
+    if D % 4 == 0:
+        # every token gathers its own k rows (fixed summation order, no atomics): pos = where each pair went
+        pos = torch.empty(P, dtype=torch.int32, device=ids.device)
+        pos[order] = torch.arange(P, dtype=torch.int32, device=ids.device)
+        pos = torch.where(flat >= 0, pos, torch.full_like(pos, -1))          # skipped pairs contribute nothing
+        return kk.moe_combine_weighted(y2, pos, w, T, k)
+    w = torch.where(flat >= 0, w, torch.zeros_like(w))[order]
     out = torch.zeros((T, D), dtype=torch.float32, device=ids.device)
     out.index_add_(0, tok, y2 * w.unsqueeze(1))
     return out
@@ -639,6 +645,10 @@ def gdn(qkv: torch.Tensor, z: torch.Tensor, beta: torch.Tensor, alpha: torch.Ten
         return _k().gdn_recurrent(qkv, z, beta, alpha, dt_bias, a_log, norm_w, state, batch.cu_q, batch.seq_slots,
                                   Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=eps)
     slots = batch.seq_slots.tolist()
+    if chunked and qkv.is_cuda and os.environ.get("TSB_GDN_CHUNK_KERNELS", "1") != "0" and _k().gdn_chunked_supported(Dk, Dv) \
+            and qkv.dtype == torch.float32 and beta.dtype == alpha.dtype and beta.stride(0) == alpha.stride(0):
+        return _k().gdn_chunked(qkv, z, beta, alpha, dt_bias, a_log, norm_w, state, batch.cu_q, list(batch.h_cu_q), slots,
+                                Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=eps)
     if chunked:                                 # every sequence of a batch that took this route, short ones included
         carry = None
         if qkv.is_cuda and os.environ.get("TSB_GDN_CARRY_KERNEL", "1") != "0" and _k().gdn_chunk_carry_supported(Dk, Dv, 64):

@@ -205,6 +205,20 @@ def moe_grouped(*, xq=None, xds=None, xb=None, ids: torch.Tensor, weights: torch
     return out
 
 
+def moe_combine_weighted(y: torch.Tensor, pos: torch.Tensor, w: torch.Tensor, T: int, k: int) -> torch.Tensor:
+    """out[t] = sum_j w[t, j] * y[pos[t * k + j]] (f32 rows; pos < 0 = no row): each token gathers its own rows, so the
+    sum has a fixed order and needs no atomics."""
+    D = y.shape[1]
+    assert y.dtype == torch.float32 and y.is_contiguous() and pos.dtype == torch.int32 and w.dtype == torch.float32
+    out = torch.empty((T, D), dtype=torch.float32, device=y.device)
+    lib = _lib()
+    lib.tsb_moe_combine_weighted.restype = C.c_int
+    native.check(lib.tsb_moe_combine_weighted(_p(y), _p(pos.contiguous()), _p(w.contiguous()), C.c_int(T), C.c_int(k), C.c_int(D),
+                                              _p(out), _stream()), "moe_combine_weighted")
+    _count(1)
+    return out
+
+
 def sample(logits: torch.Tensor, ngen: torch.Tensor, *, temperature: float, top_k: int, top_p: float, min_p: float,
            repetition_penalty: float = 1.0, presence_penalty: float = 0.0, frequency_penalty: float = 0.0, seed: int = 0,
            counts: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -486,6 +500,20 @@ class GdnCarryArgs(C.Structure):
                 ("Hv", C.c_int), ("nc", C.c_int), ("Dk", C.c_int), ("Dv", C.c_int)]
 
 
+class GdnPrepArgs(C.Structure):
+    _fields_ = [("qkv", _vp), ("qkv_s", C.c_long), ("beta", _vp), ("alpha", _vp), ("ba_s", C.c_long), ("ba_f32", C.c_int),
+                ("dt_bias", _vp), ("a_log", _vp), ("cu_q", _vp),
+                ("U0", _vp), ("W", _vp), ("Qd", _vp), ("Kd", _vp), ("P", _vp), ("gamma", _vp),
+                ("Hk", C.c_int), ("Hv", C.c_int), ("Dk", C.c_int), ("Dv", C.c_int), ("B", C.c_int), ("nc", C.c_int),
+                ("eps", C.c_float)]
+
+
+class GdnFinishArgs(C.Structure):
+    _fields_ = [("core", _vp), ("z", _vp), ("z_s", C.c_long), ("z_f32", C.c_int), ("norm_w", _vp), ("cu_q", _vp),
+                ("out", _vp), ("out_s", C.c_long), ("Hv", C.c_int), ("Dv", C.c_int), ("B", C.c_int), ("nc", C.c_int),
+                ("eps", C.c_float)]
+
+
 class MambaArgs(C.Structure):
     _fields_ = [("xbc", _vp), ("xbc_s", C.c_long), ("dt", _vp), ("dt_s", C.c_long), ("dt_f32", C.c_int),
                 ("dt_bias", _vp), ("A", _vp), ("D", _vp), ("state", _vp), ("cu_q", _vp), ("seq_slots", _vp),
@@ -525,6 +553,53 @@ def gdn_recurrent(qkv, z, beta, alpha, dt_bias, a_log, norm_w, state, cu_q, seq_
 
 def gdn_chunk_carry_supported(Dk: int, Dv: int, chunk: int) -> bool:
     return chunk == 64 and Dk in (64, 128) and Dv % 32 == 0
+
+
+def gdn_chunked_supported(Dk: int, Dv: int) -> bool:
+    return Dk in (64, 128) and Dv % 32 == 0 and Dv <= 128
+
+
+def gdn_chunked(qkv, z, beta, alpha, dt_bias, a_log, norm_w, state, cu_q, h_cu_q, slots, *, Hk, Hv, Dk, Dv, eps) -> torch.Tensor:
+    """Chunked GatedDeltaNet prefill of a packed batch in three kernels (csrc/gdn_chunk.cu): the chunk-parallel algebra
+    (normalisation, decay, Gram products, the triangular solve) per (sequence, head, chunk); the state carried chunk
+    after chunk per (sequence, head, value slice); the gated output norm.  ``state`` [slots, Hv, Dv, Dk] f32 is updated
+    for the sequences' slots (host list ``slots``); ``cu_q`` int32 [B + 1] on the device, ``h_cu_q`` its host copy.
+    Returns bf16 [T, Hv * Dv]."""
+    T = qkv.shape[0]
+    B = len(h_cu_q) - 1
+    nc = (max(h_cu_q[i + 1] - h_cu_q[i] for i in range(B)) + 63) // 64
+    dev = qkv.device
+    assert qkv.dtype == torch.float32 and qkv.stride(1) == 1 and beta.dtype == alpha.dtype and beta.stride(0) == alpha.stride(0)
+    BH = B * Hv
+    f32 = dict(dtype=torch.float32, device=dev)
+    U0, W = torch.empty((BH, nc, 64, Dv), **f32), torch.empty((BH, nc, 64, Dk), **f32)
+    Qd, Kd = torch.empty((BH, nc, 64, Dk), **f32), torch.empty((BH, nc, 64, Dk), **f32)
+    P, gamma = torch.empty((BH, nc, 64, 64), **f32), torch.empty((BH, nc), **f32)
+    a = GdnPrepArgs()
+    a.qkv, a.qkv_s = _p(qkv), qkv.stride(0)
+    a.beta, a.alpha, a.ba_s, a.ba_f32 = _p(beta), _p(alpha), beta.stride(0), int(beta.dtype == torch.float32)
+    a.dt_bias, a.a_log, a.cu_q = _p(dt_bias), _p(a_log), _p(cu_q)
+    a.U0, a.W, a.Qd, a.Kd, a.P, a.gamma = _p(U0), _p(W), _p(Qd), _p(Kd), _p(P), _p(gamma)
+    a.Hk, a.Hv, a.Dk, a.Dv, a.B, a.nc, a.eps = Hk, Hv, Dk, Dv, B, nc, eps
+    lib = _lib()
+    native.check(lib.tsb_gdn_chunk_prep(C.byref(a), _stream()), "gdn_chunk_prep")
+    _count(1)
+    if B == 1:
+        S = state[slots[0]]
+    else:
+        idx = torch.tensor(slots, dtype=torch.long, device=dev)
+        S = state[idx].reshape(BH, Dv, Dk)
+    core = gdn_chunk_carry(U0, W, Qd, Kd, P, gamma, S)
+    if B > 1:
+        state[idx] = S.view(B, Hv, Dv, Dk)
+    out = torch.empty((T, Hv * Dv), dtype=torch.bfloat16, device=dev)
+    f = GdnFinishArgs()
+    f.core, f.z, f.z_s, f.z_f32 = _p(core), _p(z), z.stride(0), int(z.dtype == torch.float32)
+    f.norm_w, f.cu_q, f.out, f.out_s = _p(norm_w), _p(cu_q), _p(out), Hv * Dv
+    f.Hv, f.Dv, f.B, f.nc, f.eps = Hv, Dv, B, nc, eps
+    native.check(lib.tsb_gdn_chunk_finish(C.byref(f), _stream()), "gdn_chunk_finish")
+    _count(1)
+    return out
 
 
 def gdn_chunk_carry(U0, W, Qd, Kd, P, gamma, state) -> torch.Tensor:

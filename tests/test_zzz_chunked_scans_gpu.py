@@ -65,9 +65,11 @@ def test_chunk_carry_kernel_matches_the_scan_across_chunk_and_call_boundaries(mo
     dtb, a_log, nw = torch.randn(Hv, device=dev) * 0.5, -torch.rand(Hv, device=dev), torch.rand(Dv, device=dev) + 0.5
     s0 = torch.randn(2, Hv, Dv, Dk, device=dev) * 0.1
     results = {}
-    for mode, carry in (("0", "1"), ("1", "0"), ("1", "1")):        # scan kernel; chunked tensor ops; chunked + carry kernel
+    # scan kernel; chunked tensor ops; tensor ops + carry kernel; the three chunk kernels (prep, carry, finish)
+    for mode, carry, kernels in (("0", "1", "0"), ("1", "0", "0"), ("1", "1", "0"), ("1", "1", "1")):
         monkeypatch.setenv("TSB_GDN_CHUNKED", mode)
         monkeypatch.setenv("TSB_GDN_CARRY_KERNEL", carry)
+        monkeypatch.setenv("TSB_GDN_CHUNK_KERNELS", kernels)
         torch.manual_seed(2)
         st = s0.clone()
         outs = []
@@ -77,7 +79,9 @@ def test_chunk_carry_kernel_matches_the_scan_across_chunk_and_call_boundaries(mo
             z, beta, alpha = torch.randn(T, Hv * Dv, device=dev), torch.randn(T, Hv, device=dev), torch.randn(T, Hv, device=dev)
             b = _batch(lens, dev)
             outs.append(F.gdn(qkv, z, beta, alpha, dtb, a_log, nw, st, b, Hk=Hk, Hv=Hv, Dk=Dk, Dv=Dv, eps=1e-6).float())
-        results[(mode, carry)] = (torch.cat(outs), st)
-    scan, loop, kern = results[("0", "1")], results[("1", "0")], results[("1", "1")]
+        results[(mode, carry, kernels)] = (torch.cat(outs), st)
+    scan, loop, kern, full = results[("0", "1", "0")], results[("1", "0", "0")], results[("1", "1", "0")], results[("1", "1", "1")]
+    assert _rel(full[0], loop[0]) < 1e-2 and _rel(full[1], loop[1]) < 3e-3, (_rel(full[0], loop[0]), _rel(full[1], loop[1]))
+    assert _rel(full[0], scan[0]) < 2e-2 and _rel(full[1], scan[1]) < 3e-3, (_rel(full[0], scan[0]), _rel(full[1], scan[1]))
     assert _rel(kern[0], loop[0]) < 1e-2 and _rel(kern[1], loop[1]) < 3e-3, (_rel(kern[0], loop[0]), _rel(kern[1], loop[1]))
     assert _rel(kern[0], scan[0]) < 2e-2 and _rel(kern[1], scan[1]) < 3e-3, (_rel(kern[0], scan[0]), _rel(kern[1], scan[1]))
