@@ -3,6 +3,7 @@
 
     python bench_kernels.py gemv --type Q4_K --n 19456 --k 2560 --glu --m 1
     python bench_kernels.py gemv --type Q4_K --n 2560 --k 9728
+    python bench_kernels.py gemm --t 2048 --n 19456 --k 2560         # bf16 tensor-core GEMM; TSB_GEMM_WIDE=0 / 2 picks the tile
     python bench_kernels.py recurrent --op gdn --t 2048
     python bench_kernels.py recurrent --op mamba2 --t 2048
 
@@ -109,9 +110,43 @@ def recurrent(args):
                       "rel_diff_out": rel, "rel_diff_state": srel}))
 
 
+def gemm(args):
+    """The bf16 tcgen05 GEMM on [t, k] x [n, k]^T against torch.matmul (cuBLAS), cycling through weight copies larger
+    than L2.  TSB_GEMM_WIDE=0 keeps 128 x 256 tiles, 2 forces 256 x 256 (default: by tile count)."""
+    import torch
+    from tensorsharp_b200.ops import kernels
+    dev = "cuda"
+    torch.manual_seed(0)
+    copies = max(2, int(300e6 // (args.n * args.k * 2)) + 1)
+    ws = [(torch.randn(args.n, args.k, device=dev) * 0.05).bfloat16() for _ in range(copies)]
+    x = torch.randn(args.t, args.k, device=dev).bfloat16()
+    state = {"i": 0}
+
+    def ours():
+        state["i"] += 1
+        return kernels.gemm_bf16(ws[state["i"] % copies], x, out_dtype=torch.bfloat16)
+
+    def lib():
+        state["i"] += 1
+        return x @ ws[state["i"] % copies].t()
+    want = (x @ ws[0].t()).float()
+    err = float((kernels.gemm_bf16(ws[0], x, out_dtype=torch.bfloat16).float() - want).norm() / want.norm())
+    flop = 2.0 * args.t * args.n * args.k
+    us_o, us_l = time_us(ours, args.iters, args.warmup), time_us(lib, args.iters, args.warmup)
+    peak = None
+    try:
+        peak = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"]
+    except Exception:  # noqa: BLE001
+        pass
+    print(json.dumps({"kernel": "gemm_bf16", "T": args.t, "N": args.n, "K": args.k, "wide": os.environ.get("TSB_GEMM_WIDE", "0"), "persistent": os.environ.get("TSB_GEMM_PERSISTENT", "1"),
+                      "us": us_o, "tflops": flop / us_o / 1e6, "cublas_us": us_l, "cublas_tflops": flop / us_l / 1e6,
+                      "of_measured_cublas_peak": (flop / us_o / 1e6 / peak) if peak else None, "rel_diff": err,
+                      "status": int(kernels.gemm_status(torch.device(dev)).item())}))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv", "recurrent"])
+    ap.add_argument("what", choices=["gemv", "recurrent", "gemm"])
     ap.add_argument("--op", default="gdn", choices=["gdn", "mamba2"])
     ap.add_argument("--t", type=int, default=2048)
     ap.add_argument("--chunk", type=int, default=64)
@@ -125,6 +160,8 @@ def main():
     args = ap.parse_args()
     if args.what == "recurrent":
         return recurrent(args)
+    if args.what == "gemm":
+        return gemm(args)
     import torch
     from tensorsharp_b200.gguf.constants import GGMLType
     from tensorsharp_b200.ops import kernels

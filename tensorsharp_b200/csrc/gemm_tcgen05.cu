@@ -40,21 +40,24 @@ struct GemmEpi {
     const int* groups;
 };
 
-template <int BN, int STAGES>
+// MT = 1: a CTA owns 128 features; MT = 2: 256 features as two accumulators that share every token slab, which halves
+// the bytes a CTA pulls from L2 per FLOP (the limiter of the 128 x 256 tile) at the price of coarser tiles.
+template <int BN, int STAGES, int MT = 1>
 struct GemmSmem {
-    static constexpr int A_BYTES = 128 * 64 * 2;
+    static constexpr int A_BYTES = MT * 128 * 64 * 2;
     static constexpr int B_BYTES = BN * 64 * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
     static constexpr int TOTAL = BAR_OFF + (2 * STAGES + 1) * 8 + 16 + 1024;  // + alignment slack
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int MT = 1>
 __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmW,
                                                         const __grid_constant__ CUtensorMap tmX, GemmEpi ep, int K,
                                                         int* status) {
-    using L = GemmSmem<BN, STAGES>;
-    constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    using L = GemmSmem<BN, STAGES, MT>;
+    constexpr int TMEM_COLS = MT * BN < 32 ? 32 : MT * BN;
+    static_assert(MT == 1 || (MT == 2 && BN == 256), "two accumulators fill the 512 columns of tensor memory");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
@@ -63,7 +66,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * 128;       // first feature (row of W)
+    const int m0 = blockIdx.x * (128 * MT);       // first feature (row of W)
     int n0 = (int)((blockIdx.y + (unsigned)ep.tile_rot) % gridDim.y) * BN;        // first token
     int t_end = ep.T;                      // tokens at or past this row are not stored
     int w_row0 = m0;                       // row of the (stacked) weight matrix where this tile's features start
@@ -132,8 +135,13 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                 const uint32_t a = tc::smem_u32(smem + s * L::STAGE_BYTES);
                 const uint64_t da = tc::make_desc_sw128(a), db = tc::make_desc_sw128(a + L::A_BYTES);
 #pragma unroll
-                for (int k = 0; k < 4; ++k)   // 4 x (K = 16) per 64-element slab: +32 bytes = +2 descriptor units
+                for (int k = 0; k < 4; ++k) {   // 4 x (K = 16) per 64-element slab: +32 bytes = +2 descriptor units
                     tc::mma_f16_ss(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                    if (MT == 2) {              // the second 128 features: next 16 KB of the stage, next BN columns
+                        const uint64_t da2 = tc::make_desc_sw128(a + 128 * 64 * 2);
+                        tc::mma_f16_ss(tmem_base + BN, da2 + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                    }
+                }
                 tc::mma_commit(&empty_bar[s]);
             }
             if (ok) tc::mma_commit(acc_bar);
@@ -141,9 +149,11 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
         __syncwarp();
     } else {
         const int q = warp & 3;                       // TMEM lane quadrant this warp may read
-        const int n = m0 + q * 32 + lane;             // feature owned by this thread
         if (tc::mbar_wait(acc_bar, 0)) {
             tc::fence_after_sync();
+#pragma unroll 1
+          for (int half = 0; half < MT; ++half) {
+            const int n = m0 + half * 128 + q * 32 + lane;             // feature owned by this thread
             const float bias = (ep.bias && n < ep.N && (ep.rs == nullptr || ep.rs->rank == 0)) ? ep.bias[(long)group * ep.N + n] : 0.f;
             bf16* rs_dst = nullptr;
             if (ep.rs != nullptr) {
@@ -156,7 +166,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
 #pragma unroll 1
             for (int c = 0; c < BN / 16; ++c) {
                 uint32_t r[16];
-                tc::tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + c * 16, r);
+                tc::tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + half * BN + c * 16, r);
                 tc::tmem_ld_wait();
                 if (rs_dst != nullptr) {
                     if (n < ep.N) {
@@ -187,6 +197,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                     }
                 }
             }
+          }
         } else {
             atomicExch(status, 3);
         }
@@ -210,6 +221,159 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
             *g->rs_target += (unsigned)g->size * gridDim.x * (unsigned)(g->shard / BN);
         }
     }
+}
+
+// ------------------------------------------------------------------------------------------
+// Persistent form for plain GEMMs (no tensor-parallel hooks, no tile list): one CTA per SM walks the tiles
+// (feature tile fastest, so CTAs that run together share a token slab in L2), the TMA producer keeps filling the
+// shared-memory ring across tile boundaries, and tensor memory holds two accumulators: the epilogue warps drain tile i
+// while the MMA warp already multiplies tile i + 1.  With short K (the gate / up and QKV projections) the epilogue is
+// about half of a tile's time in the one-tile-per-CTA kernel above; here it disappears behind the next main loop.
+// ------------------------------------------------------------------------------------------
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192) gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap tmW,
+                                                                   const __grid_constant__ CUtensorMap tmX, GemmEpi ep, int K,
+                                                                   int m_tiles, int total_tiles, int* status) {
+    using L = GemmSmem<BN, STAGES>;
+    constexpr int TMEM_COLS = 2 * BN;
+    static_assert(TMEM_COLS >= 32 && TMEM_COLS <= 512, "two accumulators must fit tensor memory");
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_full = empty_bar + STAGES;          // [2] accumulator complete (one commit by the MMA thread)
+    uint64_t* acc_empty = acc_full + 2;               // [2] accumulator drained (one arrival per epilogue warp)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kblocks = (K + 63) / 64;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            tc::mbar_init(&full_bar[s], 1);
+            tc::mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            tc::mbar_init(&acc_full[b], 1);
+            tc::mbar_init(&acc_empty[b], 4);
+        }
+        tc::fence_barrier_init();
+    }
+    if (warp == 1) tc::tmem_alloc<TMEM_COLS>(tmem_slot);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();
+    pdl_trigger();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tc::tma_prefetch_desc(&tmW);
+            tc::tma_prefetch_desc(&tmX);
+            long it = 0;                               // k-blocks issued so far, over all tiles of this CTA
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * 128, n0 = (tile / m_tiles) * BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = (int)(it % STAGES);
+                    const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+                    if (!tc::mbar_wait(&empty_bar[s], ph ^ 1)) { atomicExch(status, 1); ok = false; break; }
+                    unsigned char* a = smem + s * L::STAGE_BYTES;
+                    tc::mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+                    tc::tma_load_2d(a, &tmW, &full_bar[s], kb * 64, m0);
+                    tc::tma_load_2d(a + L::A_BYTES, &tmX, &full_bar[s], kb * 64, n0);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = tc::make_idesc_bf16(128, BN);
+            long it = 0;
+            int j = 0;                                 // tiles done by this CTA
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++j) {
+                const int buf = j & 1;
+                const uint32_t aph = (uint32_t)(j >> 1) & 1u;
+                if (!tc::mbar_wait(&acc_empty[buf], aph ^ 1)) { atomicExch(status, 5); ok = false; break; }
+                tc::fence_after_sync();
+                const uint32_t acc = tmem_base + (uint32_t)buf * BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = (int)(it % STAGES);
+                    const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+                    if (!tc::mbar_wait(&full_bar[s], ph)) { atomicExch(status, 2); ok = false; break; }
+                    tc::fence_after_sync();
+                    const uint32_t a = tc::smem_u32(smem + s * L::STAGE_BYTES);
+                    const uint64_t da = tc::make_desc_sw128(a), db = tc::make_desc_sw128(a + L::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) tc::mma_f16_ss(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                    tc::mma_commit(&empty_bar[s]);
+                }
+                if (ok) tc::mma_commit(&acc_full[buf]);
+            }
+        }
+        __syncwarp();
+    } else {
+        const int q = warp & 3;
+        int j = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++j) {
+            const int buf = j & 1;
+            const uint32_t aph = (uint32_t)(j >> 1) & 1u;
+            const int m0 = (tile % m_tiles) * 128, n0 = (tile / m_tiles) * BN;
+            const int n = m0 + q * 32 + lane;
+            if (!tc::mbar_wait(&acc_full[buf], aph)) { atomicExch(status, 3); break; }
+            tc::fence_after_sync();
+            const float bias = (ep.bias && n < ep.N) ? ep.bias[n] : 0.f;
+#pragma unroll 1
+            for (int c = 0; c < BN / 16; ++c) {
+                uint32_t r[16];
+                tc::tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * BN + c * 16, r);
+                tc::tmem_ld_wait();
+                if (n < ep.N) {
+#pragma unroll
+                    for (int jj = 0; jj < 16; ++jj) {
+                        const int t = n0 + c * 16 + jj;
+                        if (t < ep.T) {
+                            float v = __uint_as_float(r[jj]) + bias;
+                            const long o = (long)t * ep.ldo + n;
+                            if (ep.out_f32) {
+                                if (ep.residual) v += reinterpret_cast<const float*>(ep.residual)[o];
+                                reinterpret_cast<float*>(ep.out)[o] = v;
+                            } else {
+                                if (ep.residual) v += bf2f(reinterpret_cast<const bf16*>(ep.residual)[o]);
+                                reinterpret_cast<bf16*>(ep.out)[o] = f2bf(v);
+                            }
+                        }
+                    }
+                }
+            }
+            tc::fence_before_sync();                  // this warp's reads of the accumulator are complete
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc::fence_after_sync();
+        tc::tmem_dealloc<TMEM_COLS>(tmem_base);
+    }
+}
+
+template <int BN, int STAGES>
+static int launch_gemm_persistent(const CUtensorMap& tw, const CUtensorMap& tx, const GemmEpi& ep, int K, int sms, int* status,
+                                  cudaStream_t s) {
+    using L = GemmSmem<BN, STAGES>;
+    constexpr int SMEM = L::TOTAL + 32;               // two more barrier pairs than the one-tile kernel
+    static bool configured = false;
+    if (!configured) {
+        TSB_CHECK_CUDA(cudaFuncSetAttribute(gemm_bf16_persistent_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+        configured = true;
+    }
+    const int m_tiles = (ep.N + 127) / 128, n_tiles = (ep.T + BN - 1) / BN, total = m_tiles * n_tiles;
+    const int grid = total < sms ? total : sms;
+    TSB_CHECK_CUDA(tsb_launch(gemm_bf16_persistent_kernel<BN, STAGES>, dim3(grid), dim3(192), (size_t)SMEM, s, tw, tx, ep, K, m_tiles,
+                              total, status));
+    return TSB_OK;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -249,21 +413,21 @@ int tsb_make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uin
     return TSB_OK;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int MT = 1>
 static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmEpi& ep, int K, int* status,
                        cudaStream_t s) {
-    using L = GemmSmem<BN, STAGES>;
+    using L = GemmSmem<BN, STAGES, MT>;
     static bool configured = false;
     if (!configured) {
-        TSB_CHECK_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        TSB_CHECK_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             L::TOTAL));
         configured = true;
     }
     // with a reduce-scatter epilogue the grid also covers the padding rows of the last shard, so
     // that every owner sees the same number of arrivals
     const int t_cover = ep.rs != nullptr ? ep.rs_rows : ep.T;
-    dim3 grid((ep.N + 127) / 128, (t_cover + BN - 1) / BN);
-    TSB_CHECK_CUDA(tsb_launch(gemm_bf16_kernel<BN, STAGES>, grid, dim3(192), (size_t)L::TOTAL, s, tw, tx, ep, K, status));
+    dim3 grid((ep.N + 128 * MT - 1) / (128 * MT), (t_cover + BN - 1) / BN);
+    TSB_CHECK_CUDA(tsb_launch(gemm_bf16_kernel<BN, STAGES, MT>, grid, dim3(192), (size_t)L::TOTAL, s, tw, tx, ep, K, status));
     return TSB_OK;
 }
 
@@ -313,8 +477,19 @@ extern "C" int tsb_gemm_bf16_tp(const void* W, long ldw, const void* X, long ldx
     static const int rs_small = []() { const char* e = getenv("TSB_TP_RS_TILE"); return e ? atoi(e) : 256; }();
     const bool two_per_sm = rs && rs_small == 128;
     if (two_per_sm) bn = 128;
+    // 256 x 256 tiles (two accumulators per CTA): two thirds of the L2 bytes per FLOP of the 128 x 256 tile.  Measured
+    // on 8192 x 19456 x 2560: 652 against 623 TFLOP/s, and nothing at 2048 tokens, so it is opt-in (TSB_GEMM_WIDE=1: when
+    // there are at least three waves of such tiles; 2: always); the persistent kernel below is what the default takes.
+    static const int wide_mode = []() { const char* e = getenv("TSB_GEMM_WIDE"); return e ? atoi(e) : 0; }();
+    bool wide = false;
+    if (bn == 256 && !rs && !ag && wide_mode != 0) {
+        int dev = 0, sms = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const long tiles = (long)((N + 255) / 256) * ((T + 255) / 256);
+        wide = tiles >= 3L * sms || wide_mode == 2;
+    }
     CUtensorMap tw, tx;
-    int rc = tsb_make_tmap_2d_bf16(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 128, 64);
+    int rc = tsb_make_tmap_2d_bf16(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, wide ? 256 : 128, 64);
     if (rc) return rc;
     rc = tsb_make_tmap_2d_bf16(&tx, X, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, (uint32_t)bn, 64);
     if (rc) return rc;
@@ -326,11 +501,21 @@ extern "C" int tsb_gemm_bf16_tp(const void* W, long ldw, const void* X, long ldx
     if (rs) rot = ((rank + 1) % size) * (shard / bn);
     GemmEpi ep{out, bias, residual, ldo, T, N, out_f32, (const TpSeq*)rs, (const TpSeq*)ag, shard * size, rot};
     cudaStream_t s = (cudaStream_t)stream;
+    // plain GEMMs with more tiles than SMs: the persistent kernel (epilogue of a tile under the next tile's main loop)
+    static const int persist_mode = []() { const char* e = getenv("TSB_GEMM_PERSISTENT"); return e ? atoi(e) : 1; }();
+    if (!rs && !ag && !wide && persist_mode != 0 && (bn == 256 || bn == 128)) {
+        int dev = 0, sms = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const long tiles = (long)((N + 127) / 128) * ((T + bn - 1) / bn);
+        if (tiles > sms)
+            return bn == 256 ? launch_gemm_persistent<256, 4>(tw, tx, ep, K, sms, status, s)
+                             : launch_gemm_persistent<128, 6>(tw, tx, ep, K, sms, status, s);
+    }
     switch (bn) {
     case 32: return launch_gemm<32, 8>(tw, tx, ep, K, status, s);
     case 64: return launch_gemm<64, 8>(tw, tx, ep, K, status, s);
     case 128: return two_per_sm ? launch_gemm<128, 3>(tw, tx, ep, K, status, s) : launch_gemm<128, 6>(tw, tx, ep, K, status, s);
-    default: return launch_gemm<256, 4>(tw, tx, ep, K, status, s);
+    default: return wide ? launch_gemm<256, 3, 2>(tw, tx, ep, K, status, s) : launch_gemm<256, 4>(tw, tx, ep, K, status, s);
     }
 }
 

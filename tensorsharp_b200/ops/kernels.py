@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 from typing import Optional
 
 import torch
@@ -27,6 +28,25 @@ def _p(t: Optional[torch.Tensor]):
 
 def _stream():
     return _vp(torch.cuda.current_stream().cuda_stream)
+
+
+# Debug mode TSB_CHECK_INDICES=1: before a launch, every index tensor that the kernel will use to address memory (token
+# ids, KV slots, block-table pages, cache lengths, expert ids, state slots) is checked on the host against the size of
+# what it indexes, and an IndexError names the kernel and the offending value instead of the kernel reading or writing out
+# of bounds.  Each check synchronises the stream, so the mode is for debugging only (and cannot be used while a CUDA
+# graph is being captured).  The kernels themselves index unchecked.
+CHECK_INDICES = os.environ.get("TSB_CHECK_INDICES", "0") not in ("", "0")
+
+
+def check_index(kernel: str, what: str, t: Optional[torch.Tensor], limit: int, low: int = 0) -> None:
+    """Raise IndexError unless every element of ``t`` lies in ``[low, limit)``.  No-op unless TSB_CHECK_INDICES=1."""
+    if not CHECK_INDICES or t is None or t.numel() == 0:
+        return
+    if t.is_cuda and torch.cuda.is_current_stream_capturing():
+        return
+    lo, hi = int(t.min().item()), int(t.max().item())
+    if lo < low or hi >= limit:
+        raise IndexError(f"{kernel}: {what} out of range: values span [{lo}, {hi}], allowed [{low}, {limit})")
 
 
 def _planes(w: QuantWeight):
@@ -302,6 +322,8 @@ def qkv_rope(*, q, k, v, q_strides, k_strides, v_strides, Hq, Hkv, Dh, pos, slot
              qn=None, kn=None, v_norm=False, eps=1e-6, rope: RopeParams, freq_factors=None, q_scale=1.0,
              cs_table=None):
     T = int(pos.numel())
+    check_index("qkv_rope", "KV slot", slot, k_cache.shape[0] if k_cache is not None else 1 << 62)
+    check_index("qkv_rope", "position", pos, 1 << 31)
     a = QkvArgs()
     a.q, a.k, a.v = _p(q), _p(k), _p(v)
     a.q_tok, a.q_head = q_strides
@@ -350,6 +372,7 @@ def gather_rows(w: QuantWeight, ids: Optional[torch.Tensor], scale: float = 1.0,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Embedding lookup (ids given) or whole-matrix decode to ``out_dtype`` (ids None)."""
     n = int(ids.numel()) if ids is not None else w.rows
+    check_index("gather_rows", "row id", ids, w.rows)
     if out is None:
         out = torch.empty((n, w.K), dtype=out_dtype, device=w.device)
     ps = _planes(w)
@@ -382,6 +405,8 @@ def decode_advance(sampled, batch) -> None:
 
 def _attn_args(q, k_cache, v_cache, out, block_table, kv_lens, cu_q, sinks, scale, softcap, window, Hq, Hkv, Dh,
                page_size, B):
+    check_index("attention", "block-table page", block_table, k_cache.shape[0] // page_size)
+    check_index("attention", "cache length", kv_lens, block_table.shape[1] * page_size + 1)
     a = AttnArgs()
     a.q, a.k_cache, a.v_cache, a.out = _p(q), _p(k_cache), _p(v_cache), _p(out)
     a.block_table, a.kv_lens, a.cu_q, a.sinks = _p(block_table), _p(kv_lens), _p(cu_q), _p(sinks)
@@ -524,6 +549,7 @@ class MambaArgs(C.Structure):
 def causal_conv1d(x, w, bias, state, cu_q, seq_slots, max_q, act_silu=True) -> torch.Tensor:
     """x [T, C] view (row stride allowed) -> f32 [T, C]; the per-slot tail ``state`` is updated."""
     T, Cc = x.shape
+    check_index("causal_conv1d", "state slot", seq_slots, state.shape[0])
     out = torch.empty((T, Cc), dtype=torch.float32, device=x.device)
     a = ConvArgs()
     a.x, a.xs, a.x_f32 = _p(x), x.stride(0), int(x.dtype == torch.float32)
@@ -537,6 +563,8 @@ def causal_conv1d(x, w, bias, state, cu_q, seq_slots, max_q, act_silu=True) -> t
 
 def gdn_recurrent(qkv, z, beta, alpha, dt_bias, a_log, norm_w, state, cu_q, seq_slots, *, Hk, Hv, Dk, Dv, eps):
     T = qkv.shape[0]
+    check_index("gdn_recurrent", "state slot", seq_slots, state.shape[0])
+    check_index("gdn_recurrent", "row offset", cu_q, T + 1)
     out = torch.empty((T, Hv * Dv), dtype=torch.bfloat16, device=qkv.device)
     assert qkv.dtype == torch.float32 and beta.dtype == alpha.dtype and beta.stride(0) == alpha.stride(0)
     a = GdnArgs()
@@ -621,6 +649,8 @@ def gdn_chunk_carry(U0, W, Qd, Kd, P, gamma, state) -> torch.Tensor:
 
 def mamba2_recurrent(xbc, dt, dt_bias, A, D, state, cu_q, seq_slots, *, H, P, G, N):
     T = xbc.shape[0]
+    check_index("mamba2_recurrent", "state slot", seq_slots, state.shape[0])
+    check_index("mamba2_recurrent", "row offset", cu_q, T + 1)
     y = torch.empty((T, H * P), dtype=torch.float32, device=xbc.device)
     a = MambaArgs()
     a.xbc, a.xbc_s = _p(xbc), xbc.stride(0)

@@ -239,7 +239,10 @@ def test_attn_prefill(Hq, Hkv, Dh, window, sinks, softcap):
         o += ql
 
 
-@pytest.mark.parametrize("T,N,Kd", [(5, 128, 64), (33, 200, 320), (100, 384, 2560), (300, 1000, 512), (2048, 256, 1024)])
+# the last four shapes have more tiles than SMs and take the persistent kernel (two accumulators in tensor memory, the
+# epilogue of a tile under the next tile's main loop): 256- and 128-token tiles, ragged edges, a single k-block
+@pytest.mark.parametrize("T,N,Kd", [(5, 128, 64), (33, 200, 320), (100, 384, 2560), (300, 1000, 512), (2048, 256, 1024),
+                                    (3900, 7744, 320), (4096, 7680, 64), (100, 20480, 256), (520, 19400, 192)])
 def test_gemm_bf16_tcgen05(T, N, Kd):
     torch.manual_seed(9)
     W = (torch.randn(N, Kd, device=DEV) * 0.05).bfloat16()
@@ -648,3 +651,24 @@ def test_gemv_tensor_core_batches_q4k(N, Kd, act, M):
         scale = torch.rand(M, device=DEV) + 0.5
         got = K().gemv(qw, xq=xq, xds=xds, M=M, bias=bias, residual=res, row_scale=scale)
         assert rel_err(got, y * scale[:, None] + res) < 3e-3
+
+
+def test_index_check_mode_names_the_bad_index_before_the_launch(monkeypatch):
+    """TSB_CHECK_INDICES=1: an index that would take a kernel out of bounds (a token id past the embedding, a block-table
+    page past the pool) raises IndexError on the host; nothing is launched with it."""
+    from tensorsharp_b200.ops import kernels as kmod
+    monkeypatch.setattr(kmod, "CHECK_INDICES", True)
+    w = QuantWeight.from_float(torch.randn(64, 256, device=DEV) * 0.1, GGMLType.Q8_0)
+    ok = K().gather_rows(w, torch.tensor([0, 63], dtype=torch.int32, device=DEV))
+    assert ok.shape == (2, 256)
+    with pytest.raises(IndexError, match="gather_rows: row id"):
+        K().gather_rows(w, torch.tensor([0, 64], dtype=torch.int32, device=DEV))
+    ps, lens = 16, [20]
+    kc, vc, table = _paged(sum(lens), 2, 64, ps, lens)
+    q = torch.randn(1, 4, 64, device=DEV).bfloat16()
+    kv_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    bad = table.clone()
+    bad[0, 1] = kc.shape[0] // ps                         # first page past the pool
+    with pytest.raises(IndexError, match="block-table page"):
+        K().attn_decode(q, kc, vc, bad, kv_lens, scale=0.125, Hq=4, Hkv=2, Dh=64, page_size=ps, splits=1)
+    K().attn_decode(q, kc, vc, table, kv_lens, scale=0.125, Hq=4, Hkv=2, Dh=64, page_size=ps, splits=1)
