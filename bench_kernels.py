@@ -122,9 +122,13 @@ def gemm(args):
     x = torch.randn(args.t, args.k, device=dev).bfloat16()
     state = {"i": 0}
 
+    odt = torch.float32 if args.f32 else torch.bfloat16
+    res = torch.randn(args.t, args.n, device=dev).to(odt) if args.residual else None
+    outb = torch.empty(args.t, args.n, device=dev, dtype=odt)
+
     def ours():
         state["i"] += 1
-        return kernels.gemm_bf16(ws[state["i"] % copies], x, out_dtype=torch.bfloat16)
+        return kernels.gemm_bf16(ws[state["i"] % copies], x, out_dtype=odt, residual=res, out=outb)
 
     def lib():
         state["i"] += 1
@@ -138,7 +142,7 @@ def gemm(args):
         peak = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"]
     except Exception:  # noqa: BLE001
         pass
-    print(json.dumps({"kernel": "gemm_bf16", "T": args.t, "N": args.n, "K": args.k, "wide": os.environ.get("TSB_GEMM_WIDE", "0"), "persistent": os.environ.get("TSB_GEMM_PERSISTENT", "1"),
+    print(json.dumps({"kernel": "gemm_bf16", "T": args.t, "N": args.n, "K": args.k, "f32_out": args.f32, "residual": args.residual, "wide": os.environ.get("TSB_GEMM_WIDE", "0"), "persistent": os.environ.get("TSB_GEMM_PERSISTENT", "1"),
                       "us": us_o, "tflops": flop / us_o / 1e6, "cublas_us": us_l, "cublas_tflops": flop / us_l / 1e6,
                       "of_measured_cublas_peak": (flop / us_o / 1e6 / peak) if peak else None, "rel_diff": err,
                       "status": int(kernels.gemm_status(torch.device(dev)).item())}))
@@ -155,6 +159,8 @@ def main():
     ap.add_argument("--k", type=int, default=2560)
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--glu", action="store_true")
+    ap.add_argument("--f32", action="store_true", help="gemm: float32 output")
+    ap.add_argument("--residual", action="store_true", help="gemm: add a residual of the output's type in the epilogue")
     ap.add_argument("--iters", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     args = ap.parse_args()

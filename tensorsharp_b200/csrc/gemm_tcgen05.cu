@@ -40,6 +40,37 @@ struct GemmEpi {
     const int* groups;
 };
 
+// Epilogue of one thread for 16 consecutive tokens of its feature n: out[t, n] = acc + bias (+ residual[t, n]).
+// The residual values are all requested before the first store: with the load and the store of one token back to back
+// (the residual may be the output buffer itself, so the compiler keeps their order) every token would cost a full
+// memory round trip, 16 in a row per chunk.  Each element is read and written by the same thread, so reading ahead is
+// safe for an in-place residual too.
+__device__ __forceinline__ void gemm_store16(const GemmEpi& ep, const uint32_t (&r)[16], int n, int t0, int t_end, float bias) {
+    float res[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) res[j] = 0.f;
+    if (ep.residual != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int t = t0 + j;
+            if (t < t_end) {
+                const long o = (long)t * ep.ldo + n;
+                res[j] = ep.out_f32 ? reinterpret_cast<const float*>(ep.residual)[o] : bf2f(reinterpret_cast<const bf16*>(ep.residual)[o]);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const int t = t0 + j;
+        if (t < t_end) {
+            const float v = __uint_as_float(r[j]) + bias + res[j];
+            const long o = (long)t * ep.ldo + n;
+            if (ep.out_f32) reinterpret_cast<float*>(ep.out)[o] = v;
+            else reinterpret_cast<bf16*>(ep.out)[o] = f2bf(v);
+        }
+    }
+}
+
 // MT = 1: a CTA owns 128 features; MT = 2: 256 features as two accumulators that share every token slab, which halves
 // the bytes a CTA pulls from L2 per FLOP (the limiter of the 128 x 256 tile) at the price of coarser tiles.
 template <int BN, int STAGES, int MT = 1>
@@ -180,21 +211,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                         }
                     }
                 } else if (n < ep.N) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int t = n0 + c * 16 + j;
-                        if (t < t_end) {
-                            float v = __uint_as_float(r[j]) + bias;
-                            const long o = (long)t * ep.ldo + n;
-                            if (ep.out_f32) {
-                                if (ep.residual) v += reinterpret_cast<const float*>(ep.residual)[o];
-                                reinterpret_cast<float*>(ep.out)[o] = v;
-                            } else {
-                                if (ep.residual) v += bf2f(reinterpret_cast<const bf16*>(ep.residual)[o]);
-                                reinterpret_cast<bf16*>(ep.out)[o] = f2bf(v);
-                            }
-                        }
-                    }
+                    gemm_store16(ep, r, n, n0 + c * 16, t_end, bias);
                 }
             }
           }
@@ -328,23 +345,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_persistent_kernel(const __grid_
                 uint32_t r[16];
                 tc::tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * BN + c * 16, r);
                 tc::tmem_ld_wait();
-                if (n < ep.N) {
-#pragma unroll
-                    for (int jj = 0; jj < 16; ++jj) {
-                        const int t = n0 + c * 16 + jj;
-                        if (t < ep.T) {
-                            float v = __uint_as_float(r[jj]) + bias;
-                            const long o = (long)t * ep.ldo + n;
-                            if (ep.out_f32) {
-                                if (ep.residual) v += reinterpret_cast<const float*>(ep.residual)[o];
-                                reinterpret_cast<float*>(ep.out)[o] = v;
-                            } else {
-                                if (ep.residual) v += bf2f(reinterpret_cast<const bf16*>(ep.residual)[o]);
-                                reinterpret_cast<bf16*>(ep.out)[o] = f2bf(v);
-                            }
-                        }
-                    }
-                }
+                if (n < ep.N) gemm_store16(ep, r, n, n0 + c * 16, ep.T, bias);
             }
             tc::fence_before_sync();                  // this warp's reads of the accumulator are complete
             __syncwarp();
