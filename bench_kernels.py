@@ -4,6 +4,7 @@
     python bench_kernels.py gemv --type Q4_K --n 19456 --k 2560 --glu --m 1
     python bench_kernels.py gemv --type Q4_K --n 2560 --k 9728
     python bench_kernels.py gemm --t 2048 --n 19456 --k 2560         # bf16 tensor-core GEMM; TSB_GEMM_WIDE=0 / 2 picks the tile
+    python bench_kernels.py attn --t 2048 --hq 32 --hkv 8 --dh 128   # causal flash prefill over the paged cache
     python bench_kernels.py recurrent --op gdn --t 2048
     python bench_kernels.py recurrent --op mamba2 --t 2048
 
@@ -148,9 +149,39 @@ def gemm(args):
                       "status": int(kernels.gemm_status(torch.device(dev)).item())}))
 
 
+def attn(args):
+    """Causal prefill attention of one sequence of ``--t`` tokens against the paged bf16 cache (pages of 64 in shuffled
+    order), ``--hq`` query / ``--hkv`` KV heads of ``--dh``; FLOPs counted as 4 * T^2 / 2 * Dh * Hq."""
+    import torch
+    from tensorsharp_b200.ops import kernels
+    dev, T, Hq, Hkv, Dh, ps = "cuda", args.t, args.hq, args.hkv, args.dh, 64
+    torch.manual_seed(0)
+    n_pages = (T + ps - 1) // ps
+    kc = torch.randn(n_pages * ps, Hkv, Dh, device=dev).bfloat16()
+    vc = torch.randn(n_pages * ps, Hkv, Dh, device=dev).bfloat16()
+    table = torch.randperm(n_pages, device=dev).to(torch.int32).view(1, n_pages)
+    q = torch.randn(T, Hq, Dh, device=dev).bfloat16()
+    cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+    lens = torch.tensor([T], dtype=torch.int32, device=dev)
+    out = torch.empty_like(q)
+
+    def run():
+        return kernels.attn_prefill(q, kc, vc, table, lens, cu, T, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh, page_size=ps,
+                                    window=args.window, out=out)
+    us = time_us(run, args.iters, args.warmup)
+    span = T if not args.window else min(T, args.window)
+    flop = 4.0 * T * (span if args.window else T / 2.0) * Dh * Hq
+    print(json.dumps({"kernel": "attn_prefill", "T": T, "Hq": Hq, "Hkv": Hkv, "Dh": Dh, "window": args.window, "us": us,
+                      "tflops": flop / us / 1e6}))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv", "recurrent", "gemm"])
+    ap.add_argument("what", choices=["gemv", "recurrent", "gemm", "attn"])
+    ap.add_argument("--hq", type=int, default=32)
+    ap.add_argument("--hkv", type=int, default=8)
+    ap.add_argument("--dh", type=int, default=128)
+    ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--op", default="gdn", choices=["gdn", "mamba2"])
     ap.add_argument("--t", type=int, default=2048)
     ap.add_argument("--chunk", type=int, default=64)
@@ -168,6 +199,8 @@ def main():
         return recurrent(args)
     if args.what == "gemm":
         return gemm(args)
+    if args.what == "attn":
+        return attn(args)
     import torch
     from tensorsharp_b200.gguf.constants import GGMLType
     from tensorsharp_b200.ops import kernels

@@ -524,7 +524,7 @@ __global__ void __launch_bounds__(128 * DS) attn_prefill_kernel(AttnArgs a) {
 
     const int b = blockIdx.z, h = blockIdx.y, hk = h / (a.Hq / a.Hkv);
     const int q0 = a.cu_q[b], qlen = a.cu_q[b + 1] - q0;
-    const int m0 = blockIdx.x * BM;
+    const int m0 = (int)(gridDim.x - 1 - blockIdx.x) * BM;      // last query tiles first: under a causal mask they have the most keys
     if (m0 >= qlen) return;
     const int kvlen = a.kv_lens[b];
     const int pos0 = a.q_pos0 ? a.q_pos0[b] : kvlen - qlen;   // cache position of the sequence's first query
@@ -599,39 +599,60 @@ __global__ void __launch_bounds__(128 * DS) attn_prefill_kernel(AttnArgs a) {
                 mma_bf16(s[2 * nt + 1], qa, kb[2], kb[3]);
             }
         }
-        // scale, soft-cap, mask, online softmax
-        float mx[2] = {mrow[0], mrow[1]};
+        // soft-cap, mask, online softmax.  The scores stay unscaled: with f = scale (or 1 after the soft-cap, which needs
+        // the scaled value) the row maximum is max(x) * f and p = 2^(x * f * log2 e - max * log2 e), one multiply-add and
+        // one exponential per score.  The mask compares run only in tiles that touch the diagonal, the end of the cache
+        // or the window's edge (uniform per warp); interior tiles skip them.
+        constexpr float LOG2E = 1.4426950408889634f;
+        float f = a.scale;
+        if (a.softcap > 0.f) {
+            const float inv_cap = a.scale / a.softcap;
+#pragma unroll
+            for (int nt = 0; nt < BN / 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[nt][e] = a.softcap * tanhf(s[nt][e] * inv_cap);
+            f = 1.f;
+        }
+        const int q_first = pos0 + m0 + warp * 16;               // cache position of this warp's first query row
+        const bool need_mask = (t * BN + BN - 1 > q_first) || ((t + 1) * BN > kvlen) ||
+                               (a.window > 0 && t * BN <= q_first + 15 - a.window);
+        if (need_mask) {
+#pragma unroll
+            for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = t * BN + nt * 8 + (lane & 3) * 2 + (e & 1);
+                    const int qp = (e < 2) ? qpos_a : qpos_b;
+                    const bool ok = j <= qp && j < kvlen && (a.window <= 0 || j > qp - a.window);
+                    s[nt][e] = ok ? s[nt][e] : -INFINITY;
+                }
+            }
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int nt = 0; nt < BN / 8; ++nt) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int j = t * BN + nt * 8 + (lane & 3) * 2 + (e & 1);
-                const int qp = (e < 2) ? qpos_a : qpos_b;
-                float v = s[nt][e] * a.scale;
-                if (a.softcap > 0.f) v = a.softcap * tanhf(v / a.softcap);
-                const bool ok = j <= qp && j < kvlen && (a.window <= 0 || j > qp - a.window);
-                v = ok ? v : -INFINITY;
-                s[nt][e] = v;
-                mx[e >> 1] = fmaxf(mx[e >> 1], v);
-            }
+            mx[0] = fmaxf(mx[0], fmaxf(s[nt][0], s[nt][1]));
+            mx[1] = fmaxf(mx[1], fmaxf(s[nt][2], s[nt][3]));
         }
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            mx[r] = fmaxf(mrow[r], mx[r] * f);                   // running maximum, in scaled units
         }
-        float corr[2], rsum[2] = {0.f, 0.f};
+        float corr[2], rsum[2] = {0.f, 0.f}, mneg[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-            corr[r] = (mrow[r] == -INFINITY) ? 0.f : __expf(mrow[r] - mx[r]);
+            corr[r] = (mrow[r] == -INFINITY) ? 0.f : exp2f((mrow[r] - mx[r]) * LOG2E);
             mrow[r] = mx[r];
+            mneg[r] = (mx[r] == -INFINITY) ? 0.f : -mx[r] * LOG2E;
         }
+        const float fl = f * LOG2E;
 #pragma unroll
         for (int nt = 0; nt < BN / 8; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float mref = mx[e >> 1];
-                const float p = (mref == -INFINITY) ? 0.f : __expf(s[nt][e] - mref);
+                const float p = exp2f(fmaf(s[nt][e], fl, mneg[e >> 1]));
                 s[nt][e] = p;
                 rsum[e >> 1] += p;
             }
