@@ -289,14 +289,20 @@ __global__ void __launch_bounds__(192) gemm_bf16_persistent_kernel(const __grid_
             long it = 0;                               // k-blocks issued so far, over all tiles of this CTA
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile % m_tiles) * 128, n0 = (tile / m_tiles) * BN;
+                int w_row0 = (tile % m_tiles) * 128, n0 = (tile / m_tiles) * BN;
+                if (ep.groups != nullptr) {            // grouped mode: the token tile comes from the device-built list
+                    const int* gt = ep.groups + 3 * (tile / m_tiles);
+                    if (gt[0] < 0) continue;
+                    w_row0 += gt[0] * ep.N;
+                    n0 = gt[1];
+                }
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = (int)(it % STAGES);
                     const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
                     if (!tc::mbar_wait(&empty_bar[s], ph ^ 1)) { atomicExch(status, 1); ok = false; break; }
                     unsigned char* a = smem + s * L::STAGE_BYTES;
                     tc::mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
-                    tc::tma_load_2d(a, &tmW, &full_bar[s], kb * 64, m0);
+                    tc::tma_load_2d(a, &tmW, &full_bar[s], kb * 64, w_row0);
                     tc::tma_load_2d(a + L::A_BYTES, &tmX, &full_bar[s], kb * 64, n0);
                 }
             }
@@ -308,7 +314,8 @@ __global__ void __launch_bounds__(192) gemm_bf16_persistent_kernel(const __grid_
             long it = 0;
             int j = 0;                                 // tiles done by this CTA
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++j) {
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                if (ep.groups != nullptr && ep.groups[3 * (tile / m_tiles)] < 0) continue;
                 const int buf = j & 1;
                 const uint32_t aph = (uint32_t)(j >> 1) & 1u;
                 if (!tc::mbar_wait(&acc_empty[buf], aph ^ 1)) { atomicExch(status, 5); ok = false; break; }
@@ -326,30 +333,40 @@ __global__ void __launch_bounds__(192) gemm_bf16_persistent_kernel(const __grid_
                     tc::mma_commit(&empty_bar[s]);
                 }
                 if (ok) tc::mma_commit(&acc_full[buf]);
+                ++j;
             }
         }
         __syncwarp();
     } else {
         const int q = warp & 3;
         int j = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++j) {
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            int n0 = (tile / m_tiles) * BN, t_end = ep.T, group = 0;
+            if (ep.groups != nullptr) {
+                const int* gt = ep.groups + 3 * (tile / m_tiles);
+                group = gt[0];
+                if (group < 0) continue;
+                n0 = gt[1];
+                t_end = gt[2];
+            }
             const int buf = j & 1;
             const uint32_t aph = (uint32_t)(j >> 1) & 1u;
-            const int m0 = (tile % m_tiles) * 128, n0 = (tile / m_tiles) * BN;
+            const int m0 = (tile % m_tiles) * 128;
             const int n = m0 + q * 32 + lane;
             if (!tc::mbar_wait(&acc_full[buf], aph)) { atomicExch(status, 3); break; }
             tc::fence_after_sync();
-            const float bias = (ep.bias && n < ep.N) ? ep.bias[n] : 0.f;
+            const float bias = (ep.bias && n < ep.N) ? ep.bias[(long)group * ep.N + n] : 0.f;
 #pragma unroll 1
             for (int c = 0; c < BN / 16; ++c) {
                 uint32_t r[16];
                 tc::tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * BN + c * 16, r);
                 tc::tmem_ld_wait();
-                if (n < ep.N) gemm_store16(ep, r, n, n0 + c * 16, ep.T, bias);
+                if (n < ep.N) gemm_store16(ep, r, n, n0 + c * 16, t_end, bias);
             }
             tc::fence_before_sync();                  // this warp's reads of the accumulator are complete
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
+            ++j;
         }
     }
     tc::fence_before_sync();
@@ -539,6 +556,14 @@ extern "C" int tsb_gemm_bf16_grouped(const void* W, long ldw, int E, const void*
     if (rc) return rc;
     GemmEpi ep{out, bias, nullptr, ldo, n_tiles * bn, N, out_f32, nullptr, nullptr, 0, 0, groups};
     cudaStream_t s = (cudaStream_t)stream;
+    static const int persist_mode = []() { const char* e = getenv("TSB_GEMM_PERSISTENT"); return e ? atoi(e) : 1; }();
+    if (persist_mode != 0 && (bn == 256 || bn == 128)) {
+        int dev = 0, sms = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if ((long)((N + 127) / 128) * n_tiles > sms)
+            return bn == 256 ? launch_gemm_persistent<256, 4>(tw, tx, ep, K, sms, status, s)
+                             : launch_gemm_persistent<128, 6>(tw, tx, ep, K, sms, status, s);
+    }
     switch (bn) {
     case 32: return launch_gemm<32, 8>(tw, tx, ep, K, status, s);
     case 64: return launch_gemm<64, 8>(tw, tx, ep, K, status, s);

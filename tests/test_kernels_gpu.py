@@ -423,7 +423,7 @@ def test_moe_grouped_matches_per_slot_reference(t, act, e0, E_local, Kd, Fd):
 
 
 @pytest.mark.parametrize("t,act", [(GGMLType.MXFP4, "swiglu_oai"), (GGMLType.Q4_K, "swiglu"), (GGMLType.BF16, "relu2")])
-@pytest.mark.parametrize("e0,E_local,T,k", [(0, 8, 700, 2), (4, 4, 900, 3), (0, 8, 40, 2)])
+@pytest.mark.parametrize("e0,E_local,T,k", [(0, 8, 700, 2), (4, 4, 900, 3), (0, 8, 40, 2), (0, 8, 2000, 3)])   # the last: persistent kernel
 def test_moe_prefill_grouped_gemm_matches_per_expert_route(monkeypatch, t, act, e0, E_local, T, k):
     """Large batches: both expert projections as one grouped tensor-core GEMM each over a device-built tile list
     (F.moe_experts above MOE_TILE_MAX_PAIRS) against the route that sorts on the host and runs expert after expert;
