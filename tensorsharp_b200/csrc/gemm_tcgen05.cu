@@ -261,8 +261,12 @@ __global__ void __launch_bounds__(192) gemm_bf16_persistent_kernel(const __grid_
     uint64_t* acc_full = empty_bar + STAGES;          // [2] accumulator complete (one commit by the MMA thread)
     uint64_t* acc_empty = acc_full + 2;               // [2] accumulator drained (one arrival per epilogue warp)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    // reduce-scatter epilogue: two buffers of 16 tokens x 128 features (bf16) in which the four epilogue warps turn
+    // their feature-per-lane fragments into whole token rows, so that a peer store covers 256 contiguous bytes
+    bf16* rs_stage = reinterpret_cast<bf16*>(smem + L::BAR_OFF + 256);      // past the barriers (at most 2 * 8 + 4 words) and the TMEM slot
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kblocks = (K + 63) / 64;
+    const int n_tiles = total_tiles / m_tiles;
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             tc::mbar_init(&full_bar[s], 1);
@@ -289,7 +293,14 @@ __global__ void __launch_bounds__(192) gemm_bf16_persistent_kernel(const __grid_
             long it = 0;                               // k-blocks issued so far, over all tiles of this CTA
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                int w_row0 = (tile % m_tiles) * 128, n0 = (tile / m_tiles) * BN;
+                int w_row0 = (tile % m_tiles) * 128, n0 = (int)((tile / m_tiles + (unsigned)ep.tile_rot) % n_tiles) * BN;
+                if (ep.ag != nullptr) {
+                    // the rows of this token tile come from one rank; its stores are complete once its arrival counter
+                    // here has reached the target left by the preceding gather kernel
+                    const TpSeq* g = ep.ag;
+                    const int owner = n0 / g->shard;
+                    if (owner < g->size && !tp_wait_counter(g->ag_arrive[g->rank] + owner, *g->ag_target)) atomicExch(status, 4);
+                }
                 if (ep.groups != nullptr) {            // grouped mode: the token tile comes from the device-built list
                     const int* gt = ep.groups + 3 * (tile / m_tiles);
                     if (gt[0] < 0) continue;
@@ -341,7 +352,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_persistent_kernel(const __grid_
         const int q = warp & 3;
         int j = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-            int n0 = (tile / m_tiles) * BN, t_end = ep.T, group = 0;
+            int n0 = (int)((tile / m_tiles + (unsigned)ep.tile_rot) % n_tiles) * BN, t_end = ep.T, group = 0;
             if (ep.groups != nullptr) {
                 const int* gt = ep.groups + 3 * (tile / m_tiles);
                 group = gt[0];
@@ -355,17 +366,68 @@ __global__ void __launch_bounds__(192) gemm_bf16_persistent_kernel(const __grid_
             const int n = m0 + q * 32 + lane;
             if (!tc::mbar_wait(&acc_full[buf], aph)) { atomicExch(status, 3); break; }
             tc::fence_after_sync();
-            const float bias = (ep.bias && n < ep.N) ? ep.bias[(long)group * ep.N + n] : 0.f;
+            const float bias = (ep.bias && n < ep.N && (ep.rs == nullptr || ep.rs->rank == 0)) ? ep.bias[(long)group * ep.N + n] : 0.f;
+            if (ep.rs == nullptr) {
 #pragma unroll 1
-            for (int c = 0; c < BN / 16; ++c) {
-                uint32_t r[16];
-                tc::tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * BN + c * 16, r);
-                tc::tmem_ld_wait();
-                if (n < ep.N) gemm_store16(ep, r, n, n0 + c * 16, t_end, bias);
+                for (int c = 0; c < BN / 16; ++c) {
+                    uint32_t r[16];
+                    tc::tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * BN + c * 16, r);
+                    tc::tmem_ld_wait();
+                    if (n < ep.N) gemm_store16(ep, r, n, n0 + c * 16, t_end, bias);
+                }
+                tc::fence_before_sync();              // this warp's reads of the accumulator are complete
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
+            } else {
+                // GEMM -> reduce-scatter: this rank's slot of the token owner's accumulator, over NVLink.  Rows past T
+                // are written too (zeros from the zero-filled X tile) so the owner never reads a stale slot row.
+                const TpSeq* g = ep.rs;
+                const int owner = n0 / g->shard;                    // a token tile never straddles two shards
+                bf16* rs_dst = nullptr;
+                if (owner < g->size)
+                    rs_dst = g->acc[owner] + ((long)(*g->rs_phase & 1u) * g->size + g->rank) * g->shard * g->ld -
+                             (long)owner * g->shard * g->ld;
+                const int et = threadIdx.x - 64;                    // 0..127 among the epilogue threads
+#pragma unroll 1
+                for (int c = 0; c < BN / 16; ++c) {
+                    uint32_t r[16];
+                    tc::tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)buf * BN + c * 16, r);
+                    tc::tmem_ld_wait();
+                    bf16* st = rs_stage + (c & 1) * (16 * 128);
+#pragma unroll
+                    for (int jj = 0; jj < 16; ++jj)
+                        st[jj * 128 + q * 32 + lane] = f2bf(__uint_as_float(r[jj]) + (n0 + c * 16 + jj < ep.T ? bias : 0.f));
+                    asm volatile("bar.sync 1, 128;" ::: "memory");  // the 16 x 128 chunk is complete
+                    if (rs_dst != nullptr) {
+                        // thread -> tokens et / 16 and et / 16 + 8, eight features: 16 threads cover one 256-byte row
+#pragma unroll
+                        for (int rr = 0; rr < 2; ++rr) {
+                            const int tok = (et >> 4) + rr * 8, f0 = (et & 15) * 8;
+                            const int nn = m0 + f0;
+                            if (nn < ep.N) {                        // N is a multiple of 8 (checked by the host)
+                                const uint4 v = *reinterpret_cast<const uint4*>(st + tok * 128 + f0);
+                                *reinterpret_cast<uint4*>(rs_dst + (long)(n0 + c * 16 + tok) * g->ld + nn) = v;
+                            }
+                        }
+                    }
+                    // the other buffer is written next; this one again two chunks on, after the next barrier
+                }
+                tc::fence_before_sync();
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
+                __threadfence_system();                             // this thread's peer stores are visible before the arrival
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (et == 0) {
+                    if (owner < g->size) red_release_inc_sys(g->rs_arrive[owner]);
+                    const unsigned done = atomicAdd(g->ticket, 1u);
+                    if (done == (unsigned)total_tiles - 1u) {
+                        // every owner receives (feature tiles) x (token tiles per shard) arrivals from each rank
+                        *g->ticket = 0;
+                        __threadfence();
+                        *g->rs_target += (unsigned)g->size * (unsigned)m_tiles * (unsigned)(g->shard / BN);
+                    }
+                }
             }
-            tc::fence_before_sync();                  // this warp's reads of the accumulator are complete
-            __syncwarp();
-            if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
             ++j;
         }
     }
@@ -381,13 +443,16 @@ template <int BN, int STAGES>
 static int launch_gemm_persistent(const CUtensorMap& tw, const CUtensorMap& tx, const GemmEpi& ep, int K, int sms, int* status,
                                   cudaStream_t s) {
     using L = GemmSmem<BN, STAGES>;
-    constexpr int SMEM = L::TOTAL + 32;               // two more barrier pairs than the one-tile kernel
+    constexpr int SMEM = L::TOTAL + 256 + 2 * 16 * 128 * 2;      // more barriers than the one-tile kernel + the reduce-scatter staging rows
     static bool configured = false;
     if (!configured) {
         TSB_CHECK_CUDA(cudaFuncSetAttribute(gemm_bf16_persistent_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
         configured = true;
     }
-    const int m_tiles = (ep.N + 127) / 128, n_tiles = (ep.T + BN - 1) / BN, total = m_tiles * n_tiles;
+    // with a reduce-scatter epilogue the tiles also cover the padding rows of the last shard, so that every owner sees
+    // the same number of arrivals
+    const int t_cover = ep.rs != nullptr ? ep.rs_rows : ep.T;
+    const int m_tiles = (ep.N + 127) / 128, n_tiles = (t_cover + BN - 1) / BN, total = m_tiles * n_tiles;
     const int grid = total < sms ? total : sms;
     TSB_CHECK_CUDA(tsb_launch(gemm_bf16_persistent_kernel<BN, STAGES>, dim3(grid), dim3(192), (size_t)SMEM, s, tw, tx, ep, K, m_tiles,
                               total, status));
@@ -521,11 +586,11 @@ extern "C" int tsb_gemm_bf16_tp(const void* W, long ldw, const void* X, long ldx
     cudaStream_t s = (cudaStream_t)stream;
     // plain GEMMs with more tiles than SMs: the persistent kernel (epilogue of a tile under the next tile's main loop)
     static const int persist_mode = []() { const char* e = getenv("TSB_GEMM_PERSISTENT"); return e ? atoi(e) : 1; }();
-    if (!rs && !ag && !wide && persist_mode != 0 && (bn == 256 || bn == 128)) {
+    if (!wide && persist_mode != 0 && (bn == 256 || bn == 128) && !two_per_sm && (!rs || N % 8 == 0)) {
         int dev = 0, sms = 148;
         if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        const long tiles = (long)((N + 127) / 128) * ((T + bn - 1) / bn);
-        if (tiles > sms)
+        const long tiles = (long)((N + 127) / 128) * (((rs ? shard * size : T) + bn - 1) / bn);
+        if (tiles > sms || persist_mode == 2)
             return bn == 256 ? launch_gemm_persistent<256, 4>(tw, tx, ep, K, sms, status, s)
                              : launch_gemm_persistent<128, 6>(tw, tx, ep, K, sms, status, s);
     }

@@ -20,8 +20,8 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _run_ranks(n, *model_paths):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+def _run_ranks(n, *model_paths, **extra_env):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **extra_env)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
            "--master-port", str(_free_port()), os.path.join(HERE, "tp_worker.py"), *model_paths]
     p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
@@ -200,3 +200,14 @@ def test_mailbox_all_reduce_in_gemma_qwen35_nemotron(n, tmp_path_factory):
         assert r["fused_vs_nccl"] <= 1e-2 * max(1.0, r["scale"]), r
         assert r["fused_vs_single"] <= 3e-2 * max(1.0, r["scale"]), r
         assert r["graph_tokens"] == r["eager_tokens"], r
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_sequence_parallel_prefill_through_the_persistent_gemm(n, kv8_model_path, moe_model_path):
+    """The same checks with every GEMM forced onto the persistent kernel (TSB_GEMM_PERSISTENT=2; by default only GEMMs
+    with more tiles than SMs take it, which these small models never have): all-gather wait in its producer, reduce-
+    scatter epilogue with whole-row peer stores, arrival counting per tile."""
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+    for r in _run_ranks(n, kv8_model_path, moe_model_path, TSB_GEMM_PERSISTENT="2"):
+        check_result(r)
