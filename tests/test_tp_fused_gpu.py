@@ -197,7 +197,9 @@ def test_mailbox_all_reduce_in_gemma_qwen35_nemotron(n, tmp_path_factory):
     assert p.returncode == 0 and len(res) == 3, f"rc={p.returncode}\nstdout:\n{p.stdout[-3000:]}\nstderr:\n{p.stderr[-3000:]}"
     for r in res:
         assert r["status"] == 0 and r["exchanges"] > 0, r
-        assert r["fused_vs_nccl"] <= 1e-2 * max(1.0, r["scale"]), r
+        # two ranks: a + b in either order, the same bits as NCCL; more ranks: rank order against NCCL's order, then int8
+        # re-quantisation of the activations (Gemma's sandwich norms amplify the last bit the most)
+        assert r["fused_vs_nccl"] <= (1e-2 if n == 2 else 2.5e-2) * max(1.0, r["scale"]), r
         assert r["fused_vs_single"] <= 3e-2 * max(1.0, r["scale"]), r
         assert r["graph_tokens"] == r["eager_tokens"], r
 

@@ -257,7 +257,8 @@ def check_model(path, comm):
     nccl = run(model)
     model.reset_kv_cache()
     nccl_long = model.forward(long_prompt).float().clone()
-    nccl_next = model.forward([int(nccl_long.argmax())]).float().clone()
+    # the same token as the fused run took (random-init logits are nearly flat: each path's own arg-max can differ)
+    nccl_next = model.forward([int(seq_logits.argmax())]).float().clone()
     res = {"world": world, "arch": model.arch, "status": status, "exchanges": exchanges,
            "fused_vs_nccl": float((fused - nccl).abs().max()), "graph_tokens": graph_tokens, "eager_tokens": eager_tokens,
            "seq_status": seq_status, "seq_vs_nccl": float((seq_logits - nccl_long).abs().max()),
