@@ -250,7 +250,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(192) gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap tmW,
                                                                    const __grid_constant__ CUtensorMap tmX, GemmEpi ep, int K,
-                                                                   int m_tiles, int total_tiles, int* status) {
+                                                                   int m_tiles, int total_tiles, int n_fast, int* status) {
     using L = GemmSmem<BN, STAGES>;
     constexpr int TMEM_COLS = 2 * BN;
     static_assert(TMEM_COLS >= 32 && TMEM_COLS <= 512, "two accumulators must fit tensor memory");
@@ -267,6 +267,11 @@ __global__ void __launch_bounds__(192) gemm_bf16_persistent_kernel(const __grid_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kblocks = (K + 63) / 64;
     const int n_tiles = total_tiles / m_tiles;
+    // Tile order.  Feature tile fastest: the CTAs that run together share one token slab.  Token tile fastest (plain
+    // GEMMs whose weight matrix is the larger operand): the CTAs that run together share a few weight tiles, so the
+    // weights come from DRAM once instead of once per token tile.
+    auto tile_m = [&](int tile) { return n_fast ? tile / n_tiles : tile % m_tiles; };
+    auto tile_n = [&](int tile) { return n_fast ? tile % n_tiles : tile / m_tiles; };
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             tc::mbar_init(&full_bar[s], 1);
@@ -293,7 +298,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_persistent_kernel(const __grid_
             long it = 0;                               // k-blocks issued so far, over all tiles of this CTA
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                int w_row0 = (tile % m_tiles) * 128, n0 = (int)((tile / m_tiles + (unsigned)ep.tile_rot) % n_tiles) * BN;
+                int w_row0 = tile_m(tile) * 128, n0 = (int)((tile_n(tile) + (unsigned)ep.tile_rot) % n_tiles) * BN;
                 if (ep.ag != nullptr) {
                     // the rows of this token tile come from one rank; its stores are complete once its arrival counter
                     // here has reached the target left by the preceding gather kernel
@@ -302,7 +307,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_persistent_kernel(const __grid_
                     if (owner < g->size && !tp_wait_counter(g->ag_arrive[g->rank] + owner, *g->ag_target)) atomicExch(status, 4);
                 }
                 if (ep.groups != nullptr) {            // grouped mode: the token tile comes from the device-built list
-                    const int* gt = ep.groups + 3 * (tile / m_tiles);
+                    const int* gt = ep.groups + 3 * tile_n(tile);
                     if (gt[0] < 0) continue;
                     w_row0 += gt[0] * ep.N;
                     n0 = gt[1];
@@ -326,7 +331,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_persistent_kernel(const __grid_
             int j = 0;                                 // tiles done by this CTA
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                if (ep.groups != nullptr && ep.groups[3 * (tile / m_tiles)] < 0) continue;
+                if (ep.groups != nullptr && ep.groups[3 * tile_n(tile)] < 0) continue;
                 const int buf = j & 1;
                 const uint32_t aph = (uint32_t)(j >> 1) & 1u;
                 if (!tc::mbar_wait(&acc_empty[buf], aph ^ 1)) { atomicExch(status, 5); ok = false; break; }
@@ -352,9 +357,9 @@ __global__ void __launch_bounds__(192) gemm_bf16_persistent_kernel(const __grid_
         const int q = warp & 3;
         int j = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-            int n0 = (int)((tile / m_tiles + (unsigned)ep.tile_rot) % n_tiles) * BN, t_end = ep.T, group = 0;
+            int n0 = (int)((tile_n(tile) + (unsigned)ep.tile_rot) % n_tiles) * BN, t_end = ep.T, group = 0;
             if (ep.groups != nullptr) {
-                const int* gt = ep.groups + 3 * (tile / m_tiles);
+                const int* gt = ep.groups + 3 * tile_n(tile);
                 group = gt[0];
                 if (group < 0) continue;
                 n0 = gt[1];
@@ -362,7 +367,7 @@ __global__ void __launch_bounds__(192) gemm_bf16_persistent_kernel(const __grid_
             }
             const int buf = j & 1;
             const uint32_t aph = (uint32_t)(j >> 1) & 1u;
-            const int m0 = (tile % m_tiles) * 128;
+            const int m0 = tile_m(tile) * 128;
             const int n = m0 + q * 32 + lane;
             if (!tc::mbar_wait(&acc_full[buf], aph)) { atomicExch(status, 3); break; }
             tc::fence_after_sync();
@@ -454,8 +459,11 @@ static int launch_gemm_persistent(const CUtensorMap& tw, const CUtensorMap& tx, 
     const int t_cover = ep.rs != nullptr ? ep.rs_rows : ep.T;
     const int m_tiles = (ep.N + 127) / 128, n_tiles = (t_cover + BN - 1) / BN, total = m_tiles * n_tiles;
     const int grid = total < sms ? total : sms;
+    static const int order_mode = []() { const char* e = getenv("TSB_GEMM_ORDER"); return e ? atoi(e) : -1; }();
+    int n_fast = (ep.rs == nullptr && ep.ag == nullptr && ep.groups == nullptr && ep.N > t_cover) ? 1 : 0;
+    if (order_mode >= 0 && ep.rs == nullptr && ep.ag == nullptr) n_fast = order_mode;
     TSB_CHECK_CUDA(tsb_launch(gemm_bf16_persistent_kernel<BN, STAGES>, dim3(grid), dim3(192), (size_t)SMEM, s, tw, tx, ep, K, m_tiles,
-                              total, status));
+                              total, n_fast, status));
     return TSB_OK;
 }
 
