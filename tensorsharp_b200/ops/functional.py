@@ -674,7 +674,11 @@ def mamba2(xbc: torch.Tensor, dt: torch.Tensor, dt_bias, A, D, state: torch.Tens
     outs = []
     slots = batch.seq_slots.tolist()
     scan = ref.mamba2_chunked if chunked else ref.mamba2_recurrent
+    kw = {}
+    if chunked and xbc.is_cuda and os.environ.get("TSB_MAMBA_CARRY_KERNEL", "1") != "0" and _k().gdn_chunk_carry_supported(N, P, 64) \
+            and state.dtype == torch.float32:
+        kw["carry"] = _k().gdn_chunk_carry          # the state update has the delta rule's shape with nothing to correct
     for b in range(batch.B):
         q0, q1 = batch.h_cu_q[b], batch.h_cu_q[b + 1]
-        outs.append(scan(xbc[q0:q1], dt[q0:q1], dt_bias, A, D, state[slots[b]], H=H, P=P, G=G, N=N))
+        outs.append(scan(xbc[q0:q1], dt[q0:q1], dt_bias, A, D, state[slots[b]], H=H, P=P, G=G, N=N, **kw))
     return torch.cat(outs, 0)

@@ -274,10 +274,11 @@ def mamba2_recurrent(xbc, dt, dt_bias, A, D, state, *, H, P, G, N):
     return y
 
 
-def mamba2_chunked(xbc, dt, dt_bias, A, D, state, *, H, P, G, N, chunk: int = 64):
+def mamba2_chunked(xbc, dt, dt_bias, A, D, state, *, H, P, G, N, chunk: int = 64, carry=None):
     """:func:`mamba2_recurrent` in chunked (state-space duality) form: inside a chunk the outputs are one masked
     matrix product ``(decay * C B^T) (dt * x)``, the state is carried from chunk to chunk by two small products.
-    One sequence; ``state`` [H, P, N] is updated in place; runs on the inputs' device.  Returns y [n, H*P]."""
+    One sequence; ``state`` [H, P, N] is updated in place; runs on the inputs' device.  ``carry`` replaces the loop
+    over the chunks (a kernel on CUDA).  Returns y [n, H*P]."""
     n = xbc.shape[0]
     dev = xbc.device
     Cn = chunk
@@ -302,13 +303,21 @@ def mamba2_chunked(xbc, dt, dt_bias, A, D, state, *, H, P, G, N, chunk: int = 64
     Cd = Cc * torch.exp(cum).unsqueeze(-1)                                    # reads of the incoming state
     Xd = X * torch.exp(cum[..., -1:] - cum).unsqueeze(-1)                     # writes that survive to the chunk's end
     gamma = torch.exp(cum[..., -1])
-    S = state.float()                                                         # [H, P, N]
-    outs = []
-    for c in range(nc):
-        outs.append(Y_in[:, c] + Cd[:, c] @ S.transpose(-1, -2))              # [H, Cn, P]
-        S = gamma[:, c].view(H, 1, 1) * S + Xd[:, c].transpose(-1, -2) @ Bc[:, c]
-    state.copy_(S)
-    y = torch.stack(outs, 1).reshape(H, nc * Cn, P)[:, :n].transpose(0, 1)    # [n, H, P]
+    if carry is not None:
+        # the chunk-carry kernel of the delta rule (csrc/gdn_chunk.cu) with nothing to correct (W = 0) and no intra-chunk
+        # term of its own (P = 0): out = Cd S^T, S <- gamma S + Xd^T B; ``state`` [H, P, N] is updated in place
+        zw = torch.zeros((H, nc, Cn, N), dtype=torch.float32, device=dev)
+        zp = torch.zeros((H, nc, Cn, Cn), dtype=torch.float32, device=dev)
+        y = Y_in + carry(Xd, zw, Cd, Bc, zp, gamma, state)
+    else:
+        S = state.float()                                                     # [H, P, N]
+        outs = []
+        for c in range(nc):
+            outs.append(Y_in[:, c] + Cd[:, c] @ S.transpose(-1, -2))          # [H, Cn, P]
+            S = gamma[:, c].view(H, 1, 1) * S + Xd[:, c].transpose(-1, -2) @ Bc[:, c]
+        state.copy_(S)
+        y = torch.stack(outs, 1)
+    y = y.reshape(H, nc * Cn, P)[:, :n].transpose(0, 1)                        # [n, H, P]
     if D is not None:
         y = y + D.float().view(1, H, 1) * x
     return y.reshape(n, H * P)

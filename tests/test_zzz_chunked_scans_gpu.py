@@ -52,7 +52,12 @@ def test_chunked_routes_match_the_scan_kernels(monkeypatch):
         st = s0.clone()
         outs[mode] = F.mamba2(xbc, dt, dtb, A, D, st, _batch(lens, dev), H=H, P=P, G=G, N=N)
         states[mode] = st
-    assert _rel(outs["1"], outs["0"]) < 1e-3 and _rel(states["1"], states["0"]) < 1e-3
+    # the chunk loop runs in the chunk-carry kernel (tf32 operands, f32 accumulation and state)
+    assert _rel(outs["1"], outs["0"]) < 5e-3 and _rel(states["1"], states["0"]) < 5e-3, (_rel(outs["1"], outs["0"]), _rel(states["1"], states["0"]))
+    monkeypatch.setenv("TSB_MAMBA_CARRY_KERNEL", "0")
+    st = s0.clone()
+    plain = F.mamba2(xbc, dt, dtb, A, D, st, _batch(lens, dev), H=H, P=P, G=G, N=N)
+    assert _rel(plain, outs["0"]) < 1e-3 and _rel(st, states["0"]) < 1e-3
 
 
 @pytest.mark.parametrize("Hk,Hv,Dk,Dv", [(2, 4, 128, 128), (1, 2, 64, 96)])
