@@ -57,8 +57,11 @@ __device__ __forceinline__ long kv_slot(const AttnArgs& a, int b, int j) {
 // group size is 1, 2, 4 or 8; other group sizes and head size 512 take several).  Lane = token for QK^T,
 // lane = dim slice for PV.
 // ------------------------------------------------------------------------------------------
-template <int DH, int G>
-__global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
+// LEAN: the variant for batches.  With one sequence a CTA has an SM to itself and spends registers on having every K and
+// V row of its chunk in flight at once; with many sequences there are several CTAs per SM to hide latency with, so the
+// V rows are fetched eight at a time and the register budget is capped for four CTAs per SM.
+template <int DH, int G, bool LEAN = false>
+__global__ void __launch_bounds__(128, LEAN ? 4 : 1) attn_decode_kernel(AttnArgs a) {
     constexpr int DPL = DH / 32;             // output dims per lane
     pdl_wait();
     pdl_trigger();
@@ -114,7 +117,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnArgs a) {
         // All of this chunk's K rows (one per lane) and, for head sizes up to 128, all of its V rows are
         // requested before anything is used: a CTA has the SM to itself (the grid is about one CTA per SM),
         // so registers are free and the chunk costs one DRAM round trip instead of six.
-        constexpr bool PREFETCH_V = DPL <= 4;
+        constexpr bool PREFETCH_V = DPL <= 4 && !LEAN;
         constexpr int KCH = DH / 8;
         uint4 kreg[KCH <= 16 ? KCH : 1];
         uint2 vreg[PREFETCH_V ? 32 : 1];
@@ -356,6 +359,17 @@ template <int DH>
 static int launch_decode_g(const AttnArgs& a, cudaStream_t s) {
     const int G = attn_decode_chunk(a.Hq / a.Hkv, DH);
     dim3 grid(a.splits, a.Hkv * ((a.Hq / a.Hkv) / G), a.B);
+    if constexpr (DH <= 128) {
+        // more CTAs than four per SM: the lean variant (batches)
+        if ((long)grid.x * grid.y * grid.z > 4L * 148) {
+            switch (G) {
+            case 1: return tsb_launch(attn_decode_kernel<DH, 1, true>, grid, dim3(128), 0, s, a) == cudaSuccess ? TSB_OK : TSB_ERR_CUDA;
+            case 2: return tsb_launch(attn_decode_kernel<DH, 2, true>, grid, dim3(128), 0, s, a) == cudaSuccess ? TSB_OK : TSB_ERR_CUDA;
+            case 4: return tsb_launch(attn_decode_kernel<DH, 4, true>, grid, dim3(128), 0, s, a) == cudaSuccess ? TSB_OK : TSB_ERR_CUDA;
+            default: return tsb_launch(attn_decode_kernel<DH, 8, true>, grid, dim3(128), 0, s, a) == cudaSuccess ? TSB_OK : TSB_ERR_CUDA;
+            }
+        }
+    }
     switch (G) {
     case 1: if (tsb_launch(attn_decode_kernel<DH, 1>, grid, dim3(128), 0, s, a) != cudaSuccess) return TSB_ERR_CUDA; break;
     case 2: if (tsb_launch(attn_decode_kernel<DH, 2>, grid, dim3(128), 0, s, a) != cudaSuccess) return TSB_ERR_CUDA; break;

@@ -38,6 +38,11 @@ struct GemmEpi {
     // by group, and token tile y of the grid is described by groups[3 * y .. 3 * y + 2] = {matrix index or -1 for an
     // unused tile, first row, end row}.  The list is built on the device, so the host never learns the group sizes.
     const int* groups;
+    // Split-K (one-tile-per-CTA kernel, few tiles and a long K: decode batches of 9 to 64 rows): blockIdx.z takes a
+    // range of k-blocks and stores its raw partial tile into ws[z][t][n]; splitk_reduce_kernel adds the parts in order
+    // with bias and residual.  Null for an ordinary launch.
+    float* ws;
+    int kb_per_split;
 };
 
 // Epilogue of one thread for 16 consecutive tokens of its feature n: out[t, n] = acc + bias (+ residual[t, n]).
@@ -102,7 +107,9 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
     int t_end = ep.T;                      // tokens at or past this row are not stored
     int w_row0 = m0;                       // row of the (stacked) weight matrix where this tile's features start
     bool active = true;
-    const int kblocks = (K + 63) / 64;
+    const int kb_all = (K + 63) / 64;
+    const int kb_first = ep.ws != nullptr ? (int)blockIdx.z * ep.kb_per_split : 0;
+    const int kblocks = ep.ws != nullptr ? min(kb_all - kb_first, ep.kb_per_split) : kb_all;     // this CTA's share (>= 1)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -149,8 +156,8 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                 if (!tc::mbar_wait(&empty_bar[s], ph ^ 1)) { atomicExch(status, 1); break; }
                 unsigned char* a = smem + s * L::STAGE_BYTES;
                 tc::mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
-                tc::tma_load_2d(a, &tmW, &full_bar[s], kb * 64, w_row0);
-                tc::tma_load_2d(a + L::A_BYTES, &tmX, &full_bar[s], kb * 64, n0);
+                tc::tma_load_2d(a, &tmW, &full_bar[s], (kb_first + kb) * 64, w_row0);
+                tc::tma_load_2d(a + L::A_BYTES, &tmX, &full_bar[s], (kb_first + kb) * 64, n0);
             }
         }
         __syncwarp();
@@ -210,6 +217,15 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
                             rs_dst[(long)t * ep.rs->ld + n] = f2bf(__uint_as_float(r[j]) + (t < ep.T ? bias : 0.f));
                         }
                     }
+                } else if (ep.ws != nullptr) {
+                    if (n < ep.N) {
+                        float* part = ep.ws + (long)blockIdx.z * ep.T * ep.N;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int t = n0 + c * 16 + j;
+                            if (t < ep.T) part[(long)t * ep.N + n] = __uint_as_float(r[j]);
+                        }
+                    }
                 } else if (n < ep.N) {
                     gemm_store16(ep, r, n, n0 + c * 16, t_end, bias);
                 }
@@ -237,6 +253,25 @@ __global__ void __launch_bounds__(192) gemm_bf16_kernel(const __grid_constant__ 
             __threadfence();
             *g->rs_target += (unsigned)g->size * gridDim.x * (unsigned)(g->shard / BN);
         }
+    }
+}
+
+// out[t, n] = sum over the splits (in order) of ws[z][t][n] + bias[n] + residual[t, n]
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(GemmEpi ep, int splits) {
+    pdl_wait();
+    pdl_trigger();
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long)ep.T * ep.N) return;
+    const int t = (int)(i / ep.N), n = (int)(i % ep.N);
+    float v = ep.bias ? ep.bias[n] : 0.f;
+    for (int z = 0; z < splits; ++z) v += ep.ws[((long)z * ep.T + t) * ep.N + n];
+    const long o = (long)t * ep.ldo + n;
+    if (ep.out_f32) {
+        if (ep.residual) v += reinterpret_cast<const float*>(ep.residual)[o];
+        reinterpret_cast<float*>(ep.out)[o] = v;
+    } else {
+        if (ep.residual) v += bf2f(reinterpret_cast<const bf16*>(ep.residual)[o]);
+        reinterpret_cast<bf16*>(ep.out)[o] = f2bf(v);
     }
 }
 
@@ -517,30 +552,51 @@ static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmE
     // with a reduce-scatter epilogue the grid also covers the padding rows of the last shard, so
     // that every owner sees the same number of arrivals
     const int t_cover = ep.rs != nullptr ? ep.rs_rows : ep.T;
-    dim3 grid((ep.N + 128 * MT - 1) / (128 * MT), (t_cover + BN - 1) / BN);
+    const int kb_all = (K + 63) / 64;
+    const int splits = ep.ws != nullptr ? (kb_all + ep.kb_per_split - 1) / ep.kb_per_split : 1;
+    dim3 grid((ep.N + 128 * MT - 1) / (128 * MT), (t_cover + BN - 1) / BN, splits);
     TSB_CHECK_CUDA(tsb_launch(gemm_bf16_kernel<BN, STAGES, MT>, grid, dim3(192), (size_t)L::TOTAL, s, tw, tx, ep, K, status));
+    if (ep.ws != nullptr) {
+        const long n = (long)ep.T * ep.N;
+        TSB_CHECK_CUDA(tsb_launch(splitk_reduce_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, ep, splits));
+    }
     return TSB_OK;
 }
 
 // W: [N, K] bf16 row-major (ldw elements per row); X: [T, K] bf16 (ldx); out: [T, ldo].
 // `status` is a device int the kernel sets non-zero if one of its bounded waits gave up.
-extern "C" int tsb_gemm_bf16_tp(const void* W, long ldw, const void* X, long ldx, void* out, long ldo, int out_f32,
-                                const float* bias, const void* residual, int T, int N, int K, const void* rs,
-                                const void* ag, int shard, int size, int rank, int* status, void* stream);
+static int gemm_bf16_impl(const void* W, long ldw, const void* X, long ldx, void* out, long ldo, int out_f32,
+                          const float* bias, const void* residual, int T, int N, int K, const void* rs, const void* ag, int shard,
+                          int size, int rank, int* status, void* stream, void* splitk_ws, long splitk_ws_bytes);
 
 extern "C" int tsb_gemm_bf16(const void* W, long ldw, const void* X, long ldx, void* out, long ldo, int out_f32,
                              const float* bias, const void* residual, int T, int N, int K, int* status, void* stream) {
-    return tsb_gemm_bf16_tp(W, ldw, X, ldx, out, ldo, out_f32, bias, residual, T, N, K, nullptr, nullptr, 0, 1, 0, status,
-                            stream);
+    return gemm_bf16_impl(W, ldw, X, ldx, out, ldo, out_f32, bias, residual, T, N, K, nullptr, nullptr, 0, 1, 0, status, stream,
+                          nullptr, 0);
+}
+
+// The plain GEMM with a caller-provided float32 workspace, which lets launches with few tiles and a long K split K.
+extern "C" int tsb_gemm_bf16_ws(const void* W, long ldw, const void* X, long ldx, void* out, long ldo, int out_f32,
+                                const float* bias, const void* residual, int T, int N, int K, int* status, void* stream,
+                                void* ws, long ws_bytes) {
+    return gemm_bf16_impl(W, ldw, X, ldx, out, ldo, out_f32, bias, residual, T, N, K, nullptr, nullptr, 0, 1, 0, status, stream,
+                          ws, ws_bytes);
+}
+
+extern "C" int tsb_gemm_bf16_tp(const void* W, long ldw, const void* X, long ldx, void* out, long ldo, int out_f32,
+                                const float* bias, const void* residual, int T, int N, int K, const void* rs,
+                                const void* ag, int shard, int size, int rank, int* status, void* stream) {
+    return gemm_bf16_impl(W, ldw, X, ldx, out, ldo, out_f32, bias, residual, T, N, K, rs, ag, shard, size, rank, status, stream,
+                          nullptr, 0);
 }
 
 // The GEMM with the tensor-parallel prefill hooks: `rs` (device TpSeq*) sends the result to the token
 // owners' accumulators instead of `out`; `ag` makes the producer wait for X's shards.  `shard` and
 // `size` repeat the descriptor's values for the host-side launch arithmetic; the token tile is
 // 128 rows so that it divides the shard.
-extern "C" int tsb_gemm_bf16_tp(const void* W, long ldw, const void* X, long ldx, void* out, long ldo, int out_f32,
-                                const float* bias, const void* residual, int T, int N, int K, const void* rs,
-                                const void* ag, int shard, int size, int rank, int* status, void* stream) {
+static int gemm_bf16_impl(const void* W, long ldw, const void* X, long ldx, void* out, long ldo, int out_f32,
+                          const float* bias, const void* residual, int T, int N, int K, const void* rs, const void* ag, int shard,
+                          int size, int rank, int* status, void* stream, void* splitk_ws, long splitk_ws_bytes) {
     TSB_CHECK_ARG(T >= 0 && N > 0 && K > 0, "gemm_bf16: bad shape T=%d N=%d K=%d", T, N, K);
     TSB_CHECK_ARG((!rs && !ag) || (shard > 0 && shard % 128 == 0 && size >= 1), "gemm_bf16: shard=%d must be a multiple of 128", shard);
     TSB_CHECK_ARG(!rs || !residual, "gemm_bf16: reduce-scatter mode takes no residual");
@@ -592,6 +648,19 @@ extern "C" int tsb_gemm_bf16_tp(const void* W, long ldw, const void* X, long ldx
     if (rs) rot = ((rank + 1) % size) * (shard / bn);
     GemmEpi ep{out, bias, residual, ldo, T, N, out_f32, (const TpSeq*)rs, (const TpSeq*)ag, shard * size, rot};
     cudaStream_t s = (cudaStream_t)stream;
+    // Few tiles and a long K (decode batches): split K over CTAs so that the weight stream uses the whole GPU.
+    if (!rs && !ag && splitk_ws != nullptr && bn <= 64) {
+        int dev = 0, sms = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const int tiles = ((N + 127) / 128) * ((T + bn - 1) / bn), kb_all = (K + 63) / 64;
+        int want = sms / (tiles > 0 ? tiles : 1);
+        if (want > 8) want = 8;
+        if (want > kb_all / 4) want = kb_all / 4;
+        if (want >= 2 && (long)want * T * N * 4 <= splitk_ws_bytes) {
+            ep.kb_per_split = (kb_all + want - 1) / want;
+            ep.ws = (float*)splitk_ws;
+        }
+    }
     // plain GEMMs with more tiles than SMs: the persistent kernel (epilogue of a tile under the next tile's main loop)
     static const int persist_mode = []() { const char* e = getenv("TSB_GEMM_PERSISTENT"); return e ? atoi(e) : 1; }();
     if (!wide && persist_mode != 0 && (bn == 256 || bn == 128) && !two_per_sm && (!rs || N % 8 == 0)) {

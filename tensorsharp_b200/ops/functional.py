@@ -22,7 +22,10 @@ import torch
 from ..quant.qweight import QuantWeight
 from . import reference as ref
 
-GEMV_MAX_M = 16   # token count up to which the weight-streaming GEMV beats dequant + tensor-core GEMM
+GEMV_MAX_M = 16   # "small batch": token count up to which the models take their decode-style paths (int8 activations, mailbox exchanges)
+# Dense projections of 9 to 16 rows go to the tensor-core GEMM on the bf16 weight copy all the same: measured on the
+# Qwen3-4B shape at batch 16, 10.95 ms per step with the weight-streaming GEMVs against 8.15 ms (TSB_GEMV_MAX_M moves it)
+DENSE_GEMV_MAX_M = min(GEMV_MAX_M, int(os.environ.get("TSB_GEMV_MAX_M", "8")))
 
 
 @dataclass
@@ -240,7 +243,7 @@ def linear(a: Act, w: QuantWeight, *, bias: Optional[torch.Tensor] = None, resid
             y = y + residual.float()
         return y.to(out_dtype) if out_dtype != torch.float32 else y
     k = _k()
-    if T <= GEMV_MAX_M:
+    if T <= DENSE_GEMV_MAX_M or (T <= GEMV_MAX_M and (a.b is None or w.experts != 1 or w.K % 8)):
         if w.uses_q8_activations:
             _ensure_q8(a)
             return k.gemv(w, xq=a.q, xds=a.ds, M=T, out_dtype=out_dtype, bias=bias, residual=residual, act=act)
@@ -265,7 +268,7 @@ def linear_multi(a: Act, ws, *, out_dtype=torch.float32):
     type); anything else is the plain sequence of ``linear`` calls."""
     ws = list(ws)
     T = a.T
-    if (ws[0].device.type == "cuda" and T <= GEMV_MAX_M and 2 <= len(ws) <= 3 and all(w.experts == 1 and w.K == ws[0].K for w in ws)
+    if (ws[0].device.type == "cuda" and T <= DENSE_GEMV_MAX_M and 2 <= len(ws) <= 3 and all(w.experts == 1 and w.K == ws[0].K for w in ws)
             and len({w.uses_q8_activations for w in ws}) == 1):
         if ws[0].uses_q8_activations:
             _ensure_q8(a)
@@ -354,7 +357,9 @@ def decode_split_len(batch: Batch, splits: int, window: int) -> int:
 def decode_splits(batch: Batch, Hkv: int, window: int) -> int:
     """Split-KV factor for decode attention: enough CTAs to cover the GPU's 148 SMs."""
     span = batch.max_kv_len if not window else min(batch.max_kv_len, window)
-    want = max(1, (148 * 2) // max(1, batch.B * Hkv))
+    # one sequence: about two CTAs per SM; batches: up to eight (a CTA is 128 threads and latency-bound, and with 16
+    # sequences two splits per (sequence, KV head) left the kernel at a fifth of the memory rate)
+    want = max(1, (148 * (2 if batch.B == 1 else 8)) // max(1, batch.B * Hkv))
     per = int(os.environ.get("TSB_ATTN_SPLIT_LEN", "128"))
     return int(max(1, min(want, (span + per - 1) // per, 64)))
 

@@ -468,6 +468,20 @@ def gemm_status(device) -> torch.Tensor:
     return _status_words[key]
 
 
+_SPLITK_WS: dict = {}
+
+
+def _splitk_workspace(device) -> Optional[torch.Tensor]:
+    """Per-device float32 scratch (16 MB) for the partial tiles of split-K GEMMs; launches on one stream reuse it in order."""
+    if os.environ.get("TSB_GEMM_SPLITK", "1") == "0":
+        return None
+    key = torch.device(device).index or 0
+    ws = _SPLITK_WS.get(key)
+    if ws is None:
+        ws = _SPLITK_WS[key] = torch.empty(4 << 20, dtype=torch.float32, device=device)
+    return ws
+
+
 def gemm_bf16(W: torch.Tensor, X: torch.Tensor, *, out_dtype=torch.bfloat16, bias=None, residual=None,
               out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[T, N] = X[T, K] @ W[N, K]^T on tcgen05 tensor cores (bf16 in, f32 accumulate)."""
@@ -477,10 +491,13 @@ def gemm_bf16(W: torch.Tensor, X: torch.Tensor, *, out_dtype=torch.bfloat16, bia
     T = X.shape[0]
     if out is None:
         out = torch.empty((T, N), dtype=out_dtype, device=X.device)
-    native.check(_lib().tsb_gemm_bf16(_p(W), C.c_long(W.stride(0)), _p(X), C.c_long(X.stride(0)), _p(out),
+    ws = _splitk_workspace(X.device) if T <= 64 else None       # few tiles, long K: the library may split K over CTAs
+    lib = _lib()
+    lib.tsb_gemm_bf16_ws.restype = C.c_int
+    native.check(lib.tsb_gemm_bf16_ws(_p(W), C.c_long(W.stride(0)), _p(X), C.c_long(X.stride(0)), _p(out),
                                       C.c_long(out.stride(0)), C.c_int(out.dtype == torch.float32), _p(bias),
                                       _p(residual), C.c_int(T), C.c_int(N), C.c_int(K), _p(gemm_status(X.device)),
-                                      _stream()), "gemm_bf16")
+                                      _stream(), _p(ws), C.c_long(ws.numel() * 4 if ws is not None else 0)), "gemm_bf16")
     _count(1)
     return out
 

@@ -242,7 +242,8 @@ def test_attn_prefill(Hq, Hkv, Dh, window, sinks, softcap):
 # the last four shapes have more tiles than SMs and take the persistent kernel (two accumulators in tensor memory, the
 # epilogue of a tile under the next tile's main loop): 256- and 128-token tiles, ragged edges, a single k-block
 @pytest.mark.parametrize("T,N,Kd", [(5, 128, 64), (33, 200, 320), (100, 384, 2560), (300, 1000, 512), (2048, 256, 1024),
-                                    (3900, 7744, 320), (4096, 7680, 64), (100, 20480, 256), (520, 19400, 192)])
+                                    (3900, 7744, 320), (4096, 7680, 64), (100, 20480, 256), (520, 19400, 192),
+                                    (16, 2560, 9728), (33, 640, 4096), (9, 256, 8192)])     # the last three: split-K
 def test_gemm_bf16_tcgen05(T, N, Kd):
     torch.manual_seed(9)
     W = (torch.randn(N, Kd, device=DEV) * 0.05).bfloat16()
@@ -442,6 +443,7 @@ def test_moe_prefill_grouped_gemm_matches_per_expert_route(monkeypatch, t, act, 
     w = torch.rand(T, k, device=DEV)
     monkeypatch.setattr(F, "MOE_TILE_MAX_PAIRS", 0)
     monkeypatch.setattr(F, "GEMV_MAX_M", 0)
+    monkeypatch.setattr(F, "DENSE_GEMV_MAX_M", 0)         # the per-expert route multiplies in bf16 too, whatever the group size
     outs = {}
     for mode in ("1", "0"):
         monkeypatch.setenv("TSB_MOE_GROUPED_GEMM", mode)
