@@ -944,7 +944,20 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const MegaAr
                 wv[j][0] = w0.x; wv[j][1] = w0.y; wv[j][2] = w0.z; wv[j][3] = w0.w; wv[j][4] = w1.x; wv[j][5] = w1.y; wv[j][6] = w1.z; wv[j][7] = w1.w;
                 hv[j][0] = h0.x; hv[j][1] = h0.y; hv[j][2] = h0.z; hv[j][3] = h0.w; hv[j][4] = h1.x; hv[j][5] = h1.y; hv[j][6] = h1.z; hv[j][7] = h1.w;
             }
-            if (gather) {
+            if (gather && nblk <= MG_CWARPS) {
+                // one block per warp: the words of two ranks are requested together (the registers the two-block form
+                // uses for its second block), so eight ranks cost four round trips through L2 instead of eight; the
+                // parts are still added in rank order
+                for (int r0 = 0; r0 < R; r0 += 2) {
+                    float v[16];
+                    wait_pairs<8>([&](int u) -> const float2* {
+                        const int r = r0 + (u >> 2);
+                        return (warp < nblk && r < R) ? mine + off + (long)r * D + warp * 256 + lane * 8 + 2 * (u & 3) : nullptr;
+                    }, v, tag, ctl, code);
+#pragma unroll
+                    for (int u = 0; u < 16; ++u) hv[0][u & 7] += v[u];            // (an absent rank reads as 0)
+                }
+            } else if (gather) {
                 for (int r = 0; r < R; ++r) {                              // parts are added in rank order
                     float v[16];
                     wait_pairs<8>([&](int u) -> const float2* {
@@ -954,6 +967,8 @@ __global__ void __launch_bounds__(MG_THREADS, 1) mega_decode_kernel(const MegaAr
 #pragma unroll
                     for (int u = 0; u < 16; ++u) hv[u >> 3][u & 7] += v[u];
                 }
+            }
+            if (gather) {
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
                     const int b = warp + MG_CWARPS * j;
