@@ -329,10 +329,14 @@ __device__ __forceinline__ float q4_block_scale(const QW& w, long row, int kb, i
     return __half2float(reinterpret_cast<const __half*>(w.p1)[row * kb + u]);
 }
 
+#ifndef MOE_MMA_BLOCKS_IN_FLIGHT
+#define MOE_MMA_BLOCKS_IN_FLIGHT 2
+#endif
+
 template <bool GLU, bool MX>
 __global__ void __launch_bounds__(128) gemv_tiles_mma_kernel(TileArgs a) {
     constexpr int S = GLU ? 2 : 1;               // weight row sets per warp: gate (+ up)
-    constexpr int U = 2;                         // k-blocks in flight per iteration
+    constexpr int U = MOE_MMA_BLOCKS_IN_FLIGHT;    // k-blocks in flight per iteration
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int r0 = (blockIdx.x * 4 + (threadIdx.x >> 5)) * 16;
     pdl_wait();
@@ -417,6 +421,116 @@ __global__ void __launch_bounds__(128) gemv_tiles_mma_kernel(TileArgs a) {
     }
 }
 
+// The same tile GEMV with 8-byte weight loads.  In the kernel above a lane reads 4 bytes per block and row, so a warp
+// has about 1 KB of weights in flight and every request uses half a sector; at four CTAs per SM that is a third of the
+// bytes in flight the memory system needs.  Here lane t of a row's four lanes reads half (t & 1) of block ub + (t >> 1):
+// one request covers two whole blocks (a full sector), twice the bytes in flight for the same registers, and the word a
+// lane needs for a block's MMA fragment (word t) comes from lane 2q + (t >> 1) by shuffle.  The scales of a block pair
+// are one 2-byte (MXFP4) or 4-byte (Q4_0) load.  Needs an even number of blocks per row.
+template <bool GLU, bool MX>
+__global__ void __launch_bounds__(128) gemv_tiles_mma_wide_kernel(TileArgs a) {
+    constexpr int S = GLU ? 2 : 1;
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int r0 = (blockIdx.x * 4 + (threadIdx.x >> 5)) * 16;
+    pdl_wait();
+    pdl_trigger();
+    if ((int)blockIdx.y >= a.meta[0] || r0 >= a.n_out) return;
+    const int4 tile = a.tiles[blockIdx.y];
+    const int expert = tile.x, row0 = tile.y, mv = tile.z;
+    const int K = a.w.K, kb = K >> 5;
+    long wr[S][2];
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+        wr[s][0] = (long)expert * a.w.N + s * a.n_out + min(r0 + g, a.n_out - 1);
+        wr[s][1] = (long)expert * a.w.N + s * a.n_out + min(r0 + g + 8, a.n_out - 1);
+    }
+    const bool bact = g < mv;
+    const int8_t* xrow = a.xq + (long)(row0 + (bact ? g : 0)) * K + 4 * t;
+    const int c0 = 2 * t, c1 = 2 * t + 1;
+    const float2* xs0 = a.xds + (long)(row0 + (c0 < mv ? c0 : 0)) * kb;
+    const float2* xs1 = a.xds + (long)(row0 + (c1 < mv ? c1 : 0)) * kb;
+    const int src_base = lane & ~3;
+    float acc[S][4];
+#pragma unroll
+    for (int s = 0; s < S; ++s)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[s][i] = 0.f;
+    for (int u0 = 0; u0 < kb; u0 += 4) {
+        uint2 wv[2][S][2];
+        uint32_t sc[2][S][2];
+        int b0[4], b1[4];
+        float xd0[4], xd1[4];
+#pragma unroll
+        for (int P = 0; P < 2; ++P) {
+            const int ub = min(u0 + 2 * P, kb - 2);                 // (a pair past the end re-reads the last one; not used)
+#pragma unroll
+            for (int s = 0; s < S; ++s)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    wv[P][s][h] = __ldg(reinterpret_cast<const uint2*>(a.w.p0 + wr[s][h] * (K >> 1) + (ub + (t >> 1)) * 16 + (t & 1) * 8));
+                    if (MX) sc[P][s][h] = __ldg(reinterpret_cast<const unsigned short*>(a.w.p1 + wr[s][h] * kb + ub));
+                    else sc[P][s][h] = __ldg(reinterpret_cast<const uint32_t*>(a.w.p1 + 2 * (wr[s][h] * kb + ub)));
+                }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int u = min(u0 + j, kb - 1);
+            b0[j] = bact ? *reinterpret_cast<const int*>(xrow + u * 32) : 0;
+            b1[j] = bact ? *reinterpret_cast<const int*>(xrow + u * 32 + 16) : 0;
+            xd0[j] = xs0[u].x;
+            xd1[j] = xs1[u].x;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int P = j >> 1, q = j & 1;
+            const bool live = u0 + j < kb;                          // uniform over the warp
+            const int src = src_base | (2 * q + (t >> 1));
+#pragma unroll
+            for (int s = 0; s < S; ++s) {
+                uint32_t wd[2];
+                float ws[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t x = __shfl_sync(0xffffffffu, wv[P][s][h].x, src), y = __shfl_sync(0xffffffffu, wv[P][s][h].y, src);
+                    wd[h] = (t & 1) ? y : x;
+                    if (MX) ws[h] = e8m0_half_scale((uint8_t)(sc[P][s][h] >> (8 * q)));
+                    else ws[h] = __half2float(__ushort_as_half((unsigned short)(sc[P][s][h] >> (16 * q))));
+                }
+                if (live) {
+                    int af[4], c[4] = {0, 0, 0, 0};
+                    decode_q4_words<MX>(wd[0], wd[1], af);
+                    mma_s8_16x8x32(c, af, b0[j], b1[j]);
+                    acc[s][0] += ws[0] * xd0[j] * (float)c[0];
+                    acc[s][1] += ws[0] * xd1[j] * (float)c[1];
+                    acc[s][2] += ws[1] * xd0[j] * (float)c[2];
+                    acc[s][3] += ws[1] * xd1[j] * (float)c[3];
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = r0 + g + (i >> 1) * 8, col = 2 * t + (i & 1);
+        if (r >= a.n_out || col >= mv) continue;
+        float v = acc[0][i];
+        if (a.bias) v += a.bias[(long)expert * a.w.N + r];
+        if (GLU) {
+            float up = acc[S - 1][i];
+            if (a.bias) up += a.bias[(long)expert * a.w.N + r + a.n_out];
+            v = act_glu(a.act, v, up);
+        } else if (a.act == ACT_RELU2) {
+            v = fmaxf(v, 0.f);
+            v = v * v;
+        } else if (a.act == ACT_SILU) {
+            v = v / (1.f + __expf(-v));
+        }
+        if (a.row_scale) v *= a.row_scale[row0 + col];
+        const long o = (long)(row0 + col) * a.n_out + r;
+        if (a.out_f32) reinterpret_cast<float*>(a.out)[o] = v;
+        else reinterpret_cast<bf16*>(a.out)[o] = f2bf(v);
+    }
+}
+
 extern "C" int tsb_moe_gemv_tiles(const void* p0, const void* p1, const void* p2, const void* p3, int type, int N, int K,
                                   const void* xq, const void* xds, const void* xb, void* out, const float* bias,
                                   const float* row_scale, const void* tiles, const int* meta, int max_tiles, int out_f32,
@@ -441,6 +555,18 @@ extern "C" int tsb_moe_gemv_tiles(const void* p0, const void* p1, const void* p2
     if (use_mma && (type == TSB_MXFP4 || type == TSB_Q4_0)) {
         dim3 grid((a.n_out + 63) / 64, max_tiles), block(128);
         cudaStream_t st = (cudaStream_t)stream;
+        static const bool wide_loads = []() { const char* e = getenv("TSB_MOE_WIDE_LOADS"); return !e || atoi(e) != 0; }();
+        if (wide_loads && (K >> 5) % 2 == 0 && (K >> 5) >= 2) {
+            if (type == TSB_MXFP4) {
+                if (glu) TSB_CHECK_CUDA(tsb_launch(gemv_tiles_mma_wide_kernel<true, true>, grid, block, 0, st, a));
+                else TSB_CHECK_CUDA(tsb_launch(gemv_tiles_mma_wide_kernel<false, true>, grid, block, 0, st, a));
+            } else {
+                if (glu) TSB_CHECK_CUDA(tsb_launch(gemv_tiles_mma_wide_kernel<true, false>, grid, block, 0, st, a));
+                else TSB_CHECK_CUDA(tsb_launch(gemv_tiles_mma_wide_kernel<false, false>, grid, block, 0, st, a));
+            }
+            TSB_CHECK_LAUNCH();
+            return TSB_OK;
+        }
         if (type == TSB_MXFP4) {
             if (glu) TSB_CHECK_CUDA(tsb_launch(gemv_tiles_mma_kernel<true, true>, grid, block, 0, st, a));
             else TSB_CHECK_CUDA(tsb_launch(gemv_tiles_mma_kernel<false, true>, grid, block, 0, st, a));
