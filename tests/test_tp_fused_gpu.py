@@ -65,7 +65,9 @@ def test_fused_exchange_matches_nccl_and_single_gpu(n, kv8_model_path, moe_model
 
 def check_result(r):
     assert r["status"] == 0 and r["exchanges"] > 0, r
-    assert r["fused_vs_nccl"] <= 1e-2 * max(1.0, r["scale"])      # different summation orders, then int8 re-quantisation
+    # different summation orders, int8 activations with one scale per 256 (fused decode step) or per 32 (mailbox GEMV)
+    # against bf16 activations on the tensor-core GEMM for the 9-token prompt of the NCCL path
+    assert r["fused_vs_nccl"] <= 1.5e-2 * max(1.0, r["scale"]), r
     assert r["fused_vs_single"] <= 2e-2 * max(1.0, r["scale"])
     assert r["graph_tokens"] == r["eager_tokens"]
     # sequence-parallel prefill: same logits as the NCCL path and as one GPU (bf16 GEMMs on both sides)
