@@ -331,10 +331,19 @@ class ModelBase:
     def kv_donors(self) -> Dict[int, int]:
         return {}
 
+    def kv_window_layers(self) -> Dict[int, int]:
+        """Layer -> sliding window, for the layers whose attention never looks further back (families with such layers
+        override this); with TSB_KV_WINDOW_RING=1 those layers keep a ring of pages instead of the whole context."""
+        return {}
+
     def make_kv_pool(self) -> PagedKV:
         pages_per_seq = (self.max_context + self.page_size - 1) // self.page_size
+        ring_chunk = 0
+        if (os.environ.get("TSB_KV_WINDOW_RING", "0") not in ("", "0") and self.cp_comm is None and self.pp_size == 1):
+            ring_chunk = max(self.page_size, int(os.environ.get("TSB_KV_RING_CHUNK", "2048")))
         return PagedKV(self.kv_layer_shapes(), pages_per_seq * self.max_seqs, self.page_size, self.device,
-                       self.kv_dtype, self.kv_donors(), max_seqs=max(self.max_seqs, 1))
+                       self.kv_dtype, self.kv_donors(), max_seqs=max(self.max_seqs, 1),
+                       window_layers=self.kv_window_layers() if ring_chunk else None, ring_chunk=ring_chunk)
 
     # ------------------------------------------------------------------ execution
     def forward_batch(self, batch: Batch, want_logits: bool = True) -> Optional[torch.Tensor]:
@@ -388,6 +397,12 @@ class ModelBase:
                 out = self._graph_stepper().step(tokens[0])
             if out is not None:
                 return out if want_logits else None
+        chunk = self.kv.ring_chunk
+        if chunk and len(tokens) > chunk:               # window layers keep a ring of pages: prompts go in by chunks
+            tokens = list(tokens)
+            for i in range(0, len(tokens) - chunk, chunk):
+                self.forward(tokens[i:i + chunk], want_logits=False)
+            tokens = tokens[(len(tokens) - 1) // chunk * chunk:]
         batch = self.kv.build_batch([self._seq()], [list(tokens)])
         with self.timer.phase("decode" if len(tokens) == 1 else "prefill"):
             out = self.forward_batch(batch, want_logits)
@@ -400,6 +415,8 @@ class ModelBase:
         if self.device.type != "cuda" or self.tp_size > 1 or self.pp_size > 1 or self._pending_embeddings:
             return False
         if not self.supports_kv_truncation:             # recurrent state: the capture's warm-up step would advance it
+            return False
+        if self.kv.ring:                                # the steppers rewrite block-table rows themselves (full table only)
             return False
         return os.environ.get("TSB_GRAPH_FORWARD", "1") != "0"
 
@@ -519,6 +536,9 @@ class ModelBase:
             return
         if not self.supports_kv_truncation:
             raise RuntimeError(f"{type(self).__name__} cannot truncate its cache (recurrent state)")
+        if not self.kv.can_truncate(seq, n_tokens):     # the window layers' ring has overwritten what the cut needs: start over
+            self.reset_kv_cache()
+            return
         self.kv.truncate(seq, n_tokens)
 
     def warm_up_kernels(self) -> None:

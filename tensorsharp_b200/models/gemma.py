@@ -39,6 +39,9 @@ class _GemmaBase(ModelBase):
     supports_context_parallel = True
 
     # per-layer geometry, filled by parse_config
+    def kv_window_layers(self):
+        return {l: self.window for l in range(self.cfg.n_layers) if self.is_local(l)}
+
     def is_local(self, l: int) -> bool:
         raise NotImplementedError
 
@@ -116,6 +119,8 @@ class _GemmaBase(ModelBase):
             else:
                 k = v = q            # unused: this layer reads a donor layer's cache
         kc, vc = self.kv.k[kv_layer], self.kv.v[kv_layer]
+        if self.kv.is_window_layer(kv_layer):
+            batch = batch.windowed()                    # the ring's slots and block table
         qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=kc, v_cache=vc, rope=rope,
                               qn=L["q_norm"], kn=L["k_norm"], v_norm=v_norm, eps=c.eps, q_scale=1.0,
                               write_kv=write_kv)

@@ -104,6 +104,9 @@ class GptOssModel(ModelBase):
     def exchange_parts(self) -> int:
         return max(1, self.top_k)
 
+    def kv_window_layers(self):
+        return {l: self.window for l in range(self.cfg.n_layers) if l % 2 == 0}
+
     def attention_block(self, a, L, l: int, batch: Batch, mid, proj) -> torch.Tensor:
         """QKV projection (``proj(weight, bias)``), RoPE + cache write, attention -> ``[T, Hq * Dh]``."""
         c = self.cfg
@@ -116,6 +119,8 @@ class GptOssModel(ModelBase):
         else:
             q, k, v = (proj(L["wq"], L["bq"]).view(T, Hq, Dh), proj(L["wk"], L["bk"]).view(T, Hkv, Dh),
                        proj(L["wv"], L["bv"]).view(T, Hkv, Dh))
+        if self.kv.is_window_layer(l):
+            batch = batch.windowed()                    # the ring's slots and block table
         qr = F.qkv_rope_cache(q, k, v, Hq=Hq, Hkv=Hkv, Dh=Dh, batch=batch, k_cache=self.kv.k[l], v_cache=self.kv.v[l],
                               rope=self.rope, eps=c.eps)
         self.cp_sync_kv(l)

@@ -72,6 +72,23 @@ class Batch:
     h_cu_q: Tuple[int, ...] = ()
     h_kv_lens: Tuple[int, ...] = ()
     cache: dict = field(default_factory=dict)   # per-forward memo (RoPE tables); cleared by the step runner
+    # Sliding-window layers that keep a ring of pages (runtime/paged_kv.py): their own slot per token and their own block
+    # table (logical page -> physical page of the ring).  None when the pool keeps every page of every layer.
+    slots_w: Optional[torch.Tensor] = None
+    block_table_w: Optional[torch.Tensor] = None
+
+    def windowed(self) -> "Batch":
+        """The view of this batch that a sliding-window layer uses: the same tokens and lengths with the ring's slots
+        and block table in place of the full ones (the batch itself when the pool has no ring)."""
+        if self.block_table_w is None:
+            return self
+        w = self.cache.get("_windowed")
+        if w is None or w.slots is not self.slots_w:
+            import dataclasses
+            w = dataclasses.replace(self, slots=self.slots_w, block_table=self.block_table_w, slots_w=None, block_table_w=None,
+                                    cache=self.cache)
+            self.cache["_windowed"] = w
+        return w
 
     @property
     def B(self) -> int:

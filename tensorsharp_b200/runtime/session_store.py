@@ -26,6 +26,8 @@ def save_session(path: str, model, cache: KVCache, seq=None) -> int:
     """Write the first ``cache.count`` positions of ``seq`` (default: the model's own sequence)."""
     if not getattr(model, "supports_kv_truncation", True):
         raise RuntimeError(f"{type(model).__name__} keeps recurrent state that is not part of the KV pool")
+    if model.kv.ring:
+        raise RuntimeError("the window layers keep only a ring of pages (TSB_KV_WINDOW_RING=1): their cache cannot be saved")
     seq = seq or model._seq()
     n = min(cache.count, seq.length)
     slots = _slots(model.kv, seq, n)
@@ -52,6 +54,8 @@ def load_session(path: str, model, cache: KVCache, seq=None) -> int:
     d = torch.load(path, map_location="cpu", weights_only=False)
     if d["arch"] != model.arch or d["n_layers"] != len(model.kv.k):
         raise ValueError(f"session file was written by a different model ({d['arch']}, {d['n_layers']} layers)")
+    if model.kv.ring:
+        raise RuntimeError("the window layers keep only a ring of pages (TSB_KV_WINDOW_RING=1): a saved cache cannot be restored")
     seq = seq or model._seq()
     n = len(d["tokens"])
     model.kv.truncate(seq, 0)

@@ -109,3 +109,36 @@ def test_conv1d_gdn_mamba_kernels():
     yc = F.mamba2(xbc, dt, dtb, A, D, s_c, _batch(lens, "cpu"), H=H, P=P, G=G, N=N)
     yg = F.mamba2(xbc.cuda(), dt.cuda(), dtb.cuda(), A.cuda(), D.cuda(), s_g, _batch(lens, "cuda"), H=H, P=P, G=G, N=N)
     assert _rel(yg.cpu(), yc) < 1e-4 and _rel(s_g.cpu(), s_c) < 1e-4
+
+
+@pytest.mark.parametrize("family", ["gemma3", "gptoss"])
+def test_window_ring_pool_on_cuda(tmp_path, monkeypatch, family):
+    """TSB_KV_WINDOW_RING=1 on the GPU: sliding-window layers on a ring of pages give the logits of the pool that keeps
+    every page (same prefill chunks), through eager steps and through a captured decode graph that wraps the ring."""
+    from tensorsharp_b200.models import synth
+    from tensorsharp_b200.runtime.engine import DecodeGraph
+    p = str(tmp_path / "m.gguf")
+    if family == "gemma3":
+        synth.write_gemma(p, arch="gemma3", window=16, device="cpu")
+    else:
+        synth.write_gptoss(p, n_layers=2, window=16, device="cpu")
+    monkeypatch.setenv("TSB_KV_RING_CHUNK", "32")
+    monkeypatch.setenv("TSB_GRAPH_FORWARD", "0")
+    g = torch.Generator().manual_seed(13)
+    toks = torch.randint(0, 4096, (200,), generator=g).tolist()
+    logits, tokens = [], []
+    for ring in ("0", "1"):
+        monkeypatch.setenv("TSB_KV_WINDOW_RING", ring)
+        m = ModelBase.create(p, "cuda", max_context=512, page_size=16)
+        assert m.kv.ring == (ring == "1")
+        for i in range(0, 192, 32):
+            m.forward(toks[i:i + 32], want_logits=False)
+        lg = m.forward(toks[192:]).float().cpu()
+        logits.append(lg)
+        seq = m._seq()
+        dg = DecodeGraph(m, [seq], 100)
+        dg.set_tokens([int(lg.argmax())])
+        dg.capture()
+        tokens.append([int(dg.step()[0]) for _ in range(90)])
+    assert _rel(logits[1], logits[0]) < 1e-5, _rel(logits[1], logits[0])
+    assert tokens[0] == tokens[1]
