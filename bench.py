@@ -253,9 +253,12 @@ def run_ours(args) -> dict:
         e0.record()
         first = None
         per = 4 if P >= 2048 else max(4, 16384 // P)     # 8 k to 16 k tokens per forward keeps activations modest
+        rc = model.kv.ring_chunk or P                  # window layers on a ring of pages: the prompt goes in by chunks
         for i in range(0, B, per):
             chunk = seqs[i:i + per]
-            logits = model.forward_batch(model.kv.build_batch(chunk, prompts[i:i + per]))
+            for j in range(0, P, rc):
+                last = j + rc >= P
+                logits = model.forward_batch(model.kv.build_batch(chunk, [p[j:j + rc] for p in prompts[i:i + per]]), want_logits=last)
             t = F.argmax(logits)
             first = t if first is None else torch.cat([first, t])
         e1.record()
@@ -330,7 +333,10 @@ def run_ours(args) -> dict:
         model.kv.truncate(seq, keep)
         barrier()
         e0.record()
-        F.argmax(model.forward_batch(model.kv.build_batch([seq], [tail])))
+        rc = model.kv.ring_chunk or len(tail)
+        for j in range(0, len(tail), rc):
+            lg = model.forward_batch(model.kv.build_batch([seq], [tail[j:j + rc]]), want_logits=j + rc >= len(tail))
+        F.argmax(lg)
         e1.record()
         barrier()
         turn2_ms = e0.elapsed_time(e1)
@@ -383,6 +389,8 @@ def run_ours(args) -> dict:
         "e2e": {"value": B * K / (max(e2e_ms, e2e_wall_ms) / 1e3), "unit": "tok/s", "h2d_bytes_per_step": 4 * B,
                 "d2h_bytes_per_step": 4 * B, "ms_per_step_device": e2e_ms / K, "ms_per_step_wall": e2e_wall_ms / K},
         "gpu_launches": (dg.launches_per_step or launches_eager) * K,
+        "kv_cache": {"gb": round(sum(t.numel() * t.element_size() for t in {id(t): t for t in list(model.kv.k) + list(model.kv.v) if t is not None}.values()) / 1e9, 3),
+                     "window_ring_pages": model.kv.ring_pages or None},
         "second_turn": ({"kv_reused_tokens": int(args.reuse_prefix), "new_tokens": turn2_new, "ttft_ms": turn2_ms}
                         if turn2_new else None),
         "kernel_status": status,
