@@ -252,4 +252,15 @@ if __name__ == "__main__":
     os.environ["TSB_MEGA"] = "1"
     os.environ["TSB_GRAPH_FORWARD"] = "0"
     from ..models.base import ModelBase
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:      # under torch.distributed.run: one tensor-parallel shard per rank
+        from ..parallel.dist import init_from_env
+        comm = init_from_env()
+        model = ModelBase.create(cli.model, comm.device, max_context=cli.context + 256, max_seqs=2, tp_rank=comm.rank,
+                                 tp_size=comm.size, comm=comm)
+        table = phase_table(model, cli.context)
+        if comm.rank == 0:
+            print(f"rank 0 of {comm.size}\n{table}")
+        comm.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)                                     # (skip the NCCL teardown)
     print(phase_table(ModelBase.create(cli.model, "cuda", max_context=cli.context + 256), cli.context))
