@@ -52,6 +52,8 @@ def parse_args():
                     help="qwen3-4b at batch 1: measure this batch size as well and report it under \"batch16\"-style extra keys "
                          "(default 16, the other half of the configuration; 0 = skip)")
     ap.add_argument("--no-graph", action="store_true", help="run decode steps eagerly (for kernel-level profiling)")
+    ap.add_argument("--trace-prefill", default=None, metavar="FILE",
+                    help="one GPU: write the kernel timeline of one prefill to FILE and print the per-kernel table to stderr")
     ap.add_argument("--trace", default=None, metavar="FILE",
                     help="after the timed runs, record three more graph replays with the CUDA activity tracer, write the "
                          "kernel events of the middle one to FILE (JSON) and print its per-kernel table to stderr")
@@ -178,10 +180,10 @@ def ensure_model(args, rank: int, world: int) -> str:
     return path
 
 
-def trace_step(dg, path: str) -> None:
-    """Kernel timeline of one decode step inside the captured graph.  Kernels overlap under programmatic
-    dependent launch (a kernel is resident and waiting before its predecessor ends), so besides each
-    kernel's own duration the table gives its *exclusive* time: the part of it after every earlier
+def trace_step(dg, path: str, run=None, what: str = "decode step") -> None:
+    """Kernel timeline of one decode step inside the captured graph (or of one call of ``run``: a prefill).  Kernels
+    overlap under programmatic dependent launch (a kernel is resident and waiting before its predecessor ends), so
+    besides each kernel's own duration the table gives its *exclusive* time: the part of it after every earlier
     kernel had finished, which is what it adds to the step."""
     import collections
     import re
@@ -190,7 +192,7 @@ def trace_step(dg, path: str) -> None:
     from torch.profiler import ProfilerActivity, profile
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
         for _ in range(3):
-            dg.step()
+            run() if run is not None else dg.step()
         torch.cuda.synchronize()
     ev = sorted(((e.name, e.time_range.start, e.time_range.end) for e in prof.events()
                  if e.device_type == torch.autograd.DeviceType.CUDA), key=lambda x: x[1])
@@ -207,7 +209,7 @@ def trace_step(dg, path: str) -> None:
         r[1] += e - s
         r[2] += max(0.0, e - max(prev, s))
         prev = max(prev, e)
-    print(f"decode step: {n} kernels, {prev - t0:.1f} us", file=sys.stderr)
+    print(f"{what}: {n} kernels, {prev - t0:.1f} us", file=sys.stderr)
     print(f"{'kernel':50s}{'n':>4s}{'sum us':>9s}{'excl us':>9s}{'excl/n':>8s}", file=sys.stderr)
     for k, (c, du, ex) in sorted(rows.items(), key=lambda kv: -kv[1][2]):
         print(f"{k:50s}{c:4d}{du:9.1f}{ex:9.1f}{ex / c:8.2f}", file=sys.stderr)
@@ -320,6 +322,12 @@ def run_ours(args) -> dict:
 
     if args.trace and rank == 0:
         trace_step(dg, args.trace)
+    if args.trace_prefill and rank == 0 and world == 1:
+        def one_prefill():
+            ss, _, _ = prefill_once()
+            for s_ in ss:
+                model.kv.free_seq(s_)
+        trace_step(None, args.trace_prefill, run=one_prefill, what="prefill")
 
     # ---- second turn (long-context configs): keep a prefix of the first turn's cache, prefill what follows it
     turn2_ms, turn2_new = 0.0, 0
