@@ -8,10 +8,13 @@ channel LayerNorm + ReLU, input projection, conformer blocks = half-step FFW, ch
 attention with relative position logits and a tanh soft cap, light depthwise convolution module,
 second half-step FFW, block norm; output projection, unweighted RMSNorm, projection to the text
 width).  WAV is decoded here; other containers need an external decoder and raise a clear error.
+On a GPU the encoder's projections run on this package's tcgen05 GEMM (bf16 operands, bias in the epilogue);
+``TSB_AUDIO_KERNELS=0`` keeps them on library calls.
 """
 from __future__ import annotations
 
 import math
+import os
 import struct
 from typing import Dict, Optional, Tuple
 
@@ -139,7 +142,9 @@ class Gemma4AudioEncoder:
 
     def __init__(self, path: str, device="cpu"):
         self.device = torch.device(device)
+        self.native = self.device.type == "cuda" and os.environ.get("TSB_AUDIO_KERNELS", "1") != "0"
         self.w: Dict[str, torch.Tensor] = {}
+        self._wk: Dict[str, torch.Tensor] = {}
         with GGUFFile(path) as g:
             def key(name, default, getter=g.get_int):
                 v = getter("clip.audio." + name, None)
@@ -181,11 +186,28 @@ class Gemma4AudioEncoder:
         c = self.clamps.get(prefix)
         if c is not None:
             x = x.clamp(c[0], c[1])
-        y = x @ self.w[prefix + ".weight"].t()
+        W = self.w[prefix + ".weight"]
         b = self.w.get(prefix + ".bias")
-        if b is not None:
-            y = y + b
+        if self.native and x.is_cuda and W.dim() == 2 and W.numel() >= 4096:
+            y = self.gemm(x, prefix, W, b)
+        else:
+            y = x @ W.t()
+            if b is not None:
+                y = y + b
         return y.clamp(c[2], c[3]) if c is not None else y
+
+    def gemm(self, x: torch.Tensor, prefix: str, W: torch.Tensor, b: Optional[torch.Tensor]) -> torch.Tensor:
+        """The projection on the tcgen05 GEMM: a bf16 copy of the weight (input dimension padded to whole 64-column
+        k-blocks), rows of ``x`` flattened, bias in the epilogue, float32 out."""
+        from ..ops import kernels
+        K = W.shape[1]
+        Kp = (K + 63) // 64 * 64
+        Wp = self._wk.get(prefix)
+        if Wp is None:
+            Wp = self._wk[prefix] = TF.pad(W.to(torch.bfloat16), (0, Kp - K)).contiguous()
+        xb = TF.pad(x.reshape(-1, K).to(torch.bfloat16), (0, Kp - K)).contiguous()
+        y = kernels.gemm_bf16(Wp, xb, out_dtype=torch.float32, bias=b.float().contiguous() if b is not None else None)
+        return y.view(*x.shape[:-1], W.shape[0])
 
     def norm(self, x: torch.Tensor, weight_name: str) -> torch.Tensor:
         w = self.w.get(weight_name)

@@ -18,10 +18,19 @@ Parity (tensor names, metadata keys and arithmetic):
     table is built patch-major, which is what the layout it copies from intends.
 
 All encoders return float32 ``[tokens, projection_dim]`` on the compute device.
+
+On a GPU the two heavy parts of every block run on this package's own kernels (the reference's counterparts are
+the fused ``TSGgml_FusedVisionMLP`` / ``TSGgml_FusedVisionAttention`` graphs, Native/ggml_ops_fused.cpp:1490, :1519):
+the projections on the tcgen05 GEMM with the bias added in its epilogue, and the bidirectional attention on the flash
+prefill kernel, which sees the whole patch sequence as one cache page and is told, through its position override, that
+every query stands behind the last key.  Head sizes the kernel has no instance for (72 in the SigLIP towers) are padded
+with zero columns, which change neither the scores nor the kept output columns.  ``TSB_VISION_KERNELS=0`` keeps the
+encoder on library calls.
 """
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, Optional, Tuple
 
 import numpy as np
@@ -47,7 +56,9 @@ class VisionEncoderBase:
     def __init__(self, path: str, device="cpu"):
         self.device = torch.device(device)
         self.mat_dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+        self.native = self.device.type == "cuda" and os.environ.get("TSB_VISION_KERNELS", "1") != "0"
         self.w: Dict[str, torch.Tensor] = {}
+        self._wk: Dict[str, torch.Tensor] = {}      # weights with the input dimension padded to whole 64-column k-blocks
         with GGUFFile(path) as g:
             self.read_config(g)
             for name, ti in g.tensors.items():
@@ -79,17 +90,39 @@ class VisionEncoderBase:
         if c is not None:
             x = x.clamp(c[0], c[1])
         W = self.w[prefix + ".weight"]
-        y = (x.to(W.dtype) @ W.t()).float()
         b = self.w.get(prefix + ".bias") if bias else None
-        if b is not None:
-            y = y + b
+        if self.native and x.is_cuda and x.dim() == 2 and W.dtype == torch.bfloat16:
+            y = self.gemm(x, prefix + ".weight", W, b)
+        else:
+            y = (x.to(W.dtype) @ W.t()).float()
+            if b is not None:
+                y = y + b
         if c is not None:
             y = y.clamp(c[2], c[3])
         return y
 
+    def gemm(self, x: torch.Tensor, name: str, W: torch.Tensor, b: Optional[torch.Tensor]) -> torch.Tensor:
+        """``x [T, K] @ W [N, K]^T + b`` in float32 on the tcgen05 GEMM (bf16 operands, bias in the epilogue)."""
+        from ..ops import kernels
+        K = W.shape[1]
+        Kp = (K + 63) // 64 * 64
+        Wp = self._wk.get(name)
+        if Wp is None:
+            Wp = self._wk[name] = W.contiguous() if Kp == K else TF.pad(W, (0, Kp - K)).contiguous()
+        xb = x.to(torch.bfloat16)
+        xb = xb.contiguous() if Kp == K else TF.pad(xb, (0, Kp - K))
+        if b is not None:
+            b = b.float().contiguous()
+        return kernels.gemm_bf16(Wp, xb, out_dtype=torch.float32, bias=b)
+
     def project_x_w(self, x: torch.Tensor, name: str) -> torch.Tensor:
         """``x @ W`` for projector weights stored ``[in, out]`` (``mm.input_projection``)."""
         W = self.w[name]
+        if self.native and x.is_cuda and x.dim() == 2 and W.dtype == torch.bfloat16:
+            Wt = self._wk.get(name + "^T")
+            if Wt is None:
+                Wt = self._wk[name + "^T"] = W.t().contiguous()
+            return self.gemm(x, name + "^T.k", Wt, None)
         return (x.to(W.dtype) @ W).float()
 
     def layer_norm(self, x: torch.Tensor, prefix: str, eps: float) -> torch.Tensor:
@@ -101,12 +134,30 @@ class VisionEncoderBase:
         x = x[0].flatten(1).t().contiguous()
         return x + bias if bias is not None else x
 
-    @staticmethod
-    def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:
+    def attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:
         """``[n, heads, d]`` each -> ``[n, heads * d]``; full bidirectional attention."""
+        if self.native and q.is_cuda and q.shape[-1] <= 512:
+            return self.flash_attention(q, k, v, scale)
         o = TF.scaled_dot_product_attention(q.transpose(0, 1)[None], k.transpose(0, 1)[None], v.transpose(0, 1)[None],
                                             scale=scale)
         return o[0].transpose(0, 1).reshape(q.shape[0], -1)
+
+    @staticmethod
+    def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:
+        """The flash prefill kernel as a bidirectional attention: K and V are one cache page of ``n`` slots, and the
+        first query's cache position is set to ``n``, so the causal bound of every query lies behind the last key."""
+        from ..ops import kernels
+        n, H, d = q.shape
+        dp = next(s for s in (64, 128, 256, 512) if s >= d)
+
+        def prep(t):
+            t = t.to(torch.bfloat16)
+            return (TF.pad(t, (0, dp - d)) if dp != d else t).contiguous()
+        dev = q.device
+        meta = torch.tensor([0, n, n, n, 0], dtype=torch.int32, device=dev)     # cu_q | cache length | first position | page
+        o = kernels.attn_prefill(prep(q), prep(k), prep(v), meta[4:5].view(1, 1), meta[2:3], meta[0:2], n, scale=float(scale),
+                                 Hq=H, Hkv=H, Dh=dp, page_size=n, q_pos0=meta[3:4])
+        return o[..., :d].float().reshape(n, H * d)
 
     @staticmethod
     def avg_pool_grid(x: torch.Tensor, gh: int, gw: int, k: int) -> torch.Tensor:
