@@ -24,7 +24,7 @@ USAGE = ("Usage: python -m tensorsharp_b200.cli --model <path.gguf> [--input <in
          "[--benchmark [--bench-prefill N] [--bench-decode N] [--bench-runs N] [--bench-chunked]] "
          "[--test-chunked-prefill [--correct-prefill N] [--correct-decode N]] [--bench-kvcache [--bench-kv-turns N]] "
          "[--test-templates <dir>] [--log-level info|debug|trace] [--log-dir <path>] [--log-file off] [--log-console off] "
-         "[--batch-size N] [--max-context N] [--tp N | --pp N | --cp N  (one process per GPU: python -m torch.distributed.run "
+         "[--batch-size N] [--max-context N] [--kv-dtype bf16|fp8] [--tp N | --pp N | --cp N  (one process per GPU: python -m torch.distributed.run "
          "--nproc-per-node N -m tensorsharp_b200.cli ...)]")
 
 
@@ -68,6 +68,7 @@ class CliOptions:
     cp: int = 1                       # context-parallel ranks: long prompts are dealt to them slice by slice
     batch_size: int = 1               # JSONL mode: requests decoded together (continuous batching)
     max_context: Optional[int] = None
+    kv_dtype: Optional[str] = None          # "bf16" or "fp8" (exported as TSB_KV_DTYPE before the model loads)
     unknown: List[str] = field(default_factory=list)
 
 
@@ -86,6 +87,14 @@ _SAMPLING = {"--temperature": ("temperature", float), "--top-k": ("top_k", int),
              "--min-p": ("min_p", float), "--repeat-penalty": ("repetition_penalty", float),
              "--presence-penalty": ("presence_penalty", float), "--frequency-penalty": ("frequency_penalty", float),
              "--seed": ("seed", int)}
+
+
+def kv_dtype_name(v: str) -> str:
+    """``--kv-dtype``: ``bf16`` (default pages) or ``fp8`` (e4m3 bytes, half the cache)."""
+    n = {"bf16": "bf16", "bfloat16": "bf16", "fp8": "fp8", "e4m3": "fp8", "float8_e4m3fn": "fp8"}.get(v.strip().lower())
+    if n is None:
+        raise ValueError(f"Invalid value for --kv-dtype: '{v}' (bf16 or fp8).")
+    return n
 
 
 def parse_cli_args(args: Sequence[str]) -> CliOptions:
@@ -122,6 +131,8 @@ def parse_cli_args(args: Sequence[str]) -> CliOptions:
             o.sampling.stop_sequences = (o.sampling.stop_sequences or []) + [value(a)]
         elif a == "--backend":
             o.backend = value(a).lower()
+        elif a == "--kv-dtype":
+            o.kv_dtype = kv_dtype_name(value(a))
         elif a == "--system-file":
             with open(value(a), "r", encoding="utf-8") as f:
                 o.system = f.read()

@@ -582,6 +582,8 @@ def load_model(o: CliOptions, log):
     kw: Dict[str, Any] = {}
     if o.max_context:
         kw["max_context"] = o.max_context
+    if o.kv_dtype:
+        os.environ["TSB_KV_DTYPE"] = o.kv_dtype       # read by ModelBase (every rank parses the same command line)
     if o.batch_size > 1:
         kw["max_seqs"] = o.batch_size + 1          # one KV sequence per request in flight, plus the default one
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -14,37 +14,9 @@
 #include <cstdlib>
 #include <mutex>
 #include "common.cuh"
+#include "attn_args.cuh"
 #include "tsb_noalloc.h"
 
-struct AttnArgs {
-    const bf16* q;            // [Tq, Hq, Dh]
-    const bf16* k_cache;
-    const bf16* v_cache;
-    bf16* out;                // [Tq, Hq, Dh]
-    const int* block_table;   // [B, max_pages]
-    const int* kv_lens;       // [B] tokens in the cache for this sequence (including the new ones)
-    const int* cu_q;          // [B + 1] query offsets (prefill); null for decode (one query per sequence)
-    const float* sinks;       // [Hq] or null
-    float* part_o;            // decode scratch [B, Hq, splits, Dh]
-    float* part_ml;           // decode scratch [B, Hq, splits, 2]
-    float scale;
-    float softcap;            // 0 = off
-    int window;               // 0 = full causal
-    int B, Hq, Hkv, Dh, page_size, max_pages, splits;
-    // Prefill only.  Context parallelism runs the kernel once per KV shard and merges the partial results:
-    const int* q_pos0;        // [B] cache position of each sequence's first query, or null = kv_len - q_len
-    float* lse_out;           // [Tq, Hq] log-sum-exp of the scaled scores seen by this call (-inf if none), or null
-    // Decode only: the output again as int8 groups of 32 with (scale, sum), the form the following
-    // quantised projection reads, so that no separate quantise launch is needed.  Null = not wanted.
-    int8_t* out_q;            // [B, Hq * Dh]
-    float2* out_ds;           // [B, Hq * Dh / 32]
-    // Set by the launcher, not the caller: per (sequence, KV head) arrival counters.  When present, the
-    // CTA that finishes a head group last merges the split partials itself and no combine kernel runs.
-    unsigned* ticket;
-    // Decode: positions per split fixed by the caller (a multiple of 32), so that a CTA's range and its block-table
-    // entries do not wait for the sequence length; 0 = derive it from the length (ceil(span / splits), rounded to 32).
-    int split_len;
-};
 
 __device__ __forceinline__ long kv_slot(const AttnArgs& a, int b, int j) {
     const int page = a.block_table[(long)b * a.max_pages + j / a.page_size];
@@ -451,6 +423,16 @@ static int attn_decode_impl(const AttnArgs* args, void* stream, bool allow_fused
 }
 
 extern "C" int tsb_attn_decode(const AttnArgs* args, void* stream) { return attn_decode_impl(args, stream, true); }
+
+// The merge of the split partials on its own, for split kernels that live in other translation units.
+extern "C" int tsb_attn_combine(const AttnArgs* args, void* stream) {
+    const AttnArgs& a = *args;
+    TSB_CHECK_ARG(a.splits >= 1 && a.splits <= 64 && a.part_o && a.part_ml, "attn_combine: scratch for %d splits (limit 64)", a.splits);
+    if (a.B == 0) return TSB_OK;
+    TSB_CHECK_CUDA(tsb_launch(attn_combine_kernel, dim3(a.Hq, a.B), dim3((a.Dh + 31) & ~31), 0, (cudaStream_t)stream, a));
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}
 
 // ------------------------------------------------------------------------------------------
 // Allocation-free variant (see tsb_noalloc.h): the split-KV partials live in a file-scope

@@ -94,7 +94,12 @@ class ModelBase:
         self.max_context = int(max_context or (int(ctx_env) if ctx_env else 0) or self.cfg.context_length or 4096)
         self.page_size = page_size
         self.max_seqs = max_seqs
+        # TSB_KV_DTYPE=fp8: e4m3 pages, half the bytes of the bf16 cache (ops/functional.py: is_fp8)
+        if kv_dtype is None and os.environ.get("TSB_KV_DTYPE", "").lower() in ("fp8", "e4m3", "float8_e4m3fn"):
+            kv_dtype = torch.float8_e4m3fn
         self.kv_dtype = kv_dtype or (torch.bfloat16 if self.device.type == "cuda" else torch.float32)
+        if self.kv_dtype == torch.float8_e4m3fn and self.cp_comm is not None:
+            raise ValueError("the 8-bit KV cache is not combined with context parallelism (the shard exchange moves bf16 rows)")
         self.weights: Dict[str, object] = {}
         self.load_weights()
         self.kv = self.make_kv_pool()
@@ -339,7 +344,8 @@ class ModelBase:
     def make_kv_pool(self) -> PagedKV:
         pages_per_seq = (self.max_context + self.page_size - 1) // self.page_size
         ring_chunk = 0
-        if (os.environ.get("TSB_KV_WINDOW_RING", "0") not in ("", "0") and self.cp_comm is None and self.pp_size == 1):
+        if (os.environ.get("TSB_KV_WINDOW_RING", "0") not in ("", "0") and self.cp_comm is None and self.pp_size == 1
+                and self.kv_dtype != torch.float8_e4m3fn):
             ring_chunk = max(self.page_size, int(os.environ.get("TSB_KV_RING_CHUNK", "2048")))
         return PagedKV(self.kv_layer_shapes(), pages_per_seq * self.max_seqs, self.page_size, self.device,
                        self.kv_dtype, self.kv_donors(), max_seqs=max(self.max_seqs, 1),

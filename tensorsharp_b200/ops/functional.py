@@ -337,12 +337,24 @@ def qkv_rope_cache(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, Hq: int
                 batch.cache[key] = table
         q_out = torch.empty((T, Hq, Dh), dtype=torch.bfloat16, device=q.device)
         assert q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1 and q.dtype == k.dtype == v.dtype
+        slots, kc, vc = batch.slots, k_cache, v_cache
+        fp8 = write_kv and is_fp8(k_cache)
+        if fp8:
+            # 8-bit pages: the kernel leaves the finished K / V rows in dense bf16 staging rows, which one more
+            # kernel converts and scatters to their slots
+            slots = batch.cache.get("arange_T")
+            if slots is None:
+                slots = batch.cache["arange_T"] = torch.arange(T, dtype=torch.int64, device=q.device)
+            kc = torch.empty((T, Hkv, Dh), dtype=torch.bfloat16, device=q.device)
+            vc = torch.empty_like(kc)
         kk.qkv_rope(q=q, k=k, v=v, q_strides=(q.stride(0), q.stride(1)), k_strides=(k.stride(0), k.stride(1)),
                     v_strides=(v.stride(0), v.stride(1)), Hq=Hq, Hkv=Hkv if write_kv else 0, Dh=Dh,
-                    pos=batch.positions, slot=batch.slots,
-                    q_out=q_out, k_cache=k_cache, v_cache=v_cache, qn=qn, kn=kn, v_norm=v_norm, eps=eps, rope=rp,
+                    pos=batch.positions, slot=slots,
+                    q_out=q_out, k_cache=kc, v_cache=vc, qn=qn, kn=kn, v_norm=v_norm, eps=eps, rope=rp,
                     freq_factors=rope.freq_factors if rope is not None else None, q_scale=q_scale,
                     cs_table=table)
+        if fp8:
+            kk.kv_store_fp8(kc, vc, k_cache, v_cache, batch.slots)
         return q_out
     qf, kf, vf = q.float(), k.float(), v.float()
     if qn is not None:
@@ -358,9 +370,51 @@ def qkv_rope_cache(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, Hq: int
         qf = ref.apply_rope(qf, cos, sin, rope.rot_dim, rope.mode)
         kf = ref.apply_rope(kf, cos, sin, rope.rot_dim, rope.mode)
     if write_kv:
-        k_cache[batch.slots] = kf.to(k_cache.dtype)
-        v_cache[batch.slots] = vf.to(v_cache.dtype)
+        kv_scatter(k_cache, batch.slots, kf)
+        kv_scatter(v_cache, batch.slots, vf)
     return qf * q_scale
+
+
+FP8 = torch.float8_e4m3fn
+
+
+def is_fp8(cache: torch.Tensor) -> bool:
+    return cache.dtype == FP8
+
+
+def kv_scatter(cache: torch.Tensor, slots: torch.Tensor, rows: torch.Tensor) -> None:
+    """``cache[slots] = rows`` in the cache's element type (8-bit caches are indexed through their bytes)."""
+    if is_fp8(cache):
+        cache.view(torch.uint8)[slots] = rows.to(FP8).view(torch.uint8)
+    else:
+        cache[slots] = rows.to(cache.dtype)
+
+
+def kv_gather(cache: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    """``cache[idx]``; rows of an 8-bit cache come back as float32."""
+    if is_fp8(cache):
+        return cache.view(torch.uint8)[idx].view(FP8).float()
+    return cache[idx]
+
+
+def fp8_prefill_view(k_cache: torch.Tensor, v_cache: torch.Tensor, batch: Batch):
+    """The cache rows of the batch's sequences as dense bf16 tensors, laid out as one page per sequence, with the
+    block table that goes with them: (K, V, table, page size).  Converting a prompt's keys once per layer costs their
+    bytes three times over; the flash kernel then reads them once per query tile as it does bf16 pages."""
+    ps, B = batch.page_size, batch.B
+    L = (batch.max_kv_len + 63) // 64 * 64
+    key = ("fp8_idx", id(batch.block_table))
+    cached = batch.cache.get(key)
+    if cached is None:
+        j = torch.arange(L, device=k_cache.device)
+        width = batch.block_table.shape[1]
+        pages = batch.block_table.long()[:, (j // ps).clamp_max(width - 1)]           # [B, L]; rows past a sequence's end are never read
+        idx = (pages * ps + (j % ps)[None, :]).reshape(-1).contiguous()
+        table = torch.arange(B, dtype=torch.int32, device=k_cache.device).view(B, 1)
+        cached = batch.cache[key] = (idx, table)
+    idx, table = cached
+    kd, vd = _k().kv_load_fp8(k_cache, v_cache, idx)
+    return kd, vd, table, L
 
 
 def decode_split_len(batch: Batch, splits: int, window: int) -> int:
@@ -405,8 +459,11 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
                                  Dh=Dh, page_size=batch.page_size, splits=sp, split_len=decode_split_len(batch, sp, window),
                                  sinks=sinks, softcap=softcap, window=window)
         else:
-            out = kk.attn_prefill(q, k_cache, v_cache, batch.block_table, batch.kv_lens, batch.cu_q, batch.max_q_len,
-                                  scale=scale, Hq=Hq, Hkv=Hkv, Dh=Dh, page_size=batch.page_size, sinks=sinks,
+            table, ps = batch.block_table, batch.page_size
+            if is_fp8(k_cache):
+                k_cache, v_cache, table, ps = fp8_prefill_view(k_cache, v_cache, batch)
+            out = kk.attn_prefill(q, k_cache, v_cache, table, batch.kv_lens, batch.cu_q, batch.max_q_len,
+                                  scale=scale, Hq=Hq, Hkv=Hkv, Dh=Dh, page_size=ps, sinks=sinks,
                                   softcap=softcap, window=window)
         return out.view(T, Hq * Dh)
     outs = []
@@ -416,7 +473,7 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, bat
         L = batch.h_kv_lens[b]
         pages = batch.block_table[b, :(L + ps - 1) // ps].long()
         idx = (pages.unsqueeze(1) * ps + torch.arange(ps)).reshape(-1)[:L]
-        kb, vb = k_cache[idx], v_cache[idx]
+        kb, vb = kv_gather(k_cache, idx), kv_gather(v_cache, idx)
         outs.append(ref.attention(q[q0:q1], kb, vb, batch.positions[q0:q1], scale=scale, window=window, sinks=sinks,
                                   softcap=softcap))
     return torch.cat(outs, 0).reshape(T, Hq * Dh)

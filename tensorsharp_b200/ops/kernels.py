@@ -436,9 +436,45 @@ def attn_decode(q, k_cache, v_cache, block_table, kv_lens, *, scale, Hq, Hkv, Dh
         oq = torch.empty((B, Hq * Dh), dtype=torch.int8, device=q.device)
         ods = torch.empty((B, Hq * Dh // 32, 2), dtype=torch.float32, device=q.device)
         a.out_q, a.out_ds = oq.data_ptr(), ods.data_ptr()
-    native.check(_lib().tsb_attn_decode(C.byref(a), _stream()), "attn_decode")
+    if k_cache.dtype in FP8_DTYPES:           # e4m3 pages: the split kernel that reads bytes, the same merge kernel
+        lib = _lib()
+        lib.tsb_attn_decode_fp8.restype = C.c_int
+        native.check(lib.tsb_attn_decode_fp8(C.byref(a), _stream()), "attn_decode_fp8")
+    else:
+        native.check(_lib().tsb_attn_decode(C.byref(a), _stream()), "attn_decode")
     _count(2)
     return (out, oq, ods) if want_q8 else out
+
+
+FP8_DTYPES = (torch.float8_e4m3fn,)
+
+
+def kv_store_fp8(k: torch.Tensor, v: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, slots: torch.Tensor) -> None:
+    """Dense bf16 rows ``k`` / ``v`` ``[T, Hkv, Dh]`` -> e4m3 bytes at ``slots`` (int64 ``[T]``) of the paged caches."""
+    assert k.dtype == v.dtype == torch.bfloat16 and k.is_contiguous() and v.is_contiguous() and slots.dtype == torch.int64
+    assert k_cache.dtype in FP8_DTYPES and v_cache.dtype in FP8_DTYPES and k_cache.is_contiguous() and v_cache.is_contiguous()
+    T, Hkv, Dh = k.shape
+    check_index("kv_store_fp8", "cache slot", slots, k_cache.shape[0])
+    lib = _lib()
+    lib.tsb_kv_store_fp8.restype = C.c_int
+    native.check(lib.tsb_kv_store_fp8(_p(k), _p(v), _p(k_cache), _p(v_cache), _p(slots), C.c_long(T), C.c_int(Hkv), C.c_int(Dh),
+                                      _stream()), "kv_store_fp8")
+    _count(1)
+
+
+def kv_load_fp8(k_cache: torch.Tensor, v_cache: torch.Tensor, idx: torch.Tensor):
+    """Rows ``idx`` (int64 ``[n]``) of the e4m3 caches as dense bf16 ``[n, Hkv, Dh]`` tensors (K, V)."""
+    assert k_cache.dtype in FP8_DTYPES and v_cache.dtype in FP8_DTYPES and idx.dtype == torch.int64 and idx.is_contiguous()
+    n, (_, Hkv, Dh) = idx.numel(), k_cache.shape
+    check_index("kv_load_fp8", "cache slot", idx, k_cache.shape[0])
+    ko = torch.empty((n, Hkv, Dh), dtype=torch.bfloat16, device=idx.device)
+    vo = torch.empty_like(ko)
+    lib = _lib()
+    lib.tsb_kv_load_fp8.restype = C.c_int
+    native.check(lib.tsb_kv_load_fp8(_p(k_cache), _p(v_cache), _p(idx), _p(ko), _p(vo), C.c_long(n), C.c_int(Hkv), C.c_int(Dh),
+                                     _stream()), "kv_load_fp8")
+    _count(1)
+    return ko, vo
 
 
 def attn_prefill(q, k_cache, v_cache, block_table, kv_lens, cu_q, max_q_len, *, scale, Hq, Hkv, Dh, page_size,

@@ -48,11 +48,11 @@ class ContinuousBatcher:
         self.steps = 0                 # decode steps run
         self.step_rows = 0             # sequences advanced over all steps (step_rows / steps = mean batch)
         self.graph_steps = 0
-        # TSB_GATHER_GRAPH=1: decode steps replay captured graphs (engine.py: BatchGraphStepper), as the merged steps of the
-        # concurrent server do
+        # decode steps replay captured graphs (engine.py: BatchGraphStepper), as the merged steps of the concurrent
+        # server do; TSB_GATHER_GRAPH=0 keeps them eager
         import os
         self._stepper = None
-        if os.environ.get("TSB_GATHER_GRAPH", "0") == "1":
+        if os.environ.get("TSB_GATHER_GRAPH", "1") != "0":
             from .engine import BatchGraphStepper
             self._stepper = BatchGraphStepper(model, max_batch)
 

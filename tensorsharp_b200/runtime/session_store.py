@@ -22,6 +22,23 @@ def _slots(kv, seq, n: int) -> torch.Tensor:
     return (pages[pos // ps] * ps + pos % ps).to(kv.device)
 
 
+def _rows(t: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+    """``t[slots]``; one-byte element types (the 8-bit cache) are indexed through their bytes."""
+    if t.element_size() == 1:
+        return t.view(torch.uint8)[slots].view(t.dtype)
+    return t[slots]
+
+
+def _set_rows(t: torch.Tensor, slots: torch.Tensor, rows: torch.Tensor) -> None:
+    """``t[slots] = rows`` converted to the cache's element type (a session saved from a bf16 cache loads into an
+    8-bit one and the other way round)."""
+    rows = rows.to(t.device).to(t.dtype) if rows.dtype != t.dtype else rows.to(t.device)
+    if t.element_size() == 1:
+        t.view(torch.uint8)[slots] = rows.view(torch.uint8)
+    else:
+        t[slots] = rows
+
+
 def save_session(path: str, model, cache: KVCache, seq=None) -> int:
     """Write the first ``cache.count`` positions of ``seq`` (default: the model's own sequence)."""
     if not getattr(model, "supports_kv_truncation", True):
@@ -40,8 +57,8 @@ def save_session(path: str, model, cache: KVCache, seq=None) -> int:
             vs.append(None)
             continue
         seen[id(k)] = True
-        ks.append(k[slots].cpu())
-        vs.append(v[slots].cpu())
+        ks.append(_rows(k, slots).cpu())
+        vs.append(_rows(v, slots).cpu())
     logits = cache.next_logits
     torch.save({"arch": model.arch, "n_layers": len(ks), "tokens": list(cache.tokens)[:n],
                 "logits": logits.detach().cpu() if isinstance(logits, torch.Tensor) and n == cache.count else None,
@@ -67,8 +84,8 @@ def load_session(path: str, model, cache: KVCache, seq=None) -> int:
         if k is None or id(k) in seen or d["k"][l] is None:
             continue
         seen[id(k)] = True
-        k[slots] = d["k"][l].to(k.device, k.dtype)
-        v[slots] = d["v"][l].to(v.device, v.dtype)
+        _set_rows(k, slots, d["k"][l])
+        _set_rows(v, slots, d["v"][l])
     cache.reset()
     lg = d["logits"]
     cache.record_append(d["tokens"], lg.to(model.device) if lg is not None else None)

@@ -31,7 +31,7 @@ ENDPOINT_SUMMARY = (
 
 USAGE = ("No startup model configured. Launch with --model <path.gguf> --backend <type> [--mmproj <path>] "
          "[--max-tokens 20000] [--temperature F] [--top-k N] [--top-p F] [--min-p F] [--repeat-penalty F] "
-         "[--presence-penalty F] [--frequency-penalty F] [--seed N] [--stop <text>] [--max-context N] [--max-sessions N] "
+         "[--presence-penalty F] [--frequency-penalty F] [--seed N] [--stop <text>] [--max-context N] [--kv-dtype bf16|fp8] [--max-sessions N] "
          "[--max-batch N] [--replicas N] to use the Web UI.")
 
 

@@ -11,7 +11,7 @@ Hosting/HostedModelGuard.cs.
 Backends here are ``b200`` (the sm_100a kernels) and ``cpu`` (the fp32 oracle path); the
 reference's names ``cuda`` / ``ggml_cuda`` are accepted as aliases of ``b200`` and
 ``ggml_cpu`` of ``cpu`` so existing launch scripts keep working.  This build adds
-``--host --port --max-context --max-sessions --max-batch --replicas --parallel`` (tensor parallelism comes from the
+``--host --port --max-context --kv-dtype --max-sessions --max-batch --replicas --parallel`` (tensor parallelism comes from the
 process count of the launch).
 """
 from __future__ import annotations
@@ -144,7 +144,7 @@ def _parallel_layout(v) -> str:
 def parse_args(args: Sequence[str]) -> Dict[str, object]:
     out: Dict[str, object] = {"sampling": {}, "stop": None}
     plain = (("--model", "model"), ("--mmproj", "mmproj"), ("--backend", "backend"), ("--host", "host"),
-             ("--parallel", "parallel"))
+             ("--parallel", "parallel"), ("--kv-dtype", "kv_dtype"))
     ints = (("--port", "port"), ("--max-context", "max_context"), ("--max-sessions", "max_sessions"),
             ("--max-batch", "max_batch"), ("--replicas", "replicas"))
     i = 0
@@ -237,6 +237,10 @@ def build_options(args: Sequence[str], base_directory: str, env=None,
     log_dir = env.get("TENSORSHARP_LOG_DIR")
     if not log_dir or not log_dir.strip():
         log_dir = os.path.join(base_directory, "logs")
+    if p.get("kv_dtype"):
+        # bf16 (default pages) or fp8 (e4m3 bytes): exported for ModelBase, which every model load of this process reads
+        from ..cli.args import kv_dtype_name
+        os.environ["TSB_KV_DTYPE"] = kv_dtype_name(str(p["kv_dtype"]))
     return ServerHostingOptions(
         startup_model_path=model_path, startup_mmproj_path=mmproj_path, default_backend=default_backend,
         supported_backends=supported, default_web_max_tokens=max_tokens, max_text_file_chars=max_text,

@@ -84,17 +84,21 @@ def test_concurrent_requests_spread_over_the_replicas_and_sessions_stay_put(fron
 
     def one(i):
         results.append(_post(url, "/api/generate", {"model": name, "prompt": f"hello {i}", "stream": False, "options": {"num_predict": 12}}))
-    th = [threading.Thread(target=one, args=(i,)) for i in range(4)]
-    [t.start() for t in th]
-    [t.join(300) for t in th]
-    assert len(results) == 4 and all(st == 200 and json.loads(d)["done"] for st, d in results)
     host, port = url[7:].split(":")
-    c = http.client.HTTPConnection(host, int(port), timeout=30)
-    c.request("GET", "/api/queue/status")
-    q = json.loads(c.getresponse().read())
-    c.close()
-    per = [x["total_processed"] for x in q["replicas"]]
-    assert q["total_processed"] == sum(per) >= 4 and all(n >= 1 for n in per), q       # both replicas did some of the work
+    for burst in range(3):            # on a loaded machine one replica can finish a request before the next one is sent
+        th = [threading.Thread(target=one, args=(i,)) for i in range(4)]
+        [t.start() for t in th]
+        [t.join(300) for t in th]
+        assert len(results) == 4 * (burst + 1) and all(st == 200 and json.loads(d)["done"] for st, d in results)
+        c = http.client.HTTPConnection(host, int(port), timeout=30)
+        c.request("GET", "/api/queue/status")
+        q = json.loads(c.getresponse().read())
+        c.close()
+        per = [x["total_processed"] for x in q["replicas"]]
+        assert q["total_processed"] == sum(per) >= 4 * (burst + 1), q
+        if all(n >= 1 for n in per):
+            break
+    assert all(n >= 1 for n in per), q                                                # both replicas did some of the work
     # a chat session lives on one replica: the second turn finds the first one's cache there
     st, d = _post(url, "/api/sessions", None)
     sid = json.loads(d)["sessionId"]
