@@ -272,9 +272,14 @@ extern "C" int tsb_tpseq_struct_bytes() { return (int)sizeof(TpSeq); }
 //   [0, 256)                      counters: rs_arrive at +0, ag_arrive[size] at +64
 //   [256, 256 + 2*size*shard*ld*2)  the two bf16 accumulators, one slot per source rank
 //   then                            xfull: size*shard*ld bf16
+//   then                            routing records: size*shard*TP_ROUTE_KMAX expert ids (int32), then as many weights (f32)
 extern "C" long tsb_tpseq_region_bytes(int size, int shard, long ld) {
+    return 256 + 2L * size * shard * ld * 2 + (long)size * shard * ld * 2 + 2L * size * shard * TP_ROUTE_KMAX * 4;
+}
+extern "C" long tsb_tpseq_route_offset(int size, int shard, long ld) {
     return 256 + 2L * size * shard * ld * 2 + (long)size * shard * ld * 2;
 }
+extern "C" int tsb_tpseq_route_kmax() { return TP_ROUTE_KMAX; }
 
 // `regions` holds `size` device addresses of the symmetric regions (local one at index rank);
 // `local` is private device memory of >= 16 words: [rs_target, ag_target, rs_phase, -, ticket0,
@@ -302,6 +307,8 @@ extern "C" int tsb_tpseq_init(void* dev_struct, void* const* regions, void* loca
         h.ag_arrive[r] = (unsigned*)(base + 64);
         h.acc[r] = (bf16*)(base + 256);
         h.xfull[r] = (bf16*)(base + 256 + 2L * size * shard * ld * 2);
+        h.route_ids[r] = (int*)(base + tsb_tpseq_route_offset(size, shard, ld));
+        h.route_w[r] = (float*)(h.route_ids[r] + (long)size * shard * TP_ROUTE_KMAX);
     }
     unsigned* c = (unsigned*)local;
     h.rs_target = c; h.ag_target = c + 1; h.rs_phase = c + 2; h.ticket = c + 4; h.status = (int*)(c + 8);
@@ -317,9 +324,13 @@ extern "C" int tsb_tpseq_init(void* dev_struct, void* const* regions, void* loca
 //   then     y = RMSNorm(h[r]) * w  (bf16) stored into row (rank * shard + r) of every rank's gathered
 //            buffer, and one arrival per destination.
 // The last CTA advances the all-gather target (and the reduction phase).
+//   local_only: the normalised rows go to this rank's own gathered buffer and nothing is announced (the expert
+//               dispatch that follows sends them on and counts the arrivals);
+//   acc_k > 0:  the accumulators hold the expert combine: only the slots of the ranks that own one of the row's acc_k
+//               chosen experts (its routing record; `epr` experts per rank) were written, and only those are added.
 template <int NT>
 __global__ void __launch_bounds__(NT) tp_seq_norm_gather_kernel(const TpSeq* g, float* h, const float* w, float eps,
-                                                                int has_acc) {
+                                                                int has_acc, int local_only, int acc_k, int epr) {
     __shared__ float red[32];
     __shared__ int s_ok;
     pdl_wait();
@@ -336,11 +347,21 @@ __global__ void __launch_bounds__(NT) tp_seq_norm_gather_kernel(const TpSeq* g, 
     float* hr = h + (long)r * D;
     const long slot = (long)g->shard * D;
     const bf16* ar = g->acc[g->rank] + (long)(phase & 1u) * g->size * slot + (long)r * D;
+    unsigned srcs = 0xffffffffu;                        // sources whose slot of this row was written
+    if (has_acc && acc_k > 0) {
+        srcs = 0u;
+        const int* rid = g->route_ids[g->rank] + ((long)g->rank * g->shard + r) * acc_k;
+        for (int j = 0; j < acc_k; ++j) {
+            const int e = rid[j];
+            if (e >= 0) srcs |= 1u << (e / epr);
+        }
+    }
     float ss = 0.f;
     for (int i = threadIdx.x * 4; i < D; i += NT * 4) {
         float4 v = *reinterpret_cast<const float4*>(hr + i);
         if (has_acc) {
             for (int src = 0; src < g->size; ++src) {
+                if (!((srcs >> src) & 1u)) continue;
                 const uint2 a = __ldcg(reinterpret_cast<const uint2*>(ar + src * slot + i));   // remote stores: skip L1
                 const float2 lo = __bfloat1622float2(*reinterpret_cast<const bf162*>(&a.x));
                 const float2 hi = __bfloat1622float2(*reinterpret_cast<const bf162*>(&a.y));
@@ -362,7 +383,78 @@ __global__ void __launch_bounds__(NT) tp_seq_norm_gather_kernel(const TpSeq* g, 
         *reinterpret_cast<bf162*>(&o.y) = __floats2bfloat162_rn(a.z * inv * ga.z, a.w * inv * ga.w);
         *reinterpret_cast<bf162*>(&o.z) = __floats2bfloat162_rn(b.x * inv * gb.x, b.y * inv * gb.y);
         *reinterpret_cast<bf162*>(&o.w) = __floats2bfloat162_rn(b.z * inv * gb.z, b.w * inv * gb.w);
-        for (int p = 0; p < g->size; ++p) *reinterpret_cast<uint4*>(g->xfull[p] + grow * D + i) = o;
+        if (local_only) *reinterpret_cast<uint4*>(g->xfull[g->rank] + grow * D + i) = o;
+        else for (int p = 0; p < g->size; ++p) *reinterpret_cast<uint4*>(g->xfull[p] + grow * D + i) = o;
+    }
+    if (!local_only) __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (!local_only)
+            for (int p = 0; p < g->size; ++p) red_release_inc_sys(g->ag_arrive[p] + g->rank);
+        const unsigned done = atomicAdd(g->ticket + 1, 1u);
+        if (done == gridDim.x - 1) {
+            g->ticket[1] = 0;
+            __threadfence();
+            if (!local_only) *g->ag_target += gridDim.x;
+            if (has_acc) *g->rs_phase = phase + 1;
+        }
+    }
+}
+
+static int tpseq_norm_launch(const void* g, float* h_shard, const float* w, float eps, int shard, int D, int has_acc,
+                             int local_only, int acc_k, int epr, void* stream) {
+    TSB_CHECK_ARG(g && h_shard && shard > 0 && D > 0 && D % 8 == 0, "tpseq_norm_gather: bad arguments");
+    TSB_CHECK_ARG(acc_k >= 0 && acc_k <= TP_ROUTE_KMAX && (acc_k == 0 || epr > 0), "tpseq_norm_gather: acc_k=%d epr=%d", acc_k, epr);
+    TSB_CHECK_CUDA(tsb_launch(tp_seq_norm_gather_kernel<256>, dim3(shard), dim3(256), 0, (cudaStream_t)stream,
+                              (const TpSeq*)g, h_shard, w, eps, has_acc, local_only, acc_k, epr));
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}
+
+extern "C" int tsb_tpseq_norm_gather(const void* g, float* h_shard, const float* w, float eps, int shard, int D, int has_acc,
+                                     void* stream) {
+    return tpseq_norm_launch(g, h_shard, w, eps, shard, D, has_acc, 0, 0, 0, stream);
+}
+
+// The same kernel with the expert-parallel options (see the kernel's comment).
+extern "C" int tsb_tpseq_norm_ep(const void* g, float* h_shard, const float* w, float eps, int shard, int D, int has_acc,
+                                 int local_only, int acc_k, int epr, void* stream) {
+    return tpseq_norm_launch(g, h_shard, w, eps, shard, D, has_acc, local_only, acc_k, epr, stream);
+}
+
+// Expert dispatch: one CTA per row of this rank's shard.  The row (already normalised, in this rank's own gathered
+// buffer) is stored into the gathered buffer of every other rank that owns one of its k chosen experts; its routing
+// record goes to every rank (rows at or past T carry id -1 and are sent nowhere); then one arrival per destination, as
+// after the full all-gather, and the last CTA advances the all-gather target.
+__global__ void __launch_bounds__(256) tp_seq_dispatch_kernel(const TpSeq* g, const int* ids, const float* wts, int k, int epr,
+                                                              int T) {
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.x, D = (int)g->ld;
+    const long grow = (long)g->rank * g->shard + r;
+    const bool live = grow < T;
+    unsigned dests = 0u;
+    if (live)
+        for (int j = 0; j < k; ++j) {
+            const int e = ids[(long)r * k + j];
+            if (e >= 0) dests |= 1u << (e / epr);
+        }
+    if ((int)threadIdx.x < k) {
+        const int e = live ? ids[(long)r * k + threadIdx.x] : -1;
+        const float wv = live ? wts[(long)r * k + threadIdx.x] : 0.f;
+        for (int p = 0; p < g->size; ++p) {
+            g->route_ids[p][grow * k + threadIdx.x] = e;
+            g->route_w[p][grow * k + threadIdx.x] = wv;
+        }
+    }
+    dests &= ~(1u << g->rank);
+    if (dests != 0u) {
+        const bf16* src = g->xfull[g->rank] + grow * D;
+        for (int i = threadIdx.x * 8; i < D; i += 256 * 8) {
+            const uint4 v = *reinterpret_cast<const uint4*>(src + i);
+            for (int p = 0; p < g->size; ++p)
+                if ((dests >> p) & 1u) *reinterpret_cast<uint4*>(g->xfull[p] + grow * D + i) = v;
+        }
     }
     __threadfence_system();
     __syncthreads();
@@ -373,16 +465,14 @@ __global__ void __launch_bounds__(NT) tp_seq_norm_gather_kernel(const TpSeq* g, 
             g->ticket[1] = 0;
             __threadfence();
             *g->ag_target += gridDim.x;
-            if (has_acc) *g->rs_phase = phase + 1;
         }
     }
 }
 
-extern "C" int tsb_tpseq_norm_gather(const void* g, float* h_shard, const float* w, float eps, int shard, int D, int has_acc,
-                                     void* stream) {
-    TSB_CHECK_ARG(g && h_shard && shard > 0 && D > 0 && D % 8 == 0, "tpseq_norm_gather: bad arguments");
-    TSB_CHECK_CUDA(tsb_launch(tp_seq_norm_gather_kernel<256>, dim3(shard), dim3(256), 0, (cudaStream_t)stream,
-                              (const TpSeq*)g, h_shard, w, eps, has_acc));
+extern "C" int tsb_tpseq_dispatch(const void* g, const int* ids, const float* wts, int k, int epr, int T, int shard, void* stream) {
+    TSB_CHECK_ARG(g && ids && wts && k >= 1 && k <= TP_ROUTE_KMAX && epr >= 1 && shard > 0, "tpseq_dispatch: bad arguments (k=%d epr=%d)", k, epr);
+    TSB_CHECK_CUDA(tsb_launch(tp_seq_dispatch_kernel, dim3(shard), dim3(256), 0, (cudaStream_t)stream, (const TpSeq*)g, ids, wts, k,
+                              epr, T));
     TSB_CHECK_LAUNCH();
     return TSB_OK;
 }
@@ -407,7 +497,9 @@ extern "C" int tsb_tpseq_wait_all(const void* g, void* stream) {
 // the accumulator of the rank that owns token t, exactly where the GEMM epilogue would have put it, and
 // the arrival counters advance the same way, so tp_seq_norm_gather consumes it unchanged.
 #define TPS_PUSH_ROWS 8
-__global__ void __launch_bounds__(256) tp_seq_push_rows_kernel(const TpSeq* g, const float* partial, int T) {
+// k > 0 (expert combine): only the rows of tokens with one of their k chosen experts in [e0, e1) are stored; the
+// owner skips this rank's slot for the others (tp_seq_norm_gather_kernel, acc_k).
+__global__ void __launch_bounds__(256) tp_seq_push_rows_kernel(const TpSeq* g, const float* partial, int T, int k, int e0, int e1) {
     pdl_wait();
     pdl_trigger();
     const int D = (int)g->ld;
@@ -416,6 +508,12 @@ __global__ void __launch_bounds__(256) tp_seq_push_rows_kernel(const TpSeq* g, c
     bf16* dst = g->acc[owner] + ((long)(*g->rs_phase & 1u) * g->size + g->rank) * g->shard * D - (long)owner * g->shard * D;
     for (int r = 0; r < TPS_PUSH_ROWS; ++r) {
         const int t = row0 + r;
+        if (k > 0) {
+            bool mine = false;
+            const int* rid = g->route_ids[g->rank] + (long)t * k;
+            for (int j = 0; j < k; ++j) mine = mine || (rid[j] >= e0 && rid[j] < e1);
+            if (!mine) continue;                                   // uniform over the block
+        }
         for (int i = threadIdx.x * 8; i < D; i += 256 * 8) {
             uint4 o = make_uint4(0u, 0u, 0u, 0u);
             if (t < T) {
@@ -442,10 +540,22 @@ __global__ void __launch_bounds__(256) tp_seq_push_rows_kernel(const TpSeq* g, c
     }
 }
 
-extern "C" int tsb_tpseq_push_rows(const void* g, const float* partial, int T, int shard, int size, int D, void* stream) {
+static int tpseq_push_launch(const void* g, const float* partial, int T, int shard, int size, int D, int k, int e0, int e1,
+                             void* stream) {
     TSB_CHECK_ARG(g && partial && T >= 0 && shard % TPS_PUSH_ROWS == 0 && D % 8 == 0, "tpseq_push_rows: bad arguments");
+    TSB_CHECK_ARG(k >= 0 && k <= TP_ROUTE_KMAX, "tpseq_push_rows: k=%d", k);
     TSB_CHECK_CUDA(tsb_launch(tp_seq_push_rows_kernel, dim3((unsigned)(shard * size / TPS_PUSH_ROWS)), dim3(256), 0,
-                              (cudaStream_t)stream, (const TpSeq*)g, partial, T));
+                              (cudaStream_t)stream, (const TpSeq*)g, partial, T, k, e0, e1));
     TSB_CHECK_LAUNCH();
     return TSB_OK;
+}
+
+extern "C" int tsb_tpseq_push_rows(const void* g, const float* partial, int T, int shard, int size, int D, void* stream) {
+    return tpseq_push_launch(g, partial, T, shard, size, D, 0, 0, 0, stream);
+}
+
+// The expert combine: rows of tokens that chose none of this rank's experts [e0, e1) are not sent.
+extern "C" int tsb_tpseq_push_rows_ep(const void* g, const float* partial, int T, int shard, int size, int D, int k, int e0,
+                                      int e1, void* stream) {
+    return tpseq_push_launch(g, partial, T, shard, size, D, k, e0, e1, stream);
 }

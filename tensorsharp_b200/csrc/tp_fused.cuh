@@ -48,11 +48,21 @@ struct TpPush {
 // Counters only ever grow; the targets to wait for live in local device memory and are advanced
 // by the kernel that precedes the waiter in stream order, so graph replays need no new arguments.
 // Two accumulators alternate, so a fast rank's next reduction never lands in rows being read.
+//
+// Expert-parallel dispatch / combine on the same buffers and counters (mixture-of-experts layers whose experts are
+// dealt to the ranks in equal ranges): the owner normalises its rows locally, routes them, and stores each row only
+// into the gathered buffers of the ranks that hold one of its chosen experts, while the small routing records (expert
+// ids and weights of every token) go to every rank; arrivals are counted as for the full all-gather, so the waiters do
+// not change.  On the way back a rank stores partial sums only for the tokens it computed, and the owner adds only the
+// slots of the ranks its routing record names.
+#define TP_ROUTE_KMAX 8
 struct TpSeq {
     bf16* acc[TP_MAX_RANKS];             // rank r's accumulators as mapped here: [2][size][shard * ld] bf16, one slot per source
     unsigned* rs_arrive[TP_MAX_RANKS];   // rank r's reduce-scatter arrival counter (one word)
     bf16* xfull[TP_MAX_RANKS];           // rank r's gathered activations: [size * shard, ld] bf16
     unsigned* ag_arrive[TP_MAX_RANKS];   // rank r's all-gather arrival counters: [size], one per source
+    int* route_ids[TP_MAX_RANKS];        // rank r's routing records: expert ids [size * shard * k] (row stride k <= TP_ROUTE_KMAX)
+    float* route_w[TP_MAX_RANKS];        // ... and their weights
     unsigned* rs_target;                 // local: arrivals the next consumer must see
     unsigned* ag_target;                 // local: per-source arrivals the next GEMM must see
     unsigned* rs_phase;                  // local: reductions consumed so far (parity picks the accumulator)

@@ -12,6 +12,7 @@ post_attention_norm.weight, ffn_gate_inp.{weight,bias}, ffn_{gate,up,down}_exps.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -153,9 +154,11 @@ class GptOssModel(ModelBase):
 
     def forward_seq_parallel(self, h_all: torch.Tensor, batch: Batch, want_logits: bool, sp) -> Optional[torch.Tensor]:
         """Tensor + expert parallel prefill on sequence shards: o_proj reduces into the token owners from
-        its GEMM epilogue; the owners' norm kernel scatters the normalised rows to every rank, which is
-        also the expert dispatch (every rank sees every token and keeps those routed to its experts);
-        the summed outputs of a rank's experts are reduce-scattered back to the owners (the combine)."""
+        its GEMM epilogue.  Expert dispatch / combine: the owner normalises and routes its own rows, a kernel stores
+        each row into the gathered buffer of the ranks that hold one of its chosen experts (and the routing records into
+        every rank's), each rank runs its experts on the rows it received, and only those ranks store a partial sum back
+        into the owner's accumulators, which the owner's next norm kernel adds.  With ``TSB_EP_ROUTED=0`` (or experts
+        that do not divide evenly) every row goes to every rank and every rank sends a partial sum back."""
         c = self.cfg
         T = batch.T
         r0 = self.tp_rank * sp.shard
@@ -165,9 +168,30 @@ class GptOssModel(ModelBase):
             h[:mine].copy_(h_all[r0:r0 + mine])
         sp.norm_gather(h, self.layers[0]["attn_norm"], c.eps, False)
         n_layers = len(self.layers)
+        # TSB_EP_ROUTED=0: every row to every rank (all-gather) and a partial sum back from every rank (reduce-scatter)
+        epr = self.n_experts // self.tp_size
+        routed = (os.environ.get("TSB_EP_ROUTED", "1") != "0" and self.n_experts % self.tp_size == 0
+                  and (self.e0, self.e1) == (self.tp_rank * epr, (self.tp_rank + 1) * epr) and self.top_k <= sp.route_kmax)
         for l, L in enumerate(self.layers):
             o = self.attention_block(None, L, l, batch, torch.bfloat16, lambda w, b: sp.gemm_ag(w, T, bias=b))
             sp.gemm_rs(o.view(T, -1), L["wo"], bias=L["bo"])
+            nxt = self.layers[l + 1]["attn_norm"] if l + 1 < n_layers else self.out_norm
+            if routed:
+                # dispatch / combine by destination: the owner routes its own rows and sends each one only to the ranks
+                # that hold one of its experts; only those ranks send a partial sum back
+                sp.norm_gather(h, L["ffn_norm"], c.eps, True, local_only=True)
+                mine_rows = Act(sp.xfull[sp.rows])
+                logits = F.linear(mine_rows, L["router"], bias=L["router_bias"], out_dtype=torch.float32)
+                ids, w = F.route_topk_softmax(logits, self.top_k)
+                sp.dispatch(ids, w, T, epr)
+                sp.wait_all()
+                ids, w = sp.routes(T, self.top_k)
+                a = Act(sp.xfull[:T])
+                y = F.moe_experts(a, ids, w, L["gate_up_exps"], L["down_exps"], act="swiglu_oai", gate_up_bias=L["gate_up_bias"],
+                                  down_bias=L["down_bias"], expert_offset=self.e0)
+                sp.push_rows(y.contiguous(), T, k_routed=self.top_k, e0=self.e0, e1=self.e1)
+                sp.norm_gather(h, nxt, c.eps, True, acc_k=self.top_k, experts_per_rank=epr)
+                continue
             sp.norm_gather(h, L["ffn_norm"], c.eps, True)
             sp.wait_all()                                            # the router and the experts read the gathered rows
             a = Act(sp.xfull[:T])
@@ -176,7 +200,7 @@ class GptOssModel(ModelBase):
             y = F.moe_experts(a, ids, w, L["gate_up_exps"], L["down_exps"], act="swiglu_oai", gate_up_bias=L["gate_up_bias"],
                               down_bias=L["down_bias"], expert_offset=self.e0)
             sp.push_rows(y.contiguous(), T)
-            sp.norm_gather(h, self.layers[l + 1]["attn_norm"] if l + 1 < n_layers else self.out_norm, c.eps, True)
+            sp.norm_gather(h, nxt, c.eps, True)
         if not want_logits:
             return None
         sp.wait_all()

@@ -153,6 +153,9 @@ class TpSeqParallel:
       stores the rows into every rank's gathered buffer (all-gather inside the norm kernel),
     * ``gemm_ag``  column-parallel GEMM on the gathered buffer whose TMA producer waits per token
       tile for the shard it needs (all-gather -> GEMM).
+    * ``norm_gather(local_only=True)`` + ``dispatch`` + ``push_rows(k_routed=...)`` + ``norm_gather(acc_k=...)``:
+      expert-parallel dispatch and combine, in which a token's row travels only to the ranks that hold its experts and
+      only their partial sums travel back.
     """
 
     def __init__(self, comm, max_tokens: int, hidden: int):
@@ -161,9 +164,10 @@ class TpSeqParallel:
         self.shard = ((max_tokens + n - 1) // n + 127) // 128 * 128
         lib = _lib()
         for name in ("tsb_tpseq_struct_bytes", "tsb_tpseq_init", "tsb_tpseq_norm_gather", "tsb_tpseq_wait_all",
-                     "tsb_gemm_bf16_tp"):
+                     "tsb_gemm_bf16_tp", "tsb_tpseq_norm_ep", "tsb_tpseq_dispatch", "tsb_tpseq_push_rows_ep", "tsb_tpseq_route_kmax"):
             getattr(lib, name).restype = C.c_int
         lib.tsb_tpseq_region_bytes.restype = C.c_long
+        lib.tsb_tpseq_route_offset.restype = C.c_long
         self.region = SymmetricBuffer(comm, lib.tsb_tpseq_region_bytes(C.c_int(n), C.c_int(self.shard), C.c_long(self.hidden)))
         dev = comm.device
         self.local = torch.zeros(16, dtype=torch.int32, device=dev)
@@ -174,6 +178,15 @@ class TpSeqParallel:
                                         C.c_int(self.shard), C.c_long(self.hidden)), "tpseq_init")
         xoff = 256 + 2 * n * self.shard * self.hidden * 2
         self.xfull = tensor_from_ptr(self.region.local + xoff, (n * self.shard, self.hidden), torch.bfloat16, dev)
+        # routing records of the expert dispatch: ids and weights of every token, row stride = the model's top-k
+        self.route_kmax = int(lib.tsb_tpseq_route_kmax())
+        roff = int(lib.tsb_tpseq_route_offset(C.c_int(n), C.c_int(self.shard), C.c_long(self.hidden)))
+        cells = n * self.shard * self.route_kmax
+        self._route_ids = tensor_from_ptr(self.region.local + roff, (cells,), torch.int32, dev)
+        self._route_w = tensor_from_ptr(self.region.local + roff + cells * 4, (cells,), torch.float32, dev)
+        self._route_ids.fill_(-1)
+        self._route_w.zero_()
+        torch.cuda.synchronize(dev)
         comm.barrier()
 
     @property
@@ -203,13 +216,39 @@ class TpSeqParallel:
         assert x.shape[0] <= self.comm.size * self.shard and w.N == self.hidden
         self._gemm(F._dequant_scratch(w), x.contiguous(), None, bias, x.shape[0], True, False)
 
-    def norm_gather(self, h_shard: torch.Tensor, w: Optional[torch.Tensor], eps: float, has_acc: bool) -> None:
+    def norm_gather(self, h_shard: torch.Tensor, w: Optional[torch.Tensor], eps: float, has_acc: bool, *,
+                    local_only: bool = False, acc_k: int = 0, experts_per_rank: int = 0) -> None:
+        """``local_only``: keep the normalised rows here (``dispatch`` sends them on); ``acc_k``: the accumulators hold
+        an expert combine, add only the slots of the ranks that own one of the row's ``acc_k`` chosen experts."""
         from ..ops import kernels as k
         assert h_shard.dtype == torch.float32 and h_shard.shape == (self.shard, self.hidden) and h_shard.is_contiguous()
-        native.check(k._lib().tsb_tpseq_norm_gather(C.c_void_p(self.struct.data_ptr()), k._p(h_shard), k._p(w), C.c_float(eps),
+        if local_only or acc_k:
+            native.check(k._lib().tsb_tpseq_norm_ep(C.c_void_p(self.struct.data_ptr()), k._p(h_shard), k._p(w), C.c_float(eps),
                                                     C.c_int(self.shard), C.c_int(self.hidden), C.c_int(1 if has_acc else 0),
-                                                    k._stream()), "tpseq_norm_gather")
+                                                    C.c_int(1 if local_only else 0), C.c_int(acc_k), C.c_int(experts_per_rank),
+                                                    k._stream()), "tpseq_norm_ep")
+        else:
+            native.check(k._lib().tsb_tpseq_norm_gather(C.c_void_p(self.struct.data_ptr()), k._p(h_shard), k._p(w), C.c_float(eps),
+                                                        C.c_int(self.shard), C.c_int(self.hidden), C.c_int(1 if has_acc else 0),
+                                                        k._stream()), "tpseq_norm_gather")
         k._count(1)
+
+    def dispatch(self, ids: torch.Tensor, weights: torch.Tensor, T: int, experts_per_rank: int) -> None:
+        """Expert dispatch of this rank's shard: ``ids`` / ``weights`` ``[shard, k]`` are the router's choices for its
+        (locally normalised) rows; each row goes to the ranks that own one of its experts, the routing records to all."""
+        from ..ops import kernels as k
+        kk = ids.shape[1]
+        assert ids.shape == (self.shard, kk) == tuple(weights.shape) and kk <= self.route_kmax
+        ids = ids.to(torch.int32).contiguous()
+        weights = weights.float().contiguous()
+        native.check(k._lib().tsb_tpseq_dispatch(C.c_void_p(self.struct.data_ptr()), k._p(ids), k._p(weights), C.c_int(kk),
+                                                 C.c_int(experts_per_rank), C.c_int(T), C.c_int(self.shard), k._stream()),
+                     "tpseq_dispatch")
+        k._count(1)
+
+    def routes(self, T: int, kk: int):
+        """The routing records of the first ``T`` tokens as ``(ids [T, k] int32, weights [T, k] f32)`` views."""
+        return self._route_ids[:T * kk].view(T, kk), self._route_w[:T * kk].view(T, kk)
 
     def gemm_ag(self, w: QuantWeight, T: int, bias: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16) -> torch.Tensor:
         """``gathered[:T] @ w^T`` (+ bias); tiles start as soon as their shard has arrived."""
@@ -218,14 +257,21 @@ class TpSeqParallel:
         self._gemm(F._dequant_scratch(w), self.xfull, out, bias, T, False, True)
         return out
 
-    def push_rows(self, partial: torch.Tensor, T: int) -> None:
+    def push_rows(self, partial: torch.Tensor, T: int, *, k_routed: int = 0, e0: int = 0, e1: int = 0) -> None:
         """Reduce-scatter a partial ``[T, hidden]`` f32 sum that no GEMM epilogue produced (the summed
-        outputs of this rank's experts): same destination and counters as ``gemm_rs``."""
+        outputs of this rank's experts): same destination and counters as ``gemm_rs``.  ``k_routed``: after a
+        ``dispatch`` with that top-k, only the rows of tokens that chose one of the experts ``[e0, e1)`` are sent."""
         from ..ops import kernels as k
         assert partial.dtype == torch.float32 and partial.is_contiguous() and partial.shape[1] == self.hidden
-        native.check(k._lib().tsb_tpseq_push_rows(C.c_void_p(self.struct.data_ptr()), k._p(partial), C.c_int(T),
-                                                  C.c_int(self.shard), C.c_int(self.comm.size), C.c_int(self.hidden),
-                                                  k._stream()), "tpseq_push_rows")
+        if k_routed:
+            native.check(k._lib().tsb_tpseq_push_rows_ep(C.c_void_p(self.struct.data_ptr()), k._p(partial), C.c_int(T),
+                                                         C.c_int(self.shard), C.c_int(self.comm.size), C.c_int(self.hidden),
+                                                         C.c_int(k_routed), C.c_int(e0), C.c_int(e1), k._stream()),
+                         "tpseq_push_rows_ep")
+        else:
+            native.check(k._lib().tsb_tpseq_push_rows(C.c_void_p(self.struct.data_ptr()), k._p(partial), C.c_int(T),
+                                                      C.c_int(self.shard), C.c_int(self.comm.size), C.c_int(self.hidden),
+                                                      k._stream()), "tpseq_push_rows")
         k._count(1)
 
     def wait_all(self) -> None:

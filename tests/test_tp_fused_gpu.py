@@ -73,6 +73,10 @@ def check_result(r):
     # sequence-parallel prefill: same logits as the NCCL path and as one GPU (bf16 GEMMs on both sides)
     assert r["seq_status"] == 0
     assert r["seq_vs_nccl"] <= 3e-2 * max(1.0, r["scale"]) and r["seq_next_vs_nccl"] <= 3e-2 * max(1.0, r["scale"])
+    # mixture of experts: rows sent only to the ranks that hold their experts give what rows sent to every rank give
+    # (the skipped partial sums are zeros)
+    if r.get("routed_vs_allgather") is not None:
+        assert r["routed_vs_allgather"] <= 1e-5 * max(1.0, r["scale"]), r
     assert r["seq_vs_single"] <= 3e-2 * max(1.0, r["scale"])
 
 

@@ -252,6 +252,14 @@ def check_model(path, comm):
     seq_next = model.forward([int(seq_logits.argmax())]).float().clone()     # decode on the cache the prefill wrote
     sp = getattr(model, "_tpseq", None)
     seq_status = sp.status() if sp is not None else -1
+    # expert dispatch by destination against the all-gather form of the same exchange (mixture-of-experts models only)
+    routed_diff = None
+    if model.arch == "gpt-oss" or hasattr(model, "n_experts"):
+        os.environ["TSB_EP_ROUTED"] = "0"
+        model.reset_kv_cache()
+        routed_diff = float((model.forward(long_prompt).float() - seq_logits).abs().max())
+        os.environ["TSB_EP_ROUTED"] = "1"
+        seq_status |= sp.status() if sp is not None else -1
     model._tpx = False                                          # NCCL all-reduce path on the same weights
     os.environ["TSB_TP_FUSED"] = "0"
     nccl = run(model)
@@ -262,7 +270,7 @@ def check_model(path, comm):
     res = {"world": world, "arch": model.arch, "status": status, "exchanges": exchanges,
            "fused_vs_nccl": float((fused - nccl).abs().max()), "graph_tokens": graph_tokens, "eager_tokens": eager_tokens,
            "seq_status": seq_status, "seq_vs_nccl": float((seq_logits - nccl_long).abs().max()),
-           "seq_next_vs_nccl": float((seq_next - nccl_next).abs().max())}
+           "seq_next_vs_nccl": float((seq_next - nccl_next).abs().max()), "routed_vs_allgather": routed_diff}
     if rank == 0:
         single = ModelBase.create(path, comm.device, max_context=512)
         ref = run(single)
