@@ -76,3 +76,18 @@ def test_fp8_cache_is_refused_where_it_has_no_path(tiny_qwen3_path, monkeypatch)
     monkeypatch.setenv("TSB_KV_DTYPE", "fp8")
     with pytest.raises(ValueError, match="8-bit KV cache"):
         ModelBase.create(tiny_qwen3_path, "cpu", max_context=64, cp_comm=FakeComm())
+
+
+def test_kv_dtype_option_of_the_cli_and_the_server(monkeypatch, tmp_path):
+    from tensorsharp_b200.cli.args import parse_cli_args
+    from tensorsharp_b200.server import options as O
+    assert parse_cli_args(["--model", "m.gguf", "--kv-dtype", "FP8"]).kv_dtype == "fp8"
+    assert parse_cli_args(["--model", "m.gguf"]).kv_dtype is None
+    with pytest.raises(ValueError, match="--kv-dtype"):
+        parse_cli_args(["--kv-dtype", "int3"])
+    monkeypatch.delenv("TSB_KV_DTYPE", raising=False)
+    assert O.parse_args(["--kv-dtype", "e4m3", "--port", "5001"])["kv_dtype"] == "e4m3"
+    O.build_options(["--kv-dtype", "e4m3"], str(tmp_path), env={})
+    import os
+    assert os.environ.get("TSB_KV_DTYPE") == "fp8"
+    monkeypatch.delenv("TSB_KV_DTYPE", raising=False)
