@@ -41,8 +41,8 @@ def time_us(fn, iters: int, warmup: int) -> float:
 def recurrent(args):
     """The token-by-token scan kernel against the chunked form (tensor ops) on one prompt of ``--t`` tokens, at the
     Qwen3.5-35B-A3B GatedDeltaNet shape (16 QK / 32 V heads x 128) or the Nemotron-H Mamba2 shape (64 heads x 64,
-    8 groups, state 128).  Prints both times and the distance between the two outputs; for GatedDeltaNet also the
-    chunked form with its chunk-after-chunk part as one kernel (csrc/gdn_chunk.cu)."""
+    8 groups, state 128).  Prints both times and the distance between the two outputs, then the chunked form with its
+    chunk-after-chunk part as one kernel and with the chunk-parallel part as a kernel too (csrc/gdn_chunk.cu)."""
     import torch
     from tensorsharp_b200.ops import kernels
     from tensorsharp_b200.ops import reference as ref
@@ -85,6 +85,12 @@ def recurrent(args):
             s1.zero_()
             return ref.mamba2_chunked(xbc, dt, dt_bias, A, D, s1, chunk=args.chunk, **kw)
     fused = None
+    if args.op == "mamba2":
+        s2 = torch.zeros_like(s1)
+
+        def fused():
+            s2.zero_()
+            return ref.mamba2_chunked(xbc, dt, dt_bias, A, D, s2, chunk=64, carry=kernels.gdn_chunk_carry, **kw)
     if args.op == "gdn":
         s2 = torch.zeros_like(s1)
 
@@ -98,6 +104,12 @@ def recurrent(args):
         def kern3():
             s3.zero_()
             return kernels.gdn_chunked(qkv, z, beta, alpha, dt_bias, a_log, norm_w, s3, cu_q, [0, T], [0], **kw)
+    if args.op == "mamba2":
+        s3 = torch.zeros(1, H, P, N, device=dev)
+
+        def kern3():
+            s3.zero_()
+            return kernels.mamba2_chunked(xbc, dt, dt_bias, A, D, s3, cu_q, [0, T], [0], **kw)
     a, b = scan().float(), chunked().float()
     rel = float((a - b).norm() / b.norm())
     srel = float((s0[0] - s1).norm() / s1.norm())

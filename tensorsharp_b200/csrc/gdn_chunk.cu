@@ -476,6 +476,148 @@ extern "C" int tsb_gdn_chunk_prep(const GdnPrepArgs* args, void* stream) {
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// Mamba2 in chunked (state-space duality) form: the chunk-parallel part for one (sequence, head, chunk).  With
+// d = softplus(dt + bias), log-decay c = cumsum(d * A) inside the chunk, inputs X = d * x, and the group's B / C rows:
+//   U0 = X                       what a token writes
+//   Qd = C * exp(c)              reads of the state entering the chunk
+//   Kd = B * exp(c_last - c)     writes that survive to the chunk's end
+//   P  = (C B^T) * exp(c_i - c_j) for j <= i, else 0        contributions inside the chunk
+//   gamma = exp(c_last)
+// which is exactly what gdn_chunk_carry_kernel consumes with W = 0: out = Qd S^T + P U0, S <- gamma S + U0^T Kd.
+// Reference: the ssm_scan path of ggml (ggml-cuda/ssm-scan.cu) is a token-by-token scan; the chunked form is this
+// framework's own.
+// ------------------------------------------------------------------------------------------
+struct MambaPrepArgs {
+    const float* xbc; long xbc_s;          // [T, H Pd + 2 G N] rows: x heads | B groups | C groups
+    const void* dt; long dt_s; int dt_f32; // [T, H]
+    const float* dt_bias; const float* A;  // [H] (dt_bias may be null)
+    const int* cu_q;                       // [B + 1]
+    float* U0; float* Qd; float* Kd; float* P; float* gamma;
+    int H, Pd, G, N, B, nc;
+};
+
+template <int DK>
+__global__ void __launch_bounds__(256) mamba2_chunk_prep_kernel(MambaPrepArgs a) {
+    constexpr int LQ = DK + 4;
+    extern __shared__ __align__(16) float sm[];
+    float* sK = sm;                        // [64][LQ] B rows
+    float* sQ = sK + GC * LQ;              // [64][LQ] C rows
+    float* sc = sQ + GC * LQ;              // [64] running log-decay
+    float* sd = sc + GC;                   // [64] step size d
+    const int c = blockIdx.x, bh = blockIdx.y, b = bh / a.H, h = bh % a.H, grp = h / (a.H / a.G);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = a.cu_q[b], len = a.cu_q[b + 1] - row0;
+    const int valid = max(0, min(GC, len - c * GC));
+    const long tok0 = (long)row0 + (long)c * GC;
+    const long ch = (long)bh * a.nc + c;
+    const int Pd = a.Pd;
+    const long offB = (long)a.H * Pd + (long)grp * DK, offC = offB + (long)a.G * DK;
+    for (int r = warp; r < GC; r += 8) {
+        const bool ok = r < valid;
+        const float* row = a.xbc + (tok0 + r) * a.xbc_s;
+#pragma unroll
+        for (int i = 0; i < DK / 32; ++i) {
+            sK[r * LQ + lane + 32 * i] = ok ? row[offB + lane + 32 * i] : 0.f;
+            sQ[r * LQ + lane + 32 * i] = ok ? row[offC + lane + 32 * i] : 0.f;
+        }
+        float d = 0.f;
+        if (ok) {
+            const long di = (tok0 + r) * a.dt_s + h;
+            const float v = (a.dt_f32 ? reinterpret_cast<const float*>(a.dt)[di] : bf2f(reinterpret_cast<const bf16*>(a.dt)[di])) +
+                            (a.dt_bias ? a.dt_bias[h] : 0.f);
+            d = v > 20.f ? v : log1pf(__expf(v));
+        }
+        for (int e = lane; e < Pd; e += 32) a.U0[(ch * GC + r) * Pd + e] = ok ? row[(long)h * Pd + e] * d : 0.f;
+        if (lane == 0) {
+            sd[r] = d;
+            sc[r] = d * a.A[h];
+        }
+    }
+    __syncthreads();
+    if (warp == 0) {                       // inclusive running sum over the 64 tokens
+        float x0 = sc[lane], x1 = sc[lane + 32];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float y0 = __shfl_up_sync(0xffffffffu, x0, o), y1 = __shfl_up_sync(0xffffffffu, x1, o);
+            if (lane >= o) { x0 += y0; x1 += y1; }
+        }
+        x1 += __shfl_sync(0xffffffffu, x0, 31);
+        sc[lane] = x0;
+        sc[lane + 32] = x1;
+    }
+    __syncthreads();
+    const float c_last = sc[GC - 1];
+    // ---- C B^T: warp -> rows mt * 16 .. + 15, columns nq * 32 .. + 31 (split tf32: three products per term)
+    {
+        const int g = lane >> 2, t = lane & 3, mt = warp & 3, nq = warp >> 2;
+        float qk[4][4] = {};
+#pragma unroll 2
+        for (int k0 = 0; k0 < DK; k0 += 8) {
+            uint32_t qh[4], ql[4];
+            const float* qp = sQ + (mt * 16 + g) * LQ + k0 + t;
+            split_tf32(qp[0], qh[0], ql[0]); split_tf32(qp[8 * LQ], qh[1], ql[1]);
+            split_tf32(qp[4], qh[2], ql[2]); split_tf32(qp[8 * LQ + 4], qh[3], ql[3]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float* bp = sK + ((nq * 4 + j) * 8 + g) * LQ + k0 + t;
+                uint32_t b0h, b0l, b1h, b1l;
+                split_tf32(bp[0], b0h, b0l);
+                split_tf32(bp[4], b1h, b1l);
+                mma_tf32(qk[j], ql, b0h, b1h); mma_tf32(qk[j], qh, b0l, b1l); mma_tf32(qk[j], qh, b0h, b1h);
+            }
+        }
+        float* Pg = a.P + ch * GC * GC;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = mt * 16 + g + (e >> 1) * 8, jj = (nq * 4 + j) * 8 + 2 * t + (e & 1);
+                Pg[i * GC + jj] = jj <= i ? qk[j][e] * __expf(fminf(sc[i] - sc[jj], 0.f)) : 0.f;
+            }
+        }
+    }
+    for (int r = warp; r < GC; r += 8) {
+        const float dec = __expf(sc[r]), tail = __expf(c_last - sc[r]);
+#pragma unroll
+        for (int i = 0; i < DK / 32; ++i) {
+            const int d = lane + 32 * i;
+            a.Kd[(ch * GC + r) * DK + d] = sK[r * LQ + d] * tail;
+            a.Qd[(ch * GC + r) * DK + d] = sQ[r * LQ + d] * dec;
+        }
+    }
+    if (threadIdx.x == 0) a.gamma[ch] = __expf(c_last);
+}
+
+template <int DK>
+static int launch_mamba_prep(const MambaPrepArgs& a, cudaStream_t s) {
+    const size_t smem = ((size_t)2 * GC * (DK + 4) + 2 * GC) * sizeof(float);
+    static size_t configured = 0;
+    if (smem > configured) {
+        TSB_CHECK_CUDA(cudaFuncSetAttribute(mamba2_chunk_prep_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
+    }
+    mamba2_chunk_prep_kernel<DK><<<dim3(a.nc, a.B * a.H), 256, smem, s>>>(a);
+    TSB_CHECK_LAUNCH();
+    return TSB_OK;
+}
+
+extern "C" int tsb_mamba2_chunk_prep(const MambaPrepArgs* args, void* stream) {
+    TSB_CHECK_ARG(args != nullptr, "mamba2_chunk_prep: null arguments");
+    const MambaPrepArgs& a = *args;
+    TSB_CHECK_ARG(a.B > 0 && a.nc > 0 && a.H > 0 && a.G > 0 && a.H % a.G == 0, "mamba2_chunk_prep: B=%d chunks=%d heads=%d groups=%d", a.B, a.nc,
+                  a.H, a.G);
+    TSB_CHECK_ARG(a.Pd > 0, "mamba2_chunk_prep: head size %d", a.Pd);
+    TSB_CHECK_ARG((long)a.B * a.H <= 65535, "mamba2_chunk_prep: %d x %d sequence-heads exceed the grid", a.B, a.H);
+    switch (a.N) {
+    case 64: return launch_mamba_prep<64>(a, (cudaStream_t)stream);
+    case 128: return launch_mamba_prep<128>(a, (cudaStream_t)stream);
+    default:
+        tsb_set_error("mamba2_chunk_prep: state size %d unsupported (64, 128)", a.N);
+        return TSB_ERR_UNSUPPORTED;
+    }
+}
+
 extern "C" int tsb_gdn_chunk_finish(const GdnFinishArgs* args, void* stream) {
     TSB_CHECK_ARG(args != nullptr, "gdn_chunk_finish: null arguments");
     const GdnFinishArgs& a = *args;

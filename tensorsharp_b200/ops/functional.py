@@ -752,6 +752,12 @@ def mamba2(xbc: torch.Tensor, dt: torch.Tensor, dt_bias, A, D, state: torch.Tens
         return _k().mamba2_recurrent(xbc, dt, dt_bias, A, D, state, batch.cu_q, batch.seq_slots, H=H, P=P, G=G, N=N)
     outs = []
     slots = batch.seq_slots.tolist()
+    if (chunked and xbc.is_cuda and os.environ.get("TSB_MAMBA_CHUNK_KERNELS", "1") != "0"
+            and os.environ.get("TSB_MAMBA_CARRY_KERNEL", "1") != "0" and _k().mamba2_chunked_supported(N, P)
+            and _k().gdn_chunk_carry_supported(N, P, 64) and state.dtype == torch.float32 and xbc.dtype == torch.float32
+            and batch.B * H <= 65535):
+        # the whole batch in two kernels: the chunk-parallel algebra, then the chunk-carry kernel of the delta rule
+        return _k().mamba2_chunked(xbc, dt, dt_bias, A, D, state, batch.cu_q, batch.h_cu_q, slots, H=H, P=P, G=G, N=N)
     scan = ref.mamba2_chunked if chunked else ref.mamba2_recurrent
     kw = {}
     if chunked and xbc.is_cuda and os.environ.get("TSB_MAMBA_CARRY_KERNEL", "1") != "0" and _k().gdn_chunk_carry_supported(N, P, 64) \

@@ -683,6 +683,59 @@ def gdn_chunked(qkv, z, beta, alpha, dt_bias, a_log, norm_w, state, cu_q, h_cu_q
     return out
 
 
+class MambaPrepArgs(C.Structure):
+    _fields_ = [("xbc", _vp), ("xbc_s", C.c_long), ("dt", _vp), ("dt_s", C.c_long), ("dt_f32", C.c_int),
+                ("dt_bias", _vp), ("A", _vp), ("cu_q", _vp),
+                ("U0", _vp), ("Qd", _vp), ("Kd", _vp), ("P", _vp), ("gamma", _vp),
+                ("H", C.c_int), ("Pd", C.c_int), ("G", C.c_int), ("N", C.c_int), ("B", C.c_int), ("nc", C.c_int)]
+
+
+def mamba2_chunked_supported(N: int, P: int) -> bool:
+    return N in (64, 128) and P % 32 == 0
+
+
+def mamba2_chunked(xbc, dt, dt_bias, A, D, state, cu_q, h_cu_q, slots, *, H, P, G, N) -> torch.Tensor:
+    """Chunked Mamba2 prefill of a packed batch in two kernels (csrc/gdn_chunk.cu): the chunk-parallel algebra per
+    (sequence, head, chunk) - step sizes, running decay, C B^T with its decay mask, decayed reads and writes - and the
+    chunk-carry kernel of the delta rule with nothing to correct.  ``xbc`` f32 [T, H P + 2 G N] (after the convolution),
+    ``state`` [slots, H, P, N] f32 updated for the sequences' slots.  Returns y f32 [T, H * P] (skip term included)."""
+    T = xbc.shape[0]
+    B = len(h_cu_q) - 1
+    nc = (max(h_cu_q[i + 1] - h_cu_q[i] for i in range(B)) + 63) // 64
+    dev = xbc.device
+    assert xbc.dtype == torch.float32 and xbc.stride(1) == 1 and dt.stride(1) == 1 and state.dtype == torch.float32
+    BH = B * H
+    f32 = dict(dtype=torch.float32, device=dev)
+    U0, W = torch.empty((BH, nc, 64, P), **f32), torch.zeros((BH, nc, 64, N), **f32)
+    Qd, Kd = torch.empty((BH, nc, 64, N), **f32), torch.empty((BH, nc, 64, N), **f32)
+    Pm, gamma = torch.empty((BH, nc, 64, 64), **f32), torch.empty((BH, nc), **f32)
+    a = MambaPrepArgs()
+    a.xbc, a.xbc_s = _p(xbc), xbc.stride(0)
+    a.dt, a.dt_s, a.dt_f32 = _p(dt), dt.stride(0), int(dt.dtype == torch.float32)
+    a.dt_bias, a.A, a.cu_q = _p(dt_bias.float().contiguous() if dt_bias is not None else None), _p(A.float().contiguous()), _p(cu_q)
+    a.U0, a.Qd, a.Kd, a.P, a.gamma = _p(U0), _p(Qd), _p(Kd), _p(Pm), _p(gamma)
+    a.H, a.Pd, a.G, a.N, a.B, a.nc = H, P, G, N, B, nc
+    lib = _lib()
+    lib.tsb_mamba2_chunk_prep.restype = C.c_int
+    native.check(lib.tsb_mamba2_chunk_prep(C.byref(a), _stream()), "mamba2_chunk_prep")
+    _count(1)
+    if B == 1:
+        S = state[slots[0]]
+    else:
+        idx = torch.tensor(slots, dtype=torch.long, device=dev)
+        S = state[idx].reshape(BH, P, N)
+    core = gdn_chunk_carry(U0, W, Qd, Kd, Pm, gamma, S)              # [BH, nc, 64, P]
+    if B > 1:
+        state[idx] = S.view(B, H, P, N)
+    y = torch.empty((T, H, P), **f32)
+    for b in range(B):
+        q0, n = h_cu_q[b], h_cu_q[b + 1] - h_cu_q[b]
+        y[q0:q0 + n] = core[b * H:(b + 1) * H].reshape(H, nc * 64, P)[:, :n].transpose(0, 1)
+    if D is not None:
+        y = y + D.float().view(1, H, 1) * xbc[:, :H * P].view(T, H, P)
+    return y.view(T, H * P)
+
+
 def gdn_chunk_carry(U0, W, Qd, Kd, P, gamma, state) -> torch.Tensor:
     """The sequential part of the chunked GatedDeltaNet prefill for one sequence: ``state`` [Hv, Dv, Dk] f32 (contiguous,
     updated in place) carried through the chunks of U0 [Hv, nc, 64, Dv], W / Qd / Kd [Hv, nc, 64, Dk], P [Hv, nc, 64, 64],

@@ -90,3 +90,33 @@ def test_chunk_carry_kernel_matches_the_scan_across_chunk_and_call_boundaries(mo
     assert _rel(full[0], scan[0]) < 2e-2 and _rel(full[1], scan[1]) < 3e-3, (_rel(full[0], scan[0]), _rel(full[1], scan[1]))
     assert _rel(kern[0], loop[0]) < 1e-2 and _rel(kern[1], loop[1]) < 3e-3, (_rel(kern[0], loop[0]), _rel(kern[1], loop[1]))
     assert _rel(kern[0], scan[0]) < 2e-2 and _rel(kern[1], scan[1]) < 3e-3, (_rel(kern[0], scan[0]), _rel(kern[1], scan[1]))
+
+
+@pytest.mark.parametrize("H,P,G,N", [(4, 64, 2, 128), (6, 32, 1, 64), (8, 64, 8, 128)])
+def test_mamba2_chunk_kernels_match_the_scan_across_chunk_and_call_boundaries(monkeypatch, H, P, G, N):
+    """csrc/gdn_chunk.cu: mamba2_chunk_prep_kernel + the chunk-carry kernel against the token-by-token scan kernel and
+    against the chunked algebra as tensor ops: odd lengths, two sequences in a call, a state that is not zero, and calls
+    that continue from the state the previous one left."""
+    torch.manual_seed(3)
+    dev = "cuda"
+    A, D, dtb = -torch.rand(H, device=dev), torch.randn(H, device=dev), torch.randn(H, device=dev) * 0.5
+    s0 = torch.randn(2, H, P, N, device=dev) * 0.1
+    results = {}
+    # scan kernel; chunked tensor ops; tensor ops + carry kernel; prep kernel + carry kernel
+    for mode, carry, kernels in (("0", "1", "1"), ("1", "0", "0"), ("1", "1", "0"), ("1", "1", "1")):
+        monkeypatch.setenv("TSB_MAMBA_CHUNKED", mode)
+        monkeypatch.setenv("TSB_MAMBA_CARRY_KERNEL", carry)
+        monkeypatch.setenv("TSB_MAMBA_CHUNK_KERNELS", kernels)
+        torch.manual_seed(4)
+        st = s0.clone()
+        outs = []
+        for lens in ([333], [129, 64], [70]):
+            T = sum(lens)
+            xbc, dt = torch.randn(T, H * P + 2 * G * N, device=dev), torch.randn(T, H, device=dev)
+            outs.append(F.mamba2(xbc, dt, dtb, A, D, st, _batch(lens, dev), H=H, P=P, G=G, N=N).float())
+        results[(mode, carry, kernels)] = (torch.cat(outs), st)
+    scan, loop, kern, full = results[("0", "1", "1")], results[("1", "0", "0")], results[("1", "1", "0")], results[("1", "1", "1")]
+    assert _rel(loop[0], scan[0]) < 1e-3 and _rel(loop[1], scan[1]) < 1e-3
+    assert _rel(kern[0], scan[0]) < 5e-3 and _rel(kern[1], scan[1]) < 5e-3, (_rel(kern[0], scan[0]), _rel(kern[1], scan[1]))
+    assert _rel(full[0], scan[0]) < 5e-3 and _rel(full[1], scan[1]) < 5e-3, (_rel(full[0], scan[0]), _rel(full[1], scan[1]))
+    assert _rel(full[0], loop[0]) < 5e-3 and _rel(full[1], loop[1]) < 5e-3, (_rel(full[0], loop[0]), _rel(full[1], loop[1]))
