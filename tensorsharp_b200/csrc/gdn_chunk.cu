@@ -68,7 +68,8 @@ template <int DK> struct Lay {
 };
 }  // namespace
 
-template <int DK>
+// HASW = false: nothing to correct (W = 0, the Mamba2 form): U = U0, and neither W's tiles nor its product exist.
+template <int DK, bool HASW>
 __global__ void __launch_bounds__(256) gdn_chunk_carry_kernel(GdnCarryArgs a) {
     using L = Lay<DK>;
     extern __shared__ __align__(16) float sm[];
@@ -85,7 +86,7 @@ __global__ void __launch_bounds__(256) gdn_chunk_carry_kernel(GdnCarryArgs a) {
     const long hc = (long)h * nc;
     // prologue: the state slice and the first chunk's operands, in the commit order W | Qd + P | Kd kept below
     stage(sS, L::LW, Sg, DK, DVS, DK);
-    stage(sW, L::LW, a.W + hc * GC * DK, DK, GC, DK);
+    if (HASW) stage(sW, L::LW, a.W + hc * GC * DK, DK, GC, DK);
     cp_commit();
     stage(sQ, L::LW, a.Qd + hc * GC * DK, DK, GC, DK);
     stage(sP, L::LP, a.P + hc * GC * GC, GC, GC, GC);
@@ -113,7 +114,7 @@ __global__ void __launch_bounds__(256) gdn_chunk_carry_kernel(GdnCarryArgs a) {
         {
             float acc[2][4] = {};
 #pragma unroll 4
-            for (int k0 = 0; k0 < DK; k0 += 8) {
+            for (int k0 = 0; HASW && k0 < DK; k0 += 8) {
                 uint32_t af[4];
                 const float* ap = sW + (mt * 16 + g) * L::LW + k0 + t;
                 af[0] = tf32(ap[0]); af[1] = tf32(ap[8 * L::LW]); af[2] = tf32(ap[4]); af[3] = tf32(ap[8 * L::LW + 4]);
@@ -131,7 +132,7 @@ __global__ void __launch_bounds__(256) gdn_chunk_carry_kernel(GdnCarryArgs a) {
             }
         }
         __syncthreads();                  // U complete, W free
-        if (more) stage(sW, L::LW, a.W + (ch + 1) * GC * DK, DK, GC, DK);
+        if (more && HASW) stage(sW, L::LW, a.W + (ch + 1) * GC * DK, DK, GC, DK);
         cp_commit();
         cp_wait2();                       // Qd and P of this chunk
         __syncthreads();
@@ -216,17 +217,22 @@ __global__ void __launch_bounds__(256) gdn_chunk_carry_kernel(GdnCarryArgs a) {
     }
 }
 
-template <int DK>
-static int launch_carry(const GdnCarryArgs& a, cudaStream_t s) {
+template <int DK, bool HASW>
+static int launch_carry_w(const GdnCarryArgs& a, cudaStream_t s) {
     const size_t smem = (size_t)Lay<DK>::floats * sizeof(float);
     static bool configured = false;
     if (!configured) {
-        TSB_CHECK_CUDA(cudaFuncSetAttribute(gdn_chunk_carry_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TSB_CHECK_CUDA(cudaFuncSetAttribute(gdn_chunk_carry_kernel<DK, HASW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
-    gdn_chunk_carry_kernel<DK><<<dim3(a.Dv / DVS, a.Hv), 256, smem, s>>>(a);
+    gdn_chunk_carry_kernel<DK, HASW><<<dim3(a.Dv / DVS, a.Hv), 256, smem, s>>>(a);
     TSB_CHECK_LAUNCH();
     return TSB_OK;
+}
+
+template <int DK>
+static int launch_carry(const GdnCarryArgs& a, cudaStream_t s) {
+    return a.W != nullptr ? launch_carry_w<DK, true>(a, s) : launch_carry_w<DK, false>(a, s);
 }
 
 // One sequence: carries `state` through `nc` chunks of 64 tokens and writes the chunk outputs.

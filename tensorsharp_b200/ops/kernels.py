@@ -706,7 +706,7 @@ def mamba2_chunked(xbc, dt, dt_bias, A, D, state, cu_q, h_cu_q, slots, *, H, P, 
     assert xbc.dtype == torch.float32 and xbc.stride(1) == 1 and dt.stride(1) == 1 and state.dtype == torch.float32
     BH = B * H
     f32 = dict(dtype=torch.float32, device=dev)
-    U0, W = torch.empty((BH, nc, 64, P), **f32), torch.zeros((BH, nc, 64, N), **f32)
+    U0 = torch.empty((BH, nc, 64, P), **f32)
     Qd, Kd = torch.empty((BH, nc, 64, N), **f32), torch.empty((BH, nc, 64, N), **f32)
     Pm, gamma = torch.empty((BH, nc, 64, 64), **f32), torch.empty((BH, nc), **f32)
     a = MambaPrepArgs()
@@ -724,7 +724,7 @@ def mamba2_chunked(xbc, dt, dt_bias, A, D, state, cu_q, h_cu_q, slots, *, H, P, 
     else:
         idx = torch.tensor(slots, dtype=torch.long, device=dev)
         S = state[idx].reshape(BH, P, N)
-    core = gdn_chunk_carry(U0, W, Qd, Kd, Pm, gamma, S)              # [BH, nc, 64, P]
+    core = gdn_chunk_carry(U0, None, Qd, Kd, Pm, gamma, S)           # [BH, nc, 64, P]; W = 0: nothing to correct
     if B > 1:
         state[idx] = S.view(B, H, P, N)
     y = torch.empty((T, H, P), **f32)
@@ -739,10 +739,11 @@ def mamba2_chunked(xbc, dt, dt_bias, A, D, state, cu_q, h_cu_q, slots, *, H, P, 
 def gdn_chunk_carry(U0, W, Qd, Kd, P, gamma, state) -> torch.Tensor:
     """The sequential part of the chunked GatedDeltaNet prefill for one sequence: ``state`` [Hv, Dv, Dk] f32 (contiguous,
     updated in place) carried through the chunks of U0 [Hv, nc, 64, Dv], W / Qd / Kd [Hv, nc, 64, Dk], P [Hv, nc, 64, 64],
-    gamma [Hv, nc] -> outputs [Hv, nc, 64, Dv] f32."""
-    U0, W, Qd, Kd, P, gamma = (t.float().contiguous() for t in (U0, W, Qd, Kd, P, gamma))
+    gamma [Hv, nc] -> outputs [Hv, nc, 64, Dv] f32.  ``W`` None stands for zeros (no correction term)."""
+    U0, Qd, Kd, P, gamma = (t.float().contiguous() for t in (U0, Qd, Kd, P, gamma))
+    W = W.float().contiguous() if W is not None else None              # None: nothing to correct (the Mamba2 form)
     Hv, nc, Cn, Dv = U0.shape
-    Dk = W.shape[-1]
+    Dk = Qd.shape[-1]
     assert Cn == 64 and state.dtype == torch.float32 and state.is_contiguous() and state.shape == (Hv, Dv, Dk)
     out = torch.empty((Hv, nc, Cn, Dv), dtype=torch.float32, device=U0.device)
     a = GdnCarryArgs()
