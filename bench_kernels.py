@@ -5,6 +5,7 @@
     python bench_kernels.py gemv --type Q4_K --n 2560 --k 9728
     python bench_kernels.py gemm --t 2048 --n 19456 --k 2560         # bf16 tensor-core GEMM; TSB_GEMM_WIDE=0 / 2 picks the tile
     python bench_kernels.py attn --t 2048 --hq 32 --hkv 8 --dh 128   # causal flash prefill over the paged cache
+    python bench_kernels.py attn_decode --b 16 --t 2048 [--kv fp8]   # split-KV decode attention, bf16 or e4m3 pages
     python bench_kernels.py recurrent --op gdn --t 2048
     python bench_kernels.py recurrent --op mamba2 --t 2048
 
@@ -187,9 +188,50 @@ def attn(args):
                       "tflops": flop / us / 1e6}))
 
 
+def attn_decode(args):
+    """Decode attention (one query per sequence) of ``--b`` sequences at context ``--t`` against the paged cache, bf16 pages
+    or e4m3 bytes (``--kv fp8``), with the split factor the model path would pick; reports the K / V bytes per second."""
+    import torch
+    from tensorsharp_b200.ops import functional as F
+    from tensorsharp_b200.ops import kernels
+    dev, T, B, Hq, Hkv, Dh, ps = "cuda", args.t, args.b, args.hq, args.hkv, args.dh, 64
+    torch.manual_seed(0)
+    pages_per = (T + ps - 1) // ps
+    n_pages = pages_per * B
+    layers = max(2, int(300e6 // (n_pages * ps * Hkv * Dh * 2 * (1 if args.kv == "fp8" else 2))) + 1)     # cycle: larger than L2
+    caches = []
+    for _ in range(layers):
+        kc = torch.randn(n_pages * ps, Hkv, Dh, device=dev).bfloat16()
+        vc = torch.randn(n_pages * ps, Hkv, Dh, device=dev).bfloat16()
+        caches.append((kc.to(torch.float8_e4m3fn), vc.to(torch.float8_e4m3fn)) if args.kv == "fp8" else (kc, vc))
+    table = torch.randperm(n_pages, device=dev).to(torch.int32).view(B, pages_per)
+    q = torch.randn(B, Hq, Dh, device=dev).bfloat16()
+    lens = torch.full((B,), T, dtype=torch.int32, device=dev)
+
+    class Shape:                         # what decode_splits reads of a batch
+        pass
+    sh = Shape()
+    sh.B, sh.max_kv_len = B, T
+    splits = F.decode_splits(sh, Hkv, 0)
+    split_len = F.decode_split_len(sh, splits, 0)
+    state = {"i": 0}
+
+    def run():
+        kc, vc = caches[state["i"] % layers]
+        state["i"] += 1
+        return kernels.attn_decode(q, kc, vc, table, lens, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh, page_size=ps, splits=splits,
+                                   split_len=split_len)
+    us = time_us(run, args.iters, args.warmup)
+    nbytes = 2.0 * B * T * Hkv * Dh * (1 if args.kv == "fp8" else 2)
+    print(json.dumps({"kernel": "attn_decode", "kv": args.kv, "B": B, "T": T, "Hq": Hq, "Hkv": Hkv, "Dh": Dh, "splits": splits,
+                      "us": us, "kv_mb": nbytes / 1e6, "gb_s": nbytes / us / 1e3}))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv", "recurrent", "gemm", "attn"])
+    ap.add_argument("what", choices=["gemv", "recurrent", "gemm", "attn", "attn_decode"])
+    ap.add_argument("--b", type=int, default=16, help="attn_decode: sequences")
+    ap.add_argument("--kv", default="bf16", choices=["bf16", "fp8"], help="attn_decode: element type of the cache")
     ap.add_argument("--hq", type=int, default=32)
     ap.add_argument("--hkv", type=int, default=8)
     ap.add_argument("--dh", type=int, default=128)
@@ -213,6 +255,8 @@ def main():
         return gemm(args)
     if args.what == "attn":
         return attn(args)
+    if args.what == "attn_decode":
+        return attn_decode(args)
     import torch
     from tensorsharp_b200.gguf.constants import GGMLType
     from tensorsharp_b200.ops import kernels
