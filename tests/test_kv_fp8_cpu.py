@@ -85,9 +85,8 @@ def test_kv_dtype_option_of_the_cli_and_the_server(monkeypatch, tmp_path):
     assert parse_cli_args(["--model", "m.gguf"]).kv_dtype is None
     with pytest.raises(ValueError, match="--kv-dtype"):
         parse_cli_args(["--kv-dtype", "int3"])
-    monkeypatch.delenv("TSB_KV_DTYPE", raising=False)
+    monkeypatch.setenv("TSB_KV_DTYPE", "bf16")          # registered with monkeypatch, so the export below is undone afterwards
     assert O.parse_args(["--kv-dtype", "e4m3", "--port", "5001"])["kv_dtype"] == "e4m3"
     O.build_options(["--kv-dtype", "e4m3"], str(tmp_path), env={})
     import os
     assert os.environ.get("TSB_KV_DTYPE") == "fp8"
-    monkeypatch.delenv("TSB_KV_DTYPE", raising=False)
