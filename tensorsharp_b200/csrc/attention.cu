@@ -15,6 +15,7 @@
 #include <mutex>
 #include "common.cuh"
 #include "attn_args.cuh"
+#include "attn_mma.cuh"
 #include "tsb_noalloc.h"
 
 
@@ -404,6 +405,18 @@ static int attn_decode_impl(const AttnArgs* args, void* stream, bool allow_fused
     if (a.B == 0) return TSB_OK;
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
+    // Batches (more than four CTAs per SM): Q K^T and P V on the tensor cores, the query heads of a KV head as the rows
+    // of one tile (attention_decode_mma.cu).  TSB_ATTN_MMA=0 keeps the CUDA-core batch variant.
+    static const bool mma_on = []() { const char* e = getenv("TSB_ATTN_MMA"); return !e || atoi(e) != 0; }();
+    if (mma_on && (long)a.splits * a.Hkv * a.B > 4L * 148 && tsb_attn_decode_mma_supported(a)) {
+        a.ticket = nullptr;
+        rc = tsb_attn_decode_mma_launch(a, s);
+        if (rc != TSB_OK) return rc;
+        TSB_CHECK_LAUNCH();
+        TSB_CHECK_CUDA(tsb_launch(attn_combine_kernel, dim3(a.Hq, a.B), dim3((a.Dh + 31) & ~31), 0, s, a));
+        TSB_CHECK_LAUNCH();
+        return TSB_OK;
+    }
     switch (a.Dh) {
     case 64: rc = launch_decode_g<64>(a, s); break;
     case 128: rc = launch_decode_g<128>(a, s); break;
@@ -481,40 +494,6 @@ extern "C" int tsb_attn_decode_noalloc(const AttnArgs* args, void* stream) {
 // Prefill: flash attention on mma.sync m16n8k16 bf16, 64 queries x one head per CTA, 64-token
 // KV tiles streamed with cp.async double buffering from the paged cache.
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-    const uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
-
-__device__ __forceinline__ void ldsm_x4(uint32_t* r, const void* p) {
-    const uint32_t sa = (uint32_t)__cvta_generic_to_shared(p);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(sa));
-}
-__device__ __forceinline__ void ldsm_x4_t(uint32_t* r, const void* p) {
-    const uint32_t sa = (uint32_t)__cvta_generic_to_shared(p);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(sa));
-}
-__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    bf162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-
-// Tile row r, 16-byte chunk c of a [rows][DH] bf16 tile with an XOR swizzle over 8 rows.
-template <int DH>
-__device__ __forceinline__ bf16* tile_ptr(bf16* base, int r, int c) {
-    return base + r * DH + ((c ^ (r & 7)) << 3);
-}
-
 // DS > 1 (head size 512): DS sets of four warps share the tiles and the score arithmetic, each set keeps DH / DS of the
 // output columns, so that a thread's accumulators stay at the head-size-256 count.
 template <int DH, int BN, int DS>

@@ -1,0 +1,222 @@
+// Decode attention for batches on the bf16 tensor cores: the query heads that share a KV head (up to 16) are the rows
+// of one m16 tile, so Q K^T and P V of a 32-key chunk are 2 x 32 mma.sync m16n8k16 instead of the thousand multiply-adds
+// per lane the CUDA-core kernel (attention.cu: attn_decode_body) spends on it.  That kernel stays for one sequence,
+// where a CTA has an SM to itself and latency decides; this one is for grids of many CTAs per SM, where the instruction
+// stream decided (26 % of the copy rate at 16 sequences x 2048 positions).
+//
+// grid (splits, Hkv, B), 128 threads.  Each warp walks its own 32-key chunks of the split (stride 128 keys): the chunk's
+// K and V rows come through cp.async into the warp's own swizzled tiles, ldmatrix feeds the fragments, the online
+// softmax runs in registers on the accumulator layout (two rows per lane), P goes back in as the A operand of P V.
+// The four warps' partial results are merged through shared memory and written as this split's partial; the combine
+// kernel of attention.cu finishes (sinks, normalisation, int8 form).
+//
+// Replaces in the reference: flash_attn_ext_vec (ggml-cuda/fattn-vec.cuh:21) for batched decode.
+#include "attn_args.cuh"
+#include "attn_mma.cuh"
+#include "common.cuh"
+
+template <int DH>
+__global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnArgs a) {
+    constexpr int CH = DH / 8;                     // 16-byte pieces per row
+    constexpr int KT = 32;                         // keys per chunk
+    constexpr float LOG2E = 1.4426950408889634f;
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* sQ = reinterpret_cast<bf16*>(smem_raw);                          // [16][DH]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    bf16* sK = sQ + 16 * DH + warp * (2 * KT * DH);                         // this warp's [32][DH] K tile
+    bf16* sV = sK + KT * DH;                                                // and V tile
+    const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int G = a.Hq / a.Hkv, h0 = hk * G;
+
+    // query rows of the group -> rows 0 .. G - 1 of a 16-row tile, the rest zero
+    for (int i = threadIdx.x; i < 16 * CH; i += 128) {
+        const int r = i / CH, c = i % CH;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < G) v = *reinterpret_cast<const uint4*>(a.q + ((long)b * a.Hq + h0 + r) * DH + c * 8);
+        *reinterpret_cast<uint4*>(tile_ptr<DH>(sQ, r, c)) = v;
+    }
+    const int len = a.kv_lens[b];
+    const int lo = (a.window > 0 && len > a.window) ? len - a.window : 0;
+    const int span = len - lo;
+    const int per = a.split_len > 0 ? a.split_len : ((((span + a.splits - 1) / a.splits) + 31) & ~31);
+    const int s0 = lo + split * per, s1 = min(len, s0 + per);
+    __syncthreads();
+    uint32_t qa[DH / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < DH / 16; ++kk) ldsm_x4(qa[kk], tile_ptr<DH>(sQ, lane & 15, kk * 2 + (lane >> 4)));
+
+    float o[DH / 8][4];
+#pragma unroll
+    for (int i = 0; i < DH / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};          // rows lane / 4 and lane / 4 + 8
+
+    for (int base = s0 + warp * KT; base < s1; base += 4 * KT) {
+        const int j = base + lane;
+        long slot = 0;
+        if (j < s1) {
+            const int page = a.block_table[(long)b * a.max_pages + j / a.page_size];
+            slot = (long)page * a.page_size + j % a.page_size;
+        }
+        // the chunk's K and V rows -> this warp's tiles (rows past the split's end are zero: 0 x garbage would poison P V)
+#pragma unroll 4
+        for (int i = lane; i < KT * CH; i += 32) {
+            const int key = i / CH, c = i % CH;
+            const long sl = __shfl_sync(0xffffffffu, slot, key);
+            bf16* pk = tile_ptr<DH>(sK, key, c);
+            bf16* pv = tile_ptr<DH>(sV, key, c);
+            if (base + key < s1) {
+                const long off = (sl * a.Hkv + hk) * DH + c * 8;
+                cp_async16(pk, a.k_cache + off);
+                cp_async16(pv, a.v_cache + off);
+            } else {
+                *reinterpret_cast<uint4*>(pk) = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4*>(pv) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncwarp();
+
+        // S = Q K^T: 16 rows x 32 keys
+        float s[KT / 8][4];
+#pragma unroll
+        for (int i = 0; i < KT / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < DH / 16; ++kk) {
+#pragma unroll
+            for (int nt = 0; nt < KT / 16; ++nt) {
+                uint32_t kb[4];
+                const int tok = nt * 16 + ((lane >> 4) << 3) + (lane & 7);
+                ldsm_x4(kb, tile_ptr<DH>(sK, tok, kk * 2 + ((lane >> 3) & 1)));
+                mma_bf16(s[2 * nt], qa[kk], kb[0], kb[1]);
+                mma_bf16(s[2 * nt + 1], qa[kk], kb[2], kb[3]);
+            }
+        }
+        // scale, soft-cap, mask the keys past the end, online softmax (scores in natural-log units, as the combine expects)
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < KT / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float sv = s[nt][e] * a.scale;
+                if (a.softcap > 0.f) sv = a.softcap * tanhf(sv / a.softcap);
+                const int key = base + nt * 8 + (lane & 3) * 2 + (e & 1);
+                sv = key < s1 ? sv : -INFINITY;
+                s[nt][e] = sv;
+                mx[e >> 1] = fmaxf(mx[e >> 1], sv);
+            }
+        }
+        float corr[2], rsum[2] = {0.f, 0.f}, mneg[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            mx[r] = fmaxf(mrow[r], mx[r]);
+            corr[r] = (mrow[r] == -INFINITY) ? 0.f : exp2f((mrow[r] - mx[r]) * LOG2E);
+            mrow[r] = mx[r];
+            mneg[r] = (mx[r] == -INFINITY) ? 0.f : -mx[r] * LOG2E;
+        }
+#pragma unroll
+        for (int nt = 0; nt < KT / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float p = exp2f(fmaf(s[nt][e], LOG2E, mneg[e >> 1]));
+                s[nt][e] = p;
+                rsum[e >> 1] += p;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) lrow[r] = lrow[r] * corr[r] + rsum[r];
+#pragma unroll
+        for (int i = 0; i < DH / 8; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0];
+            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+        // O += P V
+#pragma unroll
+        for (int kt = 0; kt < KT / 16; ++kt) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16(s[2 * kt][0], s[2 * kt][1]);
+            pa[1] = pack_bf16(s[2 * kt][2], s[2 * kt][3]);
+            pa[2] = pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]);
+            pa[3] = pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3]);
+#pragma unroll
+            for (int dt = 0; dt < DH / 16; ++dt) {
+                uint32_t vb[4];
+                const int tok = kt * 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
+                ldsm_x4_t(vb, tile_ptr<DH>(sV, tok, dt * 2 + (lane >> 4)));
+                mma_bf16(o[2 * dt], pa, vb[0], vb[1]);
+                mma_bf16(o[2 * dt + 1], pa, vb[2], vb[3]);
+            }
+        }
+        __syncwarp();                                   // every lane is done with the tiles before the next chunk lands
+    }
+    // row sums over the four lanes that share a row
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        lrow[r] += __shfl_xor_sync(0xffffffffu, lrow[r], 1);
+        lrow[r] += __shfl_xor_sync(0xffffffffu, lrow[r], 2);
+    }
+    // merge the four warps through shared memory (over the staging tiles, which are free now)
+    __syncthreads();
+    float* red_m = reinterpret_cast<float*>(smem_raw);                      // [4][16]
+    float* red_l = red_m + 64;                                              // [4][16]
+    float* red_o = red_l + 64;                                              // [4][G][DH]
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = (lane >> 2) + 8 * r;
+        if (row < G) {
+            if ((lane & 3) == 0) { red_m[warp * 16 + row] = mrow[r]; red_l[warp * 16 + row] = lrow[r]; }
+#pragma unroll
+            for (int i = 0; i < DH / 8; ++i) {
+                float* dst = red_o + ((long)(warp * G + row)) * DH + i * 8 + (lane & 3) * 2;
+                dst[0] = o[i][2 * r];
+                dst[1] = o[i][2 * r + 1];
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < G * DH; i += 128) {
+        const int g = i / DH, d = i % DH;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red_m[w * 16 + g]);
+        float ll = 0.f, ov = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float c = (red_m[w * 16 + g] == -INFINITY) ? 0.f : __expf(red_m[w * 16 + g] - mm);
+            ll += red_l[w * 16 + g] * c;
+            ov += red_o[((long)(w * G + g)) * DH + d] * c;
+        }
+        const long pi = ((long)b * a.Hq + h0 + g) * a.splits + split;
+        a.part_o[pi * DH + d] = ov;
+        if (d == 0) { a.part_ml[pi * 2] = mm; a.part_ml[pi * 2 + 1] = ll; }
+    }
+}
+
+template <int DH>
+static int launch_decode_mma(const AttnArgs& a, cudaStream_t s) {
+    // the query tile, four warps' K and V tiles; the merge buffers reuse them (4 * 16 * DH floats at most)
+    const size_t stage = (size_t)(16 + 4 * 2 * 32) * DH * sizeof(bf16);
+    const size_t merge = (size_t)(128 + 4 * 16 * DH) * sizeof(float);
+    const size_t smem = stage > merge ? stage : merge;
+    static bool configured = false;
+    if (!configured) {
+        TSB_CHECK_CUDA(cudaFuncSetAttribute(attn_decode_mma_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    TSB_CHECK_CUDA(tsb_launch(attn_decode_mma_kernel<DH>, dim3(a.splits, a.Hkv, a.B), dim3(128), smem, s, a));
+    return TSB_OK;
+}
+
+// Whether this kernel serves the shape (the caller decides whether the grid is large enough to prefer it).
+bool tsb_attn_decode_mma_supported(const AttnArgs& a) {
+    return (a.Dh == 64 || a.Dh == 128) && a.Hkv > 0 && a.Hq % a.Hkv == 0 && a.Hq / a.Hkv <= 16;
+}
+
+// The split kernel only; the caller launches the combine.
+int tsb_attn_decode_mma_launch(const AttnArgs& a, cudaStream_t s) {
+    return a.Dh == 64 ? launch_decode_mma<64>(a, s) : launch_decode_mma<128>(a, s);
+}

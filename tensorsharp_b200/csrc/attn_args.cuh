@@ -31,3 +31,8 @@ struct AttnArgs {
     // entries do not wait for the sequence length; 0 = derive it from the length (ceil(span / splits), rounded to 32).
     int split_len;
 };
+
+// attention_decode_mma.cu: the tensor-core split kernel for decode batches (head sizes 64 / 128, up to 16 query heads
+// per KV head); the caller launches the combine.
+bool tsb_attn_decode_mma_supported(const AttnArgs& a);
+int tsb_attn_decode_mma_launch(const AttnArgs& a, cudaStream_t s);

@@ -215,6 +215,37 @@ def test_attn_decode(Hq, Hkv, Dh, window, sinks, softcap):
             assert rel_err(got[b], want[0]) < 1e-2, (b, splits, rel_err(got[b], want[0]))
 
 
+@pytest.mark.parametrize("Hq,Hkv,Dh,B,splits", [(32, 8, 128, 16, 9), (64, 8, 64, 12, 7), (16, 8, 128, 20, 4), (8, 8, 64, 20, 4),
+                                                (48, 4, 128, 40, 4), (64, 4, 64, 40, 5), (12, 4, 128, 50, 3)])
+@pytest.mark.parametrize("window,sinks,softcap", [(0, False, 0.0), (100, True, 0.0), (0, False, 30.0)])
+def test_attn_decode_batches_on_the_tensor_cores(Hq, Hkv, Dh, B, splits, window, sinks, softcap):
+    """Grids of more than four CTAs per SM take the tensor-core split kernel (csrc/attention_decode_mma.cu): groups of
+    1 to 16 query heads per KV head, ragged lengths (one key, a partial last chunk, splits left empty), window, sinks,
+    soft-cap, against the float32 softmax."""
+    assert splits * Hkv * B > 4 * 148
+    torch.manual_seed(17)
+    ps = 16
+    lens = [1 + (37 * i * i + 11 * i) % 700 for i in range(B)]
+    lens[1], lens[2] = 1, 32
+    kc, vc, table = _paged(sum(lens), Hkv, Dh, ps, lens)
+    q = torch.randn(B, Hq, Dh, device=DEV).bfloat16()
+    sk = torch.randn(Hq, device=DEV) if sinks else None
+    kv_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    got = K().attn_decode(q, kc, vc, table, kv_lens, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh, page_size=ps,
+                          splits=splits, sinks=sk, softcap=softcap, window=window)
+    assert torch.isfinite(got.float()).all()
+    for b, L in enumerate(lens):
+        want = ref.attention(q[b:b + 1], _gather(kc, table, b, L, ps), _gather(vc, table, b, L, ps),
+                             torch.tensor([L - 1], device=DEV), scale=Dh ** -0.5, window=window, sinks=sk, softcap=softcap)
+        assert rel_err(got[b], want[0]) < 1.5e-2, (b, L, rel_err(got[b], want[0]))
+    # a split length fixed by the caller (what the model path passes) gives the same result
+    sl = ((max(lens) + splits - 1) // splits + 31) & ~31
+    if not window:
+        fixed = K().attn_decode(q, kc, vc, table, kv_lens, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh, page_size=ps,
+                                splits=splits, sinks=sk, softcap=softcap, window=window, split_len=sl)
+        assert rel_err(fixed, got) < 1e-2
+
+
 @pytest.mark.parametrize("Hq,Hkv,Dh", [(4, 2, 128), (2, 2, 64), (4, 1, 256), (4, 2, 512), (3, 1, 128)])
 @pytest.mark.parametrize("window,sinks,softcap", [(0, False, 0.0), (70, True, 0.0), (0, False, 50.0)])
 def test_attn_prefill(Hq, Hkv, Dh, window, sinks, softcap):
