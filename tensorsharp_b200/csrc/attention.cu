@@ -413,11 +413,14 @@ static int attn_decode_impl(const AttnArgs* args, void* stream, bool allow_fused
     static const long mma_min_ctas = []() { const char* e = getenv("TSB_ATTN_MMA_MIN_CTAS"); return e ? atol(e) : 1L; }();
     if (mma_on && (long)a.splits * a.Hkv * a.B >= mma_min_ctas && tsb_attn_decode_mma_supported(a)) {
         a.ticket = nullptr;
-        rc = tsb_attn_decode_mma_launch(a, s);
+        bool merged = false;
+        rc = tsb_attn_decode_mma_launch(a, s, &merged);
         if (rc != TSB_OK) return rc;
         TSB_CHECK_LAUNCH();
-        TSB_CHECK_CUDA(tsb_launch(attn_combine_kernel, dim3(a.Hq, a.B), dim3((a.Dh + 31) & ~31), 0, s, a));
-        TSB_CHECK_LAUNCH();
+        if (!merged) {
+            TSB_CHECK_CUDA(tsb_launch(attn_combine_kernel, dim3(a.Hq, a.B), dim3((a.Dh + 31) & ~31), 0, s, a));
+            TSB_CHECK_LAUNCH();
+        }
         return TSB_OK;
     }
     switch (a.Dh) {

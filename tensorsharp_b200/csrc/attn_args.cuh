@@ -33,6 +33,6 @@ struct AttnArgs {
 };
 
 // attention_decode_mma.cu: the tensor-core split kernel for decode batches (head sizes 64 / 128, up to 16 query heads
-// per KV head); the caller launches the combine.
+// per KV head); the caller launches the combine unless `*merged` comes back true (splits merged by a thread-block cluster).
 bool tsb_attn_decode_mma_supported(const AttnArgs& a);
-int tsb_attn_decode_mma_launch(const AttnArgs& a, cudaStream_t s);
+int tsb_attn_decode_mma_launch(const AttnArgs& a, cudaStream_t s, bool* merged);

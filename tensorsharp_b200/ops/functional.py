@@ -432,7 +432,15 @@ def decode_splits(batch: Batch, Hkv: int, window: int) -> int:
     # sequences two splits per (sequence, KV head) left the kernel at a fifth of the memory rate)
     want = max(1, (148 * (2 if batch.B == 1 else 8)) // max(1, batch.B * Hkv))
     per = int(os.environ.get("TSB_ATTN_SPLIT_LEN", "128"))
-    return int(max(1, min(want, (span + per - 1) // per, 64)))
+    n = int(max(1, min(want, (span + per - 1) // per, 64)))
+    # TSB_ATTN_CLUSTER=1: 8 or 16 splits are merged inside the attention kernel by a thread-block cluster (no combine
+    # launch), so take those counts when the natural one is close (measured slower than the combine launch: off by default)
+    if os.environ.get("TSB_ATTN_CLUSTER", "0") not in ("", "0"):
+        if want >= 16 and 13 <= n <= 20:
+            return 16
+        if want >= 8 and 7 <= n <= 10:
+            return 8
+    return n
 
 
 def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, batch: Batch, *, scale: float,

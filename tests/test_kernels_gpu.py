@@ -216,17 +216,21 @@ def test_attn_decode(Hq, Hkv, Dh, window, sinks, softcap):
 
 
 @pytest.mark.parametrize("Hq,Hkv,Dh,B,splits", [(32, 8, 128, 16, 9), (64, 8, 64, 12, 7), (16, 8, 128, 20, 4), (8, 8, 64, 20, 4),
-                                                (48, 4, 128, 40, 4), (64, 4, 64, 40, 5), (12, 4, 128, 50, 3)])
+                                                (48, 4, 128, 40, 4), (64, 4, 64, 40, 5), (12, 4, 128, 50, 3),
+                                                # 8 or 16 splits: merged inside the kernel by a thread-block cluster
+                                                (32, 8, 128, 1, 16), (32, 8, 128, 3, 8), (64, 8, 64, 2, 16), (16, 2, 128, 5, 8),
+                                                (32, 2, 64, 4, 16), (8, 8, 64, 3, 16)])
 @pytest.mark.parametrize("window,sinks,softcap", [(0, False, 0.0), (100, True, 0.0), (0, False, 30.0)])
-def test_attn_decode_batches_on_the_tensor_cores(Hq, Hkv, Dh, B, splits, window, sinks, softcap):
+def test_attn_decode_batches_on_the_tensor_cores(Hq, Hkv, Dh, B, splits, window, sinks, softcap, monkeypatch):
     """Grids of more than four CTAs per SM take the tensor-core split kernel (csrc/attention_decode_mma.cu): groups of
     1 to 16 query heads per KV head, ragged lengths (one key, a partial last chunk, splits left empty), window, sinks,
-    soft-cap, against the float32 softmax."""
-    assert splits * Hkv * B > 4 * 148
+    soft-cap, against the float32 softmax.  With 8 or 16 splits the cluster form of the kernel (off by default) runs."""
+    monkeypatch.setenv("TSB_ATTN_CLUSTER", "1")
     torch.manual_seed(17)
     ps = 16
-    lens = [1 + (37 * i * i + 11 * i) % 700 for i in range(B)]
-    lens[1], lens[2] = 1, 32
+    lens = [1 + (37 * i * i + 11 * i + 600) % 700 for i in range(B)]
+    if B > 2:
+        lens[1], lens[2] = 1, 32
     kc, vc, table = _paged(sum(lens), Hkv, Dh, ps, lens)
     q = torch.randn(B, Hq, Dh, device=DEV).bfloat16()
     sk = torch.randn(Hq, device=DEV) if sinks else None
@@ -244,6 +248,11 @@ def test_attn_decode_batches_on_the_tensor_cores(Hq, Hkv, Dh, B, splits, window,
         fixed = K().attn_decode(q, kc, vc, table, kv_lens, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh, page_size=ps,
                                 splits=splits, sinks=sk, softcap=softcap, window=window, split_len=sl)
         assert rel_err(fixed, got) < 1e-2
+    # the int8 form for the following projection equals a separate quantise of the bf16 output
+    out, oq, ods = K().attn_decode(q, kc, vc, table, kv_lens, scale=Dh ** -0.5, Hq=Hq, Hkv=Hkv, Dh=Dh, page_size=ps,
+                                   splits=splits, sinks=sk, softcap=softcap, window=window, want_q8=True)
+    wq, wds = K().quantize_q8(out.view(B, Hq * Dh))
+    assert torch.equal(out, got) and torch.equal(oq, wq) and torch.equal(ods, wds)
 
 
 @pytest.mark.parametrize("Hq,Hkv,Dh", [(4, 2, 128), (2, 2, 64), (4, 1, 256), (4, 2, 512), (3, 1, 128)])
