@@ -1,8 +1,8 @@
-// Decode attention for batches on the bf16 tensor cores: the query heads that share a KV head (up to 16) are the rows
-// of one m16 tile, so Q K^T and P V of a 32-key chunk are 2 x 32 mma.sync m16n8k16 instead of the thousand multiply-adds
-// per lane the CUDA-core kernel (attention.cu: attn_decode_body) spends on it.  That kernel stays for one sequence,
-// where a CTA has an SM to itself and latency decides; this one is for grids of many CTAs per SM, where the instruction
-// stream decided (26 % of the copy rate at 16 sequences x 2048 positions).
+// Decode attention on the bf16 tensor cores: the query heads that share a KV head (up to 16) are the rows of one m16
+// tile, so Q K^T and P V of a 32-key chunk are 2 x 32 mma.sync m16n8k16 instead of the thousand multiply-adds per lane
+// the CUDA-core kernels (attention.cu: attn_decode_body) spend on it.  Serves head sizes 64 and 128, one sequence or a
+// batch; the CUDA-core kernels keep the other shapes.  Measured on the Qwen3-4B shape at context 2048: one sequence 12.0
+// -> 5.3 us per launch inside the decode step, 16 sequences 77.9 -> 40.0 us (51 % of the measured copy rate).
 //
 // grid (splits, Hkv, B), 128 threads.  Each warp walks its own 32-key chunks of the split (stride 128 keys): the chunk's
 // K and V rows come through cp.async into the warp's own swizzled tiles, ldmatrix feeds the fragments, the online
@@ -10,7 +10,7 @@
 // The four warps' partial results are merged through shared memory and written as this split's partial; the combine
 // kernel of attention.cu finishes (sinks, normalisation, int8 form).
 //
-// Replaces in the reference: flash_attn_ext_vec (ggml-cuda/fattn-vec.cuh:21) for batched decode.
+// Replaces in the reference: flash_attn_ext_vec (ggml-cuda/fattn-vec.cuh:21).
 #include <cooperative_groups.h>
 
 #include "attn_args.cuh"
