@@ -90,3 +90,27 @@ def test_kv_dtype_option_of_the_cli_and_the_server(monkeypatch, tmp_path):
     O.build_options(["--kv-dtype", "e4m3"], str(tmp_path), env={})
     import os
     assert os.environ.get("TSB_KV_DTYPE") == "fp8"
+
+
+@pytest.mark.parametrize("name", ["gptoss", "gemma3", "gemma4", "gemma4_wide_heads", "mistral3", "qwen35_dense", "nemotron_h"])
+def test_every_family_runs_on_the_fp8_cache(name, tmp_path, monkeypatch):
+    """Sliding windows, sinks, shared KV layers, wide heads and the attention layers of the hybrid models read the 8-bit
+    pages through the same helpers: logits stay close to the float32-cache model, and prefix + suffix equals one pass."""
+    from tests.test_model_families_cpu import FAMILIES
+    fn, kw = FAMILIES[name]
+    p = str(tmp_path / f"{name}.gguf")
+    fn(p, device="cpu", **kw)
+    ref = ModelBase.create(p, "cpu", max_context=256)
+    monkeypatch.setenv("TSB_KV_DTYPE", "fp8")
+    m = ModelBase.create(p, "cpu", max_context=256)
+    assert all(k is None or k.dtype == torch.float8_e4m3fn for k in m.kv.k)
+    g = torch.Generator().manual_seed(7)
+    ids = torch.randint(0, 4096, (70,), generator=g).tolist()
+    want, full = ref.forward(ids), m.forward(ids)
+    assert torch.isfinite(full).all()
+    rel = float((full - want).abs().max() / want.abs().max())
+    assert rel < 0.15, rel
+    m.reset_kv_cache()
+    m.forward(ids[:40], want_logits=False)
+    inc = m.forward(ids[40:])
+    assert float((inc - full).abs().max()) < 2e-2 * max(1.0, float(full.abs().max()))
