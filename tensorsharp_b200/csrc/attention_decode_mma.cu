@@ -12,6 +12,8 @@
 //
 // Replaces in the reference: flash_attn_ext_vec (ggml-cuda/fattn-vec.cuh:21).
 #include <cooperative_groups.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 #include "attn_args.cuh"
 #include "attn_mma.cuh"
@@ -19,12 +21,37 @@
 
 namespace cg = cooperative_groups;
 
+// The e4m3 cache (FP8 = true): the tiles hold half values (the hardware converts two e4m3 bytes to a half pair in one
+// instruction, exactly), the query rows are converted from bf16 to half as they are staged, and the products are the
+// f16 form of the same mma.  K / V pieces are fetched with plain 16-byte loads (16 values each), all of a chunk's
+// requests issued before the first conversion.
+__device__ __forceinline__ void mma_f16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ uint32_t e4m3x2_to_half2(uint32_t two_bytes) {
+    const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)two_bytes, __NV_E4M3);
+    return (uint32_t)h.x | ((uint32_t)h.y << 16);
+}
+// 16 e4m3 bytes -> two 16-byte pieces of 8 halves each
+__device__ __forceinline__ void e4m3x16_to_half(const uint4& raw, uint4& lo, uint4& hi) {
+    lo.x = e4m3x2_to_half2(raw.x & 0xffffu); lo.y = e4m3x2_to_half2(raw.x >> 16);
+    lo.z = e4m3x2_to_half2(raw.y & 0xffffu); lo.w = e4m3x2_to_half2(raw.y >> 16);
+    hi.x = e4m3x2_to_half2(raw.z & 0xffffu); hi.y = e4m3x2_to_half2(raw.z >> 16);
+    hi.z = e4m3x2_to_half2(raw.w & 0xffffu); hi.w = e4m3x2_to_half2(raw.w >> 16);
+}
+
 // CS > 0: the CS splits of a (sequence, KV head) are one thread-block cluster, and instead of writing partials for a
 // second kernel every CTA leaves its partial in its own shared memory, the cluster synchronises, and each CTA reads the
 // others' partials through distributed shared memory to finish 1 / CS of the group's output columns (sinks,
 // normalisation, bf16 and int8 forms: the arithmetic of attn_combine_kernel).  No CTA returns before the second
 // cluster barrier, so no shared memory disappears under a reader.
-template <int DH, int CS>
+template <int DH, int CS, bool FP8 = false>
 __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnArgs a) {
     constexpr int CH = DH / 8;                     // 16-byte pieces per row
     constexpr int KT = 32;                         // keys per chunk
@@ -44,6 +71,17 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnArgs a) {
         const int r = i / CH, c = i % CH;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
         if (r < G) v = *reinterpret_cast<const uint4*>(a.q + ((long)b * a.Hq + h0 + r) * DH + c * 8);
+        if constexpr (FP8) {                                // bf16 -> half, pair by pair
+            const bf162* p2 = reinterpret_cast<const bf162*>(&v);
+            uint4 hv;
+            uint32_t* hp = reinterpret_cast<uint32_t*>(&hv);
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                const float2 f = __bfloat1622float2(p2[q4]);
+                hp[q4] = pack_f16(f.x, f.y);
+            }
+            v = hv;
+        }
         *reinterpret_cast<uint4*>(tile_ptr<DH>(sQ, r, c)) = v;
     }
     const int len = a.kv_lens[b];
@@ -69,6 +107,33 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnArgs a) {
             slot = (long)page * a.page_size + j % a.page_size;
         }
         // the chunk's K and V rows -> this warp's tiles (rows past the split's end are zero: 0 x garbage would poison P V)
+        if constexpr (FP8) {
+            constexpr int PC = DH / 16;                 // 16-byte pieces (16 values) per e4m3 row
+            constexpr int NP = KT * PC / 32;            // pieces per lane and matrix
+            const uint8_t* kc8 = reinterpret_cast<const uint8_t*>(a.k_cache);
+            const uint8_t* vc8 = reinterpret_cast<const uint8_t*>(a.v_cache);
+            uint4 kr[NP], vr[NP];
+#pragma unroll
+            for (int r = 0; r < NP; ++r) {
+                const int i = lane + 32 * r, key = i / PC, pc = i % PC;
+                const long sl = __shfl_sync(0xffffffffu, slot, key);
+                const long off = (sl * a.Hkv + hk) * DH + pc * 16;
+                const bool ok = base + key < s1;
+                kr[r] = ok ? *reinterpret_cast<const uint4*>(kc8 + off) : make_uint4(0u, 0u, 0u, 0u);
+                vr[r] = ok ? *reinterpret_cast<const uint4*>(vc8 + off) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int r = 0; r < NP; ++r) {
+                const int i = lane + 32 * r, key = i / PC, pc = i % PC;
+                uint4 lo, hi;
+                e4m3x16_to_half(kr[r], lo, hi);
+                *reinterpret_cast<uint4*>(tile_ptr<DH>(sK, key, 2 * pc)) = lo;
+                *reinterpret_cast<uint4*>(tile_ptr<DH>(sK, key, 2 * pc + 1)) = hi;
+                e4m3x16_to_half(vr[r], lo, hi);
+                *reinterpret_cast<uint4*>(tile_ptr<DH>(sV, key, 2 * pc)) = lo;
+                *reinterpret_cast<uint4*>(tile_ptr<DH>(sV, key, 2 * pc + 1)) = hi;
+            }
+        } else {
 #pragma unroll 4
         for (int i = lane; i < KT * CH; i += 32) {
             const int key = i / CH, c = i % CH;
@@ -86,6 +151,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnArgs a) {
         }
         cp_async_commit();
         cp_async_wait<0>();
+        }
         __syncwarp();
 
         // S = Q K^T: 16 rows x 32 keys
@@ -99,8 +165,13 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnArgs a) {
                 uint32_t kb[4];
                 const int tok = nt * 16 + ((lane >> 4) << 3) + (lane & 7);
                 ldsm_x4(kb, tile_ptr<DH>(sK, tok, kk * 2 + ((lane >> 3) & 1)));
-                mma_bf16(s[2 * nt], qa[kk], kb[0], kb[1]);
-                mma_bf16(s[2 * nt + 1], qa[kk], kb[2], kb[3]);
+                if constexpr (FP8) {
+                    mma_f16(s[2 * nt], qa[kk], kb[0], kb[1]);
+                    mma_f16(s[2 * nt + 1], qa[kk], kb[2], kb[3]);
+                } else {
+                    mma_bf16(s[2 * nt], qa[kk], kb[0], kb[1]);
+                    mma_bf16(s[2 * nt + 1], qa[kk], kb[2], kb[3]);
+                }
             }
         }
         // scale, soft-cap, mask the keys past the end, online softmax (scores in natural-log units, as the combine expects)
@@ -147,17 +218,29 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnArgs a) {
 #pragma unroll
         for (int kt = 0; kt < KT / 16; ++kt) {
             uint32_t pa[4];
-            pa[0] = pack_bf16(s[2 * kt][0], s[2 * kt][1]);
-            pa[1] = pack_bf16(s[2 * kt][2], s[2 * kt][3]);
-            pa[2] = pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]);
-            pa[3] = pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3]);
+            if constexpr (FP8) {
+                pa[0] = pack_f16(s[2 * kt][0], s[2 * kt][1]);
+                pa[1] = pack_f16(s[2 * kt][2], s[2 * kt][3]);
+                pa[2] = pack_f16(s[2 * kt + 1][0], s[2 * kt + 1][1]);
+                pa[3] = pack_f16(s[2 * kt + 1][2], s[2 * kt + 1][3]);
+            } else {
+                pa[0] = pack_bf16(s[2 * kt][0], s[2 * kt][1]);
+                pa[1] = pack_bf16(s[2 * kt][2], s[2 * kt][3]);
+                pa[2] = pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]);
+                pa[3] = pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3]);
+            }
 #pragma unroll
             for (int dt = 0; dt < DH / 16; ++dt) {
                 uint32_t vb[4];
                 const int tok = kt * 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
                 ldsm_x4_t(vb, tile_ptr<DH>(sV, tok, dt * 2 + (lane >> 4)));
-                mma_bf16(o[2 * dt], pa, vb[0], vb[1]);
-                mma_bf16(o[2 * dt + 1], pa, vb[2], vb[3]);
+                if constexpr (FP8) {
+                    mma_f16(o[2 * dt], pa, vb[0], vb[1]);
+                    mma_f16(o[2 * dt + 1], pa, vb[2], vb[3]);
+                } else {
+                    mma_bf16(o[2 * dt], pa, vb[0], vb[1]);
+                    mma_bf16(o[2 * dt + 1], pa, vb[2], vb[3]);
+                }
             }
         }
         __syncwarp();                                   // every lane is done with the tiles before the next chunk lands
@@ -247,7 +330,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnArgs a) {
     }
 }
 
-template <int DH, int CS>
+template <int DH, int CS, bool FP8 = false>
 static int launch_decode_mma(const AttnArgs& a, cudaStream_t s) {
     // the query tile, four warps' K and V tiles; the merge buffers reuse them (4 * 16 * DH floats, and with a cluster
     // this CTA's finished partial behind them)
@@ -256,12 +339,12 @@ static int launch_decode_mma(const AttnArgs& a, cudaStream_t s) {
     const size_t smem = stage > merge ? stage : merge;
     static bool configured = false;
     if (!configured) {
-        TSB_CHECK_CUDA(cudaFuncSetAttribute(attn_decode_mma_kernel<DH, CS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        if (CS > 8) TSB_CHECK_CUDA(cudaFuncSetAttribute(attn_decode_mma_kernel<DH, CS>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+        TSB_CHECK_CUDA(cudaFuncSetAttribute(attn_decode_mma_kernel<DH, CS, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (CS > 8) TSB_CHECK_CUDA(cudaFuncSetAttribute(attn_decode_mma_kernel<DH, CS, FP8>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
         configured = true;
     }
     if constexpr (CS == 0) {
-        TSB_CHECK_CUDA(tsb_launch(attn_decode_mma_kernel<DH, 0>, dim3(a.splits, a.Hkv, a.B), dim3(128), smem, s, a));
+        TSB_CHECK_CUDA(tsb_launch(attn_decode_mma_kernel<DH, 0, FP8>, dim3(a.splits, a.Hkv, a.B), dim3(128), smem, s, a));
     } else {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(a.splits, a.Hkv, a.B);
@@ -277,7 +360,7 @@ static int launch_decode_mma(const AttnArgs& a, cudaStream_t s) {
         at[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = at;
         cfg.numAttrs = tsb_pdl_enabled() ? 2 : 1;
-        TSB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<DH, CS>, a));
+        TSB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<DH, CS, FP8>, a));
     }
     return TSB_OK;
 }
@@ -306,4 +389,9 @@ int tsb_attn_decode_mma_launch(const AttnArgs& a, cudaStream_t s, bool* merged) 
     if (cl && a.splits == 8) return a.Dh == 64 ? launch_decode_mma<64, 8>(a, s) : launch_decode_mma<128, 8>(a, s);
     if (cl) return a.Dh == 64 ? launch_decode_mma<64, 16>(a, s) : launch_decode_mma<128, 16>(a, s);
     return a.Dh == 64 ? launch_decode_mma<64, 0>(a, s) : launch_decode_mma<128, 0>(a, s);
+}
+
+// The same split kernel on e4m3 pages (`k_cache` / `v_cache` point at bytes); the caller launches the combine.
+int tsb_attn_decode_mma_fp8_launch(const AttnArgs& a, cudaStream_t s) {
+    return a.Dh == 64 ? launch_decode_mma<64, 0, true>(a, s) : launch_decode_mma<128, 0, true>(a, s);
 }

@@ -286,6 +286,14 @@ extern "C" int tsb_attn_decode_fp8(const AttnArgs* args, void* stream) {
     if (a.B == 0) return TSB_OK;
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
+    // head sizes 64 / 128 with up to 16 query heads per KV head: the tensor-core split kernel (attention_decode_mma.cu)
+    static const bool mma_on = []() { const char* e = getenv("TSB_ATTN_MMA"); return !e || atoi(e) != 0; }();
+    if (mma_on && tsb_attn_decode_mma_supported(a)) {
+        rc = tsb_attn_decode_mma_fp8_launch(a, s);
+        if (rc != TSB_OK) return rc;
+        TSB_CHECK_LAUNCH();
+        return tsb_attn_combine(&a, stream);
+    }
     switch (a.Dh) {
     case 64: rc = launch_fp8_g<64>(a, s); break;
     case 128: rc = launch_fp8_g<128>(a, s); break;

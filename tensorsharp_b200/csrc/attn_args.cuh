@@ -36,3 +36,4 @@ struct AttnArgs {
 // per KV head); the caller launches the combine unless `*merged` comes back true (splits merged by a thread-block cluster).
 bool tsb_attn_decode_mma_supported(const AttnArgs& a);
 int tsb_attn_decode_mma_launch(const AttnArgs& a, cudaStream_t s, bool* merged);
+int tsb_attn_decode_mma_fp8_launch(const AttnArgs& a, cudaStream_t s);      // e4m3 pages; the caller launches the combine
