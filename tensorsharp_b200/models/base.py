@@ -488,6 +488,33 @@ class ModelBase:
             out.append(("fused decode step", x.status_word))
         return out
 
+    def recover_exchanges(self) -> int:
+        """Recovery after a bounded device wait gave up (``ExchangeTimeoutError``): fail the request, then call this on
+        every rank at the same point.  It drops every in-kernel exchange of this model (mailboxes, sequence-parallel
+        regions, the context-parallel ring, the fused decode step) together with their symmetric buffers, so that the
+        next call that needs one sets it up afresh across the ranks; forgets the captured graphs, which point into the
+        old buffers; clears the status words; and empties the KV pool's sequences (a step that gave up left rows of
+        unknown content).  The weights stay where they are.  Returns the number of exchange objects closed."""
+        closed = 0
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        for name in ("_tpx", "_tpseq", "_cpa", "_mega"):
+            x = self.__dict__.pop(name, None)
+            for e in (list(x.values()) if isinstance(x, dict) else [x]):
+                if e is not None and e is not False and hasattr(e, "close"):
+                    try:
+                        e.close()
+                    finally:
+                        closed += 1
+        self.__dict__.pop("_steppers", None)
+        self.__dict__.pop("_status_poll", None)
+        self.__dict__["_cp_ctx"] = None
+        for _, word in self.status_sources():           # what is left: the GEMM pipeline's word
+            word.zero_()
+        if self._default_seq is not None:
+            self.reset_kv_cache()
+        return closed
+
     def raise_on_status(self, names, values) -> None:
         from ..parallel.errors import ExchangeTimeoutError
         for name, v in zip(names, values):

@@ -66,6 +66,12 @@ class LeaderModel:
         self._tell("warm_up")
         self._model.warm_up_kernels()
 
+    def recover_exchanges(self) -> int:
+        """After an ``ExchangeTimeoutError``: every rank drops its in-kernel exchanges and symmetric buffers at the same
+        point and rebuilds them on next use (ModelBase.recover_exchanges); weights stay resident, the caches are reset."""
+        self._tell("recover")
+        return self._model.recover_exchanges()
+
     # ------------------------------------------------------------------ cache and sequences
     def reset_kv_cache(self) -> None:
         self._tell("reset")
@@ -192,6 +198,8 @@ def follower_main(comm, create: Optional[Callable] = None, device=None) -> int:
             model.set_vision_embeddings(args[0].to(model.device), args[1])
         elif op == "warm_up":
             model.warm_up_kernels()
+        elif op == "recover":
+            model.recover_exchanges()
         elif op == "reset":
             model.reset_kv_cache()
         elif op == "truncate":

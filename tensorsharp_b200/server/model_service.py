@@ -15,6 +15,7 @@ sessions costs nothing until the pool is full (then the least recently used one 
 """
 from __future__ import annotations
 
+import contextlib
 import os
 import time
 from typing import Iterator, List, NamedTuple, Optional, Sequence
@@ -447,6 +448,34 @@ class ModelService:
         self._model.reset_kv_cache()
         return tokens[trim:trim + kept]
 
+    # ------------------------------------------------------------------ recovery
+    @contextlib.contextmanager
+    def _exchange_guard(self):
+        """A bounded device-side wait that gave up surfaces as ``ExchangeTimeoutError`` from a model call.  The request
+        fails (the caller sees the error), and before the next one the in-kernel exchanges are torn down and rebuilt
+        on every rank, the caches emptied and the sessions' bookkeeping reset; the weights stay loaded."""
+        from ..parallel.errors import ExchangeTimeoutError
+        try:
+            yield
+        except ExchangeTimeoutError as ex:
+            self.recover_after_exchange_failure(ex)
+            raise
+
+    def recover_after_exchange_failure(self, ex=None) -> None:
+        self._log.warning(Ev.ChatFailed, "exchange failure ({Error}): rebuilding the exchanges, resetting caches", Error=str(ex))
+        for session in {id(x): x for x in [self._active, self._intrinsic, *self._resident] if x is not None}.values():
+            session.kv_cache.reset()
+            session.tracked_history.clear()
+            if session.seq is not None:
+                self._drop_residency(session)
+        recover = getattr(self._model, "recover_exchanges", None)
+        if recover is not None:
+            try:
+                closed = recover()
+                self._log.info(Ev.SessionReset, "exchanges dropped: {Closed}; they are set up again on next use", Closed=closed)
+            except Exception as err:                       # a rank that cannot rebuild leaves the failure for the watchdog
+                self._log.error(Ev.ChatFailed, "recovery failed: {Error}", Error=str(err))
+
     # ------------------------------------------------------------------ token loop
     def _token_loop(self, session: ChatSession, logits, max_tokens: int, cfg: SamplingConfig, cancel,
                     stop_before_emit: bool, state: dict) -> Iterator[StreamItem]:
@@ -528,10 +557,11 @@ class ModelService:
             tokens = self._truncate_prompt_to_context(active, tokens, max_tokens)
             n_prompt = len(tokens)
             t0 = time.perf_counter_ns()
-            logits, reused = self._prepare_for_generation(active, tokens)
-            prompt_ns = time.perf_counter_ns() - t0
             state = {"generated": []}
-            yield from self._token_loop(active, logits, max_tokens, cfg, cancel, False, state)
+            with self._exchange_guard():
+                logits, reused = self._prepare_for_generation(active, tokens)
+                prompt_ns = time.perf_counter_ns() - t0
+                yield from self._token_loop(active, logits, max_tokens, cfg, cancel, False, state)
             total_ns = time.perf_counter_ns() - t0
             generated = state["generated"]
             text = bytes(state.get("raw", b"")).decode("utf-8", errors="replace")
@@ -585,11 +615,12 @@ class ModelService:
             self.reset_session(active)
             t0 = time.perf_counter_ns()
             queued = self._mm_queue(0)
-            logits = self._forward_prompt_prefill(list(tokens), allow_chunking=not queued)
-            active.kv_cache.record_append(list(tokens), logits)
-            prompt_ns = time.perf_counter_ns() - t0
             state = {"generated": []}
-            yield from self._token_loop(active, logits, max_tokens, cfg, cancel, True, state)
+            with self._exchange_guard():
+                logits = self._forward_prompt_prefill(list(tokens), allow_chunking=not queued)
+                active.kv_cache.record_append(list(tokens), logits)
+                prompt_ns = time.perf_counter_ns() - t0
+                yield from self._token_loop(active, logits, max_tokens, cfg, cancel, True, state)
             total_ns = time.perf_counter_ns() - t0
             generated = state["generated"]
             text = bytes(state.get("raw", b"")).decode("utf-8", errors="replace")
