@@ -498,6 +498,11 @@ class ModelBase:
         closed = 0
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
+        # no rank unmaps or frees a buffer while another rank's kernels may still store into it: every rank has drained
+        # its own device above, and nobody goes on before all of them have
+        for comm in (self.comm, self.cp_comm):
+            if comm is not None and getattr(comm, "size", 1) > 1:
+                comm.barrier()
         for name in ("_tpx", "_tpseq", "_cpa", "_mega"):
             x = self.__dict__.pop(name, None)
             for e in (list(x.values()) if isinstance(x, dict) else [x]):
