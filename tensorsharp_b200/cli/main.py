@@ -492,9 +492,21 @@ def run_jsonl_batch(model, path: str, output_file: Optional[str], default_max_to
         except Exception as e:                                  # one bad request must not end the batch
             log.error(Ev.CliFailed, "batch request {Index} id={Id} failed: {Error}", exc=e, Index=idx + 1, Id=rid, Error=str(e))
             results.append(dotnet_json({"id": rid, "error": str(e)}))
+            recover_if_exchange_failed(model, e, log)
     log.info(Ev.CliCompleted, "batch completed: {Completed}/{Total} in {Seconds:.1f}s", Completed=done, Total=len(lines),
              Seconds=time.perf_counter() - t_all)
     return _emit_jsonl_results(results, output_file, con)
+
+
+def recover_if_exchange_failed(model, error, log) -> bool:
+    """A bounded device-side wait that gave up ends a request with ``ExchangeTimeoutError``; the requests that follow
+    need the exchanges rebuilt and the cache emptied (ModelBase.recover_exchanges; the weights stay loaded)."""
+    from ..parallel.errors import ExchangeTimeoutError
+    if not isinstance(error, ExchangeTimeoutError) or not hasattr(model, "recover_exchanges"):
+        return False
+    closed = model.recover_exchanges()
+    log.warning(Ev.CliFailed, "exchange failure: {Closed} exchange objects dropped, they are rebuilt on next use", Closed=closed)
+    return True
 
 
 def _emit_jsonl_results(results: List[str], output_file: Optional[str], con: Console) -> int:

@@ -110,3 +110,18 @@ def test_leader_tells_the_followers_to_recover(monkeypatch):
         device = torch.device("cpu")
     n = R.follower_main(Comm(), create=lambda path, dev, **kw: follower_shard)
     assert n == 4 and follower_shard.calls == ["recover", "reset"]
+
+
+def test_cli_helper_recovers_only_after_an_exchange_failure():
+    from tensorsharp_b200.cli.main import recover_if_exchange_failed
+    from tensorsharp_b200.runtime.logging import NULL_LOGGER
+
+    class M:
+        n = 0
+
+        def recover_exchanges(self):
+            self.n += 1
+            return 1
+    m = M()
+    assert recover_if_exchange_failed(m, ValueError("bad request"), NULL_LOGGER) is False and m.n == 0
+    assert recover_if_exchange_failed(m, ExchangeTimeoutError("sequence-parallel prefill exchange", 10), NULL_LOGGER) is True and m.n == 1
