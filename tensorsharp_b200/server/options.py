@@ -108,6 +108,23 @@ def _pos_int(s: Optional[str]) -> Optional[int]:
     return v if v > 0 else None
 
 
+def _listener_from_urls(urls: Optional[str]):
+    """Host and port of the first ``http://`` entry of an ``ASPNETCORE_URLS`` value (``http://0.0.0.0:8080;...``), the
+    listener setting the reference's host process reads; ``(None, None)`` when there is none.  ``*`` and ``+`` mean
+    every interface."""
+    for part in (urls or "").split(";"):
+        part = part.strip()
+        if not part.lower().startswith("http://"):
+            continue
+        rest = part[7:].split("/", 1)[0]
+        host, _, port = rest.rpartition(":") if ":" in rest and not rest.endswith("]") else (rest, "", "")
+        host = host.strip("[]")
+        if host in ("*", "+", ""):
+            host = "0.0.0.0"
+        return host, _pos_int(port) or 80
+    return None, None
+
+
 def _pfloat(flag: str, s: str) -> float:
     try:
         return float(s)
@@ -246,8 +263,8 @@ def build_options(args: Sequence[str], base_directory: str, env=None,
         supported_backends=supported, default_web_max_tokens=max_tokens, max_text_file_chars=max_text,
         upload_directory=upload_dir, log_directory=log_dir, file_logging_enabled=env.get("TENSORSHARP_LOG_FILE") != "0",
         default_sampling_config=resolve_default_sampling(p["sampling"], p["stop"], env),
-        host=p.get("host") or env.get("TENSORSHARP_HOST") or "127.0.0.1",
-        port=int(p.get("port") or _pos_int(env.get("PORT")) or 5000),
+        host=p.get("host") or env.get("TENSORSHARP_HOST") or _listener_from_urls(env.get("ASPNETCORE_URLS"))[0] or "127.0.0.1",
+        port=int(p.get("port") or _pos_int(env.get("PORT")) or _listener_from_urls(env.get("ASPNETCORE_URLS"))[1] or 5000),
         max_context=p.get("max_context"), max_sessions=int(p.get("max_sessions") or 1),
         max_batch=int(p.get("max_batch") or _pos_int(env.get("TENSORSHARP_MAX_BATCH")) or 1),
         replicas=int(p.get("replicas") or _pos_int(env.get("TENSORSHARP_REPLICAS")) or 1),

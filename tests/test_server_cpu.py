@@ -223,6 +223,15 @@ def test_build_options_flags_env_and_errors(tmp_path):
     assert o.startup_mmproj_path == os.path.join(os.path.dirname(os.path.abspath("m/x.gguf")), "proj.gguf")
     assert o.default_web_max_tokens == 77 and o.max_text_file_chars == 123 and not o.file_logging_enabled
     assert build_options([], base, env={"MAX_TOKENS": "5"}).default_web_max_tokens == 5
+    # listener: --host / --port, then TENSORSHARP_HOST / PORT, then the first http:// entry of ASPNETCORE_URLS
+    o = build_options([], base, env={"ASPNETCORE_URLS": "https://+:5001;http://*:8088"})
+    assert (o.host, o.port) == ("0.0.0.0", 8088)
+    o = build_options(["--port", "7000"], base, env={"ASPNETCORE_URLS": "http://localhost:8088", "PORT": "9"})
+    assert (o.host, o.port) == ("localhost", 7000)
+    o = build_options([], base, env={"ASPNETCORE_URLS": "http://localhost:8088", "PORT": "9", "TENSORSHARP_HOST": "10.0.0.1"})
+    assert (o.host, o.port) == ("10.0.0.1", 9)
+    o = build_options([], base, env={})
+    assert (o.host, o.port) == ("127.0.0.1", 5000)
 
 
 def test_backend_catalog():
