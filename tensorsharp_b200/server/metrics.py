@@ -25,6 +25,7 @@ class ServingMetrics:
             self.kv_reused_tokens = 0
             self.prefill_seconds = 0.0
             self.decode_seconds = 0.0
+            self.exchange_recoveries = 0
             self.http: Dict[str, int] = {}
 
     def record_generation(self, prompt_tokens: int, generated: int, reused: int, prompt_ns: int, eval_ns: int,
@@ -37,6 +38,10 @@ class ServingMetrics:
             self.kv_reused_tokens += int(reused)
             self.prefill_seconds += prompt_ns / 1e9
             self.decode_seconds += eval_ns / 1e9
+
+    def record_exchange_recovery(self) -> None:
+        with self._lock:
+            self.exchange_recoveries += 1
 
     def record_http(self, client: Optional[str], status: int) -> None:
         key = f"{client or 'other'}:{status // 100}xx"
@@ -59,6 +64,8 @@ class ServingMetrics:
             metric("tensorsharp_kv_reused_tokens_total", "counter", "Prompt tokens served from a session's KV cache.", self.kv_reused_tokens)
             metric("tensorsharp_prefill_seconds_total", "counter", "Time spent preparing prompts.", f"{self.prefill_seconds:.6f}")
             metric("tensorsharp_decode_seconds_total", "counter", "Time spent in token loops.", f"{self.decode_seconds:.6f}")
+            metric("tensorsharp_exchange_recoveries_total", "counter",
+                   "Requests ended by a device-side wait that gave up, after which the exchanges were rebuilt.", self.exchange_recoveries)
             for key in sorted(self.http):
                 client, cls = key.split(":")
                 metric("tensorsharp_http_responses_total", "counter", "HTTP responses by client kind and status class.",

@@ -463,6 +463,7 @@ class ModelService:
 
     def recover_after_exchange_failure(self, ex=None) -> None:
         self._log.warning(Ev.ChatFailed, "exchange failure ({Error}): rebuilding the exchanges, resetting caches", Error=str(ex))
+        METRICS.record_exchange_recovery()
         for session in {id(x): x for x in [self._active, self._intrinsic, *self._resident] if x is not None}.values():
             session.kv_cache.reset()
             session.tracked_history.clear()

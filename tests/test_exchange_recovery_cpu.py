@@ -70,6 +70,8 @@ def test_service_fails_the_request_recovers_and_serves_the_next_one():
     with pytest.raises(ExchangeTimeoutError):
         list(svc.chat_stream_with_metrics(hist2, 32, sampling=GREEDY))
     assert recovered == [1]
+    from tensorsharp_b200.server.metrics import METRICS
+    assert METRICS.exchange_recoveries >= 1 and "tensorsharp_exchange_recoveries_total" in METRICS.render()
     assert svc._intrinsic.kv_cache.count == 0 and not svc._intrinsic.tracked_history       # nothing of the failed turn is trusted
     # the service keeps serving: same weights, fresh cache (a full prefill, no prefix reuse)
     model.forward = plain_forward
