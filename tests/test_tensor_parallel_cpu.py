@@ -215,6 +215,11 @@ def _serve_worker(rank, world, port, path, out_path, mode="tp"):
         hist += [ChatMessage(role="assistant", content=first), ChatMessage(role="user", content="and again")]
         items = list(svc.chat_stream_with_metrics(hist, 5, sampling=greedy))
         second = "".join(i.piece for i in items if i.piece)
+        # recovery after an exchange failure (injected here: no device is involved): every rank drops its exchanges and
+        # empties its cache at the same point, and the same chat gives the same text again
+        from tensorsharp_b200.parallel.errors import ExchangeTimeoutError
+        svc.recover_after_exchange_failure(ExchangeTimeoutError("injected", 1))
+        again = "".join(svc.chat_stream([ChatMessage(role="user", content="Hello there")], 6, sampling=greedy))
         # two resident chats: sequences are created, bound and freed on every rank alike
         from tensorsharp_b200.server.sessions import SessionManager
         svc2 = ModelService(model_factory=leader_factory(comm), max_context=256, max_sessions=2)
@@ -229,7 +234,7 @@ def _serve_worker(rank, world, port, path, out_path, mode="tp"):
         svc2.dispose_session(sb)
         svc2.close()
         shutdown_followers(comm)
-        torch.save((first, second, ta, tb, ta2), f"{out_path}.0")
+        torch.save((first, second, ta, tb, ta2, again), f"{out_path}.0")
     finally:
         dist.destroy_process_group()
 
@@ -256,6 +261,7 @@ def test_front_end_on_rank0_with_follower_shards(tiny_qwen3_path, tmp_path, mode
     assert got[:2] == (first, second)
     assert got[2] == first[:len(got[2])] or len(got[2]) > 0        # same prompt, fewer tokens: a prefix of the first answer
     assert all(isinstance(t, str) for t in got[2:])
+    assert got[5] == first                      # after the recovery on both ranks
     assert torch.load(f"{out}.1") > 10          # the follower executed the leader's commands
 
 
